@@ -1,0 +1,304 @@
+#!/usr/bin/env python
+"""Benchmark of the int8 MATMUL hot path (tb200 C ABI) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload: batched int8 MATMUL, A[64,1024,4096] x B[64,4096,1024] -> int32, A_zp = 3, B_zp = -2, synthetic
+uniform int8 operands from a fixed seed.  One step = one tb200_matmul call over the whole batch (zero-point row /
+column sums + the tensor-core GEMM).  The operands (537 MB) exceed the 126 MB L2, so no flush is needed between
+timed steps.  With N > 1 (torchrun) every rank runs the same workload on its own GPU (the batch dimension shards
+with no exchange), `value` is the total over ranks divided by the slowest rank's device time.
+
+Prints one JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_BATCH, H, C, W = 64, 1024, 4096, 1024
+A_ZP, B_ZP = 3, -2
+OPS_PER_STEP = 2.0 * N_BATCH * H * C * W          # 549.76 GOP
+ALG_BYTES_PER_STEP = N_BATCH * (H * C + C * W + 4 * H * W)
+SEED = 20251125 + 1
+METRIC = "int8 MATMUL throughput, 64x[1024x4096]x[4096x1024], A_zp=3 B_zp=-2, int32 out"
+WORKLOAD = "matmul_int8_64x1024x4096x1024_zp3_-2"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"bf16_burst": p["bf16_tflops"], "bf16_sustained": p["bf16_tflops_sustained"], "hbm": p["hbm_gbs"],
+                "source": "measured"}
+    return {"bf16_burst": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_operands(rank):
+    r = np.random.default_rng(SEED + 1000 * rank)
+    a = r.integers(-128, 128, size=(N_BATCH, H, C), dtype=np.int8)
+    b = r.integers(-128, 128, size=(N_BATCH, C, W), dtype=np.int8)
+    return a, b
+
+
+def cpu_port_rate(threads, target_seconds, a, b):
+    """Times the CPU restatement of the reference's MATMUL on a bounded sample; returns (TOPS, sample text)."""
+    from oracle import oracle as orc
+    t0 = time.perf_counter()
+    orc.matmul(a[:1], b[:1], A_ZP, B_ZP, nthreads=threads)
+    t1 = time.perf_counter() - t0
+    nb = int(max(1, min(N_BATCH, round(target_seconds / max(t1, 1e-3)))))
+    t0 = time.perf_counter()
+    orc.matmul(a[:nb], b[:nb], A_ZP, B_ZP, nthreads=threads)
+    dt = time.perf_counter() - t0
+    ops = 2.0 * nb * H * C * W
+    return ops / dt / 1e12, "%d of %d batches (%.1f s)" % (nb, N_BATCH, dt), nb, dt
+
+
+def run_reference(args, rank, world):
+    """The reference's CPU algorithm for this path (its Eigen build cannot be compiled here, so the line-faithful
+    C restatement stands in), on all host threads, on a bounded sample of the same workload per step."""
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+    threads = orc.num_procs()
+    a, b = make_operands(0)
+    nb = 2
+    for _ in range(args.warmup):
+        orc.matmul(a[:1], b[:1], A_ZP, B_ZP, nthreads=threads)
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        lo = (s * nb) % N_BATCH
+        orc.matmul(a[lo:lo + nb], b[lo:lo + nb], A_ZP, B_ZP, nthreads=threads)
+    dt = time.perf_counter() - t0
+    ops = 2.0 * nb * H * C * W * args.steps
+    tops = ops / dt / 1e12
+    sample = "%d of %d batches per step" % (nb, N_BATCH)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="tb200")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import reference_model_b200 as tb
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    a_np, b_np = make_operands(rank)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ctx = tb.Context(local_rank, stream.cuda_stream)
+        a_pin = torch.from_numpy(a_np).pin_memory()
+        b_pin = torch.from_numpy(b_np).pin_memory()
+        out_pin = torch.empty((N_BATCH, H, W), dtype=torch.int32).pin_memory()
+        ta = ctx.empty(tb.DType.INT8, (N_BATCH, H, C))
+        tbm = ctx.empty(tb.DType.INT8, (N_BATCH, C, W))
+        to = ctx.empty(tb.DType.INT32, (N_BATCH, H, W))
+        lib = ctx.lib
+        import ctypes
+
+        def upload():
+            lib.tb200_tensor_upload(ctx.handle, ta.handle, ctypes.c_void_p(a_pin.data_ptr()), a_pin.numel())
+            lib.tb200_tensor_upload(ctx.handle, tbm.handle, ctypes.c_void_p(b_pin.data_ptr()), b_pin.numel())
+
+        def step():
+            ctx.matmul(ta, tbm, to, A_ZP, B_ZP)
+
+        def download():
+            return lib.tb200_tensor_download(ctx.handle, to.handle, ctypes.c_void_p(out_pin.data_ptr()),
+                                             out_pin.numel() * 4)
+
+        upload()
+        for _ in range(args.warmup):
+            step()
+        st = ctx.sync()
+        assert st == tb.Status.OK, ctx.last_error()
+        kernel_name = ctx.last_kernel()
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        # ---- device-resident timing
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        ctx.timer_enable(True)
+        ctx.timer_read()
+        launches0 = ctx.launch_count()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        gemm_ms, gemm_n = ctx.timer_read()
+        ctx.timer_enable(False)
+        launches = ctx.launch_count() - launches0
+        clocks = sampler.stop() if rank == 0 else None
+        st = ctx.sync()
+        assert st == tb.Status.OK, ctx.last_error()
+
+        # ---- end to end through the C ABI with host buffers: upload, matmul, download every step
+        for _ in range(1):
+            upload(); step(); download()
+        barrier()
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record(stream)
+        for _ in range(args.e2e_steps):
+            upload()
+            step()
+            st = download()
+            assert st == 0
+        e3.record(stream)
+        barrier()
+        e2e_ms = e2.elapsed_time(e3)
+
+        times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(times[0]), float(times[1])
+
+    if rank == 0:
+        peaks = measured_peaks()
+        total_ops = OPS_PER_STEP * args.steps * world
+        value = total_ops / (ms * 1e-3) / 1e12
+        e2e_value = OPS_PER_STEP * args.e2e_steps * world / (e2e_ms * 1e-3) / 1e12
+        gemm_avg_ms = gemm_ms / max(gemm_n, 1)
+        achieved = OPS_PER_STEP / (gemm_avg_ms * 1e-3) / 1e12
+        # int8 dense peak is not in MEASURED_PEAKS.json: twice the measured bf16 figure stands in for it; the
+        # sustained figure applies because the kernel is timed inside a seconds-long back-to-back loop
+        long_loop = ms > 1000.0
+        peak = 2.0 * (peaks["bf16_sustained"] if long_loop else peaks["bf16_burst"])
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "tc_gemm_i8_matmul_traffic.json")
+        if os.path.exists(tpath):
+            with open(tpath) as f:
+                traffic = json.load(f).get("dram_bytes_per_launch_full_workload")
+        cpu_threads = None
+        try:
+            from oracle import oracle as orc
+            cpu_threads = orc.num_procs()
+            cpu_tops, sample, _, _ = cpu_port_rate(cpu_threads, 10.0, a_np, b_np)
+            cpu_baseline = {"value": cpu_tops, "unit": "TOPS", "cores": cpu_threads, "kind": "port", "sample": sample}
+        except Exception as exc:  # the baseline is a report, never a dependency of the GPU path
+            cpu_baseline = {"value": None, "unit": "TOPS", "cores": cpu_threads, "kind": "port", "sample": "failed: %s" % exc}
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "batches_per_gpu": N_BATCH, "H": H, "C": C, "W": W,
+                       "l2": "operands (537 MB) larger than L2, no flush", "kernel": kernel_name},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": int(a_pin.numel() + b_pin.numel()),
+                    "d2h_bytes_per_step": int(out_pin.numel() * 4), "steps": args.e2e_steps,
+                    "ms_per_step": e2e_ms / args.e2e_steps},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s",
+                         "frac": achieved / peak, "traffic": traffic, "kernel": kernel_name,
+                         "kernel_ms": gemm_avg_ms, "launches_timed": gemm_n,
+                         "peak_source": "2 x %s bf16 %s (int8 peak not measured on this pool); nominal dense int8 is 4500"
+                                        % (peaks["source"], "sustained" if long_loop else "burst"),
+                         "frac_of_nominal_int8": achieved / 4500.0,
+                         "algorithmic_bytes_per_launch": ALG_BYTES_PER_STEP},
+            "cpu_baseline": cpu_baseline,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

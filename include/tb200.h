@@ -1,0 +1,219 @@
+/*
+ * tb200 — C ABI of the B200 (sm_100a) compute path for the TOSA reference model's
+ * CONV2D / DEPTHWISE_CONV2D / MATMUL / RESCALE / CLAMP / ADD / MAX_POOL2D / AVG_POOL2D nodes.
+ *
+ * This is the boundary a reference-side adapter binds: a GraphNode subclass's eval()
+ * (reference_model/src/graph_node.h:176-179) or a CustomOpInterface::eval()
+ * (reference_model/include/custom_op_interface.h:25-35) calls one entry point per node.
+ * Plain C: opaque handles, pointers and sizes only; nothing throws or aborts across it.
+ *
+ * Conventions
+ *  - Tensors are row-major in TOSA shape order at their true element width (int8 is 1 byte,
+ *    fp16/bf16 2 bytes): NHWC activations, OHWI CONV2D weights, [KH,KW,C,M] DEPTHWISE weights,
+ *    [N,H,C] x [N,C,W] MATMUL operands.  This is the layout of every external buffer of the
+ *    reference (reference_model/src/tensor.cpp:2157-2179), not its internal column-major Eigen storage.
+ *  - Zero points are passed as scalars; the adapter reads element (0) of the reference's rank-1
+ *    zero-point operands (reference_model/src/ops/tensor_ops.cpp:804,810).
+ *  - Every call returns a tb200_status.  Shape / attribute violations (the reference's ERROR_IF)
+ *    are detected on the host before any launch and return TB200_ERROR.  Data-dependent REQUIRE
+ *    failures (RESCALE range checks, int32 ADD overflow) are recorded by the kernels in a device
+ *    status word and reported by tb200_sync / tb200_tensor_download as TB200_UNPREDICTABLE.
+ *  - All work is asynchronous on the context's stream.  Calls on one context must be serialised
+ *    by the caller (the reference is single-threaded, reference_model/src/model_runner.cpp:22-23).
+ */
+#ifndef TB200_H
+#define TB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C"
+{
+#endif
+
+#if defined(__GNUC__)
+#define TB200_API __attribute__((visibility("default")))
+#else
+#define TB200_API
+#endif
+
+    /* Mirrors GraphStatus {TOSA_VALID, TOSA_UNPREDICTABLE, TOSA_ERROR}
+     * (reference_model/include/graph_status.h:18-23); TB200_INTERNAL covers CUDA / driver failures,
+     * which the adapter should surface as TOSA_ERROR. */
+    typedef enum tb200_status
+    {
+        TB200_OK            = 0,
+        TB200_UNPREDICTABLE = 1,
+        TB200_ERROR         = 2,
+        TB200_INTERNAL      = 3
+    } tb200_status;
+
+    /* Same numeric values as tosa_datatype_t (reference_model/include/types.h:27-44). */
+    typedef enum tb200_dtype
+    {
+        TB200_BF16   = 0,
+        TB200_FP16   = 2,
+        TB200_FP32   = 3,
+        TB200_INT16  = 4,
+        TB200_INT32  = 5,
+        TB200_INT8   = 8,
+        TB200_UINT16 = 9,
+        TB200_UINT8  = 10
+    } tb200_dtype;
+
+    /* RoundingMode of the RESCALE attribute (reference_model/src/ops/type_conversion.cpp:229-231). */
+    typedef enum tb200_rounding
+    {
+        TB200_SINGLE_ROUND  = 0,
+        TB200_DOUBLE_ROUND  = 1,
+        TB200_INEXACT_ROUND = 2
+    } tb200_rounding;
+
+    typedef struct tb200_ctx tb200_ctx;
+    typedef struct tb200_tensor tb200_tensor;
+
+    /* ---- context ------------------------------------------------------------------------------ */
+
+    /* Creates a context on CUDA device `device`.  `stream` is a cudaStream_t the caller owns, or NULL
+     * to let the context create its own.  One context per (process, device); stands where the reference
+     * has its process-wide model state (reference_model/src/model_runner_impl.cpp:24-28). */
+    TB200_API tb200_status tb200_ctx_create(int device, void* stream, tb200_ctx** out);
+    TB200_API tb200_status tb200_ctx_destroy(tb200_ctx* ctx);
+    /* Text of the last error recorded on this context (never NULL). */
+    TB200_API const char* tb200_last_error(const tb200_ctx* ctx);
+    /* Waits for the stream, then reports and clears the device status word: TB200_OK,
+     * TB200_UNPREDICTABLE (a REQUIRE failed in some kernel since the last sync) or TB200_INTERNAL.
+     * Stands where SubgraphTraverser reads the graph status after evaluateAll
+     * (reference_model/src/model_runner_impl.cpp:56-126). */
+    TB200_API tb200_status tb200_sync(tb200_ctx* ctx);
+    /* Number of kernels this context has launched since creation (for accounting in benchmarks). */
+    TB200_API uint64_t tb200_launch_count(const tb200_ctx* ctx);
+    /* Measurement aid with no counterpart in the reference (which has no timers): while enabled, the main
+     * kernel of every CONV2D / MATMUL call (the tensor-core GEMM or the fp32 SGEMM, not its small preparation
+     * kernels) is bracketed by CUDA events on the context's stream.  tb200_timer_read synchronises, returns the
+     * summed device time in milliseconds and the number of bracketed launches since the last read, and clears. */
+    TB200_API tb200_status tb200_timer_enable(tb200_ctx* ctx, int32_t on);
+    TB200_API tb200_status tb200_timer_read(tb200_ctx* ctx, double* total_ms, int32_t* launches);
+
+    /* ---- tensors -------------------------------------------------------------------------------
+     * Device-resident replacements for TensorTemplate<Eigen::Tensor<T,R>> buffers
+     * (reference_model/src/tensor.h:365-440): allocate stands for Tensor::allocate (:380-398),
+     * upload / download for setTensorValue* / getTensorValue* (reference_model/src/tensor.cpp:2157-2179, :3662). */
+    TB200_API tb200_status tb200_tensor_alloc(tb200_ctx* ctx, tb200_dtype dtype, int rank, const int32_t* shape,
+                                              tb200_tensor** out);
+    /* Wraps device memory the caller owns (for hosts that manage device buffers themselves). */
+    TB200_API tb200_status tb200_tensor_wrap(tb200_ctx* ctx, tb200_dtype dtype, int rank, const int32_t* shape,
+                                             void* device_ptr, tb200_tensor** out);
+    TB200_API tb200_status tb200_tensor_free(tb200_ctx* ctx, tb200_tensor* t);
+    /* `host` holds `bytes` = element count x element width, row-major.  Upload is asynchronous when `host`
+     * is pinned; download synchronises the stream and returns the status tb200_sync would. */
+    TB200_API tb200_status tb200_tensor_upload(tb200_ctx* ctx, tb200_tensor* t, const void* host, size_t bytes);
+    TB200_API tb200_status tb200_tensor_download(tb200_ctx* ctx, const tb200_tensor* t, void* host, size_t bytes);
+    TB200_API void* tb200_tensor_data(const tb200_tensor* t);
+    TB200_API size_t tb200_tensor_bytes(const tb200_tensor* t);
+
+    /* ---- fused epilogue ------------------------------------------------------------------------
+     * Lets the host collapse CONV2D/MATMUL -> RESCALE -> CLAMP chains whose intermediates have a single
+     * consumer (reference_model/src/tensor.h:92-100).  NULL means the plain op. */
+    typedef struct tb200_rescale_attr
+    {
+        const tb200_tensor* multiplier; /* INT32 when scale32 else INT16; [C] when per_channel else [1] */
+        const tb200_tensor* shift;      /* INT8; same length as multiplier */
+        int32_t input_zp;
+        int32_t output_zp;
+        int32_t scale32;
+        int32_t rounding_mode; /* tb200_rounding */
+        int32_t per_channel;
+        int32_t input_unsigned;
+        int32_t output_unsigned;
+    } tb200_rescale_attr;
+
+    typedef struct tb200_epilogue
+    {
+        int32_t has_rescale; /* integer paths only: int32 accumulator -> `out` dtype */
+        tb200_rescale_attr rescale;
+        int32_t has_clamp;
+        int32_t clamp_min_i; /* integer outputs */
+        int32_t clamp_max_i;
+        float clamp_min_f; /* floating outputs */
+        float clamp_max_f;
+    } tb200_epilogue;
+
+    /* ---- operators -----------------------------------------------------------------------------*/
+
+    /* CONV2D.  Replaces OpConv2d<In,W,Acc,Out>::eval (reference_model/src/ops/tensor_ops.cpp:723-882) and the
+     * checks of check_conv_attribute (:120-226) / OpConv2d::checkTensorAttributes (:690-720).
+     * input NHWC, weight OHWI, bias [OC] or [1]; pad = {top,bottom,left,right}, stride = {y,x}, dilation = {y,x}.
+     * Supported tuples (in/weight/bias/out): INT8/INT8/INT32/INT32, FP16/FP16/FP16/FP16, BF16/BF16/BF16/BF16,
+     * FP32/FP32/FP32/FP32; floating types accumulate in fp32.  With an epilogue carrying RESCALE the output is
+     * the RESCALE's output dtype. */
+    TB200_API tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
+                                        const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp,
+                                        const int32_t pad[4], const int32_t stride[2], const int32_t dilation[2],
+                                        const tb200_epilogue* epilogue, tb200_tensor* output);
+
+    /* DEPTHWISE_CONV2D.  Replaces OpDepthwiseConv2d::eval (reference_model/src/ops/tensor_ops.cpp:1172-1334).
+     * weight [KH,KW,C,M]; output channel c*M+m. */
+    TB200_API tb200_status tb200_depthwise_conv2d(tb200_ctx* ctx, const tb200_tensor* input,
+                                                  const tb200_tensor* weight, const tb200_tensor* bias,
+                                                  int32_t input_zp, int32_t weight_zp, const int32_t pad[4],
+                                                  const int32_t stride[2], const int32_t dilation[2],
+                                                  const tb200_epilogue* epilogue, tb200_tensor* output);
+
+    /* MATMUL.  Replaces OpMatMul<A,B,Out>::eval (reference_model/src/ops/tensor_ops.cpp:1423-1492, checks :1347-1420).
+     * a [N,H,C], b [N,C,W], output [N,H,W]; INT8xINT8->INT32, FP16/BF16->same or FP32, FP32->FP32 (FFMA, no TF32). */
+    TB200_API tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, const tb200_tensor* b, int32_t a_zp,
+                                        int32_t b_zp, const tb200_epilogue* epilogue, tb200_tensor* output);
+
+    /* RESCALE.  Replaces OpRescale<Rank,In,Out>::eval (reference_model/src/ops/type_conversion.cpp:223-422, checks
+     * :71-154) with QuantUtil::apply_scale_32 / apply_scale_16 (reference_model/src/quant_util.h:45-108). */
+    TB200_API tb200_status tb200_rescale(tb200_ctx* ctx, const tb200_tensor* input, const tb200_rescale_attr* attr,
+                                         tb200_tensor* output);
+
+    /* CLAMP.  Replaces OpClamp<Rank,T> (reference_model/src/ops/activation_funcs.cpp:27-128).  Integer tensors use
+     * min_i/max_i, floating tensors min_f/max_f; nan_ignore selects NanPropagationMode_IGNORE. */
+    TB200_API tb200_status tb200_clamp(tb200_ctx* ctx, const tb200_tensor* input, int32_t min_i, int32_t max_i,
+                                       float min_f, float max_f, int32_t nan_ignore, tb200_tensor* output);
+
+    /* ADD.  Replaces OpAdd<Rank,T> (reference_model/src/ops/ewise_binary.cpp:144-173) including the size-1
+     * broadcast of BinaryNodeBase::broadcast (:81-111).  INT32, FP16, BF16, FP32. */
+    TB200_API tb200_status tb200_add(tb200_ctx* ctx, const tb200_tensor* a, const tb200_tensor* b,
+                                     tb200_tensor* output);
+
+    /* Residual join of a quantized graph in one pass: RESCALE(a) and RESCALE(b) to INT32, ADD, RESCALE to the output
+     * dtype, CLAMP.  Equivalent to the five reference nodes evaluated one after another (INT32 ADD is the only integer
+     * ADD, reference_model/src/ops/op_factory.cpp:189-195). */
+    TB200_API tb200_status tb200_residual_add(tb200_ctx* ctx, const tb200_tensor* a, const tb200_rescale_attr* a_attr,
+                                              const tb200_tensor* b, const tb200_rescale_attr* b_attr,
+                                              const tb200_rescale_attr* out_attr, int32_t has_clamp, int32_t clamp_min,
+                                              int32_t clamp_max, tb200_tensor* output);
+
+    /* MAX_POOL2D.  Replaces OpMaxPool2d<T>::eval (reference_model/src/ops/tensor_ops.cpp:1545-1641; checks :28-117).
+     * kernel = {y,x}. */
+    TB200_API tb200_status tb200_max_pool2d(tb200_ctx* ctx, const tb200_tensor* input, const int32_t kernel[2],
+                                            const int32_t pad[4], const int32_t stride[2], tb200_tensor* output);
+
+    /* AVG_POOL2D.  Replaces OpAvgPool2d<T,Acc>::eval (reference_model/src/ops/tensor_ops.cpp:542-671) with
+     * QuantUtil::reciprocal_scale (reference_model/src/quant_util.h:32-43). */
+    TB200_API tb200_status tb200_avg_pool2d(tb200_ctx* ctx, const tb200_tensor* input, const int32_t kernel[2],
+                                            const int32_t pad[4], const int32_t stride[2], int32_t input_zp,
+                                            int32_t output_zp, tb200_tensor* output);
+
+    /* ---- host-buffer conveniences --------------------------------------------------------------
+     * One call per node for hosts that keep tensors in host memory: upload the operands, run the node,
+     * download the result, synchronise.  The timed end-to-end path of the benchmark. */
+    TB200_API tb200_status tb200_matmul_host(tb200_ctx* ctx, tb200_dtype in_dtype, tb200_dtype out_dtype,
+                                             const void* a, const void* b, int32_t N, int32_t H, int32_t C,
+                                             int32_t W, int32_t a_zp, int32_t b_zp, void* out);
+
+    /* Selects kernels: 0 = automatic (tensor-core kernels where the shape qualifies), 1 = force the
+     * CUDA-core kernels (for A/B checks).  Returns the previous value. */
+    TB200_API int tb200_set_kernel_policy(tb200_ctx* ctx, int policy);
+    /* Name of the kernel family the last operator call used ("tc_gemm_i8", "direct_conv", ...). */
+    TB200_API const char* tb200_last_kernel(const tb200_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TB200_H */

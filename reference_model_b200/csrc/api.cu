@@ -1,0 +1,1247 @@
+// C-ABI entry points of libtb200: context and tensor management, host-side validation that mirrors the
+// reference's checkTensorAttributes / ERROR_IF rules, and dispatch to the kernels.
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <new>
+
+#include "common.h"
+#include "kernels_cc.cuh"
+
+using namespace tb200;
+
+namespace tb200
+{
+
+tb200_status ensure_scratch(tb200_ctx* ctx, size_t bytes)
+{
+    if (bytes <= ctx->scratch_bytes)
+        return TB200_OK;
+    // the old block may still be in use by kernels queued on the stream
+    TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->scratch)
+        TB200_CUDA_CHECK(ctx, cudaFree(ctx->scratch));
+    ctx->scratch       = nullptr;
+    ctx->scratch_bytes = 0;
+    size_t want        = std::max(bytes, (size_t)1 << 20);
+    TB200_CUDA_CHECK(ctx, cudaMalloc(&ctx->scratch, want));
+    ctx->scratch_bytes = want;
+    return TB200_OK;
+}
+
+tb200_status post_launch(tb200_ctx* ctx, const char* kernel_name, int n_launches)
+{
+    ctx->launches += (uint64_t)n_launches;
+    ctx->last_kernel = kernel_name;
+    cudaError_t e    = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail(ctx, TB200_INTERNAL, "launch of %s failed: %s", kernel_name, cudaGetErrorString(e));
+    return TB200_OK;
+}
+
+void timer_begin(tb200_ctx* ctx)
+{
+    if (!ctx->timing)
+        return;
+    cudaEvent_t a = nullptr, b = nullptr;
+    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess)
+        return;
+    cudaEventRecord(a, ctx->stream);
+    ctx->timed.emplace_back(a, b);
+}
+
+void timer_end(tb200_ctx* ctx)
+{
+    if (!ctx->timing || ctx->timed.empty())
+        return;
+    cudaEventRecord(ctx->timed.back().second, ctx->stream);
+}
+
+static int grid_for(tb200_ctx* ctx, int64_t work_items, int block)
+{
+    int64_t blocks = (work_items + block - 1) / block;
+    int64_t cap    = (int64_t)ctx->num_sms * 16;
+    return (int)std::max<int64_t>(1, std::min(blocks, cap));
+}
+
+static bool same_shape(const tb200_tensor* a, const tb200_tensor* b)
+{
+    if (a->rank != b->rank)
+        return false;
+    for (int i = 0; i < a->rank; i++)
+        if (a->shape[i] != b->shape[i])
+            return false;
+    return true;
+}
+
+static int dtype_bits(tb200_dtype d)
+{
+    return (int)dtype_size(d) * 8;
+}
+
+static bool is_int_dtype(tb200_dtype d)
+{
+    return d == TB200_INT8 || d == TB200_INT16 || d == TB200_INT32 || d == TB200_UINT8 || d == TB200_UINT16;
+}
+
+// Validates a RESCALE attribute the way OpRescale::checkTensorAttributes / eval do
+// (reference_model/src/ops/type_conversion.cpp:71-154, :242-255) and fills the device descriptor.
+static tb200_status make_rescale_dev(tb200_ctx* ctx, const tb200_rescale_attr* a, tb200_dtype in_dt, tb200_dtype out_dt,
+                                     int channels, RescaleDev* r)
+{
+    TB200_ERROR_IF(ctx, !a || !a->multiplier || !a->shift, "OpRescale: missing multiplier / shift operand");
+    TB200_ERROR_IF(ctx, !is_int_dtype(in_dt) || !is_int_dtype(out_dt), "OpRescale: integer tensors only");
+    TB200_ERROR_IF(ctx, a->rounding_mode < TB200_SINGLE_ROUND || a->rounding_mode > TB200_INEXACT_ROUND,
+                   "OpRescale: only SINGLE_ROUND, DOUBLE_ROUND and INEXACT_ROUND are supported");
+    TB200_ERROR_IF(ctx, !a->scale32 && a->rounding_mode == TB200_DOUBLE_ROUND,
+                   "OpRescale: Scale set to false but double round set to true");
+    TB200_ERROR_IF(ctx, a->input_unsigned && a->output_unsigned, "OpRescale: input and output cannot both be unsigned");
+    const int in_bits = dtype_bits(in_dt), out_bits = dtype_bits(out_dt);
+    TB200_ERROR_IF(ctx, (in_bits == 32 && a->input_unsigned) || (out_bits == 32 && a->output_unsigned),
+                   "OpRescale: unsigned is not allowed with int32 tensors");
+    TB200_ERROR_IF(ctx, a->multiplier->dtype != (a->scale32 ? TB200_INT32 : TB200_INT16),
+                   "OpRescale: multiplier must be INT32 when scale32 else INT16");
+    TB200_ERROR_IF(ctx, a->shift->dtype != TB200_INT8, "OpRescale: shift must be INT8");
+    TB200_ERROR_IF(ctx, a->multiplier->rank != 1 || a->shift->rank != 1, "OpRescale: multiplier and shift must be rank 1");
+    const int need = a->per_channel ? channels : 1;
+    TB200_ERROR_IF(ctx, a->multiplier->shape[0] != need,
+                   "OpRescale: multiplier size %d does not match %s (%d)", a->multiplier->shape[0],
+                   a->per_channel ? "the channel count" : "per_channel=false", need);
+    TB200_ERROR_IF(ctx, a->shift->shape[0] != need, "OpRescale: shift size %d does not match %s (%d)",
+                   a->shift->shape[0], a->per_channel ? "the channel count" : "per_channel=false", need);
+    const int64_t in_zp  = value_extend64_dev(a->input_zp, in_bits, a->input_unsigned != 0);
+    const int64_t out_zp = value_extend64_dev(a->output_zp, out_bits, a->output_unsigned != 0);
+    TB200_ERROR_IF(ctx, in_bits != 8 && !(in_bits == 16 && a->input_unsigned) && in_zp != 0,
+                   "OpRescale: Input TOSA_REF_TYPE not INT8/UINT8/UINT16 and zero point not 0");
+    TB200_ERROR_IF(ctx, out_bits != 8 && !(out_bits == 16 && a->output_unsigned) && out_zp != 0,
+                   "OpRescale: Output TOSA_REF_TYPE not INT8/UINT8/UINT16 and zero point not 0");
+    TB200_ERROR_IF(ctx, in_bits == 16 && a->input_unsigned && in_zp != 0 && in_zp != 32768,
+                   "OpRescale: Input unsigned int16 and zero point not 0 or 32768");
+    TB200_ERROR_IF(ctx, out_bits == 16 && a->output_unsigned && out_zp != 0 && out_zp != 32768,
+                   "OpRescale: Output unsigned int16 and zero point not 0 or 32768");
+    r->mult         = a->multiplier->data;
+    r->shift        = reinterpret_cast<const int8_t*>(a->shift->data);
+    r->mult_is_i16  = !a->scale32;
+    r->per_channel  = a->per_channel;
+    r->scale32      = a->scale32;
+    r->rounding     = a->rounding_mode;
+    r->in_zp_ext    = in_zp;
+    r->out_zp_ext   = out_zp;
+    r->in_bits      = in_bits;
+    r->out_bits     = out_bits;
+    r->in_unsigned  = a->input_unsigned;
+    r->out_unsigned = a->output_unsigned;
+    if (a->output_unsigned)
+    {
+        r->qmin = 0;
+        r->qmax = out_bits == 8 ? 255 : 65535;
+    }
+    else
+    {
+        r->qmin = -((int64_t)1 << (out_bits - 1));
+        r->qmax = ((int64_t)1 << (out_bits - 1)) - 1;
+    }
+    return TB200_OK;
+}
+
+// check_conv_attribute (reference_model/src/ops/tensor_ops.cpp:120-226)
+static tb200_status check_conv_attr(tb200_ctx* ctx, const char* op, int IH, int IW, int OH, int OW, int KH, int KW,
+                                    const int32_t* pad, const int32_t* stride, const int32_t* dilation)
+{
+    for (int i = 0; i < 4; i++)
+        TB200_ERROR_IF(ctx, pad[i] < 0, "%s: At least one pad is smaller than zero", op);
+    for (int i = 0; i < 2; i++)
+        TB200_ERROR_IF(ctx, stride[i] < 1, "%s: At least one stride dimension is smaller than one", op);
+    for (int i = 0; i < 2; i++)
+        TB200_ERROR_IF(ctx, dilation[i] < 1, "%s: At least one dilation dimension is smaller than one", op);
+    const int full_H = IH - 1 + pad[0] + pad[1] - (KH - 1) * dilation[0];
+    const int full_W = IW - 1 + pad[2] + pad[3] - (KW - 1) * dilation[1];
+    TB200_ERROR_IF(ctx, (full_H % stride[0] != 0) || (full_W % stride[1] != 0),
+                   "%s: Parameters must yield exact integer output dimensions", op);
+    TB200_ERROR_IF(ctx, (OH != full_H / stride[0] + 1) || (OW != full_W / stride[1] + 1),
+                   "%s: Mismatch between output shape provided and expected output shape (%d,%d)", op,
+                   full_H / stride[0] + 1, full_W / stride[1] + 1);
+    return TB200_OK;
+}
+
+// check_pool2d_attribute (reference_model/src/ops/tensor_ops.cpp:28-117)
+static tb200_status check_pool_attr(tb200_ctx* ctx, const char* op, int IH, int IW, int OH, int OW, const int32_t* kernel,
+                                    const int32_t* pad, const int32_t* stride)
+{
+    for (int i = 0; i < 4; i++)
+        TB200_ERROR_IF(ctx, pad[i] < 0, "%s: At least one pad is smaller than zero", op);
+    for (int i = 0; i < 2; i++)
+        TB200_ERROR_IF(ctx, kernel[i] < 1, "%s: At least one kernel dimension is smaller than one", op);
+    for (int i = 0; i < 2; i++)
+        TB200_ERROR_IF(ctx, stride[i] < 1, "%s: At least one stride dimension is smaller than one", op);
+    TB200_ERROR_IF(ctx, pad[0] >= kernel[0] || pad[1] >= kernel[0] || pad[2] >= kernel[1] || pad[3] >= kernel[1],
+                   "%s: At least one pad is >= kernel dimension", op);
+    const int full_H = IH + pad[0] + pad[1] - kernel[0];
+    const int full_W = IW + pad[2] + pad[3] - kernel[1];
+    TB200_ERROR_IF(ctx, (full_H % stride[0] != 0) || (full_W % stride[1] != 0),
+                   "%s: Parameters must yield exact integer output dimensions", op);
+    TB200_ERROR_IF(ctx, (OH != full_H / stride[0] + 1) || (OW != full_W / stride[1] + 1),
+                   "%s: Mismatch between output shape provided and expected output shape (%d,%d)", op,
+                   full_H / stride[0] + 1, full_W / stride[1] + 1);
+    return TB200_OK;
+}
+
+struct EpiInfo
+{
+    bool has_rescale = false;
+    bool has_clamp   = false;
+    RescaleDev rs;
+    int32_t clamp_lo = 0, clamp_hi = 0;
+    float clamp_lo_f = 0.f, clamp_hi_f = 0.f;
+};
+
+static tb200_status parse_epilogue(tb200_ctx* ctx, const char* op, const tb200_epilogue* e, bool int_path, int channels,
+                                   tb200_dtype out_dt, EpiInfo* info)
+{
+    memset(&info->rs, 0, sizeof(info->rs));
+    if (!e)
+    {
+        TB200_ERROR_IF(ctx, int_path && out_dt != TB200_INT32, "%s: integer accumulator output must be INT32", op);
+        return TB200_OK;
+    }
+    if (e->has_rescale)
+    {
+        TB200_ERROR_IF(ctx, !int_path, "%s: a RESCALE epilogue needs an integer accumulator", op);
+        tb200_status st = make_rescale_dev(ctx, &e->rescale, TB200_INT32, out_dt, channels, &info->rs);
+        if (st != TB200_OK)
+            return st;
+        info->has_rescale = true;
+    }
+    else
+        TB200_ERROR_IF(ctx, int_path && out_dt != TB200_INT32, "%s: integer accumulator output must be INT32", op);
+    if (e->has_clamp)
+    {
+        TB200_ERROR_IF(ctx, int_path && !e->has_rescale, "%s: CLAMP is not defined on INT32 tensors", op);
+        if (int_path)
+        {
+            TB200_ERROR_IF(ctx, e->clamp_max_i < e->clamp_min_i, "OpClamp: max smaller than min");
+            info->clamp_lo = e->clamp_min_i;
+            info->clamp_hi = e->clamp_max_i;
+        }
+        else
+        {
+            TB200_ERROR_IF(ctx, std::isnan(e->clamp_min_f) || std::isnan(e->clamp_max_f), "OpClamp: min/max cannot be NaN");
+            TB200_ERROR_IF(ctx, e->clamp_max_f < e->clamp_min_f, "OpClamp: max smaller than min");
+            info->clamp_lo_f = e->clamp_min_f;
+            info->clamp_hi_f = e->clamp_max_f;
+        }
+        info->has_clamp = true;
+    }
+    return TB200_OK;
+}
+
+static void fill_conv_dev(ConvDev* d, const EpiInfo& e)
+{
+    d->has_rescale = e.has_rescale;
+    d->rs          = e.rs;
+    d->has_clamp   = e.has_clamp;
+    d->clamp_lo    = e.clamp_lo;
+    d->clamp_hi    = e.clamp_hi;
+    d->clamp_lo_f  = e.clamp_lo_f;
+    d->clamp_hi_f  = e.clamp_hi_f;
+}
+
+// Tensor-core epilogue fields shared by conv and matmul.
+static void fill_tc_epilogue(TcProblem* q, const EpiInfo& e, tb200_dtype out_dt)
+{
+    q->out_dtype = out_dt;
+    q->has_clamp = e.has_clamp;
+    if (e.has_rescale)
+    {
+        q->epi          = TC_EPI_RESCALE;
+        q->multiplier   = reinterpret_cast<const int32_t*>(e.rs.mult);
+        q->shift        = e.rs.shift;
+        q->per_channel  = e.rs.per_channel;
+        q->double_round = e.rs.rounding == TB200_DOUBLE_ROUND;
+        q->out_zp       = (int32_t)e.rs.out_zp_ext;
+        int64_t lo = e.rs.qmin, hi = e.rs.qmax;
+        if (e.has_clamp)
+        {
+            // clip to [qmin, qmax] followed by CLAMP [cmin, cmax] is one clip to [L, H]
+            lo = std::min<int64_t>(std::max<int64_t>(e.rs.qmin, e.clamp_lo), e.clamp_hi);
+            hi = std::min<int64_t>(std::max<int64_t>(e.rs.qmax, e.clamp_lo), e.clamp_hi);
+        }
+        q->clamp_lo = (int32_t)lo;
+        q->clamp_hi = (int32_t)hi;
+    }
+    q->clamp_lo_f = e.clamp_lo_f;
+    q->clamp_hi_f = e.clamp_hi_f;
+}
+
+}    // namespace tb200
+
+// =================================================================================================== context
+extern "C" tb200_status tb200_ctx_create(int device, void* stream, tb200_ctx** out)
+{
+    if (!out)
+        return TB200_ERROR;
+    *out          = nullptr;
+    tb200_ctx* c  = new (std::nothrow) tb200_ctx();
+    if (!c)
+        return TB200_INTERNAL;
+    c->device = device;
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess)
+    {
+        fprintf(stderr, "tb200_ctx_create: cudaSetDevice(%d) failed: %s\n", device, cudaGetErrorString(e));
+        delete c;
+        return TB200_INTERNAL;
+    }
+    if (stream)
+        c->stream = reinterpret_cast<cudaStream_t>(stream);
+    else
+    {
+        if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess)
+        {
+            delete c;
+            return TB200_INTERNAL;
+        }
+        c->owns_stream = true;
+    }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) == cudaSuccess)
+        c->num_sms = prop.multiProcessorCount;
+    if (cudaMalloc(&c->d_status, sizeof(int)) != cudaSuccess || cudaMallocHost(&c->h_status, sizeof(int)) != cudaSuccess ||
+        cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream) != cudaSuccess)
+    {
+        fprintf(stderr, "tb200_ctx_create: status word allocation failed: %s\n", cudaGetErrorString(cudaGetLastError()));
+        delete c;
+        return TB200_INTERNAL;
+    }
+    const char* pol = getenv("TB200_KERNEL_POLICY");
+    if (pol)
+        c->policy = atoi(pol);
+    *out = c;
+    return TB200_OK;
+}
+
+extern "C" tb200_status tb200_ctx_destroy(tb200_ctx* ctx)
+{
+    if (!ctx)
+        return TB200_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->scratch)
+        cudaFree(ctx->scratch);
+    if (ctx->d_status)
+        cudaFree(ctx->d_status);
+    if (ctx->h_status)
+        cudaFreeHost(ctx->h_status);
+    if (ctx->owns_stream)
+        cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return TB200_OK;
+}
+
+extern "C" const char* tb200_last_error(const tb200_ctx* ctx)
+{
+    return ctx ? ctx->err.c_str() : "null context";
+}
+
+extern "C" uint64_t tb200_launch_count(const tb200_ctx* ctx)
+{
+    return ctx ? ctx->launches : 0;
+}
+
+extern "C" tb200_status tb200_timer_enable(tb200_ctx* ctx, int32_t on)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    ctx->timing = on != 0;
+    return TB200_OK;
+}
+
+extern "C" tb200_status tb200_timer_read(tb200_ctx* ctx, double* total_ms, int32_t* launches)
+{
+    if (!ctx || !total_ms || !launches)
+        return TB200_ERROR;
+    TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    double sum = 0.0;
+    int n      = 0;
+    for (auto& pr : ctx->timed)
+    {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, pr.first, pr.second) == cudaSuccess)
+        {
+            sum += ms;
+            n++;
+        }
+        cudaEventDestroy(pr.first);
+        cudaEventDestroy(pr.second);
+    }
+    ctx->timed.clear();
+    *total_ms = sum;
+    *launches = n;
+    return TB200_OK;
+}
+
+extern "C" int tb200_set_kernel_policy(tb200_ctx* ctx, int policy)
+{
+    int old     = ctx->policy;
+    ctx->policy = policy;
+    return old;
+}
+
+extern "C" const char* tb200_last_kernel(const tb200_ctx* ctx)
+{
+    return ctx ? ctx->last_kernel : "none";
+}
+
+extern "C" tb200_status tb200_sync(tb200_ctx* ctx)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    TB200_CUDA_CHECK(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+    TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    const int s = *ctx->h_status;
+    if (s & TB200_DEV_TIMEOUT)
+        return fail(ctx, TB200_INTERNAL, "a kernel gave up waiting on its pipeline (device status 0x%x)", s);
+    if (s & TB200_DEV_UNPREDICTABLE)
+        return fail(ctx, TB200_UNPREDICTABLE, "a REQUIRE condition failed on the device (RESCALE range / ADD overflow)");
+    return TB200_OK;
+}
+
+// =================================================================================================== tensors
+static tb200_status make_tensor(tb200_ctx* ctx, tb200_dtype dtype, int rank, const int32_t* shape, void* ptr, bool owns,
+                                tb200_tensor** out)
+{
+    TB200_ERROR_IF(ctx, !out, "null output handle");
+    *out = nullptr;
+    TB200_ERROR_IF(ctx, rank < 0 || rank > 6, "tensor rank %d out of range", rank);
+    TB200_ERROR_IF(ctx, dtype_size(dtype) == 0, "unsupported dtype %d", (int)dtype);
+    int64_t n = 1;
+    for (int i = 0; i < rank; i++)
+    {
+        TB200_ERROR_IF(ctx, shape[i] < 0, "negative dimension");
+        n *= shape[i];
+        // the reference caps tensors at 2^31-1 elements (reference_model/src/subgraph_traverser.cpp:583-598)
+        TB200_ERROR_IF(ctx, n > 2147483647LL, "tensor exceeds 2^31-1 elements");
+    }
+    tb200_tensor* t = new (std::nothrow) tb200_tensor();
+    if (!t)
+        return fail(ctx, TB200_INTERNAL, "out of host memory");
+    t->dtype = dtype;
+    t->rank  = rank;
+    for (int i = 0; i < 6; i++)
+        t->shape[i] = i < rank ? shape[i] : 1;
+    t->bytes = (size_t)n * dtype_size(dtype);
+    t->owns  = owns;
+    t->data  = ptr;
+    if (owns)
+    {
+        cudaError_t e = cudaMalloc(&t->data, std::max<size_t>(t->bytes, 16));
+        if (e != cudaSuccess)
+        {
+            delete t;
+            return fail(ctx, TB200_INTERNAL, "cudaMalloc of %zu bytes failed: %s", t->bytes, cudaGetErrorString(e));
+        }
+    }
+    *out = t;
+    return TB200_OK;
+}
+
+extern "C" tb200_status tb200_tensor_alloc(tb200_ctx* ctx, tb200_dtype dtype, int rank, const int32_t* shape,
+                                           tb200_tensor** out)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    return make_tensor(ctx, dtype, rank, shape, nullptr, true, out);
+}
+
+extern "C" tb200_status tb200_tensor_wrap(tb200_ctx* ctx, tb200_dtype dtype, int rank, const int32_t* shape,
+                                          void* device_ptr, tb200_tensor** out)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !device_ptr, "null device pointer");
+    TB200_ERROR_IF(ctx, (reinterpret_cast<uintptr_t>(device_ptr) & 15) != 0, "device pointer must be 16-byte aligned");
+    return make_tensor(ctx, dtype, rank, shape, device_ptr, false, out);
+}
+
+extern "C" tb200_status tb200_tensor_free(tb200_ctx* ctx, tb200_tensor* t)
+{
+    if (!t)
+        return TB200_OK;
+    if (t->owns && t->data)
+    {
+        if (ctx)
+            cudaStreamSynchronize(ctx->stream);
+        cudaFree(t->data);
+    }
+    delete t;
+    return TB200_OK;
+}
+
+extern "C" tb200_status tb200_tensor_upload(tb200_ctx* ctx, tb200_tensor* t, const void* host, size_t bytes)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !t || !host, "null tensor or host buffer");
+    TB200_ERROR_IF(ctx, bytes != t->bytes, "upload of %zu bytes into a tensor of %zu bytes", bytes, t->bytes);
+    if (bytes)
+        TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(t->data, host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return TB200_OK;
+}
+
+extern "C" tb200_status tb200_tensor_download(tb200_ctx* ctx, const tb200_tensor* t, void* host, size_t bytes)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !t || !host, "null tensor or host buffer");
+    TB200_ERROR_IF(ctx, bytes != t->bytes, "download of %zu bytes from a tensor of %zu bytes", bytes, t->bytes);
+    if (bytes)
+        TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(host, t->data, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return tb200_sync(ctx);
+}
+
+extern "C" void* tb200_tensor_data(const tb200_tensor* t)
+{
+    return t ? t->data : nullptr;
+}
+
+extern "C" size_t tb200_tensor_bytes(const tb200_tensor* t)
+{
+    return t ? t->bytes : 0;
+}
+
+// =================================================================================================== CONV2D
+extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
+                                     const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp, const int32_t pad[4],
+                                     const int32_t stride[2], const int32_t dilation[2], const tb200_epilogue* epilogue,
+                                     tb200_tensor* output)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !input || !weight || !bias || !output || !pad || !stride || !dilation, "OpConv2d: null operand");
+    // OpConv2d::checkTensorAttributes (reference_model/src/ops/tensor_ops.cpp:690-720)
+    TB200_ERROR_IF(ctx, input->rank != 4 || weight->rank != 4 || output->rank != 4 || bias->rank != 1,
+                   "OpConv2d: input, weight and output must be rank 4 and bias rank 1");
+    const int N = input->shape[0], IH = input->shape[1], IW = input->shape[2], IC = input->shape[3];
+    const int OC = weight->shape[0], KH = weight->shape[1], KW = weight->shape[2];
+    const int OH = output->shape[1], OW = output->shape[2];
+    tb200_status st = check_conv_attr(ctx, "OpConv2d", IH, IW, OH, OW, KH, KW, pad, stride, dilation);
+    if (st != TB200_OK)
+        return st;
+    // OpConv2d::eval ERROR_IFs (:742-748)
+    TB200_ERROR_IF(ctx, N != output->shape[0], "OpConv2d: tensor batch mismatch %d != %d", N, output->shape[0]);
+    TB200_ERROR_IF(ctx, weight->shape[3] != IC, "OpConv2d: tensor input channel mismatch %d != %d", weight->shape[3], IC);
+    TB200_ERROR_IF(ctx, OC != output->shape[3], "OpConv2d: tensor output channel mismatch %d != %d", OC, output->shape[3]);
+    TB200_ERROR_IF(ctx, bias->shape[0] != OC && bias->shape[0] != 1, "OpConv2d: bias channel mismatch %d != %d",
+                   bias->shape[0], OC);
+    const bool int_path = input->dtype == TB200_INT8;
+    TB200_ERROR_IF(ctx, weight->dtype != input->dtype, "OpConv2d: input and weight dtypes differ");
+    if (int_path)
+        TB200_ERROR_IF(ctx, bias->dtype != TB200_INT32, "OpConv2d: INT8 convolution needs an INT32 bias");
+    else
+    {
+        TB200_ERROR_IF(ctx, !dtype_is_float(input->dtype), "OpConv2d: unsupported input dtype %d", (int)input->dtype);
+        TB200_ERROR_IF(ctx, bias->dtype != input->dtype || output->dtype != input->dtype,
+                       "OpConv2d: floating bias and output must have the input dtype");
+        // :805,811
+        TB200_ERROR_IF(ctx, input_zp != 0, "Input zero point must be zero for non int8_t data");
+        TB200_ERROR_IF(ctx, weight_zp != 0, "Weight zero point must be zero for non int8_t data");
+    }
+    TB200_ERROR_IF(ctx, input_zp < -128 || input_zp > 127 || weight_zp < -128 || weight_zp > 127,
+                   "OpConv2d: zero point outside the int8 range");
+    EpiInfo epi;
+    st = parse_epilogue(ctx, "OpConv2d", epilogue, int_path, OC, output->dtype, &epi);
+    if (st != TB200_OK)
+        return st;
+    if (numel(output) == 0)
+        return TB200_OK;
+
+    // ---- tensor-core path
+    const bool tc_rescale_ok = !epi.has_rescale || (epi.rs.scale32 && epi.rs.rounding != TB200_INEXACT_ROUND &&
+                                                    !epi.rs.out_unsigned);
+    if (ctx->policy == 0 && (!int_path || weight_zp == 0) && tc_rescale_ok &&
+        (int_path || input->dtype != TB200_FP32))
+    {
+        TcProblem q;
+        memset(&q, 0, sizeof(q));
+        q.in_dtype = input->dtype;
+        q.a        = input->data;
+        q.N = N; q.IH = IH; q.IW = IW; q.IC = IC;
+        q.OH = OH; q.OW = OW; q.OC = OC;
+        q.KH = KH; q.KW = KW;
+        q.pad_t = pad[0]; q.pad_l = pad[2];
+        q.stride_y = stride[0]; q.stride_x = stride[1];
+        q.dil_y = dilation[0]; q.dil_x = dilation[1];
+        q.b   = weight->data;
+        q.out = output->data;
+        q.epi = int_path ? TC_EPI_I32 : TC_EPI_FLOAT;
+        fill_tc_epilogue(&q, epi, output->dtype);
+        std::string why;
+        if (tc_gemm_supported(q, &why))
+        {
+            if (int_path)
+            {
+                const size_t table_elems = (size_t)(KH + 1) * (KW + 1) * OC + 2 * (size_t)OC;
+                st = ensure_scratch(ctx, table_elems * sizeof(int32_t));
+                if (st != TB200_OK)
+                    return st;
+                int32_t* table = reinterpret_cast<int32_t*>(ctx->scratch);
+                conv_weight_tables_kernel<<<(OC + 127) / 128, 128, 0, ctx->stream>>>(
+                    reinterpret_cast<const int8_t*>(weight->data), reinterpret_cast<const int32_t*>(bias->data),
+                    bias->shape[0], OC, KH, KW, IC, input_zp, table);
+                st = post_launch(ctx, "conv_weight_tables");
+                if (st != TB200_OK)
+                    return st;
+                q.col_corr = table + (size_t)(KH + 1) * (KW + 1) * OC + OC;
+                const bool padded = pad[0] || pad[1] || pad[2] || pad[3];
+                q.wsum_prefix = (input_zp != 0 && padded) ? table : nullptr;
+                q.in_zp       = input_zp;
+            }
+            else
+            {
+                st = ensure_scratch(ctx, (size_t)bias->shape[0] * sizeof(float));
+                if (st != TB200_OK)
+                    return st;
+                float* bf = reinterpret_cast<float*>(ctx->scratch);
+                if (input->dtype == TB200_FP16)
+                    bias_to_f32_kernel<__half><<<(bias->shape[0] + 127) / 128, 128, 0, ctx->stream>>>(
+                        reinterpret_cast<const __half*>(bias->data), bf, bias->shape[0]);
+                else
+                    bias_to_f32_kernel<__nv_bfloat16><<<(bias->shape[0] + 127) / 128, 128, 0, ctx->stream>>>(
+                        reinterpret_cast<const __nv_bfloat16*>(bias->data), bf, bias->shape[0]);
+                st = post_launch(ctx, "bias_to_f32");
+                if (st != TB200_OK)
+                    return st;
+                q.bias_f = bf;
+                q.bias_n = bias->shape[0];
+            }
+            return tc_gemm_launch(ctx, q);
+        }
+    }
+
+    // ---- CUDA-core path
+    ConvDev d;
+    memset(&d, 0, sizeof(d));
+    d.N = N; d.IH = IH; d.IW = IW; d.IC = IC; d.OH = OH; d.OW = OW; d.OC = OC; d.KH = KH; d.KW = KW; d.M = 1;
+    d.pad_t = pad[0]; d.pad_l = pad[2]; d.sy = stride[0]; d.sx = stride[1]; d.dy = dilation[0]; d.dx = dilation[1];
+    d.in_zp = input_zp; d.w_zp = weight_zp; d.bias_n = bias->shape[0];
+    fill_conv_dev(&d, epi);
+    const int block = 256;
+    const int grid  = grid_for(ctx, numel(output), block);
+    if (int_path)
+    {
+        const int8_t* in  = reinterpret_cast<const int8_t*>(input->data);
+        const int8_t* w   = reinterpret_cast<const int8_t*>(weight->data);
+        const int32_t* b  = reinterpret_cast<const int32_t*>(bias->data);
+        switch (dtype_size(output->dtype))
+        {
+            case 1:
+                conv2d_direct_i8_kernel<int8_t><<<grid, block, 0, ctx->stream>>>(in, w, b, reinterpret_cast<int8_t*>(output->data), d, ctx->d_status);
+                break;
+            case 2:
+                conv2d_direct_i8_kernel<int16_t><<<grid, block, 0, ctx->stream>>>(in, w, b, reinterpret_cast<int16_t*>(output->data), d, ctx->d_status);
+                break;
+            default:
+                conv2d_direct_i8_kernel<int32_t><<<grid, block, 0, ctx->stream>>>(in, w, b, reinterpret_cast<int32_t*>(output->data), d, ctx->d_status);
+                break;
+        }
+    }
+    else if (input->dtype == TB200_FP16)
+        conv2d_direct_fp_kernel<__half><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __half*>(input->data), reinterpret_cast<const __half*>(weight->data),
+            reinterpret_cast<const __half*>(bias->data), reinterpret_cast<__half*>(output->data), d);
+    else if (input->dtype == TB200_BF16)
+        conv2d_direct_fp_kernel<__nv_bfloat16><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __nv_bfloat16*>(input->data), reinterpret_cast<const __nv_bfloat16*>(weight->data),
+            reinterpret_cast<const __nv_bfloat16*>(bias->data), reinterpret_cast<__nv_bfloat16*>(output->data), d);
+    else
+        conv2d_direct_fp_kernel<float><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const float*>(input->data), reinterpret_cast<const float*>(weight->data),
+            reinterpret_cast<const float*>(bias->data), reinterpret_cast<float*>(output->data), d);
+    return post_launch(ctx, "conv2d_direct");
+}
+
+// =================================================================================================== DEPTHWISE
+extern "C" tb200_status tb200_depthwise_conv2d(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
+                                               const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp,
+                                               const int32_t pad[4], const int32_t stride[2], const int32_t dilation[2],
+                                               const tb200_epilogue* epilogue, tb200_tensor* output)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !input || !weight || !bias || !output || !pad || !stride || !dilation,
+                   "OpDepthwiseConv2d: null operand");
+    TB200_ERROR_IF(ctx, input->rank != 4 || weight->rank != 4 || output->rank != 4 || bias->rank != 1,
+                   "OpDepthwiseConv2d: input, weight and output must be rank 4 and bias rank 1");
+    const int N = input->shape[0], IH = input->shape[1], IW = input->shape[2], C = input->shape[3];
+    const int KH = weight->shape[0], KW = weight->shape[1], M = weight->shape[3];
+    const int OH = output->shape[1], OW = output->shape[2];
+    // kernel dims start at offset 0 of the weight shape (reference_model/src/ops/tensor_ops.cpp:1139-1169)
+    tb200_status st = check_conv_attr(ctx, "OpDepthwiseConv2d", IH, IW, OH, OW, KH, KW, pad, stride, dilation);
+    if (st != TB200_OK)
+        return st;
+    // OpDepthwiseConv2d::eval ERROR_IFs (:1196-1205)
+    TB200_ERROR_IF(ctx, N != output->shape[0], "OpDepthwiseConv2d: tensor batch mismatch %d != %d", N, output->shape[0]);
+    TB200_ERROR_IF(ctx, weight->shape[2] != C, "OpDepthwiseConv2d: tensor input channel mismatch %d != %d",
+                   weight->shape[2], C);
+    TB200_ERROR_IF(ctx, C * M != output->shape[3], "OpDepthwiseConv2d: tensor output channel mismatch %d != %d", C * M,
+                   output->shape[3]);
+    TB200_ERROR_IF(ctx, bias->shape[0] != C * M && bias->shape[0] != 1,
+                   "OpDepthwiseConv2d: bias channels mismatch %d != %d", bias->shape[0], C * M);
+    const bool int_path = input->dtype == TB200_INT8;
+    TB200_ERROR_IF(ctx, weight->dtype != input->dtype, "OpDepthwiseConv2d: input and weight dtypes differ");
+    if (int_path)
+        TB200_ERROR_IF(ctx, bias->dtype != TB200_INT32, "OpDepthwiseConv2d: INT8 convolution needs an INT32 bias");
+    else
+    {
+        TB200_ERROR_IF(ctx, !dtype_is_float(input->dtype), "OpDepthwiseConv2d: unsupported input dtype");
+        TB200_ERROR_IF(ctx, bias->dtype != input->dtype || output->dtype != input->dtype,
+                       "OpDepthwiseConv2d: floating bias and output must have the input dtype");
+        TB200_ERROR_IF(ctx, input_zp != 0, "Input zero point must be zero for non int8_t data");
+        TB200_ERROR_IF(ctx, weight_zp != 0, "Weight zero point must be zero for non int8_t data");
+    }
+    TB200_ERROR_IF(ctx, input_zp < -128 || input_zp > 127 || weight_zp < -128 || weight_zp > 127,
+                   "OpDepthwiseConv2d: zero point outside the int8 range");
+    EpiInfo epi;
+    st = parse_epilogue(ctx, "OpDepthwiseConv2d", epilogue, int_path, C * M, output->dtype, &epi);
+    if (st != TB200_OK)
+        return st;
+    if (numel(output) == 0)
+        return TB200_OK;
+    ConvDev d;
+    memset(&d, 0, sizeof(d));
+    d.N = N; d.IH = IH; d.IW = IW; d.IC = C; d.OH = OH; d.OW = OW; d.OC = C * M; d.KH = KH; d.KW = KW; d.M = M;
+    d.pad_t = pad[0]; d.pad_l = pad[2]; d.sy = stride[0]; d.sx = stride[1]; d.dy = dilation[0]; d.dx = dilation[1];
+    d.in_zp = input_zp; d.w_zp = weight_zp; d.bias_n = bias->shape[0];
+    fill_conv_dev(&d, epi);
+    const int block = 256;
+    if (int_path)
+    {
+        const int grid    = grid_for(ctx, numel(output), block);
+        const int8_t* in  = reinterpret_cast<const int8_t*>(input->data);
+        const int8_t* w   = reinterpret_cast<const int8_t*>(weight->data);
+        const int32_t* b  = reinterpret_cast<const int32_t*>(bias->data);
+        switch (dtype_size(output->dtype))
+        {
+            case 1:
+                depthwise_direct_i8_kernel<int8_t><<<grid, block, 0, ctx->stream>>>(in, w, b, reinterpret_cast<int8_t*>(output->data), d, ctx->d_status);
+                break;
+            case 2:
+                depthwise_direct_i8_kernel<int16_t><<<grid, block, 0, ctx->stream>>>(in, w, b, reinterpret_cast<int16_t*>(output->data), d, ctx->d_status);
+                break;
+            default:
+                depthwise_direct_i8_kernel<int32_t><<<grid, block, 0, ctx->stream>>>(in, w, b, reinterpret_cast<int32_t*>(output->data), d, ctx->d_status);
+                break;
+        }
+        return post_launch(ctx, "depthwise_direct_i8");
+    }
+    const bool x8 = (M == 1) && (C % 8 == 0) && input->dtype != TB200_FP32 && ctx->policy == 0 &&
+                    ((reinterpret_cast<uintptr_t>(input->data) | reinterpret_cast<uintptr_t>(weight->data) |
+                      reinterpret_cast<uintptr_t>(output->data)) & 15) == 0;
+    if (x8)
+    {
+        const int grid = grid_for(ctx, numel(output) / 8, block);
+        if (input->dtype == TB200_FP16)
+            depthwise_fp_x8_kernel<__half><<<grid, block, 0, ctx->stream>>>(
+                reinterpret_cast<const __half*>(input->data), reinterpret_cast<const __half*>(weight->data),
+                reinterpret_cast<const __half*>(bias->data), reinterpret_cast<__half*>(output->data), d);
+        else
+            depthwise_fp_x8_kernel<__nv_bfloat16><<<grid, block, 0, ctx->stream>>>(
+                reinterpret_cast<const __nv_bfloat16*>(input->data), reinterpret_cast<const __nv_bfloat16*>(weight->data),
+                reinterpret_cast<const __nv_bfloat16*>(bias->data), reinterpret_cast<__nv_bfloat16*>(output->data), d);
+        return post_launch(ctx, "depthwise_fp_x8");
+    }
+    const int grid = grid_for(ctx, numel(output), block);
+    if (input->dtype == TB200_FP16)
+        depthwise_direct_fp_kernel<__half><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __half*>(input->data), reinterpret_cast<const __half*>(weight->data),
+            reinterpret_cast<const __half*>(bias->data), reinterpret_cast<__half*>(output->data), d);
+    else if (input->dtype == TB200_BF16)
+        depthwise_direct_fp_kernel<__nv_bfloat16><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __nv_bfloat16*>(input->data), reinterpret_cast<const __nv_bfloat16*>(weight->data),
+            reinterpret_cast<const __nv_bfloat16*>(bias->data), reinterpret_cast<__nv_bfloat16*>(output->data), d);
+    else
+        depthwise_direct_fp_kernel<float><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const float*>(input->data), reinterpret_cast<const float*>(weight->data),
+            reinterpret_cast<const float*>(bias->data), reinterpret_cast<float*>(output->data), d);
+    return post_launch(ctx, "depthwise_direct_fp");
+}
+
+// =================================================================================================== MATMUL
+extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, const tb200_tensor* b, int32_t a_zp,
+                                     int32_t b_zp, const tb200_epilogue* epilogue, tb200_tensor* output)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !a || !b || !output, "OpMatMul: null operand");
+    // OpMatMul::checkTensorAttributes (reference_model/src/ops/tensor_ops.cpp:1347-1420)
+    TB200_ERROR_IF(ctx, a->rank != 3 || b->rank != 3 || output->rank != 3, "OpMatMul: operands must be rank 3");
+    const int N = a->shape[0], H = a->shape[1], C = a->shape[2], W = b->shape[2];
+    TB200_ERROR_IF(ctx, b->shape[0] != N || output->shape[0] != N, "OpMatMul operator a.shape[0], b.shape[0] and output.shape[0] should match");
+    TB200_ERROR_IF(ctx, output->shape[1] != H, "OpMatMul operator output.shape[1] should match a.shape[1]");
+    TB200_ERROR_IF(ctx, b->shape[1] != C, "OpMatMul operator a.shape[2] should match b.shape[1]");
+    TB200_ERROR_IF(ctx, output->shape[2] != W, "OpMatMul operator output.shape[2] should match b.shape[2]");
+    TB200_ERROR_IF(ctx, a->dtype != b->dtype, "OpMatMul: operand dtypes differ");
+    const bool int_path = a->dtype == TB200_INT8;
+    if (!int_path)
+    {
+        TB200_ERROR_IF(ctx, !dtype_is_float(a->dtype), "OpMatMul: unsupported dtype");
+        // :1433-1434
+        TB200_ERROR_IF(ctx, a_zp != 0, "OpMatMul: A zeropoint must be zero for non int8_t data");
+        TB200_ERROR_IF(ctx, b_zp != 0, "OpMatMul: B zeropoint must be zero for non int8_t data");
+        TB200_ERROR_IF(ctx, output->dtype != a->dtype && output->dtype != TB200_FP32, "OpMatMul: output dtype must be the input dtype or FP32");
+    }
+    TB200_ERROR_IF(ctx, a_zp < -128 || a_zp > 127 || b_zp < -128 || b_zp > 127, "OpMatMul: zero point outside the int8 range");
+    EpiInfo epi;
+    tb200_status st = parse_epilogue(ctx, "OpMatMul", epilogue, int_path, W, output->dtype, &epi);
+    if (st != TB200_OK)
+        return st;
+    TB200_ERROR_IF(ctx, epi.has_rescale || epi.has_clamp, "OpMatMul: fused epilogues are not available for MATMUL");
+    if (numel(output) == 0)
+        return TB200_OK;
+
+    if (a->dtype == TB200_FP32)
+    {
+        if (ctx->policy == 0)
+            return sgemm_f32_launch(ctx, reinterpret_cast<const float*>(a->data), reinterpret_cast<const float*>(b->data),
+                                    reinterpret_cast<float*>(output->data), N, H, C, W);
+    }
+    else if (ctx->policy == 0)
+    {
+        TcProblem q;
+        memset(&q, 0, sizeof(q));
+        q.in_dtype = a->dtype;
+        q.a        = a->data;
+        q.N = 1; q.IH = N; q.IW = H; q.IC = C;
+        q.OH = N; q.OW = H; q.OC = W;
+        q.KH = 1; q.KW = 1;
+        q.stride_y = q.stride_x = q.dil_y = q.dil_x = 1;
+        q.b          = b->data;
+        q.b_mn_major = 1;
+        q.out        = output->data;
+        q.epi        = int_path ? TC_EPI_I32 : TC_EPI_FLOAT;
+        fill_tc_epilogue(&q, epi, output->dtype);
+        std::string why;
+        if (tc_gemm_supported(q, &why))
+        {
+            if (int_path && (a_zp != 0 || b_zp != 0))
+            {
+                const size_t rows = (size_t)N * H, cols = (size_t)N * W;
+                st = ensure_scratch(ctx, (rows + cols) * sizeof(int32_t));
+                if (st != TB200_OK)
+                    return st;
+                int32_t* row_corr = reinterpret_cast<int32_t*>(ctx->scratch);
+                int32_t* col_corr = row_corr + rows;
+                int launches = 0;
+                if (b_zp != 0)
+                {
+                    const int block = 256;
+                    matmul_row_corr_kernel<<<grid_for(ctx, (int64_t)rows * 32, block), block, 0, ctx->stream>>>(
+                        reinterpret_cast<const int8_t*>(a->data), row_corr, (int64_t)rows, C, a_zp, b_zp);
+                    q.row_corr = row_corr;
+                    launches++;
+                }
+                if (a_zp != 0)
+                {
+                    dim3 grid((W + 127) / 128, N), block(32, 8);
+                    matmul_col_corr_kernel<<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const int8_t*>(b->data),
+                                                                           col_corr, C, W, a_zp);
+                    q.col_corr         = col_corr;
+                    q.col_corr_ystride = W;
+                    launches++;
+                }
+                st = post_launch(ctx, "matmul_zp_sums", launches);
+                if (st != TB200_OK)
+                    return st;
+            }
+            return tc_gemm_launch(ctx, q);
+        }
+    }
+
+    const int block = 256;
+    const int grid  = grid_for(ctx, numel(output), block);
+    if (int_path)
+        matmul_direct_i8_kernel<<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const int8_t*>(a->data),
+                                                                 reinterpret_cast<const int8_t*>(b->data),
+                                                                 reinterpret_cast<int32_t*>(output->data), N, H, C, W, a_zp, b_zp);
+    else if (a->dtype == TB200_FP32)
+        matmul_direct_fp_kernel<float, float><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const float*>(a->data), reinterpret_cast<const float*>(b->data),
+            reinterpret_cast<float*>(output->data), N, H, C, W);
+    else if (a->dtype == TB200_FP16 && output->dtype == TB200_FP16)
+        matmul_direct_fp_kernel<__half, __half><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __half*>(a->data), reinterpret_cast<const __half*>(b->data),
+            reinterpret_cast<__half*>(output->data), N, H, C, W);
+    else if (a->dtype == TB200_FP16)
+        matmul_direct_fp_kernel<__half, float><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __half*>(a->data), reinterpret_cast<const __half*>(b->data),
+            reinterpret_cast<float*>(output->data), N, H, C, W);
+    else if (output->dtype == TB200_BF16)
+        matmul_direct_fp_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __nv_bfloat16*>(a->data), reinterpret_cast<const __nv_bfloat16*>(b->data),
+            reinterpret_cast<__nv_bfloat16*>(output->data), N, H, C, W);
+    else
+        matmul_direct_fp_kernel<__nv_bfloat16, float><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __nv_bfloat16*>(a->data), reinterpret_cast<const __nv_bfloat16*>(b->data),
+            reinterpret_cast<float*>(output->data), N, H, C, W);
+    return post_launch(ctx, "matmul_direct");
+}
+
+// =================================================================================================== RESCALE
+template <typename TIn>
+static void launch_rescale_out(tb200_ctx* ctx, const tb200_tensor* in, tb200_tensor* out, int64_t n, int C,
+                               const RescaleDev& r, bool vec4)
+{
+    const int block = 256;
+    const TIn* ip   = reinterpret_cast<const TIn*>(in->data);
+#define TB200_RS_LAUNCH(TOUT)                                                                                          \
+    if (vec4)                                                                                                          \
+        rescale_kernel<TIn, TOUT, 4><<<grid_for(ctx, n / 4, block), block, 0, ctx->stream>>>(                          \
+            ip, reinterpret_cast<TOUT*>(out->data), n, C, r, ctx->d_status);                                           \
+    else                                                                                                               \
+        rescale_kernel<TIn, TOUT, 1><<<grid_for(ctx, n, block), block, 0, ctx->stream>>>(                              \
+            ip, reinterpret_cast<TOUT*>(out->data), n, C, r, ctx->d_status);
+    switch (dtype_size(out->dtype))
+    {
+        case 1:
+            TB200_RS_LAUNCH(int8_t)
+            break;
+        case 2:
+            TB200_RS_LAUNCH(int16_t)
+            break;
+        default:
+            TB200_RS_LAUNCH(int32_t)
+            break;
+    }
+#undef TB200_RS_LAUNCH
+}
+
+extern "C" tb200_status tb200_rescale(tb200_ctx* ctx, const tb200_tensor* input, const tb200_rescale_attr* attr,
+                                      tb200_tensor* output)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !input || !attr || !output, "OpRescale: null operand");
+    TB200_ERROR_IF(ctx, !same_shape(input, output), "OpRescale: input and output shapes differ");
+    const int C = input->rank > 0 ? input->shape[input->rank - 1] : 1;
+    RescaleDev r;
+    tb200_status st = make_rescale_dev(ctx, attr, input->dtype, output->dtype, C, &r);
+    if (st != TB200_OK)
+        return st;
+    const int64_t n = numel(input);
+    if (n == 0)
+        return TB200_OK;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(input->data) | reinterpret_cast<uintptr_t>(output->data)) & 15) == 0;
+    const bool vec4    = aligned && (n % 4 == 0) && (!attr->per_channel || C % 4 == 0);
+    switch (dtype_size(input->dtype))
+    {
+        case 1:
+            launch_rescale_out<int8_t>(ctx, input, output, n, C, r, vec4);
+            break;
+        case 2:
+            launch_rescale_out<int16_t>(ctx, input, output, n, C, r, vec4);
+            break;
+        default:
+            launch_rescale_out<int32_t>(ctx, input, output, n, C, r, vec4);
+            break;
+    }
+    return post_launch(ctx, "rescale");
+}
+
+// =================================================================================================== CLAMP
+extern "C" tb200_status tb200_clamp(tb200_ctx* ctx, const tb200_tensor* input, int32_t min_i, int32_t max_i, float min_f,
+                                    float max_f, int32_t nan_ignore, tb200_tensor* output)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !input || !output, "OpClamp: null operand");
+    TB200_ERROR_IF(ctx, !same_shape(input, output) || input->dtype != output->dtype,
+                   "OpClamp: input and output must have the same shape and dtype");
+    const int64_t n = numel(input);
+    const int block = 256;
+    const int grid  = grid_for(ctx, std::max<int64_t>(1, n / 8), block);
+    switch (input->dtype)
+    {
+        case TB200_INT8:
+            TB200_ERROR_IF(ctx, max_i < min_i, "OpClamp: max smaller than min");
+            if (n)
+                clamp_int_kernel<int8_t><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const int8_t*>(input->data), reinterpret_cast<int8_t*>(output->data), n, min_i, max_i);
+            break;
+        case TB200_INT16:
+            TB200_ERROR_IF(ctx, max_i < min_i, "OpClamp: max smaller than min");
+            if (n)
+                clamp_int_kernel<int16_t><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const int16_t*>(input->data), reinterpret_cast<int16_t*>(output->data), n, min_i, max_i);
+            break;
+        case TB200_FP16:
+        case TB200_BF16:
+        case TB200_FP32:
+            TB200_ERROR_IF(ctx, std::isnan(min_f) || std::isnan(max_f), "OpClamp: min/max cannot be NaN");
+            TB200_ERROR_IF(ctx, max_f < min_f, "OpClamp: max smaller than min");
+            if (n)
+            {
+                if (input->dtype == TB200_FP16)
+                    clamp_fp_kernel<__half><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const __half*>(input->data), reinterpret_cast<__half*>(output->data), n, min_f, max_f, nan_ignore);
+                else if (input->dtype == TB200_BF16)
+                    clamp_fp_kernel<__nv_bfloat16><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const __nv_bfloat16*>(input->data), reinterpret_cast<__nv_bfloat16*>(output->data), n, min_f, max_f, nan_ignore);
+                else
+                    clamp_fp_kernel<float><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const float*>(input->data), reinterpret_cast<float*>(output->data), n, min_f, max_f, nan_ignore);
+            }
+            break;
+        default:
+            // the reference instantiates CLAMP for INT8, INT16 and the floating types only
+            return fail(ctx, TB200_ERROR, "OpClamp: unsupported TOSA_REF_TYPE %d", (int)input->dtype);
+    }
+    if (n == 0)
+        return TB200_OK;
+    return post_launch(ctx, "clamp");
+}
+
+// =================================================================================================== ADD
+extern "C" tb200_status tb200_add(tb200_ctx* ctx, const tb200_tensor* a, const tb200_tensor* b, tb200_tensor* output)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !a || !b || !output, "OpAdd: null operand");
+    // BinaryNodeBase::checkTensorAttributes / broadcast (reference_model/src/ops/ewise_binary.cpp:40-111)
+    TB200_ERROR_IF(ctx, a->rank != b->rank || a->dtype != b->dtype, "Binary operator input types must match");
+    TB200_ERROR_IF(ctx, output->rank != a->rank, "Binary operators ADD lhs input and output rank/shape must match");
+    TB200_ERROR_IF(ctx, output->dtype != a->dtype, "Binary operator type doesn't match");
+    BcastDev bc;
+    memset(&bc, 0, sizeof(bc));
+    bc.rank       = a->rank;
+    bc.same_shape = 1;
+    for (int i = 0; i < a->rank; i++)
+    {
+        int cs = a->shape[i];
+        if (cs == 1)
+            cs = b->shape[i];
+        else
+            TB200_ERROR_IF(ctx, b->shape[i] != 1 && b->shape[i] != cs,
+                           "Broadcast_shape failure, input shapes are not compatible");
+        TB200_ERROR_IF(ctx, cs != output->shape[i], "Broadcast_shape failure, calculated_shape and result_shape don't match");
+        bc.oshape[i] = output->shape[i];
+        if (a->shape[i] != output->shape[i] || b->shape[i] != output->shape[i])
+            bc.same_shape = 0;
+    }
+    int64_t as = 1, bs = 1;
+    for (int i = a->rank - 1; i >= 0; i--)
+    {
+        bc.astride[i] = (a->shape[i] == 1 && output->shape[i] != 1) ? 0 : as;
+        bc.bstride[i] = (b->shape[i] == 1 && output->shape[i] != 1) ? 0 : bs;
+        as *= a->shape[i];
+        bs *= b->shape[i];
+    }
+    const int64_t n = numel(output);
+    if (n == 0)
+        return TB200_OK;
+    if (((reinterpret_cast<uintptr_t>(a->data) | reinterpret_cast<uintptr_t>(b->data) |
+          reinterpret_cast<uintptr_t>(output->data)) & 15) != 0 && bc.same_shape)
+    {
+        // unaligned views take the indexed path
+        bc.same_shape = 0;
+    }
+    const int block = 256;
+    const int grid  = grid_for(ctx, bc.same_shape ? std::max<int64_t>(1, n / 4) : n, block);
+    switch (a->dtype)
+    {
+        case TB200_INT32:
+            add_kernel<int32_t><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const int32_t*>(a->data), reinterpret_cast<const int32_t*>(b->data), reinterpret_cast<int32_t*>(output->data), n, bc, ctx->d_status);
+            break;
+        case TB200_FP32:
+            add_kernel<float><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const float*>(a->data), reinterpret_cast<const float*>(b->data), reinterpret_cast<float*>(output->data), n, bc, ctx->d_status);
+            break;
+        case TB200_FP16:
+            add_kernel<__half><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const __half*>(a->data), reinterpret_cast<const __half*>(b->data), reinterpret_cast<__half*>(output->data), n, bc, ctx->d_status);
+            break;
+        case TB200_BF16:
+            add_kernel<__nv_bfloat16><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const __nv_bfloat16*>(a->data), reinterpret_cast<const __nv_bfloat16*>(b->data), reinterpret_cast<__nv_bfloat16*>(output->data), n, bc, ctx->d_status);
+            break;
+        default:
+            // integer ADD exists for INT32 only (reference_model/src/ops/op_factory.cpp:189-195)
+            return fail(ctx, TB200_ERROR, "OpAdd: unsupported TOSA_REF_TYPE %d", (int)a->dtype);
+    }
+    return post_launch(ctx, "add");
+}
+
+extern "C" tb200_status tb200_residual_add(tb200_ctx* ctx, const tb200_tensor* a, const tb200_rescale_attr* a_attr,
+                                           const tb200_tensor* b, const tb200_rescale_attr* b_attr,
+                                           const tb200_rescale_attr* out_attr, int32_t has_clamp, int32_t clamp_min,
+                                           int32_t clamp_max, tb200_tensor* output)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !a || !b || !output || !a_attr || !b_attr || !out_attr, "residual_add: null operand");
+    TB200_ERROR_IF(ctx, !same_shape(a, b) || !same_shape(a, output), "residual_add: operand shapes differ");
+    TB200_ERROR_IF(ctx, a->dtype != TB200_INT8 || b->dtype != TB200_INT8 || output->dtype != TB200_INT8,
+                   "residual_add: INT8 tensors only");
+    TB200_ERROR_IF(ctx, has_clamp && clamp_max < clamp_min, "OpClamp: max smaller than min");
+    const int C = a->rank > 0 ? a->shape[a->rank - 1] : 1;
+    ResidualDev r;
+    memset(&r, 0, sizeof(r));
+    tb200_status st = make_rescale_dev(ctx, a_attr, TB200_INT8, TB200_INT32, C, &r.ra);
+    if (st == TB200_OK)
+        st = make_rescale_dev(ctx, b_attr, TB200_INT8, TB200_INT32, C, &r.rb);
+    if (st == TB200_OK)
+        st = make_rescale_dev(ctx, out_attr, TB200_INT32, TB200_INT8, C, &r.ro);
+    if (st != TB200_OK)
+        return st;
+    r.has_clamp = has_clamp;
+    r.clamp_min = clamp_min;
+    r.clamp_max = clamp_max;
+    const int64_t n = numel(a);
+    if (n == 0)
+        return TB200_OK;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(a->data) | reinterpret_cast<uintptr_t>(b->data) |
+                           reinterpret_cast<uintptr_t>(output->data)) & 15) == 0;
+    const bool pc = a_attr->per_channel || b_attr->per_channel || out_attr->per_channel;
+    const int block = 256;
+    if (aligned && n % 16 == 0 && (!pc || C % 16 == 0))
+        residual_add_i8_kernel<16><<<grid_for(ctx, n / 16, block), block, 0, ctx->stream>>>(
+            reinterpret_cast<const int8_t*>(a->data), reinterpret_cast<const int8_t*>(b->data),
+            reinterpret_cast<int8_t*>(output->data), n, C, r, ctx->d_status);
+    else
+        residual_add_i8_kernel<1><<<grid_for(ctx, n, block), block, 0, ctx->stream>>>(
+            reinterpret_cast<const int8_t*>(a->data), reinterpret_cast<const int8_t*>(b->data),
+            reinterpret_cast<int8_t*>(output->data), n, C, r, ctx->d_status);
+    return post_launch(ctx, "residual_add_i8");
+}
+
+// =================================================================================================== pools
+static tb200_status pool_common(tb200_ctx* ctx, const char* op, const tb200_tensor* input, const int32_t* kernel,
+                                const int32_t* pad, const int32_t* stride, const tb200_tensor* output, PoolDev* p)
+{
+    TB200_ERROR_IF(ctx, !input || !output || !kernel || !pad || !stride, "%s: null operand", op);
+    TB200_ERROR_IF(ctx, input->rank != 4 || output->rank != 4, "%s: input and output must be rank 4", op);
+    TB200_ERROR_IF(ctx, input->dtype != output->dtype, "%s: input and output dtypes differ", op);
+    tb200_status st = check_pool_attr(ctx, op, input->shape[1], input->shape[2], output->shape[1], output->shape[2],
+                                      kernel, pad, stride);
+    if (st != TB200_OK)
+        return st;
+    TB200_ERROR_IF(ctx, input->shape[0] != output->shape[0], "%s: tensor batch mismatch %d != %d", op, input->shape[0],
+                   output->shape[0]);
+    TB200_ERROR_IF(ctx, input->shape[3] != output->shape[3], "%s: tensor channel mismatch %d != %d", op, input->shape[3],
+                   output->shape[3]);
+    p->N = input->shape[0]; p->IH = input->shape[1]; p->IW = input->shape[2]; p->C = input->shape[3];
+    p->OH = output->shape[1]; p->OW = output->shape[2];
+    p->ky = kernel[0]; p->kx = kernel[1]; p->pad_t = pad[0]; p->pad_l = pad[2]; p->sy = stride[0]; p->sx = stride[1];
+    return TB200_OK;
+}
+
+extern "C" tb200_status tb200_max_pool2d(tb200_ctx* ctx, const tb200_tensor* input, const int32_t kernel[2],
+                                         const int32_t pad[4], const int32_t stride[2], tb200_tensor* output)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    PoolDev p;
+    tb200_status st = pool_common(ctx, "OpMaxPool2d", input, kernel, pad, stride, output, &p);
+    if (st != TB200_OK)
+        return st;
+    const int64_t n = numel(output);
+    if (n == 0)
+        return TB200_OK;
+    const int block = 256;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(input->data) | reinterpret_cast<uintptr_t>(output->data)) & 15) == 0;
+    switch (input->dtype)
+    {
+        case TB200_INT8:
+            if (p.C % 16 == 0 && aligned && ctx->policy == 0)
+                max_pool_i8x16_kernel<<<grid_for(ctx, n / 16, block), block, 0, ctx->stream>>>(
+                    reinterpret_cast<const int8_t*>(input->data), reinterpret_cast<int8_t*>(output->data), p);
+            else
+                max_pool_kernel<int8_t, int32_t><<<grid_for(ctx, n, block), block, 0, ctx->stream>>>(
+                    reinterpret_cast<const int8_t*>(input->data), reinterpret_cast<int8_t*>(output->data), p, -128);
+            break;
+        case TB200_INT16:
+            max_pool_kernel<int16_t, int32_t><<<grid_for(ctx, n, block), block, 0, ctx->stream>>>(
+                reinterpret_cast<const int16_t*>(input->data), reinterpret_cast<int16_t*>(output->data), p, -32768);
+            break;
+        case TB200_FP16:
+            max_pool_kernel<__half, float><<<grid_for(ctx, n, block), block, 0, ctx->stream>>>(
+                reinterpret_cast<const __half*>(input->data), reinterpret_cast<__half*>(output->data), p, -65504.0f);
+            break;
+        case TB200_BF16:
+            max_pool_kernel<__nv_bfloat16, float><<<grid_for(ctx, n, block), block, 0, ctx->stream>>>(
+                reinterpret_cast<const __nv_bfloat16*>(input->data), reinterpret_cast<__nv_bfloat16*>(output->data), p,
+                -3.3895313892515355e38f);
+            break;
+        case TB200_FP32:
+            max_pool_kernel<float, float><<<grid_for(ctx, n, block), block, 0, ctx->stream>>>(
+                reinterpret_cast<const float*>(input->data), reinterpret_cast<float*>(output->data), p, -3.402823466e38f);
+            break;
+        default:
+            return fail(ctx, TB200_ERROR, "OpMaxPool2d: unsupported dtype %d", (int)input->dtype);
+    }
+    return post_launch(ctx, "max_pool2d");
+}
+
+extern "C" tb200_status tb200_avg_pool2d(tb200_ctx* ctx, const tb200_tensor* input, const int32_t kernel[2],
+                                         const int32_t pad[4], const int32_t stride[2], int32_t input_zp,
+                                         int32_t output_zp, tb200_tensor* output)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    PoolDev p;
+    tb200_status st = pool_common(ctx, "OpAvgPool2d", input, kernel, pad, stride, output, &p);
+    if (st != TB200_OK)
+        return st;
+    // reference_model/src/ops/tensor_ops.cpp:568-571
+    TB200_ERROR_IF(ctx, input->dtype != TB200_INT8 && input_zp != 0, "OpAvgPool2d: Input zeropoint must be zero for non int8_t data");
+    TB200_ERROR_IF(ctx, input->dtype != TB200_INT8 && output_zp != 0, "OpAvgPool2d: Output zeropoint must be zero for non int8_t data");
+    TB200_ERROR_IF(ctx, input_zp < -128 || input_zp > 127 || output_zp < -128 || output_zp > 127,
+                   "OpAvgPool2d: zero point outside the int8 range");
+    const int64_t n = numel(output);
+    if (n == 0)
+        return TB200_OK;
+    const int block = 256;
+    const int grid  = grid_for(ctx, n, block);
+    switch (input->dtype)
+    {
+        case TB200_INT8:
+            avg_pool_int_kernel<int8_t><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const int8_t*>(input->data), reinterpret_cast<int8_t*>(output->data), p, input_zp, output_zp, -128, 127, ctx->d_status);
+            break;
+        case TB200_INT16:
+            avg_pool_int_kernel<int16_t><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const int16_t*>(input->data), reinterpret_cast<int16_t*>(output->data), p, 0, 0, -32768, 32767, ctx->d_status);
+            break;
+        case TB200_FP16:
+            avg_pool_fp_kernel<__half><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const __half*>(input->data), reinterpret_cast<__half*>(output->data), p);
+            break;
+        case TB200_BF16:
+            avg_pool_fp_kernel<__nv_bfloat16><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const __nv_bfloat16*>(input->data), reinterpret_cast<__nv_bfloat16*>(output->data), p);
+            break;
+        case TB200_FP32:
+            avg_pool_fp_kernel<float><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const float*>(input->data), reinterpret_cast<float*>(output->data), p);
+            break;
+        default:
+            return fail(ctx, TB200_ERROR, "OpAvgPool2d: unsupported dtype %d", (int)input->dtype);
+    }
+    return post_launch(ctx, "avg_pool2d");
+}
+
+// =================================================================================================== host buffers
+extern "C" tb200_status tb200_matmul_host(tb200_ctx* ctx, tb200_dtype in_dtype, tb200_dtype out_dtype, const void* a,
+                                          const void* b, int32_t N, int32_t H, int32_t C, int32_t W, int32_t a_zp,
+                                          int32_t b_zp, void* out)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !a || !b || !out, "matmul_host: null buffer");
+    tb200_tensor *ta = nullptr, *tb = nullptr, *to = nullptr;
+    const int32_t sa[3] = { N, H, C }, sb[3] = { N, C, W }, so[3] = { N, H, W };
+    tb200_status st = tb200_tensor_alloc(ctx, in_dtype, 3, sa, &ta);
+    if (st == TB200_OK)
+        st = tb200_tensor_alloc(ctx, in_dtype, 3, sb, &tb);
+    if (st == TB200_OK)
+        st = tb200_tensor_alloc(ctx, out_dtype, 3, so, &to);
+    if (st == TB200_OK)
+        st = tb200_tensor_upload(ctx, ta, a, ta->bytes);
+    if (st == TB200_OK)
+        st = tb200_tensor_upload(ctx, tb, b, tb->bytes);
+    if (st == TB200_OK)
+        st = tb200_matmul(ctx, ta, tb, a_zp, b_zp, nullptr, to);
+    if (st == TB200_OK)
+        st = tb200_tensor_download(ctx, to, out, to->bytes);
+    tb200_tensor_free(ctx, ta);
+    tb200_tensor_free(ctx, tb);
+    tb200_tensor_free(ctx, to);
+    return st;
+}

@@ -1,0 +1,175 @@
+// Shared host-side definitions of the tb200 library: context, tensor handle, status helpers.
+#pragma once
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <cuda_runtime.h>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/tb200.h"
+
+struct tb200_tensor
+{
+    tb200_dtype dtype;
+    int rank;
+    int32_t shape[6];
+    void* data;
+    size_t bytes;
+    bool owns;
+};
+
+// Bits of the device status word (one int32 per context, OR-ed into by kernels).
+enum : int
+{
+    TB200_DEV_UNPREDICTABLE = 1,    // a REQUIRE condition of the reference failed for some element
+    TB200_DEV_TIMEOUT       = 2,    // a bounded pipeline wait gave up (internal error)
+};
+
+struct tb200_ctx
+{
+    int device           = 0;
+    cudaStream_t stream  = nullptr;
+    bool owns_stream     = false;
+    int* d_status        = nullptr;    // device status word
+    int* h_status        = nullptr;    // pinned mirror
+    void* scratch        = nullptr;    // grow-on-demand device scratch (zero-point sums, weight tables)
+    size_t scratch_bytes = 0;
+    uint64_t launches    = 0;
+    int policy           = 0;
+    int num_sms          = 148;
+    const char* last_kernel = "none";
+    std::string err;
+    // optional CUDA-event brackets around the main kernels (tb200_timer_enable)
+    bool timing = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;
+};
+
+namespace tb200
+{
+
+inline size_t dtype_size(tb200_dtype d)
+{
+    switch (d)
+    {
+        case TB200_INT8:
+        case TB200_UINT8:
+            return 1;
+        case TB200_BF16:
+        case TB200_FP16:
+        case TB200_INT16:
+        case TB200_UINT16:
+            return 2;
+        case TB200_FP32:
+        case TB200_INT32:
+            return 4;
+    }
+    return 0;
+}
+
+inline bool dtype_is_float(tb200_dtype d)
+{
+    return d == TB200_FP16 || d == TB200_BF16 || d == TB200_FP32;
+}
+
+inline int64_t numel(const tb200_tensor* t)
+{
+    int64_t n = 1;
+    for (int i = 0; i < t->rank; i++)
+        n *= t->shape[i];
+    return n;
+}
+
+inline tb200_status fail(tb200_ctx* ctx, tb200_status st, const char* fmt, ...)
+{
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    if (ctx)
+        ctx->err = buf;
+    return st;
+}
+
+#define TB200_CUDA_CHECK(ctx, expr)                                                                        \
+    do                                                                                                     \
+    {                                                                                                      \
+        cudaError_t e__ = (expr);                                                                          \
+        if (e__ != cudaSuccess)                                                                            \
+            return tb200::fail((ctx), TB200_INTERNAL, "%s failed: %s", #expr, cudaGetErrorString(e__));    \
+    } while (0)
+
+// The reference's ERROR_IF: a violated graph rule ends evaluation with TOSA_ERROR
+// (reference_model/include/func_debug.h:112-178).
+#define TB200_ERROR_IF(ctx, cond, ...)                                                                     \
+    do                                                                                                     \
+    {                                                                                                      \
+        if (cond)                                                                                          \
+            return tb200::fail((ctx), TB200_ERROR, __VA_ARGS__);                                           \
+    } while (0)
+
+tb200_status ensure_scratch(tb200_ctx* ctx, size_t bytes);
+tb200_status post_launch(tb200_ctx* ctx, const char* kernel_name, int n_launches = 1);
+// Event brackets for tb200_timer_*: call timer_begin before and timer_end after the main kernel's launch.
+void timer_begin(tb200_ctx* ctx);
+void timer_end(tb200_ctx* ctx);
+
+// ----------------------------------------------------------------------------------------------
+// Tensor-core GEMM / implicit-GEMM convolution (tc_gemm.cu)
+// ----------------------------------------------------------------------------------------------
+enum TcEpilogue : int
+{
+    TC_EPI_I32     = 0,    // int32 out = acc + row_corr[row] + col_corr[col]
+    TC_EPI_RESCALE = 1,    // int8/int16/int32 out = clamp(rescale(acc + col_corr[col]) + out_zp)
+    TC_EPI_FLOAT   = 2,    // fp16/bf16/fp32 out = clamp(acc + bias[col])
+};
+
+struct TcProblem
+{
+    // element type of A and B: TB200_INT8, TB200_FP16 or TB200_BF16
+    tb200_dtype in_dtype;
+    // A: activation tensor viewed as [N][IH][IW][IC] (matmul: [1][batch][M][K])
+    const void* a;
+    int N, IH, IW, IC;
+    // output pixel grid [N][OH][OW] and columns OC (matmul: [1][batch][M] x Ncols)
+    int OH, OW, OC;
+    int KH, KW;
+    int pad_t, pad_l, stride_y, stride_x, dil_y, dil_x;
+    // B: K-major weights [OC][KH*KW*IC] (b_mn_major == 0) or MN-major [batch][K][OC] (b_mn_major == 1, matmul)
+    const void* b;
+    int b_mn_major;
+    // epilogue
+    int epi;
+    tb200_dtype out_dtype;
+    void* out;
+    const int32_t* row_corr;    // [N*OH*OW] or null
+    const int32_t* col_corr;    // int32 [OC] (or [batch][OC] when col_corr_ystride != 0) or null
+    int col_corr_ystride;
+    const float* bias_f;        // TC_EPI_FLOAT: [OC] or [1] or null
+    int bias_n;
+    // zero-point border fix for padded convolutions: prefix sums over taps of the per-channel weight sums,
+    // table [(KH+1)*(KW+1)][OC]; used when in_zp != 0 and the tile touches the border
+    const int32_t* wsum_prefix;
+    int32_t in_zp;
+    // rescale (TC_EPI_RESCALE)
+    const int32_t* multiplier;
+    const int8_t* shift;
+    int per_channel, double_round;
+    int32_t out_zp;
+    int32_t clamp_lo, clamp_hi;    // also the dtype range
+    float clamp_lo_f, clamp_hi_f;
+    int has_clamp;
+};
+
+// Returns TB200_OK and launches, or TB200_ERROR with ctx->err set when the shape does not qualify
+// (the caller then uses the CUDA-core kernels).
+bool tc_gemm_supported(const TcProblem& p, std::string* why);
+tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& p);
+
+// fp32 SGEMM on CUDA cores (sgemm_f32.cu): out[n] = a[n] x b[n], a [N,H,C], b [N,C,W]
+tb200_status sgemm_f32_launch(tb200_ctx* ctx, const float* a, const float* b, float* out, int N, int H, int C, int W);
+
+}    // namespace tb200

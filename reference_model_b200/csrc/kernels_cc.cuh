@@ -1,0 +1,925 @@
+// CUDA-core kernels: elementwise RESCALE / CLAMP / ADD / residual join, pooling, depthwise convolution,
+// general direct CONV2D / MATMUL (any shape; also the on-device cross-check of the tensor-core path), and the
+// small preparation kernels (zero-point row / column sums, per-tap weight sums).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <type_traits>
+
+#include "common.h"
+#include "rescale_math.cuh"
+
+namespace tb200
+{
+
+// ------------------------------------------------------------------------------------------------ type helpers
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v)
+{
+    return v;
+}
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v)
+{
+    return __half2float(v);
+}
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v)
+{
+    return __bfloat162float(v);
+}
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v)
+{
+    return v;
+}
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v)
+{
+    return __float2half_rn(v);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v)
+{
+    return __float2bfloat16_rn(v);
+}
+
+// ------------------------------------------------------------------------------------------------ RESCALE
+struct RescaleDev
+{
+    const void* mult;
+    const int8_t* shift;
+    int mult_is_i16, per_channel, scale32, rounding;
+    int64_t in_zp_ext, out_zp_ext;
+    int in_bits, out_bits;
+    int in_unsigned, out_unsigned;
+    int64_t qmin, qmax;
+};
+
+__device__ __forceinline__ int32_t rescale_elem(int32_t raw, int ch, const RescaleDev& r, bool& bad)
+{
+    const int64_t v64 = value_extend64_dev(raw, r.in_bits, r.in_unsigned != 0) - r.in_zp_ext;
+    const int c       = r.per_channel ? ch : 0;
+    const int32_t m   = r.mult_is_i16 ? (int32_t) reinterpret_cast<const int16_t*>(r.mult)[c]
+                                      : reinterpret_cast<const int32_t*>(r.mult)[c];
+    const int32_t s   = (int32_t)r.shift[c];
+    int32_t scaled;
+    bool b = false;
+    if (r.rounding != TB200_INEXACT_ROUND)
+    {
+        if (r.scale32)
+            scaled = apply_scale_32_dev((int32_t)v64, m, s, r.rounding == TB200_DOUBLE_ROUND, b);
+        else
+            scaled = apply_scale_16_dev(v64, (int16_t)m, s, b);
+    }
+    else
+    {
+        // INEXACT_ROUND in fp32 maths (reference_model/src/ops/type_conversion.cpp:318-323)
+        const float res = __fmul_rn(__fmul_rn((float)v64, (float)m), exp2f((float)(-s)));
+        scaled          = (int32_t)rintf(res);
+    }
+    int64_t z = (int64_t)scaled + r.out_zp_ext;
+    b |= (z > 2147483647LL) || (z < -2147483648LL);
+    z = z < r.qmin ? r.qmin : z;
+    z = z > r.qmax ? r.qmax : z;
+    bad |= b;
+    return b ? 0 : (int32_t)z;
+}
+
+template <typename TIn, typename TOut, int VEC>
+__global__ void rescale_kernel(const TIn* __restrict__ in, TOut* __restrict__ out, int64_t n, int C, RescaleDev r,
+                               int* status)
+{
+    bool bad            = false;
+    const int64_t nvec  = n / VEC;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += step)
+    {
+        TIn vi[VEC];
+        TOut vo[VEC];
+        if (VEC == 4)
+        {
+            if (sizeof(TIn) == 4)
+                *reinterpret_cast<int4*>(vi) = reinterpret_cast<const int4*>(in)[i];
+            else if (sizeof(TIn) == 2)
+                *reinterpret_cast<int2*>(vi) = reinterpret_cast<const int2*>(in)[i];
+            else
+                *reinterpret_cast<int*>(vi) = reinterpret_cast<const int*>(in)[i];
+        }
+        else
+            vi[0] = in[i];
+        const int ch0 = (int)((i * VEC) % C);
+#pragma unroll
+        for (int j = 0; j < VEC; j++)
+            vo[j] = (TOut)rescale_elem((int32_t)vi[j], ch0 + j, r, bad);
+        if (VEC == 4)
+        {
+            if (sizeof(TOut) == 4)
+                reinterpret_cast<int4*>(out)[i] = *reinterpret_cast<int4*>(vo);
+            else if (sizeof(TOut) == 2)
+                reinterpret_cast<int2*>(out)[i] = *reinterpret_cast<int2*>(vo);
+            else
+                reinterpret_cast<int*>(out)[i] = *reinterpret_cast<int*>(vo);
+        }
+        else
+            out[i] = vo[0];
+    }
+    if (bad)
+        atomicOr(status, TB200_DEV_UNPREDICTABLE);
+}
+
+// Residual join: out = clamp(rescale_o(rescale_a(a) + rescale_b(b))), 16 int8 values per thread.
+struct ResidualDev
+{
+    RescaleDev ra, rb, ro;
+    int has_clamp;
+    int32_t clamp_min, clamp_max;
+};
+
+template <int VEC>
+__global__ void residual_add_i8_kernel(const int8_t* __restrict__ a, const int8_t* __restrict__ b,
+                                       int8_t* __restrict__ out, int64_t n, int C, ResidualDev r, int* status)
+{
+    bool bad           = false;
+    const int64_t nvec = n / VEC;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += step)
+    {
+        int8_t va[VEC], vb[VEC], vo[VEC];
+        if (VEC == 16)
+        {
+            *reinterpret_cast<int4*>(va) = reinterpret_cast<const int4*>(a)[i];
+            *reinterpret_cast<int4*>(vb) = reinterpret_cast<const int4*>(b)[i];
+        }
+        else
+        {
+            va[0] = a[i];
+            vb[0] = b[i];
+        }
+        const int ch0 = (int)((i * VEC) % C);
+#pragma unroll
+        for (int j = 0; j < VEC; j++)
+        {
+            const int32_t x = rescale_elem((int32_t)va[j], ch0 + j, r.ra, bad);
+            const int32_t y = rescale_elem((int32_t)vb[j], ch0 + j, r.rb, bad);
+            const int64_t s = (int64_t)x + (int64_t)y;
+            bad |= (s > 2147483647LL) || (s < -2147483648LL);
+            int32_t z = rescale_elem((int32_t)(uint32_t)((uint32_t)x + (uint32_t)y), ch0 + j, r.ro, bad);
+            if (r.has_clamp)
+            {
+                z = z >= r.clamp_min ? z : r.clamp_min;
+                z = z < r.clamp_max ? z : r.clamp_max;
+            }
+            vo[j] = (int8_t)z;
+        }
+        if (VEC == 16)
+            reinterpret_cast<int4*>(out)[i] = *reinterpret_cast<int4*>(vo);
+        else
+            out[i] = vo[0];
+    }
+    if (bad)
+        atomicOr(status, TB200_DEV_UNPREDICTABLE);
+}
+
+// ------------------------------------------------------------------------------------------------ CLAMP
+template <typename T>
+__global__ void clamp_int_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t n, int32_t lo, int32_t hi)
+{
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    constexpr int VEC  = 16 / sizeof(T);
+    const int64_t nvec = n / VEC;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += step)
+    {
+        T v[VEC];
+        *reinterpret_cast<int4*>(v) = reinterpret_cast<const int4*>(in)[i];
+#pragma unroll
+        for (int j = 0; j < VEC; j++)
+        {
+            int32_t x = (int32_t)v[j];
+            x         = x >= lo ? x : lo;
+            x         = x < hi ? x : hi;
+            v[j]      = (T)x;
+        }
+        reinterpret_cast<int4*>(out)[i] = *reinterpret_cast<int4*>(v);
+    }
+    for (int64_t i = nvec * VEC + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step)
+    {
+        int32_t x = (int32_t)in[i];
+        x         = x >= lo ? x : lo;
+        x         = x < hi ? x : hi;
+        out[i]    = (T)x;
+    }
+}
+
+// applyClip then fpTrunc (reference_model/src/ops/activation_funcs.cpp:105-111, src/arith_util.h:340-413)
+template <typename T>
+__device__ __forceinline__ T clamp_fp_elem(T raw, float lo, float hi, int nan_ignore)
+{
+    float v = to_f32<T>(raw);
+    if (isnan(v))
+        v = nan_ignore ? lo : v;
+    else
+        v = (v >= lo) ? v : lo;
+    if (!isnan(v))
+        v = (v < hi) ? v : hi;
+    return from_f32<T>(v);
+}
+
+template <typename T>
+__global__ void clamp_fp_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t n, float lo, float hi,
+                                int nan_ignore)
+{
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    constexpr int VEC  = 16 / sizeof(T);
+    const int64_t nvec = n / VEC;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += step)
+    {
+        T v[VEC];
+        *reinterpret_cast<int4*>(v) = reinterpret_cast<const int4*>(in)[i];
+#pragma unroll
+        for (int j = 0; j < VEC; j++)
+            v[j] = clamp_fp_elem<T>(v[j], lo, hi, nan_ignore);
+        reinterpret_cast<int4*>(out)[i] = *reinterpret_cast<int4*>(v);
+    }
+    for (int64_t i = nvec * VEC + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step)
+        out[i] = clamp_fp_elem<T>(in[i], lo, hi, nan_ignore);
+}
+
+// ------------------------------------------------------------------------------------------------ ADD
+struct BcastDev
+{
+    int rank;
+    int oshape[6];
+    int64_t astride[6], bstride[6];    // 0 where the operand broadcasts
+    int same_shape;
+};
+
+template <typename T>
+__device__ __forceinline__ T add_elem(T a, T b, bool& bad);
+template <>
+__device__ __forceinline__ int32_t add_elem<int32_t>(int32_t a, int32_t b, bool& bad)
+{
+    const int64_t s = (int64_t)a + (int64_t)b;
+    bad |= (s > 2147483647LL) || (s < -2147483648LL);
+    return (int32_t)((uint32_t)a + (uint32_t)b);
+}
+template <>
+__device__ __forceinline__ float add_elem<float>(float a, float b, bool&)
+{
+    return a + b;
+}
+template <>
+__device__ __forceinline__ __half add_elem<__half>(__half a, __half b, bool&)
+{
+    return __float2half_rn(__half2float(a) + __half2float(b));
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 add_elem<__nv_bfloat16>(__nv_bfloat16 a, __nv_bfloat16 b, bool&)
+{
+    return __float2bfloat16_rn(__bfloat162float(a) + __bfloat162float(b));
+}
+
+template <typename T>
+__global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n,
+                           BcastDev bc, int* status)
+{
+    bool bad           = false;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    if (bc.same_shape)
+    {
+        constexpr int VEC  = 16 / sizeof(T);
+        const int64_t nvec = n / VEC;
+        for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += step)
+        {
+            T va[VEC], vb[VEC];
+            *reinterpret_cast<int4*>(va) = reinterpret_cast<const int4*>(a)[i];
+            *reinterpret_cast<int4*>(vb) = reinterpret_cast<const int4*>(b)[i];
+#pragma unroll
+            for (int j = 0; j < VEC; j++)
+                va[j] = add_elem<T>(va[j], vb[j], bad);
+            reinterpret_cast<int4*>(out)[i] = *reinterpret_cast<int4*>(va);
+        }
+        for (int64_t i = nvec * VEC + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step)
+            out[i] = add_elem<T>(a[i], b[i], bad);
+    }
+    else
+    {
+        for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step)
+        {
+            int64_t rem = i, ai = 0, bi = 0;
+            for (int d = bc.rank - 1; d >= 0; d--)
+            {
+                const int64_t c = rem % bc.oshape[d];
+                rem /= bc.oshape[d];
+                ai += c * bc.astride[d];
+                bi += c * bc.bstride[d];
+            }
+            out[i] = add_elem<T>(a[ai], b[bi], bad);
+        }
+    }
+    if (bad)
+        atomicOr(status, TB200_DEV_UNPREDICTABLE);
+}
+
+// ------------------------------------------------------------------------------------------------ pooling
+struct PoolDev
+{
+    int N, IH, IW, C, OH, OW;
+    int ky, kx, pad_t, pad_l, sy, sx;
+};
+
+// MAX_POOL2D on int8 NHWC, 16 channels per thread (C % 16 == 0)
+__global__ void max_pool_i8x16_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ out, PoolDev p)
+{
+    const int cv        = p.C / 16;
+    const int64_t total = (int64_t)p.N * p.OH * p.OW * cv;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int c16 = (int)(i % cv);
+        int64_t r     = i / cv;
+        const int ox  = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        const int n  = (int)(r / p.OH);
+        uint32_t m[4] = { 0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u };    // four lanes of -128
+        for (int ky = 0; ky < p.ky; ky++)
+        {
+            const int y = oy * p.sy - p.pad_t + ky;
+            if (y < 0 || y >= p.IH)
+                continue;
+            for (int kx = 0; kx < p.kx; kx++)
+            {
+                const int x = ox * p.sx - p.pad_l + kx;
+                if (x < 0 || x >= p.IW)
+                    continue;
+                const uint4 v =
+                    *reinterpret_cast<const uint4*>(in + (((int64_t)n * p.IH + y) * p.IW + x) * p.C + c16 * 16);
+                m[0] = __vmaxs4(m[0], v.x);
+                m[1] = __vmaxs4(m[1], v.y);
+                m[2] = __vmaxs4(m[2], v.z);
+                m[3] = __vmaxs4(m[3], v.w);
+            }
+        }
+        *reinterpret_cast<uint4*>(out + (((int64_t)n * p.OH + oy) * p.OW + ox) * p.C + c16 * 16) =
+            make_uint4(m[0], m[1], m[2], m[3]);
+    }
+}
+
+// general MAX_POOL2D, one element per thread; `lowest` is the padding value of the dtype
+template <typename T, typename TCmp>
+__global__ void max_pool_kernel(const T* __restrict__ in, T* __restrict__ out, PoolDev p, TCmp lowest)
+{
+    const int64_t total = (int64_t)p.N * p.OH * p.OW * p.C;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int c  = (int)(i % p.C);
+        int64_t r    = i / p.C;
+        const int ox = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        const int n  = (int)(r / p.OH);
+        TCmp m       = lowest;
+        bool nan     = false;
+        for (int ky = 0; ky < p.ky; ky++)
+            for (int kx = 0; kx < p.kx; kx++)
+            {
+                const int y = oy * p.sy - p.pad_t + ky;
+                const int x = ox * p.sx - p.pad_l + kx;
+                if (y < 0 || y >= p.IH || x < 0 || x >= p.IW)
+                    continue;
+                const TCmp v = (TCmp)in[(((int64_t)n * p.IH + y) * p.IW + x) * p.C + c];
+                if constexpr (std::is_floating_point<TCmp>::value)
+                {
+                    if (isnan(v))
+                        nan = true;
+                }
+                m = (m >= v) ? m : v;
+            }
+        if constexpr (std::is_floating_point<TCmp>::value)
+        {
+            if (nan)
+                m = NAN;    // NaN-propagating mode
+        }
+        out[i] = (T)m;
+    }
+}
+
+// AVG_POOL2D integer path (reference_model/src/ops/tensor_ops.cpp:604-653)
+template <typename T>
+__global__ void avg_pool_int_kernel(const T* __restrict__ in, T* __restrict__ out, PoolDev p, int32_t in_zp,
+                                    int32_t out_zp, int32_t qmin, int32_t qmax, int* status)
+{
+    const int64_t total = (int64_t)p.N * p.OH * p.OW * p.C;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    bool bad            = false;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int c  = (int)(i % p.C);
+        int64_t r    = i / p.C;
+        const int ox = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        const int n  = (int)(r / p.OH);
+        int32_t acc  = 0;
+        int count    = 0;
+        for (int ky = 0; ky < p.ky; ky++)
+            for (int kx = 0; kx < p.kx; kx++)
+            {
+                const int y = oy * p.sy - p.pad_t + ky;
+                const int x = ox * p.sx - p.pad_l + kx;
+                if (y < 0 || y >= p.IH || x < 0 || x >= p.IW)
+                    continue;
+                acc += (int32_t)in[(((int64_t)n * p.IH + y) * p.IW + x) * p.C + c] - in_zp;
+                count++;
+            }
+        int32_t mult, shift;
+        reciprocal_scale_dev(count, mult, shift);
+        bool b    = false;
+        int32_t v = apply_scale_32_dev(acc, mult, shift, false, b);
+        if (b)
+            v = 0;
+        bad |= b;
+        v = (int32_t)((uint32_t)v + (uint32_t)out_zp);
+        v = v > qmin ? v : qmin;
+        v = v < qmax ? v : qmax;
+        out[i] = (T)v;
+    }
+    if (bad)
+        atomicOr(status, TB200_DEV_UNPREDICTABLE);
+}
+
+template <typename T>
+__global__ void avg_pool_fp_kernel(const T* __restrict__ in, T* __restrict__ out, PoolDev p)
+{
+    const int64_t total = (int64_t)p.N * p.OH * p.OW * p.C;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int c  = (int)(i % p.C);
+        int64_t r    = i / p.C;
+        const int ox = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        const int n  = (int)(r / p.OH);
+        float acc    = 0.f;
+        int count    = 0;
+        for (int ky = 0; ky < p.ky; ky++)
+            for (int kx = 0; kx < p.kx; kx++)
+            {
+                const int y = oy * p.sy - p.pad_t + ky;
+                const int x = ox * p.sx - p.pad_l + kx;
+                if (y < 0 || y >= p.IH || x < 0 || x >= p.IW)
+                    continue;
+                acc += to_f32<T>(in[(((int64_t)n * p.IH + y) * p.IW + x) * p.C + c]);
+                count++;
+            }
+        out[i] = from_f32<T>(acc / (float)count);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ direct conv
+struct ConvDev
+{
+    int N, IH, IW, IC, OH, OW, OC, KH, KW, M;    // M: depthwise multiplier
+    int pad_t, pad_l, sy, sx, dy, dx;
+    int32_t in_zp, w_zp;
+    int bias_n;
+    // optional fused epilogue
+    int has_rescale;
+    RescaleDev rs;
+    int has_clamp;
+    int32_t clamp_lo, clamp_hi;
+    float clamp_lo_f, clamp_hi_f;
+};
+
+// One thread per output element, channel fastest.  Integer: int32 accumulation of (in - in_zp)(w - w_zp)
+// over in-scope taps in ky, kx, ic order (reference_model/src/ops/tensor_ops.cpp:828-873).
+template <typename TOut>
+__global__ void conv2d_direct_i8_kernel(const int8_t* __restrict__ in, const int8_t* __restrict__ w,
+                                        const int32_t* __restrict__ bias, TOut* __restrict__ out, ConvDev p,
+                                        int* status)
+{
+    const int64_t total = (int64_t)p.N * p.OH * p.OW * p.OC;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    bool bad            = false;
+    const bool vec4 = (p.IC % 4) == 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int oc = (int)(i % p.OC);
+        int64_t r    = i / p.OC;
+        const int ox = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        const int n  = (int)(r / p.OH);
+        int32_t acc  = 0;
+        for (int ky = 0; ky < p.KH; ky++)
+        {
+            const int y = oy * p.sy + ky * p.dy - p.pad_t;
+            if (y < 0 || y >= p.IH)
+                continue;
+            for (int kx = 0; kx < p.KW; kx++)
+            {
+                const int x = ox * p.sx + kx * p.dx - p.pad_l;
+                if (x < 0 || x >= p.IW)
+                    continue;
+                const int8_t* ip = in + (((int64_t)n * p.IH + y) * p.IW + x) * p.IC;
+                const int8_t* wp = w + (((int64_t)oc * p.KH + ky) * p.KW + kx) * p.IC;
+                if (vec4)
+                {
+                    // sum (a - za)(b - zb) = sum ab - zb sum a - za sum b + n za zb, four lanes at a time
+                    int32_t sab = 0, sa = 0, sb = 0;
+                    for (int ic = 0; ic < p.IC; ic += 4)
+                    {
+                        const int a4 = *reinterpret_cast<const int*>(ip + ic);
+                        const int b4 = *reinterpret_cast<const int*>(wp + ic);
+                        sab          = __dp4a(a4, b4, sab);
+                        sa           = __dp4a(a4, 0x01010101, sa);
+                        sb           = __dp4a(b4, 0x01010101, sb);
+                    }
+                    acc += sab - p.w_zp * sa - p.in_zp * sb + p.IC * p.in_zp * p.w_zp;
+                }
+                else
+                {
+                    for (int ic = 0; ic < p.IC; ic++)
+                        acc += ((int32_t)ip[ic] - p.in_zp) * ((int32_t)wp[ic] - p.w_zp);
+                }
+            }
+        }
+        int32_t v = (int32_t)((uint32_t)bias[p.bias_n == 1 ? 0 : oc] + (uint32_t)acc);
+        if (p.has_rescale)
+        {
+            v = rescale_elem(v, oc, p.rs, bad);
+            if (p.has_clamp)
+            {
+                v = v >= p.clamp_lo ? v : p.clamp_lo;
+                v = v < p.clamp_hi ? v : p.clamp_hi;
+            }
+        }
+        out[i] = (TOut)v;
+    }
+    if (bad)
+        atomicOr(status, TB200_DEV_UNPREDICTABLE);
+}
+
+// Floating types: sequential fp32 accumulation, result (plus optional CLAMP) rounded once to the storage type.
+template <typename T>
+__global__ void conv2d_direct_fp_kernel(const T* __restrict__ in, const T* __restrict__ w, const T* __restrict__ bias,
+                                        T* __restrict__ out, ConvDev p)
+{
+    const int64_t total = (int64_t)p.N * p.OH * p.OW * p.OC;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int oc = (int)(i % p.OC);
+        int64_t r    = i / p.OC;
+        const int ox = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        const int n  = (int)(r / p.OH);
+        float acc    = 0.f;
+        for (int ky = 0; ky < p.KH; ky++)
+        {
+            const int y = oy * p.sy + ky * p.dy - p.pad_t;
+            if (y < 0 || y >= p.IH)
+                continue;
+            for (int kx = 0; kx < p.KW; kx++)
+            {
+                const int x = ox * p.sx + kx * p.dx - p.pad_l;
+                if (x < 0 || x >= p.IW)
+                    continue;
+                const T* ip = in + (((int64_t)n * p.IH + y) * p.IW + x) * p.IC;
+                const T* wp = w + (((int64_t)oc * p.KH + ky) * p.KW + kx) * p.IC;
+                for (int ic = 0; ic < p.IC; ic++)
+                    acc = fmaf(to_f32<T>(ip[ic]), to_f32<T>(wp[ic]), acc);
+            }
+        }
+        float v = to_f32<T>(bias[p.bias_n == 1 ? 0 : oc]) + acc;
+        if (p.has_clamp)
+        {
+            v = (v < p.clamp_lo_f) ? p.clamp_lo_f : v;
+            v = (v > p.clamp_hi_f) ? p.clamp_hi_f : v;
+        }
+        out[i] = from_f32<T>(v);
+    }
+}
+
+// DEPTHWISE_CONV2D, weights [KH,KW,C,M], output channel c*M+m (reference_model/src/ops/tensor_ops.cpp:1283-1325)
+template <typename TOut>
+__global__ void depthwise_direct_i8_kernel(const int8_t* __restrict__ in, const int8_t* __restrict__ w,
+                                           const int32_t* __restrict__ bias, TOut* __restrict__ out, ConvDev p,
+                                           int* status)
+{
+    const int OC        = p.IC * p.M;
+    const int64_t total = (int64_t)p.N * p.OH * p.OW * OC;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    bool bad            = false;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int oc = (int)(i % OC);
+        int64_t r    = i / OC;
+        const int ox = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        const int n  = (int)(r / p.OH);
+        const int c = oc / p.M, m = oc % p.M;
+        int32_t acc = 0;
+        for (int ky = 0; ky < p.KH; ky++)
+        {
+            const int y = oy * p.sy + ky * p.dy - p.pad_t;
+            if (y < 0 || y >= p.IH)
+                continue;
+            for (int kx = 0; kx < p.KW; kx++)
+            {
+                const int x = ox * p.sx + kx * p.dx - p.pad_l;
+                if (x < 0 || x >= p.IW)
+                    continue;
+                acc += ((int32_t)in[(((int64_t)n * p.IH + y) * p.IW + x) * p.IC + c] - p.in_zp) *
+                       ((int32_t)w[(((int64_t)ky * p.KW + kx) * p.IC + c) * p.M + m] - p.w_zp);
+            }
+        }
+        int32_t v = (int32_t)((uint32_t)bias[p.bias_n == 1 ? 0 : oc] + (uint32_t)acc);
+        if (p.has_rescale)
+        {
+            v = rescale_elem(v, oc, p.rs, bad);
+            if (p.has_clamp)
+            {
+                v = v >= p.clamp_lo ? v : p.clamp_lo;
+                v = v < p.clamp_hi ? v : p.clamp_hi;
+            }
+        }
+        out[i] = (TOut)v;
+    }
+    if (bad)
+        atomicOr(status, TB200_DEV_UNPREDICTABLE);
+}
+
+template <typename T>
+__global__ void depthwise_direct_fp_kernel(const T* __restrict__ in, const T* __restrict__ w,
+                                           const T* __restrict__ bias, T* __restrict__ out, ConvDev p)
+{
+    const int OC        = p.IC * p.M;
+    const int64_t total = (int64_t)p.N * p.OH * p.OW * OC;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int oc = (int)(i % OC);
+        int64_t r    = i / OC;
+        const int ox = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        const int n  = (int)(r / p.OH);
+        const int c = oc / p.M, m = oc % p.M;
+        float acc = 0.f;
+        for (int ky = 0; ky < p.KH; ky++)
+        {
+            const int y = oy * p.sy + ky * p.dy - p.pad_t;
+            if (y < 0 || y >= p.IH)
+                continue;
+            for (int kx = 0; kx < p.KW; kx++)
+            {
+                const int x = ox * p.sx + kx * p.dx - p.pad_l;
+                if (x < 0 || x >= p.IW)
+                    continue;
+                acc = fmaf(to_f32<T>(in[(((int64_t)n * p.IH + y) * p.IW + x) * p.IC + c]),
+                           to_f32<T>(w[(((int64_t)ky * p.KW + kx) * p.IC + c) * p.M + m]), acc);
+            }
+        }
+        float v = to_f32<T>(bias[p.bias_n == 1 ? 0 : oc]) + acc;
+        if (p.has_clamp)
+        {
+            v = (v < p.clamp_lo_f) ? p.clamp_lo_f : v;
+            v = (v > p.clamp_hi_f) ? p.clamp_hi_f : v;
+        }
+        out[i] = from_f32<T>(v);
+    }
+}
+
+// Depthwise, multiplier 1, 8 channels (one 128-bit load) per thread, fp16 / bf16 storage, fp32 accumulation.
+template <typename T>
+__global__ void depthwise_fp_x8_kernel(const T* __restrict__ in, const T* __restrict__ w, const T* __restrict__ bias,
+                                       T* __restrict__ out, ConvDev p)
+{
+    const int cv        = p.IC / 8;
+    const int64_t total = (int64_t)p.N * p.OH * p.OW * cv;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int c8 = (int)(i % cv) * 8;
+        int64_t r    = i / cv;
+        const int ox = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        const int n  = (int)(r / p.OH);
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            acc[j] = 0.f;
+        for (int ky = 0; ky < p.KH; ky++)
+        {
+            const int y = oy * p.sy + ky * p.dy - p.pad_t;
+            if (y < 0 || y >= p.IH)
+                continue;
+            for (int kx = 0; kx < p.KW; kx++)
+            {
+                const int x = ox * p.sx + kx * p.dx - p.pad_l;
+                if (x < 0 || x >= p.IW)
+                    continue;
+                T vi[8], vw[8];
+                *reinterpret_cast<int4*>(vi) =
+                    *reinterpret_cast<const int4*>(in + (((int64_t)n * p.IH + y) * p.IW + x) * p.IC + c8);
+                *reinterpret_cast<int4*>(vw) =
+                    *reinterpret_cast<const int4*>(w + ((int64_t)ky * p.KW + kx) * p.IC + c8);
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    acc[j] = fmaf(to_f32<T>(vi[j]), to_f32<T>(vw[j]), acc[j]);
+            }
+        }
+        T vo[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+        {
+            float v = to_f32<T>(bias[p.bias_n == 1 ? 0 : c8 + j]) + acc[j];
+            if (p.has_clamp)
+            {
+                v = (v < p.clamp_lo_f) ? p.clamp_lo_f : v;
+                v = (v > p.clamp_hi_f) ? p.clamp_hi_f : v;
+            }
+            vo[j] = from_f32<T>(v);
+        }
+        *reinterpret_cast<int4*>(out + (((int64_t)n * p.OH + oy) * p.OW + ox) * p.IC + c8) =
+            *reinterpret_cast<int4*>(vo);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ direct matmul
+__global__ void matmul_direct_i8_kernel(const int8_t* __restrict__ a, const int8_t* __restrict__ b,
+                                        int32_t* __restrict__ out, int N, int H, int C, int W, int32_t a_zp,
+                                        int32_t b_zp)
+{
+    const int64_t total = (int64_t)N * H * W;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int wc = (int)(i % W);
+        int64_t r    = i / W;
+        const int h  = (int)(r % H);
+        const int n  = (int)(r / H);
+        const int8_t* ap = a + ((int64_t)n * H + h) * C;
+        const int8_t* bp = b + (int64_t)n * C * W + wc;
+        int32_t acc = 0;
+        for (int c = 0; c < C; c++)
+            acc += ((int32_t)ap[c] - a_zp) * ((int32_t)bp[(int64_t)c * W] - b_zp);
+        out[i] = acc;
+    }
+}
+
+template <typename T, typename TOut>
+__global__ void matmul_direct_fp_kernel(const T* __restrict__ a, const T* __restrict__ b, TOut* __restrict__ out,
+                                        int N, int H, int C, int W)
+{
+    const int64_t total = (int64_t)N * H * W;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int wc = (int)(i % W);
+        int64_t r    = i / W;
+        const int h  = (int)(r % H);
+        const int n  = (int)(r / H);
+        const T* ap  = a + ((int64_t)n * H + h) * C;
+        const T* bp  = b + (int64_t)n * C * W + wc;
+        float acc    = 0.f;
+        for (int c = 0; c < C; c++)
+            acc = fmaf(to_f32<T>(ap[c]), to_f32<T>(bp[(int64_t)c * W]), acc);
+        out[i] = from_f32<TOut>(acc);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ preparation
+// MATMUL zero points: sum (a - za)(b - zb) = sum ab - zb rowsum(a) - za colsum(b) + C za zb.
+// row_corr[n*H + h] = -zb * rowsum(A[n,h,:]) + C za zb ; one warp per row.
+__global__ void matmul_row_corr_kernel(const int8_t* __restrict__ a, int32_t* __restrict__ row_corr, int64_t rows,
+                                       int C, int32_t a_zp, int32_t b_zp)
+{
+    const int lane     = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nw   = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t r = warp; r < rows; r += nw)
+    {
+        const int8_t* ap = a + r * C;
+        int32_t s        = 0;
+        if ((C & 15) == 0)
+        {
+            for (int c = lane * 16; c < C; c += 32 * 16)
+            {
+                const int4 v = *reinterpret_cast<const int4*>(ap + c);
+                s = __dp4a(v.x, 0x01010101, s);
+                s = __dp4a(v.y, 0x01010101, s);
+                s = __dp4a(v.z, 0x01010101, s);
+                s = __dp4a(v.w, 0x01010101, s);
+            }
+        }
+        else
+        {
+            for (int c = lane; c < C; c += 32)
+                s += ap[c];
+        }
+        for (int o = 16; o > 0; o >>= 1)
+            s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0)
+            row_corr[r] = -b_zp * s + C * a_zp * b_zp;
+    }
+}
+
+// col_corr[n*W + w] = -za * colsum(B[n,:,w]); block (32, 8): 32 x 4 columns, K split over 8 row groups.
+__global__ void matmul_col_corr_kernel(const int8_t* __restrict__ b, int32_t* __restrict__ col_corr, int C, int W,
+                                       int32_t a_zp)
+{
+    __shared__ int32_t part[8][128];
+    const int n    = blockIdx.y;
+    const int col0 = blockIdx.x * 128 + threadIdx.x * 4;
+    int32_t s[4]   = { 0, 0, 0, 0 };
+    const int8_t* bp = b + (int64_t)n * C * W;
+    if ((W & 3) == 0)
+    {
+        if (col0 < W)
+            for (int c = threadIdx.y; c < C; c += 8)
+            {
+                const int v = *reinterpret_cast<const int*>(bp + (int64_t)c * W + col0);
+                s[0] += (int8_t)(v & 0xff);
+                s[1] += (int8_t)((v >> 8) & 0xff);
+                s[2] += (int8_t)((v >> 16) & 0xff);
+                s[3] += (int8_t)((v >> 24) & 0xff);
+            }
+    }
+    else
+    {
+        for (int c = threadIdx.y; c < C; c += 8)
+            for (int j = 0; j < 4; j++)
+                if (col0 + j < W)
+                    s[j] += bp[(int64_t)c * W + col0 + j];
+    }
+    for (int j = 0; j < 4; j++)
+        part[threadIdx.y][threadIdx.x * 4 + j] = s[j];
+    __syncthreads();
+    if (threadIdx.y == 0)
+        for (int j = 0; j < 4; j++)
+        {
+            int32_t t = 0;
+            for (int g = 0; g < 8; g++)
+                t += part[g][threadIdx.x * 4 + j];
+            if (col0 + j < W)
+                col_corr[(int64_t)n * W + col0 + j] = -a_zp * t;
+        }
+}
+
+// CONV2D zero-point tables for weights OHWI (w_zp == 0 path):
+//   prefix[(ky)(kx)][oc], (KH+1)x(KW+1) inclusive 2-D prefix sums over taps of sum_ic w[oc,ky,kx,ic]
+//   bias_full[oc]  (bias broadcast resolved), stored right after the prefix table
+//   col_corr[oc] = bias_full[oc] - in_zp * prefix[KH][KW][oc], stored after bias_full
+__global__ void conv_weight_tables_kernel(const int8_t* __restrict__ w, const int32_t* __restrict__ bias, int bias_n,
+                                          int OC, int KH, int KW, int IC, int32_t in_zp, int32_t* __restrict__ table)
+{
+    const int oc = blockIdx.x * blockDim.x + threadIdx.x;
+    if (oc >= OC)
+        return;
+    const int W1 = KW + 1;
+    for (int ky = 0; ky <= KH; ky++)
+        for (int kx = 0; kx <= KW; kx++)
+        {
+            int32_t v = 0;
+            if (ky > 0 && kx > 0)
+            {
+                int32_t s        = 0;
+                const int8_t* wp = w + (((int64_t)oc * KH + (ky - 1)) * KW + (kx - 1)) * IC;
+                for (int ic = 0; ic < IC; ic++)
+                    s += wp[ic];
+                v = s + table[((ky - 1) * W1 + kx) * OC + oc] + table[(ky * W1 + kx - 1) * OC + oc] -
+                    table[((ky - 1) * W1 + kx - 1) * OC + oc];
+            }
+            table[(ky * W1 + kx) * OC + oc] = v;
+        }
+    const int32_t b       = bias[bias_n == 1 ? 0 : oc];
+    int32_t* bias_full    = table + (size_t)(KH + 1) * W1 * OC;
+    int32_t* col_corr     = bias_full + OC;
+    bias_full[oc]         = b;
+    col_corr[oc]          = b - in_zp * table[(KH * W1 + KW) * OC + oc];
+}
+
+// fp bias to float for the tensor-core epilogue
+template <typename T>
+__global__ void bias_to_f32_kernel(const T* __restrict__ bias, float* __restrict__ out, int n)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n)
+        out[i] = to_f32<T>(bias[i]);
+}
+
+}    // namespace tb200

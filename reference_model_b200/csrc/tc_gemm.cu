@@ -1,0 +1,869 @@
+// Tensor-core GEMM / implicit-GEMM convolution for sm_100a.
+//
+// One persistent, warp-specialised kernel serves MATMUL and CONV2D:
+//   warp 0     : issues TMA tile loads (activation patches per filter tap, weight tiles) into a multi-stage
+//                shared-memory ring; zero fill outside the tensor implements the convolution padding
+//   warp 1     : owns tensor memory (TMEM) and issues tcgen05.mma (kind::i8 with s32 accumulators, or kind::f16
+//                with f32 accumulators); two accumulator buffers alternate so the epilogue of one output tile
+//                overlaps the MMAs of the next
+//   warps 2..5 : epilogue; each thread owns one output row (pixel), reads its accumulators from TMEM and applies
+//                zero-point corrections / bias / RESCALE / CLAMP before the store
+// Every wait on an mbarrier is bounded; a wait that gives up sets TB200_DEV_TIMEOUT in the context's status word
+// and the kernel drains and exits.
+#include <algorithm>
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <mutex>
+
+#include "common.h"
+#include "ptx_sm100.cuh"
+#include "rescale_math.cuh"
+
+namespace tb200
+{
+
+namespace
+{
+
+constexpr int kMaxStages   = 8;
+constexpr int kTileM       = 128;
+constexpr int kNumThreads  = 192;
+constexpr long long kWaitLimitCycles = 4000000000LL;    // about two seconds of SM clock
+
+struct TcKernelParams
+{
+    CUtensorMap tmA;
+    CUtensorMap tmB;
+    // tile grid
+    int tiles_x, tiles_y, tiles_n, tiles_col, num_tiles;
+    int BW, BH, BN;
+    int N, OH, OW, OC;
+    int IH, IW;
+    int block_n;
+    // K loop
+    int KH, KW, chunks_per_tap, total_chunks, ksub, num_kstages, chunk_elems;
+    int pad_t, pad_l, stride_y, stride_x, dil_y, dil_x;
+    int b_mn_major, b_nbox, b_box_n, b_box_bytes;
+    // shared memory ring
+    int a_chunk_bytes, b_chunk_bytes, stage_bytes, num_stages, tx_bytes_per_chunk;
+    // MMA
+    uint64_t a_desc_hi, b_desc_hi;
+    int b_kstep_bytes, mmas_per_chunk;
+    uint32_t idesc;
+    int is_f16_kind;
+    int tmem_cols;
+    // epilogue
+    void* out;
+    int out_es;
+    int out_is_bf16;
+    const int32_t* row_corr;
+    const int32_t* col_corr;
+    int col_corr_ystride;
+    const int32_t* bias_i32;       // full-length int bias for border rows
+    const int32_t* wsum_prefix;    // [(KH+1)*(KW+1)][OC]
+    int32_t in_zp;
+    const float* bias_f;
+    int bias_n;
+    const int32_t* multiplier;
+    const int8_t* shift;
+    int per_channel, double_round;
+    int32_t out_zp, clamp_lo, clamp_hi;
+    float clamp_lo_f, clamp_hi_f;
+    int has_clamp;
+    int* status;
+};
+
+struct TileCoord
+{
+    int x0, y0, n0, col0;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const TcKernelParams& p, int tile)
+{
+    TileCoord t;
+    int c  = tile % p.tiles_col;
+    int r  = tile / p.tiles_col;
+    t.col0 = c * p.block_n;
+    t.x0   = (r % p.tiles_x) * p.BW;
+    r /= p.tiles_x;
+    t.y0 = (r % p.tiles_y) * p.BH;
+    t.n0 = (r / p.tiles_y) * p.BN;
+    return t;
+}
+
+// 16 consecutive int8 results
+__device__ __forceinline__ uint32_t pack4_i8(int a, int b, int c, int d)
+{
+    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
+           ((uint32_t)(d & 0xff) << 24);
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_constant__ TcKernelParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[kMaxStages];
+    __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
+    __shared__ __align__(8) uint64_t bar_tmem_full[2];
+    __shared__ __align__(8) uint64_t bar_tmem_empty[2];
+    __shared__ uint32_t tmem_base_holder;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // ring buffer base, 1024-byte aligned (swizzle atoms repeat every 1024 bytes)
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+
+    if (threadIdx.x == 0)
+    {
+        for (int s = 0; s < p.num_stages; s++)
+        {
+            ptx::mbar_init(ptx::smem_u32(&bar_full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bar_empty[s]), 1);
+        }
+        for (int a = 0; a < 2; a++)
+        {
+            ptx::mbar_init(ptx::smem_u32(&bar_tmem_full[a]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bar_tmem_empty[a]), 128);
+        }
+        abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tmap(&p.tmA);
+        ptx::prefetch_tmap(&p.tmB);
+    }
+    if (warp == 1)
+    {
+        ptx::tmem_alloc(ptx::smem_u32(&tmem_base_holder), (uint32_t)p.tmem_cols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_holder;
+
+    if (warp == 0)
+    {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0)
+        {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x)
+            {
+                const TileCoord t = decode_tile(p, tile);
+                for (int ks = 0; ks < p.num_kstages; ks++)
+                {
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, kWaitLimitCycles))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    const int first   = ks * p.ksub;
+                    const int nchunks = min(p.ksub, p.total_chunks - first);
+                    const uint32_t full = ptx::smem_u32(&bar_full[stage]);
+                    ptx::mbar_arrive_expect_tx(full, (uint32_t)(nchunks * p.tx_bytes_per_chunk));
+                    const uint32_t sA = smem_base + stage * p.stage_bytes;
+                    const uint32_t sB = sA + p.ksub * p.a_chunk_bytes;
+                    for (int j = 0; j < nchunks; j++)
+                    {
+                        const int chunk = first + j;
+                        const int tap   = chunk / p.chunks_per_tap;
+                        const int cc    = chunk - tap * p.chunks_per_tap;
+                        const int ky    = tap / p.KW;
+                        const int kx    = tap - ky * p.KW;
+                        ptx::tma_load_4d(sA + j * p.a_chunk_bytes, &p.tmA, full, cc * p.chunk_elems,
+                                         t.x0 * p.stride_x + kx * p.dil_x - p.pad_l,
+                                         t.y0 * p.stride_y + ky * p.dil_y - p.pad_t, t.n0);
+                        if (!p.b_mn_major)
+                        {
+                            ptx::tma_load_3d(sB + j * p.b_chunk_bytes, &p.tmB, full, chunk * p.chunk_elems, t.col0, 0);
+                        }
+                        else
+                        {
+                            for (int bx = 0; bx < p.b_nbox; bx++)
+                                ptx::tma_load_3d(sB + j * p.b_chunk_bytes + bx * p.b_box_bytes, &p.tmB, full,
+                                                 t.col0 + bx * p.b_box_n, chunk * p.chunk_elems, t.y0);
+                        }
+                    }
+                    if (++stage == p.num_stages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok)
+            {
+                atomicOr(p.status, TB200_DEV_TIMEOUT);
+                atomicExch(&abort_flag, 1);
+            }
+        }
+    }
+    else if (warp == 1)
+    {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0)
+        {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x)
+            {
+                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, kWaitLimitCycles))
+                {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.block_n);
+                for (int ks = 0; ks < p.num_kstages; ks++)
+                {
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_full[stage]), phase, kWaitLimitCycles))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const int first   = ks * p.ksub;
+                    const int nchunks = min(p.ksub, p.total_chunks - first);
+                    const uint32_t sA = smem_base + stage * p.stage_bytes;
+                    const uint32_t sB = sA + p.ksub * p.a_chunk_bytes;
+                    for (int j = 0; j < nchunks; j++)
+                    {
+                        for (int m = 0; m < p.mmas_per_chunk; m++)
+                        {
+                            const uint64_t ad = ptx::smem_desc(p.a_desc_hi, sA + j * p.a_chunk_bytes + m * 32);
+                            const uint64_t bd =
+                                ptx::smem_desc(p.b_desc_hi, sB + j * p.b_chunk_bytes + m * p.b_kstep_bytes);
+                            const uint32_t accum = (ks | j | m) != 0 ? 1u : 0u;
+                            if (p.is_f16_kind)
+                                ptx::mma_f16_ss(d_tmem, ad, bd, p.idesc, accum);
+                            else
+                                ptx::mma_i8_ss(d_tmem, ad, bd, p.idesc, accum);
+                        }
+                    }
+                    ptx::mma_commit(ptx::smem_u32(&bar_empty[stage]));
+                    if (++stage == p.num_stages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok)
+                    break;
+                ptx::mma_commit(ptx::smem_u32(&bar_tmem_full[acc]));
+                acc ^= 1;
+                if (acc == 0)
+                    acc_phase ^= 1u;
+            }
+            if (!ok)
+            {
+                atomicOr(p.status, TB200_DEV_TIMEOUT);
+                atomicExch(&abort_flag, 1);
+            }
+        }
+    }
+    else
+    {
+        // ------------------------------------------------------------------ epilogue warps
+        const int quarter = warp & 3;    // TMEM lane quarter this warp may read
+        const int row     = quarter * 32 + lane;
+        const int xx      = row % p.BW;
+        const int yy      = (row / p.BW) % p.BH;
+        const int nn      = row / (p.BW * p.BH);
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        int dev_flags = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x)
+        {
+            const TileCoord t = decode_tile(p, tile);
+            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_full[acc]), acc_phase, kWaitLimitCycles);
+            // the whole warp must agree before the warp-collective TMEM loads
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok)
+                break;
+            ptx::tc_fence_after_sync();
+
+            const int ox = t.x0 + xx, oy = t.y0 + yy, on = t.n0 + nn;
+            const bool row_valid = (nn < p.BN) && (ox < p.OW) && (oy < p.OH) && (on < p.N);
+            const int64_t pix    = ((int64_t)on * p.OH + oy) * p.OW + ox;
+
+            // border rows of a padded convolution with a non-zero input zero point need the sum of the weights
+            // of the taps that fall inside the image
+            bool border = false;
+            int ky_lo = 0, ky_hi = p.KH, kx_lo = 0, kx_hi = p.KW;
+            if (EPI != TC_EPI_FLOAT && p.wsum_prefix != nullptr && row_valid)
+            {
+                const int iy0 = oy * p.stride_y - p.pad_t;
+                const int ix0 = ox * p.stride_x - p.pad_l;
+                if (iy0 < 0)
+                    ky_lo = (-iy0 + p.dil_y - 1) / p.dil_y;
+                if (ix0 < 0)
+                    kx_lo = (-ix0 + p.dil_x - 1) / p.dil_x;
+                if (iy0 + (p.KH - 1) * p.dil_y >= p.IH)
+                    ky_hi = (p.IH - 1 - iy0) / p.dil_y + 1;
+                if (ix0 + (p.KW - 1) * p.dil_x >= p.IW)
+                    kx_hi = (p.IW - 1 - ix0) / p.dil_x + 1;
+                ky_lo = min(ky_lo, p.KH);
+                kx_lo = min(kx_lo, p.KW);
+                ky_hi = max(ky_hi, ky_lo);
+                kx_hi = max(kx_hi, kx_lo);
+                border = (ky_lo != 0) || (kx_lo != 0) || (ky_hi != p.KH) || (kx_hi != p.KW);
+            }
+
+            int32_t rc = 0;
+            if (EPI == TC_EPI_I32 && p.row_corr != nullptr && row_valid)
+                rc = p.row_corr[pix];
+            const int32_t* cc_base =
+                p.col_corr ? p.col_corr + (int64_t)(p.col_corr_ystride ? oy : 0) * p.col_corr_ystride : nullptr;
+
+            const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n);
+            const int ncol_chunks = p.block_n / 32;
+            for (int c = 0; c < ncol_chunks; c++)
+            {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(taddr_row + (uint32_t)(c * 32), v);
+                ptx::tmem_ld_wait();
+                const int col = t.col0 + c * 32;
+                if (!row_valid || col >= p.OC)
+                    continue;
+                const int nvalid = min(32, p.OC - col);
+
+                if (EPI == TC_EPI_I32)
+                {
+                    int32_t* o = reinterpret_cast<int32_t*>(p.out) + pix * p.OC + col;
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                    {
+                        int32_t a = (int32_t)v[i] + rc;
+                        if (i < nvalid)
+                        {
+                            if (border)
+                            {
+                                const int32_t* P = p.wsum_prefix;
+                                const int W1 = p.KW + 1;
+                                int32_t rs = P[(ky_hi * W1 + kx_hi) * p.OC + col + i] -
+                                             P[(ky_lo * W1 + kx_hi) * p.OC + col + i] -
+                                             P[(ky_hi * W1 + kx_lo) * p.OC + col + i] +
+                                             P[(ky_lo * W1 + kx_lo) * p.OC + col + i];
+                                a += p.bias_i32[col + i] - p.in_zp * rs;
+                            }
+                            else if (cc_base)
+                                a += cc_base[col + i];
+                        }
+                        v[i] = (uint32_t)a;
+                    }
+                    if (nvalid == 32 && ((p.OC & 3) == 0))
+                    {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            *reinterpret_cast<int4*>(o + i) = make_int4((int)v[i], (int)v[i + 1], (int)v[i + 2], (int)v[i + 3]);
+                    }
+                    else
+                    {
+                        _Pragma("unroll") for (int i = 0; i < 32; i++)
+                            if (i < nvalid)
+                                o[i] = (int32_t)v[i];
+                    }
+                }
+                else if (EPI == TC_EPI_RESCALE)
+                {
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                    {
+                        int32_t r = 0;
+                        if (i < nvalid)
+                        {
+                            int32_t a = (int32_t)v[i];
+                            if (border)
+                            {
+                                const int32_t* P = p.wsum_prefix;
+                                const int W1 = p.KW + 1;
+                                int32_t rs = P[(ky_hi * W1 + kx_hi) * p.OC + col + i] -
+                                             P[(ky_lo * W1 + kx_hi) * p.OC + col + i] -
+                                             P[(ky_hi * W1 + kx_lo) * p.OC + col + i] +
+                                             P[(ky_lo * W1 + kx_lo) * p.OC + col + i];
+                                a += p.bias_i32[col + i] - p.in_zp * rs;
+                            }
+                            else if (cc_base)
+                                a += cc_base[col + i];
+                            const int ch = p.per_channel ? (col + i) : 0;
+                            bool bad = false;
+                            int32_t s = apply_scale_32_dev(a, p.multiplier[ch], (int32_t)p.shift[ch], p.double_round != 0, bad);
+                            int64_t z = (int64_t)s + (int64_t)p.out_zp;
+                            bad |= (z > 2147483647LL) || (z < -2147483648LL);
+                            z = z < (int64_t)p.clamp_lo ? (int64_t)p.clamp_lo : z;
+                            z = z > (int64_t)p.clamp_hi ? (int64_t)p.clamp_hi : z;
+                            r = bad ? 0 : (int32_t)z;
+                            if (bad)
+                                dev_flags |= TB200_DEV_UNPREDICTABLE;
+                        }
+                        v[i] = (uint32_t)r;
+                    }
+                    if (p.out_es == 1)
+                    {
+                        int8_t* o = reinterpret_cast<int8_t*>(p.out) + pix * p.OC + col;
+                        if (nvalid == 32 && ((p.OC & 15) == 0))
+                        {
+                            uint4 w0 = make_uint4(pack4_i8(v[0], v[1], v[2], v[3]), pack4_i8(v[4], v[5], v[6], v[7]),
+                                                  pack4_i8(v[8], v[9], v[10], v[11]), pack4_i8(v[12], v[13], v[14], v[15]));
+                            uint4 w1 = make_uint4(pack4_i8(v[16], v[17], v[18], v[19]), pack4_i8(v[20], v[21], v[22], v[23]),
+                                                  pack4_i8(v[24], v[25], v[26], v[27]), pack4_i8(v[28], v[29], v[30], v[31]));
+                            *reinterpret_cast<uint4*>(o)      = w0;
+                            *reinterpret_cast<uint4*>(o + 16) = w1;
+                        }
+                        else
+                        {
+                            _Pragma("unroll") for (int i = 0; i < 32; i++)
+                                if (i < nvalid)
+                                    o[i] = (int8_t)(int32_t)v[i];
+                        }
+                    }
+                    else if (p.out_es == 2)
+                    {
+                        int16_t* o = reinterpret_cast<int16_t*>(p.out) + pix * p.OC + col;
+                        _Pragma("unroll") for (int i = 0; i < 32; i++)
+                            if (i < nvalid)
+                                o[i] = (int16_t)(int32_t)v[i];
+                    }
+                    else
+                    {
+                        int32_t* o = reinterpret_cast<int32_t*>(p.out) + pix * p.OC + col;
+                        _Pragma("unroll") for (int i = 0; i < 32; i++)
+                            if (i < nvalid)
+                                o[i] = (int32_t)v[i];
+                    }
+                }
+                else
+                {
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                    {
+                        float a = __uint_as_float(v[i]);
+                        if (p.bias_f != nullptr && i < nvalid)
+                            a += p.bias_f[p.bias_n == 1 ? 0 : (col + i)];
+                        if (p.has_clamp)
+                        {
+                            // NaN propagates: comparisons with NaN are false on both sides
+                            a = (a < p.clamp_lo_f) ? p.clamp_lo_f : a;
+                            a = (a > p.clamp_hi_f) ? p.clamp_hi_f : a;
+                        }
+                        f[i] = a;
+                    }
+                    if (p.out_es == 4)
+                    {
+                        float* o = reinterpret_cast<float*>(p.out) + pix * p.OC + col;
+                        if (nvalid == 32 && ((p.OC & 3) == 0))
+                        {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4)
+                                *reinterpret_cast<float4*>(o + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+                        }
+                        else
+                        {
+                            _Pragma("unroll") for (int i = 0; i < 32; i++)
+                                if (i < nvalid)
+                                    o[i] = f[i];
+                        }
+                    }
+                    else
+                    {
+                        uint16_t h[32];
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                        {
+                            if (p.out_is_bf16)
+                                h[i] = __bfloat16_as_ushort(__float2bfloat16_rn(f[i]));
+                            else
+                                h[i] = __half_as_ushort(__float2half_rn(f[i]));
+                        }
+                        uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + pix * p.OC + col;
+                        if (nvalid == 32 && ((p.OC & 7) == 0))
+                        {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8)
+                            {
+                                uint4 w = make_uint4((uint32_t)h[i] | ((uint32_t)h[i + 1] << 16),
+                                                     (uint32_t)h[i + 2] | ((uint32_t)h[i + 3] << 16),
+                                                     (uint32_t)h[i + 4] | ((uint32_t)h[i + 5] << 16),
+                                                     (uint32_t)h[i + 6] | ((uint32_t)h[i + 7] << 16));
+                                *reinterpret_cast<uint4*>(o + i) = w;
+                            }
+                        }
+                        else
+                        {
+                            _Pragma("unroll") for (int i = 0; i < 32; i++)
+                                if (i < nvalid)
+                                    o[i] = h[i];
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[acc]));
+            acc ^= 1;
+            if (acc == 0)
+                acc_phase ^= 1u;
+        }
+        if (!ok && lane == 0)
+        {
+            atomicOr(p.status, TB200_DEV_TIMEOUT);
+            atomicExch(&abort_flag, 1);
+        }
+        if (dev_flags)
+            atomicOr(p.status, dev_flags);
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && abort_flag)
+    {
+        // a role gave up: let copies that may still be in flight land before the CTA's shared memory is released
+        for (int s = 0; s < p.num_stages; s++)
+        {
+            ptx::mbar_wait_bounded(ptx::smem_u32(&bar_full[s]), 0u, 2000000LL);
+            ptx::mbar_wait_bounded(ptx::smem_u32(&bar_full[s]), 1u, 2000000LL);
+        }
+    }
+    __syncthreads();
+    if (warp == 1)
+    {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+PFN_encodeTiled get_encode_fn()
+{
+    static PFN_encodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_encodeTiled>(sym);
+    });
+    return fn;
+}
+
+int env_int(const char* name, int dflt)
+{
+    const char* v = getenv(name);
+    return v ? atoi(v) : dflt;
+}
+
+struct TcPlan
+{
+    TcKernelParams kp;
+    int smem_bytes;
+    int grid;
+    // tensor map recipes (filled by plan, encoded at launch)
+    cuuint64_t a_dims[4], a_strides[3];
+    cuuint32_t a_box[4], a_estr[4];
+    cuuint64_t b_dims[3], b_strides[2];
+    cuuint32_t b_box[3];
+    CUtensorMapDataType dt;
+    CUtensorMapSwizzle a_swz, b_swz;
+};
+
+bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
+{
+    auto no = [&](const char* m) {
+        if (why)
+            *why = m;
+        return false;
+    };
+    const int es = (int)dtype_size(q.in_dtype);
+    if (!(q.in_dtype == TB200_INT8 || q.in_dtype == TB200_FP16 || q.in_dtype == TB200_BF16))
+        return no("element type has no tensor-core path");
+    if ((reinterpret_cast<uintptr_t>(q.a) & 15) || (reinterpret_cast<uintptr_t>(q.b) & 15))
+        return no("operand base not 16-byte aligned");
+    const int row_bytes = q.IC * es;    // contiguous K bytes of one tap
+    if (row_bytes % 32 != 0)
+        return no("channel run is not a multiple of 32 bytes");
+    const int swz = (row_bytes % 128 == 0) ? 128 : (row_bytes % 64 == 0) ? 64 : 32;
+
+    TcKernelParams& k = plan->kp;
+    memset(&k, 0, sizeof(k));
+    // A view.  A stride-1, pad-0 1x1 convolution (and MATMUL) is a plain GEMM over flattened pixels.
+    int N = q.N, IH = q.IH, IW = q.IW, OH = q.OH, OW = q.OW;
+    const bool pure_gemm = q.KH == 1 && q.KW == 1 && q.stride_y == 1 && q.stride_x == 1 && q.pad_t == 0 &&
+                           q.pad_l == 0 && OH == IH && OW == IW && !q.b_mn_major;
+    if (pure_gemm)
+    {
+        int64_t pixels = (int64_t)N * IH * IW;
+        if (pixels >= (1LL << 31))
+            return no("too many pixels");
+        IW = OW = (int)pixels;
+        IH = OH = 1;
+        N  = 1;
+    }
+    if (q.stride_x > 2 || q.stride_y > 256)
+        return no("stride too large for the tile loader");
+    int BW, BH = 1, BN = 1;
+    if (OW >= kTileM)
+        BW = kTileM;
+    else
+    {
+        BW = OW;
+        BH = std::min(OH, kTileM / BW);
+        // prefer a row count that divides OH when it costs little
+        for (int cand = BH; cand >= std::max(1, BH - 2); cand--)
+            if (OH % cand == 0)
+            {
+                BH = cand;
+                break;
+            }
+        if (BH == OH)
+            BN = std::min(N, kTileM / (BW * BH));
+    }
+    if (q.b_mn_major)
+    {
+        BH = 1;
+        BN = 1;
+    }
+    if (BW * q.stride_x > 256 || BH * q.stride_y > 256)
+        return no("tile span exceeds the TMA box limit");
+
+    k.BW = BW;
+    k.BH = BH;
+    k.BN = BN;
+    k.N  = N;
+    k.OH = OH;
+    k.OW = OW;
+    k.OC = q.OC;
+    k.IH = IH;
+    k.IW = IW;
+    k.tiles_x = (OW + BW - 1) / BW;
+    k.tiles_y = (OH + BH - 1) / BH;
+    k.tiles_n = (N + BN - 1) / BN;
+
+    int block_n = env_int("TB200_TC_BLOCK_N", 0);
+    if (block_n == 0)
+        block_n = q.OC >= 256 ? 256 : q.OC > 64 ? 128 : q.OC > 32 ? 64 : 32;
+    if (q.b_mn_major && (block_n * es) % 128 != 0)
+        block_n = 128 / es * ((block_n * es + 127) / 128);
+    if (block_n > 256 || block_n % 32 != 0)
+        return no("bad block_n");
+    k.block_n   = block_n;
+    k.tiles_col = (q.OC + block_n - 1) / block_n;
+    int64_t nt  = (int64_t)k.tiles_x * k.tiles_y * k.tiles_n * k.tiles_col;
+    if (nt >= (1LL << 31))
+        return no("too many tiles");
+    k.num_tiles = (int)nt;
+
+    k.KH = q.KH;
+    k.KW = q.KW;
+    k.chunk_elems    = swz / es;
+    k.chunks_per_tap = row_bytes / swz;
+    k.total_chunks   = q.KH * q.KW * k.chunks_per_tap;
+    k.ksub           = std::min(std::max(1, 128 / swz), k.total_chunks);
+    k.num_kstages    = (k.total_chunks + k.ksub - 1) / k.ksub;
+    k.pad_t = q.pad_t;
+    k.pad_l = q.pad_l;
+    k.stride_y = q.stride_y;
+    k.stride_x = q.stride_x;
+    k.dil_y = q.dil_y;
+    k.dil_x = q.dil_x;
+    k.mmas_per_chunk = swz / 32;
+
+    const uint32_t layout = swz == 128 ? 2u : swz == 64 ? 4u : 6u;
+    k.a_chunk_bytes = ((kTileM * swz) + 1023) & ~1023;
+    k.a_desc_hi     = ptx::make_smem_desc_hi(16, 8 * swz, layout);
+    k.b_mn_major    = q.b_mn_major;
+    int a_tx        = BW * BH * BN * swz;
+    int b_tx;
+    if (!q.b_mn_major)
+    {
+        if (((int64_t)q.KH * q.KW * q.IC * es) % 16 != 0)
+            return no("weight row stride not 16-byte aligned");
+        k.b_chunk_bytes = ((block_n * swz) + 1023) & ~1023;
+        k.b_desc_hi     = ptx::make_smem_desc_hi(16, 8 * swz, layout);
+        k.b_kstep_bytes = 32;
+        b_tx            = block_n * swz;
+    }
+    else
+    {
+        if (swz != 128)
+            return no("MN-major B needs 128-byte K chunks of A");
+        if ((q.OC * es) % 16 != 0)
+            return no("B row stride not 16-byte aligned");
+        k.b_box_n       = 128 / es;
+        k.b_nbox        = block_n / k.b_box_n;
+        k.b_box_bytes   = k.chunk_elems * 128;
+        k.b_chunk_bytes = k.b_nbox * k.b_box_bytes;
+        const int lbo   = env_int("TB200_TC_MN_LBO", k.b_box_bytes);
+        const int sbo   = env_int("TB200_TC_MN_SBO", 1024);
+        k.b_desc_hi     = ptx::make_smem_desc_hi(lbo, sbo, 2u);
+        k.b_kstep_bytes = env_int("TB200_TC_MN_KSTEP", (32 / es) * 128);
+        b_tx            = k.b_chunk_bytes;
+    }
+    k.tx_bytes_per_chunk = a_tx + b_tx;
+    k.stage_bytes        = k.ksub * (k.a_chunk_bytes + k.b_chunk_bytes);
+    const int smem_budget = 200 * 1024;
+    k.num_stages = std::min(kMaxStages, smem_budget / k.stage_bytes);
+    k.num_stages = std::min(k.num_stages, std::max(2, k.num_kstages * 2));
+    const int forced = env_int("TB200_TC_STAGES", 0);
+    if (forced > 0)
+        k.num_stages = std::min(forced, kMaxStages);
+    if (k.num_stages < 2)
+        return no("stage does not fit in shared memory");
+    plan->smem_bytes = k.num_stages * k.stage_bytes + 1024;
+
+    const bool is_f16 = q.in_dtype != TB200_INT8;
+    k.is_f16_kind     = is_f16;
+    const uint32_t ab_fmt = is_f16 ? (q.in_dtype == TB200_BF16 ? 1u : 0u) : (uint32_t)env_int("TB200_TC_I8_FMT", 1);
+    k.idesc = ptx::make_idesc(is_f16 ? 1u : 2u, ab_fmt, ab_fmt, 0u, q.b_mn_major ? 1u : 0u, kTileM, (uint32_t)block_n);
+    int cols = 32;
+    while (cols < 2 * block_n)
+        cols *= 2;
+    k.tmem_cols = cols;
+
+    // tensor maps
+    plan->dt    = q.in_dtype == TB200_INT8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                  : q.in_dtype == TB200_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                             : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    plan->a_swz = swz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : swz == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+    plan->a_dims[0] = (cuuint64_t)q.IC;
+    plan->a_dims[1] = (cuuint64_t)IW;
+    plan->a_dims[2] = (cuuint64_t)IH;
+    plan->a_dims[3] = (cuuint64_t)N;
+    plan->a_strides[0] = (cuuint64_t)q.IC * es;
+    plan->a_strides[1] = plan->a_strides[0] * IW;
+    plan->a_strides[2] = plan->a_strides[1] * IH;
+    plan->a_box[0]  = (cuuint32_t)k.chunk_elems;
+    plan->a_box[1]  = (cuuint32_t)(BW * q.stride_x);
+    plan->a_box[2]  = (cuuint32_t)(BH * q.stride_y);
+    plan->a_box[3]  = (cuuint32_t)BN;
+    plan->a_estr[0] = 1;
+    plan->a_estr[1] = (cuuint32_t)q.stride_x;
+    plan->a_estr[2] = (cuuint32_t)q.stride_y;
+    plan->a_estr[3] = 1;
+    if (!q.b_mn_major)
+    {
+        const cuuint64_t ktot = (cuuint64_t)q.KH * q.KW * q.IC;
+        plan->b_swz        = plan->a_swz;
+        plan->b_dims[0]    = ktot;
+        plan->b_dims[1]    = (cuuint64_t)q.OC;
+        plan->b_dims[2]    = 1;
+        plan->b_strides[0] = ktot * es;
+        plan->b_strides[1] = ktot * es * q.OC;
+        plan->b_box[0]     = (cuuint32_t)k.chunk_elems;
+        plan->b_box[1]     = (cuuint32_t)block_n;
+        plan->b_box[2]     = 1;
+    }
+    else
+    {
+        plan->b_swz        = CU_TENSOR_MAP_SWIZZLE_128B;
+        plan->b_dims[0]    = (cuuint64_t)q.OC;
+        plan->b_dims[1]    = (cuuint64_t)q.IC;
+        plan->b_dims[2]    = (cuuint64_t)q.OH;    // batches
+        plan->b_strides[0] = (cuuint64_t)q.OC * es;
+        plan->b_strides[1] = (cuuint64_t)q.OC * es * q.IC;
+        plan->b_box[0]     = (cuuint32_t)k.b_box_n;
+        plan->b_box[1]     = (cuuint32_t)k.chunk_elems;
+        plan->b_box[2]     = 1;
+    }
+    for (int i = 0; i < 3; i++)
+        if (plan->a_strides[i] % 16 != 0 || plan->a_strides[i] >= (1ULL << 40))
+            return no("activation stride not usable by TMA");
+    plan->grid = std::min(k.num_tiles, num_sms);
+    return true;
+}
+
+}    // namespace
+
+bool tc_gemm_supported(const TcProblem& p, std::string* why)
+{
+    TcPlan plan;
+    return make_plan(p, 148, &plan, why);
+}
+
+tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
+{
+    TcPlan plan;
+    std::string why;
+    if (!make_plan(q, ctx->num_sms, &plan, &why))
+        return fail(ctx, TB200_ERROR, "tensor-core path not applicable: %s", why.c_str());
+    PFN_encodeTiled enc = get_encode_fn();
+    if (!enc)
+        return fail(ctx, TB200_INTERNAL, "cuTensorMapEncodeTiled is not available from the driver");
+    TcKernelParams& k = plan.kp;
+    CUresult r = enc(&k.tmA, plan.dt, 4, const_cast<void*>(q.a), plan.a_dims, plan.a_strides, plan.a_box, plan.a_estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, plan.a_swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(ctx, TB200_INTERNAL, "tensor map for A rejected (CUresult %d)", (int)r);
+    cuuint32_t b_estr[3] = { 1, 1, 1 };
+    r = enc(&k.tmB, plan.dt, 3, const_cast<void*>(q.b), plan.b_dims, plan.b_strides, plan.b_box, b_estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, plan.b_swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(ctx, TB200_INTERNAL, "tensor map for B rejected (CUresult %d)", (int)r);
+
+    k.out              = q.out;
+    k.out_es           = (int)dtype_size(q.out_dtype);
+    k.out_is_bf16      = q.out_dtype == TB200_BF16;
+    k.row_corr         = q.row_corr;
+    k.col_corr         = q.col_corr;
+    k.col_corr_ystride = q.col_corr_ystride;
+    k.bias_i32         = nullptr;
+    k.wsum_prefix      = q.wsum_prefix;
+    k.in_zp            = q.in_zp;
+    if (q.wsum_prefix)
+        k.bias_i32 = q.wsum_prefix + (size_t)(q.KH + 1) * (q.KW + 1) * q.OC;    // table is followed by the full bias
+    k.bias_f       = q.bias_f;
+    k.bias_n       = q.bias_n;
+    k.multiplier   = q.multiplier;
+    k.shift        = q.shift;
+    k.per_channel  = q.per_channel;
+    k.double_round = q.double_round;
+    k.out_zp       = q.out_zp;
+    k.clamp_lo     = q.clamp_lo;
+    k.clamp_hi     = q.clamp_hi;
+    k.clamp_lo_f   = q.clamp_lo_f;
+    k.clamp_hi_f   = q.clamp_hi_f;
+    k.has_clamp    = q.has_clamp;
+    k.status       = ctx->d_status;
+
+    void (*kern)(const TcKernelParams) = nullptr;
+    const char* name                   = "";
+    switch (q.epi)
+    {
+        case TC_EPI_I32:
+            kern = tc_gemm_kernel<TC_EPI_I32>;
+            name = "tc_gemm_i8_i32";
+            break;
+        case TC_EPI_RESCALE:
+            kern = tc_gemm_kernel<TC_EPI_RESCALE>;
+            name = "tc_gemm_i8_rescale";
+            break;
+        default:
+            kern = tc_gemm_kernel<TC_EPI_FLOAT>;
+            name = "tc_gemm_f16";
+            break;
+    }
+    TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
+    timer_begin(ctx);
+    kern<<<plan.grid, kNumThreads, plan.smem_bytes, ctx->stream>>>(k);
+    timer_end(ctx);
+    return post_launch(ctx, name);
+}
+
+}    // namespace tb200

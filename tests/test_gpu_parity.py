@@ -1,0 +1,620 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle: bit-exact for every integer path, within the
+TOSA dot-product bound (against the fp64 oracle) for floating point."""
+import os
+
+import numpy as np
+import pytest
+
+import reference_model_b200 as tb
+from oracle import oracle as orc
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+I8, I16, I32, F16, BF16, F32 = (tb.DType.INT8, tb.DType.INT16, tb.DType.INT32, tb.DType.FP16, tb.DType.BF16,
+                                tb.DType.FP32)
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = tb.Context(0)
+    yield c
+    c.close()
+
+
+def _free(*ts):
+    for t in ts:
+        t.free()
+
+
+def run_conv_i8(ctx, x, w, b, pad, stride, dil, izp, wzp, rescale=None, clamp=None, depthwise=False, policy=0):
+    """Runs CONV2D / DEPTHWISE (optionally with a fused RESCALE [+CLAMP]) on the device; returns (status, out, kernel)."""
+    N, IH, IW, IC = x.shape
+    if depthwise:
+        KH, KW, _, M = w.shape
+        OC = IC * M
+    else:
+        OC, KH, KW, _ = w.shape
+    OH, OW = orc.conv_out_hw(IH, IW, KH, KW, pad, stride, dil)
+    tx, tw, tbias = ctx.from_numpy(x), ctx.from_numpy(w), ctx.from_numpy(b)
+    epi, extra = None, []
+    out_dt = I32
+    if rescale is not None:
+        mult, shift, ozp, rounding = rescale
+        tm, ts = ctx.from_numpy(mult), ctx.from_numpy(shift)
+        extra = [tm, ts]
+        epi = tb.Epilogue(tb.RescaleAttr(tm, ts, 0, ozp, True, rounding, per_channel=mult.size > 1), clamp)
+        out_dt = I8
+    to = ctx.empty(out_dt, (N, OH, OW, OC))
+    old = ctx.set_kernel_policy(policy)
+    fn = ctx.depthwise_conv2d if depthwise else ctx.conv2d
+    fn(tx, tw, tbias, to, pad, stride, dil, izp, wzp, epi)
+    kernel = ctx.last_kernel()
+    ctx.set_kernel_policy(old)
+    st, out = to.download()
+    _free(tx, tw, tbias, to, *extra)
+    return st, out, kernel
+
+
+def oracle_conv_i8(x, w, b, pad, stride, dil, izp, wzp, rescale=None, clamp=None, depthwise=False):
+    fn = orc.depthwise_conv2d if depthwise else orc.conv2d
+    acc = fn(x, w, b, pad, stride, dil, izp, wzp, nthreads=8)
+    if rescale is None:
+        return orc.VALID, acc
+    mult, shift, ozp, rounding = rescale
+    st, out = orc.rescale(acc, mult, shift, per_channel=mult.size > 1, scale32=True, rounding=rounding, input_zp=0,
+                          output_zp=ozp, in_bits=32, out_bits=8)
+    if clamp is not None:
+        _, out = orc.clamp(out, clamp[0], clamp[1])
+    return st, out
+
+
+# ------------------------------------------------------------------------------------------- reference KATs
+ZP_CASES = [
+    ([126, -126, -120, 0], [2, 1, 4, -7], 4, 15),
+    ([122, -7, -120, 121], [2, 1, 4, -7], -10, -5),
+    ([3, -12, 5, 70], [-120, -12, 0, -7], 55, 15),
+    ([-5, 65, -1, 32], [-2, 125, 4, -1], -10, -5),
+]
+
+
+@pytest.mark.parametrize("inv,wv,izp,wzp", ZP_CASES)
+def test_zero_point_kats(ctx, inv, wv, izp, wzp):
+    # reference_model/test/ref_model_tests/tensor_ops_tests.cpp:622-683
+    exp = sum((a - izp) * (b - wzp) for a, b in zip(inv, wv))
+    x = np.array(inv, np.int8).reshape(1, 2, 2, 1)
+    st, out, _ = run_conv_i8(ctx, x, np.array(wv, np.int8).reshape(1, 2, 2, 1), np.zeros(1, np.int32), [0, 0, 0, 0],
+                             [2, 2], [1, 1], izp, wzp)
+    assert st == tb.Status.OK and out.reshape(-1).tolist() == [exp]
+    st, out, _ = run_conv_i8(ctx, x, np.array(wv, np.int8).reshape(2, 2, 1, 1), np.zeros(1, np.int32), [0, 0, 0, 0],
+                             [2, 2], [1, 1], izp, wzp, depthwise=True)
+    assert st == tb.Status.OK and out.reshape(-1).tolist() == [exp]
+    a = np.array(inv, np.int8).reshape(1, 2, 2)
+    b = np.array(wv, np.int8).reshape(1, 2, 2)
+    ta, tbb, to = ctx.from_numpy(a), ctx.from_numpy(b), ctx.empty(I32, (1, 2, 2))
+    ctx.matmul(ta, tbb, to, izp, wzp)
+    st, out = to.download()
+    assert np.array_equal(out[0], (a.astype(np.int64)[0] - izp) @ (b.astype(np.int64)[0] - wzp))
+    _free(ta, tbb, to)
+
+
+def test_bias_broadcast_kats(ctx):
+    # tensor_ops_tests.cpp:736-798
+    x = np.array([5, 9], np.int8).reshape(1, 1, 1, 2)
+    w = np.array([3, -7, -1, 4], np.int8).reshape(2, 1, 1, 2)
+    for bias, exp in (([-5], [-53, 26]), ([-5, 14], [-53, 45])):
+        st, out, _ = run_conv_i8(ctx, x, w, np.array(bias, np.int32), [0, 0, 0, 0], [1, 1], [1, 1], 0, 0)
+        assert out.reshape(-1).tolist() == exp
+    wd = np.array([3, -7], np.int8).reshape(1, 1, 2, 1)
+    for bias, exp in (([-5], [10, -68]), ([-5, 14], [10, -49])):
+        st, out, _ = run_conv_i8(ctx, x, wd, np.array(bias, np.int32), [0, 0, 0, 0], [1, 1], [1, 1], 0, 0,
+                                 depthwise=True)
+        assert out.reshape(-1).tolist() == exp
+
+
+@pytest.mark.parametrize("inv,izp,ozp", [([126, -126, -128, 0], 4, 15), ([126, 126, 127, 127], -12, -5)])
+def test_avg_pool_kats(ctx, inv, izp, ozp):
+    # tensor_ops_tests.cpp:800-822
+    x = np.array(inv, np.int8).reshape(1, 2, 2, 1)
+    tx, to = ctx.from_numpy(x), ctx.empty(I8, (1, 1, 1, 1))
+    ctx.avg_pool2d(tx, to, [2, 2], [0, 0, 0, 0], [2, 2], izp, ozp)
+    st, out = to.download()
+    s = sum(int(v) - izp for v in inv)
+    exp = min(max(((s * ((1 << 30) + 1) + (1 << 31)) >> 32) + ozp, -128), 127)
+    assert st == tb.Status.OK and int(out.reshape(-1)[0]) == exp
+    _free(tx, to)
+
+
+def _rescale_dev(ctx, x, in_dt, out_dt, mult, mult_dt, shift, **kw):
+    tx = ctx.from_numpy(x, in_dt)
+    tm = ctx.from_numpy(np.asarray(mult, dtype=np.int32 if mult_dt == I32 else np.int16), mult_dt)
+    ts = ctx.from_numpy(np.asarray(shift, dtype=np.int8))
+    to = ctx.empty(out_dt, x.shape)
+    st = ctx.rescale(tx, tb.RescaleAttr(tm, ts, **kw), to, check=False)
+    out = None
+    if st == tb.Status.OK:
+        st, out = to.download(check=False)
+    _free(tx, tm, ts, to)
+    return st, out
+
+
+def test_rescale_kats(ctx):
+    # type_conversion_tests.cpp:324-335 and :385-404
+    st, out = _rescale_dev(ctx, np.array([65], np.int8), I8, tb.DType.UINT16, [4], I16, [2], input_zp=1,
+                           output_zp=32768, scale32=False, output_unsigned=True)
+    assert st == tb.Status.OK and out.tolist() == [32832]
+    st, out = _rescale_dev(ctx, np.array([65], np.int8), I8, tb.DType.UINT16, [4], I16, [2], input_zp=1,
+                           output_zp=32768, scale32=False, rounding="INEXACT_ROUND", output_unsigned=True)
+    assert st == tb.Status.OK and out.tolist() == [32832]
+    st, out = _rescale_dev(ctx, np.array([103], np.int8), I8, tb.DType.UINT8, [147], I16, [8], input_zp=-95,
+                           output_zp=0, scale32=False, rounding="INEXACT_ROUND", output_unsigned=True)
+    assert st == tb.Status.OK and out.tolist() == [114]
+    # :337-383, operand-size ERROR_IFs
+    st, _ = _rescale_dev(ctx, np.array([20, -5, -16], np.int8), I8, I32, [4, 2], I32, [16, 5, 9], input_zp=-19,
+                         per_channel=True)
+    assert st == tb.Status.ERROR
+    st, _ = _rescale_dev(ctx, np.array([0, -12, 0, 12], np.int32), I32, I8, [4, 1024, 2048, 115], I16, [12],
+                         output_zp=-12, scale32=False, per_channel=True)
+    assert st == tb.Status.ERROR
+    st, _ = _rescale_dev(ctx, np.array([20, -5, -16], np.int8), I8, I32, [4, 519], I32, [12], input_zp=-19)
+    assert st == tb.Status.ERROR
+    st, _ = _rescale_dev(ctx, np.array([0, -12, 0, 12], np.int32), I32, I8, [4], I16, [6, 16], output_zp=-12,
+                         scale32=False)
+    assert st == tb.Status.ERROR
+
+
+# ------------------------------------------------------------------------------------------- golden fixtures
+def test_golden_qi8_example(ctx, golden_dir):
+    g = np.load(os.path.join(golden_dir, "conv2d_1x1_qi8_example.npz"))
+    resc = (g["multiplier"], g["shift"], int(g["output_zp"]), "DOUBLE_ROUND")
+    for policy in (0, 1):
+        st, out, _ = run_conv_i8(ctx, g["x"], g["w"], g["bias"], [0, 0, 0, 0], [1, 1], [1, 1], int(g["input_zp"]),
+                                 int(g["weight_zp"]), rescale=resc, policy=policy)
+        assert st == tb.Status.OK and np.array_equal(out, g["expected"])
+    # unfused: CONV2D to INT32, then the RESCALE node
+    st, acc, _ = run_conv_i8(ctx, g["x"], g["w"], g["bias"], [0, 0, 0, 0], [1, 1], [1, 1], 0, 0)
+    st, out = _rescale_dev(ctx, acc, I32, I8, g["multiplier"], I32, g["shift"], output_zp=int(g["output_zp"]),
+                           rounding="DOUBLE_ROUND", per_channel=True)
+    assert st == tb.Status.OK and np.array_equal(out, g["expected"])
+
+
+def run_conv_fp(ctx, x, w, b, pad, stride, dil, dt, clamp=None, depthwise=False, policy=0):
+    N, IH, IW, IC = x.shape
+    if depthwise:
+        KH, KW, _, M = w.shape
+        OC = IC * M
+    else:
+        OC, KH, KW, _ = w.shape
+    OH, OW = orc.conv_out_hw(IH, IW, KH, KW, pad, stride, dil)
+
+    def up(a):
+        if dt == F32:
+            return ctx.from_numpy(a.astype(np.float32))
+        if dt == F16:
+            return ctx.from_numpy(a.astype(np.float16))
+        return ctx.from_numpy(util.to_bf16_bits(a), BF16)
+
+    tx, tw, tbias = up(x), up(w), up(b)
+    to = ctx.empty(dt, (N, OH, OW, OC))
+    epi = tb.Epilogue(None, (float(clamp[0]), float(clamp[1]))) if clamp is not None else None
+    old = ctx.set_kernel_policy(policy)
+    (ctx.depthwise_conv2d if depthwise else ctx.conv2d)(tx, tw, tbias, to, pad, stride, dil, 0, 0, epi)
+    kernel = ctx.last_kernel()
+    ctx.set_kernel_policy(old)
+    st, out = to.download()
+    _free(tx, tw, tbias, to)
+    if dt == BF16:
+        out = util.from_bf16_bits(out)
+    return st, out.astype(np.float32), kernel
+
+
+def test_golden_f32_example(ctx, golden_dir):
+    # reference_model/test/model_runner_tests.cpp:85-125
+    g = np.load(os.path.join(golden_dir, "conv2d_1x1_f32_example.npz"))
+    st, out, _ = run_conv_fp(ctx, g["x"], g["w"], g["bias"], [0, 0, 0, 0], [1, 1], [1, 1], F32)
+    np.testing.assert_allclose(out, g["expected"], rtol=1e-4, atol=1e-5)
+
+
+# ------------------------------------------------------------------------------------------- integer convolution
+def test_config1_conv_rescale(ctx):
+    """1x32x32x8 -> 1x1 conv -> 16 channels, input_zp 5, per-channel DOUBLE_ROUND RESCALE, output_zp -1."""
+    r = util.rng(0)
+    x, w, b = util.conv_int8_case(r, 1, 32, 32, 8, 16, 1, 1)
+    mult, shift = util.rescale_params(r, 16)
+    resc = (mult, shift, -1, "DOUBLE_ROUND")
+    est, exp = oracle_conv_i8(x, w, b, [0, 0, 0, 0], [1, 1], [1, 1], 5, 0, resc)
+    assert est == orc.VALID
+    for policy in (0, 1):
+        st, out, _ = run_conv_i8(ctx, x, w, b, [0, 0, 0, 0], [1, 1], [1, 1], 5, 0, resc, policy=policy)
+        assert st == tb.Status.OK and np.array_equal(out, exp)
+
+
+SMALL_SWEEP = [(kh, kw, s, d, p) for kh in (1, 2, 3) for kw in (1, 3) for s in (1, 2, 3) for d in (1, 2)
+               for p in ((0, 0, 0, 0), (1, 0, 2, 1))]
+
+
+def test_direct_conv_small_shape_sweep(ctx):
+    """All small kernel / stride / dilation / pad combinations that satisfy the exact-division rule, odd channels."""
+    r = util.rng(1)
+    checked = 0
+    for kh, kw, s, d, p in SMALL_SWEEP:
+        for ih, iw in ((7, 8), (8, 6)):
+            fh = ih - 1 + p[0] + p[1] - (kh - 1) * d
+            fw = iw - 1 + p[2] + p[3] - (kw - 1) * d
+            if fh < 0 or fw < 0 or fh % s or fw % s:
+                continue
+            x, w, b = util.conv_int8_case(r, 2, ih, iw, 5, 3, kh, kw)
+            izp, wzp = int(r.integers(-128, 128)), int(r.integers(-128, 128))
+            exp = orc.conv2d(x, w, b, list(p), [s, s], [d, d], izp, wzp)
+            st, out, _ = run_conv_i8(ctx, x, w, b, list(p), [s, s], [d, d], izp, wzp)
+            assert st == tb.Status.OK and np.array_equal(out, exp), (kh, kw, s, d, p, ih, iw)
+            wd = r.integers(-127, 128, size=(kh, kw, 5, 2)).astype(np.int8)
+            bd = r.integers(-1000, 1000, size=10).astype(np.int32)
+            exp = orc.depthwise_conv2d(x, wd, bd, list(p), [s, s], [d, d], izp, wzp)
+            st, out, _ = run_conv_i8(ctx, x, wd, bd, list(p), [s, s], [d, d], izp, wzp, depthwise=True)
+            assert st == tb.Status.OK and np.array_equal(out, exp), ("dw", kh, kw, s, d, p, ih, iw)
+            checked += 1
+    assert checked > 40
+
+
+TC_CONV_CASES = [
+    # N, IH, IW, IC, OC, KH, KW, stride, pad, in_zp
+    (2, 56, 56, 64, 64, 3, 3, 1, (1, 1, 1, 1), -128),     # the ResNet 3x3 layer shape (small batch)
+    (2, 28, 28, 128, 128, 3, 3, 1, (1, 1, 1, 1), 7),
+    (3, 14, 14, 256, 256, 3, 3, 1, (1, 1, 1, 1), -3),
+    (4, 7, 7, 512, 512, 3, 3, 1, (1, 1, 1, 1), 0),
+    (2, 57, 57, 64, 64, 3, 3, 2, (1, 1, 1, 1), -128),     # stride 2, exact division: (57-1+2-2)/2
+    (2, 56, 56, 64, 256, 1, 1, 1, (0, 0, 0, 0), 11),      # 1x1, plain GEMM over pixels
+    (2, 55, 55, 256, 512, 1, 1, 2, (0, 0, 0, 0), -128),   # strided 1x1 shortcut
+    (1, 20, 24, 32, 48, 3, 3, 1, (1, 1, 1, 1), 5),        # 32-byte channel runs, ragged OC
+    (1, 9, 130, 64, 64, 3, 3, 1, (1, 1, 1, 1), -128),     # rows wider than a tile
+    (2, 16, 16, 96, 40, 1, 1, 1, (0, 0, 0, 0), 3),        # 96-byte runs
+]
+
+
+@pytest.mark.parametrize("case", TC_CONV_CASES)
+def test_tensor_core_conv_int8(ctx, case):
+    N, IH, IW, IC, OC, KH, KW, s, pad, izp = case
+    r = util.rng(100 + TC_CONV_CASES.index(case))
+    x, w, b = util.conv_int8_case(r, N, IH, IW, IC, OC, KH, KW, bias_range=1 << 16)
+    args = (list(pad), [s, s], [1, 1], izp, 0)
+    _, exp = oracle_conv_i8(x, w, b, *args)
+    st, out, kernel = run_conv_i8(ctx, x, w, b, *args)
+    assert kernel.startswith("tc_gemm"), kernel
+    assert st == tb.Status.OK
+    assert np.array_equal(out, exp), "int32 accumulators differ: %d of %d" % ((out != exp).sum(), exp.size)
+    mult, shift = util.rescale_params(r, OC)
+    shift = np.maximum(shift, 34).astype(np.int8)   # keeps |acc| < 2^(shift-1) for the deepest reduction here
+    resc = (mult, shift, -128, "DOUBLE_ROUND")
+    est, exp = oracle_conv_i8(x, w, b, *args, rescale=resc, clamp=(-128, 127))
+    assert est == orc.VALID
+    st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=(-128, 127))
+    assert kernel == "tc_gemm_i8_rescale" and st == tb.Status.OK
+    assert np.array_equal(out, exp), "rescaled outputs differ: %d of %d" % ((out != exp).sum(), exp.size)
+    # the CUDA-core kernel must agree as well
+    st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=(-128, 127), policy=1)
+    assert kernel == "conv2d_direct" and np.array_equal(out, exp)
+
+
+def test_rescale_require_reports_unpredictable(ctx):
+    # shift 30 with |acc| >= 2^29 violates apply_scale_32's range check (quant_util.h:53-62)
+    x = np.full((1, 4, 4, 64), 127, np.int8)
+    w = np.full((64, 3, 3, 64), 127, np.int8)
+    b = np.full(64, (1 << 30), np.int32)
+    mult = np.full(64, 1 << 30, np.int32)
+    shift = np.full(64, 30, np.int8)
+    resc = (mult, shift, 0, "DOUBLE_ROUND")
+    est, _ = oracle_conv_i8(x, w, b, [1, 1, 1, 1], [1, 1], [1, 1], 0, 0, rescale=resc)
+    assert est == orc.UNPREDICTABLE
+    for policy in (0, 1):
+        st, _, _ = run_conv_i8(ctx, x, w, b, [1, 1, 1, 1], [1, 1], [1, 1], 0, 0, rescale=resc, policy=policy)
+        assert st == tb.Status.UNPREDICTABLE
+
+
+def test_conv_error_ifs(ctx):
+    x, w, b = util.conv_int8_case(util.rng(2), 1, 8, 8, 4, 4, 3, 3)
+    tx, tw, tbias = ctx.from_numpy(x), ctx.from_numpy(w), ctx.from_numpy(b)
+    good = ctx.empty(I32, (1, 8, 8, 4))
+    assert ctx.conv2d(tx, tw, tbias, good, [1, 1, 1, 1], [1, 1], [1, 1]) == tb.Status.OK
+    # exact-division rule and output-shape rule (tensor_ops.cpp:203-223)
+    assert ctx.conv2d(tx, tw, tbias, good, [1, 1, 1, 1], [2, 2], [1, 1], check=False) == tb.Status.ERROR
+    bad = ctx.empty(I32, (1, 7, 8, 4))
+    assert ctx.conv2d(tx, tw, tbias, bad, [1, 1, 1, 1], [1, 1], [1, 1], check=False) == tb.Status.ERROR
+    assert ctx.conv2d(tx, tw, tbias, good, [-1, 3, 1, 1], [1, 1], [1, 1], check=False) == tb.Status.ERROR
+    assert ctx.conv2d(tx, tw, tbias, good, [1, 1, 1, 1], [0, 1], [1, 1], check=False) == tb.Status.ERROR
+    # channel / bias mismatches (:742-748)
+    tb3 = ctx.from_numpy(np.zeros(3, np.int32))
+    assert ctx.conv2d(tx, tw, tb3, good, [1, 1, 1, 1], [1, 1], [1, 1], check=False) == tb.Status.ERROR
+    tw5 = ctx.from_numpy(np.zeros((4, 3, 3, 5), np.int8))
+    assert ctx.conv2d(tx, tw5, tbias, good, [1, 1, 1, 1], [1, 1], [1, 1], check=False) == tb.Status.ERROR
+    # floating conv with a zero point (:805,811)
+    fx, fw, fb = ctx.from_numpy(np.zeros((1, 8, 8, 4), np.float32)), ctx.from_numpy(np.zeros((4, 3, 3, 4), np.float32)), \
+        ctx.from_numpy(np.zeros(4, np.float32))
+    fo = ctx.empty(F32, (1, 8, 8, 4))
+    assert ctx.conv2d(fx, fw, fb, fo, [1, 1, 1, 1], [1, 1], [1, 1], input_zp=1, check=False) == tb.Status.ERROR
+    _free(tx, tw, tbias, good, bad, tb3, tw5, fx, fw, fb, fo)
+
+
+# ------------------------------------------------------------------------------------------- MATMUL
+MATMUL_I8_CASES = [(2, 256, 256, 256, 3, -2), (1, 128, 384, 512, 0, 0), (3, 200, 130, 96, -7, 5), (1, 130, 4096, 272, 3, -2),
+                   (2, 5, 7, 3, 4, 15)]
+
+
+@pytest.mark.parametrize("N,H,C,W,azp,bzp", MATMUL_I8_CASES)
+def test_matmul_int8(ctx, N, H, C, W, azp, bzp):
+    r = util.rng(200 + H + W)
+    a = r.integers(-128, 128, size=(N, H, C)).astype(np.int8)
+    b = r.integers(-128, 128, size=(N, C, W)).astype(np.int8)
+    exp = orc.matmul(a, b, azp, bzp, nthreads=8)
+    for policy in (0, 1):
+        ta, tbb, to = ctx.from_numpy(a), ctx.from_numpy(b), ctx.empty(I32, (N, H, W))
+        old = ctx.set_kernel_policy(policy)
+        ctx.matmul(ta, tbb, to, azp, bzp)
+        kernel = ctx.last_kernel()
+        ctx.set_kernel_policy(old)
+        st, out = to.download()
+        _free(ta, tbb, to)
+        assert st == tb.Status.OK
+        assert np.array_equal(out, exp), "%s: %d of %d differ" % (kernel, (out != exp).sum(), exp.size)
+    # the host-buffer entry point
+    out = np.empty((N, H, W), np.int32)
+    assert ctx.matmul_host(a, b, out, azp, bzp) == tb.Status.OK
+    assert np.array_equal(out, exp)
+
+
+def test_matmul_int8_full_size_sampled(ctx):
+    """The benchmark's MATMUL (64 x [1024x4096] x [4096x1024], zero points 3 / -2) at full size: complete output
+    rows sampled across batches against int64 numpy, plus linearity in A over the whole output."""
+    N, H, C, W = 64, 1024, 4096, 1024
+    r = util.rng(2)
+    a = r.integers(-128, 128, size=(N, H, C), dtype=np.int8)
+    b = r.integers(-128, 128, size=(N, C, W), dtype=np.int8)
+    ta, tbb, to = ctx.from_numpy(a), ctx.from_numpy(b), ctx.empty(I32, (N, H, W))
+    ctx.matmul(ta, tbb, to, 3, -2)
+    assert ctx.last_kernel().startswith("tc_gemm")
+    st, out = to.download()
+    assert st == tb.Status.OK
+    for _ in range(96):
+        n, h = int(r.integers(N)), int(r.integers(H))
+        exp = (a[n, h].astype(np.int64) - 3) @ (b[n].astype(np.int64) + 2)
+        assert np.array_equal(out[n, h].astype(np.int64), exp), (n, h)
+    # every tile edge once: first / last rows and columns of every batch
+    for n in range(N):
+        for h in (0, H - 1):
+            exp = (a[n, h].astype(np.int64) - 3) @ (b[n].astype(np.int64) + 2)
+            assert np.array_equal(out[n, h].astype(np.int64), exp), (n, h)
+    # linearity: A with zero point za equals (A - 1) with zero point za - 1 wherever A - 1 stays in range
+    a2 = np.maximum(a, -127) - 1
+    ta2, to2 = ctx.from_numpy(a2.astype(np.int8)), ctx.empty(I32, (N, H, W))
+    ta3 = ctx.from_numpy(np.maximum(a, -127).astype(np.int8))
+    ctx.matmul(ta2, tbb, to2, 2, -2)
+    ctx.matmul(ta3, tbb, to, 3, -2)
+    _, o2 = to2.download()
+    _, o3 = to.download()
+    assert np.array_equal(o2, o3)
+    _free(ta, ta2, ta3, tbb, to, to2)
+
+
+def _dot_check(out, a64, b64, fn, ks, out_name):
+    ref = fn(a64, b64, mode="f64")
+    bnd = fn(a64, b64, mode="f64", bounds=True)
+    ok, info = orc.verify_dot_product(out, ref, bnd, orc.dot_product_ksb(ks, "fp32", out_name), out=out_name)
+    return ok, info
+
+
+@pytest.mark.parametrize("dt,name", [(F32, "fp32"), (F16, "fp16"), (BF16, "bf16")])
+@pytest.mark.parametrize("shape", [(2, 256, 512, 256), (1, 130, 96, 72), (2, 64, 1000, 48)])
+def test_matmul_float(ctx, dt, name, shape):
+    N, H, C, W = shape
+    r = util.rng(300 + H)
+    a = r.standard_normal((N, H, C)).astype(np.float32)
+    b = r.standard_normal((N, C, W)).astype(np.float32)
+    if dt != F32:
+        a, b = orc.fptrunc(a, name), orc.fptrunc(b, name)
+    for policy in (0, 1):
+        def up(v):
+            return ctx.from_numpy(v) if dt == F32 else ctx.from_numpy(v.astype(np.float16)) if dt == F16 else \
+                ctx.from_numpy(util.to_bf16_bits(v), BF16)
+        ta, tbb, to = up(a), up(b), ctx.empty(dt, (N, H, W))
+        old = ctx.set_kernel_policy(policy)
+        ctx.matmul(ta, tbb, to)
+        kernel = ctx.last_kernel()
+        ctx.set_kernel_policy(old)
+        st, out = to.download()
+        _free(ta, tbb, to)
+        out = util.from_bf16_bits(out) if dt == BF16 else out.astype(np.float32)
+        ok, info = _dot_check(out, a.astype(np.float64), b.astype(np.float64), orc.matmul, C, name)
+        assert ok, (kernel, info)
+
+
+# ------------------------------------------------------------------------------------------- floating convolution
+FP_CONV_CASES = [
+    (2, 28, 28, 32, 192, 1, 1, 1, (0, 0, 0, 0)),    # the inverted-residual expand shape (small)
+    (2, 14, 14, 192, 64, 1, 1, 1, (0, 0, 0, 0)),    # project
+    (1, 12, 12, 64, 32, 3, 3, 1, (1, 1, 1, 1)),
+    (1, 13, 13, 16, 24, 3, 3, 2, (1, 1, 1, 1)),
+    (1, 6, 6, 5, 7, 3, 3, 1, (1, 1, 1, 1)),         # CUDA-core path
+]
+
+
+@pytest.mark.parametrize("dt,name", [(F16, "fp16"), (BF16, "bf16"), (F32, "fp32")])
+@pytest.mark.parametrize("case", FP_CONV_CASES)
+def test_conv_float(ctx, dt, name, case):
+    N, IH, IW, IC, OC, KH, KW, s, pad = case
+    r = util.rng(400 + IC + OC)
+    x = orc.fptrunc(r.standard_normal((N, IH, IW, IC)).astype(np.float32), name)
+    w = orc.fptrunc((r.standard_normal((OC, KH, KW, IC)) / np.sqrt(KH * KW * IC)).astype(np.float32), name)
+    b = orc.fptrunc((0.1 * r.standard_normal(OC)).astype(np.float32), name)
+    args = (list(pad), [s, s], [1, 1])
+    ref = orc.conv2d(x, w, b, *args, mode="f64")
+    bnd = orc.conv2d(x, w, b, *args, mode="f64", bounds=True)
+    ksb = orc.dot_product_ksb(KH * KW * IC + 1, "fp32", name)
+    for policy in (0, 1):
+        st, out, kernel = run_conv_fp(ctx, x, w, b, *args, dt, policy=policy)
+        ok, info = orc.verify_dot_product(out, ref, bnd, ksb, out=name)
+        assert ok, (kernel, info)
+    # fused CLAMP [0, 6]: clip then round to the storage type; exact against clip of the unfused fp32 result
+    st, out, kernel = run_conv_fp(ctx, x, w, b, *args, dt, clamp=(0.0, 6.0))
+    assert out.min() >= 0.0 and out.max() <= 6.0
+    ok, info = orc.verify_dot_product(out, np.clip(ref, 0, 6), bnd, ksb, out=name)
+    assert ok, (kernel, info)
+
+
+@pytest.mark.parametrize("dt,name", [(F16, "fp16"), (BF16, "bf16"), (F32, "fp32")])
+def test_depthwise_float(ctx, dt, name):
+    r = util.rng(500)
+    for (N, IH, IW, C, M, s, pad) in ((2, 17, 17, 64, 1, 2, (1, 1, 1, 1)), (1, 9, 9, 6, 2, 1, (1, 1, 1, 1))):
+        x = orc.fptrunc(r.standard_normal((N, IH, IW, C)).astype(np.float32), name)
+        w = orc.fptrunc((r.standard_normal((3, 3, C, M)) / 3).astype(np.float32), name)
+        b = orc.fptrunc((0.1 * r.standard_normal(C * M)).astype(np.float32), name)
+        args = (list(pad), [s, s], [1, 1])
+        ref = orc.depthwise_conv2d(x, w, b, *args, mode="f64")
+        bnd = orc.depthwise_conv2d(x, w, b, *args, mode="f64", bounds=True)
+        st, out, kernel = run_conv_fp(ctx, x, w, b, *args, dt, depthwise=True)
+        ok, info = orc.verify_dot_product(out, ref, bnd, orc.dot_product_ksb(10, "fp32", name), out=name)
+        assert ok, (kernel, info)
+
+
+# ------------------------------------------------------------------------------------------- elementwise
+def test_rescale_standalone_sweep(ctx):
+    r = util.rng(6)
+    for shape in ((4, 7, 9, 64), (3, 1000), (5, 3), (17,)):
+        C = shape[-1]
+        x32 = r.integers(-(1 << 28), 1 << 28, size=shape).astype(np.int32)
+        mult, shift = util.rescale_params(r, C)
+        for rounding in ("SINGLE_ROUND", "DOUBLE_ROUND"):
+            est, exp = orc.rescale(x32, mult, shift, True, True, rounding, 0, -5, 32, 8)
+            st, out = _rescale_dev(ctx, x32, I32, I8, mult, I32, shift, output_zp=-5, rounding=rounding,
+                                   per_channel=True)
+            assert st == est == tb.Status.OK and np.array_equal(out.astype(np.int32), exp)
+        # int8 -> int32 (the first leg of a residual join), per-tensor
+        x8 = r.integers(-128, 128, size=shape).astype(np.int8)
+        est, exp = orc.rescale(x8, [1 << 30], [20], False, True, "SINGLE_ROUND", -11, 0, 8, 32)
+        st, out = _rescale_dev(ctx, x8, I8, I32, [1 << 30], I32, [20], input_zp=-11)
+        assert st == est and np.array_equal(out, exp)
+        # int16 with scale16
+        x16 = r.integers(-32768, 32768, size=shape).astype(np.int16)
+        est, exp = orc.rescale(x16, [12345], [14], False, False, "SINGLE_ROUND", 0, 3, 16, 8)
+        st, out = _rescale_dev(ctx, x16, I16, I8, [12345], I16, [14], output_zp=3, scale32=False)
+        assert st == est and np.array_equal(out.astype(np.int32), exp)
+    # REQUIRE: |value| >= 2^(shift-1)
+    st, _ = _rescale_dev(ctx, np.array([1 << 29], np.int32), I32, I8, [1 << 30], I32, [30])
+    assert st == tb.Status.UNPREDICTABLE
+
+
+def test_clamp_and_add(ctx):
+    r = util.rng(7)
+    x = r.integers(-128, 128, size=(3, 5, 7, 33)).astype(np.int8)
+    tx, to = ctx.from_numpy(x), ctx.empty(I8, x.shape)
+    ctx.clamp(tx, to, -100, 90)
+    _, out = to.download()
+    assert np.array_equal(out.astype(np.int32), orc.clamp(x, -100, 90)[1])
+    assert ctx.clamp(tx, to, 5, 4, check=False) == tb.Status.ERROR
+    _free(tx, to)
+    xf = np.concatenate([r.standard_normal(1000).astype(np.float32) * 5, [np.nan, np.inf, -np.inf]]).astype(np.float32)
+    for dt, name in ((F16, "fp16"), (F32, "fp32")):
+        v = orc.fptrunc(xf, name)
+        tx = ctx.from_numpy(v.astype(np.float16) if dt == F16 else v)
+        to = ctx.empty(dt, v.shape)
+        for ign in (False, True):
+            ctx.clamp(tx, to, 0.0, 6.0, nan_ignore=ign)
+            _, out = to.download()
+            exp = orc.clamp(v, 0.0, 6.0, mode="f32", fdt=name, nan_ignore=ign)[1]
+            assert np.array_equal(out.astype(np.float32), exp, equal_nan=True)
+        _free(tx, to)
+    # INT32 ADD with broadcast and the overflow REQUIRE
+    a = r.integers(-1000, 1000, size=(2, 1, 4, 8)).astype(np.int32)
+    b = r.integers(-1000, 1000, size=(2, 3, 1, 8)).astype(np.int32)
+    ta, tbb, to = ctx.from_numpy(a), ctx.from_numpy(b), ctx.empty(I32, (2, 3, 4, 8))
+    assert ctx.add(ta, tbb, to) == tb.Status.OK
+    st, out = to.download()
+    assert st == tb.Status.OK and np.array_equal(out, orc.add(a, b)[1])
+    _free(ta, tbb, to)
+    a = np.array([2147483647, 5, -7, 9], np.int32)
+    ta, tbb, to = ctx.from_numpy(a), ctx.from_numpy(np.ones(4, np.int32)), ctx.empty(I32, (4,))
+    ctx.add(ta, tbb, to)
+    st, out = to.download()
+    assert st == tb.Status.UNPREDICTABLE and out.tolist() == [-2147483648, 6, -6, 10]
+    _free(ta, tbb, to)
+    ta, tbb, to = ctx.from_numpy(np.zeros((2, 3), np.int32)), ctx.from_numpy(np.zeros((2, 2), np.int32)), ctx.empty(I32, (2, 3))
+    assert ctx.add(ta, tbb, to, check=False) == tb.Status.ERROR
+    _free(ta, tbb, to)
+    # fp16 ADD: fpTrunc(a + b), 0.5 ulp against fp64
+    af = orc.fptrunc(r.standard_normal((4, 64)).astype(np.float32), "fp16")
+    bf = orc.fptrunc(r.standard_normal((4, 64)).astype(np.float32), "fp16")
+    ta, tbb, to = ctx.from_numpy(af.astype(np.float16)), ctx.from_numpy(bf.astype(np.float16)), ctx.empty(F16, (4, 64))
+    ctx.add(ta, tbb, to)
+    _, out = to.download()
+    assert np.array_equal(out.astype(np.float32), orc.add(af, bf, mode="f32", fdt="fp16")[1])
+    assert orc.verify_ulp(out, af.astype(np.float64) + bf.astype(np.float64), 0.5, out="fp16")
+    _free(ta, tbb, to)
+
+
+def test_residual_add(ctx):
+    """RESCALE(i8->i32) x2 + ADD + RESCALE(i32->i8) + CLAMP in one pass equals the five nodes run separately."""
+    r = util.rng(8)
+    for shape in ((2, 7, 7, 64), (1, 3, 5, 10)):
+        a = r.integers(-128, 128, size=shape).astype(np.int8)
+        b = r.integers(-128, 128, size=shape).astype(np.int8)
+        ma, sa, mb, sb, mo, so = [1 << 30], [11], [1518500250], [12], [1270000000], [49]
+        _, ea = orc.rescale(a, ma, sa, False, True, "SINGLE_ROUND", -128, 0, 8, 32)
+        _, eb = orc.rescale(b, mb, sb, False, True, "SINGLE_ROUND", 3, 0, 8, 32)
+        _, es = orc.add(ea, eb)
+        est, eo = orc.rescale(es, mo, so, False, True, "DOUBLE_ROUND", 0, -128, 32, 8)
+        _, eo = orc.clamp(eo, -128, 127)
+        ta, tbb, to = ctx.from_numpy(a), ctx.from_numpy(b), ctx.empty(I8, shape)
+        consts = [ctx.from_numpy(np.asarray(v, np.int32)) for v in (ma, mb, mo)] + \
+                 [ctx.from_numpy(np.asarray(v, np.int8)) for v in (sa, sb, so)]
+        ctx.residual_add(ta, tb.RescaleAttr(consts[0], consts[3], -128, 0), tbb, tb.RescaleAttr(consts[1], consts[4], 3, 0),
+                         tb.RescaleAttr(consts[2], consts[5], 0, -128, rounding="DOUBLE_ROUND"), to, clamp=(-128, 127))
+        st, out = to.download()
+        assert st == est == tb.Status.OK and np.array_equal(out.astype(np.int32), eo)
+        _free(ta, tbb, to, *consts)
+
+
+def test_pools(ctx):
+    r = util.rng(9)
+    for (N, H, W, C, k, pad, s) in ((2, 112, 112, 64, (3, 3), (1, 0, 1, 0), (2, 2)), (1, 9, 7, 5, (2, 3), (1, 0, 2, 1), (1, 1)),
+                                   (3, 7, 7, 2048, (7, 7), (0, 0, 0, 0), (1, 1))):
+        if N * H * W * C > 4_000_000:
+            N = 1
+        x = r.integers(-128, 128, size=(N, H, W, C)).astype(np.int8)
+        OH, OW = orc.pool_out_hw(H, W, k, pad, s)
+        tx, to = ctx.from_numpy(x), ctx.empty(I8, (N, OH, OW, C))
+        ctx.max_pool2d(tx, to, k, pad, s)
+        _, out = to.download()
+        assert np.array_equal(out.astype(np.int32), orc.max_pool2d(x, k, pad, s))
+        ctx.avg_pool2d(tx, to, k, pad, s, -3, 7)
+        st, out = to.download()
+        est, exp = orc.avg_pool2d(x, k, pad, s, -3, 7)
+        assert st == est == tb.Status.OK and np.array_equal(out.astype(np.int32), exp)
+        _free(tx, to)
+    tx, to = ctx.from_numpy(np.zeros((1, 8, 8, 4), np.int8)), ctx.empty(I8, (1, 8, 8, 4))
+    assert ctx.max_pool2d(tx, to, (2, 2), (2, 0, 0, 0), (1, 1), check=False) == tb.Status.ERROR   # pad >= kernel
+    _free(tx, to)
+
+
+# ------------------------------------------------------------------------------------------- full-size conv layers
+def test_resnet_3x3_layer_full_size(ctx):
+    """32x56x56x64 -> 3x3, 64 channels, input_zp -128, per-channel RESCALE to int8 (output_zp -128), CLAMP."""
+    r = util.rng(3)
+    x, w, b = util.conv_int8_case(r, 32, 56, 56, 64, 64, 3, 3, bias_range=1 << 16)
+    mult, shift = util.rescale_params(r, 64)
+    resc = (mult, shift, -128, "DOUBLE_ROUND")
+    args = ([1, 1, 1, 1], [1, 1], [1, 1], -128, 0)
+    est, exp = oracle_conv_i8(x, w, b, *args, rescale=resc, clamp=(-128, 127))
+    assert est == orc.VALID
+    st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=(-128, 127))
+    assert kernel == "tc_gemm_i8_rescale" and st == tb.Status.OK and np.array_equal(out, exp)
+
+
+def test_resnet_stem_layer(ctx):
+    """7x7 stride-2 stem on 224x224x3 with the TOSA-legal pad [3,2,3,2] (batch 4 here)."""
+    r = util.rng(4)
+    x, w, b = util.conv_int8_case(r, 4, 224, 224, 3, 64, 7, 7, bias_range=1 << 16)
+    mult, shift = util.rescale_params(r, 64)
+    resc = (mult, shift, -128, "DOUBLE_ROUND")
+    args = ([3, 2, 3, 2], [2, 2], [1, 1], -128, 0)
+    est, exp = oracle_conv_i8(x, w, b, *args, rescale=resc, clamp=(-128, 127))
+    st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=(-128, 127))
+    assert st == est == tb.Status.OK and np.array_equal(out, exp)
