@@ -33,6 +33,17 @@ METRIC = "int8 MATMUL throughput, 64x[1024x4096]x[4096x1024], A_zp=3 B_zp=-2, in
 WORKLOAD = "matmul_int8_64x1024x4096x1024_zp3_-2"
 
 
+def set_batches(nb):
+    """Shrinks the workload to `nb` batches per GPU (profiling runs only; the benchmark line uses 64)."""
+    global N_BATCH, OPS_PER_STEP, ALG_BYTES_PER_STEP, WORKLOAD
+    if nb == N_BATCH:
+        return
+    N_BATCH = nb
+    OPS_PER_STEP = 2.0 * N_BATCH * H * C * W
+    ALG_BYTES_PER_STEP = N_BATCH * (H * C + C * W + 4 * H * W)
+    WORKLOAD = "matmul_int8_%dx1024x4096x1024_zp3_-2 (reduced batch count, profiling only)" % nb
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -152,6 +163,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="tb200")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--batches", type=int, default=N_BATCH,
+                    help="batches per GPU; the default is the benchmark workload, smaller values are for profiling")
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
 
@@ -162,6 +176,7 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
+    set_batches(args.batches)
 
     import torch
     import torch.distributed as dist
@@ -233,7 +248,7 @@ def main():
         assert st == tb.Status.OK, ctx.last_error()
 
         # ---- end to end through the C ABI with host buffers: upload, matmul, download every step
-        for _ in range(1):
+        if args.e2e_steps > 0:
             upload(); step(); download()
         barrier()
         e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -256,7 +271,7 @@ def main():
         peaks = measured_peaks()
         total_ops = OPS_PER_STEP * args.steps * world
         value = total_ops / (ms * 1e-3) / 1e12
-        e2e_value = OPS_PER_STEP * args.e2e_steps * world / (e2e_ms * 1e-3) / 1e12
+        e2e_value = OPS_PER_STEP * args.e2e_steps * world / (e2e_ms * 1e-3) / 1e12 if args.e2e_steps > 0 else None
         gemm_avg_ms = gemm_ms / max(gemm_n, 1)
         achieved = OPS_PER_STEP / (gemm_avg_ms * 1e-3) / 1e12
         # int8 dense peak is not in MEASURED_PEAKS.json: twice the measured bf16 figure stands in for it; the
@@ -270,6 +285,8 @@ def main():
                 traffic = json.load(f).get("dram_bytes_per_launch_full_workload")
         cpu_threads = None
         try:
+            if args.skip_cpu_baseline:
+                raise RuntimeError("skipped by --skip-cpu-baseline")
             from oracle import oracle as orc
             cpu_threads = orc.num_procs()
             cpu_tops, sample, _, _ = cpu_port_rate(cpu_threads, 10.0, a_np, b_np)
@@ -285,7 +302,7 @@ def main():
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": int(a_pin.numel() + b_pin.numel()),
                     "d2h_bytes_per_step": int(out_pin.numel() * 4), "steps": args.e2e_steps,
-                    "ms_per_step": e2e_ms / args.e2e_steps},
+                    "ms_per_step": e2e_ms / max(args.e2e_steps, 1)},
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s",
                          "frac": achieved / peak, "traffic": traffic, "kernel": kernel_name,

@@ -207,6 +207,32 @@ extern "C"
                                              const void* a, const void* b, int32_t N, int32_t H, int32_t C,
                                              int32_t W, int32_t a_zp, int32_t b_zp, void* out);
 
+    /* Largest N*(H+W) the built-in scratch of tb200_matmul_i8_noalloc holds (int32 entries, 1 MiB in total). */
+#define TB200_NOALLOC_MAX_SUMS 262144
+
+    /* INT8 MATMUL with zero points, out[N,H,W] (INT32) = (a[N,H,C] - a_zp) x (b[N,C,W] - b_zp), on raw device
+     * pointers, performing no device allocation.  It has no counterpart in the reference, which allocates freely
+     * on the host; it exists for hosts that must not allocate device memory at evaluation time: an adapter that
+     * was handed a fixed set of device buffers by the application embedding it (all device memory belongs to that
+     * application's pool), or a latency-bound evaluation loop that cannot take the device-wide synchronisation of
+     * cudaMalloc / cudaFree.  tb200_matmul keeps its zero-point row / column sums in context scratch obtained with
+     * cudaMalloc; this variant keeps them in a fixed array inside the library image instead, which every GPU that
+     * loads the library holds until the process exits (1 MiB + 256 bytes).
+     *
+     *  - Limit: N*(H+W) <= TB200_NOALLOC_MAX_SUMS, otherwise TB200_ERROR with a message naming the limit.
+     *  - The CUDA device that owns the pointers must be current.  The first call on each device looks up the
+     *    device address of the built-in array (a one-time set-up); make that first call outside any stream
+     *    capture.  No call invokes cudaMalloc, cudaFree or any allocating library routine.
+     *  - All calls on a device share the one array, and it keeps the previous call's contents.  The status word
+     *    in it is cleared at the start of each call; the sums are rewritten for the extent in use.  Two calls
+     *    whose kernels overlap on the GPU (different streams without ordering) race on it: order them.
+     *  - a, b, out: 16-byte aligned device pointers, row-major.  `stream` is a cudaStream_t (NULL = default).
+     *    Work is enqueued on `stream`; with synchronize != 0 the call also waits for it and reports a kernel
+     *    that gave up on its pipeline as TB200_INTERNAL.  `err` (may be NULL) receives a message on failure. */
+    TB200_API tb200_status tb200_matmul_i8_noalloc(void* stream, const int8_t* a, const int8_t* b, int32_t* out,
+                                                   int32_t N, int32_t H, int32_t C, int32_t W, int32_t a_zp,
+                                                   int32_t b_zp, int32_t synchronize, char* err, size_t err_len);
+
     /* Selects kernels: 0 = automatic (tensor-core kernels where the shape qualifies), 1 = force the
      * CUDA-core kernels (for A/B checks).  Returns the previous value. */
     TB200_API int tb200_set_kernel_policy(tb200_ctx* ctx, int policy);

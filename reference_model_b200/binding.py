@@ -70,7 +70,7 @@ EXPORTS = [
     "tb200_tensor_alloc", "tb200_tensor_wrap", "tb200_tensor_free", "tb200_tensor_upload", "tb200_tensor_download",
     "tb200_tensor_data", "tb200_tensor_bytes", "tb200_conv2d", "tb200_depthwise_conv2d", "tb200_matmul",
     "tb200_rescale", "tb200_clamp", "tb200_add", "tb200_residual_add", "tb200_max_pool2d", "tb200_avg_pool2d",
-    "tb200_matmul_host", "tb200_set_kernel_policy", "tb200_last_kernel",
+    "tb200_matmul_host", "tb200_set_kernel_policy", "tb200_last_kernel", "tb200_matmul_i8_noalloc",
 ]
 
 
@@ -111,6 +111,8 @@ def load_library():
         "tb200_max_pool2d": (i32, [vp, vp, p_i32, p_i32, p_i32, vp]),
         "tb200_avg_pool2d": (i32, [vp, vp, p_i32, p_i32, p_i32, i32, i32, vp]),
         "tb200_matmul_host": (i32, [vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
+        "tb200_matmul_i8_noalloc": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, ctypes.c_char_p,
+                                          ctypes.c_size_t]),
         "tb200_set_kernel_policy": (ctypes.c_int, [vp, ctypes.c_int]),
         "tb200_last_kernel": (cp, [vp]),
     }
@@ -124,6 +126,20 @@ def load_library():
 
 def _ivec(v):
     return (ctypes.c_int32 * len(v))(*[int(x) for x in v])
+
+
+NOALLOC_MAX_SUMS = 262144   # TB200_NOALLOC_MAX_SUMS
+
+
+def matmul_i8_noalloc(a_ptr, b_ptr, out_ptr, N, H, C, W, a_zp=0, b_zp=0, stream=None, synchronize=True):
+    """tb200_matmul_i8_noalloc on raw device pointers (ints).  The owning CUDA device must be current.
+    Returns (Status, error text)."""
+    buf = ctypes.create_string_buffer(256)
+    st = load_library().tb200_matmul_i8_noalloc(ctypes.c_void_p(stream) if stream else None, ctypes.c_void_p(a_ptr),
+                                                ctypes.c_void_p(b_ptr), ctypes.c_void_p(out_ptr), int(N), int(H),
+                                                int(C), int(W), int(a_zp), int(b_zp), int(bool(synchronize)), buf,
+                                                len(buf))
+    return Status(st), buf.value.decode()
 
 
 class RescaleAttr:
