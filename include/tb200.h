@@ -207,7 +207,8 @@ extern "C"
                                              const void* a, const void* b, int32_t N, int32_t H, int32_t C,
                                              int32_t W, int32_t a_zp, int32_t b_zp, void* out);
 
-    /* Largest N*(H+W) the built-in scratch of tb200_matmul_i8_noalloc holds (int32 entries, 1 MiB in total). */
+    /* Largest N*(H + W rounded up to a multiple of 256) the built-in scratch of tb200_matmul_i8_noalloc holds
+     * (int32 entries, 1 MiB in total). */
 #define TB200_NOALLOC_MAX_SUMS 262144
 
     /* INT8 MATMUL with zero points, out[N,H,W] (INT32) = (a[N,H,C] - a_zp) x (b[N,C,W] - b_zp), on raw device
@@ -219,7 +220,8 @@ extern "C"
      * cudaMalloc; this variant keeps them in a fixed array inside the library image instead, which every GPU that
      * loads the library holds until the process exits (1 MiB + 256 bytes).
      *
-     *  - Limit: N*(H+W) <= TB200_NOALLOC_MAX_SUMS, otherwise TB200_ERROR with a message naming the limit.
+     *  - Limit: N*(H + roundup(W, 256)) <= TB200_NOALLOC_MAX_SUMS, otherwise TB200_ERROR with a message naming
+     *    the limit.
      *  - The CUDA device that owns the pointers must be current.  The first call on each device looks up the
      *    device address of the built-in array (a one-time set-up); make that first call outside any stream
      *    capture.  No call invokes cudaMalloc, cudaFree or any allocating library routine.

@@ -254,9 +254,6 @@ static void fill_tc_epilogue(TcProblem* q, const EpiInfo& e, tb200_dtype out_dt)
     if (e.has_rescale)
     {
         q->epi          = TC_EPI_RESCALE;
-        q->multiplier   = reinterpret_cast<const int32_t*>(e.rs.mult);
-        q->shift        = e.rs.shift;
-        q->per_channel  = e.rs.per_channel;
         q->double_round = e.rs.rounding == TB200_DOUBLE_ROUND;
         q->out_zp       = (int32_t)e.rs.out_zp_ext;
         int64_t lo = e.rs.qmin, hi = e.rs.qmax;
@@ -579,43 +576,61 @@ extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, 
         std::string why;
         if (tc_gemm_supported(q, &why))
         {
+            const int OCpad = (OC + 255) / 256 * 256;
             if (int_path)
             {
-                const size_t table_elems = (size_t)(KH + 1) * (KW + 1) * OC + 2 * (size_t)OC;
-                st = ensure_scratch(ctx, table_elems * sizeof(int32_t));
-                if (st != TB200_OK)
-                    return st;
-                int32_t* table = reinterpret_cast<int32_t*>(ctx->scratch);
-                conv_weight_tables_kernel<<<(OC + 127) / 128, 128, 0, ctx->stream>>>(
-                    reinterpret_cast<const int8_t*>(weight->data), reinterpret_cast<const int32_t*>(bias->data),
-                    bias->shape[0], OC, KH, KW, IC, input_zp, table);
-                st = post_launch(ctx, "conv_weight_tables");
-                if (st != TB200_OK)
-                    return st;
-                q.col_corr = table + (size_t)(KH + 1) * (KW + 1) * OC + OC;
-                const bool padded = pad[0] || pad[1] || pad[2] || pad[3];
-                q.wsum_prefix = (input_zp != 0 && padded) ? table : nullptr;
-                q.in_zp       = input_zp;
+                const bool padded  = pad[0] || pad[1] || pad[2] || pad[3];
+                const bool classes = input_zp != 0 && padded;
+                const size_t ncls  = classes ? (size_t)(KH + 1) * (KH + 1) * (KW + 1) * (KW + 1) : 1;
+                // scratch: prefix | corr | mult_pad | shift_pad
+                const size_t prefix_elems = (size_t)(KH + 1) * (KW + 1) * OC;
+                const size_t corr_elems   = ncls * OCpad;
+                const size_t bytes        = (prefix_elems + corr_elems + OCpad) * sizeof(int32_t) + OCpad + 64;
+                if (bytes <= ((size_t)64 << 20))
+                {
+                    st = ensure_scratch(ctx, bytes);
+                    if (st != TB200_OK)
+                        return st;
+                    int32_t* prefix   = reinterpret_cast<int32_t*>(ctx->scratch);
+                    int32_t* corr     = prefix + ((prefix_elems + 3) & ~(size_t)3);
+                    int32_t* mult_pad = corr + corr_elems;
+                    int8_t* shift_pad = reinterpret_cast<int8_t*>(mult_pad + OCpad);
+                    conv_epilogue_tables_kernel<<<(OCpad + 127) / 128, 128, 0, ctx->stream>>>(
+                        reinterpret_cast<const int8_t*>(weight->data), reinterpret_cast<const int32_t*>(bias->data),
+                        bias->shape[0], OC, OCpad, KH, KW, IC, input_zp, classes ? 1 : 0,
+                        epi.has_rescale ? reinterpret_cast<const int32_t*>(epi.rs.mult) : nullptr,
+                        epi.has_rescale ? epi.rs.shift : nullptr, epi.rs.per_channel, prefix, corr,
+                        epi.has_rescale ? mult_pad : nullptr, shift_pad);
+                    st = post_launch(ctx, "conv_epilogue_tables");
+                    if (st != TB200_OK)
+                        return st;
+                    q.corr         = corr;
+                    q.corr_stride  = OCpad;
+                    q.corr_classes = classes ? 1 : 0;
+                    q.mult_pad     = mult_pad;
+                    q.shift_pad    = shift_pad;
+                    return tc_gemm_launch(ctx, q);
+                }
             }
             else
             {
-                st = ensure_scratch(ctx, (size_t)bias->shape[0] * sizeof(float));
+                st = ensure_scratch(ctx, (size_t)OCpad * sizeof(float));
                 if (st != TB200_OK)
                     return st;
                 float* bf = reinterpret_cast<float*>(ctx->scratch);
                 if (input->dtype == TB200_FP16)
-                    bias_to_f32_kernel<__half><<<(bias->shape[0] + 127) / 128, 128, 0, ctx->stream>>>(
-                        reinterpret_cast<const __half*>(bias->data), bf, bias->shape[0]);
+                    bias_to_f32_kernel<__half><<<(OCpad + 127) / 128, 128, 0, ctx->stream>>>(
+                        reinterpret_cast<const __half*>(bias->data), bias->shape[0], OC, bf, OCpad);
                 else
-                    bias_to_f32_kernel<__nv_bfloat16><<<(bias->shape[0] + 127) / 128, 128, 0, ctx->stream>>>(
-                        reinterpret_cast<const __nv_bfloat16*>(bias->data), bf, bias->shape[0]);
+                    bias_to_f32_kernel<__nv_bfloat16><<<(OCpad + 127) / 128, 128, 0, ctx->stream>>>(
+                        reinterpret_cast<const __nv_bfloat16*>(bias->data), bias->shape[0], OC, bf, OCpad);
                 st = post_launch(ctx, "bias_to_f32");
                 if (st != TB200_OK)
                     return st;
-                q.bias_f = bf;
-                q.bias_n = bias->shape[0];
+                q.bias_f_pad  = bf;
+                q.corr_stride = OCpad;
+                return tc_gemm_launch(ctx, q);
             }
-            return tc_gemm_launch(ctx, q);
         }
     }
 
@@ -826,12 +841,13 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
         {
             if (int_path && (a_zp != 0 || b_zp != 0))
             {
-                const size_t rows = (size_t)N * H, cols = (size_t)N * W;
-                st = ensure_scratch(ctx, (rows + cols) * sizeof(int32_t));
+                const int Wpad    = (W + 255) / 256 * 256;
+                const size_t rows = (size_t)N * H, cols = (size_t)N * Wpad;
+                st = ensure_scratch(ctx, (((rows + 3) & ~(size_t)3) + cols) * sizeof(int32_t));
                 if (st != TB200_OK)
                     return st;
                 int32_t* row_corr = reinterpret_cast<int32_t*>(ctx->scratch);
-                int32_t* col_corr = row_corr + rows;
+                int32_t* col_corr = row_corr + ((rows + 3) & ~(size_t)3);
                 int launches = 0;
                 if (b_zp != 0)
                 {
@@ -843,11 +859,17 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
                 }
                 if (a_zp != 0)
                 {
-                    dim3 grid((W + 127) / 128, N), block(32, 8);
-                    matmul_col_corr_kernel<<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const int8_t*>(b->data),
-                                                                           col_corr, C, W, a_zp);
-                    q.col_corr         = col_corr;
-                    q.col_corr_ystride = W;
+                    TB200_CUDA_CHECK(ctx, cudaMemsetAsync(col_corr, 0, cols * sizeof(int32_t), ctx->stream));
+                    const int xblocks = (W + 511) / 512;
+                    int ksplit        = std::max(1, std::min((C + 63) / 64, (4 * ctx->num_sms) / std::max(1, xblocks * N)));
+                    const int kper    = ((C + ksplit - 1) / ksplit + 7) / 8 * 8;
+                    ksplit            = (C + kper - 1) / kper;
+                    dim3 grid(xblocks, ksplit, N);
+                    matmul_col_corr_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const int8_t*>(b->data),
+                                                                         col_corr, C, W, Wpad, kper, a_zp);
+                    q.corr         = col_corr;
+                    q.corr_stride  = Wpad;
+                    q.corr_ystride = Wpad;
                     launches++;
                 }
                 st = post_launch(ctx, "matmul_zp_sums", launches);

@@ -145,19 +145,16 @@ struct TcProblem
     int epi;
     tb200_dtype out_dtype;
     void* out;
-    const int32_t* row_corr;    // [N*OH*OW] or null
-    const int32_t* col_corr;    // int32 [OC] (or [batch][OC] when col_corr_ystride != 0) or null
-    int col_corr_ystride;
-    const float* bias_f;        // TC_EPI_FLOAT: [OC] or [1] or null
-    int bias_n;
-    // zero-point border fix for padded convolutions: prefix sums over taps of the per-channel weight sums,
-    // table [(KH+1)*(KW+1)][OC]; used when in_zp != 0 and the tile touches the border
-    const int32_t* wsum_prefix;
-    int32_t in_zp;
-    // rescale (TC_EPI_RESCALE)
-    const int32_t* multiplier;
-    const int8_t* shift;
-    int per_channel, double_round;
+    const int32_t* row_corr;    // [N*OH*OW] added to every column of a row, or null
+    // per-column additive constants, padded: [classes][corr_stride]; corr_stride must be a multiple of 256 and cover
+    // OC.  corr_classes != 0: the table has (KH+1)^2 (KW+1)^2 rows indexed by the rectangle of in-scope filter taps
+    // ((ky_lo*(KH+1)+ky_hi)*(KW+1)+kx_lo)*(KW+1)+kx_hi.  corr_ystride: MATMUL, elements to advance per batch.
+    const int32_t* corr;
+    int corr_stride, corr_ystride, corr_classes;
+    const float* bias_f_pad;     // TC_EPI_FLOAT: fp32 bias padded to corr_stride, or null
+    const int32_t* mult_pad;     // TC_EPI_RESCALE: multipliers / shifts expanded per column and padded to corr_stride
+    const int8_t* shift_pad;
+    int double_round;
     int32_t out_zp;
     int32_t clamp_lo, clamp_hi;    // also the dtype range
     float clamp_lo_f, clamp_hi_f;

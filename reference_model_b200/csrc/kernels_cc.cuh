@@ -838,59 +838,94 @@ __global__ void matmul_row_corr_kernel(const int8_t* __restrict__ a, int32_t* __
     }
 }
 
-// col_corr[n*W + w] = -za * colsum(B[n,:,w]); block (32, 8): 32 x 4 columns, K split over 8 row groups.
-__global__ void matmul_col_corr_kernel(const int8_t* __restrict__ b, int32_t* __restrict__ col_corr, int C, int W,
-                                       int32_t a_zp)
+// col_corr[n*Wpad + w] += -za * sum over this block's K range of B[n,k,w].  The destination (stride Wpad, zeroed by
+// the caller) receives one atomic add per K split.  Block = 8 warps; a warp row covers 512 columns (16 per lane,
+// one 128-bit load); warps interleave over the K range.
+__global__ void __launch_bounds__(256) matmul_col_corr_kernel(const int8_t* __restrict__ b, int32_t* __restrict__ col_corr,
+                                                              int C, int W, int Wpad, int k_per_block, int32_t a_zp)
 {
-    __shared__ int32_t part[8][128];
-    const int n    = blockIdx.y;
-    const int col0 = blockIdx.x * 128 + threadIdx.x * 4;
-    int32_t s[4]   = { 0, 0, 0, 0 };
+    __shared__ int32_t part[8][512];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n    = blockIdx.z;
+    const int col0 = blockIdx.x * 512 + lane * 16;
+    const int k0   = blockIdx.y * k_per_block;
+    const int k1   = min(C, k0 + k_per_block);
     const int8_t* bp = b + (int64_t)n * C * W;
-    if ((W & 3) == 0)
+    int32_t s[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++)
+        s[j] = 0;
+    if ((W & 15) == 0)
     {
         if (col0 < W)
-            for (int c = threadIdx.y; c < C; c += 8)
+        {
+            for (int k = k0 + warp; k < k1; k += 8)
             {
-                const int v = *reinterpret_cast<const int*>(bp + (int64_t)c * W + col0);
-                s[0] += (int8_t)(v & 0xff);
-                s[1] += (int8_t)((v >> 8) & 0xff);
-                s[2] += (int8_t)((v >> 16) & 0xff);
-                s[3] += (int8_t)((v >> 24) & 0xff);
+                const int4 v = __ldg(reinterpret_cast<const int4*>(bp + (int64_t)k * W + col0));
+                const int w4[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+                {
+                    s[4 * q + 0] = __dp4a(w4[q], 0x00000001, s[4 * q + 0]);
+                    s[4 * q + 1] = __dp4a(w4[q], 0x00000100, s[4 * q + 1]);
+                    s[4 * q + 2] = __dp4a(w4[q], 0x00010000, s[4 * q + 2]);
+                    s[4 * q + 3] = __dp4a(w4[q], 0x01000000, s[4 * q + 3]);
+                }
             }
+        }
     }
     else
     {
-        for (int c = threadIdx.y; c < C; c += 8)
-            for (int j = 0; j < 4; j++)
+        for (int k = k0 + warp; k < k1; k += 8)
+#pragma unroll
+            for (int j = 0; j < 16; j++)
                 if (col0 + j < W)
-                    s[j] += bp[(int64_t)c * W + col0 + j];
+                    s[j] += bp[(int64_t)k * W + col0 + j];
     }
-    for (int j = 0; j < 4; j++)
-        part[threadIdx.y][threadIdx.x * 4 + j] = s[j];
+#pragma unroll
+    for (int j = 0; j < 16; j++)
+        part[warp][lane * 16 + j] = s[j];
     __syncthreads();
-    if (threadIdx.y == 0)
-        for (int j = 0; j < 4; j++)
-        {
-            int32_t t = 0;
-            for (int g = 0; g < 8; g++)
-                t += part[g][threadIdx.x * 4 + j];
-            if (col0 + j < W)
-                col_corr[(int64_t)n * W + col0 + j] = -a_zp * t;
-        }
+    for (int c = threadIdx.x; c < 512; c += 256)
+    {
+        int32_t t = 0;
+#pragma unroll
+        for (int g = 0; g < 8; g++)
+            t += part[g][c];
+        const int col = blockIdx.x * 512 + c;
+        if (col < W && t != 0)
+            atomicAdd(&col_corr[(int64_t)n * Wpad + col], -a_zp * t);
+    }
 }
 
-// CONV2D zero-point tables for weights OHWI (w_zp == 0 path):
-//   prefix[(ky)(kx)][oc], (KH+1)x(KW+1) inclusive 2-D prefix sums over taps of sum_ic w[oc,ky,kx,ic]
-//   bias_full[oc]  (bias broadcast resolved), stored right after the prefix table
-//   col_corr[oc] = bias_full[oc] - in_zp * prefix[KH][KW][oc], stored after bias_full
-__global__ void conv_weight_tables_kernel(const int8_t* __restrict__ w, const int32_t* __restrict__ bias, int bias_n,
-                                          int OC, int KH, int KW, int IC, int32_t in_zp, int32_t* __restrict__ table)
+// CONV2D epilogue constants for int8 weights OHWI with weight_zp == 0, one thread per padded output channel:
+//   prefix[(KH+1)(KW+1)][OC]  scratch: inclusive 2-D prefix sums over taps of sum_ic w[oc,ky,kx,ic]
+//   corr[classes][OCpad]      bias[oc] - in_zp * (sum of the weights of the in-scope taps).  With `classes` the table
+//                             has (KH+1)^2 (KW+1)^2 rows indexed ((ky_lo*(KH+1)+ky_hi)*(KW+1)+kx_lo)*(KW+1)+kx_hi;
+//                             otherwise a single row for the full filter
+//   mult_pad / shift_pad      RESCALE operands expanded per channel (per_channel == 0 repeats element 0), zero padded
+__global__ void conv_epilogue_tables_kernel(const int8_t* __restrict__ w, const int32_t* __restrict__ bias, int bias_n,
+                                            int OC, int OCpad, int KH, int KW, int IC, int32_t in_zp, int classes,
+                                            const int32_t* __restrict__ mult, const int8_t* __restrict__ shift,
+                                            int per_channel, int32_t* __restrict__ prefix, int32_t* __restrict__ corr,
+                                            int32_t* __restrict__ mult_pad, int8_t* __restrict__ shift_pad)
 {
     const int oc = blockIdx.x * blockDim.x + threadIdx.x;
-    if (oc >= OC)
+    if (oc >= OCpad)
         return;
-    const int W1 = KW + 1;
+    const int W1 = KW + 1, H1 = KH + 1;
+    const int ncls = classes ? H1 * H1 * W1 * W1 : 1;
+    if (oc >= OC)
+    {
+        for (int c = 0; c < ncls; c++)
+            corr[(int64_t)c * OCpad + oc] = 0;
+        if (mult_pad)
+        {
+            mult_pad[oc]  = 0;
+            shift_pad[oc] = 2;
+        }
+        return;
+    }
     for (int ky = 0; ky <= KH; ky++)
         for (int kx = 0; kx <= KW; kx++)
         {
@@ -901,25 +936,42 @@ __global__ void conv_weight_tables_kernel(const int8_t* __restrict__ w, const in
                 const int8_t* wp = w + (((int64_t)oc * KH + (ky - 1)) * KW + (kx - 1)) * IC;
                 for (int ic = 0; ic < IC; ic++)
                     s += wp[ic];
-                v = s + table[((ky - 1) * W1 + kx) * OC + oc] + table[(ky * W1 + kx - 1) * OC + oc] -
-                    table[((ky - 1) * W1 + kx - 1) * OC + oc];
+                v = s + prefix[((ky - 1) * W1 + kx) * OC + oc] + prefix[(ky * W1 + kx - 1) * OC + oc] -
+                    prefix[((ky - 1) * W1 + kx - 1) * OC + oc];
             }
-            table[(ky * W1 + kx) * OC + oc] = v;
+            prefix[(ky * W1 + kx) * OC + oc] = v;
         }
-    const int32_t b       = bias[bias_n == 1 ? 0 : oc];
-    int32_t* bias_full    = table + (size_t)(KH + 1) * W1 * OC;
-    int32_t* col_corr     = bias_full + OC;
-    bias_full[oc]         = b;
-    col_corr[oc]          = b - in_zp * table[(KH * W1 + KW) * OC + oc];
+    const int32_t b = bias[bias_n == 1 ? 0 : oc];
+    if (!classes)
+        corr[oc] = b - in_zp * prefix[(KH * W1 + KW) * OC + oc];
+    else
+    {
+        for (int yl = 0; yl <= KH; yl++)
+            for (int yh = 0; yh <= KH; yh++)
+                for (int xl = 0; xl <= KW; xl++)
+                    for (int xh = 0; xh <= KW; xh++)
+                    {
+                        int32_t rs = 0;
+                        if (yh > yl && xh > xl)
+                            rs = prefix[(yh * W1 + xh) * OC + oc] - prefix[(yl * W1 + xh) * OC + oc] -
+                                 prefix[(yh * W1 + xl) * OC + oc] + prefix[(yl * W1 + xl) * OC + oc];
+                        corr[(int64_t)(((yl * H1 + yh) * W1 + xl) * W1 + xh) * OCpad + oc] = b - in_zp * rs;
+                    }
+    }
+    if (mult_pad)
+    {
+        mult_pad[oc]  = mult[per_channel ? oc : 0];
+        shift_pad[oc] = shift[per_channel ? oc : 0];
+    }
 }
 
-// fp bias to float for the tensor-core epilogue
+// fp bias widened to fp32 and zero padded for the tensor-core epilogue (bias_n == 1 broadcasts)
 template <typename T>
-__global__ void bias_to_f32_kernel(const T* __restrict__ bias, float* __restrict__ out, int n)
+__global__ void bias_to_f32_kernel(const T* __restrict__ bias, int bias_n, int OC, float* __restrict__ out, int OCpad)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n)
-        out[i] = to_f32<T>(bias[i]);
+    if (i < OCpad)
+        out[i] = i < OC ? to_f32<T>(bias[bias_n == 1 ? 0 : i]) : 0.f;
 }
 
 }    // namespace tb200

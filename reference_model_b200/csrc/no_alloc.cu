@@ -18,10 +18,10 @@ namespace
 
 // Zero-point sums of this variant (same arithmetic as the context path's preparation kernels):
 //   row_corr[n*H + h] = -b_zp * sum_c A[n,h,c] + C * a_zp * b_zp      (one warp per row)
-//   col_corr[n*W + w] = -a_zp * sum_c B[n,c,w]                         (one thread per column, after the rows)
+//   col_corr[n*Wpad + w] = -a_zp * sum_c B[n,c,w]                      (one thread per column, after the rows)
 __global__ void noalloc_zp_sums_kernel(const int8_t* __restrict__ a, const int8_t* __restrict__ b,
                                        int32_t* __restrict__ row_corr, int32_t* __restrict__ col_corr, int N, int H,
-                                       int C, int W, int32_t a_zp, int32_t b_zp)
+                                       int C, int W, int Wpad, int32_t a_zp, int32_t b_zp)
 {
     const int lane      = threadIdx.x & 31;
     const int64_t gtid  = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -38,15 +38,19 @@ __global__ void noalloc_zp_sums_kernel(const int8_t* __restrict__ a, const int8_
         if (lane == 0)
             row_corr[r] = -b_zp * s + C * a_zp * b_zp;
     }
-    const int64_t cols = (int64_t)N * W;
+    // column sums are stored with a row stride padded to a multiple of 256 (the GEMM reads them 128 bits at a time)
+    const int64_t cols = (int64_t)N * Wpad;
     for (int64_t j = gtid; j < cols; j += nthr)
     {
-        const int n      = (int)(j / W);
-        const int w      = (int)(j - (int64_t)n * W);
-        const int8_t* bp = b + (int64_t)n * C * W + w;
-        int32_t s        = 0;
-        for (int c = 0; c < C; c++)
-            s += bp[(int64_t)c * W];
+        const int n = (int)(j / Wpad);
+        const int w = (int)(j - (int64_t)n * Wpad);
+        int32_t s   = 0;
+        if (w < W)
+        {
+            const int8_t* bp = b + (int64_t)n * C * W + w;
+            for (int c = 0; c < C; c++)
+                s += bp[(int64_t)c * W];
+        }
         col_corr[j] = -a_zp * s;
     }
 }
@@ -118,12 +122,13 @@ extern "C" tb200_status tb200_matmul_i8_noalloc(void* stream, const int8_t* a, c
         set_err(err, err_len, "tb200_matmul_i8_noalloc: tensor exceeds 2^31-1 elements");
         return TB200_ERROR;
     }
-    const int64_t rows = (int64_t)N * H, cols = (int64_t)N * W;
+    const int Wpad     = (W + 255) / 256 * 256;
+    const int64_t rows = ((int64_t)N * H + 3) & ~(int64_t)3, cols = (int64_t)N * Wpad;
     if (rows + cols > kMaxSumEntries)
     {
         char msg[200];
         snprintf(msg, sizeof(msg),
-                 "tb200_matmul_i8_noalloc: N*(H+W) = %lld exceeds the built-in scratch of %d entries; use tb200_matmul",
+                 "tb200_matmul_i8_noalloc: N*(H+roundup(W,256)) = %lld exceeds the built-in scratch of %d entries; use tb200_matmul",
                  (long long)(rows + cols), kMaxSumEntries);
         set_err(err, err_len, msg);
         return TB200_ERROR;
@@ -206,10 +211,11 @@ extern "C" tb200_status tb200_matmul_i8_noalloc(void* stream, const int8_t* a, c
             const int block     = 256;
             const int64_t items = std::max(rows * 32, cols);
             const int grid      = (int)std::max<int64_t>(1, std::min<int64_t>((items + block - 1) / block, (int64_t)local.num_sms * 16));
-            noalloc_zp_sums_kernel<<<grid, block, 0, local.stream>>>(a, b, row_corr, col_corr, N, H, C, W, a_zp, b_zp);
-            q.row_corr         = row_corr;
-            q.col_corr         = col_corr;
-            q.col_corr_ystride = W;
+            noalloc_zp_sums_kernel<<<grid, block, 0, local.stream>>>(a, b, row_corr, col_corr, N, H, C, W, Wpad, a_zp, b_zp);
+            q.row_corr     = row_corr;
+            q.corr         = col_corr;
+            q.corr_stride  = Wpad;
+            q.corr_ystride = Wpad;
         }
         st = tc_gemm_launch(ctx, q);
     }

@@ -58,20 +58,19 @@ struct TcKernelParams
     void* out;
     int out_es;
     int out_is_bf16;
-    const int32_t* row_corr;
-    const int32_t* col_corr;
-    int col_corr_ystride;
-    const int32_t* bias_i32;       // full-length int bias for border rows
-    const int32_t* wsum_prefix;    // [(KH+1)*(KW+1)][OC]
-    int32_t in_zp;
-    const float* bias_f;
-    int bias_n;
-    const int32_t* multiplier;
-    const int8_t* shift;
-    int per_channel, double_round;
+    const int32_t* row_corr;       // [rows] int32 added to every column of a row (MATMUL b_zp term) or null
+    const int32_t* corr;           // [classes][corr_stride] per-column additive constants or null
+    int corr_stride;               // padded column count (multiple of the tile width)
+    int corr_ystride;              // MATMUL: elements to advance per batch; 0 otherwise
+    int corr_classes;              // 1: rows select a table row by their rectangle of in-scope filter taps
+    const float* bias_f_pad;       // TC_EPI_FLOAT: padded fp32 bias or null
+    const int32_t* mult_pad;       // TC_EPI_RESCALE: padded per-column multipliers and shifts
+    const int8_t* shift_pad;
+    int double_round;
     int32_t out_zp, clamp_lo, clamp_hi;
     float clamp_lo_f, clamp_hi_f;
     int has_clamp;
+    int debug;    // diagnostic bit mask (TB200_TC_DEBUG): 1 skip epilogue memory work, 2 skip MMA issue, 4 skip loads
     int* status;
 };
 
@@ -155,6 +154,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x)
             {
                 const TileCoord t = decode_tile(p, tile);
+                const int ax0 = t.x0 * p.stride_x - p.pad_l;
+                const int ay0 = t.y0 * p.stride_y - p.pad_t;
+                int chunk = 0, cc = 0, ky = 0, kx = 0;    // running chunk index and its (tap, channel block)
                 for (int ks = 0; ks < p.num_kstages; ks++)
                 {
                     if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, kWaitLimitCycles))
@@ -162,31 +164,44 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
                         ok = false;
                         break;
                     }
-                    const int first   = ks * p.ksub;
-                    const int nchunks = min(p.ksub, p.total_chunks - first);
+                    const int nchunks   = min(p.ksub, p.total_chunks - chunk);
                     const uint32_t full = ptx::smem_u32(&bar_full[stage]);
-                    ptx::mbar_arrive_expect_tx(full, (uint32_t)(nchunks * p.tx_bytes_per_chunk));
-                    const uint32_t sA = smem_base + stage * p.stage_bytes;
-                    const uint32_t sB = sA + p.ksub * p.a_chunk_bytes;
-                    for (int j = 0; j < nchunks; j++)
+                    uint32_t sA         = smem_base + stage * p.stage_bytes;
+                    uint32_t sB         = sA + p.ksub * p.a_chunk_bytes;
+                    if (p.debug & 4)
                     {
-                        const int chunk = first + j;
-                        const int tap   = chunk / p.chunks_per_tap;
-                        const int cc    = chunk - tap * p.chunks_per_tap;
-                        const int ky    = tap / p.KW;
-                        const int kx    = tap - ky * p.KW;
-                        ptx::tma_load_4d(sA + j * p.a_chunk_bytes, &p.tmA, full, cc * p.chunk_elems,
-                                         t.x0 * p.stride_x + kx * p.dil_x - p.pad_l,
-                                         t.y0 * p.stride_y + ky * p.dil_y - p.pad_t, t.n0);
-                        if (!p.b_mn_major)
+                        ptx::mbar_arrive(full);
+                        chunk += nchunks;
+                    }
+                    else
+                    {
+                        ptx::mbar_arrive_expect_tx(full, (uint32_t)(nchunks * p.tx_bytes_per_chunk));
+                        for (int j = 0; j < nchunks; j++)
                         {
-                            ptx::tma_load_3d(sB + j * p.b_chunk_bytes, &p.tmB, full, chunk * p.chunk_elems, t.col0, 0);
-                        }
-                        else
-                        {
-                            for (int bx = 0; bx < p.b_nbox; bx++)
-                                ptx::tma_load_3d(sB + j * p.b_chunk_bytes + bx * p.b_box_bytes, &p.tmB, full,
-                                                 t.col0 + bx * p.b_box_n, chunk * p.chunk_elems, t.y0);
+                            ptx::tma_load_4d(sA, &p.tmA, full, cc * p.chunk_elems, ax0 + kx * p.dil_x, ay0 + ky * p.dil_y,
+                                             t.n0);
+                            if (!p.b_mn_major)
+                            {
+                                ptx::tma_load_3d(sB, &p.tmB, full, chunk * p.chunk_elems, t.col0, 0);
+                            }
+                            else
+                            {
+                                for (int bx = 0; bx < p.b_nbox; bx++)
+                                    ptx::tma_load_3d(sB + bx * p.b_box_bytes, &p.tmB, full, t.col0 + bx * p.b_box_n,
+                                                     chunk * p.chunk_elems, t.y0);
+                            }
+                            sA += p.a_chunk_bytes;
+                            sB += p.b_chunk_bytes;
+                            chunk++;
+                            if (++cc == p.chunks_per_tap)
+                            {
+                                cc = 0;
+                                if (++kx == p.KW)
+                                {
+                                    kx = 0;
+                                    ky++;
+                                }
+                            }
                         }
                     }
                     if (++stage == p.num_stages)
@@ -230,22 +245,26 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    const int first   = ks * p.ksub;
-                    const int nchunks = min(p.ksub, p.total_chunks - first);
+                    const int nchunks = min(p.ksub, p.total_chunks - ks * p.ksub);
                     const uint32_t sA = smem_base + stage * p.stage_bytes;
                     const uint32_t sB = sA + p.ksub * p.a_chunk_bytes;
-                    for (int j = 0; j < nchunks; j++)
+                    if (!(p.debug & 2))
                     {
-                        for (int m = 0; m < p.mmas_per_chunk; m++)
+                        for (int j = 0; j < nchunks; j++)
                         {
-                            const uint64_t ad = ptx::smem_desc(p.a_desc_hi, sA + j * p.a_chunk_bytes + m * 32);
-                            const uint64_t bd =
-                                ptx::smem_desc(p.b_desc_hi, sB + j * p.b_chunk_bytes + m * p.b_kstep_bytes);
-                            const uint32_t accum = (ks | j | m) != 0 ? 1u : 0u;
-                            if (p.is_f16_kind)
-                                ptx::mma_f16_ss(d_tmem, ad, bd, p.idesc, accum);
-                            else
-                                ptx::mma_i8_ss(d_tmem, ad, bd, p.idesc, accum);
+                            // descriptors differ only in the 14-bit start-address field (16-byte units)
+                            uint64_t ad = ptx::smem_desc(p.a_desc_hi, sA + j * p.a_chunk_bytes);
+                            uint64_t bd = ptx::smem_desc(p.b_desc_hi, sB + j * p.b_chunk_bytes);
+                            for (int m = 0; m < p.mmas_per_chunk; m++)
+                            {
+                                const uint32_t accum = (ks | j | m) != 0 ? 1u : 0u;
+                                if (EPI == TC_EPI_FLOAT)
+                                    ptx::mma_f16_ss(d_tmem, ad, bd, p.idesc, accum);
+                                else
+                                    ptx::mma_i8_ss(d_tmem, ad, bd, p.idesc, accum);
+                                ad += 2;    // 32 bytes of K
+                                bd += (uint64_t)(p.b_kstep_bytes >> 4);
+                            }
                         }
                     }
                     ptx::mma_commit(ptx::smem_u32(&bar_empty[stage]));
@@ -295,34 +314,41 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
             const bool row_valid = (nn < p.BN) && (ox < p.OW) && (oy < p.OH) && (on < p.N);
             const int64_t pix    = ((int64_t)on * p.OH + oy) * p.OW + ox;
 
-            // border rows of a padded convolution with a non-zero input zero point need the sum of the weights
-            // of the taps that fall inside the image
-            bool border = false;
-            int ky_lo = 0, ky_hi = p.KH, kx_lo = 0, kx_hi = p.KW;
-            if (EPI != TC_EPI_FLOAT && p.wsum_prefix != nullptr && row_valid)
+            // Additive per-column constants of this row (bias and zero-point terms).  For a padded convolution with a
+            // non-zero input zero point the constant depends on which filter taps fall inside the image, so the table
+            // has one row per (ky_lo, ky_hi, kx_lo, kx_hi) rectangle of in-scope taps; interior pixels share one row.
+            const int32_t* corr_row = nullptr;
+            if (EPI != TC_EPI_FLOAT && p.corr != nullptr)
             {
-                const int iy0 = oy * p.stride_y - p.pad_t;
-                const int ix0 = ox * p.stride_x - p.pad_l;
-                if (iy0 < 0)
-                    ky_lo = (-iy0 + p.dil_y - 1) / p.dil_y;
-                if (ix0 < 0)
-                    kx_lo = (-ix0 + p.dil_x - 1) / p.dil_x;
-                if (iy0 + (p.KH - 1) * p.dil_y >= p.IH)
-                    ky_hi = (p.IH - 1 - iy0) / p.dil_y + 1;
-                if (ix0 + (p.KW - 1) * p.dil_x >= p.IW)
-                    kx_hi = (p.IW - 1 - ix0) / p.dil_x + 1;
-                ky_lo = min(ky_lo, p.KH);
-                kx_lo = min(kx_lo, p.KW);
-                ky_hi = max(ky_hi, ky_lo);
-                kx_hi = max(kx_hi, kx_lo);
-                border = (ky_lo != 0) || (kx_lo != 0) || (ky_hi != p.KH) || (kx_hi != p.KW);
+                int cls = 0;
+                if (p.corr_classes)
+                {
+                    int ky_lo = 0, ky_hi = p.KH, kx_lo = 0, kx_hi = p.KW;
+                    if (row_valid)
+                    {
+                        const int iy0 = oy * p.stride_y - p.pad_t;
+                        const int ix0 = ox * p.stride_x - p.pad_l;
+                        if (iy0 < 0)
+                            ky_lo = (-iy0 + p.dil_y - 1) / p.dil_y;
+                        if (ix0 < 0)
+                            kx_lo = (-ix0 + p.dil_x - 1) / p.dil_x;
+                        if (iy0 + (p.KH - 1) * p.dil_y >= p.IH)
+                            ky_hi = (p.IH - 1 - iy0) / p.dil_y + 1;
+                        if (ix0 + (p.KW - 1) * p.dil_x >= p.IW)
+                            kx_hi = (p.IW - 1 - ix0) / p.dil_x + 1;
+                        ky_lo = min(ky_lo, p.KH);
+                        kx_lo = min(kx_lo, p.KW);
+                        ky_hi = max(ky_hi, ky_lo);
+                        kx_hi = max(kx_hi, kx_lo);
+                    }
+                    cls = ((ky_lo * (p.KH + 1) + ky_hi) * (p.KW + 1) + kx_lo) * (p.KW + 1) + kx_hi;
+                }
+                corr_row = p.corr + (int64_t)cls * p.corr_stride +
+                           (int64_t)((p.corr_ystride && row_valid) ? oy : 0) * p.corr_ystride;
             }
-
             int32_t rc = 0;
             if (EPI == TC_EPI_I32 && p.row_corr != nullptr && row_valid)
                 rc = p.row_corr[pix];
-            const int32_t* cc_base =
-                p.col_corr ? p.col_corr + (int64_t)(p.col_corr_ystride ? oy : 0) * p.col_corr_ystride : nullptr;
 
             const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n);
             const int ncol_chunks = p.block_n / 32;
@@ -332,113 +358,123 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
                 ptx::tmem_ld_32x32b_x32(taddr_row + (uint32_t)(c * 32), v);
                 ptx::tmem_ld_wait();
                 const int col = t.col0 + c * 32;
-                if (!row_valid || col >= p.OC)
+                if (col >= p.OC || (p.debug & 1))
                     continue;
                 const int nvalid = min(32, p.OC - col);
 
+                if (EPI != TC_EPI_FLOAT && corr_row != nullptr)
+                {
+                    // every per-column array is padded to a multiple of the tile width: unconditional 128-bit loads
+                    const int4* cp = reinterpret_cast<const int4*>(corr_row + col);
+#pragma unroll
+                    for (int q = 0; q < 8; q++)
+                    {
+                        const int4 cv = __ldg(cp + q);
+                        v[4 * q + 0] += (uint32_t)cv.x;
+                        v[4 * q + 1] += (uint32_t)cv.y;
+                        v[4 * q + 2] += (uint32_t)cv.z;
+                        v[4 * q + 3] += (uint32_t)cv.w;
+                    }
+                }
+
                 if (EPI == TC_EPI_I32)
                 {
-                    int32_t* o = reinterpret_cast<int32_t*>(p.out) + pix * p.OC + col;
 #pragma unroll
                     for (int i = 0; i < 32; i++)
+                        v[i] += (uint32_t)rc;
+                    if (row_valid)
                     {
-                        int32_t a = (int32_t)v[i] + rc;
-                        if (i < nvalid)
+                        int32_t* o = reinterpret_cast<int32_t*>(p.out) + pix * p.OC + col;
+                        if (nvalid == 32 && ((p.OC & 3) == 0))
                         {
-                            if (border)
-                            {
-                                const int32_t* P = p.wsum_prefix;
-                                const int W1 = p.KW + 1;
-                                int32_t rs = P[(ky_hi * W1 + kx_hi) * p.OC + col + i] -
-                                             P[(ky_lo * W1 + kx_hi) * p.OC + col + i] -
-                                             P[(ky_hi * W1 + kx_lo) * p.OC + col + i] +
-                                             P[(ky_lo * W1 + kx_lo) * p.OC + col + i];
-                                a += p.bias_i32[col + i] - p.in_zp * rs;
-                            }
-                            else if (cc_base)
-                                a += cc_base[col + i];
-                        }
-                        v[i] = (uint32_t)a;
-                    }
-                    if (nvalid == 32 && ((p.OC & 3) == 0))
-                    {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4)
-                            *reinterpret_cast<int4*>(o + i) = make_int4((int)v[i], (int)v[i + 1], (int)v[i + 2], (int)v[i + 3]);
-                    }
-                    else
-                    {
-                        _Pragma("unroll") for (int i = 0; i < 32; i++)
-                            if (i < nvalid)
-                                o[i] = (int32_t)v[i];
+                            for (int i = 0; i < 32; i += 4)
+                                *reinterpret_cast<int4*>(o + i) =
+                                    make_int4((int)v[i], (int)v[i + 1], (int)v[i + 2], (int)v[i + 3]);
+                        }
+                        else
+                        {
+#pragma unroll
+                            for (int i = 0; i < 32; i++)
+                                if (i < nvalid)
+                                    o[i] = (int32_t)v[i];
+                        }
                     }
                 }
                 else if (EPI == TC_EPI_RESCALE)
                 {
+                    int32_t mv[32];
+                    uint32_t sw[8];
+                    {
+                        const int4* mp = reinterpret_cast<const int4*>(p.mult_pad + col);
+#pragma unroll
+                        for (int q = 0; q < 8; q++)
+                        {
+                            const int4 m4 = __ldg(mp + q);
+                            mv[4 * q + 0] = m4.x;
+                            mv[4 * q + 1] = m4.y;
+                            mv[4 * q + 2] = m4.z;
+                            mv[4 * q + 3] = m4.w;
+                        }
+                        const int4* sp = reinterpret_cast<const int4*>(p.shift_pad + col);
+                        const int4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
+                        sw[0] = (uint32_t)s0.x; sw[1] = (uint32_t)s0.y; sw[2] = (uint32_t)s0.z; sw[3] = (uint32_t)s0.w;
+                        sw[4] = (uint32_t)s1.x; sw[5] = (uint32_t)s1.y; sw[6] = (uint32_t)s1.z; sw[7] = (uint32_t)s1.w;
+                    }
+                    bool bad = false;
 #pragma unroll
                     for (int i = 0; i < 32; i++)
                     {
-                        int32_t r = 0;
-                        if (i < nvalid)
-                        {
-                            int32_t a = (int32_t)v[i];
-                            if (border)
-                            {
-                                const int32_t* P = p.wsum_prefix;
-                                const int W1 = p.KW + 1;
-                                int32_t rs = P[(ky_hi * W1 + kx_hi) * p.OC + col + i] -
-                                             P[(ky_lo * W1 + kx_hi) * p.OC + col + i] -
-                                             P[(ky_hi * W1 + kx_lo) * p.OC + col + i] +
-                                             P[(ky_lo * W1 + kx_lo) * p.OC + col + i];
-                                a += p.bias_i32[col + i] - p.in_zp * rs;
-                            }
-                            else if (cc_base)
-                                a += cc_base[col + i];
-                            const int ch = p.per_channel ? (col + i) : 0;
-                            bool bad = false;
-                            int32_t s = apply_scale_32_dev(a, p.multiplier[ch], (int32_t)p.shift[ch], p.double_round != 0, bad);
-                            int64_t z = (int64_t)s + (int64_t)p.out_zp;
-                            bad |= (z > 2147483647LL) || (z < -2147483648LL);
-                            z = z < (int64_t)p.clamp_lo ? (int64_t)p.clamp_lo : z;
-                            z = z > (int64_t)p.clamp_hi ? (int64_t)p.clamp_hi : z;
-                            r = bad ? 0 : (int32_t)z;
-                            if (bad)
-                                dev_flags |= TB200_DEV_UNPREDICTABLE;
-                        }
-                        v[i] = (uint32_t)r;
+                        const int32_t sh = (int32_t)(int8_t)((sw[i >> 2] >> ((i & 3) * 8)) & 0xffu);
+                        bool b = false;
+                        const int32_t sc = apply_scale_32_dev((int32_t)v[i], mv[i], sh, p.double_round != 0, b);
+                        int64_t z = (int64_t)sc + (int64_t)p.out_zp;
+                        b |= (z > 2147483647LL) || (z < -2147483648LL);
+                        z = z < (int64_t)p.clamp_lo ? (int64_t)p.clamp_lo : z;
+                        z = z > (int64_t)p.clamp_hi ? (int64_t)p.clamp_hi : z;
+                        v[i] = b ? 0u : (uint32_t)(int32_t)z;
+                        bad |= b && (i < nvalid);
                     }
-                    if (p.out_es == 1)
+                    if (bad && row_valid)
+                        dev_flags |= TB200_DEV_UNPREDICTABLE;
+                    if (row_valid)
                     {
-                        int8_t* o = reinterpret_cast<int8_t*>(p.out) + pix * p.OC + col;
-                        if (nvalid == 32 && ((p.OC & 15) == 0))
+                        if (p.out_es == 1)
                         {
-                            uint4 w0 = make_uint4(pack4_i8(v[0], v[1], v[2], v[3]), pack4_i8(v[4], v[5], v[6], v[7]),
-                                                  pack4_i8(v[8], v[9], v[10], v[11]), pack4_i8(v[12], v[13], v[14], v[15]));
-                            uint4 w1 = make_uint4(pack4_i8(v[16], v[17], v[18], v[19]), pack4_i8(v[20], v[21], v[22], v[23]),
-                                                  pack4_i8(v[24], v[25], v[26], v[27]), pack4_i8(v[28], v[29], v[30], v[31]));
-                            *reinterpret_cast<uint4*>(o)      = w0;
-                            *reinterpret_cast<uint4*>(o + 16) = w1;
+                            int8_t* o = reinterpret_cast<int8_t*>(p.out) + pix * p.OC + col;
+                            if (nvalid == 32 && ((p.OC & 15) == 0))
+                            {
+                                uint4 w0 = make_uint4(pack4_i8(v[0], v[1], v[2], v[3]), pack4_i8(v[4], v[5], v[6], v[7]),
+                                                      pack4_i8(v[8], v[9], v[10], v[11]), pack4_i8(v[12], v[13], v[14], v[15]));
+                                uint4 w1 = make_uint4(pack4_i8(v[16], v[17], v[18], v[19]), pack4_i8(v[20], v[21], v[22], v[23]),
+                                                      pack4_i8(v[24], v[25], v[26], v[27]), pack4_i8(v[28], v[29], v[30], v[31]));
+                                *reinterpret_cast<uint4*>(o)      = w0;
+                                *reinterpret_cast<uint4*>(o + 16) = w1;
+                            }
+                            else
+                            {
+#pragma unroll
+                                for (int i = 0; i < 32; i++)
+                                    if (i < nvalid)
+                                        o[i] = (int8_t)(int32_t)v[i];
+                            }
+                        }
+                        else if (p.out_es == 2)
+                        {
+                            int16_t* o = reinterpret_cast<int16_t*>(p.out) + pix * p.OC + col;
+#pragma unroll
+                            for (int i = 0; i < 32; i++)
+                                if (i < nvalid)
+                                    o[i] = (int16_t)(int32_t)v[i];
                         }
                         else
                         {
-                            _Pragma("unroll") for (int i = 0; i < 32; i++)
+                            int32_t* o = reinterpret_cast<int32_t*>(p.out) + pix * p.OC + col;
+#pragma unroll
+                            for (int i = 0; i < 32; i++)
                                 if (i < nvalid)
-                                    o[i] = (int8_t)(int32_t)v[i];
+                                    o[i] = (int32_t)v[i];
                         }
-                    }
-                    else if (p.out_es == 2)
-                    {
-                        int16_t* o = reinterpret_cast<int16_t*>(p.out) + pix * p.OC + col;
-                        _Pragma("unroll") for (int i = 0; i < 32; i++)
-                            if (i < nvalid)
-                                o[i] = (int16_t)(int32_t)v[i];
-                    }
-                    else
-                    {
-                        int32_t* o = reinterpret_cast<int32_t*>(p.out) + pix * p.OC + col;
-                        _Pragma("unroll") for (int i = 0; i < 32; i++)
-                            if (i < nvalid)
-                                o[i] = (int32_t)v[i];
                     }
                 }
                 else
@@ -446,18 +482,32 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
                     float f[32];
 #pragma unroll
                     for (int i = 0; i < 32; i++)
+                        f[i] = __uint_as_float(v[i]);
+                    if (p.bias_f_pad != nullptr)
                     {
-                        float a = __uint_as_float(v[i]);
-                        if (p.bias_f != nullptr && i < nvalid)
-                            a += p.bias_f[p.bias_n == 1 ? 0 : (col + i)];
-                        if (p.has_clamp)
+                        const float4* bp = reinterpret_cast<const float4*>(p.bias_f_pad + col);
+#pragma unroll
+                        for (int q = 0; q < 8; q++)
+                        {
+                            const float4 b4 = __ldg(bp + q);
+                            f[4 * q + 0] += b4.x;
+                            f[4 * q + 1] += b4.y;
+                            f[4 * q + 2] += b4.z;
+                            f[4 * q + 3] += b4.w;
+                        }
+                    }
+                    if (p.has_clamp)
+                    {
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
                         {
                             // NaN propagates: comparisons with NaN are false on both sides
-                            a = (a < p.clamp_lo_f) ? p.clamp_lo_f : a;
-                            a = (a > p.clamp_hi_f) ? p.clamp_hi_f : a;
+                            f[i] = (f[i] < p.clamp_lo_f) ? p.clamp_lo_f : f[i];
+                            f[i] = (f[i] > p.clamp_hi_f) ? p.clamp_hi_f : f[i];
                         }
-                        f[i] = a;
                     }
+                    if (!row_valid)
+                        continue;
                     if (p.out_es == 4)
                     {
                         float* o = reinterpret_cast<float*>(p.out) + pix * p.OC + col;
@@ -469,7 +519,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
                         }
                         else
                         {
-                            _Pragma("unroll") for (int i = 0; i < 32; i++)
+#pragma unroll
+                            for (int i = 0; i < 32; i++)
                                 if (i < nvalid)
                                     o[i] = f[i];
                         }
@@ -500,7 +551,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
                         }
                         else
                         {
-                            _Pragma("unroll") for (int i = 0; i < 32; i++)
+#pragma unroll
+                            for (int i = 0; i < 32; i++)
                                 if (i < nvalid)
                                     o[i] = h[i];
                         }
@@ -820,19 +872,14 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
     k.out              = q.out;
     k.out_es           = (int)dtype_size(q.out_dtype);
     k.out_is_bf16      = q.out_dtype == TB200_BF16;
-    k.row_corr         = q.row_corr;
-    k.col_corr         = q.col_corr;
-    k.col_corr_ystride = q.col_corr_ystride;
-    k.bias_i32         = nullptr;
-    k.wsum_prefix      = q.wsum_prefix;
-    k.in_zp            = q.in_zp;
-    if (q.wsum_prefix)
-        k.bias_i32 = q.wsum_prefix + (size_t)(q.KH + 1) * (q.KW + 1) * q.OC;    // table is followed by the full bias
-    k.bias_f       = q.bias_f;
-    k.bias_n       = q.bias_n;
-    k.multiplier   = q.multiplier;
-    k.shift        = q.shift;
-    k.per_channel  = q.per_channel;
+    k.row_corr     = q.row_corr;
+    k.corr         = q.corr;
+    k.corr_stride  = q.corr_stride;
+    k.corr_ystride = q.corr_ystride;
+    k.corr_classes = q.corr_classes;
+    k.bias_f_pad   = q.bias_f_pad;
+    k.mult_pad     = q.mult_pad;
+    k.shift_pad    = q.shift_pad;
     k.double_round = q.double_round;
     k.out_zp       = q.out_zp;
     k.clamp_lo     = q.clamp_lo;
@@ -841,6 +888,7 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
     k.clamp_hi_f   = q.clamp_hi_f;
     k.has_clamp    = q.has_clamp;
     k.status       = ctx->d_status;
+    k.debug        = env_int("TB200_TC_DEBUG", 0);
 
     void (*kern)(const TcKernelParams) = nullptr;
     const char* name                   = "";
