@@ -325,6 +325,21 @@ extern "C" tb200_status tb200_ctx_destroy(tb200_ctx* ctx)
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch)
         cudaFree(ctx->scratch);
+    if (ctx->pipe.ready)
+    {
+        cudaStreamSynchronize(ctx->pipe.h2d);
+        cudaStreamSynchronize(ctx->pipe.d2h);
+        for (int i = 0; i < 2; i++)
+        {
+            if (ctx->pipe.buf[i])
+                cudaFree(ctx->pipe.buf[i]);
+            cudaEventDestroy(ctx->pipe.up[i]);
+            cudaEventDestroy(ctx->pipe.done[i]);
+            cudaEventDestroy(ctx->pipe.down[i]);
+        }
+        cudaStreamDestroy(ctx->pipe.h2d);
+        cudaStreamDestroy(ctx->pipe.d2h);
+    }
     if (ctx->d_status)
         cudaFree(ctx->d_status);
     if (ctx->h_status)
@@ -1240,6 +1255,43 @@ extern "C" tb200_status tb200_avg_pool2d(tb200_ctx* ctx, const tb200_tensor* inp
 }
 
 // =================================================================================================== host buffers
+static tb200_status pipe_prepare(tb200_ctx* ctx, size_t bytes_per_slot)
+{
+    auto& p = ctx->pipe;
+    if (!p.ready)
+    {
+        TB200_CUDA_CHECK(ctx, cudaStreamCreateWithFlags(&p.h2d, cudaStreamNonBlocking));
+        TB200_CUDA_CHECK(ctx, cudaStreamCreateWithFlags(&p.d2h, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; i++)
+        {
+            TB200_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&p.up[i], cudaEventDisableTiming));
+            TB200_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&p.done[i], cudaEventDisableTiming));
+            TB200_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&p.down[i], cudaEventDisableTiming));
+        }
+        p.ready = true;
+    }
+    if (bytes_per_slot > p.cap)
+    {
+        TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+        TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(p.h2d));
+        TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(p.d2h));
+        for (int i = 0; i < 2; i++)
+        {
+            if (p.buf[i])
+                cudaFree(p.buf[i]);
+            p.buf[i] = nullptr;
+        }
+        p.cap = 0;
+        for (int i = 0; i < 2; i++)
+            TB200_CUDA_CHECK(ctx, cudaMalloc(&p.buf[i], bytes_per_slot));
+        p.cap = bytes_per_slot;
+    }
+    return TB200_OK;
+}
+
+// MATMUL on host buffers.  The batch is cut into chunks that flow through two device staging slots: while chunk i
+// is multiplied, chunk i+1 is uploaded and chunk i-1 downloaded on separate copy streams, so that the PCIe link
+// carries both directions at once.  Pinned host buffers make the copies asynchronous; pageable ones still work.
 extern "C" tb200_status tb200_matmul_host(tb200_ctx* ctx, tb200_dtype in_dtype, tb200_dtype out_dtype, const void* a,
                                           const void* b, int32_t N, int32_t H, int32_t C, int32_t W, int32_t a_zp,
                                           int32_t b_zp, void* out)
@@ -1247,23 +1299,59 @@ extern "C" tb200_status tb200_matmul_host(tb200_ctx* ctx, tb200_dtype in_dtype, 
     if (!ctx)
         return TB200_ERROR;
     TB200_ERROR_IF(ctx, !a || !b || !out, "matmul_host: null buffer");
-    tb200_tensor *ta = nullptr, *tb = nullptr, *to = nullptr;
-    const int32_t sa[3] = { N, H, C }, sb[3] = { N, C, W }, so[3] = { N, H, W };
-    tb200_status st = tb200_tensor_alloc(ctx, in_dtype, 3, sa, &ta);
-    if (st == TB200_OK)
-        st = tb200_tensor_alloc(ctx, in_dtype, 3, sb, &tb);
-    if (st == TB200_OK)
-        st = tb200_tensor_alloc(ctx, out_dtype, 3, so, &to);
-    if (st == TB200_OK)
-        st = tb200_tensor_upload(ctx, ta, a, ta->bytes);
-    if (st == TB200_OK)
-        st = tb200_tensor_upload(ctx, tb, b, tb->bytes);
-    if (st == TB200_OK)
-        st = tb200_matmul(ctx, ta, tb, a_zp, b_zp, nullptr, to);
-    if (st == TB200_OK)
-        st = tb200_tensor_download(ctx, to, out, to->bytes);
-    tb200_tensor_free(ctx, ta);
-    tb200_tensor_free(ctx, tb);
-    tb200_tensor_free(ctx, to);
-    return st;
+    TB200_ERROR_IF(ctx, N < 0 || H < 0 || C < 0 || W < 0, "matmul_host: negative dimension");
+    const size_t es_in = dtype_size(in_dtype), es_out = dtype_size(out_dtype);
+    TB200_ERROR_IF(ctx, es_in == 0 || es_out == 0, "matmul_host: unsupported dtype");
+    if (N == 0 || H == 0 || W == 0)
+        return TB200_OK;
+    const size_t a_b = (size_t)H * C * es_in, b_b = (size_t)C * W * es_in, o_b = (size_t)H * W * es_out;
+    auto up256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    // about 32 MB of A per chunk
+    int nb = (int)std::max<size_t>(1, std::min<size_t>((size_t)N, ((size_t)32 << 20) / std::max<size_t>(a_b, 1)));
+    const size_t off_b = up256((size_t)nb * a_b), off_o = off_b + up256((size_t)nb * b_b);
+    const size_t slot_bytes = off_o + up256((size_t)nb * o_b);
+    tb200_status st = pipe_prepare(ctx, slot_bytes);
+    if (st != TB200_OK)
+        return st;
+    auto& p = ctx->pipe;
+    // order the copy streams after whatever the caller queued on the compute stream, and clear stale events
+    TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    int chunk_idx = 0;
+    for (int n0 = 0; n0 < N; n0 += nb, chunk_idx++)
+    {
+        const int cnt  = std::min(nb, N - n0);
+        const int slot = chunk_idx & 1;
+        uint8_t* base  = reinterpret_cast<uint8_t*>(p.buf[slot]);
+        if (chunk_idx >= 2)
+        {
+            // the slot's inputs are free once its previous product is done; its output once that was downloaded
+            TB200_CUDA_CHECK(ctx, cudaStreamWaitEvent(p.h2d, p.done[slot], 0));
+            TB200_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->stream, p.down[slot], 0));
+        }
+        TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(base, reinterpret_cast<const uint8_t*>(a) + (size_t)n0 * a_b,
+                                              (size_t)cnt * a_b, cudaMemcpyHostToDevice, p.h2d));
+        TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(base + off_b, reinterpret_cast<const uint8_t*>(b) + (size_t)n0 * b_b,
+                                              (size_t)cnt * b_b, cudaMemcpyHostToDevice, p.h2d));
+        TB200_CUDA_CHECK(ctx, cudaEventRecord(p.up[slot], p.h2d));
+        TB200_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->stream, p.up[slot], 0));
+        tb200_tensor ta{ in_dtype, 3, { cnt, H, C, 1, 1, 1 }, base, (size_t)cnt * a_b, false };
+        tb200_tensor tbm{ in_dtype, 3, { cnt, C, W, 1, 1, 1 }, base + off_b, (size_t)cnt * b_b, false };
+        tb200_tensor to{ out_dtype, 3, { cnt, H, W, 1, 1, 1 }, base + off_o, (size_t)cnt * o_b, false };
+        st = tb200_matmul(ctx, &ta, &tbm, a_zp, b_zp, nullptr, &to);
+        if (st != TB200_OK)
+            break;
+        TB200_CUDA_CHECK(ctx, cudaEventRecord(p.done[slot], ctx->stream));
+        TB200_CUDA_CHECK(ctx, cudaStreamWaitEvent(p.d2h, p.done[slot], 0));
+        TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(reinterpret_cast<uint8_t*>(out) + (size_t)n0 * o_b, base + off_o,
+                                              (size_t)cnt * o_b, cudaMemcpyDeviceToHost, p.d2h));
+        TB200_CUDA_CHECK(ctx, cudaEventRecord(p.down[slot], p.d2h));
+    }
+    cudaError_t e1 = cudaStreamSynchronize(p.h2d);
+    cudaError_t e2 = cudaStreamSynchronize(p.d2h);
+    tb200_status sync_st = tb200_sync(ctx);
+    if (st != TB200_OK)
+        return st;
+    if (e1 != cudaSuccess || e2 != cudaSuccess)
+        return fail(ctx, TB200_INTERNAL, "matmul_host: copy stream failed: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    return sync_st;
 }

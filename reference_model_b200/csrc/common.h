@@ -42,6 +42,15 @@ struct tb200_ctx
     int num_sms          = 148;
     const char* last_kernel = "none";
     std::string err;
+    // host-buffer pipeline of tb200_matmul_host: copy streams, events and two sets of device staging buffers
+    struct HostPipe
+    {
+        cudaStream_t h2d = nullptr, d2h = nullptr;
+        cudaEvent_t up[2] = {}, done[2] = {}, down[2] = {};
+        void* buf[2]      = {};
+        size_t cap        = 0;
+        bool ready        = false;
+    } pipe;
     // optional CUDA-event brackets around the main kernels (tb200_timer_enable)
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;

@@ -1,0 +1,170 @@
+"""Device timings of the benchmark configurations other than the one bench.py reports.
+
+    python -m reference_model_b200.measure [--configs c1,c2b,c3a,c3b,c4] [--iters 20]
+
+Prints one JSON line per configuration: device time per call (CUDA events on the context's stream, after warm-up,
+operands resident in HBM), derived throughput, and the roofline figure that bounds it.  Synthetic seeded operands of
+the shapes named by the configurations; between timed calls an L2-sized buffer is overwritten when the working set
+is smaller than L2.
+"""
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import reference_model_b200 as tb  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p["hbm_gbs"], p["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class Timer:
+    def __init__(self, ctx, stream, torch):
+        self.ctx, self.stream, self.torch = ctx, stream, torch
+        self.flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device="cuda")
+
+    def time(self, fn, iters, working_set_bytes):
+        torch = self.torch
+        for _ in range(3):
+            fn()
+        self.ctx.sync()
+        need_flush = working_set_bytes < 2 * L2_BYTES
+        total = 0.0
+        for _ in range(iters):
+            if need_flush:
+                self.flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(self.stream)
+            fn()
+            e1.record(self.stream)
+            e1.synchronize()
+            total += e0.elapsed_time(e1)
+        st = self.ctx.sync()
+        assert st == tb.Status.OK, self.ctx.last_error()
+        return total / iters, ("L2 flushed between calls" if need_flush else "working set larger than L2")
+
+
+def rescale_consts(ctx, r, channels):
+    mult = r.integers(1 << 30, (1 << 31) - 1, size=channels, endpoint=True, dtype=np.int64).astype(np.int32)
+    shift = r.integers(32, 40, size=channels, endpoint=True, dtype=np.int64).astype(np.int8)
+    return ctx.from_numpy(mult), ctx.from_numpy(shift)
+
+
+def conv_i8_config(ctx, timer, name, N, IH, IW, IC, OC, KH, KW, stride, pad, izp, iters, seed):
+    r = np.random.default_rng(seed)
+    x = r.integers(-128, 128, size=(N, IH, IW, IC), dtype=np.int8)
+    w = r.integers(-127, 128, size=(OC, KH, KW, IC), dtype=np.int8)
+    b = r.integers(-65536, 65536, size=OC).astype(np.int32)
+    OH = (IH - 1 + pad[0] + pad[1] - (KH - 1)) // stride + 1
+    OW = (IW - 1 + pad[2] + pad[3] - (KW - 1)) // stride + 1
+    tx, tw, tbias = ctx.from_numpy(x), ctx.from_numpy(w), ctx.from_numpy(b)
+    tm, ts = rescale_consts(ctx, r, OC)
+    to = ctx.empty(tb.DType.INT8, (N, OH, OW, OC))
+    epi = tb.Epilogue(tb.RescaleAttr(tm, ts, 0, -128, True, "DOUBLE_ROUND", per_channel=True), (-128, 127))
+    fn = lambda: ctx.conv2d(tx, tw, tbias, to, pad, [stride, stride], [1, 1], izp, 0, epi)
+    nbytes = x.nbytes + w.nbytes + N * OH * OW * OC
+    ms, note = timer.time(fn, iters, nbytes)
+    ops = 2.0 * N * OH * OW * OC * KH * KW * IC
+    return {"config": name, "kernel": ctx.last_kernel(), "ms": ms, "TOPS": ops / ms / 1e9, "GBps": nbytes / ms / 1e6,
+            "algorithmic_ops": ops, "algorithmic_bytes": nbytes, "l2": note}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--configs", default="c1,c2b,c3a,c3b,c4")
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    import torch
+
+    hbm, bf16, src = _peaks()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ctx = tb.Context(0, stream.cuda_stream)
+        timer = Timer(ctx, stream, torch)
+        for name in args.configs.split(","):
+            if name == "c1":
+                res = conv_i8_config(ctx, timer, "c1 conv1x1 1x32x32x8->16 +RESCALE", 1, 32, 32, 8, 16, 1, 1, 1,
+                                     [0, 0, 0, 0], 5, args.iters, 1)
+                res["bound"] = "latency"
+            elif name == "c3a":
+                res = conv_i8_config(ctx, timer, "c3a conv3x3 32x56x56x64->64 +RESCALE+CLAMP", 32, 56, 56, 64, 64, 3, 3, 1,
+                                     [1, 1, 1, 1], -128, args.iters, 3)
+                res.update(bound="tensor", peak_TOPS=2 * bf16, frac=res["TOPS"] / (2 * bf16),
+                           peak_source="2 x %s bf16 burst" % src)
+            elif name == "c3b":
+                res = conv_i8_config(ctx, timer, "c3b conv7x7s2 32x224x224x3->64 +RESCALE+CLAMP", 32, 224, 224, 3, 64, 7, 7,
+                                     2, [3, 2, 3, 2], -128, max(3, args.iters // 4), 4)
+                res.update(bound="hbm", peak_GBps=hbm, frac=res["GBps"] / hbm, peak_source=src)
+            elif name == "c2b":
+                N, H, C, W = 64, 1024, 4096, 1024
+                a = torch.randn((N, H, C), dtype=torch.float32, device="cuda")
+                b = torch.randn((N, C, W), dtype=torch.float32, device="cuda")
+                o = torch.empty((N, H, W), dtype=torch.float32, device="cuda")
+                ta = ctx.wrap(tb.DType.FP32, (N, H, C), a.data_ptr(), a)
+                tbm = ctx.wrap(tb.DType.FP32, (N, C, W), b.data_ptr(), b)
+                to = ctx.wrap(tb.DType.FP32, (N, H, W), o.data_ptr(), o)
+                ms, note = timer.time(lambda: ctx.matmul(ta, tbm, to), max(2, args.iters // 5), 4 * (a.numel() + b.numel()))
+                flops = 2.0 * N * H * C * W
+                clk = torch.cuda.get_device_properties(0).clock_rate / 1e6 if hasattr(torch.cuda.get_device_properties(0), "clock_rate") else 1.965
+                peak = 148 * 128 * 2 * 1.965e9 / 1e12
+                res = {"config": "c2b matmul fp32 64x1024x4096x1024 (FFMA, no TF32)", "kernel": ctx.last_kernel(), "ms": ms,
+                       "TFLOPS": flops / ms / 1e9, "bound": "fp32 CUDA cores", "peak_TFLOPS": peak,
+                       "frac": flops / ms / 1e9 / peak, "peak_source": "148 SMs x 128 lanes x 2 x 1.965 GHz (nominal max clock)",
+                       "l2": note}
+            elif name == "c4":
+                res = c4_block(ctx, timer, torch, args.iters, hbm, src)
+            else:
+                continue
+            print(json.dumps(res))
+            sys.stdout.flush()
+        ctx.close()
+
+
+def c4_block(ctx, timer, torch, iters, hbm, src):
+    """Inverted-residual block, fp16: 1x1 conv 32->192 + CLAMP[0,6], 3x3 depthwise s2 + CLAMP[0,6], 1x1 conv 192->64."""
+    out = {}
+    for dt_name, dt, tdt in (("fp16", tb.DType.FP16, torch.float16), ("bf16", tb.DType.BF16, torch.bfloat16)):
+        N = 64
+        g = torch.Generator(device="cuda").manual_seed(4)
+        x = torch.randn((N, 112, 112, 32), device="cuda", generator=g).to(tdt)
+        w1 = (torch.randn((192, 1, 1, 32), device="cuda", generator=g) / 32 ** 0.5).to(tdt)
+        wd = (torch.randn((3, 3, 192, 1), device="cuda", generator=g) / 3).to(tdt)
+        w2 = (torch.randn((64, 1, 1, 192), device="cuda", generator=g) / 192 ** 0.5).to(tdt)
+        b1, bd, b2 = (torch.zeros(n, device="cuda", dtype=tdt) for n in (192, 192, 64))
+        t1 = torch.empty((N, 112, 112, 192), device="cuda", dtype=tdt)
+        t2 = torch.empty((N, 56, 56, 192), device="cuda", dtype=tdt)
+        y = torch.empty((N, 56, 56, 64), device="cuda", dtype=tdt)
+        W = lambda t: ctx.wrap(dt, tuple(t.shape), t.data_ptr(), t)
+        X, W1, WD, W2, B1, BD, B2, T1, T2, Y = map(W, (x, w1, wd, w2, b1, bd, b2, t1, t2, y))
+        relu6 = tb.Epilogue(None, (0.0, 6.0))
+
+        def block():
+            ctx.conv2d(X, W1, B1, T1, [0, 0, 0, 0], [1, 1], [1, 1], 0, 0, relu6)
+            ctx.depthwise_conv2d(T1, WD, BD, T2, [1, 0, 1, 0], [2, 2], [1, 1], 0, 0, relu6)
+            ctx.conv2d(T2, W2, B2, Y, [0, 0, 0, 0], [1, 1], [1, 1], 0, 0, None)
+
+        unfused = 2 * (x.numel() + 2 * t1.numel() + 2 * t2.numel() + y.numel())
+        ms, note = timer.time(block, iters, unfused)
+        flops = 2.0 * N * (112 * 112 * 32 * 192 + 56 * 56 * 192 * 9 + 56 * 56 * 192 * 64)
+        out[dt_name] = {"ms": ms, "TFLOPS": flops / ms / 1e9, "GBps_unfused_traffic": unfused / ms / 1e6,
+                        "frac_of_hbm": unfused / ms / 1e6 / hbm}
+    return {"config": "c4 inverted residual block 64x112x112x32 (3 kernels, intermediates in HBM)", "bound": "hbm",
+            "peak_GBps": hbm, "peak_source": src, "algorithmic_bytes_unfused": unfused, **out}
+
+
+if __name__ == "__main__":
+    main()

@@ -362,6 +362,21 @@ def test_matmul_int8(ctx, N, H, C, W, azp, bzp):
     assert np.array_equal(out, exp)
 
 
+def test_matmul_host_pipelined_chunks(ctx):
+    """tb200_matmul_host cuts a large batch into chunks that overlap upload, product and download."""
+    N, H, C, W = 80, 256, 4096, 64        # 1 MB of A per batch -> 32 batches per chunk -> 3 chunks
+    r = util.rng(210)
+    a = r.integers(-128, 128, size=(N, H, C), dtype=np.int8)
+    b = r.integers(-128, 128, size=(N, C, W), dtype=np.int8)
+    out = np.empty((N, H, W), np.int32)
+    assert ctx.matmul_host(a, b, out, -5, 9) == tb.Status.OK
+    assert np.array_equal(out, orc.matmul(a, b, -5, 9, nthreads=8))
+    # a second call reuses the staging slots
+    out2 = np.empty((N, H, W), np.int32)
+    assert ctx.matmul_host(a[::-1].copy(), b[::-1].copy(), out2, -5, 9) == tb.Status.OK
+    assert np.array_equal(out2, out[::-1])
+
+
 def test_matmul_int8_full_size_sampled(ctx):
     """The benchmark's MATMUL (64 x [1024x4096] x [4096x1024], zero points 3 / -2) at full size: complete output
     rows sampled across batches against int64 numpy, plus linearity in A over the whole output."""
