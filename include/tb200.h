@@ -110,6 +110,16 @@ extern "C"
      * is pinned; download synchronises the stream and returns the status tb200_sync would. */
     TB200_API tb200_status tb200_tensor_upload(tb200_ctx* ctx, tb200_tensor* t, const void* host, size_t bytes);
     TB200_API tb200_status tb200_tensor_download(tb200_ctx* ctx, const tb200_tensor* t, void* host, size_t bytes);
+    /* SLICE as a zero-copy view: replaces OpSlice<Rank,T>::eval (reference_model/src/ops/data_layout.cpp:369-398)
+     * with the same start / size rules.  The view shares its parent's memory (free the view before the parent) and
+     * keeps its pitch; it is accepted as the input of tb200_conv2d (e.g. the 55x55 cut that makes a stride-2 1x1
+     * shortcut convolution legal under the exact-division rule); other operators need contiguous tensors. */
+    TB200_API tb200_status tb200_tensor_slice(tb200_ctx* ctx, const tb200_tensor* parent, const int32_t* start,
+                                              const int32_t* size, tb200_tensor** out);
+    /* RESHAPE as a zero-copy view of a contiguous tensor: replaces OpReshape::eval
+     * (reference_model/src/ops/data_layout.cpp:227-). */
+    TB200_API tb200_status tb200_tensor_reshape(tb200_ctx* ctx, const tb200_tensor* parent, int rank,
+                                                const int32_t* shape, tb200_tensor** out);
     TB200_API void* tb200_tensor_data(const tb200_tensor* t);
     TB200_API size_t tb200_tensor_bytes(const tb200_tensor* t);
 

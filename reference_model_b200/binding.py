@@ -68,7 +68,7 @@ EXPORTS = [
     "tb200_ctx_create", "tb200_ctx_destroy", "tb200_last_error", "tb200_sync", "tb200_launch_count",
     "tb200_timer_enable", "tb200_timer_read",
     "tb200_tensor_alloc", "tb200_tensor_wrap", "tb200_tensor_free", "tb200_tensor_upload", "tb200_tensor_download",
-    "tb200_tensor_data", "tb200_tensor_bytes", "tb200_conv2d", "tb200_depthwise_conv2d", "tb200_matmul",
+    "tb200_tensor_data", "tb200_tensor_bytes", "tb200_tensor_slice", "tb200_tensor_reshape", "tb200_conv2d", "tb200_depthwise_conv2d", "tb200_matmul",
     "tb200_rescale", "tb200_clamp", "tb200_add", "tb200_residual_add", "tb200_max_pool2d", "tb200_avg_pool2d",
     "tb200_matmul_host", "tb200_set_kernel_policy", "tb200_last_kernel", "tb200_matmul_i8_noalloc",
 ]
@@ -98,6 +98,8 @@ def load_library():
         "tb200_tensor_free": (i32, [vp, vp]),
         "tb200_tensor_upload": (i32, [vp, vp, vp, ctypes.c_size_t]),
         "tb200_tensor_download": (i32, [vp, vp, vp, ctypes.c_size_t]),
+        "tb200_tensor_slice": (i32, [vp, vp, p_i32, p_i32, ctypes.POINTER(vp)]),
+        "tb200_tensor_reshape": (i32, [vp, vp, ctypes.c_int, p_i32, ctypes.POINTER(vp)]),
         "tb200_tensor_data": (vp, [vp]),
         "tb200_tensor_bytes": (ctypes.c_size_t, [vp]),
         "tb200_conv2d": (i32, [vp, vp, vp, vp, i32, i32, p_i32, p_i32, p_i32, ctypes.POINTER(_Epilogue), vp]),
@@ -201,6 +203,20 @@ class Tensor:
         st = load_library().tb200_tensor_download(self.ctx.handle, self.handle, out.ctypes.data_as(ctypes.c_void_p),
                                                   out.nbytes)
         return self.ctx._check(st, check), out
+
+    def slice(self, start, size):
+        """SLICE as a zero-copy view (keeps this tensor alive)."""
+        h = ctypes.c_void_p()
+        self.ctx._check(load_library().tb200_tensor_slice(self.ctx.handle, self.handle, _ivec(start), _ivec(size),
+                                                          ctypes.byref(h)))
+        return Tensor(self.ctx, self.dtype, size, h, keepalive=self)
+
+    def reshape(self, shape):
+        """RESHAPE as a zero-copy view of a contiguous tensor."""
+        h = ctypes.c_void_p()
+        self.ctx._check(load_library().tb200_tensor_reshape(self.ctx.handle, self.handle, len(shape), _ivec(shape),
+                                                            ctypes.byref(h)))
+        return Tensor(self.ctx, self.dtype, shape, h, keepalive=self)
 
     def free(self):
         if self.handle is not None:

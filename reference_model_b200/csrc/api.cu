@@ -64,6 +64,14 @@ static int grid_for(tb200_ctx* ctx, int64_t work_items, int block)
     return (int)std::max<int64_t>(1, std::min(blocks, cap));
 }
 
+static bool all_contiguous(std::initializer_list<const tb200_tensor*> ts)
+{
+    for (const tb200_tensor* t : ts)
+        if (t && !t->contiguous)
+            return false;
+    return true;
+}
+
 static bool same_shape(const tb200_tensor* a, const tb200_tensor* b)
 {
     if (a->rank != b->rank)
@@ -90,6 +98,7 @@ static tb200_status make_rescale_dev(tb200_ctx* ctx, const tb200_rescale_attr* a
                                      int channels, RescaleDev* r)
 {
     TB200_ERROR_IF(ctx, !a || !a->multiplier || !a->shift, "OpRescale: missing multiplier / shift operand");
+    TB200_ERROR_IF(ctx, !a->multiplier->contiguous || !a->shift->contiguous, "OpRescale: multiplier / shift must be contiguous");
     TB200_ERROR_IF(ctx, !is_int_dtype(in_dt) || !is_int_dtype(out_dt), "OpRescale: integer tensors only");
     TB200_ERROR_IF(ctx, a->rounding_mode < TB200_SINGLE_ROUND || a->rounding_mode > TB200_INEXACT_ROUND,
                    "OpRescale: only SINGLE_ROUND, DOUBLE_ROUND and INEXACT_ROUND are supported");
@@ -445,6 +454,14 @@ static tb200_status make_tensor(tb200_ctx* ctx, tb200_dtype dtype, int rank, con
     t->bytes = (size_t)n * dtype_size(dtype);
     t->owns  = owns;
     t->data  = ptr;
+    int64_t st = 1;
+    for (int i = 5; i >= 0; i--)
+    {
+        t->stride[i] = st;
+        st *= t->shape[i];
+    }
+    // shape[] is padded with ones after `rank`, so the loop above yields row-major strides for the first `rank` dims
+    t->contiguous = true;
     if (owns)
     {
         cudaError_t e = cudaMalloc(&t->data, std::max<size_t>(t->bytes, 16));
@@ -495,6 +512,7 @@ extern "C" tb200_status tb200_tensor_upload(tb200_ctx* ctx, tb200_tensor* t, con
     if (!ctx)
         return TB200_ERROR;
     TB200_ERROR_IF(ctx, !t || !host, "null tensor or host buffer");
+    TB200_ERROR_IF(ctx, !t->contiguous, "upload needs a contiguous tensor");
     TB200_ERROR_IF(ctx, bytes != t->bytes, "upload of %zu bytes into a tensor of %zu bytes", bytes, t->bytes);
     if (bytes)
         TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(t->data, host, bytes, cudaMemcpyHostToDevice, ctx->stream));
@@ -506,6 +524,7 @@ extern "C" tb200_status tb200_tensor_download(tb200_ctx* ctx, const tb200_tensor
     if (!ctx)
         return TB200_ERROR;
     TB200_ERROR_IF(ctx, !t || !host, "null tensor or host buffer");
+    TB200_ERROR_IF(ctx, !t->contiguous, "download needs a contiguous tensor");
     TB200_ERROR_IF(ctx, bytes != t->bytes, "download of %zu bytes from a tensor of %zu bytes", bytes, t->bytes);
     if (bytes)
         TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(host, t->data, bytes, cudaMemcpyDeviceToHost, ctx->stream));
@@ -522,6 +541,62 @@ extern "C" size_t tb200_tensor_bytes(const tb200_tensor* t)
     return t ? t->bytes : 0;
 }
 
+// SLICE as a zero-copy view (OpSlice::eval, reference_model/src/ops/data_layout.cpp:369-398): same ERROR_IFs, the
+// view keeps the parent's pitch.  Views are accepted as the input of tb200_conv2d; other operators need contiguous
+// tensors and report TB200_ERROR for a view.
+extern "C" tb200_status tb200_tensor_slice(tb200_ctx* ctx, const tb200_tensor* parent, const int32_t* start,
+                                           const int32_t* size, tb200_tensor** out)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !parent || !start || !size || !out, "OpSlice: null operand");
+    *out = nullptr;
+    int64_t offset = 0, n = 1;
+    for (int i = 0; i < parent->rank; i++)
+    {
+        const int32_t b = start[i], sz = size[i];
+        TB200_ERROR_IF(ctx, b < 0 || b >= parent->shape[i], "OpSlice: start out of boundary");
+        TB200_ERROR_IF(ctx, (b + sz) < 0 || (b + sz) > parent->shape[i], "OpSlice: (start+size) out of boundary");
+        TB200_ERROR_IF(ctx, sz <= 0, "OpSlice: output must be positive");
+        offset += (int64_t)b * parent->stride[i];
+        n *= sz;
+    }
+    const size_t es = dtype_size(parent->dtype);
+    TB200_ERROR_IF(ctx, ((offset * (int64_t)es) & 15) != 0, "OpSlice: a zero-copy view must start on a 16-byte boundary");
+    tb200_tensor* t = new (std::nothrow) tb200_tensor(*parent);
+    if (!t)
+        return fail(ctx, TB200_INTERNAL, "out of host memory");
+    t->owns = false;
+    t->data = reinterpret_cast<uint8_t*>(parent->data) + offset * (int64_t)es;
+    bool contig = parent->contiguous;
+    for (int i = 0; i < parent->rank; i++)
+    {
+        if (size[i] != parent->shape[i] && i != 0)
+            contig = false;    // anything but a cut along the outermost dimension leaves gaps
+        t->shape[i] = size[i];
+    }
+    t->bytes      = (size_t)n * es;
+    t->contiguous = contig;
+    *out          = t;
+    return TB200_OK;
+}
+
+// RESHAPE as a zero-copy view of a contiguous tensor (OpReshape::eval, reference_model/src/ops/data_layout.cpp:227-):
+// element counts must match.
+extern "C" tb200_status tb200_tensor_reshape(tb200_ctx* ctx, const tb200_tensor* parent, int rank, const int32_t* shape,
+                                             tb200_tensor** out)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !parent || !shape || !out, "OpReshape: null operand");
+    TB200_ERROR_IF(ctx, !parent->contiguous, "OpReshape: a zero-copy reshape needs a contiguous tensor");
+    int64_t n = 1;
+    for (int i = 0; i < rank; i++)
+        n *= shape[i];
+    TB200_ERROR_IF(ctx, rank < 0 || rank > 6 || n != numel(parent), "OpReshape: input and output element counts differ");
+    return make_tensor(ctx, parent->dtype, rank, shape, parent->data, false, out);
+}
+
 // =================================================================================================== CONV2D
 extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
                                      const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp, const int32_t pad[4],
@@ -531,6 +606,7 @@ extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, 
     if (!ctx)
         return TB200_ERROR;
     TB200_ERROR_IF(ctx, !input || !weight || !bias || !output || !pad || !stride || !dilation, "OpConv2d: null operand");
+    TB200_ERROR_IF(ctx, !all_contiguous({ weight, bias, output }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "OpConv2d");
     // OpConv2d::checkTensorAttributes (reference_model/src/ops/tensor_ops.cpp:690-720)
     TB200_ERROR_IF(ctx, input->rank != 4 || weight->rank != 4 || output->rank != 4 || bias->rank != 1,
                    "OpConv2d: input, weight and output must be rank 4 and bias rank 1");
@@ -579,6 +655,7 @@ extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, 
         q.in_dtype = input->dtype;
         q.a        = input->data;
         q.N = N; q.IH = IH; q.IW = IW; q.IC = IC;
+        q.a_stride_w = input->stride[2]; q.a_stride_h = input->stride[1]; q.a_stride_n = input->stride[0];
         q.OH = OH; q.OW = OW; q.OC = OC;
         q.KH = KH; q.KW = KW;
         q.pad_t = pad[0]; q.pad_l = pad[2];
@@ -610,7 +687,7 @@ extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, 
                     int32_t* corr     = prefix + ((prefix_elems + 3) & ~(size_t)3);
                     int32_t* mult_pad = corr + corr_elems;
                     int8_t* shift_pad = reinterpret_cast<int8_t*>(mult_pad + OCpad);
-                    conv_epilogue_tables_kernel<<<(OCpad + 127) / 128, 128, 0, ctx->stream>>>(
+                    conv_epilogue_tables_kernel<<<(OCpad * 32 + 127) / 128, 128, 0, ctx->stream>>>(
                         reinterpret_cast<const int8_t*>(weight->data), reinterpret_cast<const int32_t*>(bias->data),
                         bias->shape[0], OC, OCpad, KH, KW, IC, input_zp, classes ? 1 : 0,
                         epi.has_rescale ? reinterpret_cast<const int32_t*>(epi.rs.mult) : nullptr,
@@ -655,6 +732,8 @@ extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, 
     d.N = N; d.IH = IH; d.IW = IW; d.IC = IC; d.OH = OH; d.OW = OW; d.OC = OC; d.KH = KH; d.KW = KW; d.M = 1;
     d.pad_t = pad[0]; d.pad_l = pad[2]; d.sy = stride[0]; d.sx = stride[1]; d.dy = dilation[0]; d.dx = dilation[1];
     d.in_zp = input_zp; d.w_zp = weight_zp; d.bias_n = bias->shape[0];
+    d.in_sn = input->stride[0]; d.in_sh = input->stride[1]; d.in_sw = input->stride[2];
+    TB200_ERROR_IF(ctx, input->stride[3] != 1, "OpConv2d: the channel dimension of the input must be dense");
     fill_conv_dev(&d, epi);
     const int block = 256;
     const int grid  = grid_for(ctx, numel(output), block);
@@ -701,6 +780,7 @@ extern "C" tb200_status tb200_depthwise_conv2d(tb200_ctx* ctx, const tb200_tenso
         return TB200_ERROR;
     TB200_ERROR_IF(ctx, !input || !weight || !bias || !output || !pad || !stride || !dilation,
                    "OpDepthwiseConv2d: null operand");
+    TB200_ERROR_IF(ctx, !all_contiguous({ input, weight, bias, output }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "OpDepthwiseConv2d");
     TB200_ERROR_IF(ctx, input->rank != 4 || weight->rank != 4 || output->rank != 4 || bias->rank != 1,
                    "OpDepthwiseConv2d: input, weight and output must be rank 4 and bias rank 1");
     const int N = input->shape[0], IH = input->shape[1], IW = input->shape[2], C = input->shape[3];
@@ -741,6 +821,7 @@ extern "C" tb200_status tb200_depthwise_conv2d(tb200_ctx* ctx, const tb200_tenso
     ConvDev d;
     memset(&d, 0, sizeof(d));
     d.N = N; d.IH = IH; d.IW = IW; d.IC = C; d.OH = OH; d.OW = OW; d.OC = C * M; d.KH = KH; d.KW = KW; d.M = M;
+    d.in_sn = input->stride[0]; d.in_sh = input->stride[1]; d.in_sw = input->stride[2];
     d.pad_t = pad[0]; d.pad_l = pad[2]; d.sy = stride[0]; d.sx = stride[1]; d.dy = dilation[0]; d.dx = dilation[1];
     d.in_zp = input_zp; d.w_zp = weight_zp; d.bias_n = bias->shape[0];
     fill_conv_dev(&d, epi);
@@ -804,6 +885,7 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
     if (!ctx)
         return TB200_ERROR;
     TB200_ERROR_IF(ctx, !a || !b || !output, "OpMatMul: null operand");
+    TB200_ERROR_IF(ctx, !all_contiguous({ a, b, output }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "OpMatMul");
     // OpMatMul::checkTensorAttributes (reference_model/src/ops/tensor_ops.cpp:1347-1420)
     TB200_ERROR_IF(ctx, a->rank != 3 || b->rank != 3 || output->rank != 3, "OpMatMul: operands must be rank 3");
     const int N = a->shape[0], H = a->shape[1], C = a->shape[2], W = b->shape[2];
@@ -959,6 +1041,7 @@ extern "C" tb200_status tb200_rescale(tb200_ctx* ctx, const tb200_tensor* input,
     if (!ctx)
         return TB200_ERROR;
     TB200_ERROR_IF(ctx, !input || !attr || !output, "OpRescale: null operand");
+    TB200_ERROR_IF(ctx, !all_contiguous({ input, output, attr->multiplier, attr->shift }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "OpRescale");
     TB200_ERROR_IF(ctx, !same_shape(input, output), "OpRescale: input and output shapes differ");
     const int C = input->rank > 0 ? input->shape[input->rank - 1] : 1;
     RescaleDev r;
@@ -992,6 +1075,7 @@ extern "C" tb200_status tb200_clamp(tb200_ctx* ctx, const tb200_tensor* input, i
     if (!ctx)
         return TB200_ERROR;
     TB200_ERROR_IF(ctx, !input || !output, "OpClamp: null operand");
+    TB200_ERROR_IF(ctx, !all_contiguous({ input, output }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "OpClamp");
     TB200_ERROR_IF(ctx, !same_shape(input, output) || input->dtype != output->dtype,
                    "OpClamp: input and output must have the same shape and dtype");
     const int64_t n = numel(input);
@@ -1039,6 +1123,7 @@ extern "C" tb200_status tb200_add(tb200_ctx* ctx, const tb200_tensor* a, const t
     if (!ctx)
         return TB200_ERROR;
     TB200_ERROR_IF(ctx, !a || !b || !output, "OpAdd: null operand");
+    TB200_ERROR_IF(ctx, !all_contiguous({ a, b, output }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "OpAdd");
     // BinaryNodeBase::checkTensorAttributes / broadcast (reference_model/src/ops/ewise_binary.cpp:40-111)
     TB200_ERROR_IF(ctx, a->rank != b->rank || a->dtype != b->dtype, "Binary operator input types must match");
     TB200_ERROR_IF(ctx, output->rank != a->rank, "Binary operators ADD lhs input and output rank/shape must match");
@@ -1108,6 +1193,7 @@ extern "C" tb200_status tb200_residual_add(tb200_ctx* ctx, const tb200_tensor* a
     if (!ctx)
         return TB200_ERROR;
     TB200_ERROR_IF(ctx, !a || !b || !output || !a_attr || !b_attr || !out_attr, "residual_add: null operand");
+    TB200_ERROR_IF(ctx, !all_contiguous({ a, b, output }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "residual_add");
     TB200_ERROR_IF(ctx, !same_shape(a, b) || !same_shape(a, output), "residual_add: operand shapes differ");
     TB200_ERROR_IF(ctx, a->dtype != TB200_INT8 || b->dtype != TB200_INT8 || output->dtype != TB200_INT8,
                    "residual_add: INT8 tensors only");
@@ -1148,6 +1234,7 @@ static tb200_status pool_common(tb200_ctx* ctx, const char* op, const tb200_tens
                                 const int32_t* pad, const int32_t* stride, const tb200_tensor* output, PoolDev* p)
 {
     TB200_ERROR_IF(ctx, !input || !output || !kernel || !pad || !stride, "%s: null operand", op);
+    TB200_ERROR_IF(ctx, !all_contiguous({ input, output }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", op);
     TB200_ERROR_IF(ctx, input->rank != 4 || output->rank != 4, "%s: input and output must be rank 4", op);
     TB200_ERROR_IF(ctx, input->dtype != output->dtype, "%s: input and output dtypes differ", op);
     tb200_status st = check_pool_attr(ctx, op, input->shape[1], input->shape[2], output->shape[1], output->shape[2],
@@ -1334,9 +1421,9 @@ extern "C" tb200_status tb200_matmul_host(tb200_ctx* ctx, tb200_dtype in_dtype, 
                                               (size_t)cnt * b_b, cudaMemcpyHostToDevice, p.h2d));
         TB200_CUDA_CHECK(ctx, cudaEventRecord(p.up[slot], p.h2d));
         TB200_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->stream, p.up[slot], 0));
-        tb200_tensor ta{ in_dtype, 3, { cnt, H, C, 1, 1, 1 }, base, (size_t)cnt * a_b, false };
-        tb200_tensor tbm{ in_dtype, 3, { cnt, C, W, 1, 1, 1 }, base + off_b, (size_t)cnt * b_b, false };
-        tb200_tensor to{ out_dtype, 3, { cnt, H, W, 1, 1, 1 }, base + off_o, (size_t)cnt * o_b, false };
+        tb200_tensor ta{ in_dtype, 3, { cnt, H, C, 1, 1, 1 }, base, (size_t)cnt * a_b, false, { 0, 0, 0, 0, 0, 0 }, true };
+        tb200_tensor tbm{ in_dtype, 3, { cnt, C, W, 1, 1, 1 }, base + off_b, (size_t)cnt * b_b, false, { 0, 0, 0, 0, 0, 0 }, true };
+        tb200_tensor to{ out_dtype, 3, { cnt, H, W, 1, 1, 1 }, base + off_o, (size_t)cnt * o_b, false, { 0, 0, 0, 0, 0, 0 }, true };
         st = tb200_matmul(ctx, &ta, &tbm, a_zp, b_zp, nullptr, &to);
         if (st != TB200_OK)
             break;

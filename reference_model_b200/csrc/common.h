@@ -19,6 +19,9 @@ struct tb200_tensor
     void* data;
     size_t bytes;
     bool owns;
+    // element strides per dimension; a view made by tb200_tensor_slice shares its parent's memory and pitch
+    int64_t stride[6];
+    bool contiguous;
 };
 
 // Bits of the device status word (one int32 per context, OR-ed into by kernels).
@@ -143,6 +146,7 @@ struct TcProblem
     // A: activation tensor viewed as [N][IH][IW][IC] (matmul: [1][batch][M][K])
     const void* a;
     int N, IH, IW, IC;
+    int64_t a_stride_w, a_stride_h, a_stride_n;    // element strides of A (0 = contiguous NHWC)
     // output pixel grid [N][OH][OW] and columns OC (matmul: [1][batch][M] x Ncols)
     int OH, OW, OC;
     int KH, KW;

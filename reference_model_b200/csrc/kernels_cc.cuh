@@ -490,6 +490,7 @@ struct ConvDev
 {
     int N, IH, IW, IC, OH, OW, OC, KH, KW, M;    // M: depthwise multiplier
     int pad_t, pad_l, sy, sx, dy, dx;
+    int64_t in_sn, in_sh, in_sw;    // element strides of the input (a SLICE view keeps its parent's pitch)
     int32_t in_zp, w_zp;
     int bias_n;
     // optional fused epilogue
@@ -510,7 +511,7 @@ __global__ void conv2d_direct_i8_kernel(const int8_t* __restrict__ in, const int
     const int64_t total = (int64_t)p.N * p.OH * p.OW * p.OC;
     const int64_t step  = (int64_t)gridDim.x * blockDim.x;
     bool bad            = false;
-    const bool vec4 = (p.IC % 4) == 0;
+    const bool vec4 = (p.IC % 4) == 0 && (p.in_sw % 4) == 0 && (p.in_sh % 4) == 0 && (p.in_sn % 4) == 0;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
     {
         const int oc = (int)(i % p.OC);
@@ -530,7 +531,7 @@ __global__ void conv2d_direct_i8_kernel(const int8_t* __restrict__ in, const int
                 const int x = ox * p.sx + kx * p.dx - p.pad_l;
                 if (x < 0 || x >= p.IW)
                     continue;
-                const int8_t* ip = in + (((int64_t)n * p.IH + y) * p.IW + x) * p.IC;
+                const int8_t* ip = in + (int64_t)n * p.in_sn + (int64_t)y * p.in_sh + (int64_t)x * p.in_sw;
                 const int8_t* wp = w + (((int64_t)oc * p.KH + ky) * p.KW + kx) * p.IC;
                 if (vec4)
                 {
@@ -595,7 +596,7 @@ __global__ void conv2d_direct_fp_kernel(const T* __restrict__ in, const T* __res
                 const int x = ox * p.sx + kx * p.dx - p.pad_l;
                 if (x < 0 || x >= p.IW)
                     continue;
-                const T* ip = in + (((int64_t)n * p.IH + y) * p.IW + x) * p.IC;
+                const T* ip = in + (int64_t)n * p.in_sn + (int64_t)y * p.in_sh + (int64_t)x * p.in_sw;
                 const T* wp = w + (((int64_t)oc * p.KH + ky) * p.KW + kx) * p.IC;
                 for (int ic = 0; ic < p.IC; ic++)
                     acc = fmaf(to_f32<T>(ip[ic]), to_f32<T>(wp[ic]), acc);
@@ -898,8 +899,8 @@ __global__ void __launch_bounds__(256) matmul_col_corr_kernel(const int8_t* __re
     }
 }
 
-// CONV2D epilogue constants for int8 weights OHWI with weight_zp == 0, one thread per padded output channel:
-//   prefix[(KH+1)(KW+1)][OC]  scratch: inclusive 2-D prefix sums over taps of sum_ic w[oc,ky,kx,ic]
+// CONV2D epilogue constants for int8 weights OHWI with weight_zp == 0, one warp per padded output channel:
+//   prefix[OC][(KH+1)(KW+1)]  scratch: inclusive 2-D prefix sums over taps of sum_ic w[oc,ky,kx,ic]
 //   corr[classes][OCpad]      bias[oc] - in_zp * (sum of the weights of the in-scope taps).  With `classes` the table
 //                             has (KH+1)^2 (KW+1)^2 rows indexed ((ky_lo*(KH+1)+ky_hi)*(KW+1)+kx_lo)*(KW+1)+kx_hi;
 //                             otherwise a single row for the full filter
@@ -910,55 +911,81 @@ __global__ void conv_epilogue_tables_kernel(const int8_t* __restrict__ w, const 
                                             int per_channel, int32_t* __restrict__ prefix, int32_t* __restrict__ corr,
                                             int32_t* __restrict__ mult_pad, int8_t* __restrict__ shift_pad)
 {
-    const int oc = blockIdx.x * blockDim.x + threadIdx.x;
+    // One warp per output channel: lanes split the channel run of each tap (128-bit loads), the warp-reduced tap
+    // sums become 2-D prefix sums kept in registers by lane 0 .. and mirrored to `prefix` for the class loop, which
+    // the lanes split again.
+    const int lane = threadIdx.x & 31;
+    const int oc   = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (oc >= OCpad)
         return;
     const int W1 = KW + 1, H1 = KH + 1;
     const int ncls = classes ? H1 * H1 * W1 * W1 : 1;
     if (oc >= OC)
     {
-        for (int c = 0; c < ncls; c++)
+        for (int c = lane; c < ncls; c += 32)
             corr[(int64_t)c * OCpad + oc] = 0;
-        if (mult_pad)
+        if (mult_pad && lane == 0)
         {
             mult_pad[oc]  = 0;
             shift_pad[oc] = 2;
         }
         return;
     }
+    int32_t* P = prefix + (int64_t)oc * H1 * W1;    // this channel's (KH+1) x (KW+1) prefix sums
     for (int ky = 0; ky <= KH; ky++)
         for (int kx = 0; kx <= KW; kx++)
         {
             int32_t v = 0;
             if (ky > 0 && kx > 0)
             {
-                int32_t s        = 0;
                 const int8_t* wp = w + (((int64_t)oc * KH + (ky - 1)) * KW + (kx - 1)) * IC;
-                for (int ic = 0; ic < IC; ic++)
-                    s += wp[ic];
-                v = s + prefix[((ky - 1) * W1 + kx) * OC + oc] + prefix[(ky * W1 + kx - 1) * OC + oc] -
-                    prefix[((ky - 1) * W1 + kx - 1) * OC + oc];
+                int32_t s        = 0;
+                if ((IC & 15) == 0)
+                {
+                    for (int ic = lane * 16; ic < IC; ic += 512)
+                    {
+                        const int4 q = __ldg(reinterpret_cast<const int4*>(wp + ic));
+                        s = __dp4a(q.x, 0x01010101, s);
+                        s = __dp4a(q.y, 0x01010101, s);
+                        s = __dp4a(q.z, 0x01010101, s);
+                        s = __dp4a(q.w, 0x01010101, s);
+                    }
+                }
+                else
+                {
+                    for (int ic = lane; ic < IC; ic += 32)
+                        s += wp[ic];
+                }
+                for (int o = 16; o > 0; o >>= 1)
+                    s += __shfl_xor_sync(0xffffffffu, s, o);
+                v = s;
             }
-            prefix[(ky * W1 + kx) * OC + oc] = v;
+            if (lane == 0)
+            {
+                if (ky > 0 && kx > 0)
+                    v += P[(ky - 1) * W1 + kx] + P[ky * W1 + kx - 1] - P[(ky - 1) * W1 + kx - 1];
+                P[ky * W1 + kx] = v;
+            }
         }
+    __syncwarp();
     const int32_t b = bias[bias_n == 1 ? 0 : oc];
     if (!classes)
-        corr[oc] = b - in_zp * prefix[(KH * W1 + KW) * OC + oc];
+    {
+        if (lane == 0)
+            corr[oc] = b - in_zp * P[KH * W1 + KW];
+    }
     else
     {
-        for (int yl = 0; yl <= KH; yl++)
-            for (int yh = 0; yh <= KH; yh++)
-                for (int xl = 0; xl <= KW; xl++)
-                    for (int xh = 0; xh <= KW; xh++)
-                    {
-                        int32_t rs = 0;
-                        if (yh > yl && xh > xl)
-                            rs = prefix[(yh * W1 + xh) * OC + oc] - prefix[(yl * W1 + xh) * OC + oc] -
-                                 prefix[(yh * W1 + xl) * OC + oc] + prefix[(yl * W1 + xl) * OC + oc];
-                        corr[(int64_t)(((yl * H1 + yh) * W1 + xl) * W1 + xh) * OCpad + oc] = b - in_zp * rs;
-                    }
+        for (int c = lane; c < ncls; c += 32)
+        {
+            const int xh = c % W1, xl = (c / W1) % W1, yh = (c / (W1 * W1)) % H1, yl = c / (W1 * W1 * H1);
+            int32_t rs = 0;
+            if (yh > yl && xh > xl)
+                rs = P[yh * W1 + xh] - P[yl * W1 + xh] - P[yh * W1 + xl] + P[yl * W1 + xl];
+            corr[(int64_t)c * OCpad + oc] = b - in_zp * rs;
+        }
     }
-    if (mult_pad)
+    if (mult_pad && lane == 0)
     {
         mult_pad[oc]  = mult[per_channel ? oc : 0];
         shift_pad[oc] = shift[per_channel ? oc : 0];

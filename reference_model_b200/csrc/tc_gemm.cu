@@ -109,6 +109,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
     __shared__ __align__(8) uint64_t bar_tmem_empty[2];
     __shared__ uint32_t tmem_base_holder;
     __shared__ int abort_flag;
+    // TC_EPI_RESCALE: per-column scaling constants of the current column block, written once per block by the
+    // epilogue threads: {multiplier, shift, round(v >= 0) lo/hi, round(v < 0) lo/hi, largest |v| allowed, 0}
+    __shared__ __align__(16) int32_t epi_cols[EPI == TC_EPI_RESCALE ? 256 : 1][8];
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -300,14 +303,46 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
         uint32_t acc_phase = 0;
         bool ok = true;
         int dev_flags = 0;
+        int cols_loaded_for = -1;
         for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x)
         {
             const TileCoord t = decode_tile(p, tile);
+            if (EPI == TC_EPI_RESCALE && cols_loaded_for != t.col0)
+            {
+                // (re)build the per-column constants; the named barrier keeps the 128 epilogue threads in step
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                for (int c = (int)threadIdx.x - 64; c < p.block_n; c += 128)
+                {
+                    const int32_t m = __ldg(p.mult_pad + t.col0 + c);
+                    const int32_t s = (int32_t)__ldg(p.shift_pad + t.col0 + c);
+                    const bool valid  = (m >= 0) && (s >= 2) && (s <= 62);
+                    const int32_t sc  = valid ? s : 2;
+                    const int64_t half = (int64_t)1 << (sc - 1);
+                    int64_t rpos = half, rneg = half;
+                    if (p.double_round && sc > 31)
+                    {
+                        rpos += (int64_t)1 << 30;
+                        rneg -= (int64_t)1 << 30;
+                    }
+                    // apply_scale_32 requires -2^(shift-1) <= v < 2^(shift-1); invalid operands fail every value
+                    const int32_t vlim = !valid ? -1 : (sc - 1 >= 31 ? 2147483647 : (int32_t)(half - 1));
+                    int4 lo4 = make_int4(m, sc, (int32_t)(uint32_t)(rpos & 0xffffffffLL), (int32_t)(rpos >> 32));
+                    int4 hi4 = make_int4((int32_t)(uint32_t)(rneg & 0xffffffffLL), (int32_t)(rneg >> 32), vlim, 0);
+                    *reinterpret_cast<int4*>(&epi_cols[c][0]) = lo4;
+                    *reinterpret_cast<int4*>(&epi_cols[c][4]) = hi4;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                cols_loaded_for = t.col0;
+            }
+            // After a wait has given up this warp only keeps visiting the named barrier above (the other epilogue
+            // warps may still be running and would otherwise block on it); it does no further work.
+            if (!ok)
+                continue;
             ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_full[acc]), acc_phase, kWaitLimitCycles);
             // the whole warp must agree before the warp-collective TMEM loads
             ok = __all_sync(0xffffffffu, ok);
             if (!ok)
-                break;
+                continue;
             ptx::tc_fence_after_sync();
 
             const int ox = t.x0 + xx, oy = t.y0 + yy, on = t.n0 + nn;
@@ -403,32 +438,20 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
                 }
                 else if (EPI == TC_EPI_RESCALE)
                 {
-                    int32_t mv[32];
-                    uint32_t sw[8];
-                    {
-                        const int4* mp = reinterpret_cast<const int4*>(p.mult_pad + col);
-#pragma unroll
-                        for (int q = 0; q < 8; q++)
-                        {
-                            const int4 m4 = __ldg(mp + q);
-                            mv[4 * q + 0] = m4.x;
-                            mv[4 * q + 1] = m4.y;
-                            mv[4 * q + 2] = m4.z;
-                            mv[4 * q + 3] = m4.w;
-                        }
-                        const int4* sp = reinterpret_cast<const int4*>(p.shift_pad + col);
-                        const int4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
-                        sw[0] = (uint32_t)s0.x; sw[1] = (uint32_t)s0.y; sw[2] = (uint32_t)s0.z; sw[3] = (uint32_t)s0.w;
-                        sw[4] = (uint32_t)s1.x; sw[5] = (uint32_t)s1.y; sw[6] = (uint32_t)s1.z; sw[7] = (uint32_t)s1.w;
-                    }
                     bool bad = false;
 #pragma unroll
                     for (int i = 0; i < 32; i++)
                     {
-                        const int32_t sh = (int32_t)(int8_t)((sw[i >> 2] >> ((i & 3) * 8)) & 0xffu);
-                        bool b = false;
-                        const int32_t sc = apply_scale_32_dev((int32_t)v[i], mv[i], sh, p.double_round != 0, b);
-                        int64_t z = (int64_t)sc + (int64_t)p.out_zp;
+                        // QuantUtil::apply_scale_32 with the per-column constants prepared above
+                        const int4 c0 = *reinterpret_cast<const int4*>(&epi_cols[c * 32 + i][0]);
+                        const int4 c1 = *reinterpret_cast<const int4*>(&epi_cols[c * 32 + i][4]);
+                        const int32_t a = (int32_t)v[i];
+                        const int64_t rpos = ((int64_t)c0.w << 32) | (uint32_t)c0.z;
+                        const int64_t rneg = ((int64_t)c1.y << 32) | (uint32_t)c1.x;
+                        const int64_t prod = (int64_t)a * (int64_t)c0.x + (a >= 0 ? rpos : rneg);
+                        const int64_t res  = prod >> c0.y;
+                        bool b = (a > c1.z) || (a < ~c1.z) || (res != (int64_t)(int32_t)res);
+                        int64_t z = res + (int64_t)p.out_zp;
                         b |= (z > 2147483647LL) || (z < -2147483648LL);
                         z = z < (int64_t)p.clamp_lo ? (int64_t)p.clamp_lo : z;
                         z = z > (int64_t)p.clamp_hi ? (int64_t)p.clamp_hi : z;
@@ -625,6 +648,7 @@ struct TcPlan
     TcKernelParams kp;
     int smem_bytes;
     int grid;
+    int ctas_per_sm;
     // tensor map recipes (filled by plan, encoded at launch)
     cuuint64_t a_dims[4], a_strides[3];
     cuuint32_t a_box[4], a_estr[4];
@@ -655,8 +679,12 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     memset(&k, 0, sizeof(k));
     // A view.  A stride-1, pad-0 1x1 convolution (and MATMUL) is a plain GEMM over flattened pixels.
     int N = q.N, IH = q.IH, IW = q.IW, OH = q.OH, OW = q.OW;
+    const int64_t sw = q.a_stride_w ? q.a_stride_w : (int64_t)q.IC;
+    const int64_t sh = q.a_stride_h ? q.a_stride_h : sw * q.IW;
+    const int64_t sn = q.a_stride_n ? q.a_stride_n : sh * q.IH;
+    const bool dense = sw == q.IC && sh == sw * q.IW && sn == sh * q.IH;
     const bool pure_gemm = q.KH == 1 && q.KW == 1 && q.stride_y == 1 && q.stride_x == 1 && q.pad_t == 0 &&
-                           q.pad_l == 0 && OH == IH && OW == IW && !q.b_mn_major;
+                           q.pad_l == 0 && OH == IH && OW == IW && !q.b_mn_major && dense;
     if (pure_gemm)
     {
         int64_t pixels = (int64_t)N * IH * IW;
@@ -725,7 +753,7 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     k.chunk_elems    = swz / es;
     k.chunks_per_tap = row_bytes / swz;
     k.total_chunks   = q.KH * q.KW * k.chunks_per_tap;
-    k.ksub           = std::min(std::max(1, 128 / swz), k.total_chunks);
+    k.ksub           = std::min(std::max(1, env_int("TB200_TC_KSUB", 128 / swz)), k.total_chunks);
     k.num_kstages    = (k.total_chunks + k.ksub - 1) / k.ksub;
     k.pad_t = q.pad_t;
     k.pad_l = q.pad_l;
@@ -768,7 +796,11 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     }
     k.tx_bytes_per_chunk = a_tx + b_tx;
     k.stage_bytes        = k.ksub * (k.a_chunk_bytes + k.b_chunk_bytes);
-    const int smem_budget = 200 * 1024;
+    // Small column blocks leave most of a tile's time in fixed per-tile synchronisation; two co-resident CTAs per SM
+    // (half the shared-memory budget each, 2 x TMEM columns <= 512) overlap one CTA's bubbles with the other's work.
+    plan->ctas_per_sm = env_int("TB200_TC_CTAS_PER_SM", (block_n <= 128 && 4 * k.stage_bytes <= 100 * 1024) ? 2 : 1);
+    plan->ctas_per_sm = std::max(1, std::min(plan->ctas_per_sm, 512 / std::max(32, 2 * block_n)));
+    const int smem_budget = (plan->ctas_per_sm > 1 ? 208 / plan->ctas_per_sm : 200) * 1024;
     k.num_stages = std::min(kMaxStages, smem_budget / k.stage_bytes);
     k.num_stages = std::min(k.num_stages, std::max(2, k.num_kstages * 2));
     const int forced = env_int("TB200_TC_STAGES", 0);
@@ -796,9 +828,18 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     plan->a_dims[1] = (cuuint64_t)IW;
     plan->a_dims[2] = (cuuint64_t)IH;
     plan->a_dims[3] = (cuuint64_t)N;
-    plan->a_strides[0] = (cuuint64_t)q.IC * es;
-    plan->a_strides[1] = plan->a_strides[0] * IW;
-    plan->a_strides[2] = plan->a_strides[1] * IH;
+    if (pure_gemm)
+    {
+        plan->a_strides[0] = (cuuint64_t)q.IC * es;
+        plan->a_strides[1] = plan->a_strides[0] * IW;
+        plan->a_strides[2] = plan->a_strides[1] * IH;
+    }
+    else
+    {
+        plan->a_strides[0] = (cuuint64_t)sw * es;
+        plan->a_strides[1] = (cuuint64_t)sh * es;
+        plan->a_strides[2] = (cuuint64_t)sn * es;
+    }
     plan->a_box[0]  = (cuuint32_t)k.chunk_elems;
     plan->a_box[1]  = (cuuint32_t)(BW * q.stride_x);
     plan->a_box[2]  = (cuuint32_t)(BH * q.stride_y);
@@ -835,7 +876,7 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     for (int i = 0; i < 3; i++)
         if (plan->a_strides[i] % 16 != 0 || plan->a_strides[i] >= (1ULL << 40))
             return no("activation stride not usable by TMA");
-    plan->grid = std::min(k.num_tiles, num_sms);
+    plan->grid = std::min(k.num_tiles, num_sms * plan->ctas_per_sm);
     return true;
 }
 

@@ -335,6 +335,56 @@ def test_conv_error_ifs(ctx):
     _free(tx, tw, tbias, good, bad, tb3, tw5, fx, fw, fb, fo)
 
 
+def test_slice_view_as_conv_input_and_reshape(ctx):
+    """SLICE / RESHAPE as zero-copy views: the 55x55 cut of a 56x56 tensor feeds a stride-2 1x1 convolution (legal
+    under the exact-division rule only on the odd size), on both kernel families; other operators refuse a view."""
+    r = util.rng(11)
+    x, w, b = util.conv_int8_case(r, 2, 56, 56, 64, 128, 1, 1, bias_range=1 << 16)
+    tx, tw, tbias = ctx.from_numpy(x), ctx.from_numpy(w), ctx.from_numpy(b)
+    view = tx.slice([0, 0, 0, 0], [2, 55, 55, 64])
+    exp = orc.conv2d(x[:, :55, :55, :], w, b, [0, 0, 0, 0], [2, 2], [1, 1], -128, 0)
+    to = ctx.empty(I32, (2, 28, 28, 128))
+    for policy, family in ((0, "tc_gemm"), (1, "conv2d_direct")):
+        old = ctx.set_kernel_policy(policy)
+        ctx.conv2d(view, tw, tbias, to, [0, 0, 0, 0], [2, 2], [1, 1], -128, 0)
+        assert ctx.last_kernel().startswith(family)
+        ctx.set_kernel_policy(old)
+        st, out = to.download()
+        assert st == tb.Status.OK and np.array_equal(out, exp)
+    # an interior cut with an offset (16-byte aligned start): rows 8.., columns 4..
+    view2 = tx.slice([1, 8, 4, 0], [1, 20, 30, 64])
+    exp2 = orc.conv2d(x[1:2, 8:28, 4:34, :], w, b, [0, 0, 0, 0], [1, 1], [1, 1], 3, 0)
+    to2 = ctx.empty(I32, (1, 20, 30, 128))
+    ctx.conv2d(view2, tw, tbias, to2, [0, 0, 0, 0], [1, 1], [1, 1], 3, 0)
+    st, out = to2.download()
+    assert np.array_equal(out, exp2)
+    # OpSlice ERROR_IFs (data_layout.cpp:369-398) and the contiguity rule of the other operators
+    with pytest.raises(tb.Tb200Error):
+        tx.slice([0, 56, 0, 0], [2, 1, 1, 64])
+    with pytest.raises(tb.Tb200Error):
+        tx.slice([0, 0, 0, 0], [2, 57, 56, 64])
+    with pytest.raises(tb.Tb200Error):
+        tx.slice([0, 0, 0, 0], [2, 0, 56, 64])
+    tc = ctx.empty(I8, (2, 55, 55, 64))
+    assert ctx.clamp(view, tc, -5, 5, check=False) == tb.Status.ERROR
+    # a cut along the batch dimension only stays contiguous
+    first = tx.slice([1, 0, 0, 0], [1, 56, 56, 64])
+    tc1 = ctx.empty(I8, (1, 56, 56, 64))
+    assert ctx.clamp(first, tc1, -5, 5) == tb.Status.OK
+    _, out = tc1.download()
+    assert np.array_equal(out, np.clip(x[1:2], -5, 5))
+    # RESHAPE: [N,1,1,C] pooled features -> [1,N,C] MATMUL operand
+    feat = r.integers(-128, 128, size=(4, 1, 1, 256)).astype(np.int8)
+    wfc = r.integers(-128, 128, size=(1, 256, 40)).astype(np.int8)
+    tf, twf, tlog = ctx.from_numpy(feat), ctx.from_numpy(wfc), ctx.empty(I32, (1, 4, 40))
+    ctx.matmul(tf.reshape([1, 4, 256]), twf, tlog, -128, 0)
+    _, out = tlog.download()
+    assert np.array_equal(out, orc.matmul(feat.reshape(1, 4, 256), wfc, -128, 0))
+    with pytest.raises(tb.Tb200Error):
+        tf.reshape([1, 4, 255])
+    _free(view, view2, first, tx, tw, tbias, to, to2, tc, tc1, tf, twf, tlog)
+
+
 # ------------------------------------------------------------------------------------------- MATMUL
 MATMUL_I8_CASES = [(2, 256, 256, 256, 3, -2), (1, 128, 384, 512, 0, 0), (3, 200, 130, 96, -7, 5), (1, 130, 4096, 272, 3, -2),
                    (2, 5, 7, 3, 4, 15)]
