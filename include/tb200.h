@@ -96,6 +96,18 @@ extern "C"
     TB200_API tb200_status tb200_timer_enable(tb200_ctx* ctx, int32_t on);
     TB200_API tb200_status tb200_timer_read(tb200_ctx* ctx, double* total_ms, int32_t* launches);
 
+    /* Whole-evaluation replay.  The reference evaluates a graph node by node from its ready list
+     * (reference_model/src/subgraph_traverser.cpp:1190-1202); on the device the same sequence of operator calls can
+     * be recorded once into a CUDA graph and replayed with a single launch.  Between tb200_capture_begin and
+     * tb200_capture_end the operator entry points enqueue nothing for execution, they only record; no call may
+     * need to grow the context's scratch memory (run the sequence once eagerly first), and uploads / downloads /
+     * tb200_sync are not allowed.  Operands must stay allocated for as long as the graph is replayed. */
+    typedef struct tb200_graph tb200_graph;
+    TB200_API tb200_status tb200_capture_begin(tb200_ctx* ctx);
+    TB200_API tb200_status tb200_capture_end(tb200_ctx* ctx, tb200_graph** out);
+    TB200_API tb200_status tb200_graph_launch(tb200_ctx* ctx, tb200_graph* graph);
+    TB200_API tb200_status tb200_graph_destroy(tb200_ctx* ctx, tb200_graph* graph);
+
     /* ---- tensors -------------------------------------------------------------------------------
      * Device-resident replacements for TensorTemplate<Eigen::Tensor<T,R>> buffers
      * (reference_model/src/tensor.h:365-440): allocate stands for Tensor::allocate (:380-398),

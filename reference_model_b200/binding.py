@@ -66,7 +66,8 @@ _LIB = None
 # every symbol include/tb200.h declares
 EXPORTS = [
     "tb200_ctx_create", "tb200_ctx_destroy", "tb200_last_error", "tb200_sync", "tb200_launch_count",
-    "tb200_timer_enable", "tb200_timer_read",
+    "tb200_timer_enable", "tb200_timer_read", "tb200_capture_begin", "tb200_capture_end", "tb200_graph_launch",
+    "tb200_graph_destroy",
     "tb200_tensor_alloc", "tb200_tensor_wrap", "tb200_tensor_free", "tb200_tensor_upload", "tb200_tensor_download",
     "tb200_tensor_data", "tb200_tensor_bytes", "tb200_tensor_slice", "tb200_tensor_reshape", "tb200_conv2d", "tb200_depthwise_conv2d", "tb200_matmul",
     "tb200_rescale", "tb200_clamp", "tb200_add", "tb200_residual_add", "tb200_max_pool2d", "tb200_avg_pool2d",
@@ -93,6 +94,10 @@ def load_library():
         "tb200_launch_count": (ctypes.c_uint64, [vp]),
         "tb200_timer_enable": (i32, [vp, i32]),
         "tb200_timer_read": (i32, [vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_int32)]),
+        "tb200_capture_begin": (i32, [vp]),
+        "tb200_capture_end": (i32, [vp, ctypes.POINTER(vp)]),
+        "tb200_graph_launch": (i32, [vp, vp]),
+        "tb200_graph_destroy": (i32, [vp, vp]),
         "tb200_tensor_alloc": (i32, [vp, i32, ctypes.c_int, p_i32, ctypes.POINTER(vp)]),
         "tb200_tensor_wrap": (i32, [vp, i32, ctypes.c_int, p_i32, vp, ctypes.POINTER(vp)]),
         "tb200_tensor_free": (i32, [vp, vp]),
@@ -264,6 +269,21 @@ class Context:
         ms, n = ctypes.c_double(0.0), ctypes.c_int32(0)
         self._check(self.lib.tb200_timer_read(self.handle, ctypes.byref(ms), ctypes.byref(n)))
         return float(ms.value), int(n.value)
+
+    def capture_begin(self):
+        return self._check(self.lib.tb200_capture_begin(self.handle))
+
+    def capture_end(self):
+        """Ends the capture and returns the graph handle for graph_launch."""
+        h = ctypes.c_void_p()
+        self._check(self.lib.tb200_capture_end(self.handle, ctypes.byref(h)))
+        return h
+
+    def graph_launch(self, graph):
+        return self._check(self.lib.tb200_graph_launch(self.handle, graph))
+
+    def graph_destroy(self, graph):
+        return self._check(self.lib.tb200_graph_destroy(self.handle, graph))
 
     def set_kernel_policy(self, policy):
         return self.lib.tb200_set_kernel_policy(self.handle, int(policy))

@@ -17,6 +17,8 @@ tb200_status ensure_scratch(tb200_ctx* ctx, size_t bytes)
 {
     if (bytes <= ctx->scratch_bytes)
         return TB200_OK;
+    if (ctx->capturing)
+        return fail(ctx, TB200_ERROR, "scratch memory would have to grow during capture; evaluate once eagerly first");
     // the old block may still be in use by kernels queued on the stream
     TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
     if (ctx->scratch)
@@ -401,6 +403,77 @@ extern "C" tb200_status tb200_timer_read(tb200_ctx* ctx, double* total_ms, int32
     return TB200_OK;
 }
 
+extern "C" tb200_status tb200_capture_begin(tb200_ctx* ctx)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, ctx->capturing, "capture already in progress");
+    TB200_ERROR_IF(ctx, ctx->timing, "disable the kernel timer before capturing");
+    TB200_CUDA_CHECK(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    ctx->capturing = true;
+    return TB200_OK;
+}
+
+extern "C" tb200_status tb200_capture_end(tb200_ctx* ctx, tb200_graph** out)
+{
+    if (!ctx || !out)
+        return TB200_ERROR;
+    *out = nullptr;
+    TB200_ERROR_IF(ctx, !ctx->capturing, "no capture in progress");
+    ctx->capturing   = false;
+    cudaGraph_t g    = nullptr;
+    cudaError_t e    = cudaStreamEndCapture(ctx->stream, &g);
+    if (e != cudaSuccess || !g)
+        return fail(ctx, TB200_INTERNAL, "cudaStreamEndCapture failed: %s", cudaGetErrorString(e));
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, g, 0);
+    if (e != cudaSuccess)
+    {
+        cudaGraphDestroy(g);
+        return fail(ctx, TB200_INTERNAL, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+    }
+    tb200_graph* tg = new (std::nothrow) tb200_graph();
+    if (!tg)
+    {
+        cudaGraphExecDestroy(exec);
+        cudaGraphDestroy(g);
+        return fail(ctx, TB200_INTERNAL, "out of host memory");
+    }
+    tg->graph = g;
+    tg->exec  = exec;
+    size_t n  = 0;
+    if (cudaGraphGetNodes(g, nullptr, &n) == cudaSuccess)
+        tg->launches = n;
+    *out = tg;
+    return TB200_OK;
+}
+
+extern "C" tb200_status tb200_graph_launch(tb200_ctx* ctx, tb200_graph* graph)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !graph || !graph->exec, "null graph");
+    TB200_ERROR_IF(ctx, ctx->capturing, "a captured graph cannot be launched while capturing");
+    TB200_CUDA_CHECK(ctx, cudaGraphLaunch(graph->exec, ctx->stream));
+    ctx->launches += graph->launches;
+    ctx->last_kernel = "cuda_graph_replay";
+    return TB200_OK;
+}
+
+extern "C" tb200_status tb200_graph_destroy(tb200_ctx* ctx, tb200_graph* graph)
+{
+    if (!graph)
+        return TB200_OK;
+    if (ctx)
+        cudaStreamSynchronize(ctx->stream);
+    if (graph->exec)
+        cudaGraphExecDestroy(graph->exec);
+    if (graph->graph)
+        cudaGraphDestroy(graph->graph);
+    delete graph;
+    return TB200_OK;
+}
+
 extern "C" int tb200_set_kernel_policy(tb200_ctx* ctx, int policy)
 {
     int old     = ctx->policy;
@@ -417,6 +490,7 @@ extern "C" tb200_status tb200_sync(tb200_ctx* ctx)
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ERROR_IF(ctx, ctx->capturing, "tb200_sync is not allowed while capturing");
     TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     TB200_CUDA_CHECK(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
     TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
@@ -513,6 +587,7 @@ extern "C" tb200_status tb200_tensor_upload(tb200_ctx* ctx, tb200_tensor* t, con
         return TB200_ERROR;
     TB200_ERROR_IF(ctx, !t || !host, "null tensor or host buffer");
     TB200_ERROR_IF(ctx, !t->contiguous, "upload needs a contiguous tensor");
+    TB200_ERROR_IF(ctx, ctx->capturing, "uploads are not allowed while capturing");
     TB200_ERROR_IF(ctx, bytes != t->bytes, "upload of %zu bytes into a tensor of %zu bytes", bytes, t->bytes);
     if (bytes)
         TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(t->data, host, bytes, cudaMemcpyHostToDevice, ctx->stream));
@@ -525,6 +600,7 @@ extern "C" tb200_status tb200_tensor_download(tb200_ctx* ctx, const tb200_tensor
         return TB200_ERROR;
     TB200_ERROR_IF(ctx, !t || !host, "null tensor or host buffer");
     TB200_ERROR_IF(ctx, !t->contiguous, "download needs a contiguous tensor");
+    TB200_ERROR_IF(ctx, ctx->capturing, "downloads are not allowed while capturing");
     TB200_ERROR_IF(ctx, bytes != t->bytes, "download of %zu bytes from a tensor of %zu bytes", bytes, t->bytes);
     if (bytes)
         TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(host, t->data, bytes, cudaMemcpyDeviceToHost, ctx->stream));

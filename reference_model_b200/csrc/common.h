@@ -31,6 +31,13 @@ enum : int
     TB200_DEV_TIMEOUT       = 2,    // a bounded pipeline wait gave up (internal error)
 };
 
+struct tb200_graph
+{
+    cudaGraph_t graph    = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t launches    = 0;    // kernels recorded
+};
+
 struct tb200_ctx
 {
     int device           = 0;
@@ -43,6 +50,7 @@ struct tb200_ctx
     uint64_t launches    = 0;
     int policy           = 0;
     int num_sms          = 148;
+    bool capturing       = false;    // between tb200_capture_begin / tb200_capture_end
     const char* last_kernel = "none";
     std::string err;
     // host-buffer pipeline of tb200_matmul_host: copy streams, events and two sets of device staging buffers
