@@ -156,8 +156,146 @@ def run_reference(args, rank, world):
     }))
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# Second workload: the whole int8 ResNet-50-shaped TOSA graph, batch 256 split by N over the ranks, logits gathered
+# with NCCL.  `python bench.py --workload resnet50 [--gpus N]` (strong scaling: the batch is fixed).
+# ---------------------------------------------------------------------------------------------------------------------
+GRAPH_BATCH = 256
+
+
+def run_resnet50(args, rank, local_rank, world):
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    import reference_model_b200 as tb
+    from reference_model_b200 import graph as G
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    total = args.graph_batch
+    assert total % world == 0
+    nb = total // world
+    g = G.resnet50_int8(nb)
+    images = G.synthetic_images(total)[rank * nb:(rank + 1) * nb]
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ctx = tb.Context(local_rank, stream.cuda_stream)
+        logits = torch.empty((1, nb, 1000), dtype=torch.int32, device="cuda")
+        gathered = torch.empty((world, nb, 1000), dtype=torch.int32, device="cuda")
+        ext = {"logits": ctx.wrap(tb.DType.INT32, (1, nb, 1000), logits.data_ptr(), logits)}
+        run = G.DeviceRunner(ctx, g, fused=True, external=ext)
+        x_pin = torch.from_numpy(images).pin_memory()
+        out_pin = torch.empty((world, nb, 1000), dtype=torch.int32).pin_memory()
+        x_dev = run.t["input"]
+
+        def upload():
+            ctx.lib.tb200_tensor_upload(ctx.handle, x_dev.handle, ctypes.c_void_p(x_pin.data_ptr()), x_pin.numel())
+
+        def step():
+            run.run()
+            if world > 1:
+                dist.all_gather_into_tensor(gathered.view(-1), logits.view(-1))
+            else:
+                gathered.copy_(logits)
+
+        upload()
+        launches_per_eval = run.launches_per_run()
+        run.capture()
+        for _ in range(max(args.warmup, 3)):
+            step()
+        assert ctx.sync() == tb.Status.OK, ctx.last_error()
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop() if rank == 0 else None
+        assert ctx.sync() == tb.Status.OK, ctx.last_error()
+        # end to end: pinned host images in, gathered logits back on the host, every step
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            upload()
+            step()
+            out_pin.copy_(gathered, non_blocking=True)
+            stream.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+        barrier()
+        times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(times[0]), float(times[1])
+    if rank == 0:
+        peaks = measured_peaks()
+        img_s = total * args.steps / (ms * 1e-3)
+        macs = g.macs() / nb
+        # activation traffic with fused epilogues: every tensor a device step reads or writes, once
+        act_bytes = 0
+        for kind, payload in run.steps:
+            ops = [o for o in (payload if isinstance(payload, tuple) else (payload,)) if o is not None]
+            if kind in ("SLICE", "RESHAPE"):
+                continue
+            names = {ops[0].inputs[0], ops[-1].outputs[0]}
+            if kind == "RESIDUAL_JOIN":
+                names.add(ops[1].inputs[0])
+            for nme in names:
+                dt, shape = g.meta[nme]
+                act_bytes += int(np.prod(shape)) * (4 if dt == tb.DType.INT32 else 1)
+        weight_bytes = sum(int(a.nbytes) for a in g.consts.values())
+        bytes_per_step = (act_bytes + weight_bytes) * world
+        cpu = {"value": None, "unit": "images/s", "cores": None, "kind": "port", "sample": "skipped"}
+        if not args.skip_cpu_baseline:
+            from oracle import oracle as orc
+            from tests import graph_oracle
+            g1 = G.resnet50_int8(2)
+            t0 = time.perf_counter()
+            graph_oracle.evaluate(g1, {"input": G.synthetic_images(2)}, nthreads=orc.num_procs())
+            dt = time.perf_counter() - t0
+            cpu = {"value": 2 / dt, "unit": "images/s", "cores": orc.num_procs(), "kind": "port",
+                   "sample": "2 images, node by node (%.1f s)" % dt}
+        print(json.dumps({
+            "metric": "int8 ResNet-50-shaped TOSA graph throughput, batch %d split by N" % total, "value": img_s,
+            "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "resnet50_int8_graph_batch%d" % total, "images_per_gpu": nb,
+                       "device_steps_per_eval": len(run.steps), "kernel_launches_per_eval": launches_per_eval,
+                       "replay": "CUDA graph", "gather": "NCCL all_gather of int32 logits" if world > 1 else "none",
+                       "l2": "activations of one evaluation exceed L2, no flush"},
+            "clocks": clocks,
+            "e2e": {"value": total * args.e2e_steps / (e2e_ms * 1e-3) if args.e2e_steps else None, "unit": "images/s",
+                    "h2d_bytes_per_step": int(x_pin.numel()), "d2h_bytes_per_step": int(out_pin.numel() * 4),
+                    "steps": args.e2e_steps},
+            "gpu_launches": int(launches_per_eval * args.steps),
+            "roofline": {"bound": "hbm", "achieved": bytes_per_step * args.steps / (ms * 1e-3) / 1e9, "peak": peaks["hbm"] * world,
+                         "unit": "GB/s", "frac": bytes_per_step * args.steps / (ms * 1e-3) / 1e9 / (peaks["hbm"] * world),
+                         "traffic": None, "algorithmic_bytes_per_step": bytes_per_step,
+                         "tensor_TOPS": 2.0 * macs * total * args.steps / (ms * 1e-3) / 1e12,
+                         "tensor_frac_of_2x_bf16": 2.0 * macs * total * args.steps / (ms * 1e-3) / 1e12 / (2 * peaks["bf16_burst"] * world)},
+            "cpu_baseline": cpu,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="matmul", choices=["matmul", "resnet50"])
+    ap.add_argument("--graph-batch", type=int, default=GRAPH_BATCH)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -173,6 +311,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
 
+    if args.workload == "resnet50" and args.impl != "reference":
+        run_resnet50(args, rank, local_rank, world)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return

@@ -802,6 +802,75 @@ extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, 
         }
     }
 
+    // ---- few-channel int8 convolutions (IC <= 8, e.g. the RGB stem): window re-layout + tensor cores
+    if (ctx->policy == 0 && int_path && weight_zp == 0 && tc_rescale_ok && input->contiguous && IC <= 8 &&
+        (IC % 32) != 0 && dilation[0] == 1 && dilation[1] == 1 && KW >= 2)
+    {
+        const int Cp  = (stride[1] % 2 == 0) ? 8 : 16;
+        int win       = KW * Cp;
+        win           = win <= 32 ? 32 : win <= 64 ? 64 : win <= 128 ? 128 : 0;
+        const int Hp  = IH + pad[0] + pad[1];
+        const int Wp0 = IW + pad[2] + pad[3];
+        // every window [ox*stride*Cp, +win) must stay inside its row
+        const int Wp  = std::max(Wp0, ((OW - 1) * stride[1] * Cp + win + Cp - 1) / Cp);
+        const int OCpad = (OC + 255) / 256 * 256;
+        const size_t xp_bytes = ((size_t)N * Hp * Wp * Cp + 255) & ~(size_t)255;
+        const size_t wr_bytes = ((size_t)OC * KH * win + 255) & ~(size_t)255;
+        const size_t prefix_elems = ((size_t)(KH + 1) * 2 * OC + 3) & ~(size_t)3;
+        const size_t tab_bytes = (prefix_elems + 2 * (size_t)OCpad) * sizeof(int32_t) + OCpad + 64;
+        if (win != 0 && xp_bytes + wr_bytes + tab_bytes <= ((size_t)8 << 30))
+        {
+            TcProblem q;
+            memset(&q, 0, sizeof(q));
+            q.in_dtype = TB200_INT8;
+            q.N = N; q.IH = Hp; q.IW = OW; q.IC = win;
+            q.a_stride_w = (int64_t)stride[1] * Cp; q.a_stride_h = (int64_t)Wp * Cp; q.a_stride_n = (int64_t)Hp * Wp * Cp;
+            q.OH = OH; q.OW = OW; q.OC = OC;
+            q.KH = KH; q.KW = 1;
+            q.stride_y = stride[0]; q.stride_x = 1; q.dil_y = 1; q.dil_x = 1;
+            q.out = output->data;
+            q.epi = TC_EPI_I32;
+            fill_tc_epilogue(&q, epi, output->dtype);
+            st = ensure_scratch(ctx, xp_bytes + wr_bytes + tab_bytes);
+            if (st != TB200_OK)
+                return st;
+            int8_t* xp = reinterpret_cast<int8_t*>(ctx->scratch);
+            int8_t* wr = xp + xp_bytes;
+            q.a = xp;
+            q.b = wr;
+            std::string why;
+            if (tc_gemm_supported(q, &why))
+            {
+                int32_t* prefix   = reinterpret_cast<int32_t*>(wr + wr_bytes);
+                int32_t* corr     = prefix + prefix_elems;
+                int32_t* mult_pad = corr + OCpad;
+                int8_t* shift_pad = reinterpret_cast<int8_t*>(mult_pad + OCpad);
+                const int block   = 256;
+                pad_expand_i8_kernel<<<grid_for(ctx, (int64_t)N * Hp * Wp, block), block, 0, ctx->stream>>>(
+                    reinterpret_cast<const int8_t*>(input->data), xp, N, IH, IW, IC, Hp, Wp, Cp, pad[0], pad[2], input_zp);
+                repack_weights_smallc_kernel<<<(int)(((int64_t)OC * KH * win + block - 1) / block), block, 0, ctx->stream>>>(
+                    reinterpret_cast<const int8_t*>(weight->data), wr, OC, KH, KW, IC, Cp, win);
+                // the border holds the zero point, so every tap is in scope and one correction row serves all pixels
+                conv_epilogue_tables_kernel<<<(OCpad * 32 + 127) / 128, 128, 0, ctx->stream>>>(
+                    wr, reinterpret_cast<const int32_t*>(bias->data), bias->shape[0], OC, OCpad, KH, 1, win, input_zp, 0,
+                    epi.has_rescale ? reinterpret_cast<const int32_t*>(epi.rs.mult) : nullptr,
+                    epi.has_rescale ? epi.rs.shift : nullptr, epi.rs.per_channel, prefix, corr,
+                    epi.has_rescale ? mult_pad : nullptr, shift_pad);
+                st = post_launch(ctx, "conv_window_relayout", 3);
+                if (st != TB200_OK)
+                    return st;
+                q.corr        = corr;
+                q.corr_stride = OCpad;
+                q.mult_pad    = mult_pad;
+                q.shift_pad   = shift_pad;
+                st = tc_gemm_launch(ctx, q);
+                // a driver that refuses the overlapping-window tensor map sends this shape to the CUDA-core kernel
+                if (!(st == TB200_INTERNAL && ctx->err.find("rejected") != std::string::npos))
+                    return st;
+            }
+        }
+    }
+
     // ---- CUDA-core path
     ConvDev d;
     memset(&d, 0, sizeof(d));

@@ -992,6 +992,59 @@ __global__ void conv_epilogue_tables_kernel(const int8_t* __restrict__ w, const 
     }
 }
 
+// Few-channel convolutions (an RGB stem) on the tensor cores.  The image is copied once into a border-padded,
+// channel-padded buffer  xp[N][Hp][Wp][Cp]  (border and slack filled with the input zero point, pad channels with
+// anything: their weights are zero).  With Cp * stride_x a multiple of 16 bytes, the KW taps of one filter row are
+// one contiguous window of `win` bytes per output pixel, so the convolution becomes a KH-tap implicit GEMM whose
+// "channel" run is that window.
+__global__ void pad_expand_i8_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ xp, int N, int IH, int IW, int IC,
+                                     int Hp, int Wp, int Cp, int pad_t, int pad_l, int32_t zp)
+{
+    const int64_t total = (int64_t)N * Hp * Wp;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int xpix = (int)(i % Wp);
+        int64_t r      = i / Wp;
+        const int ypix = (int)(r % Hp);
+        const int n    = (int)(r / Hp);
+        const int y = ypix - pad_t, x = xpix - pad_l;
+        const bool inside = (y >= 0) && (y < IH) && (x >= 0) && (x < IW);
+        const int8_t* src = in + (((int64_t)n * IH + y) * IW + x) * IC;
+        int8_t v[16];
+#pragma unroll
+        for (int c = 0; c < 16; c++)
+            v[c] = (int8_t)zp;
+        if (inside)
+            for (int c = 0; c < IC; c++)
+                v[c] = src[c];
+        int8_t* dst = xp + i * Cp;
+        if (Cp == 8)
+            *reinterpret_cast<int2*>(dst) = *reinterpret_cast<int2*>(v);
+        else
+            *reinterpret_cast<int4*>(dst) = *reinterpret_cast<int4*>(v);
+    }
+}
+
+// weights OHWI [OC][KH][KW][IC] -> [OC][KH][win] with win >= KW*Cp, element (kx*Cp + c) = w[oc][ky][kx][c], rest 0
+__global__ void repack_weights_smallc_kernel(const int8_t* __restrict__ w, int8_t* __restrict__ wr, int OC, int KH, int KW,
+                                             int IC, int Cp, int win)
+{
+    const int64_t total = (int64_t)OC * KH * win;
+    const int64_t i     = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total)
+        return;
+    const int k  = (int)(i % win);
+    const int64_t r = i / win;
+    const int ky = (int)(r % KH);
+    const int oc = (int)(r / KH);
+    const int kx = k / Cp, c = k % Cp;
+    int8_t v = 0;
+    if (kx < KW && c < IC)
+        v = w[(((int64_t)oc * KH + ky) * KW + kx) * IC + c];
+    wr[i] = v;
+}
+
 // fp bias widened to fp32 and zero padded for the tensor-core epilogue (bias_n == 1 broadcasts)
 template <typename T>
 __global__ void bias_to_f32_kernel(const T* __restrict__ bias, int bias_n, int OC, float* __restrict__ out, int OCpad)

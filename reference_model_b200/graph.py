@@ -219,9 +219,11 @@ class DeviceRunner:
     """Evaluates a Graph on one tb200 context.  Constants are uploaded once (they are CONST node outputs in the
     reference, decoded at graph initialisation); activations are allocated once and reused across runs."""
 
-    def __init__(self, ctx, graph, fused=True):
+    def __init__(self, ctx, graph, fused=True, external=None):
+        """external: optional name -> Tensor for tensors the caller owns (e.g. an output wrapped over a buffer that a
+        collective reads)."""
         self.ctx, self.graph = ctx, graph
-        self.t = {}
+        self.t = dict(external or {})
         for name_, arr in graph.consts.items():
             self.t[name_] = ctx.from_numpy(arr, graph.meta[name_][0])
         self.steps = fuse(graph) if fused else [(op.kind, op) for op in graph.ops]

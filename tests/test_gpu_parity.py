@@ -296,6 +296,33 @@ def test_tensor_core_conv_int8(ctx, case):
     assert kernel == "conv2d_direct" and np.array_equal(out, exp)
 
 
+FEW_CHANNEL_CASES = [
+    # N, IH, IW, IC, OC, KH, KW, stride, pad, in_zp
+    (2, 32, 32, 3, 64, 7, 7, 2, (3, 2, 3, 2), -128),
+    (1, 17, 23, 3, 16, 3, 3, 1, (1, 1, 1, 1), 9),
+    (2, 20, 20, 4, 24, 5, 5, 1, (2, 2, 2, 2), -7),
+    (1, 15, 15, 1, 8, 3, 3, 2, (1, 1, 1, 1), 0),
+    (1, 12, 40, 8, 40, 3, 4, 2, (1, 0, 2, 0), 33),
+]
+
+
+@pytest.mark.parametrize("case", FEW_CHANNEL_CASES)
+def test_few_channel_conv_int8(ctx, case):
+    """Convolutions with up to 8 input channels (an RGB stem) take the window re-layout + tensor-core path."""
+    N, IH, IW, IC, OC, KH, KW, s, pad, izp = case
+    r = util.rng(150 + FEW_CHANNEL_CASES.index(case))
+    x, w, b = util.conv_int8_case(r, N, IH, IW, IC, OC, KH, KW, bias_range=1 << 16)
+    args = (list(pad), [s, s], [1, 1], izp, 0)
+    _, exp = oracle_conv_i8(x, w, b, *args)
+    st, out, kernel = run_conv_i8(ctx, x, w, b, *args)
+    assert st == tb.Status.OK and np.array_equal(out, exp), kernel
+    mult, shift = util.rescale_params(r, OC)
+    resc = (mult, np.maximum(shift, 33).astype(np.int8), -128, "DOUBLE_ROUND")
+    est, exp = oracle_conv_i8(x, w, b, *args, rescale=resc, clamp=(-100, 100))
+    st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=(-100, 100))
+    assert st == est == tb.Status.OK and np.array_equal(out, exp), kernel
+
+
 def test_rescale_require_reports_unpredictable(ctx):
     # shift 30 with |acc| >= 2^29 violates apply_scale_32's range check (quant_util.h:53-62)
     x = np.full((1, 4, 4, 64), 127, np.int8)
