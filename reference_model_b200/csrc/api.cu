@@ -1363,6 +1363,34 @@ extern "C" tb200_status tb200_residual_add(tb200_ctx* ctx, const tb200_tensor* a
                            reinterpret_cast<uintptr_t>(output->data)) & 15) == 0;
     const bool pc = a_attr->per_channel || b_attr->per_channel || out_attr->per_channel;
     const int block = 256;
+    const bool simple = !pc && a_attr->scale32 && b_attr->scale32 && out_attr->scale32 &&
+                        a_attr->rounding_mode != TB200_INEXACT_ROUND && b_attr->rounding_mode != TB200_INEXACT_ROUND &&
+                        out_attr->rounding_mode != TB200_INEXACT_ROUND && !a_attr->input_unsigned &&
+                        !b_attr->input_unsigned && !out_attr->output_unsigned && ctx->policy == 0;
+    if (simple && aligned && n % 16 == 0)
+    {
+        ResidualFast f;
+        auto leg = [](const tb200_rescale_attr* at) {
+            ResidualLeg l;
+            l.mult         = reinterpret_cast<const int32_t*>(at->multiplier->data);
+            l.shift        = reinterpret_cast<const int8_t*>(at->shift->data);
+            l.zp_in        = (int32_t)(int8_t)at->input_zp;
+            l.zp_out       = (int32_t)(int8_t)at->output_zp;
+            l.double_round = at->rounding_mode == TB200_DOUBLE_ROUND;
+            return l;
+        };
+        f.a = leg(a_attr);
+        f.b = leg(b_attr);
+        f.o = leg(out_attr);
+        f.o.zp_in = 0;    // INT32 input of the last leg has no zero point (checked above)
+        // clip to int8, then CLAMP: one clip to [lo, hi]
+        f.lo = has_clamp ? std::min(std::max(-128, clamp_min), clamp_max) : -128;
+        f.hi = has_clamp ? std::min(std::max(127, clamp_min), clamp_max) : 127;
+        residual_add_i8_fast_kernel<<<grid_for(ctx, n / 16, block), block, 0, ctx->stream>>>(
+            reinterpret_cast<const int8_t*>(a->data), reinterpret_cast<const int8_t*>(b->data),
+            reinterpret_cast<int8_t*>(output->data), n / 16, f, ctx->d_status);
+        return post_launch(ctx, "residual_add_i8_fast");
+    }
     if (aligned && n % 16 == 0 && (!pc || C % 16 == 0))
         residual_add_i8_kernel<16><<<grid_for(ctx, n / 16, block), block, 0, ctx->stream>>>(
             reinterpret_cast<const int8_t*>(a->data), reinterpret_cast<const int8_t*>(b->data),

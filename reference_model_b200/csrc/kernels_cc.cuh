@@ -187,6 +187,119 @@ __global__ void residual_add_i8_kernel(const int8_t* __restrict__ a, const int8_
         atomicOr(status, TB200_DEV_UNPREDICTABLE);
 }
 
+// Fast residual join for the common case: per-tensor scale32 RESCALEs whose int8 -> int32 legs cannot violate any
+// REQUIRE (checked on the host from the operands' ranges).  16 int8 values per thread, 64-bit products split into
+// words so every shift is a 32-bit operation.
+struct Scale32Fast
+{
+    int32_t mult, shift;
+    int32_t rpos_lo, rpos_hi, rneg_lo, rneg_hi;    // rounding constant for v >= 0 / v < 0
+    int32_t zp_in, zp_out;
+};
+
+__device__ __forceinline__ int32_t scale32_fast(int32_t v, const Scale32Fast& c, bool& narrow_overflow)
+{
+    const int64_t rpos = ((int64_t)c.rpos_hi << 32) | (uint32_t)c.rpos_lo;
+    const int64_t rneg = ((int64_t)c.rneg_hi << 32) | (uint32_t)c.rneg_lo;
+    const int64_t prod = (int64_t)v * (int64_t)c.mult + (v >= 0 ? rpos : rneg);
+    const uint32_t plo = (uint32_t)prod;
+    const int32_t phi  = (int32_t)(prod >> 32);
+    if (c.shift >= 32)
+        return phi >> (c.shift - 32);
+    const int32_t res = (int32_t)__funnelshift_r(plo, (uint32_t)phi, c.shift);
+    narrow_overflow |= (phi >> c.shift) != (res >> 31);
+    return res;
+}
+
+// per-tensor leg described by device pointers to its multiplier / shift (read once per thread)
+struct ResidualLeg
+{
+    const int32_t* mult;
+    const int8_t* shift;
+    int32_t zp_in, zp_out, double_round;
+};
+
+struct ResidualFast
+{
+    ResidualLeg a, b, o;
+    int32_t lo, hi;    // int8 clip folded with the CLAMP bounds
+};
+
+// Builds the constants of one leg; *vlim receives the largest |v| apply_scale_32 accepts (-1: invalid operands)
+__device__ __forceinline__ Scale32Fast make_scale32_fast(const ResidualLeg& l, int32_t* vlim)
+{
+    Scale32Fast c;
+    const int32_t m = __ldg(l.mult);
+    const int32_t s = (int32_t)__ldg(l.shift);
+    const bool valid = (m >= 0) && (s >= 2) && (s <= 62);
+    c.mult  = m;
+    c.shift = valid ? s : 2;
+    const int64_t half = (int64_t)1 << (c.shift - 1);
+    int64_t rpos = half, rneg = half;
+    if (l.double_round && c.shift > 31)
+    {
+        rpos += (int64_t)1 << 30;
+        rneg -= (int64_t)1 << 30;
+    }
+    c.rpos_lo = (int32_t)(uint32_t)(rpos & 0xffffffffLL);
+    c.rpos_hi = (int32_t)(rpos >> 32);
+    c.rneg_lo = (int32_t)(uint32_t)(rneg & 0xffffffffLL);
+    c.rneg_hi = (int32_t)(rneg >> 32);
+    c.zp_in   = l.zp_in;
+    c.zp_out  = l.zp_out;
+    *vlim     = !valid ? -1 : (c.shift - 1 >= 31 ? 2147483647 : (int32_t)(half - 1));
+    return c;
+}
+
+__global__ void __launch_bounds__(256) residual_add_i8_fast_kernel(const int8_t* __restrict__ a, const int8_t* __restrict__ b,
+                                                                   int8_t* __restrict__ out, int64_t n16, ResidualFast r,
+                                                                   int* status)
+{
+    int32_t vlim_a, vlim_b, vlim_o;
+    const Scale32Fast ca = make_scale32_fast(r.a, &vlim_a);
+    const Scale32Fast cb = make_scale32_fast(r.b, &vlim_b);
+    const Scale32Fast co = make_scale32_fast(r.o, &vlim_o);
+    bool bad = false;
+    const int32_t zp_add_hi = co.zp_out > 0 ? 2147483647 - co.zp_out : 2147483647;
+    const int32_t zp_add_lo = co.zp_out < 0 ? (int32_t)(-2147483647 - 1 - co.zp_out) : (-2147483647 - 1);
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += step)
+    {
+        const int4 va = __ldg(reinterpret_cast<const int4*>(a) + i);
+        const int4 vb = __ldg(reinterpret_cast<const int4*>(b) + i);
+        const int wa[4] = { va.x, va.y, va.z, va.w }, wb[4] = { vb.x, vb.y, vb.z, vb.w };
+        uint32_t wo[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+        {
+            uint32_t packed = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+            {
+                const int32_t xa = (int32_t)(int8_t)((wa[q] >> (8 * j)) & 0xff) - ca.zp_in;
+                const int32_t xb = (int32_t)(int8_t)((wb[q] >> (8 * j)) & 0xff) - cb.zp_in;
+                bool ov = (xa > vlim_a) || (xa < ~vlim_a) || (xb > vlim_b) || (xb < ~vlim_b);
+                // legs a and b add output_zp 0 (INT32 outputs cannot carry a zero point)
+                const int32_t ya  = scale32_fast(xa, ca, ov);
+                const int32_t yb  = scale32_fast(xb, cb, ov);
+                const int32_t sum = (int32_t)((uint32_t)ya + (uint32_t)yb);
+                // INT32 ADD: the mathematical sum must fit (signs equal and result sign differs = overflow)
+                ov |= ((ya ^ sum) & (yb ^ sum)) < 0;
+                const int32_t res = scale32_fast(sum, co, ov);
+                bad |= ov || (sum > vlim_o) || (sum < ~vlim_o) || (res > zp_add_hi) || (res < zp_add_lo);
+                int32_t z = res + co.zp_out;
+                z = max(z, r.lo);
+                z = min(z, r.hi);
+                packed |= (uint32_t)(z & 0xff) << (8 * j);
+            }
+            wo[q] = packed;
+        }
+        reinterpret_cast<uint4*>(out)[i] = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+    }
+    if (bad)
+        atomicOr(status, TB200_DEV_UNPREDICTABLE);
+}
+
 // ------------------------------------------------------------------------------------------------ CLAMP
 template <typename T>
 __global__ void clamp_int_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t n, int32_t lo, int32_t hi)

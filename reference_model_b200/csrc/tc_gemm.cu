@@ -29,7 +29,8 @@ namespace
 
 constexpr int kMaxStages   = 8;
 constexpr int kTileM       = 128;
-constexpr int kNumThreads  = 192;
+constexpr int kNumThreads  = 320;    // TMA warp, MMA warp, 8 epilogue warps
+constexpr int kEpiThreads  = 256;
 constexpr long long kWaitLimitCycles = 4000000000LL;    // about two seconds of SM clock
 
 struct TcKernelParams
@@ -68,6 +69,7 @@ struct TcKernelParams
     const int8_t* shift_pad;
     int double_round;
     int32_t out_zp, clamp_lo, clamp_hi;
+    int32_t zp_add_lo, zp_add_hi;    // range of scaled values for which value + out_zp stays inside int32
     float clamp_lo_f, clamp_hi_f;
     int has_clamp;
     int debug;    // diagnostic bit mask (TB200_TC_DEBUG): 1 skip epilogue memory work, 2 skip MMA issue, 4 skip loads
@@ -100,7 +102,7 @@ __device__ __forceinline__ uint32_t pack4_i8(int a, int b, int c, int d)
 }
 
 template <int EPI>
-__global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_constant__ TcKernelParams p)
+__global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_constant__ TcKernelParams p)
 {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[kMaxStages];
@@ -129,7 +131,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
         for (int a = 0; a < 2; a++)
         {
             ptx::mbar_init(ptx::smem_u32(&bar_tmem_full[a]), 1);
-            ptx::mbar_init(ptx::smem_u32(&bar_tmem_empty[a]), 128);
+            ptx::mbar_init(ptx::smem_u32(&bar_tmem_empty[a]), kEpiThreads);
         }
         abort_flag = 0;
         ptx::fence_barrier_init();
@@ -295,6 +297,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
     {
         // ------------------------------------------------------------------ epilogue warps
         const int quarter = warp & 3;    // TMEM lane quarter this warp may read
+        const int half    = (warp - 2) >> 2;    // two warps share a quarter: even / odd 32-column chunks
         const int row     = quarter * 32 + lane;
         const int xx      = row % p.BW;
         const int yy      = (row / p.BW) % p.BH;
@@ -310,8 +313,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
             if (EPI == TC_EPI_RESCALE && cols_loaded_for != t.col0)
             {
                 // (re)build the per-column constants; the named barrier keeps the 128 epilogue threads in step
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                for (int c = (int)threadIdx.x - 64; c < p.block_n; c += 128)
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                for (int c = (int)threadIdx.x - 64; c < p.block_n; c += kEpiThreads)
                 {
                     const int32_t m = __ldg(p.mult_pad + t.col0 + c);
                     const int32_t s = (int32_t)__ldg(p.shift_pad + t.col0 + c);
@@ -331,7 +334,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
                     *reinterpret_cast<int4*>(&epi_cols[c][0]) = lo4;
                     *reinterpret_cast<int4*>(&epi_cols[c][4]) = hi4;
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
                 cols_loaded_for = t.col0;
             }
             // After a wait has given up this warp only keeps visiting the named barrier above (the other epilogue
@@ -387,7 +390,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
 
             const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n);
             const int ncol_chunks = p.block_n / 32;
-            for (int c = 0; c < ncol_chunks; c++)
+            for (int c = half; c < ncol_chunks; c += 2)
             {
                 uint32_t v[32];
                 ptx::tmem_ld_32x32b_x32(taddr_row + (uint32_t)(c * 32), v);
@@ -442,19 +445,26 @@ __global__ void __launch_bounds__(kNumThreads, 1) tc_gemm_kernel(const __grid_co
 #pragma unroll
                     for (int i = 0; i < 32; i++)
                     {
-                        // QuantUtil::apply_scale_32 with the per-column constants prepared above
+                        // QuantUtil::apply_scale_32 with the per-column constants prepared above; the 64-bit
+                        // product is kept as two words so that the shift is one 32-bit operation either way
                         const int4 c0 = *reinterpret_cast<const int4*>(&epi_cols[c * 32 + i][0]);
                         const int4 c1 = *reinterpret_cast<const int4*>(&epi_cols[c * 32 + i][4]);
                         const int32_t a = (int32_t)v[i];
                         const int64_t rpos = ((int64_t)c0.w << 32) | (uint32_t)c0.z;
                         const int64_t rneg = ((int64_t)c1.y << 32) | (uint32_t)c1.x;
                         const int64_t prod = (int64_t)a * (int64_t)c0.x + (a >= 0 ? rpos : rneg);
-                        const int64_t res  = prod >> c0.y;
-                        bool b = (a > c1.z) || (a < ~c1.z) || (res != (int64_t)(int32_t)res);
-                        int64_t z = res + (int64_t)p.out_zp;
-                        b |= (z > 2147483647LL) || (z < -2147483648LL);
-                        z = z < (int64_t)p.clamp_lo ? (int64_t)p.clamp_lo : z;
-                        z = z > (int64_t)p.clamp_hi ? (int64_t)p.clamp_hi : z;
+                        const uint32_t plo = (uint32_t)prod;
+                        const int32_t phi  = (int32_t)(prod >> 32);
+                        const int32_t sh   = c0.y;
+                        const bool wide    = sh >= 32;
+                        const int32_t res  = wide ? (phi >> (sh - 32)) : (int32_t)__funnelshift_r(plo, (uint32_t)phi, sh);
+                        // the scaled value must fit int32: automatic for shifts of 32 and more
+                        bool b = (a > c1.z) || (a < ~c1.z) || (!wide && ((phi >> sh) != (res >> 31)));
+                        // adding the output zero point must stay inside int32 as well
+                        b |= (res > p.zp_add_hi) || (res < p.zp_add_lo);
+                        int32_t z = res + p.out_zp;
+                        z = max(z, p.clamp_lo);
+                        z = min(z, p.clamp_hi);
                         v[i] = b ? 0u : (uint32_t)(int32_t)z;
                         bad |= b && (i < nvalid);
                     }
@@ -923,6 +933,8 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
     k.shift_pad    = q.shift_pad;
     k.double_round = q.double_round;
     k.out_zp       = q.out_zp;
+    k.zp_add_hi    = q.out_zp > 0 ? 2147483647 - q.out_zp : 2147483647;
+    k.zp_add_lo    = q.out_zp < 0 ? (int32_t)(-2147483647 - 1 - q.out_zp) : (-2147483647 - 1);
     k.clamp_lo     = q.clamp_lo;
     k.clamp_hi     = q.clamp_hi;
     k.clamp_lo_f   = q.clamp_lo_f;

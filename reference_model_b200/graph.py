@@ -171,6 +171,16 @@ def synthetic_images(batch, seed=20251125 + 5, image=224):
                                                          endpoint=True).astype(np.int8)
 
 
+def shard_range(total, rank, world):
+    """Images [lo, hi) of a batch of `total` that rank `rank` of `world` evaluates: the batch dimension is the only
+    sharded axis (no operator of the graph reduces over it), so shards are contiguous, equal blocks and the gathered
+    logits are the concatenation in rank order."""
+    if total % world != 0:
+        raise ValueError("batch %d does not split evenly over %d ranks" % (total, world))
+    nb = total // world
+    return rank * nb, (rank + 1) * nb
+
+
 # ------------------------------------------------------------------------------------------------ fuser
 def fuse(graph):
     """Returns a list of device steps.  A step is (kind, op-or-ops): fused convolutions carry their RESCALE / CLAMP,
@@ -248,9 +258,22 @@ class DeviceRunner:
                               a["rounding"], a["per_channel"], a.get("input_unsigned", False),
                               a.get("output_unsigned", False))
 
-    def _eval(self):
+    def profile(self, sync_time):
+        """Eager evaluation with a device synchronisation after every step.  `sync_time()` must synchronise and return
+        a host timestamp in seconds.  Returns [(step kind, output tensor, kernel family, milliseconds)]."""
+        rows = []
+        for step in self.steps:
+            t0 = sync_time()
+            self._eval([step])
+            t1 = sync_time()
+            payload = step[1]
+            last = [o for o in (payload if isinstance(payload, tuple) else (payload,)) if o is not None][-1]
+            rows.append((step[0], last.outputs[0], self.ctx.last_kernel(), (t1 - t0) * 1e3))
+        return rows
+
+    def _eval(self, steps=None):
         ctx, t = self.ctx, self.t
-        for kind, p in self.steps:
+        for kind, p in (self.steps if steps is None else steps):
             if kind == "CONV_RESCALE_CLAMP":
                 conv, r, c = p
                 epi = tb.Epilogue(self._rescale_attr(r), (c.attr["min_val"], c.attr["max_val"]) if c else None)

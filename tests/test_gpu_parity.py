@@ -657,11 +657,31 @@ def test_residual_add(ctx):
         ta, tbb, to = ctx.from_numpy(a), ctx.from_numpy(b), ctx.empty(I8, shape)
         consts = [ctx.from_numpy(np.asarray(v, np.int32)) for v in (ma, mb, mo)] + \
                  [ctx.from_numpy(np.asarray(v, np.int8)) for v in (sa, sb, so)]
-        ctx.residual_add(ta, tb.RescaleAttr(consts[0], consts[3], -128, 0), tbb, tb.RescaleAttr(consts[1], consts[4], 3, 0),
-                         tb.RescaleAttr(consts[2], consts[5], 0, -128, rounding="DOUBLE_ROUND"), to, clamp=(-128, 127))
-        st, out = to.download()
-        assert st == est == tb.Status.OK and np.array_equal(out.astype(np.int32), eo)
+        for policy, kernel in ((0, "residual_add_i8_fast"), (1, "residual_add_i8")):
+            if policy == 0 and a.size % 16:
+                kernel = "residual_add_i8"
+            old = ctx.set_kernel_policy(policy)
+            ctx.residual_add(ta, tb.RescaleAttr(consts[0], consts[3], -128, 0), tbb,
+                             tb.RescaleAttr(consts[1], consts[4], 3, 0),
+                             tb.RescaleAttr(consts[2], consts[5], 0, -128, rounding="DOUBLE_ROUND"), to, clamp=(-128, 127))
+            assert ctx.last_kernel() == kernel
+            ctx.set_kernel_policy(old)
+            st, out = to.download()
+            assert st == est == tb.Status.OK and np.array_equal(out.astype(np.int32), eo)
         _free(ta, tbb, to, *consts)
+    # REQUIRE of the first leg: shift 8 accepts |v| < 128 only, and 127 - (-128) = 255 violates it
+    a = np.full((1, 4, 4, 16), 127, np.int8)
+    ta, to = ctx.from_numpy(a), ctx.empty(I8, a.shape)
+    consts = [ctx.from_numpy(np.asarray([1 << 20], np.int32)), ctx.from_numpy(np.asarray([8], np.int8)),
+              ctx.from_numpy(np.asarray([1 << 30], np.int32)), ctx.from_numpy(np.asarray([40], np.int8))]
+    leg, outleg = tb.RescaleAttr(consts[0], consts[1], -128, 0), tb.RescaleAttr(consts[2], consts[3], 0, 0)
+    assert orc.rescale(a, [1 << 20], [8], False, True, "SINGLE_ROUND", -128, 0, 8, 32)[0] == orc.UNPREDICTABLE
+    for policy in (0, 1):
+        old = ctx.set_kernel_policy(policy)
+        ctx.residual_add(ta, leg, ta, leg, outleg, to)
+        ctx.set_kernel_policy(old)
+        assert to.download(check=False)[0] == tb.Status.UNPREDICTABLE
+    _free(ta, to, *consts)
 
 
 def test_pools(ctx):
