@@ -255,10 +255,37 @@ __global__ void __launch_bounds__(256) residual_add_i8_fast_kernel(const int8_t*
                                                                    int8_t* __restrict__ out, int64_t n16, ResidualFast r,
                                                                    int* status)
 {
-    int32_t vlim_a, vlim_b, vlim_o;
-    const Scale32Fast ca = make_scale32_fast(r.a, &vlim_a);
-    const Scale32Fast cb = make_scale32_fast(r.b, &vlim_b);
+    // The int8 -> int32 legs have only 256 possible inputs each: tabulate them once per block, with their REQUIRE
+    // verdicts, and leave the per-element work to the INT32 ADD and the output leg.
+    __shared__ int32_t lut[2][256];
+    __shared__ int lut_bad[2];
+    int32_t vlim_o;
     const Scale32Fast co = make_scale32_fast(r.o, &vlim_o);
+    if (threadIdx.x < 2)
+        lut_bad[threadIdx.x] = 0;
+    __syncthreads();
+    {
+        int32_t vlim;
+        for (int leg = 0; leg < 2; leg++)
+        {
+            const Scale32Fast c = make_scale32_fast(leg == 0 ? r.a : r.b, &vlim);
+            const int32_t x     = (int32_t)(int8_t)(threadIdx.x ^ 0x80) - c.zp_in;    // table index = raw byte ^ 0x80
+            bool ov             = (x > vlim) || (x < ~vlim);
+            lut[leg][threadIdx.x] = scale32_fast(x, c, ov);
+            if (ov)
+                lut_bad[leg] = 1;
+        }
+    }
+    __syncthreads();
+    // with a bad entry in a table the legs are re-checked per element below (the entry may never be used)
+    const bool recheck = lut_bad[0] || lut_bad[1];
+    int32_t vlim_a = 0, vlim_b = 0;
+    Scale32Fast ca = co, cb = co;
+    if (recheck)
+    {
+        ca = make_scale32_fast(r.a, &vlim_a);
+        cb = make_scale32_fast(r.b, &vlim_b);
+    }
     bool bad = false;
     const int32_t zp_add_hi = co.zp_out > 0 ? 2147483647 - co.zp_out : 2147483647;
     const int32_t zp_add_lo = co.zp_out < 0 ? (int32_t)(-2147483647 - 1 - co.zp_out) : (-2147483647 - 1);
@@ -267,7 +294,10 @@ __global__ void __launch_bounds__(256) residual_add_i8_fast_kernel(const int8_t*
     {
         const int4 va = __ldg(reinterpret_cast<const int4*>(a) + i);
         const int4 vb = __ldg(reinterpret_cast<const int4*>(b) + i);
-        const int wa[4] = { va.x, va.y, va.z, va.w }, wb[4] = { vb.x, vb.y, vb.z, vb.w };
+        const uint32_t wa[4] = { (uint32_t)va.x ^ 0x80808080u, (uint32_t)va.y ^ 0x80808080u, (uint32_t)va.z ^ 0x80808080u,
+                                 (uint32_t)va.w ^ 0x80808080u };
+        const uint32_t wb[4] = { (uint32_t)vb.x ^ 0x80808080u, (uint32_t)vb.y ^ 0x80808080u, (uint32_t)vb.z ^ 0x80808080u,
+                                 (uint32_t)vb.w ^ 0x80808080u };
         uint32_t wo[4];
 #pragma unroll
         for (int q = 0; q < 4; q++)
@@ -276,14 +306,18 @@ __global__ void __launch_bounds__(256) residual_add_i8_fast_kernel(const int8_t*
 #pragma unroll
             for (int j = 0; j < 4; j++)
             {
-                const int32_t xa = (int32_t)(int8_t)((wa[q] >> (8 * j)) & 0xff) - ca.zp_in;
-                const int32_t xb = (int32_t)(int8_t)((wb[q] >> (8 * j)) & 0xff) - cb.zp_in;
-                bool ov = (xa > vlim_a) || (xa < ~vlim_a) || (xb > vlim_b) || (xb < ~vlim_b);
-                // legs a and b add output_zp 0 (INT32 outputs cannot carry a zero point)
-                const int32_t ya  = scale32_fast(xa, ca, ov);
-                const int32_t yb  = scale32_fast(xb, cb, ov);
+                const uint32_t ia = (wa[q] >> (8 * j)) & 0xffu, ib = (wb[q] >> (8 * j)) & 0xffu;
+                const int32_t ya = lut[0][ia], yb = lut[1][ib];
+                bool ov = false;
+                if (recheck)
+                {
+                    const int32_t xa = (int32_t)(int8_t)(ia ^ 0x80) - ca.zp_in, xb = (int32_t)(int8_t)(ib ^ 0x80) - cb.zp_in;
+                    ov = (xa > vlim_a) || (xa < ~vlim_a) || (xb > vlim_b) || (xb < ~vlim_b);
+                    (void)scale32_fast(xa, ca, ov);
+                    (void)scale32_fast(xb, cb, ov);
+                }
                 const int32_t sum = (int32_t)((uint32_t)ya + (uint32_t)yb);
-                // INT32 ADD: the mathematical sum must fit (signs equal and result sign differs = overflow)
+                // INT32 ADD: the mathematical sum must fit (operand signs equal and result sign differs = overflow)
                 ov |= ((ya ^ sum) & (yb ^ sum)) < 0;
                 const int32_t res = scale32_fast(sum, co, ov);
                 bad |= ov || (sum > vlim_o) || (sum < ~vlim_o) || (res > zp_add_hi) || (res < zp_add_lo);

@@ -114,6 +114,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
     // TC_EPI_RESCALE: per-column scaling constants of the current column block, written once per block by the
     // epilogue threads: {multiplier, shift, round(v >= 0) lo/hi, round(v < 0) lo/hi, largest |v| allowed, 0}
     __shared__ __align__(16) int32_t epi_cols[EPI == TC_EPI_RESCALE ? 256 : 1][8];
+    __shared__ int32_t epi_vlim_min;    // smallest per-column value limit of the current column block
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -314,6 +315,9 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             {
                 // (re)build the per-column constants; the named barrier keeps the 128 epilogue threads in step
                 asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (threadIdx.x == 64)
+                    epi_vlim_min = 2147483647;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
                 for (int c = (int)threadIdx.x - 64; c < p.block_n; c += kEpiThreads)
                 {
                     const int32_t m = __ldg(p.mult_pad + t.col0 + c);
@@ -331,6 +335,8 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     const int32_t vlim = !valid ? -1 : (sc - 1 >= 31 ? 2147483647 : (int32_t)(half - 1));
                     int4 lo4 = make_int4(m, sc, (int32_t)(uint32_t)(rpos & 0xffffffffLL), (int32_t)(rpos >> 32));
                     int4 hi4 = make_int4((int32_t)(uint32_t)(rneg & 0xffffffffLL), (int32_t)(rneg >> 32), vlim, 0);
+                    if (t.col0 + c < p.OC)
+                        atomicMin(&epi_vlim_min, vlim);
                     *reinterpret_cast<int4*>(&epi_cols[c][0]) = lo4;
                     *reinterpret_cast<int4*>(&epi_cols[c][4]) = hi4;
                 }
@@ -441,14 +447,41 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                 }
                 else if (EPI == TC_EPI_RESCALE)
                 {
+                    // REQUIRE checks of apply_scale_32.  With multiplier < 2^31, a value inside the accepted range
+                    // -2^(shift-1) <= v < 2^(shift-1) always scales to |result| <= 2^30 + 1, so the "fits int32" checks
+                    // (before and after adding the small output zero point) follow from the range check.  The range
+                    // check itself is done on the largest magnitude of the 32 values against the smallest limit of
+                    // the column block; only when that fails are the columns compared one by one.
                     bool bad = false;
+                    {
+                        int32_t vmax = -2147483647 - 1, vmin = 2147483647;
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                        {
+                            vmax = max(vmax, (int32_t)v[i]);
+                            vmin = min(vmin, (int32_t)v[i]);
+                        }
+                        const int32_t lim = epi_vlim_min;
+                        if (vmax > lim || vmin < ~lim)
+                        {
+                            for (int i = 0; i < nvalid; i++)
+                            {
+                                const int32_t vl = epi_cols[c * 32 + i][6];
+                                int32_t a = 0;
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    a = (j == i) ? (int32_t)v[j] : a;
+                                bad |= (a > vl) || (a < ~vl);
+                            }
+                        }
+                    }
 #pragma unroll
                     for (int i = 0; i < 32; i++)
                     {
-                        // QuantUtil::apply_scale_32 with the per-column constants prepared above; the 64-bit
-                        // product is kept as two words so that the shift is one 32-bit operation either way
+                        // QuantUtil::apply_scale_32 with the per-column constants prepared above; the 64-bit product
+                        // is kept as two words so that the shift is one 32-bit operation either way
                         const int4 c0 = *reinterpret_cast<const int4*>(&epi_cols[c * 32 + i][0]);
-                        const int4 c1 = *reinterpret_cast<const int4*>(&epi_cols[c * 32 + i][4]);
+                        const int2 c1 = *reinterpret_cast<const int2*>(&epi_cols[c * 32 + i][4]);
                         const int32_t a = (int32_t)v[i];
                         const int64_t rpos = ((int64_t)c0.w << 32) | (uint32_t)c0.z;
                         const int64_t rneg = ((int64_t)c1.y << 32) | (uint32_t)c1.x;
@@ -456,17 +489,11 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         const uint32_t plo = (uint32_t)prod;
                         const int32_t phi  = (int32_t)(prod >> 32);
                         const int32_t sh   = c0.y;
-                        const bool wide    = sh >= 32;
-                        const int32_t res  = wide ? (phi >> (sh - 32)) : (int32_t)__funnelshift_r(plo, (uint32_t)phi, sh);
-                        // the scaled value must fit int32: automatic for shifts of 32 and more
-                        bool b = (a > c1.z) || (a < ~c1.z) || (!wide && ((phi >> sh) != (res >> 31)));
-                        // adding the output zero point must stay inside int32 as well
-                        b |= (res > p.zp_add_hi) || (res < p.zp_add_lo);
+                        const int32_t res  = sh >= 32 ? (phi >> (sh - 32)) : (int32_t)__funnelshift_r(plo, (uint32_t)phi, sh);
                         int32_t z = res + p.out_zp;
                         z = max(z, p.clamp_lo);
                         z = min(z, p.clamp_hi);
-                        v[i] = b ? 0u : (uint32_t)(int32_t)z;
-                        bad |= b && (i < nvalid);
+                        v[i] = (uint32_t)z;
                     }
                     if (bad && row_valid)
                         dev_flags |= TB200_DEV_UNPREDICTABLE;
