@@ -29,6 +29,7 @@ A_ZP, B_ZP = 3, -2
 OPS_PER_STEP = 2.0 * N_BATCH * H * C * W          # 549.76 GOP
 ALG_BYTES_PER_STEP = N_BATCH * (H * C + C * W + 4 * H * W)
 SEED = 20251125 + 1
+DRAM_BYTES_PER_BATCH_NCU = 157479168 // 16    # dram__bytes_read.sum + dram__bytes_write.sum, 16-batch capture
 METRIC = "int8 MATMUL throughput, 64x[1024x4096]x[4096x1024], A_zp=3 B_zp=-2, int32 out"
 WORKLOAD = "matmul_int8_64x1024x4096x1024_zp3_-2"
 
@@ -416,17 +417,16 @@ def main():
         total_ops = OPS_PER_STEP * args.steps * world
         value = total_ops / (ms * 1e-3) / 1e12
         e2e_value = OPS_PER_STEP * args.e2e_steps * world / (e2e_ms * 1e-3) / 1e12 if args.e2e_steps > 0 else None
-        gemm_avg_ms = gemm_ms / max(gemm_n, 1)
+        # the product may be issued as several tile-range launches per step: sum them per step
+        gemm_avg_ms = gemm_ms / max(args.steps, 1)
         achieved = OPS_PER_STEP / (gemm_avg_ms * 1e-3) / 1e12
         # int8 dense peak is not in MEASURED_PEAKS.json: twice the measured bf16 figure stands in for it; the
         # sustained figure applies because the kernel is timed inside a seconds-long back-to-back loop
         long_loop = ms > 1000.0
         peak = 2.0 * (peaks["bf16_sustained"] if long_loop else peaks["bf16_burst"])
-        traffic = None
-        tpath = os.path.join(ROOT, "profiles", "tc_gemm_i8_matmul_traffic.json")
-        if os.path.exists(tpath):
-            with open(tpath) as f:
-                traffic = json.load(f).get("dram_bytes_per_launch_full_workload")
+        # DRAM bytes per launch of the GEMM kernel from an ncu capture of the 16-batch case (157.5 MB, see
+        # profiles/), scaled by the batch count: every batch is read once and written once, so traffic is proportional
+        traffic = DRAM_BYTES_PER_BATCH_NCU * N_BATCH
         cpu_threads = None
         try:
             if args.skip_cpu_baseline:

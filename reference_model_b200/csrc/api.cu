@@ -351,6 +351,14 @@ extern "C" tb200_status tb200_ctx_destroy(tb200_ctx* ctx)
         cudaStreamDestroy(ctx->pipe.h2d);
         cudaStreamDestroy(ctx->pipe.d2h);
     }
+    if (ctx->aux_stream)
+    {
+        cudaStreamSynchronize(ctx->aux_stream);
+        cudaEventDestroy(ctx->aux_fork);
+        for (int i = 0; i < 8; i++)
+            cudaEventDestroy(ctx->aux_join[i]);
+        cudaStreamDestroy(ctx->aux_stream);
+    }
     if (ctx->d_status)
         cudaFree(ctx->d_status);
     if (ctx->h_status)
@@ -1078,45 +1086,123 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
         q.out        = output->data;
         q.epi        = int_path ? TC_EPI_I32 : TC_EPI_FLOAT;
         fill_tc_epilogue(&q, epi, output->dtype);
+        // B rows that are not a multiple of 16 bytes cannot be described to TMA: they are copied once into scratch
+        // with a padded pitch (the pad columns lie outside the tensor map and read as zero)
+        const size_t es_in  = dtype_size(a->dtype);
+        const bool pad_b    = ((size_t)W * es_in) % 16 != 0;
+        const int64_t b_ld  = pad_b ? (int64_t)((((size_t)W * es_in + 15) & ~(size_t)15) / es_in) : 0;
+        const size_t padb_bytes = pad_b ? (((size_t)N * C * b_ld * es_in + 255) & ~(size_t)255) : 0;
+        q.b_ld = b_ld;
         std::string why;
         if (tc_gemm_supported(q, &why))
         {
-            if (int_path && (a_zp != 0 || b_zp != 0))
+            const bool need_sums = int_path && (a_zp != 0 || b_zp != 0);
+            const int Wpad       = (W + 255) / 256 * 256;
+            const size_t rows = (size_t)N * H, cols = (size_t)N * Wpad;
+            const size_t sums_bytes = need_sums ? (((rows + 3) & ~(size_t)3) + cols) * sizeof(int32_t) : 0;
+            if (pad_b || need_sums)
             {
-                const int Wpad    = (W + 255) / 256 * 256;
-                const size_t rows = (size_t)N * H, cols = (size_t)N * Wpad;
-                st = ensure_scratch(ctx, (((rows + 3) & ~(size_t)3) + cols) * sizeof(int32_t));
+                st = ensure_scratch(ctx, padb_bytes + sums_bytes);
                 if (st != TB200_OK)
                     return st;
-                int32_t* row_corr = reinterpret_cast<int32_t*>(ctx->scratch);
+            }
+            if (pad_b)
+            {
+                TB200_CUDA_CHECK(ctx, cudaMemcpy2DAsync(ctx->scratch, (size_t)b_ld * es_in, b->data, (size_t)W * es_in,
+                                                        (size_t)W * es_in, (size_t)N * C, cudaMemcpyDeviceToDevice,
+                                                        ctx->stream));
+                q.b = ctx->scratch;
+            }
+            if (need_sums)
+            {
+                int32_t* row_corr = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(ctx->scratch) + padb_bytes);
                 int32_t* col_corr = row_corr + ((rows + 3) & ~(size_t)3);
-                int launches = 0;
                 if (b_zp != 0)
-                {
-                    const int block = 256;
-                    matmul_row_corr_kernel<<<grid_for(ctx, (int64_t)rows * 32, block), block, 0, ctx->stream>>>(
-                        reinterpret_cast<const int8_t*>(a->data), row_corr, (int64_t)rows, C, a_zp, b_zp);
                     q.row_corr = row_corr;
-                    launches++;
-                }
                 if (a_zp != 0)
                 {
-                    TB200_CUDA_CHECK(ctx, cudaMemsetAsync(col_corr, 0, cols * sizeof(int32_t), ctx->stream));
-                    const int xblocks = (W + 511) / 512;
-                    int ksplit        = std::max(1, std::min((C + 63) / 64, (4 * ctx->num_sms) / std::max(1, xblocks * N)));
-                    const int kper    = ((C + ksplit - 1) / ksplit + 7) / 8 * 8;
-                    ksplit            = (C + kper - 1) / kper;
-                    dim3 grid(xblocks, ksplit, N);
-                    matmul_col_corr_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const int8_t*>(b->data),
-                                                                         col_corr, C, W, Wpad, kper, a_zp);
                     q.corr         = col_corr;
                     q.corr_stride  = Wpad;
                     q.corr_ystride = Wpad;
-                    launches++;
                 }
-                st = post_launch(ctx, "matmul_zp_sums", launches);
-                if (st != TB200_OK)
-                    return st;
+                // zero-point sums of batches [lo, hi) on `stream`
+                auto launch_sums = [&](cudaStream_t stream, int lo, int hi) -> tb200_status {
+                    const int nb  = hi - lo;
+                    int launches  = 0;
+                    if (b_zp != 0)
+                    {
+                        const int block = 256;
+                        matmul_row_corr_kernel<<<grid_for(ctx, (int64_t)nb * H * 32, block), block, 0, stream>>>(
+                            reinterpret_cast<const int8_t*>(a->data) + (size_t)lo * H * C, row_corr + (size_t)lo * H,
+                            (int64_t)nb * H, C, a_zp, b_zp);
+                        launches++;
+                    }
+                    if (a_zp != 0)
+                    {
+                        TB200_CUDA_CHECK(ctx, cudaMemsetAsync(col_corr + (size_t)lo * Wpad, 0,
+                                                              (size_t)nb * Wpad * sizeof(int32_t), stream));
+                        const int xblocks = (W + 511) / 512;
+                        int ksplit     = std::max(1, std::min((C + 63) / 64, (4 * ctx->num_sms) / std::max(1, xblocks * nb)));
+                        const int kper = ((C + ksplit - 1) / ksplit + 7) / 8 * 8;
+                        ksplit         = (C + kper - 1) / kper;
+                        dim3 grid(xblocks, ksplit, nb);
+                        matmul_col_corr_kernel<<<grid, 256, 0, stream>>>(
+                            reinterpret_cast<const int8_t*>(b->data) + (size_t)lo * C * W, col_corr + (size_t)lo * Wpad, C, W,
+                            Wpad, kper, a_zp);
+                        launches++;
+                    }
+                    return post_launch(ctx, "matmul_zp_sums", launches);
+                };
+                // Large batched products: the sums of later batches run on a second stream beside the GEMM of earlier
+                // ones.  The GEMM is cut at whole waves of tiles (1, 3, 5 waves, then the rest) so that no launch ends
+                // with a partial wave, and each piece waits only for the sums of the batches its tiles touch.
+                int num_tiles = 0, tiles_per_batch = 0;
+                const int wave = ctx->num_sms;
+                const bool pipelined = !pad_b && getenv("TB200_MATMUL_NO_OVERLAP") == nullptr &&
+                                       tc_gemm_tile_counts(q, &num_tiles, &tiles_per_batch) && tiles_per_batch > 0 &&
+                                       num_tiles >= 6 * wave && N >= 8;
+                if (!pipelined)
+                {
+                    st = launch_sums(ctx->stream, 0, N);
+                    if (st != TB200_OK)
+                        return st;
+                    return tc_gemm_launch(ctx, q);
+                }
+                if (!ctx->aux_stream)
+                {
+                    TB200_CUDA_CHECK(ctx, cudaStreamCreateWithFlags(&ctx->aux_stream, cudaStreamNonBlocking));
+                    TB200_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->aux_fork, cudaEventDisableTiming));
+                    for (int i = 0; i < 8; i++)
+                        TB200_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->aux_join[i], cudaEventDisableTiming));
+                }
+                // the second stream starts after everything already queued on the main one (operands, and earlier
+                // products that still read the shared sums)
+                TB200_CUDA_CHECK(ctx, cudaEventRecord(ctx->aux_fork, ctx->stream));
+                TB200_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->aux_stream, ctx->aux_fork, 0));
+                const int cuts[4] = { 1 * wave, 4 * wave, 9 * wave, num_tiles };
+                int tile_lo = 0, batch_lo = 0;
+                for (int k = 0; k < 4 && tile_lo < num_tiles; k++)
+                {
+                    const int tile_hi  = std::min(num_tiles, std::max(cuts[k], tile_lo + 1));
+                    const int batch_hi = std::min(N, (tile_hi + tiles_per_batch - 1) / tiles_per_batch);
+                    if (batch_hi > batch_lo)
+                    {
+                        st = launch_sums(ctx->aux_stream, batch_lo, batch_hi);
+                        if (st != TB200_OK)
+                            return st;
+                        batch_lo = batch_hi;
+                    }
+                    TB200_CUDA_CHECK(ctx, cudaEventRecord(ctx->aux_join[k], ctx->aux_stream));
+                    TB200_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->stream, ctx->aux_join[k], 0));
+                    TcProblem piece = q;
+                    piece.tile_begin = tile_lo;
+                    piece.tile_end   = tile_hi;
+                    st = tc_gemm_launch(ctx, piece);
+                    if (st != TB200_OK)
+                        return st;
+                    tile_lo = tile_hi;
+                }
+                return TB200_OK;
             }
             return tc_gemm_launch(ctx, q);
         }

@@ -62,6 +62,9 @@ struct tb200_ctx
         size_t cap        = 0;
         bool ready        = false;
     } pipe;
+    // second stream and events that let MATMUL's zero-point sums of later batches run beside the GEMM of earlier ones
+    cudaStream_t aux_stream = nullptr;
+    cudaEvent_t aux_fork = nullptr, aux_join[8] = {};
     // optional CUDA-event brackets around the main kernels (tb200_timer_enable)
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;
@@ -162,6 +165,7 @@ struct TcProblem
     // B: K-major weights [OC][KH*KW*IC] (b_mn_major == 0) or MN-major [batch][K][OC] (b_mn_major == 1, matmul)
     const void* b;
     int b_mn_major;
+    int64_t b_ld;    // MN-major B: elements between consecutive K rows (0 = OC)
     // epilogue
     int epi;
     tb200_dtype out_dtype;
@@ -180,12 +184,16 @@ struct TcProblem
     int32_t clamp_lo, clamp_hi;    // also the dtype range
     float clamp_lo_f, clamp_hi_f;
     int has_clamp;
+    // optional: launch only tiles [tile_begin, tile_end) of the problem (both 0 = all tiles)
+    int tile_begin, tile_end;
 };
 
 // Returns TB200_OK and launches, or TB200_ERROR with ctx->err set when the shape does not qualify
 // (the caller then uses the CUDA-core kernels).
 bool tc_gemm_supported(const TcProblem& p, std::string* why);
 tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& p);
+// Total tile count of a problem and the tiles per row block (per batch for MATMUL); tiles are numbered batch-major.
+bool tc_gemm_tile_counts(const TcProblem& p, int* num_tiles, int* tiles_per_row_block);
 
 // fp32 SGEMM on CUDA cores (sgemm_f32.cu): out[n] = a[n] x b[n], a [N,H,C], b [N,C,W]
 tb200_status sgemm_f32_launch(tb200_ctx* ctx, const float* a, const float* b, float* out, int N, int H, int C, int W);

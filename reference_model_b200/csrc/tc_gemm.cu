@@ -39,6 +39,7 @@ struct TcKernelParams
     CUtensorMap tmB;
     // tile grid
     int tiles_x, tiles_y, tiles_n, tiles_col, num_tiles;
+    int tile_begin, tile_end;    // range of tiles this launch covers
     int BW, BH, BN;
     int N, OH, OW, OC;
     int IH, IW;
@@ -157,7 +158,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x)
+            for (int tile = p.tile_begin + blockIdx.x; tile < p.tile_end && ok; tile += gridDim.x)
             {
                 const TileCoord t = decode_tile(p, tile);
                 const int ax0 = t.x0 * p.stride_x - p.pad_l;
@@ -234,7 +235,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x)
+            for (int tile = p.tile_begin + blockIdx.x; tile < p.tile_end && ok; tile += gridDim.x)
             {
                 if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, kWaitLimitCycles))
                 {
@@ -308,7 +309,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
         bool ok = true;
         int dev_flags = 0;
         int cols_loaded_for = -1;
-        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x)
+        for (int tile = p.tile_begin + blockIdx.x; tile < p.tile_end; tile += gridDim.x)
         {
             const TileCoord t = decode_tile(p, tile);
             if (EPI == TC_EPI_RESCALE && cols_loaded_for != t.col0)
@@ -819,7 +820,7 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     {
         if (swz != 128)
             return no("MN-major B needs 128-byte K chunks of A");
-        if ((q.OC * es) % 16 != 0)
+        if (((q.b_ld ? q.b_ld : (int64_t)q.OC) * es) % 16 != 0)
             return no("B row stride not 16-byte aligned");
         k.b_box_n       = 128 / es;
         k.b_nbox        = block_n / k.b_box_n;
@@ -904,8 +905,8 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
         plan->b_dims[0]    = (cuuint64_t)q.OC;
         plan->b_dims[1]    = (cuuint64_t)q.IC;
         plan->b_dims[2]    = (cuuint64_t)q.OH;    // batches
-        plan->b_strides[0] = (cuuint64_t)q.OC * es;
-        plan->b_strides[1] = (cuuint64_t)q.OC * es * q.IC;
+        plan->b_strides[0] = (cuuint64_t)(q.b_ld ? q.b_ld : (int64_t)q.OC) * es;
+        plan->b_strides[1] = plan->b_strides[0] * q.IC;
         plan->b_box[0]     = (cuuint32_t)k.b_box_n;
         plan->b_box[1]     = (cuuint32_t)k.chunk_elems;
         plan->b_box[2]     = 1;
@@ -913,7 +914,14 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     for (int i = 0; i < 3; i++)
         if (plan->a_strides[i] % 16 != 0 || plan->a_strides[i] >= (1ULL << 40))
             return no("activation stride not usable by TMA");
-    plan->grid = std::min(k.num_tiles, num_sms * plan->ctas_per_sm);
+    k.tile_begin = 0;
+    k.tile_end   = k.num_tiles;
+    if (q.tile_end > q.tile_begin)
+    {
+        k.tile_begin = std::max(0, q.tile_begin);
+        k.tile_end   = std::min(k.num_tiles, q.tile_end);
+    }
+    plan->grid = std::max(1, std::min(k.tile_end - k.tile_begin, num_sms * plan->ctas_per_sm));
     return true;
 }
 
@@ -923,6 +931,16 @@ bool tc_gemm_supported(const TcProblem& p, std::string* why)
 {
     TcPlan plan;
     return make_plan(p, 148, &plan, why);
+}
+
+bool tc_gemm_tile_counts(const TcProblem& p, int* num_tiles, int* tiles_per_row_block)
+{
+    TcPlan plan;
+    if (!make_plan(p, 148, &plan, nullptr))
+        return false;
+    *num_tiles           = plan.kp.num_tiles;
+    *tiles_per_row_block = plan.kp.tiles_x * plan.kp.tiles_col;
+    return true;
 }
 
 tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
