@@ -351,14 +351,6 @@ extern "C" tb200_status tb200_ctx_destroy(tb200_ctx* ctx)
         cudaStreamDestroy(ctx->pipe.h2d);
         cudaStreamDestroy(ctx->pipe.d2h);
     }
-    if (ctx->aux_stream)
-    {
-        cudaStreamSynchronize(ctx->aux_stream);
-        cudaEventDestroy(ctx->aux_fork);
-        for (int i = 0; i < 8; i++)
-            cudaEventDestroy(ctx->aux_join[i]);
-        cudaStreamDestroy(ctx->aux_stream);
-    }
     if (ctx->d_status)
         cudaFree(ctx->d_status);
     if (ctx->h_status)
@@ -1153,56 +1145,13 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
                     }
                     return post_launch(ctx, "matmul_zp_sums", launches);
                 };
-                // Large batched products: the sums of later batches run on a second stream beside the GEMM of earlier
-                // ones.  The GEMM is cut at whole waves of tiles (1, 3, 5 waves, then the rest) so that no launch ends
-                // with a partial wave, and each piece waits only for the sums of the batches its tiles touch.
-                int num_tiles = 0, tiles_per_batch = 0;
-                const int wave = ctx->num_sms;
-                const bool pipelined = !pad_b && getenv("TB200_MATMUL_NO_OVERLAP") == nullptr &&
-                                       tc_gemm_tile_counts(q, &num_tiles, &tiles_per_batch) && tiles_per_batch > 0 &&
-                                       num_tiles >= 6 * wave && N >= 8;
-                if (!pipelined)
-                {
-                    st = launch_sums(ctx->stream, 0, N);
-                    if (st != TB200_OK)
-                        return st;
-                    return tc_gemm_launch(ctx, q);
-                }
-                if (!ctx->aux_stream)
-                {
-                    TB200_CUDA_CHECK(ctx, cudaStreamCreateWithFlags(&ctx->aux_stream, cudaStreamNonBlocking));
-                    TB200_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->aux_fork, cudaEventDisableTiming));
-                    for (int i = 0; i < 8; i++)
-                        TB200_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->aux_join[i], cudaEventDisableTiming));
-                }
-                // the second stream starts after everything already queued on the main one (operands, and earlier
-                // products that still read the shared sums)
-                TB200_CUDA_CHECK(ctx, cudaEventRecord(ctx->aux_fork, ctx->stream));
-                TB200_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->aux_stream, ctx->aux_fork, 0));
-                const int cuts[4] = { 1 * wave, 4 * wave, 9 * wave, num_tiles };
-                int tile_lo = 0, batch_lo = 0;
-                for (int k = 0; k < 4 && tile_lo < num_tiles; k++)
-                {
-                    const int tile_hi  = std::min(num_tiles, std::max(cuts[k], tile_lo + 1));
-                    const int batch_hi = std::min(N, (tile_hi + tiles_per_batch - 1) / tiles_per_batch);
-                    if (batch_hi > batch_lo)
-                    {
-                        st = launch_sums(ctx->aux_stream, batch_lo, batch_hi);
-                        if (st != TB200_OK)
-                            return st;
-                        batch_lo = batch_hi;
-                    }
-                    TB200_CUDA_CHECK(ctx, cudaEventRecord(ctx->aux_join[k], ctx->aux_stream));
-                    TB200_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->stream, ctx->aux_join[k], 0));
-                    TcProblem piece = q;
-                    piece.tile_begin = tile_lo;
-                    piece.tile_end   = tile_hi;
-                    st = tc_gemm_launch(ctx, piece);
-                    if (st != TB200_OK)
-                        return st;
-                    tile_lo = tile_hi;
-                }
-                return TB200_OK;
+                // (Running the sums of later batches on a second stream beside tile-range pieces of the GEMM was
+                // measured slower than this plain sequence: the memory-bound sums slow the concurrent GEMM by more
+                // than they hide.)
+                st = launch_sums(ctx->stream, 0, N);
+                if (st != TB200_OK)
+                    return st;
+                return tc_gemm_launch(ctx, q);
             }
             return tc_gemm_launch(ctx, q);
         }

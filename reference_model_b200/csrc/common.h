@@ -62,9 +62,6 @@ struct tb200_ctx
         size_t cap        = 0;
         bool ready        = false;
     } pipe;
-    // second stream and events that let MATMUL's zero-point sums of later batches run beside the GEMM of earlier ones
-    cudaStream_t aux_stream = nullptr;
-    cudaEvent_t aux_fork = nullptr, aux_join[8] = {};
     // optional CUDA-event brackets around the main kernels (tb200_timer_enable)
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;

@@ -50,6 +50,7 @@ struct TcKernelParams
     int b_mn_major, b_nbox, b_box_n, b_box_bytes;
     // shared memory ring
     int a_chunk_bytes, b_chunk_bytes, stage_bytes, num_stages, tx_bytes_per_chunk;
+    int commit_group;    // stages released per tcgen05.commit (each commit costs tensor-pipe idle time)
     // MMA
     uint64_t a_desc_hi, b_desc_hi;
     int b_kstep_bytes, mmas_per_chunk;
@@ -155,51 +156,61 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0)
         {
-            int stage = 0;
+            // All loop-carried quantities are running counters: this single thread sits on the critical path of the
+            // pipeline, so it avoids divisions and recomputed addresses.
+            int stage = 0, group_pos = 0;
             uint32_t phase = 0;
             bool ok = true;
+            const int ksub = p.ksub, num_stages = p.num_stages, group = p.commit_group;
+            const int a_chunk_bytes = p.a_chunk_bytes, b_chunk_bytes = p.b_chunk_bytes, chunk_elems = p.chunk_elems;
+            const uint32_t tx_per_chunk = (uint32_t)p.tx_bytes_per_chunk;
+            uint32_t sA_stage = smem_base;
             for (int tile = p.tile_begin + blockIdx.x; tile < p.tile_end && ok; tile += gridDim.x)
             {
                 const TileCoord t = decode_tile(p, tile);
                 const int ax0 = t.x0 * p.stride_x - p.pad_l;
                 const int ay0 = t.y0 * p.stride_y - p.pad_t;
-                int chunk = 0, cc = 0, ky = 0, kx = 0;    // running chunk index and its (tap, channel block)
-                for (int ks = 0; ks < p.num_kstages; ks++)
+                int chunk_k = 0, cc = 0, ky = 0, kx = 0;    // K offset of the running chunk, its (tap, channel block)
+                int chunks_left = p.total_chunks;
+                while (chunks_left > 0)
                 {
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, kWaitLimitCycles))
+                    // stages are released in groups of `commit_group` (one tcgen05.commit per group): the first stage
+                    // of a group waits for the group's last barrier, the others are free by then
+                    if (group_pos == 0 &&
+                        !ptx::mbar_wait_bounded(ptx::smem_u32(&bar_empty[stage + group - 1]), phase ^ 1u, kWaitLimitCycles))
                     {
                         ok = false;
                         break;
                     }
-                    const int nchunks   = min(p.ksub, p.total_chunks - chunk);
+                    const int nchunks   = min(ksub, chunks_left);
+                    chunks_left -= nchunks;
                     const uint32_t full = ptx::smem_u32(&bar_full[stage]);
-                    uint32_t sA         = smem_base + stage * p.stage_bytes;
-                    uint32_t sB         = sA + p.ksub * p.a_chunk_bytes;
+                    uint32_t sA         = sA_stage;
+                    uint32_t sB         = sA_stage + ksub * a_chunk_bytes;
                     if (p.debug & 4)
                     {
                         ptx::mbar_arrive(full);
-                        chunk += nchunks;
                     }
                     else
                     {
-                        ptx::mbar_arrive_expect_tx(full, (uint32_t)(nchunks * p.tx_bytes_per_chunk));
+                        ptx::mbar_arrive_expect_tx(full, (uint32_t)nchunks * tx_per_chunk);
                         for (int j = 0; j < nchunks; j++)
                         {
-                            ptx::tma_load_4d(sA, &p.tmA, full, cc * p.chunk_elems, ax0 + kx * p.dil_x, ay0 + ky * p.dil_y,
+                            ptx::tma_load_4d(sA, &p.tmA, full, cc * chunk_elems, ax0 + kx * p.dil_x, ay0 + ky * p.dil_y,
                                              t.n0);
                             if (!p.b_mn_major)
                             {
-                                ptx::tma_load_3d(sB, &p.tmB, full, chunk * p.chunk_elems, t.col0, 0);
+                                ptx::tma_load_3d(sB, &p.tmB, full, chunk_k, t.col0, 0);
                             }
                             else
                             {
                                 for (int bx = 0; bx < p.b_nbox; bx++)
-                                    ptx::tma_load_3d(sB + bx * p.b_box_bytes, &p.tmB, full, t.col0 + bx * p.b_box_n,
-                                                     chunk * p.chunk_elems, t.y0);
+                                    ptx::tma_load_3d(sB + bx * p.b_box_bytes, &p.tmB, full, t.col0 + bx * p.b_box_n, chunk_k,
+                                                     t.y0);
                             }
-                            sA += p.a_chunk_bytes;
-                            sB += p.b_chunk_bytes;
-                            chunk++;
+                            sA += a_chunk_bytes;
+                            sB += b_chunk_bytes;
+                            chunk_k += chunk_elems;
                             if (++cc == p.chunks_per_tap)
                             {
                                 cc = 0;
@@ -211,9 +222,13 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                             }
                         }
                     }
-                    if (++stage == p.num_stages)
+                    if (++group_pos == group)
+                        group_pos = 0;
+                    sA_stage += p.stage_bytes;
+                    if (++stage == num_stages)
                     {
-                        stage = 0;
+                        stage    = 0;
+                        sA_stage = smem_base;
                         phase ^= 1u;
                     }
                 }
@@ -230,11 +245,22 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0)
         {
-            int stage = 0;
+            // Same discipline as the producer: running counters and descriptor words only.  The two descriptors
+            // differ between MMAs only in their 14-bit start-address field (16-byte units), so they are advanced by
+            // adding to the low word.
+            int stage = 0, group_pos = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
+            const int ksub = p.ksub, num_stages = p.num_stages, group = p.commit_group, mmas = p.mmas_per_chunk;
+            const uint32_t idesc = p.idesc;
+            const uint64_t a_chunk16 = (uint64_t)(p.a_chunk_bytes >> 4), b_chunk16 = (uint64_t)(p.b_chunk_bytes >> 4);
+            const uint64_t b_kstep16 = (uint64_t)(p.b_kstep_bytes >> 4), stage16 = (uint64_t)(p.stage_bytes >> 4);
+            const uint64_t ad_ring0 = ptx::smem_desc(p.a_desc_hi, smem_base);
+            const uint64_t bd_ring0 = ptx::smem_desc(p.b_desc_hi, smem_base + ksub * p.a_chunk_bytes);
+            uint64_t ad_stage = ad_ring0, bd_stage = bd_ring0;
+            const bool issue = !(p.debug & 2);
             for (int tile = p.tile_begin + blockIdx.x; tile < p.tile_end && ok; tile += gridDim.x)
             {
                 if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, kWaitLimitCycles))
@@ -244,7 +270,9 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                 }
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.block_n);
-                for (int ks = 0; ks < p.num_kstages; ks++)
+                uint32_t accum  = 0;    // the first MMA of a tile overwrites the accumulator
+                int chunks_left = p.total_chunks;
+                while (chunks_left > 0)
                 {
                     if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_full[stage]), phase, kWaitLimitCycles))
                     {
@@ -252,32 +280,40 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    const int nchunks = min(p.ksub, p.total_chunks - ks * p.ksub);
-                    const uint32_t sA = smem_base + stage * p.stage_bytes;
-                    const uint32_t sB = sA + p.ksub * p.a_chunk_bytes;
-                    if (!(p.debug & 2))
+                    const int nchunks = min(ksub, chunks_left);
+                    chunks_left -= nchunks;
+                    if (issue)
                     {
+                        uint64_t ad_chunk = ad_stage, bd_chunk = bd_stage;
                         for (int j = 0; j < nchunks; j++)
                         {
-                            // descriptors differ only in the 14-bit start-address field (16-byte units)
-                            uint64_t ad = ptx::smem_desc(p.a_desc_hi, sA + j * p.a_chunk_bytes);
-                            uint64_t bd = ptx::smem_desc(p.b_desc_hi, sB + j * p.b_chunk_bytes);
-                            for (int m = 0; m < p.mmas_per_chunk; m++)
+                            uint64_t ad = ad_chunk, bd = bd_chunk;
+                            for (int m = 0; m < mmas; m++)
                             {
-                                const uint32_t accum = (ks | j | m) != 0 ? 1u : 0u;
                                 if (EPI == TC_EPI_FLOAT)
-                                    ptx::mma_f16_ss(d_tmem, ad, bd, p.idesc, accum);
+                                    ptx::mma_f16_ss(d_tmem, ad, bd, idesc, accum);
                                 else
-                                    ptx::mma_i8_ss(d_tmem, ad, bd, p.idesc, accum);
+                                    ptx::mma_i8_ss(d_tmem, ad, bd, idesc, accum);
+                                accum = 1;
                                 ad += 2;    // 32 bytes of K
-                                bd += (uint64_t)(p.b_kstep_bytes >> 4);
+                                bd += b_kstep16;
                             }
+                            ad_chunk += a_chunk16;
+                            bd_chunk += b_chunk16;
                         }
                     }
-                    ptx::mma_commit(ptx::smem_u32(&bar_empty[stage]));
-                    if (++stage == p.num_stages)
+                    if (++group_pos == group)
                     {
-                        stage = 0;
+                        ptx::mma_commit(ptx::smem_u32(&bar_empty[stage]));
+                        group_pos = 0;
+                    }
+                    ad_stage += stage16;
+                    bd_stage += stage16;
+                    if (++stage == num_stages)
+                    {
+                        stage    = 0;
+                        ad_stage = ad_ring0;
+                        bd_stage = bd_ring0;
                         phase ^= 1u;
                     }
                 }
@@ -846,6 +882,9 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
         k.num_stages = std::min(forced, kMaxStages);
     if (k.num_stages < 2)
         return no("stage does not fit in shared memory");
+    k.commit_group = env_int("TB200_TC_COMMIT_GROUP", 1);
+    if (k.commit_group < 1 || k.num_stages % k.commit_group != 0 || k.num_stages / k.commit_group < 2)
+        k.commit_group = 1;
     plan->smem_bytes = k.num_stages * k.stage_bytes + 1024;
 
     const bool is_f16 = q.in_dtype != TB200_INT8;
