@@ -336,6 +336,8 @@ extern "C" tb200_status tb200_ctx_destroy(tb200_ctx* ctx)
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch)
         cudaFree(ctx->scratch);
+    if (ctx->join_table)
+        cudaFree(ctx->join_table);
     if (ctx->pipe.ready)
     {
         cudaStreamSynchronize(ctx->pipe.h2d);
@@ -1421,6 +1423,26 @@ extern "C" tb200_status tb200_residual_add(tb200_ctx* ctx, const tb200_tensor* a
         // clip to int8, then CLAMP: one clip to [lo, hi]
         f.lo = has_clamp ? std::min(std::max(-128, clamp_min), clamp_max) : -128;
         f.hi = has_clamp ? std::min(std::max(127, clamp_min), clamp_max) : 127;
+        // Large joins pay for tabulating all 65536 byte pairs first (two launches, one lookup per element after that)
+        if (n >= ((int64_t)1 << 22) && (ctx->join_table != nullptr || !ctx->capturing))
+        {
+            constexpr size_t kTableSmem = kJoinTableBytes + kJoinBadWords * sizeof(uint32_t);
+            if (ctx->join_table == nullptr)
+            {
+                TB200_CUDA_CHECK(ctx, cudaMalloc(&ctx->join_table, kTableSmem));
+                TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(residual_add_i8_table_kernel,
+                                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTableSmem));
+            }
+            uint8_t* table     = reinterpret_cast<uint8_t*>(ctx->join_table);
+            uint32_t* bad_bits = reinterpret_cast<uint32_t*>(table + kJoinTableBytes);
+            residual_table_kernel<<<256, 256, 0, ctx->stream>>>(f, table, bad_bits);
+            const int tblock = 512;
+            const int tgrid  = (int)std::min<int64_t>((n / 16 + tblock - 1) / tblock, (int64_t)ctx->num_sms * 2);
+            residual_add_i8_table_kernel<<<tgrid, tblock, kTableSmem, ctx->stream>>>(
+                reinterpret_cast<const int8_t*>(a->data), reinterpret_cast<const int8_t*>(b->data),
+                reinterpret_cast<int8_t*>(output->data), n / 16, table, bad_bits, ctx->d_status);
+            return post_launch(ctx, "residual_add_i8_table", 2);
+        }
         residual_add_i8_fast_kernel<<<grid_for(ctx, n / 16, block), block, 0, ctx->stream>>>(
             reinterpret_cast<const int8_t*>(a->data), reinterpret_cast<const int8_t*>(b->data),
             reinterpret_cast<int8_t*>(output->data), n / 16, f, ctx->d_status);

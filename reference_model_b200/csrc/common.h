@@ -47,6 +47,7 @@ struct tb200_ctx
     int* h_status        = nullptr;    // pinned mirror
     void* scratch        = nullptr;    // grow-on-demand device scratch (zero-point sums, weight tables)
     size_t scratch_bytes = 0;
+    void* join_table     = nullptr;    // 64 KiB result table + 8 KiB REQUIRE bits of the per-tensor residual join
     uint64_t launches    = 0;
     int policy           = 0;
     int num_sms          = 148;

@@ -334,6 +334,99 @@ __global__ void __launch_bounds__(256) residual_add_i8_fast_kernel(const int8_t*
         atomicOr(status, TB200_DEV_UNPREDICTABLE);
 }
 
+// Residual join through one table.  With per-tensor parameters the whole RESCALE, RESCALE, ADD, RESCALE, CLAMP chain is
+// a function of the two input bytes alone.  residual_table_kernel evaluates it for all 65536 byte pairs (with every
+// REQUIRE verdict as one bit per pair), and residual_add_i8_table_kernel keeps the table in shared memory and spends one
+// byte lookup per element.  Row a of the table is stored with its b index XOR-ed by 4 * (a mod 32) so that equal b
+// values next to different a values fall into different shared-memory banks.
+constexpr int kJoinTableBytes = 65536;
+constexpr int kJoinBadWords   = 2048;
+
+__device__ __forceinline__ uint32_t join_table_slot(uint32_t ua, uint32_t ub)
+{
+    return (ua << 8) | (ub ^ ((ua & 31u) << 2));
+}
+
+__global__ void __launch_bounds__(256) residual_table_kernel(ResidualFast r, uint8_t* __restrict__ table,
+                                                             uint32_t* __restrict__ bad_bits)
+{
+    int32_t vlim_a, vlim_b, vlim_o;
+    const Scale32Fast ca = make_scale32_fast(r.a, &vlim_a);
+    const Scale32Fast cb = make_scale32_fast(r.b, &vlim_b);
+    const Scale32Fast co = make_scale32_fast(r.o, &vlim_o);
+    // raw bytes of the two operands; thread t of block a fills slot (a << 8 | t)
+    const uint32_t ua = blockIdx.x, ub = threadIdx.x ^ ((blockIdx.x & 31u) << 2);
+    const int32_t xa  = (int32_t)(int8_t)ua - ca.zp_in;
+    const int32_t xb  = (int32_t)(int8_t)ub - cb.zp_in;
+    bool ov           = (xa > vlim_a) || (xa < ~vlim_a) || (xb > vlim_b) || (xb < ~vlim_b);
+    const int32_t ya  = scale32_fast(xa, ca, ov);
+    const int32_t yb  = scale32_fast(xb, cb, ov);
+    const int32_t sum = (int32_t)((uint32_t)ya + (uint32_t)yb);
+    // INT32 ADD: the mathematical sum must fit (operand signs equal and result sign differs = overflow)
+    ov |= ((ya ^ sum) & (yb ^ sum)) < 0;
+    const int32_t res       = scale32_fast(sum, co, ov);
+    const int32_t zp_add_hi = co.zp_out > 0 ? 2147483647 - co.zp_out : 2147483647;
+    const int32_t zp_add_lo = co.zp_out < 0 ? (int32_t)(-2147483647 - 1 - co.zp_out) : (-2147483647 - 1);
+    ov |= (sum > vlim_o) || (sum < ~vlim_o) || (res > zp_add_hi) || (res < zp_add_lo);
+    int32_t z = res + co.zp_out;
+    z = max(z, r.lo);
+    z = min(z, r.hi);
+    const uint32_t slot = join_table_slot(ua, ub);    // == (ua << 8) | threadIdx.x
+    table[slot]      = (uint8_t)(z & 0xff);
+    const uint32_t m = __ballot_sync(0xffffffffu, ov);
+    if ((threadIdx.x & 31) == 0)
+        bad_bits[slot >> 5] = m;
+}
+
+__global__ void __launch_bounds__(512, 2) residual_add_i8_table_kernel(const int8_t* __restrict__ a, const int8_t* __restrict__ b,
+                                                                       int8_t* __restrict__ out, int64_t n16,
+                                                                       const uint8_t* __restrict__ table,
+                                                                       const uint32_t* __restrict__ bad_bits, int* status)
+{
+    extern __shared__ __align__(16) uint8_t join_smem[];
+    uint8_t* tab   = join_smem;
+    uint32_t* bits = reinterpret_cast<uint32_t*>(join_smem + kJoinTableBytes);
+    for (int i = threadIdx.x; i < kJoinTableBytes / 16; i += blockDim.x)
+        reinterpret_cast<int4*>(tab)[i] = __ldg(reinterpret_cast<const int4*>(table) + i);
+    uint32_t any = 0;
+    for (int i = threadIdx.x; i < kJoinBadWords; i += blockDim.x)
+    {
+        const uint32_t w = __ldg(bad_bits + i);
+        bits[i] = w;
+        any |= w;
+    }
+    // (also the barrier that publishes the table)
+    const bool check = __syncthreads_or(any != 0) != 0;
+    bool bad = false;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += step)
+    {
+        const int4 va = __ldg(reinterpret_cast<const int4*>(a) + i);
+        const int4 vb = __ldg(reinterpret_cast<const int4*>(b) + i);
+        const uint32_t wa[4] = { (uint32_t)va.x, (uint32_t)va.y, (uint32_t)va.z, (uint32_t)va.w };
+        const uint32_t wb[4] = { (uint32_t)vb.x, (uint32_t)vb.y, (uint32_t)vb.z, (uint32_t)vb.w };
+        uint32_t wo[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+        {
+            // two 16-bit slots per word: (a byte << 8 | b byte), then the bank swizzle on both at once
+            uint32_t p01 = __byte_perm(wa[q], wb[q], 0x1504);
+            uint32_t p23 = __byte_perm(wa[q], wb[q], 0x3726);
+            p01 ^= (p01 >> 6) & 0x007c007cu;
+            p23 ^= (p23 >> 6) & 0x007c007cu;
+            const uint32_t i0 = p01 & 0xffffu, i1 = p01 >> 16, i2 = p23 & 0xffffu, i3 = p23 >> 16;
+            const uint32_t r0 = tab[i0], r1 = tab[i1], r2 = tab[i2], r3 = tab[i3];
+            if (check)
+                bad |= (((bits[i0 >> 5] >> (i0 & 31)) | (bits[i1 >> 5] >> (i1 & 31)) | (bits[i2 >> 5] >> (i2 & 31)) |
+                         (bits[i3 >> 5] >> (i3 & 31))) & 1u) != 0;
+            wo[q] = __byte_perm(__byte_perm(r0, r1, 0x0040), __byte_perm(r2, r3, 0x0040), 0x5410);
+        }
+        reinterpret_cast<uint4*>(out)[i] = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+    }
+    if (bad)
+        atomicOr(status, TB200_DEV_UNPREDICTABLE);
+}
+
 // ------------------------------------------------------------------------------------------------ CLAMP
 template <typename T>
 __global__ void clamp_int_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t n, int32_t lo, int32_t hi)

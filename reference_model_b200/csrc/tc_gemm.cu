@@ -57,6 +57,7 @@ struct TcKernelParams
     uint32_t idesc;
     int is_f16_kind;
     int tmem_cols;
+    int acc_bufs;    // TMEM accumulator buffers: 2 overlaps a tile's epilogue with the next tile's MMAs, 1 halves TMEM use
     // epilogue
     void* out;
     int out_es;
@@ -103,6 +104,52 @@ __device__ __forceinline__ uint32_t pack4_i8(int a, int b, int c, int d)
            ((uint32_t)(d & 0xff) << 24);
 }
 
+// four int32 values saturated to int8 and packed, first value in the low byte
+__device__ __forceinline__ uint32_t pack4_sat_i8(int a, int b, int c, int d)
+{
+    uint32_t hi, r;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
+    return r;
+}
+
+// Column-block property found while the RESCALE constants are built
+enum : int
+{
+    EPI_COLS_GENERIC = 1,    // some column has operands outside what the high-word form below handles
+};
+
+// apply_scale_32 + output zero point + CLAMP + int8 packing of four accumulators, for column blocks whose shifts all
+// lie in [32, 54] (the usual case for a convolution's RESCALE).  With shift >= 32 apply_scale_32 accepts every int32
+// value, the result is the high word of the 64-bit sum shifted by shift - 32, and adding out_zp * 2^shift to the
+// rounding constant before the arithmetic shift adds exactly out_zp after it (|sum| < 2^62 + 2^61 + 2^54).
+//   cols[i] = {multiplier, shift - 32, R(v >= 0) lo, hi, R(v < 0) lo, hi},  R = 2^(shift-1) +- 2^30 + out_zp * 2^shift
+// (the two constants are equal without double rounding).  Measured on this part, one 64-bit multiply-add with a
+// selected addend is cheaper than a high and a low multiply with the carry worked out by hand.
+template <bool DOUBLE_ROUND, bool NARROW_CLAMP>
+__device__ __forceinline__ uint32_t rescale32_high_x4(const uint32_t* v, const int32_t (*cols)[8], int32_t clamp_lo,
+                                                      int32_t clamp_hi)
+{
+    int32_t z[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+    {
+        const int4 c0   = *reinterpret_cast<const int4*>(&cols[i][0]);
+        const int32_t a = (int32_t)v[i];
+        int64_t r       = ((int64_t)c0.w << 32) | (uint32_t)c0.z;
+        if (DOUBLE_ROUND)
+        {
+            const int2 c1 = *reinterpret_cast<const int2*>(&cols[i][4]);
+            r             = a >= 0 ? r : (((int64_t)c1.y << 32) | (uint32_t)c1.x);
+        }
+        const int64_t prod = (int64_t)a * (int64_t)c0.x + r;
+        z[i]               = (int32_t)(prod >> 32) >> c0.y;
+        if (NARROW_CLAMP)
+            z[i] = min(max(z[i], clamp_lo), clamp_hi);
+    }
+    return pack4_sat_i8(z[0], z[1], z[2], z[3]);
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_constant__ TcKernelParams p)
 {
@@ -117,6 +164,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
     // epilogue threads: {multiplier, shift, round(v >= 0) lo/hi, round(v < 0) lo/hi, largest |v| allowed, 0}
     __shared__ __align__(16) int32_t epi_cols[EPI == TC_EPI_RESCALE ? 256 : 1][8];
     __shared__ int32_t epi_vlim_min;    // smallest per-column value limit of the current column block
+    __shared__ int epi_flags;           // EPI_COLS_* of the current column block
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -320,9 +368,11 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                 if (!ok)
                     break;
                 ptx::mma_commit(ptx::smem_u32(&bar_tmem_full[acc]));
-                acc ^= 1;
-                if (acc == 0)
+                if (++acc == p.acc_bufs)
+                {
+                    acc = 0;
                     acc_phase ^= 1u;
+                }
             }
             if (!ok)
             {
@@ -353,8 +403,30 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                 // (re)build the per-column constants; the named barrier keeps the 128 epilogue threads in step
                 asm volatile("bar.sync 1, 256;" ::: "memory");
                 if (threadIdx.x == 64)
+                {
                     epi_vlim_min = 2147483647;
+                    // the short form packs to int8 with saturation and stores whole 32-column chunks
+                    const bool shortable = p.out_es == 1 && (p.OC & 31) == 0 && p.clamp_lo >= -128 &&
+                                           p.clamp_hi <= 127 && p.clamp_lo <= p.clamp_hi && p.out_zp >= -128 &&
+                                           p.out_zp <= 127 && !(p.debug & 8);
+                    epi_flags = shortable ? 0 : EPI_COLS_GENERIC;
+                }
                 asm volatile("bar.sync 1, 256;" ::: "memory");
+                for (int c = (int)threadIdx.x - 64; c < p.block_n; c += kEpiThreads)
+                {
+                    if (t.col0 + c >= p.OC)
+                        continue;
+                    const int32_t m = __ldg(p.mult_pad + t.col0 + c);
+                    const int32_t s = (int32_t)__ldg(p.shift_pad + t.col0 + c);
+                    int f = 0;
+                    // high-word form: every int32 value accepted, out_zp * 2^shift clear of the int64 range
+                    if (m < 0 || s < 32 || s > 54)
+                        f |= EPI_COLS_GENERIC;
+                    if (f & ~epi_flags)
+                        atomicOr(&epi_flags, f);
+                }
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                const bool high_form = !(epi_flags & EPI_COLS_GENERIC);
                 for (int c = (int)threadIdx.x - 64; c < p.block_n; c += kEpiThreads)
                 {
                     const int32_t m = __ldg(p.mult_pad + t.col0 + c);
@@ -363,15 +435,28 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     const int32_t sc  = valid ? s : 2;
                     const int64_t half = (int64_t)1 << (sc - 1);
                     int64_t rpos = half, rneg = half;
-                    if (p.double_round && sc > 31)
+                    const bool dr = p.double_round && sc > 31;
+                    if (dr)
                     {
                         rpos += (int64_t)1 << 30;
                         rneg -= (int64_t)1 << 30;
                     }
                     // apply_scale_32 requires -2^(shift-1) <= v < 2^(shift-1); invalid operands fail every value
                     const int32_t vlim = !valid ? -1 : (sc - 1 >= 31 ? 2147483647 : (int32_t)(half - 1));
-                    int4 lo4 = make_int4(m, sc, (int32_t)(uint32_t)(rpos & 0xffffffffLL), (int32_t)(rpos >> 32));
-                    int4 hi4 = make_int4((int32_t)(uint32_t)(rneg & 0xffffffffLL), (int32_t)(rneg >> 32), vlim, 0);
+                    int4 lo4, hi4;
+                    if (high_form && t.col0 + c < p.OC)
+                    {
+                        const int64_t z64 = (int64_t)p.out_zp * ((int64_t)1 << sc);
+                        rpos += z64;
+                        rneg += z64;
+                        lo4 = make_int4(m, sc - 32, (int32_t)(uint32_t)(rpos & 0xffffffffLL), (int32_t)(rpos >> 32));
+                        hi4 = make_int4((int32_t)(uint32_t)(rneg & 0xffffffffLL), (int32_t)(rneg >> 32), vlim, 0);
+                    }
+                    else
+                    {
+                        lo4 = make_int4(m, sc, (int32_t)(uint32_t)(rpos & 0xffffffffLL), (int32_t)(rpos >> 32));
+                        hi4 = make_int4((int32_t)(uint32_t)(rneg & 0xffffffffLL), (int32_t)(rneg >> 32), vlim, 0);
+                    }
                     if (t.col0 + c < p.OC)
                         atomicMin(&epi_vlim_min, vlim);
                     *reinterpret_cast<int4*>(&epi_cols[c][0]) = lo4;
@@ -394,6 +479,9 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             const int ox = t.x0 + xx, oy = t.y0 + yy, on = t.n0 + nn;
             const bool row_valid = (nn < p.BN) && (ox < p.OW) && (oy < p.OH) && (on < p.N);
             const int64_t pix    = ((int64_t)on * p.OH + oy) * p.OW + ox;
+            // the neighbouring lane's row (lane ^ 1), for stores that fill whole 32-byte sectors between two lanes
+            const int64_t pix_pair     = __shfl_xor_sync(0xffffffffu, pix, 1);
+            const bool row_valid_pair  = __shfl_xor_sync(0xffffffffu, (int)row_valid, 1) != 0;
 
             // Additive per-column constants of this row (bias and zero-point terms).  For a padded convolution with a
             // non-zero input zero point the constant depends on which filter taps fall inside the image, so the table
@@ -443,7 +531,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     continue;
                 const int nvalid = min(32, p.OC - col);
 
-                if (EPI != TC_EPI_FLOAT && corr_row != nullptr)
+                if (EPI != TC_EPI_FLOAT && corr_row != nullptr && !(p.debug & 16))
                 {
                     // every per-column array is padded to a multiple of the tile width: unconditional 128-bit loads
                     const int4* cp = reinterpret_cast<const int4*>(corr_row + col);
@@ -489,10 +577,56 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     // (before and after adding the small output zero point) follow from the range check.  The range
                     // check itself is done on the largest magnitude of the 32 values against the smallest limit of
                     // the column block; only when that fails are the columns compared one by one.
+                    if (!(epi_flags & EPI_COLS_GENERIC))
+                    {
+                        // every shift of the block is at least 32: apply_scale_32 accepts all of int32, nothing to check
+                        uint32_t w[8];
+                        const bool narrow = p.clamp_lo > -128 || p.clamp_hi < 127;
+                        if (p.double_round && !narrow)
+                        {
+#pragma unroll
+                            for (int q = 0; q < 8; q++)
+                                w[q] = rescale32_high_x4<true, false>(&v[4 * q], &epi_cols[c * 32 + 4 * q], 0, 0);
+                        }
+                        else if (p.double_round)
+                        {
+#pragma unroll
+                            for (int q = 0; q < 8; q++)
+                                w[q] = rescale32_high_x4<true, true>(&v[4 * q], &epi_cols[c * 32 + 4 * q], p.clamp_lo, p.clamp_hi);
+                        }
+                        else
+                        {
+#pragma unroll
+                            for (int q = 0; q < 8; q++)
+                                w[q] = rescale32_high_x4<false, true>(&v[4 * q], &epi_cols[c * 32 + 4 * q], p.clamp_lo, p.clamp_hi);
+                        }
+                        // Each lane holds the 32 output bytes of its own row.  Two 16-byte stores per lane would hand the
+                        // memory system half-filled 32-byte sectors; instead the two lanes of a pair swap halves so that
+                        // one store instruction writes the even lane's row and the next one the odd lane's row, each
+                        // sector complete.
+                        {
+                            const bool odd = (lane & 1) != 0;
+                            uint32_t other[4];
+#pragma unroll
+                            for (int k = 0; k < 4; k++)
+                                other[k] = __shfl_xor_sync(0xffffffffu, odd ? w[k] : w[4 + k], 1);
+                            int8_t* o_own  = reinterpret_cast<int8_t*>(p.out) + pix * p.OC + col + (odd ? 16 : 0);
+                            int8_t* o_pair = reinterpret_cast<int8_t*>(p.out) + pix_pair * p.OC + col + (odd ? 16 : 0);
+                            const uint4 mine   = odd ? make_uint4(w[4], w[5], w[6], w[7]) : make_uint4(w[0], w[1], w[2], w[3]);
+                            const uint4 theirs = make_uint4(other[0], other[1], other[2], other[3]);
+                            const bool skip = (p.debug & 32) && w[0] != 0x12345678u;
+                            // first instruction: the even lane's row, second: the odd lane's row
+                            if ((odd ? row_valid_pair : row_valid) && !skip)
+                                *reinterpret_cast<uint4*>(odd ? o_pair : o_own) = odd ? theirs : mine;
+                            if ((odd ? row_valid : row_valid_pair) && !skip)
+                                *reinterpret_cast<uint4*>(odd ? o_own : o_pair) = odd ? mine : theirs;
+                        }
+                        continue;
+                    }
                     bool bad = false;
                     {
                         int32_t vmax = -2147483647 - 1, vmin = 2147483647;
-#pragma unroll
+                #pragma unroll
                         for (int i = 0; i < 32; i++)
                         {
                             vmax = max(vmax, (int32_t)v[i]);
@@ -505,14 +639,14 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                             {
                                 const int32_t vl = epi_cols[c * 32 + i][6];
                                 int32_t a = 0;
-#pragma unroll
+                #pragma unroll
                                 for (int j = 0; j < 32; j++)
                                     a = (j == i) ? (int32_t)v[j] : a;
                                 bad |= (a > vl) || (a < ~vl);
                             }
                         }
                     }
-#pragma unroll
+                #pragma unroll
                     for (int i = 0; i < 32; i++)
                     {
                         // QuantUtil::apply_scale_32 with the per-column constants prepared above; the 64-bit product
@@ -532,8 +666,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         z = min(z, p.clamp_hi);
                         v[i] = (uint32_t)z;
                     }
-                    if (bad && row_valid)
-                        dev_flags |= TB200_DEV_UNPREDICTABLE;
+
                     if (row_valid)
                     {
                         if (p.out_es == 1)
@@ -550,7 +683,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                             }
                             else
                             {
-#pragma unroll
+                #pragma unroll
                                 for (int i = 0; i < 32; i++)
                                     if (i < nvalid)
                                         o[i] = (int8_t)(int32_t)v[i];
@@ -559,7 +692,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         else if (p.out_es == 2)
                         {
                             int16_t* o = reinterpret_cast<int16_t*>(p.out) + pix * p.OC + col;
-#pragma unroll
+                #pragma unroll
                             for (int i = 0; i < 32; i++)
                                 if (i < nvalid)
                                     o[i] = (int16_t)(int32_t)v[i];
@@ -567,12 +700,15 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         else
                         {
                             int32_t* o = reinterpret_cast<int32_t*>(p.out) + pix * p.OC + col;
-#pragma unroll
+                #pragma unroll
                             for (int i = 0; i < 32; i++)
                                 if (i < nvalid)
                                     o[i] = (int32_t)v[i];
                         }
                     }
+
+                    if (bad && row_valid)
+                        dev_flags |= TB200_DEV_UNPREDICTABLE;
                 }
                 else
                 {
@@ -658,9 +794,11 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             }
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[acc]));
-            acc ^= 1;
-            if (acc == 0)
+            if (++acc == p.acc_bufs)
+            {
+                acc = 0;
                 acc_phase ^= 1u;
+            }
         }
         if (!ok && lane == 0)
         {
@@ -872,8 +1010,17 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     k.stage_bytes        = k.ksub * (k.a_chunk_bytes + k.b_chunk_bytes);
     // Small column blocks leave most of a tile's time in fixed per-tile synchronisation; two co-resident CTAs per SM
     // (half the shared-memory budget each, 2 x TMEM columns <= 512) overlap one CTA's bubbles with the other's work.
-    plan->ctas_per_sm = env_int("TB200_TC_CTAS_PER_SM", (block_n <= 128 && 4 * k.stage_bytes <= 100 * 1024) ? 2 : 1);
-    plan->ctas_per_sm = std::max(1, std::min(plan->ctas_per_sm, 512 / std::max(32, 2 * block_n)));
+    // Layers whose tiles carry little MMA work (short K) spend their time in the epilogue.  With a 256-column block
+    // a single accumulator buffer (256 TMEM columns) lets two CTAs share an SM there, which doubles the epilogue warps
+    // in flight; the lost MMA / epilogue overlap inside one CTA is made up by the neighbour CTA.
+    const int mmas_per_tile = k.total_chunks * k.mmas_per_chunk;
+    k.acc_bufs = env_int("TB200_TC_ACC_BUFS", (block_n == 256 && mmas_per_tile <= 16) ? 1 : 2);
+    if (k.acc_bufs != 1)
+        k.acc_bufs = 2;
+    const bool pair_small = block_n <= 128 && 4 * k.stage_bytes <= 100 * 1024;
+    const bool pair_short = k.acc_bufs == 1 && 2 * k.stage_bytes <= 100 * 1024;
+    plan->ctas_per_sm     = env_int("TB200_TC_CTAS_PER_SM", (pair_small || pair_short) ? 2 : 1);
+    plan->ctas_per_sm = std::max(1, std::min(plan->ctas_per_sm, 512 / std::max(32, k.acc_bufs * block_n)));
     const int smem_budget = (plan->ctas_per_sm > 1 ? 208 / plan->ctas_per_sm : 200) * 1024;
     k.num_stages = std::min(kMaxStages, smem_budget / k.stage_bytes);
     k.num_stages = std::min(k.num_stages, std::max(2, k.num_kstages * 2));
@@ -892,7 +1039,7 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     const uint32_t ab_fmt = is_f16 ? (q.in_dtype == TB200_BF16 ? 1u : 0u) : (uint32_t)env_int("TB200_TC_I8_FMT", 1);
     k.idesc = ptx::make_idesc(is_f16 ? 1u : 2u, ab_fmt, ab_fmt, 0u, q.b_mn_major ? 1u : 0u, kTileM, (uint32_t)block_n);
     int cols = 32;
-    while (cols < 2 * block_n)
+    while (cols < k.acc_bufs * block_n)
         cols *= 2;
     k.tmem_cols = cols;
 

@@ -58,9 +58,12 @@ class Timer:
         return total / iters, ("L2 flushed between calls" if need_flush else "working set larger than L2")
 
 
+SHIFT_RANGE = [32, 40]    # per-channel RESCALE shifts are drawn from this closed range (--shifts)
+
+
 def rescale_consts(ctx, r, channels):
     mult = r.integers(1 << 30, (1 << 31) - 1, size=channels, endpoint=True, dtype=np.int64).astype(np.int32)
-    shift = r.integers(32, 40, size=channels, endpoint=True, dtype=np.int64).astype(np.int8)
+    shift = r.integers(SHIFT_RANGE[0], SHIFT_RANGE[1], size=channels, endpoint=True, dtype=np.int64).astype(np.int8)
     return ctx.from_numpy(mult), ctx.from_numpy(shift)
 
 
@@ -93,7 +96,11 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="c1,c2b,c3a,c3b,c4")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--shifts", default="32,40", help="closed range of the per-channel RESCALE shifts, lo,hi")
+    ap.add_argument("--conv", default=None,
+                    help="also time one int8 CONV2D+RESCALE+CLAMP layer: N,IH,IW,IC,OC,K,stride,pad (pad on all four sides)")
     args = ap.parse_args()
+    SHIFT_RANGE[:] = [int(v) for v in args.shifts.split(",")]
     import torch
 
     hbm, bf16, src = _peaks()
@@ -101,6 +108,12 @@ def main():
     with torch.cuda.stream(stream):
         ctx = tb.Context(0, stream.cuda_stream)
         timer = Timer(ctx, stream, torch)
+        if args.conv:
+            n, ih, iw, ic, oc, k, st, pd = (int(v) for v in args.conv.split(","))
+            res = conv_i8_config(ctx, timer, "conv %s" % args.conv, n, ih, iw, ic, oc, k, k, st, [pd, pd, pd, pd], -128,
+                                 args.iters, 9)
+            print(json.dumps(res))
+            sys.stdout.flush()
         for name in args.configs.split(","):
             if name == "c1":
                 res = conv_i8_config(ctx, timer, "c1 conv1x1 1x32x32x8->16 +RESCALE", 1, 32, 32, 8, 16, 1, 1, 1,

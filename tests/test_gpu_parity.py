@@ -323,6 +323,48 @@ def test_few_channel_conv_int8(ctx, case):
     assert st == est == tb.Status.OK and np.array_equal(out, exp), kernel
 
 
+EPILOGUE_FORM_CASES = [
+    # shift range, rounding, output zero point, clamp, bias range: each picks one form of the fused RESCALE arithmetic
+    ((33, 54), "DOUBLE_ROUND", -128, (-128, 127), 1 << 30),    # high-word form, widest accumulators
+    ((33, 40), "SINGLE_ROUND", 127, (-128, 127), 1 << 24),     # high-word form without the sign-dependent term
+    ((33, 45), "DOUBLE_ROUND", -3, (-77, 101), 1 << 28),       # narrower CLAMP than int8
+    ((32, 40), "DOUBLE_ROUND", -128, (-128, 127), 1 << 24),    # a shift of exactly 32 in the block
+    ((32, 36), "SINGLE_ROUND", 5, (-128, 127), 1 << 20),
+    ((26, 40), "DOUBLE_ROUND", -128, (-128, 127), 1 << 16),    # shifts below 32: pre-scaled values, range checked
+    ((26, 31), "SINGLE_ROUND", 17, (-50, 127), 1 << 16),
+    ((50, 58), "DOUBLE_ROUND", -128, (-128, 127), 1 << 30),    # shifts above 54 take the general form
+    ((2, 62), "DOUBLE_ROUND", 0, None, 0),                      # anything goes, RESCALE without CLAMP
+]
+
+
+@pytest.mark.parametrize("case", EPILOGUE_FORM_CASES)
+def test_fused_rescale_forms(ctx, case):
+    """Every arithmetic form of the tensor-core kernel's RESCALE epilogue against apply_scale_32 of the oracle
+    (reference_model/include/quant_util.h:49-80), on accumulators that span the whole accepted range."""
+    (slo, shi), rounding, ozp, clamp, brange = case
+    r = util.rng(900 + EPILOGUE_FORM_CASES.index(case))
+    N, H, W, IC, OC = 2, 9, 16, 64, 96
+    x, w, _ = util.conv_int8_case(r, N, H, W, IC, OC, 1, 1)
+    shift = r.integers(slo, shi, size=OC, endpoint=True).astype(np.int8)
+    mult = r.integers(1 << 30, (1 << 31) - 1, size=OC, endpoint=True, dtype=np.int64).astype(np.int32)
+    # biases spread the accumulators over the range each column's shift accepts (|v| < 2^(shift-1), int32 at most)
+    lim = np.minimum((1 << np.minimum(shift.astype(np.int64) - 1, 31)) - (1 << 22), (1 << 31) - (1 << 22) - 1)
+    lim = np.maximum(lim, 0)
+    b = (r.uniform(-1, 1, size=OC) * np.minimum(lim, brange)).astype(np.int64).astype(np.int32)
+    if slo < 24:
+        w[shift < 24] = 0    # tiny shifts accept tiny values only: keep those columns at their bias
+        small = (1 << np.clip(shift.astype(np.int64) - 1, 0, 23)) - 1
+        b[shift < 24] = (r.uniform(-1, 1, size=OC) * small).astype(np.int32)[shift < 24]
+    args = ([0, 0, 0, 0], [1, 1], [1, 1], 0, 0)
+    resc = (mult, shift, ozp, rounding)
+    est, exp = oracle_conv_i8(x, w, b, *args, rescale=resc, clamp=clamp)
+    assert est == orc.VALID
+    st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=clamp)
+    assert kernel == "tc_gemm_i8_rescale" and st == tb.Status.OK
+    assert np.array_equal(out, exp), "rescaled outputs differ: %d of %d" % ((out != exp).sum(), exp.size)
+    assert len(np.unique(exp)) > 4    # the case must not saturate everywhere
+
+
 def test_rescale_require_reports_unpredictable(ctx):
     # shift 30 with |acc| >= 2^29 violates apply_scale_32's range check (quant_util.h:53-62)
     x = np.full((1, 4, 4, 64), 127, np.int8)
@@ -682,6 +724,58 @@ def test_residual_add(ctx):
         ctx.set_kernel_policy(old)
         assert to.download(check=False)[0] == tb.Status.UNPREDICTABLE
     _free(ta, to, *consts)
+
+
+def test_residual_add_table(ctx):
+    """Large per-tensor joins go through the 65536-entry byte-pair table: same bits as the five separate nodes, and the
+    REQUIRE verdict depends on which table entries the data actually touches."""
+    r = util.rng(81)
+    shape = (8, 64, 64, 128)    # 2^22 elements: the smallest size that takes the table kernel
+    ma, sa, mb, sb, mo, so = [1 << 30], [11], [1518500250], [12], [1270000000], [49]
+    consts = [ctx.from_numpy(np.asarray(v, np.int32)) for v in (ma, mb, mo)] + \
+             [ctx.from_numpy(np.asarray(v, np.int8)) for v in (sa, sb, so)]
+    for clamp in ((-128, 127), (-100, 90)):
+        a = r.integers(-128, 128, size=shape).astype(np.int8)
+        b = r.integers(-128, 128, size=shape).astype(np.int8)
+        # runs of equal values next to varying ones (the shared-memory bank pattern the table layout is built for)
+        b[:, ::2] = -128
+        _, ea = orc.rescale(a, ma, sa, False, True, "SINGLE_ROUND", -128, 0, 8, 32)
+        _, eb = orc.rescale(b, mb, sb, False, True, "SINGLE_ROUND", 3, 0, 8, 32)
+        _, es = orc.add(ea, eb)
+        est, eo = orc.rescale(es, mo, so, False, True, "DOUBLE_ROUND", 0, -128, 32, 8)
+        _, eo = orc.clamp(eo, *clamp)
+        ta, tbb, to = ctx.from_numpy(a), ctx.from_numpy(b), ctx.empty(I8, shape)
+        ctx.residual_add(ta, tb.RescaleAttr(consts[0], consts[3], -128, 0), tbb,
+                         tb.RescaleAttr(consts[1], consts[4], 3, 0),
+                         tb.RescaleAttr(consts[2], consts[5], 0, -128, rounding="DOUBLE_ROUND"), to, clamp=clamp)
+        assert ctx.last_kernel() == "residual_add_i8_table"
+        st, out = to.download()
+        assert st == est == tb.Status.OK and np.array_equal(out.astype(np.int32), eo)
+        _free(ta, tbb, to)
+    _free(*consts)
+    # First leg with shift 8 accepts |v - zp| < 128 only.  Inputs below 0 stay inside (v + 128 <= 127); the table holds
+    # failing entries for v >= 0, and the status must follow the data, not the table.
+    consts = [ctx.from_numpy(np.asarray([1 << 20], np.int32)), ctx.from_numpy(np.asarray([8], np.int8)),
+              ctx.from_numpy(np.asarray([1 << 30], np.int32)), ctx.from_numpy(np.asarray([40], np.int8))]
+    leg, outleg = tb.RescaleAttr(consts[0], consts[1], -128, 0), tb.RescaleAttr(consts[2], consts[3], 0, 0)
+    lo = r.integers(-128, 0, size=shape).astype(np.int8)
+    for poke, want in ((None, tb.Status.OK), (5, tb.Status.UNPREDICTABLE)):
+        a = lo.copy()
+        if poke is not None:
+            a[3, 17, 9, 77] = poke
+        est, ea = orc.rescale(a, [1 << 20], [8], False, True, "SINGLE_ROUND", -128, 0, 8, 32)
+        assert (est == orc.UNPREDICTABLE) == (want == tb.Status.UNPREDICTABLE)
+        ta, to = ctx.from_numpy(a), ctx.empty(I8, shape)
+        ctx.residual_add(ta, leg, ta, leg, outleg, to)
+        assert ctx.last_kernel() == "residual_add_i8_table"
+        st, out = to.download(check=False)
+        assert st == want
+        if want == tb.Status.OK:
+            _, es = orc.add(ea, ea)
+            _, eo = orc.rescale(es, [1 << 30], [40], False, True, "SINGLE_ROUND", 0, 0, 32, 8)
+            assert np.array_equal(out.astype(np.int32), eo)
+        _free(ta, to)
+    _free(*consts)
 
 
 def test_pools(ctx):
