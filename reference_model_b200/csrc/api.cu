@@ -1088,7 +1088,8 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
         const size_t padb_bytes = pad_b ? (((size_t)N * C * b_ld * es_in + 255) & ~(size_t)255) : 0;
         q.b_ld = b_ld;
         std::string why;
-        if (tc_gemm_supported(q, &why))
+        // (the CTA-pair kernel takes K tails the single-CTA kernel does not)
+        if (tc_gemm_pair_supported(q, ctx->num_sms) || tc_gemm_supported(q, &why))
         {
             const bool need_sums = int_path && (a_zp != 0 || b_zp != 0);
             const int Wpad       = (W + 255) / 256 * 256;

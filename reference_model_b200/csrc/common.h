@@ -193,6 +193,10 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& p);
 // Total tile count of a problem and the tiles per row block (per batch for MATMUL); tiles are numbered batch-major.
 bool tc_gemm_tile_counts(const TcProblem& p, int* num_tiles, int* tiles_per_row_block);
 
+// int8 MATMUL on CTA pairs (tc_gemm_pair.cu): large MN-major-B problems with int32 output; tc_gemm_launch routes to it
+bool tc_gemm_pair_supported(const TcProblem& p, int num_sms);
+tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& p);
+
 // fp32 SGEMM on CUDA cores (sgemm_f32.cu): out[n] = a[n] x b[n], a [N,H,C], b [N,C,W]
 tb200_status sgemm_f32_launch(tb200_ctx* ctx, const float* a, const float* b, float* out, int N, int H, int C, int W);
 

@@ -554,7 +554,13 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     if (row_valid)
                     {
                         int32_t* o = reinterpret_cast<int32_t*>(p.out) + pix * p.OC + col;
-                        if (nvalid == 32 && ((p.OC & 3) == 0))
+                        if (nvalid == 32 && ((p.OC & 7) == 0) && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0)
+                        {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8)
+                                ptx::st_global_v8(o + i, v[i], v[i + 1], v[i + 2], v[i + 3], v[i + 4], v[i + 5], v[i + 6], v[i + 7]);
+                        }
+                        else if (nvalid == 32 && ((p.OC & 3) == 0))
                         {
 #pragma unroll
                             for (int i = 0; i < 32; i += 4)
@@ -600,10 +606,18 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                             for (int q = 0; q < 8; q++)
                                 w[q] = rescale32_high_x4<false, true>(&v[4 * q], &epi_cols[c * 32 + 4 * q], p.clamp_lo, p.clamp_hi);
                         }
-                        // Each lane holds the 32 output bytes of its own row.  Two 16-byte stores per lane would hand the
-                        // memory system half-filled 32-byte sectors; instead the two lanes of a pair swap halves so that
-                        // one store instruction writes the even lane's row and the next one the odd lane's row, each
-                        // sector complete.
+                        // Each lane holds the 32 output bytes of its own row: one 32-byte store hands the memory system a
+                        // complete sector (two 16-byte stores would deliver two half-filled ones).  Outputs that are not
+                        // 32-byte aligned (views) swap halves between the two lanes of a pair instead, so that one store
+                        // instruction writes the even lane's row and the next one the odd lane's row.
+                        const bool skip = (p.debug & 32) && w[0] != 0x12345678u;
+                        if ((reinterpret_cast<uintptr_t>(p.out) & 31) == 0)
+                        {
+                            if (row_valid && !skip)
+                                ptx::st_global_v8(reinterpret_cast<int8_t*>(p.out) + pix * p.OC + col, w[0], w[1], w[2], w[3],
+                                                  w[4], w[5], w[6], w[7]);
+                        }
+                        else
                         {
                             const bool odd = (lane & 1) != 0;
                             uint32_t other[4];
@@ -614,8 +628,6 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                             int8_t* o_pair = reinterpret_cast<int8_t*>(p.out) + pix_pair * p.OC + col + (odd ? 16 : 0);
                             const uint4 mine   = odd ? make_uint4(w[4], w[5], w[6], w[7]) : make_uint4(w[0], w[1], w[2], w[3]);
                             const uint4 theirs = make_uint4(other[0], other[1], other[2], other[3]);
-                            const bool skip = (p.debug & 32) && w[0] != 0x12345678u;
-                            // first instruction: the even lane's row, second: the odd lane's row
                             if ((odd ? row_valid_pair : row_valid) && !skip)
                                 *reinterpret_cast<uint4*>(odd ? o_pair : o_own) = odd ? theirs : mine;
                             if ((odd ? row_valid : row_valid_pair) && !skip)
@@ -1131,6 +1143,8 @@ bool tc_gemm_tile_counts(const TcProblem& p, int* num_tiles, int* tiles_per_row_
 
 tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
 {
+    if (tc_gemm_pair_supported(q, ctx->num_sms))
+        return tc_gemm_pair_launch(ctx, q);
     TcPlan plan;
     std::string why;
     if (!make_plan(q, ctx->num_sms, &plan, &why))

@@ -1,0 +1,473 @@
+// int8 MATMUL on CTA pairs (tcgen05 cta_group::2) for sm_100a.
+//
+// OpMatMul with int8 operands and int32 output (reference_model/src/ops/tensor_ops.cc:1530-1610), for shapes large
+// enough to fill 256 x 256 output tiles.  The kernel is launched as clusters of two CTAs on neighbouring SMs; a pair
+// owns one 256 x 256 tile at a time:
+//   * each CTA loads its own 128 rows of A and its own 128 columns of B per 128-byte K chunk (TMA, no multi-destination
+//     copies); the tensor cores of both SMs read B from both shared memories, so a pair moves 2/3 of the bytes two
+//     independent 128 x 256 tiles would, which is what bounds the single-CTA kernel at this size (L2 -> SM traffic)
+//   * one thread of the pair's first CTA issues tcgen05.mma.cta_group::2 (M = 256, N = 256, K = 32 bytes); measured
+//     at 128 SM cycles per instruction (8192 MAC per cycle and SM) against 171 for the single-CTA form
+//   * accumulators live in both CTAs' TMEM (128 rows x 256 columns each, two buffers); each CTA's eight epilogue warps
+//     add the zero-point terms and store their own rows
+// Completion signals cross the pair: TMA byte counts of both CTAs land on the first CTA's "full" barrier,
+// tcgen05.commit arrives on the "empty" / "accumulator ready" barriers of both, and every epilogue warp arrives on the
+// first CTA's "accumulator free" barrier.  Every wait is bounded; a wait that gives up sets TB200_DEV_TIMEOUT and all
+// roles drain to the common exit.
+#include <algorithm>
+#include <cuda.h>
+#include <cstring>
+#include <cuda_runtime.h>
+#include <mutex>
+
+#include "common.h"
+#include "ptx_sm100.cuh"
+
+namespace tb200
+{
+
+namespace
+{
+
+constexpr int kPairEpiWarps   = 16;       // four per TMEM lane quarter, each taking every fourth 32-column chunk
+constexpr int kPairThreads    = 64 + 32 * kPairEpiWarps;    // TMA warp, MMA warp, epilogue warps
+constexpr int kPairMaxStages  = 8;
+constexpr int kPairChunkBytes = 16384;    // 128 rows x 128 bytes (A: rows x K, B: K rows x columns), 128-byte swizzle
+constexpr int kPairTmemCols   = 512;      // two accumulator buffers of 256 columns
+constexpr long long kPairWaitLimit = 4000000000LL;    // about two seconds of SM clock
+
+struct PairParams
+{
+    CUtensorMap tmA;    // (C, H, batch), box 128 x 128 x 1
+    CUtensorMap tmB;    // (W, C, batch), box 128 x 128 x 1
+    int NB, H, C, W;
+    int tiles_m, tiles_w, num_tiles;    // 256 x 256 tiles, numbered batch-major, columns fastest
+    int total_chunks;                   // 128-byte K chunks
+    int ksub, num_stages, stage_bytes;  // K chunks per stage (one tcgen05.commit per stage), ring depth
+    uint64_t a_desc_hi, b_desc_hi;
+    uint32_t idesc;
+    int32_t* out;
+    const int32_t* row_corr;    // [batch * H] or null
+    const int32_t* corr;        // [batch][corr_stride] or null; corr_stride a multiple of 256 that covers W
+    int corr_stride;
+    int debug;                  // diagnostic bit mask: 1 skip epilogue memory work, 2 skip MMA issue, 4 skip loads
+    int* status;
+};
+
+struct PairTile
+{
+    int n, m0, w0;
+};
+
+__device__ __forceinline__ PairTile decode_pair_tile(const PairParams& p, int tile)
+{
+    PairTile t;
+    t.w0  = (tile % p.tiles_w) * 256;
+    int r = tile / p.tiles_w;
+    t.m0  = (r % p.tiles_m) * 256;
+    t.n   = r / p.tiles_m;
+    return t;
+}
+
+__global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __grid_constant__ PairParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // identical layout in both CTAs of a pair: remote signals address a barrier by its offset
+    __shared__ __align__(8) uint64_t bar_full[kPairMaxStages];     // used in the first CTA: bytes of both CTAs
+    __shared__ __align__(8) uint64_t bar_empty[kPairMaxStages];    // per CTA: stage consumed by the MMAs
+    __shared__ __align__(8) uint64_t bar_tmem_full[2];          // per CTA: accumulator buffer complete
+    __shared__ __align__(8) uint64_t bar_tmem_empty[2];         // first CTA: buffer drained by both CTAs' epilogues
+    __shared__ uint32_t tmem_base_holder;
+
+    const int warp          = threadIdx.x >> 5;
+    const int lane          = threadIdx.x & 31;
+    const uint32_t rank     = ptx::cluster_ctarank();
+    const int cluster_id    = blockIdx.x >> 1;
+    const int num_clusters  = gridDim.x >> 1;
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+
+    if (threadIdx.x == 0)
+    {
+        for (int s = 0; s < p.num_stages; s++)
+        {
+            ptx::mbar_init(ptx::smem_u32(&bar_full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bar_empty[s]), 1);
+        }
+        for (int a = 0; a < 2; a++)
+        {
+            ptx::mbar_init(ptx::smem_u32(&bar_tmem_full[a]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bar_tmem_empty[a]), 2 * kPairEpiWarps);
+        }
+        ptx::fence_barrier_init();
+        ptx::prefetch_tmap(&p.tmA);
+        ptx::prefetch_tmap(&p.tmB);
+    }
+    if (warp == 1)
+    {
+        ptx::tmem_alloc_pair(ptx::smem_u32(&tmem_base_holder), kPairTmemCols);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    // no signal may reach the other CTA before its barriers exist
+    ptx::cluster_sync();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_holder;
+
+    if (warp == 0)
+    {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0)
+        {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters)
+            {
+                const PairTile t = decode_pair_tile(p, tile);
+                const int m0 = t.m0 + (int)rank * 128;
+                const int w0 = t.w0 + (int)rank * 128;
+                int chunks_left = p.total_chunks;
+                int k = 0;
+                while (chunks_left > 0)
+                {
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, kPairWaitLimit))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    const int nch = min(p.ksub, chunks_left);
+                    chunks_left -= nch;
+                    const uint32_t full_local = ptx::smem_u32(&bar_full[stage]);
+                    if (p.debug & 4)
+                    {
+                        if (rank == 0)
+                            ptx::mbar_arrive(full_local);
+                    }
+                    else
+                    {
+                        // the first CTA arms the barrier with the bytes of both CTAs; each CTA's copies report there
+                        if (rank == 0)
+                            ptx::mbar_arrive_expect_tx(full_local, (uint32_t)(nch * 4 * kPairChunkBytes));
+                        const uint32_t full_first = ptx::map_to_cta(full_local, 0);
+                        const uint32_t sA = smem_base + (uint32_t)(stage * p.stage_bytes);
+                        const uint32_t sB = sA + (uint32_t)(p.ksub * kPairChunkBytes);
+                        for (int j = 0; j < nch; j++)
+                        {
+                            ptx::tma_load_3d_pair(sA + (uint32_t)(j * kPairChunkBytes), &p.tmA, full_first, k, m0, t.n);
+                            ptx::tma_load_3d_pair(sB + (uint32_t)(j * kPairChunkBytes), &p.tmB, full_first, w0, k, t.n);
+                            k += 128;
+                        }
+                    }
+                    if (++stage == p.num_stages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok)
+                atomicOr(p.status, TB200_DEV_TIMEOUT);
+        }
+    }
+    else if (warp == 1)
+    {
+        // ------------------------------------------------------------------ MMA issuer (first CTA of the pair)
+        if (lane == 0 && rank == 0)
+        {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            const bool issue = !(p.debug & 2);
+            for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters)
+            {
+                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, kPairWaitLimit))
+                {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
+                uint32_t accum  = 0;    // the first MMA of a tile overwrites the accumulator
+                int chunks_left = p.total_chunks;
+                while (chunks_left > 0)
+                {
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_full[stage]), phase, kPairWaitLimit))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const int nch = min(p.ksub, chunks_left);
+                    chunks_left -= nch;
+                    if (issue)
+                    {
+                        const uint32_t sA = smem_base + (uint32_t)(stage * p.stage_bytes);
+                        const uint32_t sB = sA + (uint32_t)(p.ksub * kPairChunkBytes);
+                        for (int j = 0; j < nch; j++)
+                        {
+                            uint64_t ad = ptx::smem_desc(p.a_desc_hi, sA + (uint32_t)(j * kPairChunkBytes));
+                            uint64_t bd = ptx::smem_desc(p.b_desc_hi, sB + (uint32_t)(j * kPairChunkBytes));
+#pragma unroll
+                            for (int m = 0; m < 4; m++)
+                            {
+                                ptx::mma_i8_ss_pair(d_tmem, ad, bd, p.idesc, accum);
+                                accum = 1;
+                                ad += 2;      // 32 bytes of K inside the swizzled row
+                                bd += 256;    // 32 K rows of 128 bytes
+                            }
+                        }
+                    }
+                    // frees the stage in both CTAs once the MMAs above have read it
+                    ptx::mma_commit_pair(ptx::smem_u32(&bar_empty[stage]), 3);
+                    if (++stage == p.num_stages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok)
+                    break;
+                ptx::mma_commit_pair(ptx::smem_u32(&bar_tmem_full[acc]), 3);
+                acc ^= 1;
+                if (acc == 0)
+                    acc_phase ^= 1u;
+            }
+            if (!ok)
+                atomicOr(p.status, TB200_DEV_TIMEOUT);
+        }
+    }
+    else
+    {
+        // ------------------------------------------------------------------ epilogue warps (both CTAs)
+        const int quarter = warp & 3;           // TMEM lane quarter this warp may read
+        const int slot    = (warp - 2) >> 2;    // the warps of a quarter take the 32-column chunks round robin
+        const int row     = quarter * 32 + lane;
+        const uint32_t empty_first[2] = { ptx::map_to_cta(ptx::smem_u32(&bar_tmem_empty[0]), 0),
+                                          ptx::map_to_cta(ptx::smem_u32(&bar_tmem_empty[1]), 0) };
+        const bool wide_ok = (reinterpret_cast<uintptr_t>(p.out) & 31) == 0 && !(p.debug & 8);
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters)
+        {
+            const PairTile t = decode_pair_tile(p, tile);
+            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_full[acc]), acc_phase, kPairWaitLimit);
+            // the whole warp must agree before the warp-collective TMEM loads
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok)
+                break;
+            ptx::tc_fence_after_sync();
+
+            const int m          = t.m0 + (int)rank * 128 + row;
+            const bool row_valid = m < p.H;
+            const int64_t orow   = (int64_t)t.n * p.H + m;
+            int32_t rc = 0;
+            if (p.row_corr != nullptr && row_valid)
+                rc = __ldg(p.row_corr + orow);
+            const int32_t* corr_row = p.corr != nullptr ? p.corr + (int64_t)t.n * p.corr_stride : nullptr;
+            int32_t* out_row        = p.out + orow * p.W;
+            const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * 256);
+            for (int c = slot; c < 8; c += kPairEpiWarps / 4)
+            {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(taddr_row + (uint32_t)(c * 32), v);
+                ptx::tmem_ld_wait();
+                const int col = t.w0 + c * 32;
+                if (col >= p.W || (p.debug & 1))
+                    continue;
+                if (corr_row != nullptr)
+                {
+                    // the table is padded to a multiple of 256 columns: unconditional 128-bit loads
+                    const int4* cp = reinterpret_cast<const int4*>(corr_row + col);
+#pragma unroll
+                    for (int q = 0; q < 8; q++)
+                    {
+                        const int4 cv = __ldg(cp + q);
+                        v[4 * q + 0] += (uint32_t)cv.x + (uint32_t)rc;
+                        v[4 * q + 1] += (uint32_t)cv.y + (uint32_t)rc;
+                        v[4 * q + 2] += (uint32_t)cv.z + (uint32_t)rc;
+                        v[4 * q + 3] += (uint32_t)cv.w + (uint32_t)rc;
+                    }
+                }
+                else
+                {
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        v[i] += (uint32_t)rc;
+                }
+                if (!row_valid)
+                    continue;
+                int32_t* o = out_row + col;
+                if (col + 32 <= p.W && (p.W & 7) == 0 && wide_ok)
+                {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8)
+                        ptx::st_global_v8(o + i, v[i], v[i + 1], v[i + 2], v[i + 3], v[i + 4], v[i + 5], v[i + 6], v[i + 7]);
+                }
+                else if (col + 32 <= p.W && (p.W & 3) == 0)
+                {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<int4*>(o + i) = make_int4((int)v[i], (int)v[i + 1], (int)v[i + 2], (int)v[i + 3]);
+                }
+                else
+                {
+                    const int nvalid = min(32, p.W - col);
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if (i < nvalid)
+                            o[i] = (int32_t)v[i];
+                }
+            }
+            // this warp has read its part of the buffer: one arrival per warp on the first CTA's barrier
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                ptx::mbar_arrive_cluster(empty_first[acc]);
+            acc ^= 1;
+            if (acc == 0)
+                acc_phase ^= 1u;
+        }
+        if (!ok && lane == 0)
+            atomicOr(p.status, TB200_DEV_TIMEOUT);
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    // Neither CTA may leave (or free its TMEM) while the other can still signal it or read its shared memory.
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();
+    if (warp == 1)
+    {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, kPairTmemCols);
+    }
+}
+
+typedef CUresult (*PFN_encodeTiledPair)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                        const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                        CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+PFN_encodeTiledPair pair_encode_fn()
+{
+    static PFN_encodeTiledPair fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_encodeTiledPair>(sym);
+    });
+    return fn;
+}
+
+int pair_env_int(const char* name, int dflt)
+{
+    const char* v = getenv(name);
+    return v ? atoi(v) : dflt;
+}
+
+}    // namespace
+
+// MATMUL problems as api.cu describes them: A [1][batch][H][C], B MN-major [batch][C][W], int32 output.
+bool tc_gemm_pair_supported(const TcProblem& q, int num_sms)
+{
+    if (pair_env_int("TB200_TC_PAIR", 1) == 0)
+        return false;
+    if (q.in_dtype != TB200_INT8 || q.epi != TC_EPI_I32 || q.out_dtype != TB200_INT32 || !q.b_mn_major)
+        return false;
+    if (q.N != 1 || q.KH != 1 || q.KW != 1 || q.stride_x != 1 || q.stride_y != 1 || q.pad_t || q.pad_l)
+        return false;
+    if (q.a_stride_w || q.a_stride_h || q.a_stride_n || q.corr_classes || q.tile_begin || q.tile_end)
+        return false;
+    if (q.corr != nullptr && (q.corr_stride % 256 != 0 || q.corr_stride < q.OC || q.corr_ystride != q.corr_stride))
+        return false;
+    const int64_t ldb = q.b_ld ? q.b_ld : q.OC;
+    // whole 256 x 256 tiles must dominate, and TMA wants 16-byte row pitches
+    if (q.IW < 256 || q.OC < 256 || q.IC < 128 || q.IC % 16 != 0 || ldb % 16 != 0)
+        return false;
+    if ((reinterpret_cast<uintptr_t>(q.a) | reinterpret_cast<uintptr_t>(q.b) | reinterpret_cast<uintptr_t>(q.out)) & 15)
+        return false;
+    // fewer tiles than half the pairs: the single-CTA kernel spreads such a problem over more SMs
+    const int64_t tiles = (int64_t)q.IH * ((q.IW + 255) / 256) * ((q.OC + 255) / 256);
+    return tiles >= num_sms / 4 && tiles < (1LL << 30);
+}
+
+tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
+{
+    PFN_encodeTiledPair enc = pair_encode_fn();
+    if (!enc)
+        return fail(ctx, TB200_INTERNAL, "cuTensorMapEncodeTiled is not available from the driver");
+    PairParams k;
+    memset(&k, 0, sizeof(k));
+    k.NB = q.IH;
+    k.H  = q.IW;
+    k.C  = q.IC;
+    k.W  = q.OC;
+    const int64_t ldb = q.b_ld ? q.b_ld : q.OC;
+    k.tiles_m      = (k.H + 255) / 256;
+    k.tiles_w      = (k.W + 255) / 256;
+    k.num_tiles    = k.NB * k.tiles_m * k.tiles_w;
+    k.total_chunks = (k.C + 127) / 128;
+    // A: K-major rows of 128 bytes, 8-row groups 1024 bytes apart.  B: MN-major, one 128-byte atom of columns per CTA,
+    // K rows 128 bytes apart, 8-row groups 1024 bytes apart; an MMA's 32 K rows span 4096 bytes.
+    k.a_desc_hi = ptx::make_smem_desc_hi(16, 1024, 2);
+    k.b_desc_hi = ptx::make_smem_desc_hi(kPairChunkBytes, 1024, 2);
+    k.idesc     = ptx::make_idesc(2u, 1u, 1u, 0u, 1u, 256u, 256u);
+    k.out         = reinterpret_cast<int32_t*>(q.out);
+    k.row_corr    = q.row_corr;
+    k.corr        = q.corr;
+    k.corr_stride = q.corr_stride;
+    k.debug       = pair_env_int("TB200_TC_DEBUG", 0);
+    k.status      = ctx->d_status;
+
+    cuuint64_t a_dims[3]    = { (cuuint64_t)k.C, (cuuint64_t)k.H, (cuuint64_t)k.NB };
+    cuuint64_t a_strides[2] = { (cuuint64_t)k.C, (cuuint64_t)k.C * (cuuint64_t)k.H };
+    cuuint64_t b_dims[3]    = { (cuuint64_t)k.W, (cuuint64_t)k.C, (cuuint64_t)k.NB };
+    cuuint64_t b_strides[2] = { (cuuint64_t)ldb, (cuuint64_t)ldb * (cuuint64_t)k.C };
+    cuuint32_t box[3]       = { 128, 128, 1 };
+    cuuint32_t estr[3]      = { 1, 1, 1 };
+    CUresult r = enc(&k.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(q.a), a_dims, a_strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(ctx, TB200_INTERNAL, "tensor map for A rejected (CUresult %d)", (int)r);
+    r = enc(&k.tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(q.b), b_dims, b_strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(ctx, TB200_INTERNAL, "tensor map for B rejected (CUresult %d)", (int)r);
+
+    // The ring holds what is in flight from L2: the kernel is bound by latency x bytes in flight, so it takes all the
+    // shared memory there is.  One commit per stage; 4 MMAs (one chunk) per commit costs tensor-pipe time, 8 do not.
+    k.ksub        = std::max(1, std::min(4, pair_env_int("TB200_PAIR_KSUB", 2)));
+    k.stage_bytes = 2 * k.ksub * kPairChunkBytes;
+    k.num_stages  = std::min(kPairMaxStages, std::max(2, pair_env_int("TB200_PAIR_STAGES", (224 * 1024) / k.stage_bytes)));
+    const int smem_bytes = k.num_stages * k.stage_bytes + 1024;
+    TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(tc_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    const int clusters = std::max(1, std::min(k.num_tiles, ctx->num_sms / 2));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim          = dim3((unsigned)(2 * clusters));
+    cfg.blockDim         = dim3(kPairThreads);
+    cfg.dynamicSmemBytes = (size_t)smem_bytes;
+    cfg.stream           = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs    = attr;
+    cfg.numAttrs = 1;
+    timer_begin(ctx);
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, tc_gemm_pair_kernel, k);
+    timer_end(ctx);
+    if (le != cudaSuccess)
+        return fail(ctx, TB200_INTERNAL, "launch of tc_gemm_pair_i8_i32 failed: %s", cudaGetErrorString(le));
+    return post_launch(ctx, "tc_gemm_pair_i8_i32");
+}
+
+}    // namespace tb200

@@ -456,7 +456,11 @@ def test_slice_view_as_conv_input_and_reshape(ctx):
 
 # ------------------------------------------------------------------------------------------- MATMUL
 MATMUL_I8_CASES = [(2, 256, 256, 256, 3, -2), (1, 128, 384, 512, 0, 0), (3, 200, 130, 96, -7, 5), (1, 130, 4096, 272, 3, -2),
-                   (2, 5, 7, 3, 4, 15)]
+                   (2, 5, 7, 3, 4, 15),
+                   # enough 256 x 256 tiles for the CTA-pair kernel: ragged rows / columns / K, odd chunk counts, a B
+                   # pitch that has to be padded (W = 300), no zero points
+                   (40, 300, 224, 272, 3, -2), (10, 512, 384, 512, -128, 127), (12, 520, 640, 300, 0, 0),
+                   (37, 256, 128, 256, 1, 0)]
 
 
 @pytest.mark.parametrize("N,H,C,W,azp,bzp", MATMUL_I8_CASES)
@@ -475,6 +479,8 @@ def test_matmul_int8(ctx, N, H, C, W, azp, bzp):
         _free(ta, tbb, to)
         assert st == tb.Status.OK
         assert np.array_equal(out, exp), "%s: %d of %d differ" % (kernel, (out != exp).sum(), exp.size)
+        if policy == 0 and N >= 10:
+            assert kernel == "tc_gemm_pair_i8_i32"
     # the host-buffer entry point
     out = np.empty((N, H, W), np.int32)
     assert ctx.matmul_host(a, b, out, azp, bzp) == tb.Status.OK
