@@ -13,6 +13,13 @@ using namespace tb200;
 namespace tb200
 {
 
+// diagnostic switches read from the environment (defaults are what the tests and the bench run)
+static bool env_flag(const char* name, int dflt)
+{
+    const char* v = getenv(name);
+    return (v ? atoi(v) : dflt) != 0;
+}
+
 tb200_status ensure_scratch(tb200_ctx* ctx, size_t bytes)
 {
     if (bytes <= ctx->scratch_bytes)
@@ -1112,7 +1119,15 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
             {
                 int32_t* row_corr = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(ctx->scratch) + padb_bytes);
                 int32_t* col_corr = row_corr + ((rows + 3) & ~(size_t)3);
-                if (b_zp != 0)
+                // the CTA-pair kernel sums the rows of A itself while they sit in shared memory (saves one pass over A)
+                const bool fuse_rows = b_zp != 0 && tc_gemm_pair_supported(q, ctx->num_sms) && env_flag("TB200_FUSE_ROW_SUMS", 1);
+                if (fuse_rows)
+                {
+                    q.fuse_row_sums = 1;
+                    q.a_zp          = a_zp;
+                    q.b_zp          = b_zp;
+                }
+                else if (b_zp != 0)
                     q.row_corr = row_corr;
                 if (a_zp != 0)
                 {
@@ -1124,7 +1139,7 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
                 auto launch_sums = [&](cudaStream_t stream, int lo, int hi) -> tb200_status {
                     const int nb  = hi - lo;
                     int launches  = 0;
-                    if (b_zp != 0)
+                    if (b_zp != 0 && !fuse_rows)
                     {
                         const int block = 256;
                         matmul_row_corr_kernel<<<grid_for(ctx, (int64_t)nb * H * 32, block), block, 0, stream>>>(

@@ -169,6 +169,10 @@ struct TcProblem
     tb200_dtype out_dtype;
     void* out;
     const int32_t* row_corr;    // [N*OH*OW] added to every column of a row, or null
+    // MATMUL on the CTA-pair kernel: derive the row term from A inside the kernel instead (row_corr null):
+    // row term = -b_zp * sum_k A[row, k] + IC * a_zp * b_zp
+    int fuse_row_sums;
+    int32_t a_zp, b_zp;
     // per-column additive constants, padded: [classes][corr_stride]; corr_stride must be a multiple of 256 and cover
     // OC.  corr_classes != 0: the table has (KH+1)^2 (KW+1)^2 rows indexed by the rectangle of in-scope filter taps
     // ((ky_lo*(KH+1)+ky_hi)*(KW+1)+kx_lo)*(KW+1)+kx_hi.  corr_ystride: MATMUL, elements to advance per batch.

@@ -227,10 +227,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
     return r;
 }
 
-// arrive on an mbarrier that may live in the other CTA of the cluster (address from map_to_cta)
+// Arrive on an mbarrier that may live in the other CTA of the cluster (address from map_to_cta).  Relaxed: the
+// barriers signalled this way guard tensor memory (ordered by tcgen05.fence) or shared memory filled by the TMA unit
+// whose completion the signalling thread has observed; a release at cluster scope makes the arriving thread wait until
+// all of its earlier memory operations have been performed, about a microsecond each time.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
 {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
 // TMA tile load into this CTA's shared memory whose completion bytes are counted on an mbarrier of either CTA of the

@@ -29,8 +29,9 @@ namespace tb200
 namespace
 {
 
-constexpr int kPairEpiWarps   = 16;       // four per TMEM lane quarter, each taking every fourth 32-column chunk
-constexpr int kPairThreads    = 64 + 32 * kPairEpiWarps;    // TMA warp, MMA warp, epilogue warps
+constexpr int kPairEpiWarps   = 8;        // two per TMEM lane quarter, each taking every second 32-column chunk
+constexpr int kPairSumWarps   = 4;        // row sums of A straight from the shared-memory ring (b_zp term of MATMUL)
+constexpr int kPairThreads    = 64 + 32 * (kPairEpiWarps + kPairSumWarps);    // TMA warp, MMA warp, epilogue, sums
 constexpr int kPairMaxStages  = 8;
 constexpr int kPairChunkBytes = 16384;    // 128 rows x 128 bytes (A: rows x K, B: K rows x columns), 128-byte swizzle
 constexpr int kPairTmemCols   = 512;      // two accumulator buffers of 256 columns
@@ -48,6 +49,10 @@ struct PairParams
     uint32_t idesc;
     int32_t* out;
     const int32_t* row_corr;    // [batch * H] or null
+    // fuse_row_sums: the b_zp term of every output row, -b_zp * sum_k A[row, k] + C * a_zp * b_zp, is worked out inside
+    // the kernel from the A tiles as they pass through shared memory (row_corr is then null)
+    int fuse_row_sums;
+    int32_t a_zp, b_zp;
     const int32_t* corr;        // [batch][corr_stride] or null; corr_stride a multiple of 256 that covers W
     int corr_stride;
     int debug;                  // diagnostic bit mask: 1 skip epilogue memory work, 2 skip MMA issue, 4 skip loads
@@ -77,6 +82,10 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
     __shared__ __align__(8) uint64_t bar_empty[kPairMaxStages];    // per CTA: stage consumed by the MMAs
     __shared__ __align__(8) uint64_t bar_tmem_full[2];          // per CTA: accumulator buffer complete
     __shared__ __align__(8) uint64_t bar_tmem_empty[2];         // first CTA: buffer drained by both CTAs' epilogues
+    __shared__ __align__(8) uint64_t bar_go[kPairMaxStages];    // second CTA: "stage full" relayed by the first CTA
+    __shared__ __align__(8) uint64_t bar_rs_full[2];            // per CTA: row sums of an accumulator buffer's tile ready
+    __shared__ __align__(8) uint64_t bar_rs_empty[2];           // per CTA: epilogue has read them
+    __shared__ int32_t row_sums[2][128];
     __shared__ uint32_t tmem_base_holder;
 
     const int warp          = threadIdx.x >> 5;
@@ -91,12 +100,16 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
         for (int s = 0; s < p.num_stages; s++)
         {
             ptx::mbar_init(ptx::smem_u32(&bar_full[s]), 1);
-            ptx::mbar_init(ptx::smem_u32(&bar_empty[s]), 1);
+            // a stage is free when the MMAs have read it and, with fused row sums, the sum warps have too
+            ptx::mbar_init(ptx::smem_u32(&bar_empty[s]), 1 + (p.fuse_row_sums ? kPairSumWarps : 0));
+            ptx::mbar_init(ptx::smem_u32(&bar_go[s]), 1);
         }
         for (int a = 0; a < 2; a++)
         {
             ptx::mbar_init(ptx::smem_u32(&bar_tmem_full[a]), 1);
             ptx::mbar_init(ptx::smem_u32(&bar_tmem_empty[a]), 2 * kPairEpiWarps);
+            ptx::mbar_init(ptx::smem_u32(&bar_rs_full[a]), kPairSumWarps);
+            ptx::mbar_init(ptx::smem_u32(&bar_rs_empty[a]), kPairEpiWarps);
         }
         ptx::fence_barrier_init();
         ptx::prefetch_tmap(&p.tmA);
@@ -200,6 +213,11 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                         break;
                     }
                     ptx::tc_fence_after_sync();
+                    // The second CTA's sum warps cannot watch this barrier: tell them their A tile has landed.  (A
+                    // relaxed arrival: the tile was written by the TMA unit, whose completion this thread has just
+                    // observed; a release at cluster scope here was measured at about a microsecond per stage.)
+                    if (p.fuse_row_sums)
+                        ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&bar_go[stage]), 1));
                     const int nch = min(p.ksub, chunks_left);
                     chunks_left -= nch;
                     if (issue)
@@ -239,11 +257,90 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                 atomicOr(p.status, TB200_DEV_TIMEOUT);
         }
     }
+    else if (warp >= 2 + kPairEpiWarps)
+    {
+        // ------------------------------------------------------------------ row-sum warps (both CTAs)
+        // 128 threads, eight per row of the A tile (one 16-byte piece each; the 128-byte swizzle only permutes pieces
+        // inside a row), sixteen rows per pass.  A thread keeps the sums of its eight rows over the whole K loop.
+        if (p.fuse_row_sums)
+        {
+            const int ts    = (int)threadIdx.x - 32 * (2 + kPairEpiWarps);
+            const int piece = ts & 7, row0 = ts >> 3;
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters)
+            {
+                ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_rs_empty[acc]), acc_phase ^ 1u, kPairWaitLimit);
+                int32_t s[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    s[i] = 0;
+                int chunks_left = p.total_chunks;
+                while (chunks_left > 0 && ok)
+                {
+                    const uint32_t ready = ptx::smem_u32(rank == 0 ? &bar_full[stage] : &bar_go[stage]);
+                    if (!ptx::mbar_wait_bounded(ready, phase, kPairWaitLimit))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    const int nch = min(p.ksub, chunks_left);
+                    chunks_left -= nch;
+                    const uint8_t* sA = smem_raw + (smem_base - ptx::smem_u32(smem_raw)) + stage * p.stage_bytes;
+                    for (int j = 0; j < nch; j++)
+                    {
+                        const uint8_t* base = sA + j * kPairChunkBytes + row0 * 128 + piece * 16;
+#pragma unroll
+                        for (int i = 0; i < 8; i++)
+                        {
+                            const int4 v = *reinterpret_cast<const int4*>(base + i * 16 * 128);
+                            s[i] = __dp4a(v.x, 0x01010101, s[i]);
+                            s[i] = __dp4a(v.y, 0x01010101, s[i]);
+                            s[i] = __dp4a(v.z, 0x01010101, s[i]);
+                            s[i] = __dp4a(v.w, 0x01010101, s[i]);
+                        }
+                    }
+                    // this warp is done with the stage
+                    __syncwarp();
+                    if (lane == 0)
+                        ptx::mbar_arrive(ptx::smem_u32(&bar_empty[stage]));
+                    if (++stage == p.num_stages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok)
+                    break;
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                {
+                    s[i] += __shfl_xor_sync(0xffffffffu, s[i], 1);
+                    s[i] += __shfl_xor_sync(0xffffffffu, s[i], 2);
+                    s[i] += __shfl_xor_sync(0xffffffffu, s[i], 4);
+                    if (piece == 0)
+                        row_sums[acc][row0 + 16 * i] = s[i];
+                }
+                __syncwarp();
+                if (lane == 0)
+                    ptx::mbar_arrive(ptx::smem_u32(&bar_rs_full[acc]));
+                acc ^= 1;
+                if (acc == 0)
+                    acc_phase ^= 1u;
+            }
+            if (!ok && lane == 0)
+                atomicOr(p.status, TB200_DEV_TIMEOUT);
+        }
+    }
     else
     {
         // ------------------------------------------------------------------ epilogue warps (both CTAs)
         const int quarter = warp & 3;           // TMEM lane quarter this warp may read
         const int slot    = (warp - 2) >> 2;    // the warps of a quarter take the 32-column chunks round robin
+        const int32_t rc_const = p.fuse_row_sums ? p.C * p.a_zp * p.b_zp : 0;
         const int row     = quarter * 32 + lane;
         const uint32_t empty_first[2] = { ptx::map_to_cta(ptx::smem_u32(&bar_tmem_empty[0]), 0),
                                           ptx::map_to_cta(ptx::smem_u32(&bar_tmem_empty[1]), 0) };
@@ -267,6 +364,18 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
             int32_t rc = 0;
             if (p.row_corr != nullptr && row_valid)
                 rc = __ldg(p.row_corr + orow);
+            if (p.fuse_row_sums)
+            {
+                ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_rs_full[acc]), acc_phase, kPairWaitLimit);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok)
+                    break;
+                rc = rc_const - p.b_zp * row_sums[acc][row];
+                // every lane has its value: the sum warps may reuse the buffer
+                __syncwarp();
+                if (lane == 0)
+                    ptx::mbar_arrive(ptx::smem_u32(&bar_rs_empty[acc]));
+            }
             const int32_t* corr_row = p.corr != nullptr ? p.corr + (int64_t)t.n * p.corr_stride : nullptr;
             int32_t* out_row        = p.out + orow * p.W;
             const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * 256);
@@ -420,6 +529,9 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     k.idesc     = ptx::make_idesc(2u, 1u, 1u, 0u, 1u, 256u, 256u);
     k.out         = reinterpret_cast<int32_t*>(q.out);
     k.row_corr    = q.row_corr;
+    k.fuse_row_sums = q.fuse_row_sums;
+    k.a_zp          = q.a_zp;
+    k.b_zp          = q.b_zp;
     k.corr        = q.corr;
     k.corr_stride = q.corr_stride;
     k.debug       = pair_env_int("TB200_TC_DEBUG", 0);
