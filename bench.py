@@ -407,6 +407,30 @@ def main():
         e2e_ms = (time.perf_counter() - t0) * 1e3     # the call returns only when the result is in host memory
         barrier()
 
+        # What the link alone allows: the same bytes copied with plain pinned-memory copies, both directions at once and
+        # no arithmetic (rank 0 reports it beside the end-to-end figure; it is not part of any timed region above).
+        link_ms = None
+        if args.e2e_steps > 0 and rank == 0:
+            d_a = torch.empty_like(a_pin, device="cuda")
+            d_b = torch.empty_like(b_pin, device="cuda")
+            d_o = torch.empty(out_pin.shape, dtype=out_pin.dtype, device="cuda")
+            s_up, s_dn = torch.cuda.Stream(), torch.cuda.Stream()
+            def link_only():
+                with torch.cuda.stream(s_up):
+                    d_a.copy_(a_pin, non_blocking=True)
+                    d_b.copy_(b_pin, non_blocking=True)
+                with torch.cuda.stream(s_dn):
+                    out_scratch.copy_(d_o, non_blocking=True)
+                torch.cuda.synchronize()
+            out_scratch = torch.empty(out_pin.shape, dtype=out_pin.dtype).pin_memory()
+            link_only()
+            t0 = time.perf_counter()
+            for _ in range(args.e2e_steps):
+                link_only()
+            link_ms = (time.perf_counter() - t0) * 1e3 / args.e2e_steps
+            del d_a, d_b, d_o, out_scratch
+        barrier()
+
         times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
         if world > 1:
             dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -446,7 +470,9 @@ def main():
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": int(a_pin.numel() + b_pin.numel()),
                     "d2h_bytes_per_step": int(out_pin.numel() * 4), "steps": args.e2e_steps,
-                    "ms_per_step": e2e_ms / max(args.e2e_steps, 1)},
+                    "ms_per_step": e2e_ms / max(args.e2e_steps, 1),
+                    "link_only_ms_per_step": link_ms,
+                    "note": "link_only = the same host<->device bytes as plain pinned copies, both directions at once"},
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s",
                          "frac": achieved / peak, "traffic": traffic, "kernel": kernel_name,

@@ -1639,8 +1639,30 @@ extern "C" tb200_status tb200_matmul_host(tb200_ctx* ctx, tb200_dtype in_dtype, 
         return TB200_OK;
     const size_t a_b = (size_t)H * C * es_in, b_b = (size_t)C * W * es_in, o_b = (size_t)H * W * es_out;
     auto up256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
-    // about 32 MB of A per chunk
-    int nb = (int)std::max<size_t>(1, std::min<size_t>((size_t)N, ((size_t)32 << 20) / std::max<size_t>(a_b, 1)));
+    // About 64 MB of A per chunk in the steady state (smaller chunks were measured slower: per-chunk launch work adds
+    // up).  The link is the bottleneck, so the first chunks are small and double in size (the first product starts after
+    // one batch has been uploaded, not eight) and the last ones halve again (little is left to download after the last
+    // upload).
+    const size_t chunk_target = (size_t)std::max(1, atoi(getenv("TB200_HOST_CHUNK_MB") ? getenv("TB200_HOST_CHUNK_MB") : "64")) << 20;
+    int nb = (int)std::max<size_t>(1, std::min<size_t>((size_t)N, chunk_target / std::max<size_t>(a_b, 1)));
+    std::vector<int> sizes;
+    {
+        std::vector<int> tail;
+        int left = N;
+        for (int c = 1; c < nb && left > 2 * c; c *= 2)
+        {
+            sizes.push_back(c);
+            tail.push_back(c);
+            left -= 2 * c;
+        }
+        while (left > 0)
+        {
+            const int c = std::min(nb, left);
+            sizes.push_back(c);
+            left -= c;
+        }
+        sizes.insert(sizes.end(), tail.rbegin(), tail.rend());
+    }
     const size_t off_b = up256((size_t)nb * a_b), off_o = off_b + up256((size_t)nb * b_b);
     const size_t slot_bytes = off_o + up256((size_t)nb * o_b);
     tb200_status st = pipe_prepare(ctx, slot_bytes);
@@ -1650,9 +1672,9 @@ extern "C" tb200_status tb200_matmul_host(tb200_ctx* ctx, tb200_dtype in_dtype, 
     // order the copy streams after whatever the caller queued on the compute stream, and clear stale events
     TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
     int chunk_idx = 0;
-    for (int n0 = 0; n0 < N; n0 += nb, chunk_idx++)
+    for (int n0 = 0; n0 < N; n0 += sizes[chunk_idx], chunk_idx++)
     {
-        const int cnt  = std::min(nb, N - n0);
+        const int cnt  = sizes[chunk_idx];
         const int slot = chunk_idx & 1;
         uint8_t* base  = reinterpret_cast<uint8_t*>(p.buf[slot]);
         if (chunk_idx >= 2)
