@@ -92,6 +92,35 @@ def conv_i8_config(ctx, timer, name, N, IH, IW, IC, OC, KH, KW, stride, pad, izp
             "algorithmic_ops": ops, "algorithmic_bytes": nbytes, "l2": note}
 
 
+def graph_profile(batch):
+    """Per-step times of one eager evaluation of the benchmark graph (each step bracketed by a device sync, so the sum
+    exceeds the replayed graph's time; the shares are what this is for)."""
+    import collections
+    import time
+    from . import graph as G
+    ctx = tb.Context(0)
+    g = G.resnet50_int8(batch)
+    run = G.DeviceRunner(ctx, g)
+    run.set_input(G.synthetic_images(batch))
+    run.run()
+    ctx.sync()
+
+    def stamp():
+        ctx.sync()
+        return time.perf_counter()
+
+    run.profile(stamp)
+    rows = run.profile(stamp)
+    print(json.dumps({"graph": "resnet50_int8", "batch": batch, "steps": len(rows), "sum_ms": sum(r[3] for r in rows)}))
+    for r in sorted(rows, key=lambda r: -r[3])[:24]:
+        print("%-20s %-16s %-24s %8.3f ms  shape=%s" % (r[0], r[1], r[2], r[3], g.meta[r[1]][1]))
+    agg = collections.Counter()
+    for r in rows:
+        agg[(r[0], r[2])] += r[3]
+    for (kind, kernel), ms in agg.most_common():
+        print("%-20s %-24s %8.3f ms" % (kind, kernel, ms))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="c1,c2b,c3a,c3b,c4")
@@ -99,9 +128,16 @@ def main():
     ap.add_argument("--shifts", default="32,40", help="closed range of the per-channel RESCALE shifts, lo,hi")
     ap.add_argument("--conv", default=None,
                     help="also time one int8 CONV2D+RESCALE+CLAMP layer: N,IH,IW,IC,OC,K,stride,pad (pad on all four sides)")
+    ap.add_argument("--graph-profile", type=int, default=0, metavar="BATCH",
+                    help="evaluate the ResNet-50-shaped int8 graph at this batch step by step (a device sync around "
+                         "every step) and print the slowest steps and the time per kind of step")
     args = ap.parse_args()
     SHIFT_RANGE[:] = [int(v) for v in args.shifts.split(",")]
     import torch
+
+    if args.graph_profile > 0:
+        graph_profile(args.graph_profile)
+        return
 
     hbm, bf16, src = _peaks()
     stream = torch.cuda.Stream()
