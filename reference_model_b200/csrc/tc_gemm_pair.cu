@@ -34,7 +34,6 @@ constexpr int kPairSumWarps   = 4;        // row sums of A straight from the sha
 constexpr int kPairThreads    = 64 + 32 * (kPairEpiWarps + kPairSumWarps);    // TMA warp, MMA warp, epilogue, sums
 constexpr int kPairMaxStages  = 8;
 constexpr int kPairChunkBytes = 16384;    // 128 rows x 128 bytes (A: rows x K, B: K rows x columns), 128-byte swizzle
-constexpr int kPairSlotBytes  = 2 * kPairChunkBytes;    // one K chunk of A and of B
 constexpr int kPairTmemCols   = 512;      // two accumulator buffers of 256 columns
 constexpr long long kPairWaitLimit = 4000000000LL;    // about two seconds of SM clock
 
@@ -45,12 +44,7 @@ struct PairParams
     int NB, H, C, W;
     int tiles_m, tiles_w, num_tiles;    // 256 x 256 tiles, numbered batch-major, columns fastest
     int total_chunks;                   // 128-byte K chunks
-    // The shared-memory ring is num_slots slots of one K chunk each (A tile 16 KB + B tile 16 KB).  A stage, the unit of
-    // the full / empty handshake and of tcgen05.commit, is ksub consecutive slots (wrapping) and is identified by its
-    // first slot; stages advance by ksub slots, and after cycle_len stages the first slot is 0 again and the barrier
-    // phase flips.  An odd slot count with ksub = 2 uses all of shared memory (7 x 32 KB) where whole 64 KB stages
-    // would leave 32 KB idle, and what is in flight from L2 is what bounds this kernel.
-    int ksub, num_slots, cycle_len;
+    int ksub, num_stages, stage_bytes;  // K chunks per stage (one tcgen05.commit per stage), ring depth
     uint64_t a_desc_hi, b_desc_hi;
     uint32_t idesc;
     int32_t* out;
@@ -103,7 +97,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
 
     if (threadIdx.x == 0)
     {
-        for (int s = 0; s < p.num_slots; s++)
+        for (int s = 0; s < p.num_stages; s++)
         {
             ptx::mbar_init(ptx::smem_u32(&bar_full[s]), 1);
             // a stage is free when the MMAs have read it and, with fused row sums, the sum warps have too
@@ -138,7 +132,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
         // ------------------------------------------------------------------ TMA producer (both CTAs)
         if (lane == 0)
         {
-            int stage = 0, stage_count = 0;    // first slot of the stage, stages since the last phase flip
+            int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters)
@@ -169,23 +163,18 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                         if (rank == 0)
                             ptx::mbar_arrive_expect_tx(full_local, (uint32_t)(nch * 4 * kPairChunkBytes));
                         const uint32_t full_first = ptx::map_to_cta(full_local, 0);
-                        int slot = stage;
+                        const uint32_t sA = smem_base + (uint32_t)(stage * p.stage_bytes);
+                        const uint32_t sB = sA + (uint32_t)(p.ksub * kPairChunkBytes);
                         for (int j = 0; j < nch; j++)
                         {
-                            const uint32_t sA = smem_base + (uint32_t)(slot * kPairSlotBytes);
-                            ptx::tma_load_3d_pair(sA, &p.tmA, full_first, k, m0, t.n);
-                            ptx::tma_load_3d_pair(sA + kPairChunkBytes, &p.tmB, full_first, w0, k, t.n);
+                            ptx::tma_load_3d_pair(sA + (uint32_t)(j * kPairChunkBytes), &p.tmA, full_first, k, m0, t.n);
+                            ptx::tma_load_3d_pair(sB + (uint32_t)(j * kPairChunkBytes), &p.tmB, full_first, w0, k, t.n);
                             k += 128;
-                            if (++slot == p.num_slots)
-                                slot = 0;
                         }
                     }
-                    stage += p.ksub;
-                    if (stage >= p.num_slots)
-                        stage -= p.num_slots;
-                    if (++stage_count == p.cycle_len)
+                    if (++stage == p.num_stages)
                     {
-                        stage_count = 0;
+                        stage = 0;
                         phase ^= 1u;
                     }
                 }
@@ -199,7 +188,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
         // ------------------------------------------------------------------ MMA issuer (first CTA of the pair)
         if (lane == 0 && rank == 0)
         {
-            int stage = 0, stage_count = 0;
+            int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
@@ -233,14 +222,12 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                     chunks_left -= nch;
                     if (issue)
                     {
-                        int slot = stage;
+                        const uint32_t sA = smem_base + (uint32_t)(stage * p.stage_bytes);
+                        const uint32_t sB = sA + (uint32_t)(p.ksub * kPairChunkBytes);
                         for (int j = 0; j < nch; j++)
                         {
-                            const uint32_t sA = smem_base + (uint32_t)(slot * kPairSlotBytes);
-                            uint64_t ad = ptx::smem_desc(p.a_desc_hi, sA);
-                            uint64_t bd = ptx::smem_desc(p.b_desc_hi, sA + kPairChunkBytes);
-                            if (++slot == p.num_slots)
-                                slot = 0;
+                            uint64_t ad = ptx::smem_desc(p.a_desc_hi, sA + (uint32_t)(j * kPairChunkBytes));
+                            uint64_t bd = ptx::smem_desc(p.b_desc_hi, sB + (uint32_t)(j * kPairChunkBytes));
 #pragma unroll
                             for (int m = 0; m < 4; m++)
                             {
@@ -253,12 +240,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                     }
                     // frees the stage in both CTAs once the MMAs above have read it
                     ptx::mma_commit_pair(ptx::smem_u32(&bar_empty[stage]), 3);
-                    stage += p.ksub;
-                    if (stage >= p.num_slots)
-                        stage -= p.num_slots;
-                    if (++stage_count == p.cycle_len)
+                    if (++stage == p.num_stages)
                     {
-                        stage_count = 0;
+                        stage = 0;
                         phase ^= 1u;
                     }
                 }
@@ -282,7 +266,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
         {
             const int ts    = (int)threadIdx.x - 32 * (2 + kPairEpiWarps);
             const int piece = ts & 7, row0 = ts >> 3;
-            int stage = 0, stage_count = 0;
+            int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
@@ -305,13 +289,10 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                     }
                     const int nch = min(p.ksub, chunks_left);
                     chunks_left -= nch;
-                    const uint8_t* ring = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-                    int slot = stage;
+                    const uint8_t* sA = smem_raw + (smem_base - ptx::smem_u32(smem_raw)) + stage * p.stage_bytes;
                     for (int j = 0; j < nch; j++)
                     {
-                        const uint8_t* base = ring + slot * kPairSlotBytes + row0 * 128 + piece * 16;
-                        if (++slot == p.num_slots)
-                            slot = 0;
+                        const uint8_t* base = sA + j * kPairChunkBytes + row0 * 128 + piece * 16;
 #pragma unroll
                         for (int i = 0; i < 8; i++)
                         {
@@ -326,12 +307,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                     __syncwarp();
                     if (lane == 0)
                         ptx::mbar_arrive(ptx::smem_u32(&bar_empty[stage]));
-                    stage += p.ksub;
-                    if (stage >= p.num_slots)
-                        stage -= p.num_slots;
-                    if (++stage_count == p.cycle_len)
+                    if (++stage == p.num_stages)
                     {
-                        stage_count = 0;
+                        stage = 0;
                         phase ^= 1u;
                     }
                 }
@@ -576,21 +554,12 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     if (r != CUDA_SUCCESS)
         return fail(ctx, TB200_INTERNAL, "tensor map for B rejected (CUresult %d)", (int)r);
 
-    // The ring holds what is in flight from L2, which is what bounds this kernel: it takes all the shared memory there
-    // is.  One commit per stage: 4 MMAs (one chunk) per commit cost tensor-pipe time, 8 do not.
-    k.ksub      = std::max(1, std::min(4, pair_env_int("TB200_PAIR_KSUB", 2)));
-    k.num_slots = std::min(kPairMaxStages, std::max(2 * k.ksub, pair_env_int("TB200_PAIR_SLOTS", 7)));
-    {
-        int a = k.num_slots, b = k.ksub;
-        while (b)
-        {
-            const int t = a % b;
-            a = b;
-            b = t;
-        }
-        k.cycle_len = k.num_slots / a;
-    }
-    const int smem_bytes = k.num_slots * kPairSlotBytes + 1024;
+    // The ring holds what is in flight from L2: the kernel is bound by latency x bytes in flight, so it takes all the
+    // shared memory there is.  One commit per stage; 4 MMAs (one chunk) per commit costs tensor-pipe time, 8 do not.
+    k.ksub        = std::max(1, std::min(4, pair_env_int("TB200_PAIR_KSUB", 2)));
+    k.stage_bytes = 2 * k.ksub * kPairChunkBytes;
+    k.num_stages  = std::min(kPairMaxStages, std::max(2, pair_env_int("TB200_PAIR_STAGES", (224 * 1024) / k.stage_bytes)));
+    const int smem_bytes = k.num_stages * k.stage_bytes + 1024;
     TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(tc_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     const int clusters = std::max(1, std::min(k.num_tiles, ctx->num_sms / 2));
     cudaLaunchConfig_t cfg = {};
