@@ -1100,9 +1100,33 @@ __global__ void __launch_bounds__(256) matmul_col_corr_kernel(const int8_t* __re
     {
         if (col0 < W)
         {
-            for (int k = k0 + warp; k < k1; k += 8)
+            // four rows per pass, all four loads issued before the arithmetic (memory-level parallelism)
+            const int8_t* rp = bp + (int64_t)(k0 + warp) * W + col0;
+            const int64_t rstep = (int64_t)8 * W;
+            int k = k0 + warp;
+            for (; k + 24 < k1; k += 32, rp += 4 * rstep)
             {
-                const int4 v = __ldg(reinterpret_cast<const int4*>(bp + (int64_t)k * W + col0));
+                int4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    v[u] = __ldg(reinterpret_cast<const int4*>(rp + u * rstep));
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                {
+                    const int w4[4] = { v[u].x, v[u].y, v[u].z, v[u].w };
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+                    {
+                        s[4 * q + 0] = __dp4a(w4[q], 0x00000001, s[4 * q + 0]);
+                        s[4 * q + 1] = __dp4a(w4[q], 0x00000100, s[4 * q + 1]);
+                        s[4 * q + 2] = __dp4a(w4[q], 0x00010000, s[4 * q + 2]);
+                        s[4 * q + 3] = __dp4a(w4[q], 0x01000000, s[4 * q + 3]);
+                    }
+                }
+            }
+            for (; k < k1; k += 8, rp += rstep)
+            {
+                const int4 v = __ldg(reinterpret_cast<const int4*>(rp));
                 const int w4[4] = { v.x, v.y, v.z, v.w };
 #pragma unroll
                 for (int q = 0; q < 4; q++)
