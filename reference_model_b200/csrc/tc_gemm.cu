@@ -5,9 +5,10 @@
 //                shared-memory ring; zero fill outside the tensor implements the convolution padding
 //   warp 1     : owns tensor memory (TMEM) and issues tcgen05.mma (kind::i8 with s32 accumulators, or kind::f16
 //                with f32 accumulators); two accumulator buffers alternate so the epilogue of one output tile
-//                overlaps the MMAs of the next
-//   warps 2..5 : epilogue; each thread owns one output row (pixel), reads its accumulators from TMEM and applies
-//                zero-point corrections / bias / RESCALE / CLAMP before the store
+//                overlaps the MMAs of the next (one buffer, and two CTAs per SM, for short-K 256-column layers)
+//   warps 2..9 : epilogue; two warps per TMEM lane quarter, each thread owns one output row (pixel), reads its
+//                accumulators from TMEM and applies zero-point corrections / bias / RESCALE / CLAMP before the store
+// (Large int8 MATMULs with int32 output go to the CTA-pair kernel in tc_gemm_pair.cu instead.)
 // Every wait on an mbarrier is bounded; a wait that gives up sets TB200_DEV_TIMEOUT in the context's status word
 // and the kernel drains and exits.
 #include <algorithm>
@@ -72,7 +73,6 @@ struct TcKernelParams
     const int8_t* shift_pad;
     int double_round;
     int32_t out_zp, clamp_lo, clamp_hi;
-    int32_t zp_add_lo, zp_add_hi;    // range of scaled values for which value + out_zp stays inside int32
     float clamp_lo_f, clamp_hi_f;
     int has_clamp;
     int debug;    // diagnostic bit mask (TB200_TC_DEBUG): 1 skip epilogue memory work, 2 skip MMA issue, 4 skip loads
@@ -1178,8 +1178,6 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
     k.shift_pad    = q.shift_pad;
     k.double_round = q.double_round;
     k.out_zp       = q.out_zp;
-    k.zp_add_hi    = q.out_zp > 0 ? 2147483647 - q.out_zp : 2147483647;
-    k.zp_add_lo    = q.out_zp < 0 ? (int32_t)(-2147483647 - 1 - q.out_zp) : (-2147483647 - 1);
     k.clamp_lo     = q.clamp_lo;
     k.clamp_hi     = q.clamp_hi;
     k.clamp_lo_f   = q.clamp_lo_f;

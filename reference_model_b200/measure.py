@@ -127,7 +127,8 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--shifts", default="32,40", help="closed range of the per-channel RESCALE shifts, lo,hi")
     ap.add_argument("--conv", default=None,
-                    help="also time one int8 CONV2D+RESCALE+CLAMP layer: N,IH,IW,IC,OC,K,stride,pad (pad on all four sides)")
+                    help="also time one int8 CONV2D+RESCALE+CLAMP layer: N,IH,IW,IC,OC,K,stride,pad (one pad for all four sides, "
+                         "or four values top,bottom,left,right)")
     ap.add_argument("--graph-profile", type=int, default=0, metavar="BATCH",
                     help="evaluate the ResNet-50-shaped int8 graph at this batch step by step (a device sync around "
                          "every step) and print the slowest steps and the time per kind of step")
@@ -145,8 +146,10 @@ def main():
         ctx = tb.Context(0, stream.cuda_stream)
         timer = Timer(ctx, stream, torch)
         if args.conv:
-            n, ih, iw, ic, oc, k, st, pd = (int(v) for v in args.conv.split(","))
-            res = conv_i8_config(ctx, timer, "conv %s" % args.conv, n, ih, iw, ic, oc, k, k, st, [pd, pd, pd, pd], -128,
+            vals = [int(v) for v in args.conv.split(",")]
+            n, ih, iw, ic, oc, k, st = vals[:7]
+            pads = vals[7:] * 4 if len(vals) == 8 else vals[7:11]    # one value for all sides, or top,bottom,left,right
+            res = conv_i8_config(ctx, timer, "conv %s" % args.conv, n, ih, iw, ic, oc, k, k, st, pads, -128,
                                  args.iters, 9)
             print(json.dumps(res))
             sys.stdout.flush()
