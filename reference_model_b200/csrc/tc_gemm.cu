@@ -113,39 +113,40 @@ __device__ __forceinline__ uint32_t pack4_sat_i8(int a, int b, int c, int d)
     return r;
 }
 
-// Column-block property found while the RESCALE constants are built
+// Column-block properties found while the RESCALE constants are built
 enum : int
 {
-    EPI_COLS_GENERIC = 1,    // some column has operands outside what the high-word form below handles
+    EPI_COLS_GENERIC  = 1,    // some column has operands outside what the high-word form below handles
+    EPI_COLS_PRESHIFT = 2,    // some shift is below 32: values are pre-scaled, and apply_scale_32's range check applies
 };
 
-// apply_scale_32 + output zero point + CLAMP + int8 packing of four accumulators, for column blocks whose shifts all
-// lie in [32, 54] (the usual case for a convolution's RESCALE).  With shift >= 32 apply_scale_32 accepts every int32
-// value, the result is the high word of the 64-bit sum shifted by shift - 32, and adding out_zp * 2^shift to the
-// rounding constant before the arithmetic shift adds exactly out_zp after it (|sum| < 2^62 + 2^61 + 2^54).
-//   cols[i] = {multiplier, shift - 32, R(v >= 0) lo, hi, R(v < 0) lo, hi},  R = 2^(shift-1) +- 2^30 + out_zp * 2^shift
-// (the two constants are equal without double rounding).  Measured on this part, one 64-bit multiply-add with a
+// apply_scale_32 + output zero point + int8 saturation and packing of four accumulators, for column blocks whose
+// shifts are all at most 54.  The result is always taken as the high word of a 64-bit sum:
+//   shift >= 32: result + out_zp = high word of (v * multiplier + R) >> (shift - 32); every int32 value is accepted;
+//   shift <  32: with k = 32 - shift, ((v << k) * multiplier + (round << k)) >> 32 equals (v * multiplier + round)
+//                >> shift, and v << k fits int32 for every v inside the range apply_scale_32 accepts (checked by the
+//                caller for such blocks);
+// and adding out_zp * 2^(shift + k) to the rounding constant before the arithmetic shift adds exactly out_zp after it
+// (|sum| < 2^62 + 2^61 + 2^54).
+//   cols[i] = {multiplier, max(shift, 32) - 32, R(v >= 0) lo, hi, R(v < 0) lo, hi, largest |v| accepted, k}
+// (the two constants differ only under double rounding).  Measured on this part, one 64-bit multiply-add with a
 // selected addend is cheaper than a high and a low multiply with the carry worked out by hand.
-template <bool DOUBLE_ROUND, bool NARROW_CLAMP>
-__device__ __forceinline__ uint32_t rescale32_high_x4(const uint32_t* v, const int32_t (*cols)[8], int32_t clamp_lo,
-                                                      int32_t clamp_hi)
+template <bool PRESHIFT>
+__device__ __forceinline__ uint32_t rescale32_high_x4(const uint32_t* v, const int32_t (*cols)[8])
 {
     int32_t z[4];
 #pragma unroll
     for (int i = 0; i < 4; i++)
     {
-        const int4 c0   = *reinterpret_cast<const int4*>(&cols[i][0]);
-        const int32_t a = (int32_t)v[i];
-        int64_t r       = ((int64_t)c0.w << 32) | (uint32_t)c0.z;
-        if (DOUBLE_ROUND)
-        {
-            const int2 c1 = *reinterpret_cast<const int2*>(&cols[i][4]);
-            r             = a >= 0 ? r : (((int64_t)c1.y << 32) | (uint32_t)c1.x);
-        }
+        const int4 c0 = *reinterpret_cast<const int4*>(&cols[i][0]);
+        const int4 c1 = *reinterpret_cast<const int4*>(&cols[i][4]);
+        int32_t a     = (int32_t)v[i];
+        // (without double rounding the two constants are equal and the selection is a no-op: one code path for both)
+        const int64_t r = a >= 0 ? (((int64_t)c0.w << 32) | (uint32_t)c0.z) : (((int64_t)c1.y << 32) | (uint32_t)c1.x);
+        if (PRESHIFT)
+            a = (int32_t)((uint32_t)a << c1.w);
         const int64_t prod = (int64_t)a * (int64_t)c0.x + r;
         z[i]               = (int32_t)(prod >> 32) >> c0.y;
-        if (NARROW_CLAMP)
-            z[i] = min(max(z[i], clamp_lo), clamp_hi);
     }
     return pack4_sat_i8(z[0], z[1], z[2], z[3]);
 }
@@ -419,9 +420,11 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     const int32_t m = __ldg(p.mult_pad + t.col0 + c);
                     const int32_t s = (int32_t)__ldg(p.shift_pad + t.col0 + c);
                     int f = 0;
-                    // high-word form: every int32 value accepted, out_zp * 2^shift clear of the int64 range
-                    if (m < 0 || s < 32 || s > 54)
+                    // high-word form: out_zp * 2^shift clear of the int64 range
+                    if (m < 0 || s < 2 || s > 54)
                         f |= EPI_COLS_GENERIC;
+                    if (s < 32)
+                        f |= EPI_COLS_PRESHIFT;
                     if (f & ~epi_flags)
                         atomicOr(&epi_flags, f);
                 }
@@ -446,11 +449,12 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     int4 lo4, hi4;
                     if (high_form && t.col0 + c < p.OC)
                     {
-                        const int64_t z64 = (int64_t)p.out_zp * ((int64_t)1 << sc);
-                        rpos += z64;
-                        rneg += z64;
-                        lo4 = make_int4(m, sc - 32, (int32_t)(uint32_t)(rpos & 0xffffffffLL), (int32_t)(rpos >> 32));
-                        hi4 = make_int4((int32_t)(uint32_t)(rneg & 0xffffffffLL), (int32_t)(rneg >> 32), vlim, 0);
+                        const int k       = sc < 32 ? 32 - sc : 0;
+                        const int64_t z64 = (int64_t)p.out_zp * ((int64_t)1 << (sc + k));
+                        rpos = rpos * ((int64_t)1 << k) + z64;
+                        rneg = rneg * ((int64_t)1 << k) + z64;
+                        lo4 = make_int4(m, sc + k - 32, (int32_t)(uint32_t)(rpos & 0xffffffffLL), (int32_t)(rpos >> 32));
+                        hi4 = make_int4((int32_t)(uint32_t)(rneg & 0xffffffffLL), (int32_t)(rneg >> 32), vlim, k);
                     }
                     else
                     {
@@ -583,28 +587,55 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     // (before and after adding the small output zero point) follow from the range check.  The range
                     // check itself is done on the largest magnitude of the 32 values against the smallest limit of
                     // the column block; only when that fails are the columns compared one by one.
-                    if (!(epi_flags & EPI_COLS_GENERIC))
+                    const int cflags = epi_flags;
+                    if (!(cflags & EPI_COLS_GENERIC))
                     {
-                        // every shift of the block is at least 32: apply_scale_32 accepts all of int32, nothing to check
+                        bool bad = false;
                         uint32_t w[8];
-                        const bool narrow = p.clamp_lo > -128 || p.clamp_hi < 127;
-                        if (p.double_round && !narrow)
+                        if (cflags & EPI_COLS_PRESHIFT)
                         {
+                            // some shift of the block is below 32: the range check of apply_scale_32 can fail there
+                            int32_t vmax = -2147483647 - 1, vmin = 2147483647;
+#pragma unroll
+                            for (int i = 0; i < 32; i++)
+                            {
+                                vmax = max(vmax, (int32_t)v[i]);
+                                vmin = min(vmin, (int32_t)v[i]);
+                            }
+                            const int32_t lim = epi_vlim_min;
+                            if (vmax > lim || vmin < ~lim)
+                            {
+                                for (int i = 0; i < 32; i++)
+                                {
+                                    const int32_t vl = epi_cols[c * 32 + i][6];
+                                    int32_t a = 0;
+#pragma unroll
+                                    for (int j = 0; j < 32; j++)
+                                        a = (j == i) ? (int32_t)v[j] : a;
+                                    bad |= (a > vl) || (a < ~vl);
+                                }
+                            }
 #pragma unroll
                             for (int q = 0; q < 8; q++)
-                                w[q] = rescale32_high_x4<true, false>(&v[4 * q], &epi_cols[c * 32 + 4 * q], 0, 0);
-                        }
-                        else if (p.double_round)
-                        {
-#pragma unroll
-                            for (int q = 0; q < 8; q++)
-                                w[q] = rescale32_high_x4<true, true>(&v[4 * q], &epi_cols[c * 32 + 4 * q], p.clamp_lo, p.clamp_hi);
+                                w[q] = rescale32_high_x4<true>(&v[4 * q], &epi_cols[c * 32 + 4 * q]);
                         }
                         else
                         {
+                            // every shift of the block is at least 32: apply_scale_32 accepts all of int32
 #pragma unroll
                             for (int q = 0; q < 8; q++)
-                                w[q] = rescale32_high_x4<false, true>(&v[4 * q], &epi_cols[c * 32 + 4 * q], p.clamp_lo, p.clamp_hi);
+                                w[q] = rescale32_high_x4<false>(&v[4 * q], &epi_cols[c * 32 + 4 * q]);
+                        }
+                        if (bad && row_valid)
+                            dev_flags |= TB200_DEV_UNPREDICTABLE;
+                        // a CLAMP narrower than int8 (rare) works on the packed bytes
+                        if (p.clamp_lo > -128 || p.clamp_hi < 127)
+                        {
+                            const uint32_t lo4 = (uint32_t)(p.clamp_lo & 0xff) * 0x01010101u;
+                            const uint32_t hi4 = (uint32_t)(p.clamp_hi & 0xff) * 0x01010101u;
+#pragma unroll
+                            for (int q = 0; q < 8; q++)
+                                w[q] = __vmins4(__vmaxs4(w[q], lo4), hi4);
                         }
                         // Each lane holds the 32 output bytes of its own row: one 32-byte store hands the memory system a
                         // complete sector (two 16-byte stores would deliver two half-filled ones).  Outputs that are not

@@ -58,7 +58,7 @@ class Timer:
         return total / iters, ("L2 flushed between calls" if need_flush else "working set larger than L2")
 
 
-SHIFT_RANGE = [32, 40]    # per-channel RESCALE shifts are drawn from this closed range (--shifts)
+SHIFT_RANGE = [30, 40]    # per-channel RESCALE shifts are drawn from this closed range (--shifts)
 
 
 def rescale_consts(ctx, r, channels):
@@ -125,7 +125,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="c1,c2b,c3a,c3b,c4")
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--shifts", default="32,40", help="closed range of the per-channel RESCALE shifts, lo,hi")
+    ap.add_argument("--shifts", default="30,40", help="closed range of the per-channel RESCALE shifts, lo,hi")
     ap.add_argument("--conv", default=None,
                     help="also time one int8 CONV2D+RESCALE+CLAMP layer: N,IH,IW,IC,OC,K,stride,pad (one pad for all four sides, "
                          "or four values top,bottom,left,right)")
