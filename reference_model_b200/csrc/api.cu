@@ -345,6 +345,8 @@ extern "C" tb200_status tb200_ctx_destroy(tb200_ctx* ctx)
         cudaFree(ctx->scratch);
     if (ctx->join_table)
         cudaFree(ctx->join_table);
+    if (ctx->pair_flags)
+        cudaFree(ctx->pair_flags);
     if (ctx->pipe.ready)
     {
         cudaStreamSynchronize(ctx->pipe.h2d);
@@ -1101,7 +1103,8 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
             const bool need_sums = int_path && (a_zp != 0 || b_zp != 0);
             const int Wpad       = (W + 255) / 256 * 256;
             const size_t rows = (size_t)N * H, cols = (size_t)N * Wpad;
-            const size_t sums_bytes = need_sums ? (((rows + 3) & ~(size_t)3) + cols) * sizeof(int32_t) : 0;
+            // (up to four planes of partial sums each when the CTA-pair kernel computes them itself)
+            const size_t sums_bytes = need_sums ? 4 * (((rows + 3) & ~(size_t)3) + cols) * sizeof(int32_t) : 0;
             if (pad_b || need_sums)
             {
                 st = ensure_scratch(ctx, padb_bytes + sums_bytes);
@@ -1118,9 +1121,49 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
             if (need_sums)
             {
                 int32_t* row_corr = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(ctx->scratch) + padb_bytes);
-                int32_t* col_corr = row_corr + ((rows + 3) & ~(size_t)3);
-                // the CTA-pair kernel sums the rows of A itself while they sit in shared memory (saves one pass over A)
-                const bool fuse_rows = b_zp != 0 && tc_gemm_pair_supported(q, ctx->num_sms) && env_flag("TB200_FUSE_ROW_SUMS", 1);
+                int32_t* col_corr = row_corr + 4 * ((rows + 3) & ~(size_t)3);
+                // The CTA-pair kernel takes the sums from its own tiles while they sit in shared memory: both of them,
+                // shared between tiles through flags in global memory (no pass over A or B at all), or the row sums only.
+                // The flags carry a per-launch epoch, which a replayed CUDA graph would repeat: not while capturing.
+                const bool pair      = tc_gemm_pair_supported(q, ctx->num_sms);
+                const bool fuse_all  = pair && !ctx->capturing && env_flag("TB200_FUSE_SUMS", 1);
+                const bool fuse_rows = !fuse_all && b_zp != 0 && pair && env_flag("TB200_FUSE_ROW_SUMS", 1);
+                if (fuse_all)
+                {
+                    const size_t words = (size_t)N * 8 * ((H + 255) / 256 + (W + 255) / 256);
+                    if (words > ctx->pair_flag_words)
+                    {
+                        TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+                        if (ctx->pair_flags)
+                            TB200_CUDA_CHECK(ctx, cudaFree(ctx->pair_flags));
+                        ctx->pair_flags      = nullptr;
+                        ctx->pair_flag_words = 0;
+                        TB200_CUDA_CHECK(ctx, cudaMalloc(reinterpret_cast<void**>(&ctx->pair_flags), words * sizeof(uint32_t)));
+                        TB200_CUDA_CHECK(ctx, cudaMemset(ctx->pair_flags, 0, words * sizeof(uint32_t)));
+                        ctx->pair_flag_words = words;
+                        ctx->pair_epoch      = 0;
+                    }
+                    q.fuse_row_sums = 2;
+                    q.a_zp          = a_zp;
+                    q.b_zp          = b_zp;
+                    if (ctx->pair_epoch == 0xffffffffu)
+                    {
+                        // the epoch is about to repeat: start over from clean flags
+                        TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+                        TB200_CUDA_CHECK(ctx, cudaMemset(ctx->pair_flags, 0, ctx->pair_flag_words * sizeof(uint32_t)));
+                        ctx->pair_epoch = 0;
+                    }
+                    q.sum_flags     = ctx->pair_flags;
+                    q.sum_epoch     = ++ctx->pair_epoch;
+                    q.row_corr      = b_zp != 0 ? row_corr : nullptr;
+                    if (a_zp != 0)
+                    {
+                        q.corr         = col_corr;
+                        q.corr_stride  = Wpad;
+                        q.corr_ystride = Wpad;
+                    }
+                    return tc_gemm_launch(ctx, q);
+                }
                 if (fuse_rows)
                 {
                     q.fuse_row_sums = 1;

@@ -47,6 +47,9 @@ struct tb200_ctx
     int* h_status        = nullptr;    // pinned mirror
     void* scratch        = nullptr;    // grow-on-demand device scratch (zero-point sums, weight tables)
     size_t scratch_bytes = 0;
+    uint32_t* pair_flags = nullptr;    // flags of the CTA-pair MATMUL's in-kernel zero-point sums, zeroed when allocated
+    size_t pair_flag_words = 0;
+    uint32_t pair_epoch  = 0;          // bumped per launch; a flag equal to it means "written in this launch"
     void* join_table     = nullptr;    // 64 KiB result table + 8 KiB REQUIRE bits of the per-tensor residual join
     uint64_t launches    = 0;
     int policy           = 0;
@@ -171,8 +174,13 @@ struct TcProblem
     const int32_t* row_corr;    // [N*OH*OW] added to every column of a row, or null
     // MATMUL on the CTA-pair kernel: derive the row term from A inside the kernel instead (row_corr null):
     // row term = -b_zp * sum_k A[row, k] + IC * a_zp * b_zp
+    // 2: both zero-point sums inside the kernel, shared between tiles through global memory: row_corr / corr then point
+    // at buffers for the raw row sums of A / column sums of B (null where the other zero point is 0), sum_flags at
+    // [batch * tiles_m * 2 + batch * tiles_w * 2] words that persist between launches, sum_epoch at a value no flag holds
     int fuse_row_sums;
     int32_t a_zp, b_zp;
+    uint32_t* sum_flags;
+    uint32_t sum_epoch;
     // per-column additive constants, padded: [classes][corr_stride]; corr_stride must be a multiple of 256 and cover
     // OC.  corr_classes != 0: the table has (KH+1)^2 (KW+1)^2 rows indexed by the rectangle of in-scope filter taps
     // ((ky_lo*(KH+1)+ky_hi)*(KW+1)+kx_lo)*(KW+1)+kx_hi.  corr_ystride: MATMUL, elements to advance per batch.

@@ -193,6 +193,37 @@ __device__ __forceinline__ void tmem_ld_wait()
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---------------------------------------------------------------- flags between CTAs of one launch (global memory)
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Named barrier over `nthreads` threads of the CTA that also ANDs a predicate over them (every participating thread
+// gets the result).  Used where a role made of several warps has to leave a loop together.
+__device__ __forceinline__ bool named_barrier_and(int id, int nthreads, bool pred)
+{
+    uint32_t r;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.b32 q, %3, 0;\n"
+        "bar.red.and.pred p, %1, %2, q;\n"
+        "selp.b32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(r)
+        : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
+        : "memory");
+    return r != 0;
+}
+
 // ---------------------------------------------------------------- wide global stores
 // 32 bytes per thread in one instruction (the address must be 32-byte aligned): every thread hands the memory system a
 // complete 32-byte sector, where two 16-byte stores would deliver two half-filled ones.

@@ -49,10 +49,18 @@ struct PairParams
     uint32_t idesc;
     int32_t* out;
     const int32_t* row_corr;    // [batch * H] or null
-    // fuse_row_sums: the b_zp term of every output row, -b_zp * sum_k A[row, k] + C * a_zp * b_zp, is worked out inside
-    // the kernel from the A tiles as they pass through shared memory (row_corr is then null)
+    // Zero-point sums inside the kernel (sum warps read the tiles as they pass through shared memory):
+    //   1: every tile sums the rows of its own A tile and hands them to its epilogue through shared memory; the term
+    //      of an output row is -b_zp * sum_k A[row, k] + C * a_zp * b_zp (row_corr is then null, corr as usual)
+    //   2: sums are shared between tiles through global memory.  The tile in column-tile 0 of a row of tiles sums the
+    //      rows of A (into row_corr, raw sums), the tile in row-tile 0 of a column of tiles sums the columns of B (into
+    //      corr, raw sums), each publishes an epoch number in `flags` when its 128 rows / columns are written, and
+    //      every epilogue waits for the flags of its rows and columns.  Producers always have smaller tile numbers than
+    //      their consumers and every pair walks its tiles in increasing order, so the waits cannot form a cycle.
     int fuse_row_sums;
     int32_t a_zp, b_zp;
+    uint32_t* flags;    // mode 2: [batch * tiles_m * 2] row flags, then [batch * tiles_w * 2] column flags
+    uint32_t epoch;     // mode 2: value a flag takes in this launch
     const int32_t* corr;        // [batch][corr_stride] or null; corr_stride a multiple of 256 that covers W
     int corr_stride;
     int debug;                  // diagnostic bit mask: 1 skip epilogue memory work, 2 skip MMA issue, 4 skip loads
@@ -86,6 +94,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
     __shared__ __align__(8) uint64_t bar_rs_full[2];            // per CTA: row sums of an accumulator buffer's tile ready
     __shared__ __align__(8) uint64_t bar_rs_empty[2];           // per CTA: epilogue has read them
     __shared__ int32_t row_sums[2][128];
+    __shared__ int32_t col_red[16][128];    // mode 2: partial column sums of the 16 row groups of a B tile
     __shared__ uint32_t tmem_base_holder;
 
     const int warp          = threadIdx.x >> 5;
@@ -262,7 +271,138 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
         // ------------------------------------------------------------------ row-sum warps (both CTAs)
         // 128 threads, eight per row of the A tile (one 16-byte piece each; the 128-byte swizzle only permutes pieces
         // inside a row), sixteen rows per pass.  A thread keeps the sums of its eight rows over the whole K loop.
-        if (p.fuse_row_sums)
+        if (p.fuse_row_sums == 2)
+        {
+            // 128 threads.  A tile: eight threads per row (one 16-byte piece each), 16 rows per pass.  B tile (128 K rows
+            // of 128 column bytes, pieces XOR-swizzled by the row number): thread (piece, group) reads logical piece
+            // `piece` of the eight rows of its group and keeps sixteen column sums.
+            const int ts    = (int)threadIdx.x - 32 * (2 + kPairEpiWarps);
+            const int piece = ts & 7, grp = ts >> 3;
+            uint32_t* flags_col = p.flags + (size_t)p.NB * p.tiles_m * 2;
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters)
+            {
+                const PairTile t   = decode_pair_tile(p, tile);
+                const bool do_rows = p.row_corr != nullptr && t.w0 == 0;
+                const bool do_cols = p.corr != nullptr && t.m0 == 0;
+                int32_t s[8], cs[16];
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    s[i] = 0;
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    cs[i] = 0;
+                int chunks_left = p.total_chunks;
+                while (chunks_left > 0 && ok)
+                {
+                    const uint32_t ready = ptx::smem_u32(rank == 0 ? &bar_full[stage] : &bar_go[stage]);
+                    if (!ptx::mbar_wait_bounded(ready, phase, kPairWaitLimit))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    const int nch = min(p.ksub, chunks_left);
+                    chunks_left -= nch;
+                    const uint8_t* sA = smem_raw + (smem_base - ptx::smem_u32(smem_raw)) + stage * p.stage_bytes;
+                    const uint8_t* sB = sA + p.ksub * kPairChunkBytes;
+                    if (do_rows)
+                    {
+                        for (int j = 0; j < nch; j++)
+                        {
+                            const uint8_t* base = sA + j * kPairChunkBytes + grp * 128 + piece * 16;
+#pragma unroll
+                            for (int i = 0; i < 8; i++)
+                            {
+                                const int4 v = *reinterpret_cast<const int4*>(base + i * 16 * 128);
+                                s[i] = __dp4a(v.x, 0x01010101, s[i]);
+                                s[i] = __dp4a(v.y, 0x01010101, s[i]);
+                                s[i] = __dp4a(v.z, 0x01010101, s[i]);
+                                s[i] = __dp4a(v.w, 0x01010101, s[i]);
+                            }
+                        }
+                    }
+                    if (do_cols)
+                    {
+                        for (int j = 0; j < nch; j++)
+                        {
+                            const uint8_t* base = sB + j * kPairChunkBytes + grp * 8 * 128;
+#pragma unroll
+                            for (int i = 0; i < 8; i++)
+                            {
+                                const int4 v    = *reinterpret_cast<const int4*>(base + i * 128 + ((piece ^ i) << 4));
+                                const int w4[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+                                for (int q = 0; q < 4; q++)
+                                {
+                                    cs[4 * q + 0] = __dp4a(w4[q], 0x00000001, cs[4 * q + 0]);
+                                    cs[4 * q + 1] = __dp4a(w4[q], 0x00000100, cs[4 * q + 1]);
+                                    cs[4 * q + 2] = __dp4a(w4[q], 0x00010000, cs[4 * q + 2]);
+                                    cs[4 * q + 3] = __dp4a(w4[q], 0x01000000, cs[4 * q + 3]);
+                                }
+                            }
+                        }
+                    }
+                    // this warp is done with the stage
+                    __syncwarp();
+                    if (lane == 0)
+                        ptx::mbar_arrive(ptx::smem_u32(&bar_empty[stage]));
+                    if (++stage == p.num_stages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                // The four sum warps leave the loop together: a warp whose wait gave up must not leave the others at the
+                // named barriers below.
+                ok = ptx::named_barrier_and(2, 32 * kPairSumWarps, ok);
+                if (!ok)
+                    break;
+                if (do_rows)
+                {
+                    const int m_base = t.m0 + (int)rank * 128;
+#pragma unroll
+                    for (int i = 0; i < 8; i++)
+                    {
+                        s[i] += __shfl_xor_sync(0xffffffffu, s[i], 1);
+                        s[i] += __shfl_xor_sync(0xffffffffu, s[i], 2);
+                        s[i] += __shfl_xor_sync(0xffffffffu, s[i], 4);
+                        const int m = m_base + grp + 16 * i;
+                        if (piece == 0 && m < p.H)
+                            const_cast<int32_t*>(p.row_corr)[(int64_t)t.n * p.H + m] = s[i];
+                    }
+                }
+                if (do_cols)
+                {
+#pragma unroll
+                    for (int i = 0; i < 16; i++)
+                        col_red[grp][piece * 16 + i] = cs[i];
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                    int32_t tsum = 0;
+#pragma unroll
+                    for (int g = 0; g < 16; g++)
+                        tsum += col_red[g][ts];
+                    const_cast<int32_t*>(p.corr)[(int64_t)t.n * p.corr_stride + t.w0 + (int)rank * 128 + ts] = tsum;
+                }
+                if (do_rows || do_cols)
+                {
+                    // publish: every writer fences its own stores, then one thread raises the flags
+                    __threadfence();
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                    if (ts == 0)
+                    {
+                        if (do_rows)
+                            ptx::st_release_gpu(p.flags + ((size_t)t.n * p.tiles_m + t.m0 / 256) * 2 + rank, p.epoch);
+                        if (do_cols)
+                            ptx::st_release_gpu(flags_col + ((size_t)t.n * p.tiles_w + t.w0 / 256) * 2 + rank, p.epoch);
+                    }
+                }
+            }
+            if (!ok && lane == 0)
+                atomicOr(p.status, TB200_DEV_TIMEOUT);
+        }
+        else if (p.fuse_row_sums)
         {
             const int ts    = (int)threadIdx.x - 32 * (2 + kPairEpiWarps);
             const int piece = ts & 7, row0 = ts >> 3;
@@ -362,9 +502,36 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
             const bool row_valid = m < p.H;
             const int64_t orow   = (int64_t)t.n * p.H + m;
             int32_t rc = 0;
-            if (p.row_corr != nullptr && row_valid)
+            if (p.row_corr != nullptr && row_valid && p.fuse_row_sums != 2)
                 rc = __ldg(p.row_corr + orow);
-            if (p.fuse_row_sums)
+            int32_t col_scale = 1;    // mode 2 keeps raw column sums: corr = -a_zp * sum
+            if (p.fuse_row_sums == 2)
+            {
+                // wait for the tiles that publish this tile's row sums (own half) and column sums (both halves)
+                if (lane == 0)
+                {
+                    const uint32_t* fcol = p.flags + (size_t)p.NB * p.tiles_m * 2 + ((size_t)t.n * p.tiles_w + t.w0 / 256) * 2;
+                    const uint32_t* frow = p.flags + ((size_t)t.n * p.tiles_m + t.m0 / 256) * 2 + rank;
+                    const long long t0 = clock64();
+                    while ((p.row_corr != nullptr && ptx::ld_acquire_gpu(frow) != p.epoch) ||
+                           (p.corr != nullptr && (ptx::ld_acquire_gpu(fcol) != p.epoch || ptx::ld_acquire_gpu(fcol + 1) != p.epoch)))
+                    {
+                        if (clock64() - t0 > kPairWaitLimit)
+                        {
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok)
+                    break;
+                rc = p.C * p.a_zp * p.b_zp;
+                if (p.row_corr != nullptr && row_valid)
+                    rc -= p.b_zp * __ldcg(p.row_corr + orow);
+                col_scale = -p.a_zp;
+            }
+            else if (p.fuse_row_sums)
             {
                 ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_rs_full[acc]), acc_phase, kPairWaitLimit);
                 ok = __all_sync(0xffffffffu, ok);
@@ -394,11 +561,12 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
 #pragma unroll
                     for (int q = 0; q < 8; q++)
                     {
-                        const int4 cv = __ldg(cp + q);
-                        v[4 * q + 0] += (uint32_t)cv.x + (uint32_t)rc;
-                        v[4 * q + 1] += (uint32_t)cv.y + (uint32_t)rc;
-                        v[4 * q + 2] += (uint32_t)cv.z + (uint32_t)rc;
-                        v[4 * q + 3] += (uint32_t)cv.w + (uint32_t)rc;
+                        // (L2 loads: in mode 2 the table was written by other SMs during this launch)
+                        const int4 cv = __ldcg(cp + q);
+                        v[4 * q + 0] += (uint32_t)(cv.x * col_scale) + (uint32_t)rc;
+                        v[4 * q + 1] += (uint32_t)(cv.y * col_scale) + (uint32_t)rc;
+                        v[4 * q + 2] += (uint32_t)(cv.z * col_scale) + (uint32_t)rc;
+                        v[4 * q + 3] += (uint32_t)(cv.w * col_scale) + (uint32_t)rc;
                     }
                 }
                 else
@@ -530,6 +698,8 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     k.out         = reinterpret_cast<int32_t*>(q.out);
     k.row_corr    = q.row_corr;
     k.fuse_row_sums = q.fuse_row_sums;
+    k.flags         = q.sum_flags;
+    k.epoch         = q.sum_epoch;
     k.a_zp          = q.a_zp;
     k.b_zp          = q.b_zp;
     k.corr        = q.corr;
