@@ -1103,8 +1103,7 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
             const bool need_sums = int_path && (a_zp != 0 || b_zp != 0);
             const int Wpad       = (W + 255) / 256 * 256;
             const size_t rows = (size_t)N * H, cols = (size_t)N * Wpad;
-            // (up to four planes of partial sums each when the CTA-pair kernel computes them itself)
-            const size_t sums_bytes = need_sums ? 4 * (((rows + 3) & ~(size_t)3) + cols) * sizeof(int32_t) : 0;
+            const size_t sums_bytes = need_sums ? (((rows + 3) & ~(size_t)3) + cols) * sizeof(int32_t) : 0;
             if (pad_b || need_sums)
             {
                 st = ensure_scratch(ctx, padb_bytes + sums_bytes);
@@ -1121,7 +1120,7 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
             if (need_sums)
             {
                 int32_t* row_corr = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(ctx->scratch) + padb_bytes);
-                int32_t* col_corr = row_corr + 4 * ((rows + 3) & ~(size_t)3);
+                int32_t* col_corr = row_corr + ((rows + 3) & ~(size_t)3);
                 // The CTA-pair kernel takes the sums from its own tiles while they sit in shared memory: both of them,
                 // shared between tiles through flags in global memory (no pass over A or B at all), or the row sums only.
                 // The flags carry a per-launch epoch, which a replayed CUDA graph would repeat: not while capturing.
@@ -1130,7 +1129,7 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
                 const bool fuse_rows = !fuse_all && b_zp != 0 && pair && env_flag("TB200_FUSE_ROW_SUMS", 1);
                 if (fuse_all)
                 {
-                    const size_t words = (size_t)N * 8 * ((H + 255) / 256 + (W + 255) / 256);
+                    const size_t words = (size_t)N * 2 * ((H + 255) / 256 + (W + 255) / 256);
                     if (words > ctx->pair_flag_words)
                     {
                         TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));

@@ -535,6 +535,35 @@ def test_matmul_int8_full_size_sampled(ctx):
     _free(ta, ta2, ta3, tbb, to, to2)
 
 
+def test_matmul_int8_pair_kernel_in_a_replayed_graph(ctx):
+    """A MATMUL large enough for the CTA-pair kernel, recorded into a CUDA graph and replayed on new operand values:
+    under capture the zero-point sums take their capture-safe form (flags with a per-launch epoch cannot be replayed)."""
+    N, H, C, W = 40, 256, 384, 256
+    r = util.rng(77)
+    a = r.integers(-128, 128, size=(N, H, C)).astype(np.int8)
+    b = r.integers(-128, 128, size=(N, C, W)).astype(np.int8)
+    ta, tbb, to = ctx.from_numpy(a), ctx.from_numpy(b), ctx.empty(I32, (N, H, W))
+    ctx.matmul(ta, tbb, to, 3, -2)            # eager first: scratch memory is sized outside the capture
+    assert ctx.last_kernel() == "tc_gemm_pair_i8_i32"
+    _, eager = to.download()
+    assert np.array_equal(eager, orc.matmul(a, b, 3, -2, nthreads=8))
+    ctx.capture_begin()
+    ctx.matmul(ta, tbb, to, 3, -2)
+    graph = ctx.capture_end()
+    for seed in (78, 79):
+        r2 = util.rng(seed)
+        a2 = r2.integers(-128, 128, size=(N, H, C)).astype(np.int8)
+        b2 = r2.integers(-128, 128, size=(N, C, W)).astype(np.int8)
+        ta.upload(a2)
+        tbb.upload(b2)
+        ctx.graph_launch(graph)
+        st, out = to.download()
+        assert st == tb.Status.OK
+        assert np.array_equal(out, orc.matmul(a2, b2, 3, -2, nthreads=8)), "replay with seed %d differs" % seed
+    ctx.graph_destroy(graph)
+    _free(ta, tbb, to)
+
+
 def _dot_check(out, a64, b64, fn, ks, out_name):
     ref = fn(a64, b64, mode="f64")
     bnd = fn(a64, b64, mode="f64", bounds=True)
