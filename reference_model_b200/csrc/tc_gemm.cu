@@ -787,7 +787,16 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     if (p.out_es == 4)
                     {
                         float* o = reinterpret_cast<float*>(p.out) + pix * p.OC + col;
-                        if (nvalid == 32 && ((p.OC & 3) == 0))
+                        if (nvalid == 32 && ((p.OC & 7) == 0) && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0)
+                        {
+                            // 32 bytes per store: whole sectors (see the int32 epilogue)
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8)
+                                ptx::st_global_v8(o + i, __float_as_uint(f[i]), __float_as_uint(f[i + 1]), __float_as_uint(f[i + 2]),
+                                                  __float_as_uint(f[i + 3]), __float_as_uint(f[i + 4]), __float_as_uint(f[i + 5]),
+                                                  __float_as_uint(f[i + 6]), __float_as_uint(f[i + 7]));
+                        }
+                        else if (nvalid == 32 && ((p.OC & 3) == 0))
                         {
 #pragma unroll
                             for (int i = 0; i < 32; i += 4)
@@ -813,7 +822,20 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                                 h[i] = __half_as_ushort(__float2half_rn(f[i]));
                         }
                         uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + pix * p.OC + col;
-                        if (nvalid == 32 && ((p.OC & 7) == 0))
+                        if (nvalid == 32 && ((p.OC & 15) == 0) && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0)
+                        {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 16)
+                                ptx::st_global_v8(o + i, (uint32_t)h[i] | ((uint32_t)h[i + 1] << 16),
+                                                  (uint32_t)h[i + 2] | ((uint32_t)h[i + 3] << 16),
+                                                  (uint32_t)h[i + 4] | ((uint32_t)h[i + 5] << 16),
+                                                  (uint32_t)h[i + 6] | ((uint32_t)h[i + 7] << 16),
+                                                  (uint32_t)h[i + 8] | ((uint32_t)h[i + 9] << 16),
+                                                  (uint32_t)h[i + 10] | ((uint32_t)h[i + 11] << 16),
+                                                  (uint32_t)h[i + 12] | ((uint32_t)h[i + 13] << 16),
+                                                  (uint32_t)h[i + 14] | ((uint32_t)h[i + 15] << 16));
+                        }
+                        else if (nvalid == 32 && ((p.OC & 7) == 0))
                         {
 #pragma unroll
                             for (int i = 0; i < 32; i += 8)
@@ -990,8 +1012,10 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     k.tiles_n = (N + BN - 1) / BN;
 
     int block_n = env_int("TB200_TC_BLOCK_N", 0);
+    // one column block that covers all channels when there are at most 256 of them (no half-empty second block);
+    // the epilogue works in 32-column chunks
     if (block_n == 0)
-        block_n = q.OC >= 256 ? 256 : q.OC > 64 ? 128 : q.OC > 32 ? 64 : 32;
+        block_n = q.OC >= 256 ? 256 : q.OC > 128 ? (q.OC + 31) / 32 * 32 : q.OC > 64 ? 128 : q.OC > 32 ? 64 : 32;
     if (q.b_mn_major && (block_n * es) % 128 != 0)
         block_n = 128 / es * ((block_n * es + 127) / 128);
     if (block_n > 256 || block_n % 32 != 0)
@@ -1057,7 +1081,7 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     // a single accumulator buffer (256 TMEM columns) lets two CTAs share an SM there, which doubles the epilogue warps
     // in flight; the lost MMA / epilogue overlap inside one CTA is made up by the neighbour CTA.
     const int mmas_per_tile = k.total_chunks * k.mmas_per_chunk;
-    k.acc_bufs = env_int("TB200_TC_ACC_BUFS", (block_n == 256 && mmas_per_tile <= 16) ? 1 : 2);
+    k.acc_bufs = env_int("TB200_TC_ACC_BUFS", (block_n > 128 && mmas_per_tile <= 16) ? 1 : 2);
     if (k.acc_bufs != 1)
         k.acc_bufs = 2;
     const bool pair_small = block_n <= 128 && 4 * k.stage_bytes <= 100 * 1024;

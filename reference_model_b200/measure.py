@@ -217,9 +217,19 @@ def c4_block(ctx, timer, torch, iters, hbm, src):
 
         unfused = 2 * (x.numel() + 2 * t1.numel() + 2 * t2.numel() + y.numel())
         ms, note = timer.time(block, iters, unfused)
+        parts = {}
+        for pname, fn, nbytes in (
+                ("conv1x1_32_192", lambda: ctx.conv2d(X, W1, B1, T1, [0, 0, 0, 0], [1, 1], [1, 1], 0, 0, relu6),
+                 2 * (x.numel() + t1.numel())),
+                ("depthwise3x3_s2", lambda: ctx.depthwise_conv2d(T1, WD, BD, T2, [1, 0, 1, 0], [2, 2], [1, 1], 0, 0, relu6),
+                 2 * (t1.numel() + t2.numel())),
+                ("conv1x1_192_64", lambda: ctx.conv2d(T2, W2, B2, Y, [0, 0, 0, 0], [1, 1], [1, 1], 0, 0, None),
+                 2 * (t2.numel() + y.numel()))):
+            pms, _ = timer.time(fn, iters, nbytes)
+            parts[pname] = {"ms": pms, "GBps": nbytes / pms / 1e6, "kernel": ctx.last_kernel()}
         flops = 2.0 * N * (112 * 112 * 32 * 192 + 56 * 56 * 192 * 9 + 56 * 56 * 192 * 64)
         out[dt_name] = {"ms": ms, "TFLOPS": flops / ms / 1e9, "GBps_unfused_traffic": unfused / ms / 1e6,
-                        "frac_of_hbm": unfused / ms / 1e6 / hbm}
+                        "frac_of_hbm": unfused / ms / 1e6 / hbm, "kernels": parts}
     return {"config": "c4 inverted residual block 64x112x112x32 (3 kernels, intermediates in HBM)", "bound": "hbm",
             "peak_GBps": hbm, "peak_source": src, "algorithmic_bytes_unfused": unfused, **out}
 
