@@ -731,9 +731,7 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     k.num_stages  = std::min(kPairMaxStages, std::max(2, pair_env_int("TB200_PAIR_STAGES", (224 * 1024) / k.stage_bytes)));
     const int smem_bytes = k.num_stages * k.stage_bytes + 1024;
     TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(tc_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-    const int clusters = std::max(1, std::min(k.num_tiles, ctx->num_sms / 2));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim          = dim3((unsigned)(2 * clusters));
     cfg.blockDim         = dim3(kPairThreads);
     cfg.dynamicSmemBytes = (size_t)smem_bytes;
     cfg.stream           = ctx->stream;
@@ -744,6 +742,22 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     attr[0].val.clusterDim.z = 1;
     cfg.attrs    = attr;
     cfg.numAttrs = 1;
+    // Tiles wait for sums that other pairs publish, so every pair of the grid has to be resident at once: never more
+    // pairs than the device can hold of this kernel (asked once; one CTA per SM because of its shared memory).
+    static int max_pairs = 0;
+    if (max_pairs == 0)
+    {
+        cfg.gridDim = dim3((unsigned)(2 * (ctx->num_sms / 2)));
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, tc_gemm_pair_kernel, &cfg) != cudaSuccess || n <= 0)
+        {
+            cudaGetLastError();
+            n = ctx->num_sms / 2;
+        }
+        max_pairs = n;
+    }
+    const int clusters = std::max(1, std::min(k.num_tiles, std::min(max_pairs, ctx->num_sms / 2)));
+    cfg.gridDim        = dim3((unsigned)(2 * clusters));
     timer_begin(ctx);
     const cudaError_t le = cudaLaunchKernelEx(&cfg, tc_gemm_pair_kernel, k);
     timer_end(ctx);
