@@ -480,6 +480,8 @@ def main():
                          "peak_source": "2 x %s bf16 %s (int8 peak not measured on this pool); nominal dense int8 is 4500"
                                         % (peaks["source"], "sustained" if long_loop else "burst"),
                          "frac_of_nominal_int8": achieved / 4500.0,
+                         "note": "achieved counts 2*M*N*K only; the timed kernel also takes the zero-point row / column "
+                                 "sums from its tiles (the whole step is this one launch)",
                          "algorithmic_bytes_per_launch": ALG_BYTES_PER_STEP},
             "cpu_baseline": cpu_baseline,
         }))
