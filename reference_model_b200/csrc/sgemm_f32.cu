@@ -1,7 +1,7 @@
 // fp32 batched MATMUL on CUDA cores: FFMA only, no TF32, so every product and sum is an IEEE fp32 operation
 // and the result stays inside the reference's dot-product error bound.
 //
-// 128 x 128 output tile per 256-thread block, K stepped 8 at a time through double-buffered shared memory,
+// 128 x 128 output tile per 256-thread block, K stepped 16 at a time through double-buffered shared memory,
 // 8 x 8 accumulators per thread arranged as 2 x 2 groups of 4 x 4 so that shared-memory reads are 128-bit
 // and conflict-free.  A [N,H,C] is read along C (transposed into shared memory), B [N,C,W] along W.
 #include <cuda_runtime.h>
@@ -13,7 +13,7 @@ namespace tb200
 namespace
 {
 
-constexpr int BM = 128, BN = 128, BK = 8;
+constexpr int BM = 128, BN = 128, BK = 16;
 
 template <bool VEC>
 __global__ void __launch_bounds__(256, 2)
@@ -33,8 +33,8 @@ __global__ void __launch_bounds__(256, 2)
 
     const int tid = threadIdx.x;
     const int tx = tid % 16, ty = tid / 16;
-    // global -> shared assignment: A tile 128 rows x 8 k (one float4 along k per thread),
-    // B tile 8 k x 128 cols (one float4 along n per thread)
+    // global -> shared assignment: A tile 128 rows x 16 k (two float4 along k per thread: k halves 0-7 and 8-15),
+    // B tile 16 k x 128 cols (two float4 along n per thread: k rows b_k and b_k + 8)
     const int a_row = tid / 2, a_k = (tid % 2) * 4;
     const int b_k = tid / 32, b_col = (tid % 32) * 4;
 
@@ -45,54 +45,70 @@ __global__ void __launch_bounds__(256, 2)
         for (int j = 0; j < 8; j++)
             acc[i][j] = 0.f;
 
-    float4 ra, rb;
-    auto load_tiles = [&](int k0) {
-        const int gm = m0 + a_row, gk = k0 + a_k;
-        if (VEC)
-        {
-            ra = (gm < H && gk < C) ? *reinterpret_cast<const float4*>(Ab + (int64_t)gm * C + gk)
-                                    : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-        else
-        {
-            float t[4];
+    float4 ra[2], rb[2];
+    auto load_tiles = [&](int k0, int nbuf) {
 #pragma unroll
-            for (int j = 0; j < 4; j++)
-                t[j] = (gm < H && gk + j < C) ? Ab[(int64_t)gm * C + gk + j] : 0.f;
-            ra = make_float4(t[0], t[1], t[2], t[3]);
-        }
-        const int bk = k0 + b_k, bn = n0 + b_col;
-        if (VEC)
+        for (int h = 0; h < 2; h++)
         {
-            rb = (bk < C && bn < W) ? *reinterpret_cast<const float4*>(Bb + (int64_t)bk * W + bn)
-                                    : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-        else
-        {
-            float t[4];
+            const int gm = m0 + a_row, gk = k0 + a_k + 8 * h;
+            if (VEC)
+            {
+                ra[h] = (gm < H && gk < C) ? *reinterpret_cast<const float4*>(Ab + (int64_t)gm * C + gk)
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            else
+            {
+                float t[4];
 #pragma unroll
-            for (int j = 0; j < 4; j++)
-                t[j] = (bk < C && bn + j < W) ? Bb[(int64_t)bk * W + bn + j] : 0.f;
-            rb = make_float4(t[0], t[1], t[2], t[3]);
+                for (int j = 0; j < 4; j++)
+                    t[j] = (gm < H && gk + j < C) ? Ab[(int64_t)gm * C + gk + j] : 0.f;
+                ra[h] = make_float4(t[0], t[1], t[2], t[3]);
+            }
+            const int bk = k0 + b_k + 8 * h, bn = n0 + b_col;
+            if (VEC)
+            {
+                // B needs no transposition: an asynchronous 16-byte copy straight into the other shared-memory buffer
+                // (zero-filled outside the matrix), no staging registers
+                const bool inside = bk < C && bn < W;
+                const float* src  = inside ? Bb + (int64_t)bk * W + bn : Bb;
+                const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(&Bs[nbuf][b_k + 8 * h][b_col]));
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(inside ? 16 : 0)
+                             : "memory");
+            }
+            else
+            {
+                float t[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    t[j] = (bk < C && bn + j < W) ? Bb[(int64_t)bk * W + bn + j] : 0.f;
+                rb[h] = make_float4(t[0], t[1], t[2], t[3]);
+            }
         }
     };
     auto store_tiles = [&](int buf) {
-        As[buf][a_k + 0][a_row] = ra.x;
-        As[buf][a_k + 1][a_row] = ra.y;
-        As[buf][a_k + 2][a_row] = ra.z;
-        As[buf][a_k + 3][a_row] = ra.w;
-        *reinterpret_cast<float4*>(&Bs[buf][b_k][b_col]) = rb;
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+        {
+            As[buf][a_k + 8 * h + 0][a_row] = ra[h].x;
+            As[buf][a_k + 8 * h + 1][a_row] = ra[h].y;
+            As[buf][a_k + 8 * h + 2][a_row] = ra[h].z;
+            As[buf][a_k + 8 * h + 3][a_row] = ra[h].w;
+            if (!VEC)
+                *reinterpret_cast<float4*>(&Bs[buf][b_k + 8 * h][b_col]) = rb[h];
+        }
+        if (VEC)
+            asm volatile("cp.async.wait_all;" ::: "memory");
     };
 
     const int nk = (C + BK - 1) / BK;
-    load_tiles(0);
+    load_tiles(0, 0);
     store_tiles(0);
     __syncthreads();
     for (int kt = 0; kt < nk; kt++)
     {
         const int buf = kt & 1;
         if (kt + 1 < nk)
-            load_tiles((kt + 1) * BK);
+            load_tiles((kt + 1) * BK, buf ^ 1);
 #pragma unroll
         for (int k = 0; k < BK; k++)
         {
