@@ -129,6 +129,8 @@ def main():
     ap.add_argument("--conv", default=None,
                     help="also time one int8 CONV2D+RESCALE+CLAMP layer: N,IH,IW,IC,OC,K,stride,pad (one pad for all four sides, "
                          "or four values top,bottom,left,right)")
+    ap.add_argument("--join", default=None,
+                    help="also time one fused int8 residual join (RESCALE x2, ADD, RESCALE, CLAMP): N,H,W,C")
     ap.add_argument("--graph-profile", type=int, default=0, metavar="BATCH",
                     help="evaluate the ResNet-50-shaped int8 graph at this batch step by step (a device sync around "
                          "every step) and print the slowest steps and the time per kind of step")
@@ -152,6 +154,23 @@ def main():
             res = conv_i8_config(ctx, timer, "conv %s" % args.conv, n, ih, iw, ic, oc, k, k, st, pads, -128,
                                  args.iters, 9)
             print(json.dumps(res))
+            sys.stdout.flush()
+        if args.join:
+            shape = tuple(int(v) for v in args.join.split(","))
+            r = np.random.default_rng(5)
+            ja = ctx.from_numpy(r.integers(-128, 128, size=shape, dtype=np.int8))
+            jb = ctx.from_numpy(r.integers(-128, 128, size=shape, dtype=np.int8))
+            jo = ctx.empty(tb.DType.INT8, shape)
+            cm = [ctx.from_numpy(np.asarray([v], np.int32)) for v in (1 << 30, 1 << 30, 1270000000)]
+            cs = [ctx.from_numpy(np.asarray([v], np.int8)) for v in (21, 21, 41)]
+            nbytes = 3 * int(np.prod(shape))
+            ms, note = timer.time(lambda: ctx.residual_add(ja, tb.RescaleAttr(cm[0], cs[0], -128, 0), jb,
+                                                           tb.RescaleAttr(cm[1], cs[1], -128, 0),
+                                                           tb.RescaleAttr(cm[2], cs[2], 0, -128, rounding="DOUBLE_ROUND"),
+                                                           jo, clamp=(-128, 127)), args.iters, nbytes)
+            print(json.dumps({"config": "residual join %s" % args.join, "kernel": ctx.last_kernel(), "ms": ms,
+                              "GBps": nbytes / ms / 1e6, "algorithmic_bytes": nbytes, "peak_GBps": hbm,
+                              "frac": nbytes / ms / 1e6 / hbm, "l2": note}))
             sys.stdout.flush()
         for name in args.configs.split(","):
             if name == "c1":

@@ -535,6 +535,37 @@ def test_matmul_int8_full_size_sampled(ctx):
     _free(ta, ta2, ta3, tbb, to, to2)
 
 
+def test_matmul_int8_pair_kernel_random_shapes(ctx):
+    """Seeded random shapes and zero points on the CTA-pair kernel (ragged row / column / K tails, one or several tiles
+    per batch, zero points present or not) against the one-thread-per-output kernel, and against the oracle for the
+    first two; every shape is evaluated twice in a row (the flags between tiles carry a per-launch epoch)."""
+    r = util.rng(4242)
+    for case in range(8):
+        tiles_m, tiles_w = int(r.integers(1, 4)), int(r.integers(1, 4))
+        H = 256 * tiles_m - int(r.integers(0, 200)) if tiles_m > 1 else 256 + int(r.integers(0, 100))
+        W = (256 * tiles_w - int(r.integers(0, 200)) if tiles_w > 1 else 256 + int(r.integers(0, 100))) // 16 * 16
+        C = int(r.integers(8, 40)) * 16
+        N = -(-40 // (((H + 255) // 256) * ((W + 255) // 256))) + int(r.integers(0, 3))
+        azp, bzp = (int(r.integers(-128, 128)) if r.integers(0, 4) else 0 for _ in range(2))
+        a = r.integers(-128, 128, size=(N, H, C)).astype(np.int8)
+        b = r.integers(-128, 128, size=(N, C, W)).astype(np.int8)
+        ta, tbb, to, tref = ctx.from_numpy(a), ctx.from_numpy(b), ctx.empty(I32, (N, H, W)), ctx.empty(I32, (N, H, W))
+        old = ctx.set_kernel_policy(1)
+        ctx.matmul(ta, tbb, tref, azp, bzp)
+        ctx.set_kernel_policy(old)
+        _, ref = tref.download()
+        for rep in range(2):
+            ctx.matmul(ta, tbb, to, azp, bzp)
+            assert ctx.last_kernel() == "tc_gemm_pair_i8_i32", (case, N, H, C, W)
+            st, out = to.download()
+            assert st == tb.Status.OK
+            assert np.array_equal(out, ref), "case %d rep %d (%d,%d,%d,%d zp %d,%d): %d differ" % (
+                case, rep, N, H, C, W, azp, bzp, (out != ref).sum())
+        if case < 2:
+            assert np.array_equal(ref, orc.matmul(a, b, azp, bzp, nthreads=8))
+        _free(ta, tbb, to, tref)
+
+
 def test_matmul_int8_pair_kernel_in_a_replayed_graph(ctx):
     """A MATMUL large enough for the CTA-pair kernel, recorded into a CUDA graph and replayed on new operand values:
     under capture the zero-point sums take their capture-safe form (flags with a per-launch epoch cannot be replayed)."""
