@@ -399,10 +399,7 @@ __global__ void __launch_bounds__(512, 2) residual_add_i8_table_kernel(const int
     const bool check = __syncthreads_or(any != 0) != 0;
     bool bad = false;
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += step)
-    {
-        const int4 va = __ldg(reinterpret_cast<const int4*>(a) + i);
-        const int4 vb = __ldg(reinterpret_cast<const int4*>(b) + i);
+    auto lookup16 = [&](const int4& va, const int4& vb) -> uint4 {
         const uint32_t wa[4] = { (uint32_t)va.x, (uint32_t)va.y, (uint32_t)va.z, (uint32_t)va.w };
         const uint32_t wb[4] = { (uint32_t)vb.x, (uint32_t)vb.y, (uint32_t)vb.z, (uint32_t)vb.w };
         uint32_t wo[4];
@@ -421,7 +418,24 @@ __global__ void __launch_bounds__(512, 2) residual_add_i8_table_kernel(const int
                          (bits[i3 >> 5] >> (i3 & 31))) & 1u) != 0;
             wo[q] = __byte_perm(__byte_perm(r0, r1, 0x0040), __byte_perm(r2, r3, 0x0040), 0x5410);
         }
-        reinterpret_cast<uint4*>(out)[i] = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+        return make_uint4(wo[0], wo[1], wo[2], wo[3]);
+    };
+    // two vectors per pass: four 16-byte loads in flight per thread (the kernel waits on memory, not on arithmetic)
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + step < n16; i += 2 * step)
+    {
+        const int4 va0 = __ldg(reinterpret_cast<const int4*>(a) + i);
+        const int4 vb0 = __ldg(reinterpret_cast<const int4*>(b) + i);
+        const int4 va1 = __ldg(reinterpret_cast<const int4*>(a) + i + step);
+        const int4 vb1 = __ldg(reinterpret_cast<const int4*>(b) + i + step);
+        reinterpret_cast<uint4*>(out)[i]        = lookup16(va0, vb0);
+        reinterpret_cast<uint4*>(out)[i + step] = lookup16(va1, vb1);
+    }
+    if (i < n16)
+    {
+        const int4 va = __ldg(reinterpret_cast<const int4*>(a) + i);
+        const int4 vb = __ldg(reinterpret_cast<const int4*>(b) + i);
+        reinterpret_cast<uint4*>(out)[i] = lookup16(va, vb);
     }
     if (bad)
         atomicOr(status, TB200_DEV_UNPREDICTABLE);

@@ -10,6 +10,9 @@
 //     at 128 SM cycles per instruction (8192 MAC per cycle and SM) against 171 for the single-CTA form
 //   * accumulators live in both CTAs' TMEM (128 rows x 256 columns each, two buffers); each CTA's eight epilogue warps
 //     add the zero-point terms and store their own rows
+// Tiles are handed out in rounds of one tile per pair; the pair that takes position k of a round moves to position k+1
+// in the next one (all roles compute the same walk).  With a fixed assignment and an even number of pairs the same
+// pairs would get every tile that carries zero-point sums; the rotation spreads that extra work evenly.
 // Completion signals cross the pair: TMA byte counts of both CTAs land on the first CTA's "full" barrier,
 // tcgen05.commit arrives on the "empty" / "accumulator ready" barriers of both, and every epilogue warp arrives on the
 // first CTA's "accumulator free" barrier.  Every wait is bounded; a wait that gives up sets TB200_DEV_TIMEOUT and all
@@ -144,8 +147,11 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters)
+            for (int round = 0, base = 0; base < p.num_tiles && ok; round++, base += num_clusters)
             {
+                const int tile = base + (cluster_id + round) % num_clusters;
+                if (tile >= p.num_tiles)
+                    continue;
                 const PairTile t = decode_pair_tile(p, tile);
                 const int m0 = t.m0 + (int)rank * 128;
                 const int w0 = t.w0 + (int)rank * 128;
@@ -203,8 +209,11 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
             uint32_t acc_phase = 0;
             bool ok = true;
             const bool issue = !(p.debug & 2);
-            for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters)
+            for (int round = 0, base = 0; base < p.num_tiles && ok; round++, base += num_clusters)
             {
+                const int tile = base + (cluster_id + round) % num_clusters;
+                if (tile >= p.num_tiles)
+                    continue;
                 if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, kPairWaitLimit))
                 {
                     ok = false;
@@ -282,8 +291,11 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters)
+            for (int round = 0, base = 0; base < p.num_tiles; round++, base += num_clusters)
             {
+                const int tile = base + (cluster_id + round) % num_clusters;
+                if (tile >= p.num_tiles)
+                    continue;
                 const PairTile t   = decode_pair_tile(p, tile);
                 const bool do_rows = p.row_corr != nullptr && t.w0 == 0;
                 const bool do_cols = p.corr != nullptr && t.m0 == 0;
@@ -411,8 +423,11 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters)
+            for (int round = 0, base = 0; base < p.num_tiles && ok; round++, base += num_clusters)
             {
+                const int tile = base + (cluster_id + round) % num_clusters;
+                if (tile >= p.num_tiles)
+                    continue;
                 ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_rs_empty[acc]), acc_phase ^ 1u, kPairWaitLimit);
                 int32_t s[8];
 #pragma unroll
@@ -488,8 +503,11 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters)
+        for (int round = 0, base = 0; base < p.num_tiles; round++, base += num_clusters)
         {
+            const int tile = base + (cluster_id + round) % num_clusters;
+            if (tile >= p.num_tiles)
+                continue;
             const PairTile t = decode_pair_tile(p, tile);
             ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_full[acc]), acc_phase, kPairWaitLimit);
             // the whole warp must agree before the warp-collective TMEM loads
