@@ -183,6 +183,18 @@ extern "C"
                                                   const int32_t stride[2], const int32_t dilation[2],
                                                   const tb200_epilogue* epilogue, tb200_tensor* output);
 
+    /* TRANSPOSE_CONV2D.  Replaces OpTransposeConv2d::eval (reference_model/src/ops/tensor_ops.cpp:2059-2197) and
+     * OpTransposeConv2d::checkTensorAttributes (:1982-2056).  input NHWC, weight OHWI, bias [OC] or [1];
+     * out_pad = {top,bottom,left,right} (each > -kernel), stride = {y,x}; the output must be
+     * (IH-1)*stride_y + out_pad_top + out_pad_bottom + KH by the same in x.  Type tuples and the epilogue are
+     * those of tb200_conv2d.  Evaluated as a stride-1 CONV2D over the input spread out by the stride (gaps hold
+     * the input zero point) with the kernel mirrored, so it runs on the same tensor-core kernel. */
+    TB200_API tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tensor* input,
+                                                  const tb200_tensor* weight, const tb200_tensor* bias,
+                                                  int32_t input_zp, int32_t weight_zp, const int32_t out_pad[4],
+                                                  const int32_t stride[2], const tb200_epilogue* epilogue,
+                                                  tb200_tensor* output);
+
     /* MATMUL.  Replaces OpMatMul<A,B,Out>::eval (reference_model/src/ops/tensor_ops.cpp:1423-1492, checks :1347-1420).
      * a [N,H,C], b [N,C,W], output [N,H,W]; INT8xINT8->INT32, FP16/BF16->same or FP32, FP32->FP32 (FFMA, no TF32). */
     TB200_API tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, const tb200_tensor* b, int32_t a_zp,

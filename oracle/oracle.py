@@ -131,6 +131,34 @@ def depthwise_conv2d(x, w, bias, pad, stride, dilation, in_zp=0, w_zp=0, mode="i
                          local_bound, nthreads)
 
 
+def transpose_conv_out_hw(IH, IW, KH, KW, out_pad, stride):
+    """Output size OpTransposeConv2d::checkTensorAttributes demands (tensor_ops.cpp:2044-2045)."""
+    return ((IH - 1) * stride[0] + out_pad[0] + out_pad[1] + KH, (IW - 1) * stride[1] + out_pad[2] + out_pad[3] + KW)
+
+
+def check_transpose_conv2d_attribute(IH, IW, OH, OW, KH, KW, out_pad, stride):
+    return int(lib().orc_check_transpose_conv2d_attribute(IH, IW, OH, OW, KH, KW, _ivec(out_pad), _ivec(stride)))
+
+
+def transpose_conv2d(x, w, bias, out_pad, stride, in_zp=0, w_zp=0, mode="i32", nthreads=1):
+    """OpTransposeConv2d::eval (tensor_ops.cpp:2059-2197).  x NHWC, w OHWI; mode: i32 | f32 | f64 (precise)."""
+    N, IH, IW, IC = x.shape
+    OC, KH, KW, _ = w.shape
+    OH, OW = transpose_conv_out_hw(IH, IW, KH, KW, out_pad, stride)
+    conv = {"i32": _i32, "f32": _f32, "f64": _f64}[mode]
+    dt = {"i32": np.int32, "f32": np.float32, "f64": np.float64}[mode]
+    x_, w_, b_ = conv(x), conv(w), conv(bias).reshape(-1)
+    out = np.zeros((N, OH, OW, OC), dtype=dt)
+    args = [_p(x_), _p(w_), _p(b_), int(b_.size), N, IH, IW, IC, OC, KH, KW, OH, OW, _ivec(out_pad), _ivec(stride)]
+    if mode == "i32":
+        args += [ctypes.c_int32(int(in_zp)), ctypes.c_int32(int(w_zp))]
+    args += [_p(out), int(nthreads)]
+    fn = getattr(lib(), "orc_transpose_conv2d_%s" % mode)
+    fn.restype = None
+    fn(*args)
+    return out
+
+
 def matmul(a, b, a_zp=0, b_zp=0, mode="i32", bounds=False, nthreads=1):
     """OpMatMul::eval (tensor_ops.cpp:1423-1492); a [N,H,C], b [N,C,W]."""
     N, H, C = a.shape

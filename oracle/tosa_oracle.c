@@ -355,6 +355,93 @@ ORC_API void orc_depthwise_conv2d_f64(const double* in, const double* w, const d
 }
 
 /* ------------------------------------------------------------------------- */
+/* TRANSPOSE_CONV2D (OpTransposeConv2d::eval, src/ops/tensor_ops.cpp:2059-2197)*/
+/*   per output (oy, ox): iy = oy - out_pad_top, y = iy - ky; the tap is in     */
+/*   scope when 0 <= y < IH*stride_y and y % stride_y == 0 (same for x), and    */
+/*   then reads in(y/stride_y, x/stride_x) (:2148-2171); tap order ky -> kx ->  */
+/*   ic; out = (Out)acc + bias[oc or 0] (:2176-2177); weights OHWI, not flipped.*/
+/*   The reference's own tests hold no known-answer vector for this operator:   */
+/*   the restatement is pinned through its identity with the pinned CONV2D      */
+/*   restatement above (zero-stuffed input, mirrored kernel) and a hand case.   */
+/* ------------------------------------------------------------------------- */
+/* returns 0 when OpTransposeConv2d::checkTensorAttributes (:1982-2056) accepts the attributes */
+ORC_API int orc_check_transpose_conv2d_attribute(int IH, int IW, int OH, int OW, int KH, int KW, const int* out_pad,
+                                                 const int* stride)
+{
+    if (stride[0] < 1 || stride[1] < 1)
+        return 1;
+    if (out_pad[0] <= -KH || out_pad[1] <= -KH || out_pad[2] <= -KW || out_pad[3] <= -KW)
+        return 2;
+    if (OH != (IH - 1) * stride[0] + out_pad[0] + out_pad[1] + KH)
+        return 3;
+    if (OW != (IW - 1) * stride[1] + out_pad[2] + out_pad[3] + KW)
+        return 3;
+    return 0;
+}
+
+#define ORC_TCONV_BODY(TIN, TACC, TOUT)                                                                      \
+    _Pragma("omp parallel for collapse(2) num_threads(nthreads) if (nthreads > 1)") for (int ob = 0;        \
+                                                                                          ob < N; ob++)     \
+    {                                                                                                        \
+        for (int oy = 0; oy < OH; oy++)                                                                      \
+        {                                                                                                    \
+            for (int ox = 0; ox < OW; ox++)                                                                  \
+            {                                                                                                \
+                int iy = oy - out_pad[0];                                                                    \
+                int ix = ox - out_pad[2];                                                                    \
+                for (int oc = 0; oc < OC; oc++)                                                              \
+                {                                                                                            \
+                    TACC acc = 0;                                                                            \
+                    for (int ky = 0; ky < KH; ky++)                                                          \
+                    {                                                                                        \
+                        for (int kx = 0; kx < KW; kx++)                                                      \
+                        {                                                                                    \
+                            int y = iy - ky;                                                                 \
+                            int x = ix - kx;                                                                 \
+                            int in_scope = (0 <= y && y < IH * stride[0]) && (0 <= x && x < IW * stride[1]) && \
+                                           (y % stride[0] == 0) && (x % stride[1] == 0);                     \
+                            if (!in_scope)                                                                   \
+                                continue;                                                                    \
+                            const TIN* ip = in + (((int64_t)ob * IH + y / stride[0]) * IW + x / stride[1]) * IC; \
+                            const TIN* wp = w + (((int64_t)oc * KH + ky) * KW + kx) * IC;                    \
+                            for (int ic = 0; ic < IC; ic++)                                                  \
+                                acc += ((TACC)ip[ic] - (TACC)in_zp) * ((TACC)wp[ic] - (TACC)w_zp);          \
+                        }                                                                                    \
+                    }                                                                                        \
+                    out[(((int64_t)ob * OH + oy) * OW + ox) * OC + oc] = (TOUT)acc + bias[bias_n == 1 ? 0 : oc]; \
+                }                                                                                            \
+            }                                                                                                \
+        }                                                                                                    \
+    }
+
+/* integer instantiation <INT8,INT8,INT32,INT32> (src/ops/tensor_ops.cpp:2290) */
+ORC_API void orc_transpose_conv2d_i32(const int32_t* in, const int32_t* w, const int32_t* bias, int bias_n, int N,
+                                      int IH, int IW, int IC, int OC, int KH, int KW, int OH, int OW,
+                                      const int* out_pad, const int* stride, int32_t in_zp, int32_t w_zp,
+                                      int32_t* out, int nthreads)
+{
+    ORC_TCONV_BODY(int32_t, uint32_t, uint32_t)
+}
+
+/* floating instantiations with an fp32 accumulator (src/ops/tensor_ops.cpp:2286-2288) */
+ORC_API void orc_transpose_conv2d_f32(const float* in, const float* w, const float* bias, int bias_n, int N, int IH,
+                                      int IW, int IC, int OC, int KH, int KW, int OH, int OW, const int* out_pad,
+                                      const int* stride, float* out, int nthreads)
+{
+    const float in_zp = 0, w_zp = 0;
+    ORC_TCONV_BODY(float, float, float)
+}
+
+/* precise mode (all floating dtypes become FP64, include/dtype.h:124-152) */
+ORC_API void orc_transpose_conv2d_f64(const double* in, const double* w, const double* bias, int bias_n, int N,
+                                      int IH, int IW, int IC, int OC, int KH, int KW, int OH, int OW,
+                                      const int* out_pad, const int* stride, double* out, int nthreads)
+{
+    const double in_zp = 0, w_zp = 0;
+    ORC_TCONV_BODY(double, double, double)
+}
+
+/* ------------------------------------------------------------------------- */
 /* MATMUL (OpMatMul::eval, src/ops/tensor_ops.cpp:1423-1492)                  */
 /*   per batch n: out[n] = (A[n] - a_zp) x (B[n] - b_zp); A [N,H,C], B [N,C,W]*/
 /*   The reference hands the product to Eigen's contraction (:1472); integer   */

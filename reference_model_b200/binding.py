@@ -69,7 +69,7 @@ EXPORTS = [
     "tb200_timer_enable", "tb200_timer_read", "tb200_capture_begin", "tb200_capture_end", "tb200_graph_launch",
     "tb200_graph_destroy",
     "tb200_tensor_alloc", "tb200_tensor_wrap", "tb200_tensor_free", "tb200_tensor_upload", "tb200_tensor_download",
-    "tb200_tensor_data", "tb200_tensor_bytes", "tb200_tensor_slice", "tb200_tensor_reshape", "tb200_conv2d", "tb200_depthwise_conv2d", "tb200_matmul",
+    "tb200_tensor_data", "tb200_tensor_bytes", "tb200_tensor_slice", "tb200_tensor_reshape", "tb200_conv2d", "tb200_depthwise_conv2d", "tb200_transpose_conv2d", "tb200_matmul",
     "tb200_rescale", "tb200_clamp", "tb200_add", "tb200_residual_add", "tb200_max_pool2d", "tb200_avg_pool2d",
     "tb200_matmul_host", "tb200_set_kernel_policy", "tb200_last_kernel", "tb200_matmul_i8_noalloc",
 ]
@@ -109,6 +109,7 @@ def load_library():
         "tb200_tensor_bytes": (ctypes.c_size_t, [vp]),
         "tb200_conv2d": (i32, [vp, vp, vp, vp, i32, i32, p_i32, p_i32, p_i32, ctypes.POINTER(_Epilogue), vp]),
         "tb200_depthwise_conv2d": (i32, [vp, vp, vp, vp, i32, i32, p_i32, p_i32, p_i32, ctypes.POINTER(_Epilogue), vp]),
+        "tb200_transpose_conv2d": (i32, [vp, vp, vp, vp, i32, i32, p_i32, p_i32, ctypes.POINTER(_Epilogue), vp]),
         "tb200_matmul": (i32, [vp, vp, vp, i32, i32, ctypes.POINTER(_Epilogue), vp]),
         "tb200_rescale": (i32, [vp, vp, ctypes.POINTER(_RescaleAttr), vp]),
         "tb200_clamp": (i32, [vp, vp, i32, i32, ctypes.c_float, ctypes.c_float, i32, vp]),
@@ -331,6 +332,13 @@ class Context:
         return self._check(self.lib.tb200_depthwise_conv2d(self.handle, x.handle, w.handle, bias.handle,
                                                            int(input_zp), int(weight_zp), _ivec(pad), _ivec(stride),
                                                            _ivec(dilation),
+                                                           ctypes.byref(epilogue.c) if epilogue else None,
+                                                           out.handle), check)
+
+    def transpose_conv2d(self, x, w, bias, out, out_pad, stride, input_zp=0, weight_zp=0, epilogue=None, check=True):
+        return self._check(self.lib.tb200_transpose_conv2d(self.handle, x.handle, w.handle, bias.handle,
+                                                           int(input_zp), int(weight_zp), _ivec(out_pad),
+                                                           _ivec(stride),
                                                            ctypes.byref(epilogue.c) if epilogue else None,
                                                            out.handle), check)
 

@@ -343,6 +343,8 @@ extern "C" tb200_status tb200_ctx_destroy(tb200_ctx* ctx)
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch)
         cudaFree(ctx->scratch);
+    if (ctx->stage)
+        cudaFree(ctx->stage);
     if (ctx->join_table)
         cudaFree(ctx->join_table);
     if (ctx->pair_flags)
@@ -685,10 +687,19 @@ extern "C" tb200_status tb200_tensor_reshape(tb200_ctx* ctx, const tb200_tensor*
 }
 
 // =================================================================================================== CONV2D
-extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
-                                     const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp, const int32_t pad[4],
-                                     const int32_t stride[2], const int32_t dilation[2], const tb200_epilogue* epilogue,
-                                     tb200_tensor* output)
+// One phase of a TRANSPOSE_CONV2D writes its [N][OH][OW] pixel grid into a strided subset of the output tensor:
+// pixel (oy, ox) lands at (oy * sy + y0, ox * sx + x0).  Only the tensor-core kernel takes such a view; conv2d_impl
+// answers kNeedsDenseOutput (before launching anything) when the problem would go to another kernel.
+struct ConvOutView
+{
+    int OH, OW, sy, sx, y0, x0;
+};
+static const tb200_status kNeedsDenseOutput = (tb200_status)-77;
+
+static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
+                                const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp, const int32_t pad[4],
+                                const int32_t stride[2], const int32_t dilation[2], const tb200_epilogue* epilogue,
+                                tb200_tensor* output, const ConvOutView* view, bool dry_run)
 {
     if (!ctx)
         return TB200_ERROR;
@@ -699,7 +710,7 @@ extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, 
                    "OpConv2d: input, weight and output must be rank 4 and bias rank 1");
     const int N = input->shape[0], IH = input->shape[1], IW = input->shape[2], IC = input->shape[3];
     const int OC = weight->shape[0], KH = weight->shape[1], KW = weight->shape[2];
-    const int OH = output->shape[1], OW = output->shape[2];
+    const int OH = view ? view->OH : output->shape[1], OW = view ? view->OW : output->shape[2];
     tb200_status st = check_conv_attr(ctx, "OpConv2d", IH, IW, OH, OW, KH, KW, pad, stride, dilation);
     if (st != TB200_OK)
         return st;
@@ -750,12 +761,19 @@ extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, 
         q.dil_y = dilation[0]; q.dil_x = dilation[1];
         q.b   = weight->data;
         q.out = output->data;
+        if (view)
+        {
+            q.out_OH = output->shape[1]; q.out_OW = output->shape[2];
+            q.out_sy = view->sy; q.out_sx = view->sx; q.out_y0 = view->y0; q.out_x0 = view->x0;
+        }
         q.epi = int_path ? TC_EPI_I32 : TC_EPI_FLOAT;
         fill_tc_epilogue(&q, epi, output->dtype);
         std::string why;
         if (tc_gemm_supported(q, &why))
         {
             const int OCpad = (OC + 255) / 256 * 256;
+            if (dry_run && !int_path)
+                return TB200_OK;
             if (int_path)
             {
                 const bool padded  = pad[0] || pad[1] || pad[2] || pad[3];
@@ -767,6 +785,8 @@ extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, 
                 const size_t bytes        = (prefix_elems + corr_elems + OCpad) * sizeof(int32_t) + OCpad + 64;
                 if (bytes <= ((size_t)64 << 20))
                 {
+                    if (dry_run)
+                        return TB200_OK;
                     st = ensure_scratch(ctx, bytes);
                     if (st != TB200_OK)
                         return st;
@@ -812,6 +832,9 @@ extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, 
             }
         }
     }
+
+    if (view || dry_run)
+        return kNeedsDenseOutput;
 
     // ---- few-channel int8 convolutions (IC <= 8, e.g. the RGB stem): window re-layout + tensor cores
     if (ctx->policy == 0 && int_path && weight_zp == 0 && tc_rescale_ok && input->contiguous && IC <= 8 &&
@@ -924,6 +947,288 @@ extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, 
             reinterpret_cast<const float*>(input->data), reinterpret_cast<const float*>(weight->data),
             reinterpret_cast<const float*>(bias->data), reinterpret_cast<float*>(output->data), d);
     return post_launch(ctx, "conv2d_direct");
+}
+
+extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
+                                     const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp, const int32_t pad[4],
+                                     const int32_t stride[2], const int32_t dilation[2], const tb200_epilogue* epilogue,
+                                     tb200_tensor* output)
+{
+    return conv2d_impl(ctx, input, weight, bias, input_zp, weight_zp, pad, stride, dilation, epilogue, output, nullptr,
+                       false);
+}
+
+// =================================================================================================== TRANSPOSE_CONV2D
+// Staging that must outlive a nested tb200_conv2d call (which owns ctx->scratch).
+static tb200_status ensure_stage(tb200_ctx* ctx, size_t bytes)
+{
+    if (bytes <= ctx->stage_bytes)
+        return TB200_OK;
+    if (ctx->capturing)
+        return fail(ctx, TB200_ERROR, "staging memory would have to grow during capture; evaluate once eagerly first");
+    TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->stage)
+        TB200_CUDA_CHECK(ctx, cudaFree(ctx->stage));
+    ctx->stage       = nullptr;
+    ctx->stage_bytes = 0;
+    TB200_CUDA_CHECK(ctx, cudaMalloc(&ctx->stage, bytes));
+    ctx->stage_bytes = bytes;
+    return TB200_OK;
+}
+
+template <typename U>
+static void launch_spread(tb200_ctx* ctx, const void* in, void* out, int N, int IH, int IW, int units, int DH, int DW, int sy,
+                          int sx, U fill)
+{
+    const int block = 256;
+    spread_pixels_kernel<U><<<grid_for(ctx, (int64_t)N * DH * DW * units, block), block, 0, ctx->stream>>>(
+        reinterpret_cast<const U*>(in), reinterpret_cast<U*>(out), N, IH, IW, units, DH, DW, sy, sx, fill);
+}
+
+template <typename U>
+static void launch_mirror_u(tb200_ctx* ctx, const void* in, void* out, int OC, int KH, int KW, int units, int ky0, int sy,
+                            int Ty, int kx0, int sx, int Tx)
+{
+    const int block = 256;
+    mirror_weights_kernel<U><<<grid_for(ctx, (int64_t)OC * Ty * Tx * units, block), block, 0, ctx->stream>>>(
+        reinterpret_cast<const U*>(in), reinterpret_cast<U*>(out), OC, KH, KW, units, ky0, sy, Ty, kx0, sx, Tx);
+}
+
+// run = bytes of one pixel's channel run; 16-byte units when the run and both pointers allow it
+static void launch_mirror(tb200_ctx* ctx, const void* in, void* out, int OC, int KH, int KW, int IC, size_t es, bool vec,
+                          int ky0, int sy, int Ty, int kx0, int sx, int Tx)
+{
+    if (vec)
+        launch_mirror_u<uint4>(ctx, in, out, OC, KH, KW, (int)(IC * es / 16), ky0, sy, Ty, kx0, sx, Tx);
+    else if (es == 1)
+        launch_mirror_u<uint8_t>(ctx, in, out, OC, KH, KW, IC, ky0, sy, Ty, kx0, sx, Tx);
+    else if (es == 2)
+        launch_mirror_u<uint16_t>(ctx, in, out, OC, KH, KW, IC, ky0, sy, Ty, kx0, sx, Tx);
+    else
+        launch_mirror_u<uint32_t>(ctx, in, out, OC, KH, KW, IC, ky0, sy, Ty, kx0, sx, Tx);
+}
+
+// One axis of one phase of a strided TRANSPOSE_CONV2D.  Output positions o = p + s*j (j < J) only see the taps
+// k = k0 + s*t (t < T) with k0 = (p - out_pad) mod s, and read input index j + c - t with c = (p - out_pad - k0) / s
+// (OpTransposeConv2d::eval, reference_model/src/ops/tensor_ops.cpp:2148-2171, solved for the taps whose division is
+// exact).  With the taps mirrored this is a stride-1 convolution over input rows [start, start + len) with pads
+// (pad0, pad1).  T == 0: no tap reaches this phase (its outputs are the bias alone).
+struct PhaseAxis
+{
+    int J, k0, T, start, len, pad0, pad1;
+};
+
+static PhaseAxis plan_phase_axis(int I, int K, int O, int s, int out_pad0, int p)
+{
+    PhaseAxis a = {};
+    a.J         = O > p ? (O - p + s - 1) / s : 0;
+    a.k0        = ((p - out_pad0) % s + s) % s;
+    a.T         = K > a.k0 ? (K - a.k0 + s - 1) / s : 0;
+    if (a.J == 0 || a.T == 0)
+        return a;
+    const int c = (p - out_pad0 - a.k0) / s;    // exact by the choice of k0
+    a.pad0      = (a.T - 1) - c;
+    if (a.pad0 < 0)
+    {
+        a.start = -a.pad0;
+        a.pad0  = 0;
+    }
+    a.len  = I - a.start;
+    a.pad1 = a.J - a.len - a.pad0 + a.T - 1;
+    if (a.pad1 < 0)
+    {
+        a.len += a.pad1;
+        a.pad1 = 0;
+    }
+    if (a.len <= 0)
+        a.T = 0;
+    return a;
+}
+
+extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
+                                               const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp,
+                                               const int32_t out_pad[4], const int32_t stride[2],
+                                               const tb200_epilogue* epilogue, tb200_tensor* output)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ERROR_IF(ctx, !input || !weight || !bias || !output || !out_pad || !stride, "OpTransposeConv2d: null operand");
+    TB200_ERROR_IF(ctx, !all_contiguous({ input, weight, bias, output }), "OpTransposeConv2d: operands must be contiguous");
+    // OpTransposeConv2d::checkTensorAttributes (reference_model/src/ops/tensor_ops.cpp:1982-2056)
+    TB200_ERROR_IF(ctx, input->rank != 4 || weight->rank != 4 || output->rank != 4 || bias->rank != 1,
+                   "OpTransposeConv2d: input, weight and output must be rank 4 and bias rank 1");
+    TB200_ERROR_IF(ctx, stride[0] < 1 || stride[1] < 1, "OpTransposeConv2d: At least one stride is smaller than one");
+    const int N = input->shape[0], IH = input->shape[1], IW = input->shape[2], IC = input->shape[3];
+    const int OC = weight->shape[0], KH = weight->shape[1], KW = weight->shape[2];
+    const int OH = output->shape[1], OW = output->shape[2];
+    for (int i = 0; i < 4; i++)
+        TB200_ERROR_IF(ctx, out_pad[i] <= -weight->shape[i / 2 + 1],
+                       "OpTransposeConv2d: At least one out_pad value is larger than kernel size");
+    const int64_t H = (int64_t)(IH - 1) * stride[0] + out_pad[0] + out_pad[1] + KH;
+    const int64_t W = (int64_t)(IW - 1) * stride[1] + out_pad[2] + out_pad[3] + KW;
+    TB200_ERROR_IF(ctx, OH != H || OW != W,
+                   "OpTransposeConv2d: Mismatch between output shape provided and expected output shape (%lld,%lld)",
+                   (long long)H, (long long)W);
+    // OpTransposeConv2d::eval ERROR_IFs (:2085-2091, :2116-2122)
+    TB200_ERROR_IF(ctx, N != output->shape[0], "OpTransposeConv2d: tensor batch mismatch %d != %d", N, output->shape[0]);
+    TB200_ERROR_IF(ctx, weight->shape[3] != IC, "OpTransposeConv2d: tensor input channel mismatch %d != %d",
+                   weight->shape[3], IC);
+    TB200_ERROR_IF(ctx, OC != output->shape[3], "OpTransposeConv2d: tensor output channel mismatch %d != %d", OC,
+                   output->shape[3]);
+    TB200_ERROR_IF(ctx, bias->shape[0] != OC && bias->shape[0] != 1, "OpTransposeConv2d: bias channels mismatch %d != %d",
+                   bias->shape[0], OC);
+    TB200_ERROR_IF(ctx, weight->dtype != input->dtype, "OpTransposeConv2d: input and weight dtypes differ");
+    if (input->dtype != TB200_INT8)
+    {
+        TB200_ERROR_IF(ctx, !dtype_is_float(input->dtype), "OpTransposeConv2d: unsupported input dtype %d", (int)input->dtype);
+        TB200_ERROR_IF(ctx, input_zp != 0, "Input zero point must be zero for non int8_t data");
+        TB200_ERROR_IF(ctx, weight_zp != 0, "Weight zero point must be zero for non int8_t data");
+    }
+    TB200_ERROR_IF(ctx, input_zp < -128 || input_zp > 127 || weight_zp < -128 || weight_zp > 127,
+                   "OpTransposeConv2d: zero point outside the int8 range");
+    if (numel(output) == 0 || numel(input) == 0)
+        TB200_ERROR_IF(ctx, numel(output) != 0, "OpTransposeConv2d: empty input with a non-empty output");
+    if (numel(output) == 0)
+        return TB200_OK;
+
+    const size_t es  = dtype_size(input->dtype);
+    const size_t run = (size_t)IC * es;    // bytes of one pixel's channel run
+    const bool vec   = (run % 16) == 0 && (reinterpret_cast<uintptr_t>(input->data) % 16) == 0 &&
+                     (reinterpret_cast<uintptr_t>(weight->data) % 16) == 0;
+    const int32_t one[2] = { 1, 1 };
+    const int sy = stride[0], sx = stride[1];
+    tb200_status st;
+
+    // ---- strided: one stride-1 convolution per output phase, each over the original input with the taps that reach
+    // the phase, written straight into its pixels of the output.  Needs the tensor-core kernel for every phase.
+    if ((sy > 1 || sx > 1) && sy * sx <= 64)
+    {
+        struct Phase
+        {
+            PhaseAxis y, x;
+            int py, px;
+            size_t w_off;
+        };
+        std::vector<Phase> phases;
+        size_t w_total = 0;
+        bool ok        = true;
+        for (int py = 0; py < sy && ok; py++)
+            for (int px = 0; px < sx && ok; px++)
+            {
+                Phase ph = { plan_phase_axis(IH, KH, OH, sy, out_pad[0], py), plan_phase_axis(IW, KW, OW, sx, out_pad[2], px),
+                             py, px, w_total };
+                if (ph.y.J == 0 || ph.x.J == 0)
+                    continue;    // no output pixel in this phase
+                if (ph.y.T == 0 || ph.x.T == 0)
+                    ok = false;    // bias-only pixels: left to the dense form below
+                w_total += ((size_t)OC * ph.y.T * ph.x.T * run + 255) & ~(size_t)255;
+                phases.push_back(ph);
+            }
+        auto run_phase = [&](const Phase& ph, void* wbuf, bool dry) {
+            tb200_tensor xin = *input, wsub = *weight;
+            xin.owns = wsub.owns = false;
+            xin.data       = reinterpret_cast<uint8_t*>(input->data) + ((size_t)ph.y.start * IW + ph.x.start) * run;
+            xin.shape[1]   = ph.y.len;
+            xin.shape[2]   = ph.x.len;
+            xin.contiguous = false;
+            wsub.data      = wbuf;
+            wsub.shape[1]  = ph.y.T;
+            wsub.shape[2]  = ph.x.T;
+            wsub.bytes     = (size_t)OC * ph.y.T * ph.x.T * run;
+            wsub.stride[2] = IC;
+            wsub.stride[1] = (int64_t)ph.x.T * IC;
+            wsub.stride[0] = (int64_t)ph.y.T * ph.x.T * IC;
+            const int32_t pad[4]   = { ph.y.pad0, ph.y.pad1, ph.x.pad0, ph.x.pad1 };
+            const ConvOutView view = { ph.y.J, ph.x.J, sy, sx, ph.py, ph.px };
+            return conv2d_impl(ctx, &xin, &wsub, bias, input_zp, weight_zp, pad, one, one, epilogue, output, &view, dry);
+        };
+        if (ok && !phases.empty())
+        {
+            // the probe only looks at shapes and alignment; any 256-byte aligned address stands in for the weights
+            for (const Phase& ph : phases)
+            {
+                st = run_phase(ph, weight->data, true);
+                if (st == kNeedsDenseOutput)
+                {
+                    ok = false;
+                    break;
+                }
+                if (st != TB200_OK)
+                    return st;
+            }
+        }
+        if (ok && !phases.empty())
+        {
+            st = ensure_stage(ctx, w_total);
+            if (st != TB200_OK)
+                return st;
+            uint8_t* wbase = reinterpret_cast<uint8_t*>(ctx->stage);
+            for (const Phase& ph : phases)
+                launch_mirror(ctx, weight->data, wbase + ph.w_off, OC, KH, KW, IC, es, vec, ph.y.k0, sy, ph.y.T, ph.x.k0, sx,
+                              ph.x.T);
+            st = post_launch(ctx, "transpose_conv_phase_weights", (int)phases.size());
+            if (st != TB200_OK)
+                return st;
+            for (const Phase& ph : phases)
+            {
+                st = run_phase(ph, wbase + ph.w_off, false);
+                if (st != TB200_OK)
+                    return st == kNeedsDenseOutput ? fail(ctx, TB200_INTERNAL, "OpTransposeConv2d: phase plan changed") : st;
+            }
+            return TB200_OK;
+        }
+    }
+
+    // ---- dense form: a stride-1 CONV2D over the input spread out by the stride, with the whole kernel mirrored
+    const bool spread = sy > 1 || sx > 1;
+    const int DH = (IH - 1) * sy + 1, DW = (IW - 1) * sx + 1;
+    const size_t w_bytes = ((size_t)OC * KH * KW * run + 255) & ~(size_t)255;
+    const size_t d_bytes = spread ? (size_t)N * DH * DW * run : 0;
+    st                   = ensure_stage(ctx, w_bytes + d_bytes + 256);
+    if (st != TB200_OK)
+        return st;
+    uint8_t* wm = reinterpret_cast<uint8_t*>(ctx->stage);
+    uint8_t* dx = wm + w_bytes;
+    int launches = 1;
+    launch_mirror(ctx, weight->data, wm, OC, KH, KW, IC, es, vec, 0, 1, KH, 0, 1, KW);
+    if (spread)
+    {
+        launches = 2;
+        // floating types have zero point 0, whose bit pattern is 0 in every format
+        const uint32_t b  = (uint32_t)(uint8_t)(int8_t)input_zp;
+        const uint32_t b4 = es == 1 ? b * 0x01010101u : 0u;
+        if (vec)
+            launch_spread<uint4>(ctx, input->data, dx, N, IH, IW, (int)(run / 16), DH, DW, sy, sx, make_uint4(b4, b4, b4, b4));
+        else if (es == 1)
+            launch_spread<uint8_t>(ctx, input->data, dx, N, IH, IW, IC, DH, DW, sy, sx, (uint8_t)b);
+        else if (es == 2)
+            launch_spread<uint16_t>(ctx, input->data, dx, N, IH, IW, IC, DH, DW, sy, sx, (uint16_t)0);
+        else
+            launch_spread<uint32_t>(ctx, input->data, dx, N, IH, IW, IC, DH, DW, sy, sx, 0u);
+    }
+    st = post_launch(ctx, "transpose_conv_staging", launches);
+    if (st != TB200_OK)
+        return st;
+
+    tb200_tensor din = *input, wmir = *weight;
+    din.owns = wmir.owns = false;
+    wmir.data            = wm;
+    if (spread)
+    {
+        din.data      = dx;
+        din.shape[1]  = DH;
+        din.shape[2]  = DW;
+        din.bytes     = d_bytes;
+        din.stride[3] = 1;
+        din.stride[2] = IC;
+        din.stride[1] = (int64_t)DW * IC;
+        din.stride[0] = (int64_t)DH * DW * IC;
+    }
+    const int32_t pad[4] = { KH - 1 + out_pad[0], KH - 1 + out_pad[1], KW - 1 + out_pad[2], KW - 1 + out_pad[3] };
+    st = tb200_conv2d(ctx, &din, &wmir, bias, input_zp, weight_zp, pad, one, one, epilogue, output);
+    if (st != TB200_OK && ctx->err.compare(0, 8, "OpConv2d") == 0)
+        ctx->err = "OpTransposeConv2d (as CONV2D): " + ctx->err;
+    return st;
 }
 
 // =================================================================================================== DEPTHWISE

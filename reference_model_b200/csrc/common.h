@@ -50,6 +50,8 @@ struct tb200_ctx
     uint32_t* pair_flags = nullptr;    // flags of the CTA-pair MATMUL's in-kernel zero-point sums, zeroed when allocated
     size_t pair_flag_words = 0;
     uint32_t pair_epoch  = 0;          // bumped per launch; a flag equal to it means "written in this launch"
+    void* stage          = nullptr;    // grow-on-demand staging of TRANSPOSE_CONV2D (spread input, mirrored weights)
+    size_t stage_bytes   = 0;
     void* join_table     = nullptr;    // 64 KiB result table + 8 KiB REQUIRE bits of the per-tensor residual join
     uint64_t launches    = 0;
     int policy           = 0;
@@ -171,6 +173,9 @@ struct TcProblem
     int epi;
     tb200_dtype out_dtype;
     void* out;
+    // out_sy != 0: the output pixel grid is a strided view of a dense [N][out_OH][out_OW][OC] tensor, pixel (oy, ox)
+    // landing at (oy * out_sy + out_y0, ox * out_sx + out_x0) (one phase of a TRANSPOSE_CONV2D); 0: dense [N][OH][OW]
+    int out_OH, out_OW, out_sy, out_sx, out_y0, out_x0;
     const int32_t* row_corr;    // [N*OH*OW] added to every column of a row, or null
     // MATMUL on the CTA-pair kernel: derive the row term from A inside the kernel instead (row_corr null):
     // row term = -b_zp * sum_k A[row, k] + IC * a_zp * b_zp

@@ -1270,6 +1270,54 @@ __global__ void conv_epilogue_tables_kernel(const int8_t* __restrict__ w, const 
     }
 }
 
+// TRANSPOSE_CONV2D as a convolution: the input is spread out with (stride - 1) fill pixels between neighbours
+// (fill = the input zero point, which the convolution subtracts to 0) and the kernel is mirrored in both spatial
+// axes; a stride-1 CONV2D over that pair gives OpTransposeConv2d::eval's sums term by term
+// (reference_model/src/ops/tensor_ops.cpp:2148-2171: tap (ky, kx) of output y reads input (y - out_pad - ky) / stride
+// when that division is exact).  U is the copy unit: 16 bytes when a pixel's channel run allows it, else one element.
+template <typename U>
+__global__ void spread_pixels_kernel(const U* __restrict__ in, U* __restrict__ out, int N, int IH, int IW, int units,
+                                     int DH, int DW, int sy, int sx, U fill)
+{
+    const int64_t total = (int64_t)N * DH * DW * units;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int u  = (int)(i % units);
+        int64_t r    = i / units;
+        const int dx = (int)(r % DW);
+        r /= DW;
+        const int dy = (int)(r % DH);
+        const int n  = (int)(r / DH);
+        U v          = fill;
+        if ((dy % sy) == 0 && (dx % sx) == 0)
+            v = in[(((int64_t)n * IH + dy / sy) * IW + dx / sx) * units + u];
+        out[i] = v;
+    }
+}
+
+// OHWI weights, every (sy, sx)-th tap starting at (ky0, kx0), mirrored:
+// out[oc][ty][tx][:] = in[oc][ky0 + sy*(Ty-1-ty)][kx0 + sx*(Tx-1-tx)][:].  (0, 1, KH, 0, 1, KW) mirrors the whole kernel;
+// a phase of a strided TRANSPOSE_CONV2D uses the taps congruent to its offset.
+template <typename U>
+__global__ void mirror_weights_kernel(const U* __restrict__ in, U* __restrict__ out, int OC, int KH, int KW, int units,
+                                      int ky0, int sy, int Ty, int kx0, int sx, int Tx)
+{
+    const int64_t total = (int64_t)OC * Ty * Tx * units;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int u  = (int)(i % units);
+        int64_t r    = i / units;
+        const int tx = (int)(r % Tx);
+        r /= Tx;
+        const int ty = (int)(r % Ty);
+        const int oc = (int)(r / Ty);
+        const int ky = ky0 + sy * (Ty - 1 - ty), kx = kx0 + sx * (Tx - 1 - tx);
+        out[i]       = in[(((int64_t)oc * KH + ky) * KW + kx) * units + u];
+    }
+}
+
 // Few-channel convolutions (an RGB stem) on the tensor cores.  The image is copied once into a border-padded,
 // channel-padded buffer  xp[N][Hp][Wp][Cp]  (border and slack filled with the input zero point, pad channels with
 // anything: their weights are zero).  With Cp * stride_x a multiple of 16 bytes, the KW taps of one filter row are

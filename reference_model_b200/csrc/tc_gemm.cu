@@ -68,6 +68,7 @@ struct TcKernelParams
     int corr_stride;               // padded column count (multiple of the tile width)
     int corr_ystride;              // MATMUL: elements to advance per batch; 0 otherwise
     int corr_classes;              // 1: rows select a table row by their rectangle of in-scope filter taps
+    int out_OH, out_OW, out_sy, out_sx, out_y0, out_x0;    // output pixel (oy, ox) -> (oy*out_sy + out_y0, ox*out_sx + out_x0)
     const float* bias_f_pad;       // TC_EPI_FLOAT: padded fp32 bias or null
     const int32_t* mult_pad;       // TC_EPI_RESCALE: padded per-column multipliers and shifts
     const int8_t* shift_pad;
@@ -482,7 +483,8 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
 
             const int ox = t.x0 + xx, oy = t.y0 + yy, on = t.n0 + nn;
             const bool row_valid = (nn < p.BN) && (ox < p.OW) && (oy < p.OH) && (on < p.N);
-            const int64_t pix    = ((int64_t)on * p.OH + oy) * p.OW + ox;
+            // index of this row's pixel in the output tensor (a dense grid, or one phase of a strided one)
+            const int64_t pix = ((int64_t)on * p.out_OH + oy * p.out_sy + p.out_y0) * p.out_OW + ox * p.out_sx + p.out_x0;
             // the neighbouring lane's row (lane ^ 1), for stores that fill whole 32-byte sectors between two lanes
             const int64_t pix_pair     = __shfl_xor_sync(0xffffffffu, pix, 1);
             const bool row_valid_pair  = __shfl_xor_sync(0xffffffffu, (int)row_valid, 1) != 0;
@@ -506,9 +508,9 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         if (ix0 < 0)
                             kx_lo = (-ix0 + p.dil_x - 1) / p.dil_x;
                         if (iy0 + (p.KH - 1) * p.dil_y >= p.IH)
-                            ky_hi = (p.IH - 1 - iy0) / p.dil_y + 1;
+                            ky_hi = iy0 >= p.IH ? 0 : (p.IH - 1 - iy0) / p.dil_y + 1;
                         if (ix0 + (p.KW - 1) * p.dil_x >= p.IW)
-                            kx_hi = (p.IW - 1 - ix0) / p.dil_x + 1;
+                            kx_hi = ix0 >= p.IW ? 0 : (p.IW - 1 - ix0) / p.dil_x + 1;
                         ky_lo = min(ky_lo, p.KH);
                         kx_lo = min(kx_lo, p.KW);
                         ky_hi = max(ky_hi, ky_lo);
@@ -521,7 +523,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             }
             int32_t rc = 0;
             if (EPI == TC_EPI_I32 && p.row_corr != nullptr && row_valid)
-                rc = p.row_corr[pix];
+                rc = p.row_corr[((int64_t)on * p.OH + oy) * p.OW + ox];
 
             const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n);
             const int ncol_chunks = p.block_n / 32;
@@ -961,7 +963,7 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     const int64_t sn = q.a_stride_n ? q.a_stride_n : sh * q.IH;
     const bool dense = sw == q.IC && sh == sw * q.IW && sn == sh * q.IH;
     const bool pure_gemm = q.KH == 1 && q.KW == 1 && q.stride_y == 1 && q.stride_x == 1 && q.pad_t == 0 &&
-                           q.pad_l == 0 && OH == IH && OW == IW && !q.b_mn_major && dense;
+                           q.pad_l == 0 && OH == IH && OW == IW && !q.b_mn_major && dense && q.out_sy == 0;
     if (pure_gemm)
     {
         int64_t pixels = (int64_t)N * IH * IW;
@@ -1007,6 +1009,12 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     k.OC = q.OC;
     k.IH = IH;
     k.IW = IW;
+    k.out_OH = q.out_sy ? q.out_OH : OH;
+    k.out_OW = q.out_sy ? q.out_OW : OW;
+    k.out_sy = q.out_sy ? q.out_sy : 1;
+    k.out_sx = q.out_sy ? q.out_sx : 1;
+    k.out_y0 = q.out_sy ? q.out_y0 : 0;
+    k.out_x0 = q.out_sy ? q.out_x0 : 0;
     k.tiles_x = (OW + BW - 1) / BW;
     k.tiles_y = (OH + BH - 1) / BH;
     k.tiles_n = (N + BN - 1) / BN;

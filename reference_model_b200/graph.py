@@ -62,6 +62,10 @@ class Graph:
                 oc, kh, kw, ic = self.meta[op.inputs[1]][1]
                 n, oh, ow, _ = self.meta[op.outputs[0]][1]
                 total += n * oh * ow * oc * kh * kw * ic
+            elif op.kind == "TRANSPOSE_CONV2D":    # every input pixel stamps the whole kernel
+                oc, kh, kw, ic = self.meta[op.inputs[1]][1]
+                n, ih, iw, _ = self.meta[op.inputs[0]][1]
+                total += n * ih * iw * oc * kh * kw * ic
             elif op.kind == "MATMUL":
                 n, h, c = self.meta[op.inputs[0]][1]
                 total += n * h * c * self.meta[op.inputs[1]][1][2]
@@ -193,7 +197,7 @@ def fuse(graph):
     for i, op in enumerate(ops):
         if id(op) in skip:
             continue
-        if op.kind == "CONV2D" and single(op.outputs[0]):
+        if op.kind in ("CONV2D", "TRANSPOSE_CONV2D") and single(op.outputs[0]):
             r = cons[op.outputs[0]][0]
             if r.kind == "RESCALE" and r.attr["scale32"] and r.attr["rounding"] != "INEXACT_ROUND":
                 c = cons[r.outputs[0]][0] if single(r.outputs[0]) else None
@@ -279,8 +283,12 @@ class DeviceRunner:
                 epi = tb.Epilogue(self._rescale_attr(r), (c.attr["min_val"], c.attr["max_val"]) if c else None)
                 out = (c or r).outputs[0]
                 a = conv.attr
-                ctx.conv2d(t[conv.inputs[0]], t[conv.inputs[1]], t[conv.inputs[2]], t[out], a["pad"], a["stride"],
-                           a["dilation"], a["input_zp"], a["weight_zp"], epi)
+                if conv.kind == "TRANSPOSE_CONV2D":
+                    ctx.transpose_conv2d(t[conv.inputs[0]], t[conv.inputs[1]], t[conv.inputs[2]], t[out], a["out_pad"],
+                                         a["stride"], a["input_zp"], a["weight_zp"], epi)
+                else:
+                    ctx.conv2d(t[conv.inputs[0]], t[conv.inputs[1]], t[conv.inputs[2]], t[out], a["pad"], a["stride"],
+                               a["dilation"], a["input_zp"], a["weight_zp"], epi)
             elif kind == "RESIDUAL_JOIN":
                 ra, rb, add, ro, c = p
                 out = (c or ro).outputs[0]
@@ -291,6 +299,10 @@ class DeviceRunner:
                 a = p.attr
                 ctx.conv2d(t[p.inputs[0]], t[p.inputs[1]], t[p.inputs[2]], t[p.outputs[0]], a["pad"], a["stride"],
                            a["dilation"], a["input_zp"], a["weight_zp"])
+            elif kind == "TRANSPOSE_CONV2D":
+                a = p.attr
+                ctx.transpose_conv2d(t[p.inputs[0]], t[p.inputs[1]], t[p.inputs[2]], t[p.outputs[0]], a["out_pad"],
+                                     a["stride"], a["input_zp"], a["weight_zp"])
             elif kind == "RESCALE":
                 ctx.rescale(t[p.inputs[0]], self._rescale_attr(p), t[p.outputs[0]])
             elif kind == "CLAMP":

@@ -92,6 +92,26 @@ def conv_i8_config(ctx, timer, name, N, IH, IW, IC, OC, KH, KW, stride, pad, izp
             "algorithmic_ops": ops, "algorithmic_bytes": nbytes, "l2": note}
 
 
+def tconv_i8_config(ctx, timer, name, N, IH, IW, IC, OC, K, stride, out_pad, izp, iters, seed):
+    """int8 TRANSPOSE_CONV2D + RESCALE + CLAMP.  Algorithmic work: every input pixel stamps the whole kernel."""
+    r = np.random.default_rng(seed)
+    x = r.integers(-128, 128, size=(N, IH, IW, IC), dtype=np.int8)
+    w = r.integers(-127, 128, size=(OC, K, K, IC), dtype=np.int8)
+    b = r.integers(-65536, 65536, size=OC).astype(np.int32)
+    OH = (IH - 1) * stride + 2 * out_pad + K
+    OW = (IW - 1) * stride + 2 * out_pad + K
+    tx, tw, tbias = ctx.from_numpy(x), ctx.from_numpy(w), ctx.from_numpy(b)
+    tm, ts = rescale_consts(ctx, r, OC)
+    to = ctx.empty(tb.DType.INT8, (N, OH, OW, OC))
+    epi = tb.Epilogue(tb.RescaleAttr(tm, ts, 0, -128, True, "DOUBLE_ROUND", per_channel=True), (-128, 127))
+    fn = lambda: ctx.transpose_conv2d(tx, tw, tbias, to, [out_pad] * 4, [stride, stride], izp, 0, epi)
+    nbytes = x.nbytes + w.nbytes + N * OH * OW * OC
+    ms, note = timer.time(fn, iters, nbytes)
+    ops = 2.0 * N * IH * IW * OC * K * K * IC
+    return {"config": name, "kernel": ctx.last_kernel(), "ms": ms, "TOPS": ops / ms / 1e9, "GBps": nbytes / ms / 1e6,
+            "algorithmic_ops": ops, "algorithmic_bytes": nbytes, "l2": note}
+
+
 def graph_profile(batch):
     """Per-step times of one eager evaluation of the benchmark graph (each step bracketed by a device sync, so the sum
     exceeds the replayed graph's time; the shares are what this is for)."""
@@ -129,6 +149,8 @@ def main():
     ap.add_argument("--conv", default=None,
                     help="also time one int8 CONV2D+RESCALE+CLAMP layer: N,IH,IW,IC,OC,K,stride,pad (one pad for all four sides, "
                          "or four values top,bottom,left,right)")
+    ap.add_argument("--tconv", default=None,
+                    help="also time one int8 TRANSPOSE_CONV2D+RESCALE+CLAMP layer: N,IH,IW,IC,OC,K,stride,out_pad")
     ap.add_argument("--join", default=None,
                     help="also time one fused int8 residual join (RESCALE x2, ADD, RESCALE, CLAMP): N,H,W,C")
     ap.add_argument("--graph-profile", type=int, default=0, metavar="BATCH",
@@ -154,6 +176,11 @@ def main():
             res = conv_i8_config(ctx, timer, "conv %s" % args.conv, n, ih, iw, ic, oc, k, k, st, pads, -128,
                                  args.iters, 9)
             print(json.dumps(res))
+            sys.stdout.flush()
+        if args.tconv:
+            n, ih, iw, ic, oc, k, st, op = [int(v) for v in args.tconv.split(",")]
+            print(json.dumps(tconv_i8_config(ctx, timer, "tconv %s" % args.tconv, n, ih, iw, ic, oc, k, st, op, -128,
+                                             args.iters, 11)))
             sys.stdout.flush()
         if args.join:
             shape = tuple(int(v) for v in args.join.split(","))

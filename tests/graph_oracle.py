@@ -16,6 +16,9 @@ def evaluate(graph, inputs, nthreads=8):
         if op.kind == "CONV2D":
             out = orc.conv2d(t[op.inputs[0]], t[op.inputs[1]], t[op.inputs[2]], a["pad"], a["stride"], a["dilation"],
                              a["input_zp"], a["weight_zp"], nthreads=nthreads)
+        elif op.kind == "TRANSPOSE_CONV2D":
+            out = orc.transpose_conv2d(t[op.inputs[0]], t[op.inputs[1]], t[op.inputs[2]], a["out_pad"], a["stride"],
+                                       a["input_zp"], a["weight_zp"], nthreads=nthreads)
         elif op.kind == "RESCALE":
             in_dt, out_dt = graph.meta[op.inputs[0]][0].name, graph.meta[op.outputs[0]][0].name
             st, out = orc.rescale(t[op.inputs[0]], t[op.inputs[1]], t[op.inputs[2]], a["per_channel"], a["scale32"],

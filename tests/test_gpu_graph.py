@@ -48,3 +48,69 @@ def test_resnet50_graph_matches_oracle():
                 ctx.graph_destroy(run.captured)
     finally:
         ctx.close()
+
+
+def _decoder_graph(batch=2, seed=77):
+    """CONV2D 3x3 s2 (encoder) -> TRANSPOSE_CONV2D 4x4 s2 (decoder, cropped by out_pad -1) -> TRANSPOSE_CONV2D 2x2 s2,
+    each followed by RESCALE + CLAMP; the last accumulator is also a graph output, so that chain must stay unfused."""
+    r = np.random.default_rng(seed)
+    g = G.Graph()
+
+    def consts(tag, oc, k, ic):
+        w = g.const(tag + "_w", r.integers(-127, 127, size=(oc, k, k, ic), endpoint=True).astype(np.int8))
+        b = g.const(tag + "_b", r.integers(-(1 << 14), 1 << 14, size=oc, endpoint=True).astype(np.int32))
+        m = g.const(tag + "_m", r.integers(1 << 30, (1 << 31) - 1, size=oc, endpoint=True).astype(np.int32))
+        s = g.const(tag + "_s", r.integers(36, 42, size=oc, endpoint=True).astype(np.int8))
+        return w, b, m, s
+
+    def requant(acc, m, s, tag, shape):
+        q = g.tensor(tag + "_q", tb.DType.INT8, shape)
+        y = g.tensor(tag + "_y", tb.DType.INT8, shape)
+        g.add("RESCALE", [acc, m, s], [q], input_zp=0, output_zp=-128, scale32=True, rounding="DOUBLE_ROUND",
+              per_channel=True)
+        g.add("CLAMP", [q], [y], min_val=-128, max_val=127)
+        return y
+
+    x = g.tensor("input", tb.DType.INT8, (batch, 17, 17, 32))
+    g.inputs.append(x)
+    w, b, m, s = consts("enc", 64, 3, 32)
+    acc = g.tensor("enc_acc", tb.DType.INT32, (batch, 8, 8, 64))
+    g.add("CONV2D", [x, w, b], [acc], pad=[0, 0, 0, 0], stride=[2, 2], dilation=[1, 1], input_zp=-128, weight_zp=0)
+    y = requant(acc, m, s, "enc", (batch, 8, 8, 64))
+    w, b, m, s = consts("up1", 32, 4, 64)
+    acc = g.tensor("up1_acc", tb.DType.INT32, (batch, 16, 16, 32))      # (8-1)*2 - 1 - 1 + 4
+    g.add("TRANSPOSE_CONV2D", [y, w, b], [acc], out_pad=[-1, -1, -1, -1], stride=[2, 2], input_zp=-128, weight_zp=0)
+    y = requant(acc, m, s, "up1", (batch, 16, 16, 32))
+    w, b, m, s = consts("up2", 16, 2, 32)
+    acc = g.tensor("up2_acc", tb.DType.INT32, (batch, 32, 32, 16))      # (16-1)*2 + 2
+    g.add("TRANSPOSE_CONV2D", [y, w, b], [acc], out_pad=[0, 0, 0, 0], stride=[2, 2], input_zp=-128, weight_zp=0)
+    y = requant(acc, m, s, "up2", (batch, 32, 32, 16))
+    g.outputs += [y, acc]
+    return g
+
+
+def test_decoder_graph_with_transpose_convolutions_matches_oracle():
+    g = _decoder_graph()
+    kinds = [k for k, _ in G.fuse(g)]
+    assert kinds == ["CONV_RESCALE_CLAMP", "CONV_RESCALE_CLAMP", "TRANSPOSE_CONV2D", "RESCALE", "CLAMP"]
+    x = np.random.default_rng(5).integers(-128, 127, size=g.meta["input"][1], endpoint=True).astype(np.int8)
+    est, ref = graph_oracle.evaluate(g, {"input": x}, nthreads=8)
+    assert est == 0
+    ctx = tb.Context(0)
+    try:
+        for fused in (True, False):
+            run = G.DeviceRunner(ctx, g, fused=fused)
+            run.set_input(x)
+            run.run()
+            for name in g.outputs + ["up1_y"]:
+                st, out = run.output(name)
+                assert st == tb.Status.OK and np.array_equal(out.astype(np.int32), ref[name]), (fused, name)
+        run.capture()
+        x2 = x[::-1].copy()
+        run.set_input(x2)
+        run.run()
+        st, out2 = run.output(g.outputs[0])
+        assert st == tb.Status.OK and np.array_equal(out2[::-1].astype(np.int32), ref[g.outputs[0]])
+        ctx.graph_destroy(run.captured)
+    finally:
+        ctx.close()

@@ -676,6 +676,128 @@ def test_depthwise_float(ctx, dt, name):
 
 
 # ------------------------------------------------------------------------------------------- elementwise
+# ------------------------------------------------------------------------------------------- TRANSPOSE_CONV2D
+TCONV_I8_CASES = [
+    # N, IH, IW, IC, OC, KH, KW, stride, out_pad, input_zp, weight_zp
+    (2, 14, 14, 64, 128, 2, 2, (2, 2), (0, 0, 0, 0), -128, 0),     # 2x upsampling, no overlap
+    (1, 16, 12, 32, 48, 4, 4, (2, 2), (-1, -1, -1, -1), 7, 0),     # overlapping stamps, cropped border
+    (2, 9, 11, 64, 256, 3, 3, (1, 1), (0, 1, 2, 0), -5, 0),        # stride 1: only the kernel is mirrored
+    (1, 7, 5, 32, 32, 3, 2, (3, 2), (1, 0, 0, 2), 0, 0),           # rows of the output that no stamp reaches
+    (1, 6, 6, 32, 40, 1, 2, (2, 3), (0, 0, 0, 0), 9, 0),           # kernel smaller than the stride: bias-only phases
+    (3, 5, 9, 96, 24, 5, 3, (2, 2), (-4, 3, -2, -2), -77, 0),      # deep crop on one side, extension on the other
+    (1, 7, 5, 16, 32, 3, 2, (3, 2), (1, 0, 0, 2), 0, 0),           # 16-byte channel run: CUDA cores
+    (1, 5, 6, 7, 3, 3, 2, (2, 3), (0, 1, -1, 0), -5, 3),           # odd channels + weight zero point: CUDA cores
+]
+
+
+@pytest.mark.parametrize("case", TCONV_I8_CASES)
+def test_transpose_conv_int8(ctx, case):
+    N, IH, IW, IC, OC, KH, KW, stride, out_pad, izp, wzp = case
+    r = util.rng(900 + IH * IC + OC)
+    x, w, b = util.conv_int8_case(r, N, IH, IW, IC, OC, KH, KW)
+    OH, OW = orc.transpose_conv_out_hw(IH, IW, KH, KW, out_pad, stride)
+    ref = orc.transpose_conv2d(x, w, b, out_pad, stride, izp, wzp, nthreads=8)
+    tx, tw, tbias = ctx.from_numpy(x), ctx.from_numpy(w), ctx.from_numpy(b)
+    to = ctx.empty(I32, (N, OH, OW, OC))
+    ctx.transpose_conv2d(tx, tw, tbias, to, out_pad, stride, izp, wzp)
+    kernel = ctx.last_kernel()
+    st, out = to.download()
+    assert st == tb.Status.OK and np.array_equal(out, ref), kernel
+    if IC % 32 == 0 and wzp == 0:
+        assert kernel.startswith("tc_gemm"), kernel
+    # fused RESCALE + CLAMP, as the graph fuser would hand it over
+    mult, shift = util.rescale_params(r, OC)
+    shift = (shift + 4).astype(np.int8)
+    st_ref, ref8 = orc.rescale(ref, mult, shift, per_channel=True, scale32=True, rounding="DOUBLE_ROUND", input_zp=0,
+                               output_zp=-3, in_bits=32, out_bits=8)
+    _, ref8 = orc.clamp(ref8, -100, 90)
+    tm, ts = ctx.from_numpy(mult), ctx.from_numpy(shift)
+    epi = tb.Epilogue(tb.RescaleAttr(tm, ts, 0, -3, True, "DOUBLE_ROUND", per_channel=True), (-100, 90))
+    to8 = ctx.empty(I8, (N, OH, OW, OC))
+    ctx.transpose_conv2d(tx, tw, tbias, to8, out_pad, stride, izp, wzp, epi)
+    st, out8 = to8.download()
+    if st_ref == orc.VALID:
+        assert st == tb.Status.OK and np.array_equal(out8, ref8), ctx.last_kernel()
+    else:
+        assert st == tb.Status.UNPREDICTABLE
+    _free(tx, tw, tbias, to, to8, tm, ts)
+
+
+def test_transpose_conv_int8_random_shapes(ctx):
+    """Seeded random kernel sizes, strides and out_pads (crops and extensions) on the tensor-core path."""
+    r = util.rng(977)
+    done = 0
+    while done < 24:
+        N, IH, IW = int(r.integers(1, 4)), int(r.integers(1, 12)), int(r.integers(1, 12))
+        IC, OC = int(r.choice([32, 64, 160])), int(r.integers(1, 80))
+        KH, KW = int(r.integers(1, 6)), int(r.integers(1, 6))
+        stride = (int(r.integers(1, 4)), int(r.integers(1, 4)))
+        out_pad = [int(r.integers(-KH + 1, 4)), int(r.integers(-KH + 1, 4)), int(r.integers(-KW + 1, 4)),
+                   int(r.integers(-KW + 1, 4))]
+        OH, OW = orc.transpose_conv_out_hw(IH, IW, KH, KW, out_pad, stride)
+        if OH <= 0 or OW <= 0:
+            continue
+        done += 1
+        izp = int(r.integers(-128, 128))
+        x, w, b = util.conv_int8_case(r, N, IH, IW, IC, OC, KH, KW)
+        ref = orc.transpose_conv2d(x, w, b, out_pad, stride, izp, 0, nthreads=8)
+        tx, tw, tbias = ctx.from_numpy(x), ctx.from_numpy(w), ctx.from_numpy(b)
+        to = ctx.empty(I32, (N, OH, OW, OC))
+        ctx.transpose_conv2d(tx, tw, tbias, to, out_pad, stride, izp, 0)
+        st, out = to.download()
+        assert st == tb.Status.OK and np.array_equal(out, ref), (N, IH, IW, IC, OC, KH, KW, stride, out_pad, ctx.last_kernel())
+        assert ctx.last_kernel().startswith("tc_gemm")
+        _free(tx, tw, tbias, to)
+
+
+@pytest.mark.parametrize("dt,name", [(F16, "fp16"), (BF16, "bf16"), (F32, "fp32")])
+@pytest.mark.parametrize("case", [(2, 10, 10, 32, 64, 3, 3, (2, 2), (0, -1, -1, 0)), (1, 6, 7, 5, 9, 2, 3, (1, 2), (1, 0, 0, 0))])
+def test_transpose_conv_float(ctx, dt, name, case):
+    N, IH, IW, IC, OC, KH, KW, stride, out_pad = case
+    r = util.rng(950 + IC)
+    x = orc.fptrunc(r.standard_normal((N, IH, IW, IC)).astype(np.float32), name)
+    w = orc.fptrunc((r.standard_normal((OC, KH, KW, IC)) / np.sqrt(KH * KW * IC)).astype(np.float32), name)
+    b = orc.fptrunc((0.1 * r.standard_normal(OC)).astype(np.float32), name)
+    ref = orc.transpose_conv2d(x, w, b, out_pad, stride, mode="f64")
+    bnd = orc.transpose_conv2d(np.abs(x), np.abs(w), np.abs(b), out_pad, stride, mode="f64")
+    ksb = orc.dot_product_ksb(KH * KW * IC + 1, "fp32", name)
+    OH, OW = orc.transpose_conv_out_hw(IH, IW, KH, KW, out_pad, stride)
+
+    def up(a):
+        if dt == F32:
+            return ctx.from_numpy(a.astype(np.float32))
+        if dt == F16:
+            return ctx.from_numpy(a.astype(np.float16))
+        return ctx.from_numpy(util.to_bf16_bits(a), BF16)
+
+    tx, tw, tbias = up(x), up(w), up(b)
+    to = ctx.empty(dt, (N, OH, OW, OC))
+    ctx.transpose_conv2d(tx, tw, tbias, to, out_pad, stride)
+    st, out = to.download()
+    out = util.from_bf16_bits(out) if dt == BF16 else out
+    ok, info = orc.verify_dot_product(out.astype(np.float32), ref, bnd, ksb, out=name)
+    assert ok, (ctx.last_kernel(), info)
+    _free(tx, tw, tbias, to)
+
+
+def test_transpose_conv_error_ifs(ctx):
+    x, w, b = util.conv_int8_case(util.rng(3), 1, 4, 4, 16, 16, 3, 3)
+    tx, tw, tbias = ctx.from_numpy(x), ctx.from_numpy(w), ctx.from_numpy(b)
+    good = ctx.empty(I32, (1, 9, 9, 16))
+    assert ctx.transpose_conv2d(tx, tw, tbias, good, [0, 0, 0, 0], [2, 2]) == tb.Status.OK
+    # tensor_ops.cpp:2021-2054: stride >= 1, out_pad > -kernel, output size
+    assert ctx.transpose_conv2d(tx, tw, tbias, good, [0, 0, 0, 0], [0, 2], check=False) == tb.Status.ERROR
+    assert ctx.transpose_conv2d(tx, tw, tbias, good, [-3, 3, 0, 0], [2, 2], check=False) == tb.Status.ERROR
+    assert ctx.transpose_conv2d(tx, tw, tbias, good, [0, 1, 0, 0], [2, 2], check=False) == tb.Status.ERROR
+    assert "expected output shape (10,9)" in ctx.last_error()
+    # :2085-2091 channel and bias mismatches
+    tb3 = ctx.from_numpy(np.zeros(3, np.int32))
+    assert ctx.transpose_conv2d(tx, tw, tb3, good, [0, 0, 0, 0], [2, 2], check=False) == tb.Status.ERROR
+    tw5 = ctx.from_numpy(np.zeros((16, 3, 3, 5), np.int8))
+    assert ctx.transpose_conv2d(tx, tw5, tbias, good, [0, 0, 0, 0], [2, 2], check=False) == tb.Status.ERROR
+    _free(tx, tw, tbias, good, tb3, tw5)
+
+
 def test_rescale_standalone_sweep(ctx):
     r = util.rng(6)
     for shape in ((4, 7, 9, 64), (3, 1000), (5, 3), (17,)):

@@ -227,3 +227,63 @@ def test_precise_and_bounds_modes_and_verifier():
     assert not ok
     # multi-threaded split must not change a single bit
     assert np.array_equal(orc.conv2d(x, w, b, *args, mode="f32", nthreads=4), normal)
+
+
+# --------------------------------------------------------------------------------------------- TRANSPOSE_CONV2D
+def _spread_and_mirror(x, w, out_pad, stride, fill):
+    """The CONV2D that equals a TRANSPOSE_CONV2D: input spread by the stride, kernel mirrored, pads K-1+out_pad."""
+    N, IH, IW, IC = x.shape
+    _, KH, KW, _ = w.shape
+    d = np.full((N, (IH - 1) * stride[0] + 1, (IW - 1) * stride[1] + 1, IC), fill, x.dtype)
+    d[:, ::stride[0], ::stride[1], :] = x
+    pad = [KH - 1 + out_pad[0], KH - 1 + out_pad[1], KW - 1 + out_pad[2], KW - 1 + out_pad[3]]
+    return d, np.ascontiguousarray(w[:, ::-1, ::-1, :]), pad
+
+
+def test_transpose_conv2d_hand_case():
+    # one row [1, 2], kernel [3, 4], stride 2: every input pixel stamps the kernel, no overlap
+    x = np.array([1, 2], np.int8).reshape(1, 1, 2, 1)
+    w = np.array([3, 4], np.int8).reshape(1, 1, 2, 1)
+    out = orc.transpose_conv2d(x, w, np.array([10], np.int32), [0, 0, 0, 0], [1, 2])
+    assert out.reshape(-1).tolist() == [13, 14, 16, 18]
+    # stride 1: the stamps overlap and add; out_pad_left = -1 drops the first column, out_pad_right = 1 adds an empty one
+    out = orc.transpose_conv2d(x, w, np.array([0], np.int32), [0, 0, 0, 0], [1, 1])
+    assert out.reshape(-1).tolist() == [3, 4 + 6, 8]
+    out = orc.transpose_conv2d(x, w, np.array([0], np.int32), [0, 0, -1, 1], [1, 1])
+    assert out.reshape(-1).tolist() == [10, 8, 0]
+    # zero points are subtracted from both operands (tensor_ops.cpp:2163-2168)
+    out = orc.transpose_conv2d(x, w, np.array([0], np.int32), [0, 0, 0, 0], [1, 2], in_zp=1, w_zp=-1)
+    assert out.reshape(-1).tolist() == [0, 0, 4, 5]
+
+
+@pytest.mark.parametrize("shape,out_pad,stride", [
+    ((2, 5, 6, 7, 3, 3, 2), (0, 1, -1, 0), (2, 3)),
+    ((1, 4, 4, 3, 5, 2, 4), (-1, -1, 2, 1), (1, 1)),
+    ((1, 3, 3, 2, 2, 3, 3), (1, 0, 0, 2), (3, 2)),
+    ((1, 6, 5, 4, 4, 4, 4), (-3, -3, -3, -3), (2, 2)),
+])
+def test_transpose_conv2d_equals_conv2d_of_spread_input(shape, out_pad, stride):
+    N, IH, IW, IC, OC, KH, KW = shape
+    rng = np.random.default_rng(IH * 100 + KW)
+    x = rng.integers(-128, 128, (N, IH, IW, IC)).astype(np.int8)
+    w = rng.integers(-128, 128, (OC, KH, KW, IC)).astype(np.int8)
+    b = rng.integers(-1000, 1000, OC).astype(np.int32)
+    got = orc.transpose_conv2d(x, w, b, out_pad, stride, -5, 3)
+    assert got.shape[1:3] == orc.transpose_conv_out_hw(IH, IW, KH, KW, out_pad, stride)
+    d, wm, pad = _spread_and_mirror(x, w, out_pad, stride, -5)
+    assert np.array_equal(got, orc.conv2d(d, wm, b, pad, [1, 1], [1, 1], -5, 3))
+    assert np.array_equal(got, orc.transpose_conv2d(x, w, b, out_pad, stride, -5, 3, nthreads=4))
+    # precise mode: same sums in doubles, up to the order of the taps
+    xf, wf, bf = x.astype(np.float64) / 64, w.astype(np.float64) / 64, b.astype(np.float64) / 64
+    d, wm, pad = _spread_and_mirror(xf, wf, out_pad, stride, 0.0)
+    assert np.allclose(orc.transpose_conv2d(xf, wf, bf, out_pad, stride, mode="f64"),
+                       orc.conv2d(d, wm, bf, pad, [1, 1], [1, 1], mode="f64"), rtol=0, atol=1e-9)
+
+
+def test_transpose_conv2d_attribute_rules():
+    # tensor_ops.cpp:2038-2054: out_pad > -kernel, output size (I-1)*stride + out_pad + K
+    assert orc.check_transpose_conv2d_attribute(4, 4, 9, 9, 3, 3, [0, 0, 0, 0], [2, 2]) == 0
+    assert orc.check_transpose_conv2d_attribute(4, 4, 9, 9, 3, 3, [0, 0, 0, 0], [0, 2]) != 0
+    assert orc.check_transpose_conv2d_attribute(4, 4, 6, 9, 3, 3, [-3, 0, 0, 0], [2, 2]) != 0
+    assert orc.check_transpose_conv2d_attribute(4, 4, 7, 9, 3, 3, [-2, 0, 0, 0], [2, 2]) == 0
+    assert orc.check_transpose_conv2d_attribute(4, 4, 10, 9, 3, 3, [0, 0, 0, 0], [2, 2]) != 0
