@@ -135,6 +135,22 @@ extern "C"
     TB200_API void* tb200_tensor_data(const tb200_tensor* t);
     TB200_API size_t tb200_tensor_bytes(const tb200_tensor* t);
 
+    /* ---- NumPy files ----------------------------------------------------------------------------
+     * Replace Tensor::readFromNpyFile / Tensor::writeToNpyFile (reference_model/src/tensor.cpp:96-421, :423-640).
+     * Loading accepts the file types the reference's tools produce for a tensor of `dtype`: an int32 file for every
+     * integer tensor (:164-171; narrowed on the device, a value outside the tensor type's range is TB200_ERROR), the
+     * tensor's own width (what writeToNpyFile emits for INT8 / INT16 results, :574-600), float16 for FP16, float32
+     * for FP32, and 2-byte raw words or float32 (rounded to nearest even) for BF16.  Row-major files only.
+     * Saving writes format 1.0 with the tensor's own element type.  The payload moves through one pinned 64 MiB
+     * host buffer; no widened copy of the tensor is made on either side.
+     * tb200_npy_probe reads only the header (no context, no GPU): descr such as "<i4", rank, shape, payload offset;
+     * `err` receives the reason when it returns TB200_ERROR. */
+    TB200_API tb200_status tb200_npy_probe(const char* path, char descr[8], int32_t* rank, int32_t shape[6],
+                                           uint64_t* data_offset, char* err, size_t err_len);
+    TB200_API tb200_status tb200_tensor_load_npy(tb200_ctx* ctx, const char* path, tb200_dtype dtype,
+                                                 tb200_tensor** out);
+    TB200_API tb200_status tb200_tensor_save_npy(tb200_ctx* ctx, const tb200_tensor* t, const char* path);
+
     /* ---- fused epilogue ------------------------------------------------------------------------
      * Lets the host collapse CONV2D/MATMUL -> RESCALE -> CLAMP chains whose intermediates have a single
      * consumer (reference_model/src/tensor.h:92-100).  NULL means the plain op. */

@@ -15,4 +15,5 @@ from .binding import (  # noqa: F401
     Tensor,
     lib_path,
     load_library,
+    npy_probe,
 )

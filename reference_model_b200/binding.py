@@ -72,6 +72,7 @@ EXPORTS = [
     "tb200_tensor_data", "tb200_tensor_bytes", "tb200_tensor_slice", "tb200_tensor_reshape", "tb200_conv2d", "tb200_depthwise_conv2d", "tb200_transpose_conv2d", "tb200_matmul",
     "tb200_rescale", "tb200_clamp", "tb200_add", "tb200_residual_add", "tb200_max_pool2d", "tb200_avg_pool2d",
     "tb200_matmul_host", "tb200_set_kernel_policy", "tb200_last_kernel", "tb200_matmul_i8_noalloc",
+    "tb200_npy_probe", "tb200_tensor_load_npy", "tb200_tensor_save_npy",
 ]
 
 
@@ -121,6 +122,10 @@ def load_library():
         "tb200_matmul_host": (i32, [vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
         "tb200_matmul_i8_noalloc": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, ctypes.c_char_p,
                                           ctypes.c_size_t]),
+        "tb200_npy_probe": (i32, [cp, ctypes.c_char_p, p_i32, p_i32, ctypes.POINTER(ctypes.c_uint64), ctypes.c_char_p,
+                            ctypes.c_size_t]),
+        "tb200_tensor_load_npy": (i32, [vp, cp, i32, ctypes.POINTER(vp)]),
+        "tb200_tensor_save_npy": (i32, [vp, vp, cp]),
         "tb200_set_kernel_policy": (ctypes.c_int, [vp, ctypes.c_int]),
         "tb200_last_kernel": (cp, [vp]),
     }
@@ -130,6 +135,17 @@ def load_library():
         fn.argtypes = args
     _LIB = lib
     return lib
+
+
+def npy_probe(path):
+    """Header of a .npy file, read by the library's own parser (no GPU needed): (descr, shape, payload offset).
+    Raises ValueError with the parser's reason for a file it does not accept."""
+    descr, err = ctypes.create_string_buffer(8), ctypes.create_string_buffer(512)
+    rank, shape, off = ctypes.c_int32(0), (ctypes.c_int32 * 6)(), ctypes.c_uint64(0)
+    st = load_library().tb200_npy_probe(os.fsencode(path), descr, ctypes.byref(rank), shape, ctypes.byref(off), err, 512)
+    if st != 0:
+        raise ValueError(err.value.decode())
+    return descr.value.decode(), tuple(shape[i] for i in range(rank.value)), int(off.value)
 
 
 def _ivec(v):
@@ -209,6 +225,10 @@ class Tensor:
         st = load_library().tb200_tensor_download(self.ctx.handle, self.handle, out.ctypes.data_as(ctypes.c_void_p),
                                                   out.nbytes)
         return self.ctx._check(st, check), out
+
+    def save_npy(self, path, check=True):
+        """Writes the tensor as a .npy file of its own element type (Tensor::writeToNpyFile)."""
+        return self.ctx._check(load_library().tb200_tensor_save_npy(self.ctx.handle, self.handle, os.fsencode(path)), check)
 
     def slice(self, start, size):
         """SLICE as a zero-copy view (keeps this tensor alive)."""
@@ -320,6 +340,14 @@ class Context:
         t = self.empty(dtype, arr.shape)
         t.upload(arr)
         return t
+
+    def load_npy(self, path, dtype):
+        """Reads a .npy file into a new device tensor of `dtype` (Tensor::readFromNpyFile): int32 files are accepted
+        for every integer tensor and narrowed on the device."""
+        _, shape, _ = npy_probe(path)
+        h = ctypes.c_void_p()
+        self._check(self.lib.tb200_tensor_load_npy(self.handle, os.fsencode(path), int(dtype), ctypes.byref(h)))
+        return Tensor(self, dtype, shape, h)
 
     # ---- operators (same argument meaning as the reference's nodes)
     def conv2d(self, x, w, bias, out, pad, stride, dilation, input_zp=0, weight_zp=0, epilogue=None, check=True):

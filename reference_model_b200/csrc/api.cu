@@ -345,6 +345,8 @@ extern "C" tb200_status tb200_ctx_destroy(tb200_ctx* ctx)
         cudaFree(ctx->scratch);
     if (ctx->stage)
         cudaFree(ctx->stage);
+    if (ctx->io_pinned)
+        cudaFreeHost(ctx->io_pinned);
     if (ctx->join_table)
         cudaFree(ctx->join_table);
     if (ctx->pair_flags)
@@ -693,6 +695,9 @@ extern "C" tb200_status tb200_tensor_reshape(tb200_ctx* ctx, const tb200_tensor*
 struct ConvOutView
 {
     int OH, OW, sy, sx, y0, x0;
+    // d2s_oc != 0: the weight rows are (ky, kx, oc) blocks of d2s_oc channels and block (ky, kx) of pixel (oy, ox)
+    // lands at (oy * sy + ky, ox * sx + kx); d2s_kw is the stamp's width
+    int d2s_oc, d2s_kw;
 };
 static const tb200_status kNeedsDenseOutput = (tb200_status)-77;
 
@@ -717,7 +722,8 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
     // OpConv2d::eval ERROR_IFs (:742-748)
     TB200_ERROR_IF(ctx, N != output->shape[0], "OpConv2d: tensor batch mismatch %d != %d", N, output->shape[0]);
     TB200_ERROR_IF(ctx, weight->shape[3] != IC, "OpConv2d: tensor input channel mismatch %d != %d", weight->shape[3], IC);
-    TB200_ERROR_IF(ctx, OC != output->shape[3], "OpConv2d: tensor output channel mismatch %d != %d", OC, output->shape[3]);
+    TB200_ERROR_IF(ctx, OC != output->shape[3] && !(view && view->d2s_oc), "OpConv2d: tensor output channel mismatch %d != %d",
+                   OC, output->shape[3]);
     TB200_ERROR_IF(ctx, bias->shape[0] != OC && bias->shape[0] != 1, "OpConv2d: bias channel mismatch %d != %d",
                    bias->shape[0], OC);
     const bool int_path = input->dtype == TB200_INT8;
@@ -765,6 +771,7 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
         {
             q.out_OH = output->shape[1]; q.out_OW = output->shape[2];
             q.out_sy = view->sy; q.out_sx = view->sx; q.out_y0 = view->y0; q.out_x0 = view->x0;
+            q.d2s_oc = view->d2s_oc; q.d2s_kw = view->d2s_kw;
         }
         q.epi = int_path ? TC_EPI_I32 : TC_EPI_FLOAT;
         fill_tc_epilogue(&q, epi, output->dtype);
@@ -1099,6 +1106,91 @@ extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tenso
     const int sy = stride[0], sx = stride[1];
     tb200_status st;
 
+    // ---- kernel == stride, no out_pad: the stamps tile the output without overlap, so the operator is one GEMM over the
+    // input pixels with (ky, kx, oc) columns, each block of OC columns stored at its own output pixel.
+    if ((sy > 1 || sx > 1) && KH == sy && KW == sx && !out_pad[0] && !out_pad[1] && !out_pad[2] && !out_pad[3] &&
+        OC % 32 == 0 && (int64_t)KH * KW * OC <= 65536)
+    {
+        const int KK = KH * KW, cols = KK * OC;
+        const bool rs        = epilogue && epilogue->has_rescale && epilogue->rescale.multiplier && epilogue->rescale.shift;
+        const bool rs_per_ch = rs && epilogue->rescale.per_channel && epilogue->rescale.multiplier->shape[0] == OC &&
+                               epilogue->rescale.shift->shape[0] == OC;
+        const size_t bias_es = dtype_size(bias->dtype);
+        const size_t mult_es = rs_per_ch ? dtype_size(epilogue->rescale.multiplier->dtype) : 0;
+        auto up256           = [](size_t v) { return (v + 255) & ~(size_t)255; };
+        const size_t w_off = 0, b_off = up256((size_t)cols * run), m_off = b_off + up256((size_t)cols * bias_es),
+                     s_off = m_off + up256((size_t)cols * mult_es), total = s_off + up256((size_t)cols);
+        tb200_tensor wst = *weight, bst = *bias, mst = {}, sst = {};
+        wst.owns = bst.owns = false;
+        wst.shape[0] = cols; wst.shape[1] = 1; wst.shape[2] = 1;
+        wst.stride[0] = IC; wst.stride[1] = IC; wst.stride[2] = IC;
+        if (bias->shape[0] == OC)
+        {
+            bst.shape[0] = cols;
+            bst.bytes    = (size_t)cols * bias_es;
+        }
+        tb200_epilogue epi2;
+        if (epilogue)
+            epi2 = *epilogue;
+        if (rs_per_ch)
+        {
+            mst = *epilogue->rescale.multiplier;
+            sst = *epilogue->rescale.shift;
+            mst.owns = sst.owns = false;
+            mst.shape[0] = sst.shape[0] = cols;
+            mst.bytes                   = (size_t)cols * mult_es;
+            sst.bytes                   = (size_t)cols;
+            epi2.rescale.multiplier     = &mst;
+            epi2.rescale.shift          = &sst;
+        }
+        const int32_t zero[4]  = { 0, 0, 0, 0 };
+        const ConvOutView view = { IH, IW, sy, sx, 0, 0, OC, KW };
+        // the probe only looks at shapes and alignment: the unstaged operands stand in
+        st = conv2d_impl(ctx, input, &wst, &bst, input_zp, weight_zp, zero, one, one, epilogue ? &epi2 : nullptr, output,
+                         &view, true);
+        if (st == TB200_OK)
+        {
+            st = ensure_stage(ctx, total);
+            if (st != TB200_OK)
+                return st;
+            uint8_t* base = reinterpret_cast<uint8_t*>(ctx->stage);
+            const int block  = 256;
+            const bool rep_b = bias->shape[0] == OC;
+            const void* b_in = rep_b ? bias->data : nullptr;
+            const void* m_in = rs_per_ch ? epilogue->rescale.multiplier->data : nullptr;
+            const uint8_t* s_in = rs_per_ch ? reinterpret_cast<const uint8_t*>(epilogue->rescale.shift->data) : nullptr;
+            if (vec)
+                stamp_operands_kernel<uint4><<<grid_for(ctx, (int64_t)cols * (run / 16), block), block, 0, ctx->stream>>>(
+                    reinterpret_cast<const uint4*>(weight->data), reinterpret_cast<uint4*>(base + w_off), OC, KK,
+                    (int)(run / 16), b_in, base + b_off, (int)bias_es, m_in, base + m_off, (int)mult_es, s_in, base + s_off);
+            else if (es == 1)
+                stamp_operands_kernel<uint8_t><<<grid_for(ctx, (int64_t)cols * IC, block), block, 0, ctx->stream>>>(
+                    reinterpret_cast<const uint8_t*>(weight->data), base + w_off, OC, KK, IC, b_in, base + b_off, (int)bias_es,
+                    m_in, base + m_off, (int)mult_es, s_in, base + s_off);
+            else
+                stamp_operands_kernel<uint16_t><<<grid_for(ctx, (int64_t)cols * IC, block), block, 0, ctx->stream>>>(
+                    reinterpret_cast<const uint16_t*>(weight->data), reinterpret_cast<uint16_t*>(base + w_off), OC, KK, IC, b_in,
+                    base + b_off, (int)bias_es, m_in, base + m_off, (int)mult_es, s_in, base + s_off);
+            wst.data = base + w_off;
+            if (rep_b)
+                bst.data = base + b_off;
+            if (rs_per_ch)
+            {
+                mst.data = base + m_off;
+                sst.data = base + s_off;
+            }
+            const int launches = 1;
+            st = post_launch(ctx, "transpose_conv_stamp_operands", launches);
+            if (st != TB200_OK)
+                return st;
+            st = conv2d_impl(ctx, input, &wst, &bst, input_zp, weight_zp, zero, one, one, epilogue ? &epi2 : nullptr, output,
+                             &view, false);
+            return st == kNeedsDenseOutput ? fail(ctx, TB200_INTERNAL, "OpTransposeConv2d: stamp plan changed") : st;
+        }
+        if (st != kNeedsDenseOutput)
+            return st;
+    }
+
     // ---- strided: one stride-1 convolution per output phase, each over the original input with the taps that reach
     // the phase, written straight into its pixels of the output.  Needs the tensor-core kernel for every phase.
     if ((sy > 1 || sx > 1) && sy * sx <= 64)
@@ -1139,7 +1231,7 @@ extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tenso
             wsub.stride[1] = (int64_t)ph.x.T * IC;
             wsub.stride[0] = (int64_t)ph.y.T * ph.x.T * IC;
             const int32_t pad[4]   = { ph.y.pad0, ph.y.pad1, ph.x.pad0, ph.x.pad1 };
-            const ConvOutView view = { ph.y.J, ph.x.J, sy, sx, ph.py, ph.px };
+            const ConvOutView view = { ph.y.J, ph.x.J, sy, sx, ph.py, ph.px, 0, 0 };
             return conv2d_impl(ctx, &xin, &wsub, bias, input_zp, weight_zp, pad, one, one, epilogue, output, &view, dry);
         };
         if (ok && !phases.empty())

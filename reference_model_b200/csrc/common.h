@@ -52,6 +52,7 @@ struct tb200_ctx
     uint32_t pair_epoch  = 0;          // bumped per launch; a flag equal to it means "written in this launch"
     void* stage          = nullptr;    // grow-on-demand staging of TRANSPOSE_CONV2D (spread input, mirrored weights)
     size_t stage_bytes   = 0;
+    void* io_pinned      = nullptr;    // 64 MiB pinned host buffer of the .npy loader / writer, allocated on first use
     void* join_table     = nullptr;    // 64 KiB result table + 8 KiB REQUIRE bits of the per-tensor residual join
     uint64_t launches    = 0;
     int policy           = 0;
@@ -176,6 +177,10 @@ struct TcProblem
     // out_sy != 0: the output pixel grid is a strided view of a dense [N][out_OH][out_OW][OC] tensor, pixel (oy, ox)
     // landing at (oy * out_sy + out_y0, ox * out_sx + out_x0) (one phase of a TRANSPOSE_CONV2D); 0: dense [N][OH][OW]
     int out_OH, out_OW, out_sy, out_sx, out_y0, out_x0;
+    // d2s_oc != 0 (with out_sy != 0): the OC columns are (ky, kx, oc) blocks of d2s_oc channels; block (ky, kx) of
+    // pixel (oy, ox) is output pixel (oy * out_sy + ky, ox * out_sx + kx) of a [N][out_OH][out_OW][d2s_oc] tensor
+    // (a TRANSPOSE_CONV2D whose kernel equals its stride: one GEMM, stamps do not overlap); d2s_kw = kernel width
+    int d2s_oc, d2s_kw;
     const int32_t* row_corr;    // [N*OH*OW] added to every column of a row, or null
     // MATMUL on the CTA-pair kernel: derive the row term from A inside the kernel instead (row_corr null):
     // row term = -b_zp * sum_k A[row, k] + IC * a_zp * b_zp

@@ -1318,6 +1318,47 @@ __global__ void mirror_weights_kernel(const U* __restrict__ in, U* __restrict__ 
     }
 }
 
+// TRANSPOSE_CONV2D with kernel == stride and no out_pad: stamps do not overlap, so the operator is one GEMM whose
+// columns are (ky, kx, oc).  One launch prepares its operands: weights OHWI -> rows ((ky*KW + kx)*OC + oc) of IC
+// channels each, and the per-channel vectors (bias, RESCALE multiplier and shift; null = absent) repeated for every
+// (ky, kx) block of columns.  Vector elements are copied as raw 1-, 2- or 4-byte words.
+template <typename U>
+__global__ void stamp_operands_kernel(const U* __restrict__ w, U* __restrict__ w_out, int OC, int KK, int units,
+                                      const void* __restrict__ bias, void* __restrict__ bias_out, int bias_es,
+                                      const void* __restrict__ mult, void* __restrict__ mult_out, int mult_es,
+                                      const uint8_t* __restrict__ shift, uint8_t* __restrict__ shift_out)
+{
+    const int64_t total = (int64_t)OC * KK * units;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (int64_t i = first; i < total; i += step)
+    {
+        const int u  = (int)(i % units);
+        int64_t r    = i / units;
+        const int oc = (int)(r % OC);
+        const int kk = (int)(r / OC);
+        w_out[i]     = w[((int64_t)oc * KK + kk) * units + u];
+    }
+    auto copy_word = [](const void* src, void* dst, int es, int from, int to) {
+        if (es == 4)
+            reinterpret_cast<uint32_t*>(dst)[to] = reinterpret_cast<const uint32_t*>(src)[from];
+        else if (es == 2)
+            reinterpret_cast<uint16_t*>(dst)[to] = reinterpret_cast<const uint16_t*>(src)[from];
+        else
+            reinterpret_cast<uint8_t*>(dst)[to] = reinterpret_cast<const uint8_t*>(src)[from];
+    };
+    for (int64_t c = first; c < (int64_t)OC * KK; c += step)
+    {
+        const int oc = (int)(c % OC);
+        if (bias != nullptr)
+            copy_word(bias, bias_out, bias_es, oc, (int)c);
+        if (mult != nullptr)
+            copy_word(mult, mult_out, mult_es, oc, (int)c);
+        if (shift != nullptr)
+            shift_out[c] = shift[oc];
+    }
+}
+
 // Few-channel convolutions (an RGB stem) on the tensor cores.  The image is copied once into a border-padded,
 // channel-padded buffer  xp[N][Hp][Wp][Cp]  (border and slack filled with the input zero point, pad channels with
 // anything: their weights are zero).  With Cp * stride_x a multiple of 16 bytes, the KW taps of one filter row are

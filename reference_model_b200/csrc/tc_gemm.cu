@@ -69,6 +69,7 @@ struct TcKernelParams
     int corr_ystride;              // MATMUL: elements to advance per batch; 0 otherwise
     int corr_classes;              // 1: rows select a table row by their rectangle of in-scope filter taps
     int out_OH, out_OW, out_sy, out_sx, out_y0, out_x0;    // output pixel (oy, ox) -> (oy*out_sy + out_y0, ox*out_sx + out_x0)
+    int d2s_oc, d2s_kw;    // != 0: column c is channel c % d2s_oc of the pixel (c / d2s_oc / d2s_kw, c / d2s_oc % d2s_kw) further on
     const float* bias_f_pad;       // TC_EPI_FLOAT: padded fp32 bias or null
     const int32_t* mult_pad;       // TC_EPI_RESCALE: padded per-column multipliers and shifts
     const int8_t* shift_pad;
@@ -536,6 +537,16 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                 if (col >= p.OC || (p.debug & 1))
                     continue;
                 const int nvalid = min(32, p.OC - col);
+                // element offset of (this row, col) in the output, and of the neighbouring lane's row
+                int64_t ooff = pix * p.OC + col, ooff_pair = pix_pair * p.OC + col;
+                if (p.d2s_oc != 0)
+                {
+                    // columns are (ky, kx, oc): a block of d2s_oc channels per output pixel of the stamp
+                    const int ph = col / p.d2s_oc, ky = ph / p.d2s_kw, kx = ph - ky * p.d2s_kw;
+                    const int64_t within = ((int64_t)ky * p.out_OW + kx) * p.d2s_oc + (col - ph * p.d2s_oc);
+                    ooff      = pix * p.d2s_oc + within;
+                    ooff_pair = pix_pair * p.d2s_oc + within;
+                }
 
                 if (EPI != TC_EPI_FLOAT && corr_row != nullptr && !(p.debug & 16))
                 {
@@ -559,7 +570,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         v[i] += (uint32_t)rc;
                     if (row_valid)
                     {
-                        int32_t* o = reinterpret_cast<int32_t*>(p.out) + pix * p.OC + col;
+                        int32_t* o = reinterpret_cast<int32_t*>(p.out) + ooff;
                         if (nvalid == 32 && ((p.OC & 7) == 0) && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0)
                         {
 #pragma unroll
@@ -647,7 +658,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         if ((reinterpret_cast<uintptr_t>(p.out) & 31) == 0)
                         {
                             if (row_valid && !skip)
-                                ptx::st_global_v8(reinterpret_cast<int8_t*>(p.out) + pix * p.OC + col, w[0], w[1], w[2], w[3],
+                                ptx::st_global_v8(reinterpret_cast<int8_t*>(p.out) + ooff, w[0], w[1], w[2], w[3],
                                                   w[4], w[5], w[6], w[7]);
                         }
                         else
@@ -657,8 +668,8 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
 #pragma unroll
                             for (int k = 0; k < 4; k++)
                                 other[k] = __shfl_xor_sync(0xffffffffu, odd ? w[k] : w[4 + k], 1);
-                            int8_t* o_own  = reinterpret_cast<int8_t*>(p.out) + pix * p.OC + col + (odd ? 16 : 0);
-                            int8_t* o_pair = reinterpret_cast<int8_t*>(p.out) + pix_pair * p.OC + col + (odd ? 16 : 0);
+                            int8_t* o_own  = reinterpret_cast<int8_t*>(p.out) + ooff + (odd ? 16 : 0);
+                            int8_t* o_pair = reinterpret_cast<int8_t*>(p.out) + ooff_pair + (odd ? 16 : 0);
                             const uint4 mine   = odd ? make_uint4(w[4], w[5], w[6], w[7]) : make_uint4(w[0], w[1], w[2], w[3]);
                             const uint4 theirs = make_uint4(other[0], other[1], other[2], other[3]);
                             if ((odd ? row_valid_pair : row_valid) && !skip)
@@ -716,7 +727,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     {
                         if (p.out_es == 1)
                         {
-                            int8_t* o = reinterpret_cast<int8_t*>(p.out) + pix * p.OC + col;
+                            int8_t* o = reinterpret_cast<int8_t*>(p.out) + ooff;
                             if (nvalid == 32 && ((p.OC & 15) == 0))
                             {
                                 uint4 w0 = make_uint4(pack4_i8(v[0], v[1], v[2], v[3]), pack4_i8(v[4], v[5], v[6], v[7]),
@@ -736,7 +747,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         }
                         else if (p.out_es == 2)
                         {
-                            int16_t* o = reinterpret_cast<int16_t*>(p.out) + pix * p.OC + col;
+                            int16_t* o = reinterpret_cast<int16_t*>(p.out) + ooff;
                 #pragma unroll
                             for (int i = 0; i < 32; i++)
                                 if (i < nvalid)
@@ -744,7 +755,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         }
                         else
                         {
-                            int32_t* o = reinterpret_cast<int32_t*>(p.out) + pix * p.OC + col;
+                            int32_t* o = reinterpret_cast<int32_t*>(p.out) + ooff;
                 #pragma unroll
                             for (int i = 0; i < 32; i++)
                                 if (i < nvalid)
@@ -788,7 +799,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         continue;
                     if (p.out_es == 4)
                     {
-                        float* o = reinterpret_cast<float*>(p.out) + pix * p.OC + col;
+                        float* o = reinterpret_cast<float*>(p.out) + ooff;
                         if (nvalid == 32 && ((p.OC & 7) == 0) && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0)
                         {
                             // 32 bytes per store: whole sectors (see the int32 epilogue)
@@ -823,7 +834,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                             else
                                 h[i] = __half_as_ushort(__float2half_rn(f[i]));
                         }
-                        uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + pix * p.OC + col;
+                        uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + ooff;
                         if (nvalid == 32 && ((p.OC & 15) == 0) && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0)
                         {
 #pragma unroll
@@ -1015,6 +1026,10 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     k.out_sx = q.out_sy ? q.out_sx : 1;
     k.out_y0 = q.out_sy ? q.out_y0 : 0;
     k.out_x0 = q.out_sy ? q.out_x0 : 0;
+    k.d2s_oc = q.out_sy ? q.d2s_oc : 0;
+    k.d2s_kw = q.d2s_kw;
+    if (k.d2s_oc != 0 && (k.d2s_oc % 32 != 0 || q.OC % k.d2s_oc != 0))
+        return no("depth-to-space output needs channel blocks that are multiples of 32");
     k.tiles_x = (OW + BW - 1) / BW;
     k.tiles_y = (OH + BH - 1) / BH;
     k.tiles_n = (N + BN - 1) / BN;

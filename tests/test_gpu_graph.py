@@ -114,3 +114,44 @@ def test_decoder_graph_with_transpose_convolutions_matches_oracle():
         ctx.graph_destroy(run.captured)
     finally:
         ctx.close()
+
+
+def test_test_directory_runner_matches_oracle(tmp_path):
+    """desc.json + .npy inputs in, .npy outputs out, graph status as the return value and as the process exit code."""
+    import subprocess
+    import sys
+    from reference_model_b200 import run_test as RT
+    g = _decoder_graph()
+    x = np.random.default_rng(6).integers(-128, 127, size=g.meta["input"][1], endpoint=True).astype(np.int8)
+    est, ref = graph_oracle.evaluate(g, {"input": x}, nthreads=8)
+    assert est == 0
+    desc = RT.save_test(g, {"input": x}, str(tmp_path / "valid"))
+    status, msg, written = RT.run_test(desc)
+    assert status == 0 and msg is None and len(written) == 2
+    for name, path in zip(g.outputs, written):
+        out = np.load(path)
+        assert out.dtype == (np.int8 if g.meta[name][0] == tb.DType.INT8 else np.int32)
+        assert np.array_equal(out.astype(np.int32), ref[name])
+    # the same through the command line, node by node
+    for f in written:
+        __import__("os").remove(f)
+    r = subprocess.run([sys.executable, "-m", "reference_model_b200.run_test", "--test_desc", desc, "--unfused"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "Graph result: VALID" in r.stdout, r.stderr
+    assert np.array_equal(np.load(written[0]).astype(np.int32), ref[g.outputs[0]])
+
+    # UNPREDICTABLE: a RESCALE shift so small that apply_scale_32's range REQUIRE fails; no output file is written
+    g_bad = _decoder_graph()
+    g_bad.consts["up2_s"] = np.full_like(g_bad.consts["up2_s"], 2)
+    est_bad, _ = graph_oracle.evaluate(g_bad, {"input": x}, nthreads=8)
+    assert est_bad == 1
+    desc = RT.save_test(g_bad, {"input": x}, str(tmp_path / "unpredictable"))
+    status, msg, written = RT.run_test(desc)
+    assert status == 1 and written == []
+
+    # ERROR: an attribute that breaks the output-size rule of TRANSPOSE_CONV2D
+    g_err = _decoder_graph()
+    [op for op in g_err.ops if op.kind == "TRANSPOSE_CONV2D"][0].attr["out_pad"] = [0, -1, -1, -1]
+    desc = RT.save_test(g_err, {"input": x}, str(tmp_path / "error"))
+    status, msg, written = RT.run_test(desc)
+    assert status == 2 and "expected output shape" in msg and written == []

@@ -684,6 +684,7 @@ TCONV_I8_CASES = [
     (2, 9, 11, 64, 256, 3, 3, (1, 1), (0, 1, 2, 0), -5, 0),        # stride 1: only the kernel is mirrored
     (1, 7, 5, 32, 32, 3, 2, (3, 2), (1, 0, 0, 2), 0, 0),           # rows of the output that no stamp reaches
     (1, 6, 6, 32, 40, 1, 2, (2, 3), (0, 0, 0, 0), 9, 0),           # kernel smaller than the stride: bias-only phases
+    (3, 7, 5, 32, 96, 3, 2, (3, 2), (0, 0, 0, 0), -3, 0),          # kernel == stride, not square: one GEMM, 6 stamps
     (3, 5, 9, 96, 24, 5, 3, (2, 2), (-4, 3, -2, -2), -77, 0),      # deep crop on one side, extension on the other
     (1, 7, 5, 16, 32, 3, 2, (3, 2), (1, 0, 0, 2), 0, 0),           # 16-byte channel run: CUDA cores
     (1, 5, 6, 7, 3, 3, 2, (2, 3), (0, 1, -1, 0), -5, 3),           # odd channels + weight zero point: CUDA cores
@@ -751,7 +752,8 @@ def test_transpose_conv_int8_random_shapes(ctx):
 
 
 @pytest.mark.parametrize("dt,name", [(F16, "fp16"), (BF16, "bf16"), (F32, "fp32")])
-@pytest.mark.parametrize("case", [(2, 10, 10, 32, 64, 3, 3, (2, 2), (0, -1, -1, 0)), (1, 6, 7, 5, 9, 2, 3, (1, 2), (1, 0, 0, 0))])
+@pytest.mark.parametrize("case", [(2, 10, 10, 32, 64, 3, 3, (2, 2), (0, -1, -1, 0)), (1, 6, 7, 5, 9, 2, 3, (1, 2), (1, 0, 0, 0)),
+                                  (2, 9, 8, 48, 64, 2, 2, (2, 2), (0, 0, 0, 0))])
 def test_transpose_conv_float(ctx, dt, name, case):
     N, IH, IW, IC, OC, KH, KW, stride, out_pad = case
     r = util.rng(950 + IC)
@@ -778,6 +780,30 @@ def test_transpose_conv_float(ctx, dt, name, case):
     ok, info = orc.verify_dot_product(out.astype(np.float32), ref, bnd, ksb, out=name)
     assert ok, (ctx.last_kernel(), info)
     _free(tx, tw, tbias, to)
+
+
+def test_transpose_conv_stamp_form_with_broadcast_bias_and_per_tensor_rescale(ctx):
+    """kernel == stride: one bias for all channels, one multiplier / shift for the tensor, unfused and fused."""
+    r = util.rng(991)
+    N, IH, IW, IC, OC, K = 2, 12, 10, 64, 64, 2
+    x, w, _ = util.conv_int8_case(r, N, IH, IW, IC, OC, K, K)
+    b = np.array([-4321], np.int32)
+    ref = orc.transpose_conv2d(x, w, b, [0, 0, 0, 0], [K, K], -128, 0, nthreads=8)
+    mult, shift = np.array([1518500250], np.int32), np.array([41], np.int8)
+    st_ref, ref8 = orc.rescale(ref, mult, shift, per_channel=False, scale32=True, rounding="SINGLE_ROUND", input_zp=0,
+                               output_zp=5, in_bits=32, out_bits=8)
+    assert st_ref == orc.VALID and len(np.unique(ref8)) > 50
+    tx, tw, tbias, tm, ts = [ctx.from_numpy(a) for a in (x, w, b, mult, shift)]
+    to, to8 = ctx.empty(I32, ref.shape), ctx.empty(I8, ref.shape)
+    ctx.transpose_conv2d(tx, tw, tbias, to, [0, 0, 0, 0], [K, K], -128, 0)
+    assert ctx.last_kernel().startswith("tc_gemm")
+    st, out = to.download()
+    assert st == tb.Status.OK and np.array_equal(out, ref)
+    epi = tb.Epilogue(tb.RescaleAttr(tm, ts, 0, 5, True, "SINGLE_ROUND", per_channel=False), None)
+    ctx.transpose_conv2d(tx, tw, tbias, to8, [0, 0, 0, 0], [K, K], -128, 0, epi)
+    st, out8 = to8.download()
+    assert st == tb.Status.OK and np.array_equal(out8, ref8)
+    _free(tx, tw, tbias, tm, ts, to, to8)
 
 
 def test_transpose_conv_error_ifs(ctx):
