@@ -1193,7 +1193,7 @@ extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tenso
 
     // ---- strided: one stride-1 convolution per output phase, each over the original input with the taps that reach
     // the phase, written straight into its pixels of the output.  Needs the tensor-core kernel for every phase.
-    if ((sy > 1 || sx > 1) && sy * sx <= 64)
+    if ((sy > 1 || sx > 1) && sy * sx <= PhaseWeights::kMax)
     {
         struct Phase
         {
@@ -1255,10 +1255,32 @@ extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tenso
             if (st != TB200_OK)
                 return st;
             uint8_t* wbase = reinterpret_cast<uint8_t*>(ctx->stage);
-            for (const Phase& ph : phases)
-                launch_mirror(ctx, weight->data, wbase + ph.w_off, OC, KH, KW, IC, es, vec, ph.y.k0, sy, ph.y.T, ph.x.k0, sx,
-                              ph.x.T);
-            st = post_launch(ctx, "transpose_conv_phase_weights", (int)phases.size());
+            // all sub-kernels in one launch; the copy unit is 16 bytes when the channel run allows it, else one element
+            const size_t unit_bytes = vec ? 16 : es;
+            const int units         = (int)(run / unit_bytes);
+            PhaseWeights pw;
+            pw.count    = (int)phases.size();
+            pw.first[0] = 0;
+            for (int i = 0; i < pw.count; i++)
+            {
+                const Phase& ph = phases[i];
+                pw.ky0[i] = ph.y.k0; pw.Ty[i] = ph.y.T; pw.kx0[i] = ph.x.k0; pw.Tx[i] = ph.x.T;
+                pw.out_off[i]   = (long long)(ph.w_off / unit_bytes);
+                pw.first[i + 1] = pw.first[i] + (long long)OC * ph.y.T * ph.x.T * units;
+            }
+            const int block = 256;
+            const int grid  = grid_for(ctx, pw.first[pw.count], block);
+            if (vec)
+                mirror_phase_weights_kernel<uint4><<<grid, block, 0, ctx->stream>>>(
+                    reinterpret_cast<const uint4*>(weight->data), reinterpret_cast<uint4*>(wbase), OC, KH, KW, units, sy, sx, pw);
+            else if (es == 1)
+                mirror_phase_weights_kernel<uint8_t><<<grid, block, 0, ctx->stream>>>(
+                    reinterpret_cast<const uint8_t*>(weight->data), wbase, OC, KH, KW, units, sy, sx, pw);
+            else
+                mirror_phase_weights_kernel<uint16_t><<<grid, block, 0, ctx->stream>>>(
+                    reinterpret_cast<const uint16_t*>(weight->data), reinterpret_cast<uint16_t*>(wbase), OC, KH, KW, units, sy,
+                    sx, pw);
+            st = post_launch(ctx, "transpose_conv_phase_weights", 1);
             if (st != TB200_OK)
                 return st;
             for (const Phase& ph : phases)

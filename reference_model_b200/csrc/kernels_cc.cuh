@@ -1318,6 +1318,40 @@ __global__ void mirror_weights_kernel(const U* __restrict__ in, U* __restrict__ 
     }
 }
 
+// The sub-kernels of every phase of a strided TRANSPOSE_CONV2D in one launch: phase i owns the work items
+// [first[i], first[i+1]) and writes its mirrored taps at out + out_off[i] (both in copy units).
+struct PhaseWeights
+{
+    enum { kMax = 64 };
+    int count;
+    int ky0[kMax], Ty[kMax], kx0[kMax], Tx[kMax];
+    long long out_off[kMax], first[kMax + 1];
+};
+
+template <typename U>
+__global__ void mirror_phase_weights_kernel(const U* __restrict__ in, U* __restrict__ out, int OC, int KH, int KW, int units,
+                                            int sy, int sx, const __grid_constant__ PhaseWeights ph)
+{
+    const int64_t total = ph.first[ph.count];
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += step)
+    {
+        int p = 0;
+        while (p + 1 < ph.count && g >= ph.first[p + 1])
+            p++;
+        int64_t i    = g - ph.first[p];
+        const int Ty = ph.Ty[p], Tx = ph.Tx[p];
+        const int u  = (int)(i % units);
+        int64_t r    = i / units;
+        const int tx = (int)(r % Tx);
+        r /= Tx;
+        const int ty = (int)(r % Ty);
+        const int oc = (int)(r / Ty);
+        const int ky = ph.ky0[p] + sy * (Ty - 1 - ty), kx = ph.kx0[p] + sx * (Tx - 1 - tx);
+        out[ph.out_off[p] + i] = in[(((int64_t)oc * KH + ky) * KW + kx) * units + u];
+    }
+}
+
 // TRANSPOSE_CONV2D with kernel == stride and no out_pad: stamps do not overlap, so the operator is one GEMM whose
 // columns are (ky, kx, oc).  One launch prepares its operands: weights OHWI -> rows ((ky*KW + kx)*OC + oc) of IC
 // channels each, and the per-channel vectors (bias, RESCALE multiplier and shift; null = absent) repeated for every
