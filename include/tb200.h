@@ -59,7 +59,9 @@ extern "C"
         TB200_INT32  = 5,
         TB200_INT8   = 8,
         TB200_UINT16 = 9,
-        TB200_UINT8  = 10
+        TB200_UINT8  = 10,
+        TB200_FP8E4M3 = 12, /* 1-4-3, bias 7, no infinities (MATMUL operands only) */
+        TB200_FP8E5M2 = 13  /* 1-5-2, bias 15 (MATMUL operands only) */
     } tb200_dtype;
 
     /* RoundingMode of the RESCALE attribute (reference_model/src/ops/type_conversion.cpp:229-231). */
@@ -212,7 +214,9 @@ extern "C"
                                                   tb200_tensor* output);
 
     /* MATMUL.  Replaces OpMatMul<A,B,Out>::eval (reference_model/src/ops/tensor_ops.cpp:1423-1492, checks :1347-1420).
-     * a [N,H,C], b [N,C,W], output [N,H,W]; INT8xINT8->INT32, FP16/BF16->same or FP32, FP32->FP32 (FFMA, no TF32). */
+     * a [N,H,C], b [N,C,W], output [N,H,W]; INT8xINT8->INT32, FP16/BF16->same or FP32, FP32->FP32 (FFMA, no TF32),
+     * FP8E4M3 / FP8E5M2 in any pairing of a and b -> FP16 or FP32 (:2263-2270; fp32 accumulation on the tensor cores,
+     * `kind::f8f6f4`, rounded once to the output type). */
     TB200_API tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, const tb200_tensor* b, int32_t a_zp,
                                         int32_t b_zp, const tb200_epilogue* epilogue, tb200_tensor* output);
 

@@ -260,6 +260,28 @@ def fptrunc(x, fdt):
     return out
 
 
+def fp8_to_f32(bits, fmt):
+    """Value of every 8-bit floating code, exactly, as float32.  fmt "e4m3": 1-4-3, bias 7, no infinities, S.1111.111
+    is NaN; fmt "e5m2": 1-5-2, bias 15, IEEE-like infinities and NaNs.  These are the FP8E4M3 / FP8E5M2 tensor types
+    of OpMatMul's fp8 instantiations (tensor_ops.cpp:2263-2270); the reference converts them with a float class of
+    its serialization submodule, which is not in the tree, so this decode follows the published 8-bit formats and is
+    checked against torch's casts in the tests."""
+    b = np.asarray(bits, dtype=np.uint8).astype(np.int32)
+    sign = np.where(b & 0x80, -1.0, 1.0)
+    if fmt == "e4m3":
+        e, m, ebits, bias = (b >> 3) & 0xF, b & 0x7, 3, 7
+        special = (e == 15) & (m == 7)
+        val = np.where(e == 0, m / 8.0 * 2.0 ** (1 - bias), (1 + m / 8.0) * np.exp2(e.astype(np.float64) - bias))
+        val = np.where(special, np.nan, val)
+    elif fmt == "e5m2":
+        e, m, bias = (b >> 2) & 0x1F, b & 0x3, 15
+        val = np.where(e == 0, m / 4.0 * 2.0 ** (1 - bias), (1 + m / 4.0) * np.exp2(e.astype(np.float64) - bias))
+        val = np.where(e == 31, np.where(m == 0, np.inf, np.nan), val)
+    else:
+        raise ValueError(fmt)
+    return (sign * val).astype(np.float32)
+
+
 # ----------------------------------------------------------------------------------------------
 # pools
 # ----------------------------------------------------------------------------------------------

@@ -29,12 +29,15 @@ class DType(enum.IntEnum):
     INT8 = 8
     UINT16 = 9
     UINT8 = 10
+    FP8E4M3 = 12
+    FP8E5M2 = 13
 
 
 _ITEMSIZE = {DType.BF16: 2, DType.FP16: 2, DType.FP32: 4, DType.INT16: 2, DType.INT32: 4, DType.INT8: 1,
-             DType.UINT16: 2, DType.UINT8: 1}
+             DType.UINT16: 2, DType.UINT8: 1, DType.FP8E4M3: 1, DType.FP8E5M2: 1}
 _NP_DTYPE = {DType.FP16: np.float16, DType.FP32: np.float32, DType.INT16: np.int16, DType.INT32: np.int32,
-             DType.INT8: np.int8, DType.UINT16: np.uint16, DType.UINT8: np.uint8, DType.BF16: np.uint16}
+             DType.INT8: np.int8, DType.UINT16: np.uint16, DType.UINT8: np.uint8, DType.BF16: np.uint16,
+             DType.FP8E4M3: np.uint8, DType.FP8E5M2: np.uint8}    # bf16 and fp8 travel as raw bit patterns
 ROUNDING = {"SINGLE_ROUND": 0, "DOUBLE_ROUND": 1, "INEXACT_ROUND": 2}
 
 

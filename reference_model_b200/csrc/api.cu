@@ -1468,15 +1468,22 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
     TB200_ERROR_IF(ctx, output->shape[1] != H, "OpMatMul operator output.shape[1] should match a.shape[1]");
     TB200_ERROR_IF(ctx, b->shape[1] != C, "OpMatMul operator a.shape[2] should match b.shape[1]");
     TB200_ERROR_IF(ctx, output->shape[2] != W, "OpMatMul operator output.shape[2] should match b.shape[2]");
-    TB200_ERROR_IF(ctx, a->dtype != b->dtype, "OpMatMul: operand dtypes differ");
+    // the two fp8 formats may be paired freely (reference_model/src/ops/tensor_ops.cpp:2263-2270)
+    const bool fp8 = dtype_is_fp8(a->dtype) && dtype_is_fp8(b->dtype);
+    TB200_ERROR_IF(ctx, a->dtype != b->dtype && !fp8, "OpMatMul: operand dtypes differ");
     const bool int_path = a->dtype == TB200_INT8;
     if (!int_path)
     {
-        TB200_ERROR_IF(ctx, !dtype_is_float(a->dtype), "OpMatMul: unsupported dtype");
+        TB200_ERROR_IF(ctx, !dtype_is_float(a->dtype) && !fp8, "OpMatMul: unsupported dtype");
         // :1433-1434
         TB200_ERROR_IF(ctx, a_zp != 0, "OpMatMul: A zeropoint must be zero for non int8_t data");
         TB200_ERROR_IF(ctx, b_zp != 0, "OpMatMul: B zeropoint must be zero for non int8_t data");
-        TB200_ERROR_IF(ctx, output->dtype != a->dtype && output->dtype != TB200_FP32, "OpMatMul: output dtype must be the input dtype or FP32");
+        if (fp8)
+            TB200_ERROR_IF(ctx, output->dtype != TB200_FP16 && output->dtype != TB200_FP32,
+                           "OpMatMul: the output of an FP8 MATMUL must be FP16 or FP32");
+        else
+            TB200_ERROR_IF(ctx, output->dtype != a->dtype && output->dtype != TB200_FP32,
+                           "OpMatMul: output dtype must be the input dtype or FP32");
     }
     TB200_ERROR_IF(ctx, a_zp < -128 || a_zp > 127 || b_zp < -128 || b_zp > 127, "OpMatMul: zero point outside the int8 range");
     EpiInfo epi;
@@ -1497,8 +1504,9 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
     {
         TcProblem q;
         memset(&q, 0, sizeof(q));
-        q.in_dtype = a->dtype;
-        q.a        = a->data;
+        q.in_dtype    = a->dtype;
+        q.b_fp8_dtype = (fp8 && b->dtype != a->dtype) ? (int)b->dtype : 0;
+        q.a           = a->data;
         q.N = 1; q.IH = N; q.IW = H; q.IC = C;
         q.OH = N; q.OW = H; q.OC = W;
         q.KH = 1; q.KW = 1;
@@ -1642,6 +1650,31 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
         matmul_direct_i8_kernel<<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const int8_t*>(a->data),
                                                                  reinterpret_cast<const int8_t*>(b->data),
                                                                  reinterpret_cast<int32_t*>(output->data), N, H, C, W, a_zp, b_zp);
+    else if (fp8)
+    {
+#define TB200_FP8_MM(TA, TBB, TO)                                                                                     \
+    matmul_direct_fp_kernel<TA, TO, TBB><<<grid, block, 0, ctx->stream>>>(                                             \
+        reinterpret_cast<const TA*>(a->data), reinterpret_cast<const TBB*>(b->data), reinterpret_cast<TO*>(output->data), \
+        N, H, C, W)
+        const bool a43 = a->dtype == TB200_FP8E4M3, b43 = b->dtype == TB200_FP8E4M3, o16 = output->dtype == TB200_FP16;
+        if (a43 && b43)
+        {
+            if (o16) TB200_FP8_MM(__nv_fp8_e4m3, __nv_fp8_e4m3, __half); else TB200_FP8_MM(__nv_fp8_e4m3, __nv_fp8_e4m3, float);
+        }
+        else if (a43)
+        {
+            if (o16) TB200_FP8_MM(__nv_fp8_e4m3, __nv_fp8_e5m2, __half); else TB200_FP8_MM(__nv_fp8_e4m3, __nv_fp8_e5m2, float);
+        }
+        else if (b43)
+        {
+            if (o16) TB200_FP8_MM(__nv_fp8_e5m2, __nv_fp8_e4m3, __half); else TB200_FP8_MM(__nv_fp8_e5m2, __nv_fp8_e4m3, float);
+        }
+        else
+        {
+            if (o16) TB200_FP8_MM(__nv_fp8_e5m2, __nv_fp8_e5m2, __half); else TB200_FP8_MM(__nv_fp8_e5m2, __nv_fp8_e5m2, float);
+        }
+#undef TB200_FP8_MM
+    }
     else if (a->dtype == TB200_FP32)
         matmul_direct_fp_kernel<float, float><<<grid, block, 0, ctx->stream>>>(
             reinterpret_cast<const float*>(a->data), reinterpret_cast<const float*>(b->data),

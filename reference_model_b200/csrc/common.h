@@ -83,6 +83,8 @@ inline size_t dtype_size(tb200_dtype d)
     {
         case TB200_INT8:
         case TB200_UINT8:
+        case TB200_FP8E4M3:
+        case TB200_FP8E5M2:
             return 1;
         case TB200_BF16:
         case TB200_FP16:
@@ -99,6 +101,11 @@ inline size_t dtype_size(tb200_dtype d)
 inline bool dtype_is_float(tb200_dtype d)
 {
     return d == TB200_FP16 || d == TB200_BF16 || d == TB200_FP32;
+}
+
+inline bool dtype_is_fp8(tb200_dtype d)
+{
+    return d == TB200_FP8E4M3 || d == TB200_FP8E5M2;
 }
 
 inline int64_t numel(const tb200_tensor* t)
@@ -156,8 +163,10 @@ enum TcEpilogue : int
 
 struct TcProblem
 {
-    // element type of A and B: TB200_INT8, TB200_FP16 or TB200_BF16
+    // element type of A and B: TB200_INT8, TB200_FP16, TB200_BF16, or an fp8 format (then B may be the other fp8 format:
+    // b_fp8_dtype, 0 = same as A)
     tb200_dtype in_dtype;
+    int b_fp8_dtype;
     // A: activation tensor viewed as [N][IH][IW][IC] (matmul: [1][batch][M][K])
     const void* a;
     int N, IH, IW, IC;

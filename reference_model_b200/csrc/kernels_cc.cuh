@@ -4,6 +4,7 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <type_traits>
 
@@ -30,6 +31,18 @@ template <>
 __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v)
 {
     return __bfloat162float(v);
+}
+
+// fp8 operands are exact in fp32 (OpMatMul's FP8 instantiations, reference_model/src/ops/tensor_ops.cpp:2263-2270)
+template <>
+__device__ __forceinline__ float to_f32<__nv_fp8_e4m3>(__nv_fp8_e4m3 v)
+{
+    return float(v);
+}
+template <>
+__device__ __forceinline__ float to_f32<__nv_fp8_e5m2>(__nv_fp8_e5m2 v)
+{
+    return float(v);
 }
 
 template <typename T>
@@ -1036,8 +1049,8 @@ __global__ void matmul_direct_i8_kernel(const int8_t* __restrict__ a, const int8
     }
 }
 
-template <typename T, typename TOut>
-__global__ void matmul_direct_fp_kernel(const T* __restrict__ a, const T* __restrict__ b, TOut* __restrict__ out,
+template <typename T, typename TOut, typename TB = T>
+__global__ void matmul_direct_fp_kernel(const T* __restrict__ a, const TB* __restrict__ b, TOut* __restrict__ out,
                                         int N, int H, int C, int W)
 {
     const int64_t total = (int64_t)N * H * W;
@@ -1049,10 +1062,10 @@ __global__ void matmul_direct_fp_kernel(const T* __restrict__ a, const T* __rest
         const int h  = (int)(r % H);
         const int n  = (int)(r / H);
         const T* ap  = a + ((int64_t)n * H + h) * C;
-        const T* bp  = b + (int64_t)n * C * W + wc;
+        const TB* bp = b + (int64_t)n * C * W + wc;
         float acc    = 0.f;
         for (int c = 0; c < C; c++)
-            acc = fmaf(to_f32<T>(ap[c]), to_f32<T>(bp[(int64_t)c * W]), acc);
+            acc = fmaf(to_f32<T>(ap[c]), to_f32<TB>(bp[(int64_t)c * W]), acc);
         out[i] = from_f32<TOut>(acc);
     }
 }

@@ -56,7 +56,7 @@ struct TcKernelParams
     uint64_t a_desc_hi, b_desc_hi;
     int b_kstep_bytes, mmas_per_chunk;
     uint32_t idesc;
-    int is_f16_kind;
+    int is_f16_kind;    // 0: kind::i8, 1: kind::f16, 2: kind::f8f6f4
     int tmem_cols;
     int acc_bufs;    // TMEM accumulator buffers: 2 overlaps a tile's epilogue with the next tile's MMAs, 1 halves TMEM use
     // epilogue
@@ -342,7 +342,12 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                             for (int m = 0; m < mmas; m++)
                             {
                                 if (EPI == TC_EPI_FLOAT)
-                                    ptx::mma_f16_ss(d_tmem, ad, bd, idesc, accum);
+                                {
+                                    if (p.is_f16_kind == 2)
+                                        ptx::mma_f8_ss(d_tmem, ad, bd, idesc, accum);
+                                    else
+                                        ptx::mma_f16_ss(d_tmem, ad, bd, idesc, accum);
+                                }
                                 else
                                     ptx::mma_i8_ss(d_tmem, ad, bd, idesc, accum);
                                 accum = 1;
@@ -956,8 +961,10 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
         return false;
     };
     const int es = (int)dtype_size(q.in_dtype);
-    if (!(q.in_dtype == TB200_INT8 || q.in_dtype == TB200_FP16 || q.in_dtype == TB200_BF16))
+    if (!(q.in_dtype == TB200_INT8 || q.in_dtype == TB200_FP16 || q.in_dtype == TB200_BF16 || dtype_is_fp8(q.in_dtype)))
         return no("element type has no tensor-core path");
+    if (dtype_is_fp8(q.in_dtype) && q.epi != TC_EPI_FLOAT)
+        return no("fp8 operands need the floating epilogue");
     if ((reinterpret_cast<uintptr_t>(q.a) & 15) || (reinterpret_cast<uintptr_t>(q.b) & 15))
         return no("operand base not 16-byte aligned");
     const int row_bytes = q.IC * es;    // contiguous K bytes of one tap
@@ -1124,17 +1131,28 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
         k.commit_group = 1;
     plan->smem_bytes = k.num_stages * k.stage_bytes + 1024;
 
-    const bool is_f16 = q.in_dtype != TB200_INT8;
-    k.is_f16_kind     = is_f16;
-    const uint32_t ab_fmt = is_f16 ? (q.in_dtype == TB200_BF16 ? 1u : 0u) : (uint32_t)env_int("TB200_TC_I8_FMT", 1);
-    k.idesc = ptx::make_idesc(is_f16 ? 1u : 2u, ab_fmt, ab_fmt, 0u, q.b_mn_major ? 1u : 0u, kTileM, (uint32_t)block_n);
+    const bool is_f8  = dtype_is_fp8(q.in_dtype);
+    const bool is_f16 = q.in_dtype != TB200_INT8 && !is_f8;
+    k.is_f16_kind     = is_f8 ? 2 : is_f16 ? 1 : 0;
+    if (is_f8)
+    {
+        // kind::f8f6f4 operand formats: 0 = E4M3, 1 = E5M2, chosen per operand; fp32 accumulators
+        const tb200_dtype bdt = q.b_fp8_dtype ? (tb200_dtype)q.b_fp8_dtype : q.in_dtype;
+        k.idesc = ptx::make_idesc(1u, q.in_dtype == TB200_FP8E5M2 ? 1u : 0u, bdt == TB200_FP8E5M2 ? 1u : 0u, 0u,
+                                  q.b_mn_major ? 1u : 0u, kTileM, (uint32_t)block_n);
+    }
+    else
+    {
+        const uint32_t ab_fmt = is_f16 ? (q.in_dtype == TB200_BF16 ? 1u : 0u) : (uint32_t)env_int("TB200_TC_I8_FMT", 1);
+        k.idesc = ptx::make_idesc(is_f16 ? 1u : 2u, ab_fmt, ab_fmt, 0u, q.b_mn_major ? 1u : 0u, kTileM, (uint32_t)block_n);
+    }
     int cols = 32;
     while (cols < k.acc_bufs * block_n)
         cols *= 2;
     k.tmem_cols = cols;
 
     // tensor maps
-    plan->dt    = q.in_dtype == TB200_INT8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+    plan->dt    = (q.in_dtype == TB200_INT8 || is_f8) ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                   : q.in_dtype == TB200_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                              : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     plan->a_swz = swz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : swz == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;

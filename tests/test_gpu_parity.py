@@ -627,6 +627,59 @@ def test_matmul_float(ctx, dt, name, shape):
         assert ok, (kernel, info)
 
 
+# ------------------------------------------------------------------------------------------- fp8 MATMUL
+def _fp8_codes(r, shape, fmt):
+    """Random finite fp8 codes with magnitudes up to about 2 (no NaN / infinity codes, no huge values)."""
+    if fmt == "e4m3":
+        mag = r.integers(0, 0x41, size=shape, endpoint=True, dtype=np.int64)     # up to 0x41 = 2.25
+    else:
+        mag = r.integers(0, 0x41, size=shape, endpoint=True, dtype=np.int64)     # up to 0x41 = 2.5
+    return (mag | (r.integers(0, 2, size=shape) << 7)).astype(np.uint8)
+
+
+@pytest.mark.parametrize("fa,fb", [("e4m3", "e4m3"), ("e5m2", "e5m2"), ("e4m3", "e5m2"), ("e5m2", "e4m3")])
+@pytest.mark.parametrize("shape", [(2, 256, 512, 256), (3, 130, 96, 80), (1, 33, 50, 20)])
+def test_matmul_fp8(ctx, fa, fb, shape):
+    N, H, C, W = shape
+    r = util.rng(1300 + H + (fa == "e5m2") * 2 + (fb == "e5m2"))
+    ca, cb = _fp8_codes(r, (N, H, C), fa), _fp8_codes(r, (N, C, W), fb)
+    a, b = orc.fp8_to_f32(ca, fa), orc.fp8_to_f32(cb, fb)
+    ref = orc.matmul(a, b, mode="f64")
+    bnd = orc.matmul(np.abs(a), np.abs(b), mode="f64")
+    dts = {"e4m3": tb.DType.FP8E4M3, "e5m2": tb.DType.FP8E5M2}
+    ta, tbb = ctx.from_numpy(ca, dts[fa]), ctx.from_numpy(cb, dts[fb])
+    for out_dt, name in ((F16, "fp16"), (F32, "fp32")):
+        # products of fp8 values are exact in fp32; what is bounded is the fp32 accumulation and the final rounding
+        ksb = orc.dot_product_ksb(C, "fp32", name)
+        to = ctx.empty(out_dt, (N, H, W))
+        for policy in (0, 1):
+            old = ctx.set_kernel_policy(policy)
+            ctx.matmul(ta, tbb, to)
+            kernel = ctx.last_kernel()
+            ctx.set_kernel_policy(old)
+            st, out = to.download()
+            ok, info = orc.verify_dot_product(out.astype(np.float32), ref, bnd, ksb, out=name)
+            assert st == tb.Status.OK and ok, (kernel, info)
+            if policy == 0 and C % 32 == 0:
+                assert kernel.startswith("tc_gemm"), kernel
+            if policy == 1:
+                assert kernel == "matmul_direct"
+        to.free()
+    _free(ta, tbb)
+
+
+def test_matmul_fp8_error_ifs(ctx):
+    a8 = ctx.from_numpy(np.zeros((1, 32, 32), np.uint8), tb.DType.FP8E4M3)
+    b8 = ctx.from_numpy(np.zeros((1, 32, 32), np.uint8), tb.DType.FP8E5M2)
+    bh = ctx.from_numpy(np.zeros((1, 32, 32), np.float16))
+    o16, obf = ctx.empty(F16, (1, 32, 32)), ctx.empty(BF16, (1, 32, 32))
+    assert ctx.matmul(a8, b8, o16) == tb.Status.OK
+    assert ctx.matmul(a8, bh, o16, check=False) == tb.Status.ERROR        # fp8 pairs only with fp8
+    assert ctx.matmul(a8, b8, obf, check=False) == tb.Status.ERROR        # FP16 or FP32 outputs only
+    assert ctx.matmul(a8, b8, o16, a_zp=1, check=False) == tb.Status.ERROR
+    _free(a8, b8, bh, o16, obf)
+
+
 # ------------------------------------------------------------------------------------------- floating convolution
 FP_CONV_CASES = [
     (2, 28, 28, 32, 192, 1, 1, 1, (0, 0, 0, 0)),    # the inverted-residual expand shape (small)

@@ -287,3 +287,16 @@ def test_transpose_conv2d_attribute_rules():
     assert orc.check_transpose_conv2d_attribute(4, 4, 6, 9, 3, 3, [-3, 0, 0, 0], [2, 2]) != 0
     assert orc.check_transpose_conv2d_attribute(4, 4, 7, 9, 3, 3, [-2, 0, 0, 0], [2, 2]) == 0
     assert orc.check_transpose_conv2d_attribute(4, 4, 10, 9, 3, 3, [0, 0, 0, 0], [2, 2]) != 0
+
+
+def test_fp8_decode_matches_torch_casts():
+    import torch
+    codes = np.arange(256, dtype=np.uint8)
+    for fmt, tdt in (("e4m3", torch.float8_e4m3fn), ("e5m2", torch.float8_e5m2)):
+        mine = orc.fp8_to_f32(codes, fmt)
+        theirs = torch.from_numpy(codes.copy()).view(tdt).to(torch.float32).numpy()
+        assert np.array_equal(np.isnan(mine), np.isnan(theirs))
+        ok = ~np.isnan(mine)
+        assert np.array_equal(mine[ok], theirs[ok]) and np.array_equal(np.signbit(mine[ok]), np.signbit(theirs[ok]))
+    assert orc.fp8_to_f32([0x7E], "e4m3")[0] == 448.0 and orc.fp8_to_f32([0x01], "e4m3")[0] == 2.0 ** -9
+    assert orc.fp8_to_f32([0x7B], "e5m2")[0] == 57344.0 and orc.fp8_to_f32([0x01], "e5m2")[0] == 2.0 ** -16
