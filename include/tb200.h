@@ -60,8 +60,8 @@ extern "C"
         TB200_INT8   = 8,
         TB200_UINT16 = 9,
         TB200_UINT8  = 10,
-        TB200_FP8E4M3 = 12, /* 1-4-3, bias 7, no infinities (MATMUL operands only) */
-        TB200_FP8E5M2 = 13  /* 1-5-2, bias 15 (MATMUL operands only) */
+        TB200_FP8E4M3 = 12, /* 1-4-3, bias 7, no infinities; operands of MATMUL, CONV2D, TRANSPOSE_CONV2D */
+        TB200_FP8E5M2 = 13  /* 1-5-2, bias 15; operands of MATMUL, CONV2D, TRANSPOSE_CONV2D */
     } tb200_dtype;
 
     /* RoundingMode of the RESCALE attribute (reference_model/src/ops/type_conversion.cpp:229-231). */
@@ -186,8 +186,8 @@ extern "C"
      * checks of check_conv_attribute (:120-226) / OpConv2d::checkTensorAttributes (:690-720).
      * input NHWC, weight OHWI, bias [OC] or [1]; pad = {top,bottom,left,right}, stride = {y,x}, dilation = {y,x}.
      * Supported tuples (in/weight/bias/out): INT8/INT8/INT32/INT32, FP16/FP16/FP16/FP16, BF16/BF16/BF16/BF16,
-     * FP32/FP32/FP32/FP32; floating types accumulate in fp32.  With an epilogue carrying RESCALE the output is
-     * the RESCALE's output dtype. */
+     * FP32/FP32/FP32/FP32, FP8E4M3/FP8E4M3/FP16/FP16, FP8E5M2/FP8E5M2/FP16/FP16 (:2228-2229); floating types
+     * accumulate in fp32.  With an epilogue carrying RESCALE the output is the RESCALE's output dtype. */
     TB200_API tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
                                         const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp,
                                         const int32_t pad[4], const int32_t stride[2], const int32_t dilation[2],

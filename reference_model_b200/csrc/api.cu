@@ -732,9 +732,14 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
         TB200_ERROR_IF(ctx, bias->dtype != TB200_INT32, "OpConv2d: INT8 convolution needs an INT32 bias");
     else
     {
-        TB200_ERROR_IF(ctx, !dtype_is_float(input->dtype), "OpConv2d: unsupported input dtype %d", (int)input->dtype);
-        TB200_ERROR_IF(ctx, bias->dtype != input->dtype || output->dtype != input->dtype,
-                       "OpConv2d: floating bias and output must have the input dtype");
+        TB200_ERROR_IF(ctx, !dtype_is_float(input->dtype) && !dtype_is_fp8(input->dtype), "OpConv2d: unsupported input dtype %d",
+                       (int)input->dtype);
+        if (dtype_is_fp8(input->dtype))    // <FP8, FP8, FP16, FP16>, reference_model/src/ops/tensor_ops.cpp:2228-2229
+            TB200_ERROR_IF(ctx, bias->dtype != TB200_FP16 || output->dtype != TB200_FP16,
+                           "OpConv2d: an FP8 convolution has an FP16 bias and output");
+        else
+            TB200_ERROR_IF(ctx, bias->dtype != input->dtype || output->dtype != input->dtype,
+                           "OpConv2d: floating bias and output must have the input dtype");
         // :805,811
         TB200_ERROR_IF(ctx, input_zp != 0, "Input zero point must be zero for non int8_t data");
         TB200_ERROR_IF(ctx, weight_zp != 0, "Weight zero point must be zero for non int8_t data");
@@ -824,7 +829,7 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
                 if (st != TB200_OK)
                     return st;
                 float* bf = reinterpret_cast<float*>(ctx->scratch);
-                if (input->dtype == TB200_FP16)
+                if (bias->dtype == TB200_FP16)
                     bias_to_f32_kernel<__half><<<(OCpad + 127) / 128, 128, 0, ctx->stream>>>(
                         reinterpret_cast<const __half*>(bias->data), bias->shape[0], OC, bf, OCpad);
                 else
@@ -941,6 +946,14 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
                 break;
         }
     }
+    else if (input->dtype == TB200_FP8E4M3)
+        conv2d_direct_fp_kernel<__nv_fp8_e4m3, __half><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __nv_fp8_e4m3*>(input->data), reinterpret_cast<const __nv_fp8_e4m3*>(weight->data),
+            reinterpret_cast<const __half*>(bias->data), reinterpret_cast<__half*>(output->data), d);
+    else if (input->dtype == TB200_FP8E5M2)
+        conv2d_direct_fp_kernel<__nv_fp8_e5m2, __half><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __nv_fp8_e5m2*>(input->data), reinterpret_cast<const __nv_fp8_e5m2*>(weight->data),
+            reinterpret_cast<const __half*>(bias->data), reinterpret_cast<__half*>(output->data), d);
     else if (input->dtype == TB200_FP16)
         conv2d_direct_fp_kernel<__half><<<grid, block, 0, ctx->stream>>>(
             reinterpret_cast<const __half*>(input->data), reinterpret_cast<const __half*>(weight->data),
@@ -1087,7 +1100,8 @@ extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tenso
     TB200_ERROR_IF(ctx, weight->dtype != input->dtype, "OpTransposeConv2d: input and weight dtypes differ");
     if (input->dtype != TB200_INT8)
     {
-        TB200_ERROR_IF(ctx, !dtype_is_float(input->dtype), "OpTransposeConv2d: unsupported input dtype %d", (int)input->dtype);
+        TB200_ERROR_IF(ctx, !dtype_is_float(input->dtype) && !dtype_is_fp8(input->dtype),
+                       "OpTransposeConv2d: unsupported input dtype %d", (int)input->dtype);
         TB200_ERROR_IF(ctx, input_zp != 0, "Input zero point must be zero for non int8_t data");
         TB200_ERROR_IF(ctx, weight_zp != 0, "Weight zero point must be zero for non int8_t data");
     }

@@ -838,9 +838,10 @@ __global__ void conv2d_direct_i8_kernel(const int8_t* __restrict__ in, const int
 }
 
 // Floating types: sequential fp32 accumulation, result (plus optional CLAMP) rounded once to the storage type.
-template <typename T>
-__global__ void conv2d_direct_fp_kernel(const T* __restrict__ in, const T* __restrict__ w, const T* __restrict__ bias,
-                                        T* __restrict__ out, ConvDev p)
+// TO: type of bias and output (the operand type, or FP16 for fp8 operands)
+template <typename T, typename TO = T>
+__global__ void conv2d_direct_fp_kernel(const T* __restrict__ in, const T* __restrict__ w, const TO* __restrict__ bias,
+                                        TO* __restrict__ out, ConvDev p)
 {
     const int64_t total = (int64_t)p.N * p.OH * p.OW * p.OC;
     const int64_t step  = (int64_t)gridDim.x * blockDim.x;
@@ -869,13 +870,13 @@ __global__ void conv2d_direct_fp_kernel(const T* __restrict__ in, const T* __res
                     acc = fmaf(to_f32<T>(ip[ic]), to_f32<T>(wp[ic]), acc);
             }
         }
-        float v = to_f32<T>(bias[p.bias_n == 1 ? 0 : oc]) + acc;
+        float v = to_f32<TO>(bias[p.bias_n == 1 ? 0 : oc]) + acc;
         if (p.has_clamp)
         {
             v = (v < p.clamp_lo_f) ? p.clamp_lo_f : v;
             v = (v > p.clamp_hi_f) ? p.clamp_hi_f : v;
         }
-        out[i] = from_f32<T>(v);
+        out[i] = from_f32<TO>(v);
     }
 }
 

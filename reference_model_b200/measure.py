@@ -112,6 +112,21 @@ def tconv_i8_config(ctx, timer, name, N, IH, IW, IC, OC, K, stride, out_pad, izp
             "algorithmic_ops": ops, "algorithmic_bytes": nbytes, "l2": note}
 
 
+def matmul_fp8_config(ctx, timer, name, N, H, C, W, iters, seed):
+    """FP8E4M3 x FP8E4M3 -> FP16 batched MATMUL (finite codes of magnitude up to 2.25)."""
+    r = np.random.default_rng(seed)
+    a = (r.integers(0, 0x42, size=(N, H, C)) | (r.integers(0, 2, size=(N, H, C)) << 7)).astype(np.uint8)
+    b = (r.integers(0, 0x42, size=(N, C, W)) | (r.integers(0, 2, size=(N, C, W)) << 7)).astype(np.uint8)
+    ta, tbb = ctx.from_numpy(a, tb.DType.FP8E4M3), ctx.from_numpy(b, tb.DType.FP8E4M3)
+    to = ctx.empty(tb.DType.FP16, (N, H, W))
+    fn = lambda: ctx.matmul(ta, tbb, to)
+    nbytes = a.nbytes + b.nbytes + N * H * W * 2
+    ms, note = timer.time(fn, iters, nbytes)
+    ops = 2.0 * N * H * C * W
+    return {"config": name, "kernel": ctx.last_kernel(), "ms": ms, "TFLOPS": ops / ms / 1e9, "GBps": nbytes / ms / 1e6,
+            "algorithmic_ops": ops, "algorithmic_bytes": nbytes, "l2": note}
+
+
 def graph_profile(batch):
     """Per-step times of one eager evaluation of the benchmark graph (each step bracketed by a device sync, so the sum
     exceeds the replayed graph's time; the shares are what this is for)."""
@@ -151,6 +166,7 @@ def main():
                          "or four values top,bottom,left,right)")
     ap.add_argument("--tconv", default=None,
                     help="also time one int8 TRANSPOSE_CONV2D+RESCALE+CLAMP layer: N,IH,IW,IC,OC,K,stride,out_pad")
+    ap.add_argument("--matmul-fp8", default=None, help="also time one FP8E4M3 MATMUL with FP16 output: N,H,C,W")
     ap.add_argument("--join", default=None,
                     help="also time one fused int8 residual join (RESCALE x2, ADD, RESCALE, CLAMP): N,H,W,C")
     ap.add_argument("--graph-profile", type=int, default=0, metavar="BATCH",
@@ -181,6 +197,10 @@ def main():
             n, ih, iw, ic, oc, k, st, op = [int(v) for v in args.tconv.split(",")]
             print(json.dumps(tconv_i8_config(ctx, timer, "tconv %s" % args.tconv, n, ih, iw, ic, oc, k, st, op, -128,
                                              args.iters, 11)))
+            sys.stdout.flush()
+        if args.matmul_fp8:
+            n, h, c, w = [int(v) for v in args.matmul_fp8.split(",")]
+            print(json.dumps(matmul_fp8_config(ctx, timer, "matmul fp8 %s" % args.matmul_fp8, n, h, c, w, args.iters, 13)))
             sys.stdout.flush()
         if args.join:
             shape = tuple(int(v) for v in args.join.split(","))

@@ -660,12 +660,70 @@ def test_matmul_fp8(ctx, fa, fb, shape):
             st, out = to.download()
             ok, info = orc.verify_dot_product(out.astype(np.float32), ref, bnd, ksb, out=name)
             assert st == tb.Status.OK and ok, (kernel, info)
-            if policy == 0 and C % 32 == 0:
+            if policy == 0 and C % 32 == 0 and W % 128 == 0:
                 assert kernel.startswith("tc_gemm"), kernel
             if policy == 1:
                 assert kernel == "matmul_direct"
         to.free()
     _free(ta, tbb)
+
+
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+@pytest.mark.parametrize("case", [(2, 14, 14, 64, 96, 3, 3, 1, (1, 1, 1, 1)), (1, 13, 13, 32, 24, 3, 3, 2, (1, 1, 1, 1)),
+                                  (2, 28, 28, 32, 192, 1, 1, 1, (0, 0, 0, 0)), (1, 6, 6, 5, 7, 3, 3, 1, (1, 1, 1, 1))])
+def test_conv_fp8(ctx, fmt, case):
+    """<FP8, FP8, FP16, FP16> CONV2D: fp8 input and weights, FP16 bias and output, optional fused CLAMP."""
+    N, IH, IW, IC, OC, KH, KW, s_, pad = case
+    r = util.rng(1400 + IC + OC)
+    cx, cw = _fp8_codes(r, (N, IH, IW, IC), fmt), _fp8_codes(r, (OC, KH, KW, IC), fmt)
+    x, w = orc.fp8_to_f32(cx, fmt), orc.fp8_to_f32(cw, fmt)
+    b = orc.fptrunc(r.standard_normal(OC).astype(np.float32), "fp16")
+    args = (list(pad), [s_, s_], [1, 1])
+    ref = orc.conv2d(x, w, b, *args, mode="f64")
+    bnd = orc.conv2d(x, w, b, *args, mode="f64", bounds=True)
+    ksb = orc.dot_product_ksb(KH * KW * IC + 1, "fp32", "fp16")
+    dt = tb.DType.FP8E4M3 if fmt == "e4m3" else tb.DType.FP8E5M2
+    tx, tw, tbias = ctx.from_numpy(cx, dt), ctx.from_numpy(cw, dt), ctx.from_numpy(b.astype(np.float16))
+    OH, OW = orc.conv_out_hw(IH, IW, KH, KW, *args)
+    to = ctx.empty(F16, (N, OH, OW, OC))
+    for policy in (0, 1):
+        old = ctx.set_kernel_policy(policy)
+        ctx.conv2d(tx, tw, tbias, to, *args)
+        kernel = ctx.last_kernel()
+        ctx.set_kernel_policy(old)
+        st, out = to.download()
+        ok, info = orc.verify_dot_product(out.astype(np.float32), ref, bnd, ksb, out="fp16")
+        assert st == tb.Status.OK and ok, (kernel, info)
+        if policy == 0 and IC % 32 == 0:
+            assert kernel.startswith("tc_gemm"), kernel
+    ctx.conv2d(tx, tw, tbias, to, *args, epilogue=tb.Epilogue(None, (0.0, 6.0)))
+    st, out = to.download()
+    assert out.min() >= 0.0 and out.max() <= 6.0
+    ok, info = orc.verify_dot_product(out.astype(np.float32), np.clip(ref, 0, 6), bnd, ksb, out="fp16")
+    assert ok, info
+    # an FP8 convolution with an fp8 or fp32 output is not an instantiation of the reference
+    bad = ctx.empty(F32, (N, OH, OW, OC))
+    assert ctx.conv2d(tx, tw, tbias, bad, *args, check=False) == tb.Status.ERROR
+    _free(tx, tw, tbias, to, bad)
+
+
+def test_transpose_conv_fp8(ctx):
+    r = util.rng(1450)
+    for (N, IH, IW, IC, OC, K, s_, op) in ((2, 9, 8, 64, 32, 2, 2, 0), (1, 7, 7, 32, 40, 4, 2, -1)):
+        cx, cw = _fp8_codes(r, (N, IH, IW, IC), "e4m3"), _fp8_codes(r, (OC, K, K, IC), "e4m3")
+        x, w = orc.fp8_to_f32(cx, "e4m3"), orc.fp8_to_f32(cw, "e4m3")
+        b = orc.fptrunc(r.standard_normal(OC).astype(np.float32), "fp16")
+        ref = orc.transpose_conv2d(x, w, b, [op] * 4, [s_, s_], mode="f64")
+        bnd = orc.transpose_conv2d(np.abs(x), np.abs(w), np.abs(b), [op] * 4, [s_, s_], mode="f64")
+        ksb = orc.dot_product_ksb(K * K * IC + 1, "fp32", "fp16")
+        tx, tw = ctx.from_numpy(cx, tb.DType.FP8E4M3), ctx.from_numpy(cw, tb.DType.FP8E4M3)
+        tbias = ctx.from_numpy(b.astype(np.float16))
+        to = ctx.empty(F16, ref.shape)
+        ctx.transpose_conv2d(tx, tw, tbias, to, [op] * 4, [s_, s_])
+        st, out = to.download()
+        ok, info = orc.verify_dot_product(out.astype(np.float32), ref, bnd, ksb, out="fp16")
+        assert st == tb.Status.OK and ok and ctx.last_kernel().startswith("tc_gemm"), (ctx.last_kernel(), info)
+        _free(tx, tw, tbias, to)
 
 
 def test_matmul_fp8_error_ifs(ctx):
