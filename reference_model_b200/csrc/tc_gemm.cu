@@ -69,6 +69,7 @@ struct TcKernelParams
     int corr_ystride;              // MATMUL: elements to advance per batch; 0 otherwise
     int corr_classes;              // 1: rows select a table row by their rectangle of in-scope filter taps
     int out_OH, out_OW, out_sy, out_sx, out_y0, out_x0;    // output pixel (oy, ox) -> (oy*out_sy + out_y0, ox*out_sx + out_x0)
+    int flat_iw, flat_ih;  // != 0: OW is N*flat_ih*flat_iw flattened pixels of a strided output view
     int d2s_oc, d2s_kw;    // != 0: column c is channel c % d2s_oc of the pixel (c / d2s_oc / d2s_kw, c / d2s_oc % d2s_kw) further on
     const float* bias_f_pad;       // TC_EPI_FLOAT: padded fp32 bias or null
     const int32_t* mult_pad;       // TC_EPI_RESCALE: padded per-column multipliers and shifts
@@ -490,7 +491,16 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             const int ox = t.x0 + xx, oy = t.y0 + yy, on = t.n0 + nn;
             const bool row_valid = (nn < p.BN) && (ox < p.OW) && (oy < p.OH) && (on < p.N);
             // index of this row's pixel in the output tensor (a dense grid, or one phase of a strided one)
-            const int64_t pix = ((int64_t)on * p.out_OH + oy * p.out_sy + p.out_y0) * p.out_OW + ox * p.out_sx + p.out_x0;
+            int pn = on, py = oy, px = ox;
+            if (p.flat_iw != 0)
+            {
+                // the pixel grid was flattened to one row of N*IH*IW pixels: recover the coordinates for the strided store
+                px          = ox % p.flat_iw;
+                const int t = ox / p.flat_iw;
+                py          = t % p.flat_ih;
+                pn          = t / p.flat_ih;
+            }
+            const int64_t pix = ((int64_t)pn * p.out_OH + py * p.out_sy + p.out_y0) * p.out_OW + px * p.out_sx + p.out_x0;
             // the neighbouring lane's row (lane ^ 1), for stores that fill whole 32-byte sectors between two lanes
             const int64_t pix_pair     = __shfl_xor_sync(0xffffffffu, pix, 1);
             const bool row_valid_pair  = __shfl_xor_sync(0xffffffffu, (int)row_valid, 1) != 0;
@@ -981,7 +991,8 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     const int64_t sn = q.a_stride_n ? q.a_stride_n : sh * q.IH;
     const bool dense = sw == q.IC && sh == sw * q.IW && sn == sh * q.IH;
     const bool pure_gemm = q.KH == 1 && q.KW == 1 && q.stride_y == 1 && q.stride_x == 1 && q.pad_t == 0 &&
-                           q.pad_l == 0 && OH == IH && OW == IW && !q.b_mn_major && dense && q.out_sy == 0;
+                           q.pad_l == 0 && OH == IH && OW == IW && !q.b_mn_major && dense;
+    const int view_iw = q.IW, view_ih = q.IH;
     if (pure_gemm)
     {
         int64_t pixels = (int64_t)N * IH * IW;
@@ -1027,6 +1038,8 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     k.OC = q.OC;
     k.IH = IH;
     k.IW = IW;
+    k.flat_iw = (q.out_sy && pure_gemm) ? view_iw : 0;
+    k.flat_ih = (q.out_sy && pure_gemm) ? view_ih : 0;
     k.out_OH = q.out_sy ? q.out_OH : OH;
     k.out_OW = q.out_sy ? q.out_OW : OW;
     k.out_sy = q.out_sy ? q.out_sy : 1;
@@ -1296,7 +1309,7 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
             break;
         default:
             kern = tc_gemm_kernel<TC_EPI_FLOAT>;
-            name = "tc_gemm_f16";
+            name = dtype_is_fp8(q.in_dtype) ? "tc_gemm_f8" : "tc_gemm_f16";
             break;
     }
     TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
