@@ -20,6 +20,7 @@
 #include <algorithm>
 #include <cuda.h>
 #include <cstring>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <mutex>
 
@@ -51,6 +52,8 @@ struct PairParams
     uint64_t a_desc_hi, b_desc_hi;
     uint32_t idesc;
     int32_t* out;
+    int out_kind;               // 0: int8 operands, int32 output with the corrections below; fp8 operands (kind::f8f6f4,
+                                // fp32 accumulators, no corrections): 1 = fp32 output, 2 = fp16 output
     const int32_t* row_corr;    // [batch * H] or null
     // Zero-point sums inside the kernel (sum warps read the tiles as they pass through shared memory):
     //   1: every tile sums the rows of its own A tile and hands them to its epilogue through shared memory; the term
@@ -249,7 +252,10 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
 #pragma unroll
                             for (int m = 0; m < 4; m++)
                             {
-                                ptx::mma_i8_ss_pair(d_tmem, ad, bd, p.idesc, accum);
+                                if (p.out_kind != 0)
+                                    ptx::mma_f8_ss_pair(d_tmem, ad, bd, p.idesc, accum);
+                                else
+                                    ptx::mma_i8_ss_pair(d_tmem, ad, bd, p.idesc, accum);
                                 accum = 1;
                                 ad += 2;      // 32 bytes of K inside the swizzled row
                                 bd += 256;    // 32 K rows of 128 bytes
@@ -572,6 +578,60 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                 const int col = t.w0 + c * 32;
                 if (col >= p.W || (p.debug & 1))
                     continue;
+                if (p.out_kind != 0)
+                {
+                    // fp32 accumulators of fp8 operands: stored as they are, or rounded once to fp16
+                    if (!row_valid)
+                        continue;
+                    const int nvalid = min(32, p.W - col);
+                    if (p.out_kind == 1)
+                    {
+                        uint32_t* o = reinterpret_cast<uint32_t*>(p.out) + orow * p.W + col;
+                        if (nvalid == 32 && (p.W & 7) == 0 && wide_ok)
+                        {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8)
+                                ptx::st_global_v8(o + i, v[i], v[i + 1], v[i + 2], v[i + 3], v[i + 4], v[i + 5], v[i + 6], v[i + 7]);
+                        }
+                        else
+                        {
+#pragma unroll
+                            for (int i = 0; i < 32; i++)
+                                if (i < nvalid)
+                                    o[i] = v[i];
+                        }
+                    }
+                    else
+                    {
+                        uint32_t h[16];
+#pragma unroll
+                        for (int i = 0; i < 16; i++)
+                        {
+                            const __half2 pr = __floats2half2_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                            h[i]             = *reinterpret_cast<const uint32_t*>(&pr);
+                        }
+                        uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + orow * p.W + col;
+                        if (nvalid == 32 && (p.W & 15) == 0 && wide_ok)
+                        {
+                            ptx::st_global_v8(o, h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7]);
+                            ptx::st_global_v8(o + 16, h[8], h[9], h[10], h[11], h[12], h[13], h[14], h[15]);
+                        }
+                        else if (nvalid == 32 && (p.W & 7) == 0)
+                        {
+#pragma unroll
+                            for (int i = 0; i < 16; i += 4)
+                                *reinterpret_cast<uint4*>(o + 2 * i) = make_uint4(h[i], h[i + 1], h[i + 2], h[i + 3]);
+                        }
+                        else
+                        {
+#pragma unroll
+                            for (int i = 0; i < 32; i++)
+                                if (i < nvalid)
+                                    o[i] = (uint16_t)((i & 1) ? (h[i >> 1] >> 16) : (h[i >> 1] & 0xffffu));
+                        }
+                    }
+                    continue;
+                }
                 if (corr_row != nullptr)
                 {
                     // the table is padded to a multiple of 256 columns: unconditional 128-bit loads
@@ -673,7 +733,12 @@ bool tc_gemm_pair_supported(const TcProblem& q, int num_sms)
 {
     if (pair_env_int("TB200_TC_PAIR", 1) == 0)
         return false;
-    if (q.in_dtype != TB200_INT8 || q.epi != TC_EPI_I32 || q.out_dtype != TB200_INT32 || !q.b_mn_major)
+    const bool i8 = q.in_dtype == TB200_INT8 && q.epi == TC_EPI_I32 && q.out_dtype == TB200_INT32;
+    const bool f8 = dtype_is_fp8(q.in_dtype) && q.epi == TC_EPI_FLOAT && !q.has_clamp && q.bias_f_pad == nullptr &&
+                    (q.out_dtype == TB200_FP16 || q.out_dtype == TB200_FP32) && pair_env_int("TB200_TC_PAIR_F8", 1) != 0;
+    if ((!i8 && !f8) || !q.b_mn_major)
+        return false;
+    if (f8 && (q.corr != nullptr || q.row_corr != nullptr || q.fuse_row_sums != 0))
         return false;
     if (q.N != 1 || q.KH != 1 || q.KW != 1 || q.stride_x != 1 || q.stride_y != 1 || q.pad_t || q.pad_l)
         return false;
@@ -712,7 +777,16 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     // K rows 128 bytes apart, 8-row groups 1024 bytes apart; an MMA's 32 K rows span 4096 bytes.
     k.a_desc_hi = ptx::make_smem_desc_hi(16, 1024, 2);
     k.b_desc_hi = ptx::make_smem_desc_hi(kPairChunkBytes, 1024, 2);
-    k.idesc     = ptx::make_idesc(2u, 1u, 1u, 0u, 1u, 256u, 256u);
+    const bool f8 = dtype_is_fp8(q.in_dtype);
+    if (f8)
+    {
+        // kind::f8f6f4: operand formats 0 = E4M3, 1 = E5M2, chosen per operand; fp32 accumulators
+        const tb200_dtype bdt = q.b_fp8_dtype ? (tb200_dtype)q.b_fp8_dtype : q.in_dtype;
+        k.idesc    = ptx::make_idesc(1u, q.in_dtype == TB200_FP8E5M2 ? 1u : 0u, bdt == TB200_FP8E5M2 ? 1u : 0u, 0u, 1u, 256u, 256u);
+        k.out_kind = q.out_dtype == TB200_FP32 ? 1 : 2;
+    }
+    else
+        k.idesc = ptx::make_idesc(2u, 1u, 1u, 0u, 1u, 256u, 256u);
     k.out         = reinterpret_cast<int32_t*>(q.out);
     k.row_corr    = q.row_corr;
     k.fuse_row_sums = q.fuse_row_sums;
@@ -780,8 +854,8 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     const cudaError_t le = cudaLaunchKernelEx(&cfg, tc_gemm_pair_kernel, k);
     timer_end(ctx);
     if (le != cudaSuccess)
-        return fail(ctx, TB200_INTERNAL, "launch of tc_gemm_pair_i8_i32 failed: %s", cudaGetErrorString(le));
-    return post_launch(ctx, "tc_gemm_pair_i8_i32");
+        return fail(ctx, TB200_INTERNAL, "launch of the CTA-pair MATMUL kernel failed: %s", cudaGetErrorString(le));
+    return post_launch(ctx, f8 ? "tc_gemm_pair_f8" : "tc_gemm_pair_i8_i32");
 }
 
 }    // namespace tb200

@@ -726,6 +726,29 @@ def test_transpose_conv_fp8(ctx):
         _free(tx, tw, tbias, to)
 
 
+@pytest.mark.parametrize("shape,fa,fb", [((40, 256, 384, 256), "e4m3", "e4m3"), ((10, 512, 400, 512), "e5m2", "e4m3"),
+                                         ((12, 520, 640, 300), "e4m3", "e5m2"), ((37, 256, 128, 264), "e5m2", "e5m2")])
+def test_matmul_fp8_pair_kernel(ctx, shape, fa, fb):
+    """Shapes with enough 256 x 256 tiles run on the CTA-pair kernel: ragged M / N / K edges, both output types."""
+    N, H, C, W = shape
+    r = util.rng(1350 + H + W)
+    ca, cb = _fp8_codes(r, (N, H, C), fa), _fp8_codes(r, (N, C, W), fb)
+    a, b = orc.fp8_to_f32(ca, fa), orc.fp8_to_f32(cb, fb)
+    ref = orc.matmul(a, b, mode="f64", nthreads=16)
+    bnd = orc.matmul(np.abs(a), np.abs(b), mode="f64", nthreads=16)
+    dts = {"e4m3": tb.DType.FP8E4M3, "e5m2": tb.DType.FP8E5M2}
+    ta, tbb = ctx.from_numpy(ca, dts[fa]), ctx.from_numpy(cb, dts[fb])
+    for out_dt, name in ((F16, "fp16"), (F32, "fp32")):
+        to = ctx.empty(out_dt, (N, H, W))
+        ctx.matmul(ta, tbb, to)
+        assert ctx.last_kernel() == "tc_gemm_pair_f8", ctx.last_kernel()
+        st, out = to.download()
+        ok, info = orc.verify_dot_product(out.astype(np.float32), ref, bnd, orc.dot_product_ksb(C, "fp32", name), out=name)
+        assert st == tb.Status.OK and ok, info
+        to.free()
+    _free(ta, tbb)
+
+
 def test_matmul_fp8_error_ifs(ctx):
     a8 = ctx.from_numpy(np.zeros((1, 32, 32), np.uint8), tb.DType.FP8E4M3)
     b8 = ctx.from_numpy(np.zeros((1, 32, 32), np.uint8), tb.DType.FP8E5M2)
