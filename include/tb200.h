@@ -60,8 +60,8 @@ extern "C"
         TB200_INT8   = 8,
         TB200_UINT16 = 9,
         TB200_UINT8  = 10,
-        TB200_FP8E4M3 = 12, /* 1-4-3, bias 7, no infinities; operands of MATMUL, CONV2D, TRANSPOSE_CONV2D */
-        TB200_FP8E5M2 = 13  /* 1-5-2, bias 15; operands of MATMUL, CONV2D, TRANSPOSE_CONV2D */
+        TB200_FP8E4M3 = 12, /* 1-4-3, bias 7, no infinities; operands of MATMUL and the convolutions */
+        TB200_FP8E5M2 = 13  /* 1-5-2, bias 15; operands of MATMUL and the convolutions */
     } tb200_dtype;
 
     /* RoundingMode of the RESCALE attribute (reference_model/src/ops/type_conversion.cpp:229-231). */
@@ -194,7 +194,7 @@ extern "C"
                                         const tb200_epilogue* epilogue, tb200_tensor* output);
 
     /* DEPTHWISE_CONV2D.  Replaces OpDepthwiseConv2d::eval (reference_model/src/ops/tensor_ops.cpp:1172-1334).
-     * weight [KH,KW,C,M]; output channel c*M+m. */
+     * weight [KH,KW,C,M]; output channel c*M+m.  Type tuples as for CONV2D (fp8 operands: :2250-2251). */
     TB200_API tb200_status tb200_depthwise_conv2d(tb200_ctx* ctx, const tb200_tensor* input,
                                                   const tb200_tensor* weight, const tb200_tensor* bias,
                                                   int32_t input_zp, int32_t weight_zp, const int32_t pad[4],

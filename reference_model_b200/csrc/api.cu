@@ -1393,9 +1393,14 @@ extern "C" tb200_status tb200_depthwise_conv2d(tb200_ctx* ctx, const tb200_tenso
         TB200_ERROR_IF(ctx, bias->dtype != TB200_INT32, "OpDepthwiseConv2d: INT8 convolution needs an INT32 bias");
     else
     {
-        TB200_ERROR_IF(ctx, !dtype_is_float(input->dtype), "OpDepthwiseConv2d: unsupported input dtype");
-        TB200_ERROR_IF(ctx, bias->dtype != input->dtype || output->dtype != input->dtype,
-                       "OpDepthwiseConv2d: floating bias and output must have the input dtype");
+        TB200_ERROR_IF(ctx, !dtype_is_float(input->dtype) && !dtype_is_fp8(input->dtype),
+                       "OpDepthwiseConv2d: unsupported input dtype");
+        if (dtype_is_fp8(input->dtype))    // <FP8, FP8, FP16, FP16>, reference_model/src/ops/tensor_ops.cpp:2250-2251
+            TB200_ERROR_IF(ctx, bias->dtype != TB200_FP16 || output->dtype != TB200_FP16,
+                           "OpDepthwiseConv2d: an FP8 convolution has an FP16 bias and output");
+        else
+            TB200_ERROR_IF(ctx, bias->dtype != input->dtype || output->dtype != input->dtype,
+                           "OpDepthwiseConv2d: floating bias and output must have the input dtype");
         TB200_ERROR_IF(ctx, input_zp != 0, "Input zero point must be zero for non int8_t data");
         TB200_ERROR_IF(ctx, weight_zp != 0, "Weight zero point must be zero for non int8_t data");
     }
@@ -1435,7 +1440,7 @@ extern "C" tb200_status tb200_depthwise_conv2d(tb200_ctx* ctx, const tb200_tenso
         }
         return post_launch(ctx, "depthwise_direct_i8");
     }
-    const bool x8 = (M == 1) && (C % 8 == 0) && input->dtype != TB200_FP32 && ctx->policy == 0 &&
+    const bool x8 = (M == 1) && (C % 8 == 0) && (input->dtype == TB200_FP16 || input->dtype == TB200_BF16) && ctx->policy == 0 &&
                     ((reinterpret_cast<uintptr_t>(input->data) | reinterpret_cast<uintptr_t>(weight->data) |
                       reinterpret_cast<uintptr_t>(output->data)) & 15) == 0;
     if (x8)
@@ -1452,7 +1457,15 @@ extern "C" tb200_status tb200_depthwise_conv2d(tb200_ctx* ctx, const tb200_tenso
         return post_launch(ctx, "depthwise_fp_x8");
     }
     const int grid = grid_for(ctx, numel(output), block);
-    if (input->dtype == TB200_FP16)
+    if (input->dtype == TB200_FP8E4M3)
+        depthwise_direct_fp_kernel<__nv_fp8_e4m3, __half><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __nv_fp8_e4m3*>(input->data), reinterpret_cast<const __nv_fp8_e4m3*>(weight->data),
+            reinterpret_cast<const __half*>(bias->data), reinterpret_cast<__half*>(output->data), d);
+    else if (input->dtype == TB200_FP8E5M2)
+        depthwise_direct_fp_kernel<__nv_fp8_e5m2, __half><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __nv_fp8_e5m2*>(input->data), reinterpret_cast<const __nv_fp8_e5m2*>(weight->data),
+            reinterpret_cast<const __half*>(bias->data), reinterpret_cast<__half*>(output->data), d);
+    else if (input->dtype == TB200_FP16)
         depthwise_direct_fp_kernel<__half><<<grid, block, 0, ctx->stream>>>(
             reinterpret_cast<const __half*>(input->data), reinterpret_cast<const __half*>(weight->data),
             reinterpret_cast<const __half*>(bias->data), reinterpret_cast<__half*>(output->data), d);

@@ -930,9 +930,9 @@ __global__ void depthwise_direct_i8_kernel(const int8_t* __restrict__ in, const 
         atomicOr(status, TB200_DEV_UNPREDICTABLE);
 }
 
-template <typename T>
+template <typename T, typename TO = T>
 __global__ void depthwise_direct_fp_kernel(const T* __restrict__ in, const T* __restrict__ w,
-                                           const T* __restrict__ bias, T* __restrict__ out, ConvDev p)
+                                           const TO* __restrict__ bias, TO* __restrict__ out, ConvDev p)
 {
     const int OC        = p.IC * p.M;
     const int64_t total = (int64_t)p.N * p.OH * p.OW * OC;
@@ -961,13 +961,13 @@ __global__ void depthwise_direct_fp_kernel(const T* __restrict__ in, const T* __
                            to_f32<T>(w[(((int64_t)ky * p.KW + kx) * p.IC + c) * p.M + m]), acc);
             }
         }
-        float v = to_f32<T>(bias[p.bias_n == 1 ? 0 : oc]) + acc;
+        float v = to_f32<TO>(bias[p.bias_n == 1 ? 0 : oc]) + acc;
         if (p.has_clamp)
         {
             v = (v < p.clamp_lo_f) ? p.clamp_lo_f : v;
             v = (v > p.clamp_hi_f) ? p.clamp_hi_f : v;
         }
-        out[i] = from_f32<T>(v);
+        out[i] = from_f32<TO>(v);
     }
 }
 

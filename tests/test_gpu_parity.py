@@ -707,6 +707,32 @@ def test_conv_fp8(ctx, fmt, case):
     _free(tx, tw, tbias, to, bad)
 
 
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+def test_depthwise_fp8(ctx, fmt):
+    """<FP8, FP8, FP16, FP16> DEPTHWISE_CONV2D, multiplier 1 and 2, with a fused CLAMP."""
+    r = util.rng(1460)
+    dt = tb.DType.FP8E4M3 if fmt == "e4m3" else tb.DType.FP8E5M2
+    for (N, IH, IW, C, M, K, s_, pad) in ((2, 15, 15, 24, 1, 3, 2, (1, 1, 1, 1)), (1, 9, 8, 5, 2, 3, 1, (1, 1, 0, 2))):
+        cx, cw = _fp8_codes(r, (N, IH, IW, C), fmt), _fp8_codes(r, (K, K, C, M), fmt)
+        x, w = orc.fp8_to_f32(cx, fmt), orc.fp8_to_f32(cw, fmt)
+        b = orc.fptrunc(r.standard_normal(C * M).astype(np.float32), "fp16")
+        args = (list(pad), [s_, s_], [1, 1])
+        ref = orc.depthwise_conv2d(x, w, b, *args, mode="f64")
+        bnd = orc.depthwise_conv2d(x, w, b, *args, mode="f64", bounds=True)
+        ksb = orc.dot_product_ksb(K * K + 1, "fp32", "fp16")
+        tx, tw, tbias = ctx.from_numpy(cx, dt), ctx.from_numpy(cw, dt), ctx.from_numpy(b.astype(np.float16))
+        to = ctx.empty(F16, ref.shape)
+        ctx.depthwise_conv2d(tx, tw, tbias, to, *args)
+        st, out = to.download()
+        ok, info = orc.verify_dot_product(out.astype(np.float32), ref, bnd, ksb, out="fp16")
+        assert st == tb.Status.OK and ok, info
+        ctx.depthwise_conv2d(tx, tw, tbias, to, *args, epilogue=tb.Epilogue(None, (0.0, 6.0)))
+        st, out = to.download()
+        ok, info = orc.verify_dot_product(out.astype(np.float32), np.clip(ref, 0, 6), bnd, ksb, out="fp16")
+        assert ok and out.min() >= 0.0 and out.max() <= 6.0, info
+        _free(tx, tw, tbias, to)
+
+
 def test_transpose_conv_fp8(ctx):
     r = util.rng(1450)
     for (N, IH, IW, IC, OC, K, s_, op) in ((2, 9, 8, 64, 32, 2, 2, 0), (1, 7, 7, 32, 40, 4, 2, -1)):
