@@ -20,6 +20,7 @@
 #include <algorithm>
 #include <cuda.h>
 #include <cstring>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <mutex>
@@ -52,8 +53,13 @@ struct PairParams
     uint64_t a_desc_hi, b_desc_hi;
     uint32_t idesc;
     int32_t* out;
-    int out_kind;               // 0: int8 operands, int32 output with the corrections below; fp8 operands (kind::f8f6f4,
-                                // fp32 accumulators, no corrections): 1 = fp32 output, 2 = fp16 output
+    int out_kind;               // 0: int8 operands, int32 output with the corrections below; floating operands (fp32
+                                // accumulators, no corrections): 1 = fp32 output, 2 = fp16 output, 3 = bf16 output
+    int mma_kind;               // 0: kind::i8, 1: kind::f8f6f4, 2: kind::f16 (fp16 / bf16 operands)
+    // Geometry of a 128-byte K chunk.  8-bit operands: 128 K elements, each CTA's half of B is one box of 128 columns.
+    // 16-bit operands: 64 K elements, the half is two boxes of 64 columns (one 128-byte swizzle atom each).
+    int chunk_elems, b_boxes, b_box_cols, b_box_bytes;
+    uint32_t b_kstep16;         // descriptor advance per MMA: its K rows x 128 bytes, in 16-byte units
     const int32_t* row_corr;    // [batch * H] or null
     // Zero-point sums inside the kernel (sum warps read the tiles as they pass through shared memory):
     //   1: every tile sums the rows of its own A tile and hands them to its epilogue through shared memory; the term
@@ -186,8 +192,10 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                         for (int j = 0; j < nch; j++)
                         {
                             ptx::tma_load_3d_pair(sA + (uint32_t)(j * kPairChunkBytes), &p.tmA, full_first, k, m0, t.n);
-                            ptx::tma_load_3d_pair(sB + (uint32_t)(j * kPairChunkBytes), &p.tmB, full_first, w0, k, t.n);
-                            k += 128;
+                            for (int bx = 0; bx < p.b_boxes; bx++)
+                                ptx::tma_load_3d_pair(sB + (uint32_t)(j * kPairChunkBytes + bx * p.b_box_bytes), &p.tmB, full_first,
+                                                      w0 + bx * p.b_box_cols, k, t.n);
+                            k += p.chunk_elems;
                         }
                     }
                     if (++stage == p.num_stages)
@@ -252,13 +260,15 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
 #pragma unroll
                             for (int m = 0; m < 4; m++)
                             {
-                                if (p.out_kind != 0)
+                                if (p.mma_kind == 2)
+                                    ptx::mma_f16_ss_pair(d_tmem, ad, bd, p.idesc, accum);
+                                else if (p.mma_kind == 1)
                                     ptx::mma_f8_ss_pair(d_tmem, ad, bd, p.idesc, accum);
                                 else
                                     ptx::mma_i8_ss_pair(d_tmem, ad, bd, p.idesc, accum);
                                 accum = 1;
-                                ad += 2;      // 32 bytes of K inside the swizzled row
-                                bd += 256;    // 32 K rows of 128 bytes
+                                ad += 2;              // 32 bytes of K inside the swizzled row
+                                bd += p.b_kstep16;    // the MMA's K rows of 128 bytes (32 rows of bytes, 16 rows of halves)
                             }
                         }
                     }
@@ -604,11 +614,24 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                     else
                     {
                         uint32_t h[16];
-#pragma unroll
-                        for (int i = 0; i < 16; i++)
+                        if (p.out_kind == 2)
                         {
-                            const __half2 pr = __floats2half2_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-                            h[i]             = *reinterpret_cast<const uint32_t*>(&pr);
+#pragma unroll
+                            for (int i = 0; i < 16; i++)
+                            {
+                                const __half2 pr = __floats2half2_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                                h[i]             = *reinterpret_cast<const uint32_t*>(&pr);
+                            }
+                        }
+                        else
+                        {
+#pragma unroll
+                            for (int i = 0; i < 16; i++)
+                            {
+                                const __nv_bfloat162 pr =
+                                    __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                                h[i] = *reinterpret_cast<const uint32_t*>(&pr);
+                            }
                         }
                         uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + orow * p.W + col;
                         if (nvalid == 32 && (p.W & 15) == 0 && wide_ok)
@@ -734,12 +757,16 @@ bool tc_gemm_pair_supported(const TcProblem& q, int num_sms)
     if (pair_env_int("TB200_TC_PAIR", 1) == 0)
         return false;
     const bool i8 = q.in_dtype == TB200_INT8 && q.epi == TC_EPI_I32 && q.out_dtype == TB200_INT32;
-    const bool f8 = dtype_is_fp8(q.in_dtype) && q.epi == TC_EPI_FLOAT && !q.has_clamp && q.bias_f_pad == nullptr &&
-                    (q.out_dtype == TB200_FP16 || q.out_dtype == TB200_FP32) && pair_env_int("TB200_TC_PAIR_F8", 1) != 0;
-    if ((!i8 && !f8) || !q.b_mn_major)
+    const bool fl = q.epi == TC_EPI_FLOAT && !q.has_clamp && q.bias_f_pad == nullptr;
+    const bool f8 = fl && dtype_is_fp8(q.in_dtype) && (q.out_dtype == TB200_FP16 || q.out_dtype == TB200_FP32) &&
+                    pair_env_int("TB200_TC_PAIR_F8", 1) != 0;
+    const bool f16 = fl && (q.in_dtype == TB200_FP16 || q.in_dtype == TB200_BF16) &&
+                     (q.out_dtype == q.in_dtype || q.out_dtype == TB200_FP32) && pair_env_int("TB200_TC_PAIR_F16", 1) != 0;
+    if ((!i8 && !f8 && !f16) || !q.b_mn_major)
         return false;
-    if (f8 && (q.corr != nullptr || q.row_corr != nullptr || q.fuse_row_sums != 0))
+    if ((f8 || f16) && (q.corr != nullptr || q.row_corr != nullptr || q.fuse_row_sums != 0))
         return false;
+    const int es = f16 ? 2 : 1;
     if (q.N != 1 || q.KH != 1 || q.KW != 1 || q.stride_x != 1 || q.stride_y != 1 || q.pad_t || q.pad_l)
         return false;
     if (q.a_stride_w || q.a_stride_h || q.a_stride_n || q.corr_classes || q.tile_begin || q.tile_end)
@@ -748,7 +775,7 @@ bool tc_gemm_pair_supported(const TcProblem& q, int num_sms)
         return false;
     const int64_t ldb = q.b_ld ? q.b_ld : q.OC;
     // whole 256 x 256 tiles must dominate, and TMA wants 16-byte row pitches
-    if (q.IW < 256 || q.OC < 256 || q.IC < 128 || q.IC % 16 != 0 || ldb % 16 != 0)
+    if (q.IW < 256 || q.OC < 256 || q.IC * es < 128 || (q.IC * es) % 16 != 0 || (ldb * es) % 16 != 0)
         return false;
     if ((reinterpret_cast<uintptr_t>(q.a) | reinterpret_cast<uintptr_t>(q.b) | reinterpret_cast<uintptr_t>(q.out)) & 15)
         return false;
@@ -772,13 +799,28 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     k.tiles_m      = (k.H + 255) / 256;
     k.tiles_w      = (k.W + 255) / 256;
     k.num_tiles    = k.NB * k.tiles_m * k.tiles_w;
-    k.total_chunks = (k.C + 127) / 128;
-    // A: K-major rows of 128 bytes, 8-row groups 1024 bytes apart.  B: MN-major, one 128-byte atom of columns per CTA,
-    // K rows 128 bytes apart, 8-row groups 1024 bytes apart; an MMA's 32 K rows span 4096 bytes.
+    const bool f8  = dtype_is_fp8(q.in_dtype);
+    const bool f16 = q.in_dtype == TB200_FP16 || q.in_dtype == TB200_BF16;
+    const int es   = f16 ? 2 : 1;
+    k.chunk_elems  = 128 / es;
+    k.total_chunks = (k.C + k.chunk_elems - 1) / k.chunk_elems;
+    // A: K-major rows of 128 bytes, 8-row groups 1024 bytes apart.  B: MN-major, 128-byte atoms of columns (128 columns
+    // of bytes: one atom per CTA; 64 columns of halves: two atoms per CTA, a box of chunk_elems K rows apart), K rows
+    // 128 bytes apart, 8-row groups 1024 bytes apart; an MMA's K rows (32 of bytes, 16 of halves) span 4096 / 2048 bytes.
+    k.b_box_cols  = 128 / es;
+    k.b_boxes     = 128 / k.b_box_cols;
+    k.b_box_bytes = k.chunk_elems * 128;
+    k.b_kstep16   = (uint32_t)((32 / es) * 128) >> 4;
     k.a_desc_hi = ptx::make_smem_desc_hi(16, 1024, 2);
-    k.b_desc_hi = ptx::make_smem_desc_hi(kPairChunkBytes, 1024, 2);
-    const bool f8 = dtype_is_fp8(q.in_dtype);
-    if (f8)
+    k.b_desc_hi = ptx::make_smem_desc_hi(k.b_box_bytes, 1024, 2);
+    k.mma_kind  = f16 ? 2 : f8 ? 1 : 0;
+    if (f16)
+    {
+        const uint32_t fmt = q.in_dtype == TB200_BF16 ? 1u : 0u;
+        k.idesc    = ptx::make_idesc(1u, fmt, fmt, 0u, 1u, 256u, 256u);
+        k.out_kind = q.out_dtype == TB200_FP32 ? 1 : q.out_dtype == TB200_BF16 ? 3 : 2;
+    }
+    else if (f8)
     {
         // kind::f8f6f4: operand formats 0 = E4M3, 1 = E5M2, chosen per operand; fp32 accumulators
         const tb200_dtype bdt = q.b_fp8_dtype ? (tb200_dtype)q.b_fp8_dtype : q.in_dtype;
@@ -800,17 +842,21 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     k.status      = ctx->d_status;
 
     cuuint64_t a_dims[3]    = { (cuuint64_t)k.C, (cuuint64_t)k.H, (cuuint64_t)k.NB };
-    cuuint64_t a_strides[2] = { (cuuint64_t)k.C, (cuuint64_t)k.C * (cuuint64_t)k.H };
+    cuuint64_t a_strides[2] = { (cuuint64_t)k.C * es, (cuuint64_t)k.C * (cuuint64_t)k.H * es };
     cuuint64_t b_dims[3]    = { (cuuint64_t)k.W, (cuuint64_t)k.C, (cuuint64_t)k.NB };
-    cuuint64_t b_strides[2] = { (cuuint64_t)ldb, (cuuint64_t)ldb * (cuuint64_t)k.C };
-    cuuint32_t box[3]       = { 128, 128, 1 };
+    cuuint64_t b_strides[2] = { (cuuint64_t)ldb * es, (cuuint64_t)ldb * (cuuint64_t)k.C * es };
+    cuuint32_t box[3]       = { (cuuint32_t)k.chunk_elems, 128, 1 };                        // A: K elements x rows
+    cuuint32_t box_b[3]     = { (cuuint32_t)k.b_box_cols, (cuuint32_t)k.chunk_elems, 1 };   // B: columns x K rows
     cuuint32_t estr[3]      = { 1, 1, 1 };
-    CUresult r = enc(&k.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(q.a), a_dims, a_strides, box, estr,
+    const CUtensorMapDataType tdt = !f16                        ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                    : q.in_dtype == TB200_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                               : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    CUresult r = enc(&k.tmA, tdt, 3, const_cast<void*>(q.a), a_dims, a_strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(ctx, TB200_INTERNAL, "tensor map for A rejected (CUresult %d)", (int)r);
-    r = enc(&k.tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(q.b), b_dims, b_strides, box, estr,
+    r = enc(&k.tmB, tdt, 3, const_cast<void*>(q.b), b_dims, b_strides, box_b, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -855,7 +901,7 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     timer_end(ctx);
     if (le != cudaSuccess)
         return fail(ctx, TB200_INTERNAL, "launch of the CTA-pair MATMUL kernel failed: %s", cudaGetErrorString(le));
-    return post_launch(ctx, f8 ? "tc_gemm_pair_f8" : "tc_gemm_pair_i8_i32");
+    return post_launch(ctx, f16 ? "tc_gemm_pair_f16" : f8 ? "tc_gemm_pair_f8" : "tc_gemm_pair_i8_i32");
 }
 
 }    // namespace tb200

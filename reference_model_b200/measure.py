@@ -127,6 +127,21 @@ def matmul_fp8_config(ctx, timer, name, N, H, C, W, iters, seed):
             "algorithmic_ops": ops, "algorithmic_bytes": nbytes, "l2": note}
 
 
+def matmul_f16_config(ctx, timer, name, N, H, C, W, iters, seed):
+    """fp16 x fp16 -> fp16 batched MATMUL."""
+    r = np.random.default_rng(seed)
+    a = r.standard_normal((N, H, C)).astype(np.float16)
+    b = r.standard_normal((N, C, W)).astype(np.float16)
+    ta, tbb = ctx.from_numpy(a), ctx.from_numpy(b)
+    to = ctx.empty(tb.DType.FP16, (N, H, W))
+    fn = lambda: ctx.matmul(ta, tbb, to)
+    nbytes = a.nbytes + b.nbytes + N * H * W * 2
+    ms, note = timer.time(fn, iters, nbytes)
+    ops = 2.0 * N * H * C * W
+    return {"config": name, "kernel": ctx.last_kernel(), "ms": ms, "TFLOPS": ops / ms / 1e9, "GBps": nbytes / ms / 1e6,
+            "algorithmic_ops": ops, "algorithmic_bytes": nbytes, "l2": note}
+
+
 def graph_profile(batch):
     """Per-step times of one eager evaluation of the benchmark graph (each step bracketed by a device sync, so the sum
     exceeds the replayed graph's time; the shares are what this is for)."""
@@ -167,6 +182,7 @@ def main():
     ap.add_argument("--tconv", default=None,
                     help="also time one int8 TRANSPOSE_CONV2D+RESCALE+CLAMP layer: N,IH,IW,IC,OC,K,stride,out_pad")
     ap.add_argument("--matmul-fp8", default=None, help="also time one FP8E4M3 MATMUL with FP16 output: N,H,C,W")
+    ap.add_argument("--matmul-f16", default=None, help="also time one fp16 MATMUL with fp16 output: N,H,C,W")
     ap.add_argument("--join", default=None,
                     help="also time one fused int8 residual join (RESCALE x2, ADD, RESCALE, CLAMP): N,H,W,C")
     ap.add_argument("--graph-profile", type=int, default=0, metavar="BATCH",
@@ -201,6 +217,10 @@ def main():
         if args.matmul_fp8:
             n, h, c, w = [int(v) for v in args.matmul_fp8.split(",")]
             print(json.dumps(matmul_fp8_config(ctx, timer, "matmul fp8 %s" % args.matmul_fp8, n, h, c, w, args.iters, 13)))
+            sys.stdout.flush()
+        if args.matmul_f16:
+            n, h, c, w = [int(v) for v in args.matmul_f16.split(",")]
+            print(json.dumps(matmul_f16_config(ctx, timer, "matmul fp16 %s" % args.matmul_f16, n, h, c, w, args.iters, 17)))
             sys.stdout.flush()
         if args.join:
             shape = tuple(int(v) for v in args.join.split(","))

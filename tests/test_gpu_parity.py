@@ -627,6 +627,33 @@ def test_matmul_float(ctx, dt, name, shape):
         assert ok, (kernel, info)
 
 
+@pytest.mark.parametrize("dt,name", [(F16, "fp16"), (BF16, "bf16")])
+@pytest.mark.parametrize("shape", [(40, 256, 384, 256), (10, 512, 400, 512), (12, 520, 328, 300), (37, 256, 64, 264)])
+def test_matmul_float_pair_kernel(ctx, dt, name, shape):
+    """fp16 / bf16 shapes with enough 256 x 256 tiles run on the CTA-pair kernel: ragged edges, both output types."""
+    N, H, C, W = shape
+    r = util.rng(1370 + H + W)
+    a = orc.fptrunc(r.standard_normal((N, H, C)).astype(np.float32), name)
+    b = orc.fptrunc(r.standard_normal((N, C, W)).astype(np.float32), name)
+    ref = orc.matmul(a, b, mode="f64", nthreads=16)
+    bnd = orc.matmul(np.abs(a), np.abs(b), mode="f64", nthreads=16)
+
+    def up(x):
+        return ctx.from_numpy(x.astype(np.float16)) if dt == F16 else ctx.from_numpy(util.to_bf16_bits(x), BF16)
+
+    ta, tbb = up(a), up(b)
+    for out_dt, out_name in ((dt, name), (F32, "fp32")):
+        to = ctx.empty(out_dt, (N, H, W))
+        ctx.matmul(ta, tbb, to)
+        assert ctx.last_kernel() == "tc_gemm_pair_f16", ctx.last_kernel()
+        st, out = to.download()
+        out = util.from_bf16_bits(out) if out_dt == BF16 else out.astype(np.float32)
+        ok, info = orc.verify_dot_product(out, ref, bnd, orc.dot_product_ksb(C, "fp32", out_name), out=out_name)
+        assert st == tb.Status.OK and ok, info
+        to.free()
+    _free(ta, tbb)
+
+
 # ------------------------------------------------------------------------------------------- fp8 MATMUL
 def _fp8_codes(r, shape, fmt):
     """Random finite fp8 codes with magnitudes up to about 2 (no NaN / infinity codes, no huge values)."""
