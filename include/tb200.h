@@ -205,8 +205,10 @@ extern "C"
      * OpTransposeConv2d::checkTensorAttributes (:1982-2056).  input NHWC, weight OHWI, bias [OC] or [1];
      * out_pad = {top,bottom,left,right} (each > -kernel), stride = {y,x}; the output must be
      * (IH-1)*stride_y + out_pad_top + out_pad_bottom + KH by the same in x.  Type tuples and the epilogue are
-     * those of tb200_conv2d.  Evaluated as a stride-1 CONV2D over the input spread out by the stride (gaps hold
-     * the input zero point) with the kernel mirrored, so it runs on the same tensor-core kernel. */
+     * those of tb200_conv2d.  Never scatters: the output phases (rows and columns modulo the stride) become column
+     * blocks of one stride-1 CONV2D over the original input, stored straight at their output pixels; shapes that form
+     * cannot take run one stride-1 CONV2D per phase, or a stride-1 CONV2D over the input spread out by the stride
+     * (gaps hold the input zero point) with the kernel mirrored.  All three end in tb200_conv2d's kernels. */
     TB200_API tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tensor* input,
                                                   const tb200_tensor* weight, const tb200_tensor* bias,
                                                   int32_t input_zp, int32_t weight_zp, const int32_t out_pad[4],

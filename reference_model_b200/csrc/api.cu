@@ -1,6 +1,7 @@
 // C-ABI entry points of libtb200: context and tensor management, host-side validation that mirrors the
 // reference's checkTensorAttributes / ERROR_IF rules, and dispatch to the kernels.
 #include <algorithm>
+#include <climits>
 #include <cmath>
 #include <cstdlib>
 #include <new>
@@ -1120,89 +1121,154 @@ extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tenso
     const int sy = stride[0], sx = stride[1];
     tb200_status st;
 
-    // ---- kernel == stride, no out_pad: the stamps tile the output without overlap, so the operator is one GEMM over the
-    // input pixels with (ky, kx, oc) columns, each block of OC columns stored at its own output pixel.
-    if ((sy > 1 || sx > 1) && KH == sy && KW == sx && !out_pad[0] && !out_pad[1] && !out_pad[2] && !out_pad[3] &&
-        OC % 32 == 0 && (int64_t)KH * KW * OC <= 65536)
+    // ---- all phases as column blocks of ONE stride-1 convolution (see embed_phase_operands_kernel): its window covers
+    // the input rows any phase reads for a macro-pixel, each phase's taps sit in it mirrored with zeros elsewhere, and
+    // block (py, px) of a row is stored at output pixel (j*sy + py, i*sx + px).  With kernel == stride and no out_pad
+    // the window is one pixel and nothing is wasted; otherwise zero weights are multiplied too, which the tensor pipe
+    // has room for as long as the window is small against the kernel.
+    if ((sy > 1 || sx > 1) && sy <= PhaseEmbed::kMax && sx <= PhaseEmbed::kMax && OC % 32 == 0 &&
+        (int64_t)sy * sx * OC <= 65536 && (reinterpret_cast<uintptr_t>(output->data) & 31) == 0)
     {
-        const int KK = KH * KW, cols = KK * OC;
-        const bool rs        = epilogue && epilogue->has_rescale && epilogue->rescale.multiplier && epilogue->rescale.shift;
-        const bool rs_per_ch = rs && epilogue->rescale.per_channel && epilogue->rescale.multiplier->shape[0] == OC &&
-                               epilogue->rescale.shift->shape[0] == OC;
-        const size_t bias_es = dtype_size(bias->dtype);
-        const size_t mult_es = rs_per_ch ? dtype_size(epilogue->rescale.multiplier->dtype) : 0;
-        auto up256           = [](size_t v) { return (v + 255) & ~(size_t)255; };
-        const size_t w_off = 0, b_off = up256((size_t)cols * run), m_off = b_off + up256((size_t)cols * bias_es),
-                     s_off = m_off + up256((size_t)cols * mult_es), total = s_off + up256((size_t)cols);
-        tb200_tensor wst = *weight, bst = *bias, mst = {}, sst = {};
-        wst.owns = bst.owns = false;
-        wst.shape[0] = cols; wst.shape[1] = 1; wst.shape[2] = 1;
-        wst.stride[0] = IC; wst.stride[1] = IC; wst.stride[2] = IC;
-        if (bias->shape[0] == OC)
+        struct Axis
         {
-            bst.shape[0] = cols;
-            bst.bytes    = (size_t)cols * bias_es;
-        }
-        tb200_epilogue epi2;
-        if (epilogue)
-            epi2 = *epilogue;
-        if (rs_per_ch)
+            int J, U, pad0, pad1, start, len;
+            bool ok;
+        };
+        PhaseEmbed pe;
+        memset(&pe, 0, sizeof(pe));
+        pe.sy = sy;
+        pe.sx = sx;
+        auto plan_axis = [](int I, int K, int O, int s, int out_pad0, int* k0, int* T, int* sh, int* U_out) {
+            Axis a = {};
+            a.J    = (O + s - 1) / s;
+            int c[PhaseEmbed::kMax];
+            int cmax = INT_MIN;
+            for (int p = 0; p < s; p++)
+            {
+                k0[p] = ((p - out_pad0) % s + s) % s;
+                T[p]  = K > k0[p] ? (K - k0[p] + s - 1) / s : 0;
+                c[p]  = (p - out_pad0 - k0[p]) / s;    // exact by the choice of k0
+                if (T[p] > 0)
+                    cmax = std::max(cmax, c[p]);
+            }
+            if (cmax == INT_MIN)
+                return a;
+            int U = 0;
+            for (int p = 0; p < s; p++)
+            {
+                sh[p] = cmax - c[p];
+                if (T[p] > 0)
+                    U = std::max(U, T[p] + sh[p]);
+            }
+            a.U    = U;
+            a.pad0 = (U - 1) - cmax;
+            if (a.pad0 < 0)
+            {
+                a.start = -a.pad0;
+                a.pad0  = 0;
+            }
+            a.len  = I - a.start;
+            a.pad1 = a.J - a.len - a.pad0 + U - 1;
+            if (a.pad1 < 0)
+            {
+                a.len += a.pad1;
+                a.pad1 = 0;
+            }
+            a.ok   = a.len > 0;
+            *U_out = U;
+            return a;
+        };
+        const Axis ay = plan_axis(IH, KH, OH, sy, out_pad[0], pe.k0y, pe.Ty, pe.shy, &pe.Uy);
+        const Axis ax = plan_axis(IW, KW, OW, sx, out_pad[2], pe.k0x, pe.Tx, pe.shx, &pe.Ux);
+        // multiplied weights against useful ones: 1 for kernel == stride, 2.25 for a 4x4 kernel with stride 2
+        const double waste = ay.ok && ax.ok ? (double)pe.Uy * pe.Ux * sy * sx / ((double)KH * KW) : 1e9;
+        if (ay.ok && ax.ok && waste <= 4.5)
         {
-            mst = *epilogue->rescale.multiplier;
-            sst = *epilogue->rescale.shift;
-            mst.owns = sst.owns = false;
-            mst.shape[0] = sst.shape[0] = cols;
-            mst.bytes                   = (size_t)cols * mult_es;
-            sst.bytes                   = (size_t)cols;
-            epi2.rescale.multiplier     = &mst;
-            epi2.rescale.shift          = &sst;
-        }
-        const int32_t zero[4]  = { 0, 0, 0, 0 };
-        const ConvOutView view = { IH, IW, sy, sx, 0, 0, OC, KW };
-        // the probe only looks at shapes and alignment: the unstaged operands stand in
-        st = conv2d_impl(ctx, input, &wst, &bst, input_zp, weight_zp, zero, one, one, epilogue ? &epi2 : nullptr, output,
-                         &view, true);
-        if (st == TB200_OK)
-        {
-            st = ensure_stage(ctx, total);
-            if (st != TB200_OK)
-                return st;
-            uint8_t* base = reinterpret_cast<uint8_t*>(ctx->stage);
-            const int block  = 256;
+            const int blocks = sy * sx, cols = blocks * OC;
+            const bool rs        = epilogue && epilogue->has_rescale && epilogue->rescale.multiplier && epilogue->rescale.shift;
+            const bool rs_per_ch = rs && epilogue->rescale.per_channel && epilogue->rescale.multiplier->shape[0] == OC &&
+                                   epilogue->rescale.shift->shape[0] == OC;
+            const size_t bias_es = dtype_size(bias->dtype);
+            const size_t mult_es = rs_per_ch ? dtype_size(epilogue->rescale.multiplier->dtype) : 0;
+            auto up256           = [](size_t v) { return (v + 255) & ~(size_t)255; };
+            const size_t w_off = 0, b_off = up256((size_t)cols * pe.Uy * pe.Ux * run),
+                         m_off = b_off + up256((size_t)cols * bias_es), s_off = m_off + up256((size_t)cols * mult_es),
+                         total = s_off + up256((size_t)cols);
+            tb200_tensor xin = *input, wst = *weight, bst = *bias, mst = {}, sst = {};
+            xin.owns = wst.owns = bst.owns = false;
+            xin.data       = reinterpret_cast<uint8_t*>(input->data) + ((size_t)ay.start * IW + ax.start) * run;
+            xin.shape[1]   = ay.len;
+            xin.shape[2]   = ax.len;
+            xin.contiguous = ay.len == IH && ax.len == IW;
+            wst.shape[0] = cols; wst.shape[1] = pe.Uy; wst.shape[2] = pe.Ux;
+            wst.stride[2] = IC; wst.stride[1] = (int64_t)pe.Ux * IC; wst.stride[0] = (int64_t)pe.Uy * pe.Ux * IC;
+            wst.bytes     = (size_t)cols * pe.Uy * pe.Ux * run;
             const bool rep_b = bias->shape[0] == OC;
-            const void* b_in = rep_b ? bias->data : nullptr;
-            const void* m_in = rs_per_ch ? epilogue->rescale.multiplier->data : nullptr;
-            const uint8_t* s_in = rs_per_ch ? reinterpret_cast<const uint8_t*>(epilogue->rescale.shift->data) : nullptr;
-            if (vec)
-                stamp_operands_kernel<uint4><<<grid_for(ctx, (int64_t)cols * (run / 16), block), block, 0, ctx->stream>>>(
-                    reinterpret_cast<const uint4*>(weight->data), reinterpret_cast<uint4*>(base + w_off), OC, KK,
-                    (int)(run / 16), b_in, base + b_off, (int)bias_es, m_in, base + m_off, (int)mult_es, s_in, base + s_off);
-            else if (es == 1)
-                stamp_operands_kernel<uint8_t><<<grid_for(ctx, (int64_t)cols * IC, block), block, 0, ctx->stream>>>(
-                    reinterpret_cast<const uint8_t*>(weight->data), base + w_off, OC, KK, IC, b_in, base + b_off, (int)bias_es,
-                    m_in, base + m_off, (int)mult_es, s_in, base + s_off);
-            else
-                stamp_operands_kernel<uint16_t><<<grid_for(ctx, (int64_t)cols * IC, block), block, 0, ctx->stream>>>(
-                    reinterpret_cast<const uint16_t*>(weight->data), reinterpret_cast<uint16_t*>(base + w_off), OC, KK, IC, b_in,
-                    base + b_off, (int)bias_es, m_in, base + m_off, (int)mult_es, s_in, base + s_off);
-            wst.data = base + w_off;
             if (rep_b)
-                bst.data = base + b_off;
+            {
+                bst.shape[0] = cols;
+                bst.bytes    = (size_t)cols * bias_es;
+            }
+            tb200_epilogue epi2;
+            if (epilogue)
+                epi2 = *epilogue;
             if (rs_per_ch)
             {
-                mst.data = base + m_off;
-                sst.data = base + s_off;
+                mst = *epilogue->rescale.multiplier;
+                sst = *epilogue->rescale.shift;
+                mst.owns = sst.owns = false;
+                mst.shape[0] = sst.shape[0] = cols;
+                mst.bytes                   = (size_t)cols * mult_es;
+                sst.bytes                   = (size_t)cols;
+                epi2.rescale.multiplier     = &mst;
+                epi2.rescale.shift          = &sst;
             }
-            const int launches = 1;
-            st = post_launch(ctx, "transpose_conv_stamp_operands", launches);
-            if (st != TB200_OK)
+            const int32_t pad[4]   = { ay.pad0, ay.pad1, ax.pad0, ax.pad1 };
+            const ConvOutView view = { ay.J, ax.J, sy, sx, 0, 0, OC, sx };
+            // the probe only looks at shapes and alignment: the unstaged operands stand in
+            st = conv2d_impl(ctx, &xin, &wst, &bst, input_zp, weight_zp, pad, one, one, epilogue ? &epi2 : nullptr, output,
+                             &view, true);
+            if (st == TB200_OK)
+            {
+                st = ensure_stage(ctx, total);
+                if (st != TB200_OK)
+                    return st;
+                uint8_t* base    = reinterpret_cast<uint8_t*>(ctx->stage);
+                const int block  = 256;
+                const void* b_in = rep_b ? bias->data : nullptr;
+                const void* m_in = rs_per_ch ? epilogue->rescale.multiplier->data : nullptr;
+                const uint8_t* s_in = rs_per_ch ? reinterpret_cast<const uint8_t*>(epilogue->rescale.shift->data) : nullptr;
+                const int64_t wunits = (int64_t)cols * pe.Uy * pe.Ux;
+                if (vec)
+                    embed_phase_operands_kernel<uint4><<<grid_for(ctx, wunits * (int64_t)(run / 16), block), block, 0, ctx->stream>>>(
+                        reinterpret_cast<const uint4*>(weight->data), reinterpret_cast<uint4*>(base + w_off), OC, KH, KW,
+                        (int)(run / 16), pe, b_in, base + b_off, (int)bias_es, m_in, base + m_off, (int)mult_es, s_in, base + s_off);
+                else if (es == 1)
+                    embed_phase_operands_kernel<uint8_t><<<grid_for(ctx, wunits * IC, block), block, 0, ctx->stream>>>(
+                        reinterpret_cast<const uint8_t*>(weight->data), base + w_off, OC, KH, KW, IC, pe, b_in, base + b_off,
+                        (int)bias_es, m_in, base + m_off, (int)mult_es, s_in, base + s_off);
+                else
+                    embed_phase_operands_kernel<uint16_t><<<grid_for(ctx, wunits * IC, block), block, 0, ctx->stream>>>(
+                        reinterpret_cast<const uint16_t*>(weight->data), reinterpret_cast<uint16_t*>(base + w_off), OC, KH, KW,
+                        IC, pe, b_in, base + b_off, (int)bias_es, m_in, base + m_off, (int)mult_es, s_in, base + s_off);
+                wst.data = base + w_off;
+                if (rep_b)
+                    bst.data = base + b_off;
+                if (rs_per_ch)
+                {
+                    mst.data = base + m_off;
+                    sst.data = base + s_off;
+                }
+                st = post_launch(ctx, "transpose_conv_embed_operands", 1);
+                if (st != TB200_OK)
+                    return st;
+                st = conv2d_impl(ctx, &xin, &wst, &bst, input_zp, weight_zp, pad, one, one, epilogue ? &epi2 : nullptr, output,
+                                 &view, false);
+                return st == kNeedsDenseOutput ? fail(ctx, TB200_INTERNAL, "OpTransposeConv2d: plan changed") : st;
+            }
+            if (st != kNeedsDenseOutput)
                 return st;
-            st = conv2d_impl(ctx, input, &wst, &bst, input_zp, weight_zp, zero, one, one, epilogue ? &epi2 : nullptr, output,
-                             &view, false);
-            return st == kNeedsDenseOutput ? fail(ctx, TB200_INTERNAL, "OpTransposeConv2d: stamp plan changed") : st;
         }
-        if (st != kNeedsDenseOutput)
-            return st;
     }
 
     // ---- strided: one stride-1 convolution per output phase, each over the original input with the taps that reach

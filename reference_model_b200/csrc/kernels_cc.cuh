@@ -1366,26 +1366,48 @@ __global__ void mirror_phase_weights_kernel(const U* __restrict__ in, U* __restr
     }
 }
 
-// TRANSPOSE_CONV2D with kernel == stride and no out_pad: stamps do not overlap, so the operator is one GEMM whose
-// columns are (ky, kx, oc).  One launch prepares its operands: weights OHWI -> rows ((ky*KW + kx)*OC + oc) of IC
-// channels each, and the per-channel vectors (bias, RESCALE multiplier and shift; null = absent) repeated for every
-// (ky, kx) block of columns.  Vector elements are copied as raw 1-, 2- or 4-byte words.
-template <typename U>
-__global__ void stamp_operands_kernel(const U* __restrict__ w, U* __restrict__ w_out, int OC, int KK, int units,
-                                      const void* __restrict__ bias, void* __restrict__ bias_out, int bias_es,
-                                      const void* __restrict__ mult, void* __restrict__ mult_out, int mult_es,
-                                      const uint8_t* __restrict__ shift, uint8_t* __restrict__ shift_out)
+// TRANSPOSE_CONV2D as ONE stride-1 convolution whose output columns are (py, px, oc): phase (py, px) of the output
+// (rows py mod sy, columns px mod sx) reads, for macro-pixel (j, i), the input rows j + c_py - t with tap
+// k0_py + sy*t.  Over all phases these rows lie in one window of U rows ending at j + cmax, so every phase's taps are
+// embedded (mirrored, zero elsewhere) in a U_y x U_x kernel and the phases become column blocks of one GEMM.  One
+// launch prepares its operands: the embedded weights [(py*sx + px)*OC + oc][U_y][U_x][IC] and the per-channel vectors
+// (bias, RESCALE multiplier and shift; null = absent) repeated per block, copied as raw 1-, 2- or 4-byte words.
+struct PhaseEmbed
 {
-    const int64_t total = (int64_t)OC * KK * units;
+    enum { kMax = 8 };               // phases per axis
+    int sy, sx, Uy, Ux;
+    int k0y[kMax], Ty[kMax], shy[kMax];    // first tap, tap count, window shift (cmax - c) of every y phase
+    int k0x[kMax], Tx[kMax], shx[kMax];
+};
+
+template <typename U>
+__global__ void embed_phase_operands_kernel(const U* __restrict__ w, U* __restrict__ w_out, int OC, int KH, int KW, int units,
+                                            const __grid_constant__ PhaseEmbed e, const void* __restrict__ bias,
+                                            void* __restrict__ bias_out, int bias_es, const void* __restrict__ mult,
+                                            void* __restrict__ mult_out, int mult_es, const uint8_t* __restrict__ shift,
+                                            uint8_t* __restrict__ shift_out)
+{
+    const int blocks    = e.sy * e.sx;
+    const int64_t total = (int64_t)blocks * OC * e.Uy * e.Ux * units;
     const int64_t step  = (int64_t)gridDim.x * blockDim.x;
     const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     for (int64_t i = first; i < total; i += step)
     {
         const int u  = (int)(i % units);
         int64_t r    = i / units;
+        const int ux = e.Ux - 1 - (int)(r % e.Ux);    // stored mirrored: the convolution walks the window forwards
+        r /= e.Ux;
+        const int uy = e.Uy - 1 - (int)(r % e.Uy);
+        r /= e.Uy;
         const int oc = (int)(r % OC);
-        const int kk = (int)(r / OC);
-        w_out[i]     = w[((int64_t)oc * KK + kk) * units + u];
+        const int b  = (int)(r / OC);
+        const int py = b / e.sx, px = b - py * e.sx;
+        const int ty = uy - e.shy[py], tx = ux - e.shx[px];
+        U v;
+        memset(&v, 0, sizeof(U));
+        if (ty >= 0 && ty < e.Ty[py] && tx >= 0 && tx < e.Tx[px])
+            v = w[(((int64_t)oc * KH + e.k0y[py] + e.sy * ty) * KW + e.k0x[px] + e.sx * tx) * units + u];
+        w_out[i] = v;
     }
     auto copy_word = [](const void* src, void* dst, int es, int from, int to) {
         if (es == 4)
@@ -1395,7 +1417,7 @@ __global__ void stamp_operands_kernel(const U* __restrict__ w, U* __restrict__ w
         else
             reinterpret_cast<uint8_t*>(dst)[to] = reinterpret_cast<const uint8_t*>(src)[from];
     };
-    for (int64_t c = first; c < (int64_t)OC * KK; c += step)
+    for (int64_t c = first; c < (int64_t)OC * blocks; c += step)
     {
         const int oc = (int)(c % OC);
         if (bias != nullptr)

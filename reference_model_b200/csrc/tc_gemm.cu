@@ -554,6 +554,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                 const int nvalid = min(32, p.OC - col);
                 // element offset of (this row, col) in the output, and of the neighbouring lane's row
                 int64_t ooff = pix * p.OC + col, ooff_pair = pix_pair * p.OC + col;
+                bool rv = row_valid, rv_pair = row_valid_pair;    // validity of this row's (and the neighbour lane's) store
                 if (p.d2s_oc != 0)
                 {
                     // columns are (ky, kx, oc): a block of d2s_oc channels per output pixel of the stamp
@@ -561,6 +562,10 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     const int64_t within = ((int64_t)ky * p.out_OW + kx) * p.d2s_oc + (col - ph * p.d2s_oc);
                     ooff      = pix * p.d2s_oc + within;
                     ooff_pair = pix_pair * p.d2s_oc + within;
+                    // the last macro-pixel of a row or column may reach past the output (odd sizes, cropping out_pad)
+                    const bool inside = (py * p.out_sy + ky < p.out_OH) && (px * p.out_sx + kx < p.out_OW);
+                    rv            = rv && inside;
+                    rv_pair       = false;    // such outputs are 32-byte aligned: the paired-lane store form is never taken
                 }
 
                 if (EPI != TC_EPI_FLOAT && corr_row != nullptr && !(p.debug & 16))
@@ -583,7 +588,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
 #pragma unroll
                     for (int i = 0; i < 32; i++)
                         v[i] += (uint32_t)rc;
-                    if (row_valid)
+                    if (rv)
                     {
                         int32_t* o = reinterpret_cast<int32_t*>(p.out) + ooff;
                         if (nvalid == 32 && ((p.OC & 7) == 0) && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0)
@@ -654,7 +659,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                             for (int q = 0; q < 8; q++)
                                 w[q] = rescale32_high_x4<false>(&v[4 * q], &epi_cols[c * 32 + 4 * q]);
                         }
-                        if (bad && row_valid)
+                        if (bad && rv)
                             dev_flags |= TB200_DEV_UNPREDICTABLE;
                         // a CLAMP narrower than int8 (rare) works on the packed bytes
                         if (p.clamp_lo > -128 || p.clamp_hi < 127)
@@ -672,7 +677,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         const bool skip = (p.debug & 32) && w[0] != 0x12345678u;
                         if ((reinterpret_cast<uintptr_t>(p.out) & 31) == 0)
                         {
-                            if (row_valid && !skip)
+                            if (rv && !skip)
                                 ptx::st_global_v8(reinterpret_cast<int8_t*>(p.out) + ooff, w[0], w[1], w[2], w[3],
                                                   w[4], w[5], w[6], w[7]);
                         }
@@ -687,9 +692,9 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                             int8_t* o_pair = reinterpret_cast<int8_t*>(p.out) + ooff_pair + (odd ? 16 : 0);
                             const uint4 mine   = odd ? make_uint4(w[4], w[5], w[6], w[7]) : make_uint4(w[0], w[1], w[2], w[3]);
                             const uint4 theirs = make_uint4(other[0], other[1], other[2], other[3]);
-                            if ((odd ? row_valid_pair : row_valid) && !skip)
+                            if ((odd ? rv_pair : rv) && !skip)
                                 *reinterpret_cast<uint4*>(odd ? o_pair : o_own) = odd ? theirs : mine;
-                            if ((odd ? row_valid : row_valid_pair) && !skip)
+                            if ((odd ? rv : rv_pair) && !skip)
                                 *reinterpret_cast<uint4*>(odd ? o_own : o_pair) = odd ? mine : theirs;
                         }
                         continue;
@@ -738,7 +743,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         v[i] = (uint32_t)z;
                     }
 
-                    if (row_valid)
+                    if (rv)
                     {
                         if (p.out_es == 1)
                         {
@@ -778,7 +783,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         }
                     }
 
-                    if (bad && row_valid)
+                    if (bad && rv)
                         dev_flags |= TB200_DEV_UNPREDICTABLE;
                 }
                 else
@@ -810,7 +815,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                             f[i] = (f[i] > p.clamp_hi_f) ? p.clamp_hi_f : f[i];
                         }
                     }
-                    if (!row_valid)
+                    if (!rv)
                         continue;
                     if (p.out_es == 4)
                     {

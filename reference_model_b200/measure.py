@@ -107,8 +107,16 @@ def tconv_i8_config(ctx, timer, name, N, IH, IW, IC, OC, K, stride, out_pad, izp
     fn = lambda: ctx.transpose_conv2d(tx, tw, tbias, to, [out_pad] * 4, [stride, stride], izp, 0, epi)
     nbytes = x.nbytes + w.nbytes + N * OH * OW * OC
     ms, note = timer.time(fn, iters, nbytes)
+    # device time of the tensor-core launches alone (all phases of one call), warm L2, against the whole call
+    ctx.timer_enable(True)
+    ctx.timer_read()
+    for _ in range(5):
+        fn()
+    kms, kn = ctx.timer_read()
+    ctx.timer_enable(False)
     ops = 2.0 * N * IH * IW * OC * K * K * IC
-    return {"config": name, "kernel": ctx.last_kernel(), "ms": ms, "TOPS": ops / ms / 1e9, "GBps": nbytes / ms / 1e6,
+    return {"config": name, "kernel": ctx.last_kernel(), "ms": ms, "gemm_launches_per_call": kn // 5 if kn else None,
+            "gemm_ms_per_call_warm_l2": (kms / 5) if kn else None, "TOPS": ops / ms / 1e9, "GBps": nbytes / ms / 1e6,
             "algorithmic_ops": ops, "algorithmic_bytes": nbytes, "l2": note}
 
 

@@ -872,6 +872,9 @@ TCONV_I8_CASES = [
     (1, 7, 5, 32, 32, 3, 2, (3, 2), (1, 0, 0, 2), 0, 0),           # rows of the output that no stamp reaches
     (1, 6, 6, 32, 40, 1, 2, (2, 3), (0, 0, 0, 0), 9, 0),           # kernel smaller than the stride: bias-only phases
     (3, 7, 5, 32, 96, 3, 2, (3, 2), (0, 0, 0, 0), -3, 0),          # kernel == stride, not square: one GEMM, 6 stamps
+    (2, 7, 9, 64, 64, 3, 3, (2, 2), (0, 0, 0, 0), -128, 0),        # odd output size: the last macro-pixel is half outside
+    (1, 10, 10, 32, 32, 4, 4, (2, 2), (-1, -1, -1, -1), 11, 0),    # 4x4 stride 2, cropped: phases as column blocks
+    (2, 5, 6, 32, 64, 5, 3, (3, 2), (2, -1, -2, 3), -9, 0),        # window of 2-3 rows, extension and crop mixed
     (3, 5, 9, 96, 24, 5, 3, (2, 2), (-4, 3, -2, -2), -77, 0),      # deep crop on one side, extension on the other
     (1, 7, 5, 16, 32, 3, 2, (3, 2), (1, 0, 0, 2), 0, 0),           # 16-byte channel run: CUDA cores
     (1, 5, 6, 7, 3, 3, 2, (2, 3), (0, 1, -1, 0), -5, 3),           # odd channels + weight zero point: CUDA cores
@@ -915,9 +918,10 @@ def test_transpose_conv_int8_random_shapes(ctx):
     """Seeded random kernel sizes, strides and out_pads (crops and extensions) on the tensor-core path."""
     r = util.rng(977)
     done = 0
-    while done < 24:
+    while done < 40:
         N, IH, IW = int(r.integers(1, 4)), int(r.integers(1, 12)), int(r.integers(1, 12))
-        IC, OC = int(r.choice([32, 64, 160])), int(r.integers(1, 80))
+        IC = int(r.choice([32, 64, 160]))
+        OC = int(r.choice([32, 64, 96])) if done % 2 == 0 else int(r.integers(1, 80))    # column-block form / phases
         KH, KW = int(r.integers(1, 6)), int(r.integers(1, 6))
         stride = (int(r.integers(1, 4)), int(r.integers(1, 4)))
         out_pad = [int(r.integers(-KH + 1, 4)), int(r.integers(-KH + 1, 4)), int(r.integers(-KW + 1, 4)),
