@@ -94,6 +94,10 @@ __device__ __forceinline__ PairTile decode_pair_tile(const PairParams& p, int ti
     return t;
 }
 
+// KIND selects the operand type at compile time, so that each instantiation carries only its own MMA, tile geometry
+// and epilogue: 0 = int8 (kind::i8, int32 output with zero-point corrections), 1 = fp8 (kind::f8f6f4), 2 = fp16 / bf16
+// (kind::f16); the floating kinds store fp32 accumulators as fp32, fp16 or bf16 (p.out_kind).
+template <int KIND>
 __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __grid_constant__ PairParams p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -192,10 +196,19 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                         for (int j = 0; j < nch; j++)
                         {
                             ptx::tma_load_3d_pair(sA + (uint32_t)(j * kPairChunkBytes), &p.tmA, full_first, k, m0, t.n);
-                            for (int bx = 0; bx < p.b_boxes; bx++)
-                                ptx::tma_load_3d_pair(sB + (uint32_t)(j * kPairChunkBytes + bx * p.b_box_bytes), &p.tmB, full_first,
-                                                      w0 + bx * p.b_box_cols, k, t.n);
-                            k += p.chunk_elems;
+                            if (KIND == 2)
+                            {
+                                // halves: the CTA's 128 columns are two 64-column swizzle atoms of 64 K rows each
+                                ptx::tma_load_3d_pair(sB + (uint32_t)(j * kPairChunkBytes), &p.tmB, full_first, w0, k, t.n);
+                                ptx::tma_load_3d_pair(sB + (uint32_t)(j * kPairChunkBytes + 8192), &p.tmB, full_first, w0 + 64, k,
+                                                      t.n);
+                                k += 64;
+                            }
+                            else
+                            {
+                                ptx::tma_load_3d_pair(sB + (uint32_t)(j * kPairChunkBytes), &p.tmB, full_first, w0, k, t.n);
+                                k += 128;
+                            }
                         }
                     }
                     if (++stage == p.num_stages)
@@ -260,15 +273,15 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
 #pragma unroll
                             for (int m = 0; m < 4; m++)
                             {
-                                if (p.mma_kind == 2)
+                                if (KIND == 2)
                                     ptx::mma_f16_ss_pair(d_tmem, ad, bd, p.idesc, accum);
-                                else if (p.mma_kind == 1)
+                                else if (KIND == 1)
                                     ptx::mma_f8_ss_pair(d_tmem, ad, bd, p.idesc, accum);
                                 else
                                     ptx::mma_i8_ss_pair(d_tmem, ad, bd, p.idesc, accum);
                                 accum = 1;
-                                ad += 2;              // 32 bytes of K inside the swizzled row
-                                bd += p.b_kstep16;    // the MMA's K rows of 128 bytes (32 rows of bytes, 16 rows of halves)
+                                ad += 2;                         // 32 bytes of K inside the swizzled row
+                                bd += (KIND == 2) ? 128 : 256;    // the MMA's K rows of 128 bytes: 16 rows of halves, 32 of bytes
                             }
                         }
                     }
@@ -588,9 +601,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                 const int col = t.w0 + c * 32;
                 if (col >= p.W || (p.debug & 1))
                     continue;
-                if (p.out_kind != 0)
+                if (KIND != 0)
                 {
-                    // fp32 accumulators of fp8 operands: stored as they are, or rounded once to fp16
+                    // fp32 accumulators of floating operands: stored as they are, or rounded once to fp16 / bf16
                     if (!row_valid)
                         continue;
                     const int nvalid = min(32, p.W - col);
@@ -868,7 +881,8 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     k.stage_bytes = 2 * k.ksub * kPairChunkBytes;
     k.num_stages  = std::min(kPairMaxStages, std::max(2, pair_env_int("TB200_PAIR_STAGES", (224 * 1024) / k.stage_bytes)));
     const int smem_bytes = k.num_stages * k.stage_bytes + 1024;
-    TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(tc_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    void (*kern)(const PairParams) = f16 ? tc_gemm_pair_kernel<2> : f8 ? tc_gemm_pair_kernel<1> : tc_gemm_pair_kernel<0>;
+    TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim         = dim3(kPairThreads);
     cfg.dynamicSmemBytes = (size_t)smem_bytes;
@@ -882,12 +896,13 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     cfg.numAttrs = 1;
     // Tiles wait for sums that other pairs publish, so every pair of the grid has to be resident at once: never more
     // pairs than the device can hold of this kernel (asked once; one CTA per SM because of its shared memory).
-    static int max_pairs = 0;
+    static int max_pairs_of[3] = { 0, 0, 0 };
+    int& max_pairs = max_pairs_of[k.mma_kind];
     if (max_pairs == 0)
     {
         cfg.gridDim = dim3((unsigned)(2 * (ctx->num_sms / 2)));
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, tc_gemm_pair_kernel, &cfg) != cudaSuccess || n <= 0)
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0)
         {
             cudaGetLastError();
             n = ctx->num_sms / 2;
@@ -897,7 +912,7 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     const int clusters = std::max(1, std::min(k.num_tiles, std::min(max_pairs, ctx->num_sms / 2)));
     cfg.gridDim        = dim3((unsigned)(2 * clusters));
     timer_begin(ctx);
-    const cudaError_t le = cudaLaunchKernelEx(&cfg, tc_gemm_pair_kernel, k);
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, k);
     timer_end(ctx);
     if (le != cudaSuccess)
         return fail(ctx, TB200_INTERNAL, "launch of the CTA-pair MATMUL kernel failed: %s", cudaGetErrorString(le));
