@@ -102,13 +102,48 @@ extern "C"
      * (reference_model/src/subgraph_traverser.cpp:1190-1202); on the device the same sequence of operator calls can
      * be recorded once into a CUDA graph and replayed with a single launch.  Between tb200_capture_begin and
      * tb200_capture_end the operator entry points enqueue nothing for execution, they only record; no call may
-     * need to grow the context's scratch memory (run the sequence once eagerly first), and uploads / downloads /
-     * tb200_sync are not allowed.  Operands must stay allocated for as long as the graph is replayed. */
+     * need to grow the context's scratch memory or build a cache entry (run the sequence once eagerly first), and
+     * uploads / downloads / tb200_sync are not allowed.  Operands must stay allocated for as long as the graph is
+     * replayed.  A graph records the addresses of the context's internal blocks (scratch, staging, cached tables):
+     * while any graph of a context is alive, a block that a later eager call has to grow or drop is not freed but
+     * parked until the last graph is destroyed, so a replay never touches freed memory.  Constants changed through
+     * tb200_tensor_upload are picked up by a replay (the tables derived from them are rebuilt in place behind the
+     * copy). */
     typedef struct tb200_graph tb200_graph;
     TB200_API tb200_status tb200_capture_begin(tb200_ctx* ctx);
     TB200_API tb200_status tb200_capture_end(tb200_ctx* ctx, tb200_graph** out);
     TB200_API tb200_status tb200_graph_launch(tb200_ctx* ctx, tb200_graph* graph);
     TB200_API tb200_status tb200_graph_destroy(tb200_ctx* ctx, tb200_graph* graph);
+
+    /* Every wait a kernel makes on its own pipeline (TMA arrival, accumulator hand-over, zero-point sums published by
+     * another CTA) gives up after `sm_cycles` SM clock cycles, about two seconds by default: the kernel then drains,
+     * frees its tensor memory and exits, its output is incomplete, and the next tb200_sync / download reports
+     * TB200_INTERNAL.  The context stays usable.  No counterpart in the reference (a host interpreter cannot stall on
+     * a device pipeline); the setter exists so that a host can bound its worst case and so that the give-up path can
+     * be exercised. */
+    TB200_API tb200_status tb200_set_wait_limit(tb200_ctx* ctx, uint64_t sm_cycles);
+    /* shared != 0: other work may occupy SMs of this GPU while the context runs.  Kernels then never wait for another
+     * CTA of their own grid: the CTA-pair MATMUL takes its zero-point sums from separate kernels instead of exchanging
+     * them between tiles through flags (which needs the whole grid resident at once, true on a GPU the context has to
+     * itself, the default). */
+    TB200_API tb200_status tb200_set_shared_gpu(tb200_ctx* ctx, int32_t shared);
+
+    /* Constant-operand cache.  The reference decodes a graph's constants once
+     * (reference_model/src/subgraph_traverser.cpp:617-781); here everything an operator derives from constants alone
+     * (zero-point correction rows, per-channel RESCALE records, re-packed weights of few-channel layers, the byte-pair
+     * table of a residual join) is built on the first call that sees those operands and reused afterwards, keyed by the
+     * operands' device addresses and the attributes.  tb200_tensor_upload / tb200_tensor_load_npy into an operand
+     * rebuild what was derived from it; an operator writing into an operand makes its entries rebuild on every use;
+     * tb200_tensor_free drops them.  Memory handed over with tb200_tensor_wrap and then modified by the caller behind
+     * the library's back is the one case that needs TB200_CACHE_CLEAR. */
+    typedef enum tb200_cache_action
+    {
+        TB200_CACHE_OFF   = 0, /* drop every entry and build nothing new: every call recomputes its tables */
+        TB200_CACHE_ON    = 1, /* the default */
+        TB200_CACHE_CLEAR = 2  /* drop every entry, stay on */
+    } tb200_cache_action;
+    TB200_API tb200_status tb200_const_cache_control(tb200_ctx* ctx, int32_t action);
+    TB200_API int32_t tb200_const_cache_entries(const tb200_ctx* ctx);
 
     /* ---- tensors -------------------------------------------------------------------------------
      * Device-resident replacements for TensorTemplate<Eigen::Tensor<T,R>> buffers
@@ -263,6 +298,27 @@ extern "C"
                                              const void* a, const void* b, int32_t N, int32_t H, int32_t C,
                                              int32_t W, int32_t a_zp, int32_t b_zp, void* out);
 
+    /* ---- several GPUs ---------------------------------------------------------------------------
+     * The operators of this path are independent across the batch dimension (reference_model/src/ops/tensor_ops.cpp:828,
+     * :1283, :1454-1483 index N only on the output side), so a graph is split by giving every GPU its own process,
+     * context and slice of the batch; the one exchange is the gather of the output shards.  The reference itself is a
+     * single-process interpreter and has no counterpart.  NCCL is looked up at run time (libnccl.so.2 already in the
+     * process, else from the loader path); without it these calls return TB200_INTERNAL and nothing else is affected.
+     *  - tb200_comm_unique_id: rank 0 calls it and hands the 128 bytes to the other ranks by any means the host has.
+     *  - tb200_comm_init: collective over all ranks; creates the context's communicator on the context's device.
+     *  - tb200_comm_attach: uses a communicator (ncclComm_t) the host already has instead; the host keeps ownership.
+     *  - tb200_gather_output: all ranks call it with their shard; `gathered` receives the shards in rank order along
+     *    the shard's outermost dimension larger than one (every other dimension equal), on the context's stream.  With
+     *    one rank (no communicator) it is a device copy. */
+#define TB200_COMM_ID_BYTES 128
+    TB200_API tb200_status tb200_comm_unique_id(char id_out[TB200_COMM_ID_BYTES]);
+    TB200_API tb200_status tb200_comm_init(tb200_ctx* ctx, const char id[TB200_COMM_ID_BYTES], int32_t rank, int32_t nranks);
+    TB200_API tb200_status tb200_comm_attach(tb200_ctx* ctx, void* nccl_comm);
+    TB200_API tb200_status tb200_comm_destroy(tb200_ctx* ctx);
+    TB200_API int32_t tb200_comm_rank(const tb200_ctx* ctx);
+    TB200_API int32_t tb200_comm_size(const tb200_ctx* ctx);
+    TB200_API tb200_status tb200_gather_output(tb200_ctx* ctx, const tb200_tensor* shard, tb200_tensor* gathered);
+
     /* Largest N*(H + W rounded up to a multiple of 256) the built-in scratch of tb200_matmul_i8_noalloc holds
      * (int32 entries, 1 MiB in total). */
 #define TB200_NOALLOC_MAX_SUMS 262144
@@ -276,8 +332,8 @@ extern "C"
      * cudaMalloc; this variant keeps them in a fixed array inside the library image instead, which every GPU that
      * loads the library holds until the process exits (1 MiB + 256 bytes).
      *
-     *  - Limit: N*(H + roundup(W, 256)) <= TB200_NOALLOC_MAX_SUMS, otherwise TB200_ERROR with a message naming
-     *    the limit.
+     *  - Limit: roundup(N*H, 4) + N*roundup(W, 256) <= TB200_NOALLOC_MAX_SUMS, otherwise TB200_ERROR with a message
+     *    naming the limit.
      *  - The CUDA device that owns the pointers must be current.  The first call on each device looks up the
      *    device address of the built-in array (a one-time set-up); make that first call outside any stream
      *    capture.  No call invokes cudaMalloc, cudaFree or any allocating library routine.
@@ -286,7 +342,10 @@ extern "C"
      *    whose kernels overlap on the GPU (different streams without ordering) race on it: order them.
      *  - a, b, out: 16-byte aligned device pointers, row-major.  `stream` is a cudaStream_t (NULL = default).
      *    Work is enqueued on `stream`; with synchronize != 0 the call also waits for it and reports a kernel
-     *    that gave up on its pipeline as TB200_INTERNAL.  `err` (may be NULL) receives a message on failure. */
+     *    that gave up on its pipeline as TB200_INTERNAL.  With synchronize == 0 nobody reads the device status
+     *    word (the next call clears it): a caller that needs to know about a kernel that gave up passes
+     *    synchronize != 0, which is refused with TB200_ERROR while `stream` is being captured (a synchronisation
+     *    would invalidate the capture).  `err` (may be NULL) receives a message on failure. */
     TB200_API tb200_status tb200_matmul_i8_noalloc(void* stream, const int8_t* a, const int8_t* b, int32_t* out,
                                                    int32_t N, int32_t H, int32_t C, int32_t W, int32_t a_zp,
                                                    int32_t b_zp, int32_t synchronize, char* err, size_t err_len);

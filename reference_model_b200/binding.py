@@ -76,6 +76,9 @@ EXPORTS = [
     "tb200_rescale", "tb200_clamp", "tb200_add", "tb200_residual_add", "tb200_max_pool2d", "tb200_avg_pool2d",
     "tb200_matmul_host", "tb200_set_kernel_policy", "tb200_last_kernel", "tb200_matmul_i8_noalloc",
     "tb200_npy_probe", "tb200_tensor_load_npy", "tb200_tensor_save_npy",
+    "tb200_set_wait_limit", "tb200_set_shared_gpu", "tb200_const_cache_control", "tb200_const_cache_entries",
+    "tb200_comm_unique_id", "tb200_comm_init", "tb200_comm_attach", "tb200_comm_destroy", "tb200_comm_rank",
+    "tb200_comm_size", "tb200_gather_output",
 ]
 
 
@@ -131,6 +134,17 @@ def load_library():
         "tb200_tensor_save_npy": (i32, [vp, vp, cp]),
         "tb200_set_kernel_policy": (ctypes.c_int, [vp, ctypes.c_int]),
         "tb200_last_kernel": (cp, [vp]),
+        "tb200_set_wait_limit": (i32, [vp, ctypes.c_uint64]),
+        "tb200_set_shared_gpu": (i32, [vp, i32]),
+        "tb200_const_cache_control": (i32, [vp, i32]),
+        "tb200_const_cache_entries": (i32, [vp]),
+        "tb200_comm_unique_id": (i32, [ctypes.c_char_p]),
+        "tb200_comm_init": (i32, [vp, ctypes.c_char_p, i32, i32]),
+        "tb200_comm_attach": (i32, [vp, vp]),
+        "tb200_comm_destroy": (i32, [vp]),
+        "tb200_comm_rank": (i32, [vp]),
+        "tb200_comm_size": (i32, [vp]),
+        "tb200_gather_output": (i32, [vp, vp, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -156,6 +170,7 @@ def _ivec(v):
 
 
 NOALLOC_MAX_SUMS = 262144   # TB200_NOALLOC_MAX_SUMS
+COMM_ID_BYTES = 128         # TB200_COMM_ID_BYTES
 
 
 def matmul_i8_noalloc(a_ptr, b_ptr, out_ptr, N, H, C, W, a_zp=0, b_zp=0, stream=None, synchronize=True):
@@ -311,6 +326,44 @@ class Context:
 
     def set_kernel_policy(self, policy):
         return self.lib.tb200_set_kernel_policy(self.handle, int(policy))
+
+    def set_wait_limit(self, sm_cycles):
+        """SM clock cycles after which a kernel's pipeline wait gives up (default about two seconds)."""
+        return self._check(self.lib.tb200_set_wait_limit(self.handle, int(sm_cycles)))
+
+    def set_shared_gpu(self, shared=True):
+        return self._check(self.lib.tb200_set_shared_gpu(self.handle, int(bool(shared))))
+
+    CACHE_OFF, CACHE_ON, CACHE_CLEAR = 0, 1, 2
+
+    def const_cache_control(self, action):
+        return self._check(self.lib.tb200_const_cache_control(self.handle, int(action)))
+
+    def const_cache_entries(self):
+        return int(self.lib.tb200_const_cache_entries(self.handle))
+
+    # ---- several GPUs: one context per process and GPU, the output shards gathered in rank order
+    @staticmethod
+    def comm_unique_id():
+        """128 bytes that rank 0 creates and every rank passes to comm_init."""
+        buf = ctypes.create_string_buffer(COMM_ID_BYTES)
+        st = load_library().tb200_comm_unique_id(buf)
+        if st != 0:
+            raise Tb200Error(st, "tb200_comm_unique_id failed (is NCCL loadable?)")
+        return buf.raw
+
+    def comm_init(self, unique_id, rank, nranks):
+        return self._check(self.lib.tb200_comm_init(self.handle, ctypes.create_string_buffer(bytes(unique_id), COMM_ID_BYTES),
+                                                    int(rank), int(nranks)))
+
+    def comm_destroy(self):
+        return self._check(self.lib.tb200_comm_destroy(self.handle))
+
+    def comm_size(self):
+        return int(self.lib.tb200_comm_size(self.handle))
+
+    def gather_output(self, shard, gathered, check=True):
+        return self._check(self.lib.tb200_gather_output(self.handle, shard.handle, gathered.handle), check)
 
     def _check(self, st, check=True):
         st = Status(st)

@@ -14,11 +14,17 @@ using namespace tb200;
 namespace tb200
 {
 
-// diagnostic switches read from the environment (defaults are what the tests and the bench run)
-static bool env_flag(const char* name, int dflt)
+tb200_status raise_smem_limit(tb200_ctx* ctx, int bit, const void* kernel, int bytes)
 {
-    const char* v = getenv(name);
-    return (v ? atoi(v) : dflt) != 0;
+    if (ctx->smem_attr_set & (1u << bit))
+        return TB200_OK;
+    // a context that knows its device's limit raises the kernel to it once; a bare one (the allocation-free entry
+    // point's stack object) asks for what this launch needs, every time
+    const int want = ctx->max_smem_optin > 0 ? std::max(ctx->max_smem_optin, bytes) : bytes;
+    TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, want));
+    if (ctx->max_smem_optin > 0)
+        ctx->smem_attr_set |= 1u << bit;
+    return TB200_OK;
 }
 
 tb200_status ensure_scratch(tb200_ctx* ctx, size_t bytes)
@@ -27,10 +33,9 @@ tb200_status ensure_scratch(tb200_ctx* ctx, size_t bytes)
         return TB200_OK;
     if (ctx->capturing)
         return fail(ctx, TB200_ERROR, "scratch memory would have to grow during capture; evaluate once eagerly first");
-    // the old block may still be in use by kernels queued on the stream
-    TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
-    if (ctx->scratch)
-        TB200_CUDA_CHECK(ctx, cudaFree(ctx->scratch));
+    // the old block may still be in use by kernels queued on the stream, or by a captured graph that recorded its
+    // address: release_block waits for the former and parks the block while any graph is alive
+    release_block(ctx, ctx->scratch);
     ctx->scratch       = nullptr;
     ctx->scratch_bytes = 0;
     size_t want        = std::max(bytes, (size_t)1 << 20);
@@ -319,9 +324,11 @@ extern "C" tb200_status tb200_ctx_create(int device, void* stream, tb200_ctx** o
         }
         c->owns_stream = true;
     }
-    cudaDeviceProp prop;
-    if (cudaGetDeviceProperties(&prop, device) == cudaSuccess)
-        c->num_sms = prop.multiProcessorCount;
+    int attr_val = 0;
+    if (cudaDeviceGetAttribute(&attr_val, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && attr_val > 0)
+        c->num_sms = attr_val;
+    if (cudaDeviceGetAttribute(&attr_val, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) == cudaSuccess && attr_val > 0)
+        c->max_smem_optin = attr_val;
     if (cudaMalloc(&c->d_status, sizeof(int)) != cudaSuccess || cudaMallocHost(&c->h_status, sizeof(int)) != cudaSuccess ||
         cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream) != cudaSuccess)
     {
@@ -329,9 +336,7 @@ extern "C" tb200_status tb200_ctx_create(int device, void* stream, tb200_ctx** o
         delete c;
         return TB200_INTERNAL;
     }
-    const char* pol = getenv("TB200_KERNEL_POLICY");
-    if (pol)
-        c->policy = atoi(pol);
+    c->policy = diag_env_int("TB200_KERNEL_POLICY", 0);
     *out = c;
     return TB200_OK;
 }
@@ -342,6 +347,14 @@ extern "C" tb200_status tb200_ctx_destroy(tb200_ctx* ctx)
         return TB200_OK;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    tb200_comm_destroy(ctx);
+    for (auto& e : ctx->prepared)
+        if (e->block)
+            cudaFree(e->block);
+    ctx->prepared.clear();
+    for (void* b : ctx->retired)
+        cudaFree(b);
+    ctx->retired.clear();
     if (ctx->scratch)
         cudaFree(ctx->scratch);
     if (ctx->stage)
@@ -391,6 +404,7 @@ extern "C" tb200_status tb200_timer_enable(tb200_ctx* ctx, int32_t on)
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     ctx->timing = on != 0;
     return TB200_OK;
 }
@@ -423,6 +437,7 @@ extern "C" tb200_status tb200_capture_begin(tb200_ctx* ctx)
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, ctx->capturing, "capture already in progress");
     TB200_ERROR_IF(ctx, ctx->timing, "disable the kernel timer before capturing");
     TB200_CUDA_CHECK(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
@@ -457,6 +472,7 @@ extern "C" tb200_status tb200_capture_end(tb200_ctx* ctx, tb200_graph** out)
     }
     tg->graph = g;
     tg->exec  = exec;
+    ctx->live_graphs++;
     size_t n  = 0;
     if (cudaGraphGetNodes(g, nullptr, &n) == cudaSuccess)
         tg->launches = n;
@@ -468,6 +484,7 @@ extern "C" tb200_status tb200_graph_launch(tb200_ctx* ctx, tb200_graph* graph)
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !graph || !graph->exec, "null graph");
     TB200_ERROR_IF(ctx, ctx->capturing, "a captured graph cannot be launched while capturing");
     TB200_CUDA_CHECK(ctx, cudaGraphLaunch(graph->exec, ctx->stream));
@@ -487,6 +504,13 @@ extern "C" tb200_status tb200_graph_destroy(tb200_ctx* ctx, tb200_graph* graph)
     if (graph->graph)
         cudaGraphDestroy(graph->graph);
     delete graph;
+    if (ctx && ctx->live_graphs > 0 && --ctx->live_graphs == 0)
+    {
+        // no graph can hold the parked blocks' addresses any more
+        for (void* b : ctx->retired)
+            cudaFree(b);
+        ctx->retired.clear();
+    }
     return TB200_OK;
 }
 
@@ -495,6 +519,51 @@ extern "C" int tb200_set_kernel_policy(tb200_ctx* ctx, int policy)
     int old     = ctx->policy;
     ctx->policy = policy;
     return old;
+}
+
+extern "C" tb200_status tb200_set_wait_limit(tb200_ctx* ctx, uint64_t sm_cycles)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ENTER(ctx);
+    TB200_ERROR_IF(ctx, sm_cycles == 0 || sm_cycles > (uint64_t)1 << 62, "wait limit out of range");
+    ctx->wait_limit_cycles = (long long)sm_cycles;
+    return TB200_OK;
+}
+
+extern "C" tb200_status tb200_set_shared_gpu(tb200_ctx* ctx, int32_t shared)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ENTER(ctx);
+    ctx->shared_gpu = shared != 0;
+    return TB200_OK;
+}
+
+extern "C" tb200_status tb200_const_cache_control(tb200_ctx* ctx, int32_t action)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ENTER(ctx);
+    switch (action)
+    {
+        case TB200_CACHE_OFF:
+            cache_clear(ctx);
+            ctx->const_cache_on = false;
+            return TB200_OK;
+        case TB200_CACHE_ON:
+            ctx->const_cache_on = true;
+            return TB200_OK;
+        case TB200_CACHE_CLEAR:
+            cache_clear(ctx);
+            return TB200_OK;
+    }
+    return fail(ctx, TB200_ERROR, "unknown cache action %d", (int)action);
+}
+
+extern "C" int32_t tb200_const_cache_entries(const tb200_ctx* ctx)
+{
+    return ctx ? (int32_t)ctx->prepared.size() : 0;
 }
 
 extern "C" const char* tb200_last_kernel(const tb200_ctx* ctx)
@@ -506,6 +575,7 @@ extern "C" tb200_status tb200_sync(tb200_ctx* ctx)
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, ctx->capturing, "tb200_sync is not allowed while capturing");
     TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     TB200_CUDA_CHECK(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
@@ -570,6 +640,7 @@ extern "C" tb200_status tb200_tensor_alloc(tb200_ctx* ctx, tb200_dtype dtype, in
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     return make_tensor(ctx, dtype, rank, shape, nullptr, true, out);
 }
 
@@ -578,6 +649,7 @@ extern "C" tb200_status tb200_tensor_wrap(tb200_ctx* ctx, tb200_dtype dtype, int
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !device_ptr, "null device pointer");
     TB200_ERROR_IF(ctx, (reinterpret_cast<uintptr_t>(device_ptr) & 15) != 0, "device pointer must be 16-byte aligned");
     return make_tensor(ctx, dtype, rank, shape, device_ptr, false, out);
@@ -587,6 +659,8 @@ extern "C" tb200_status tb200_tensor_free(tb200_ctx* ctx, tb200_tensor* t)
 {
     if (!t)
         return TB200_OK;
+    if (ctx && t->data)
+        cache_note_free(ctx, t->data, std::max<size_t>(t->bytes, 1));
     if (t->owns && t->data)
     {
         if (ctx)
@@ -601,12 +675,17 @@ extern "C" tb200_status tb200_tensor_upload(tb200_ctx* ctx, tb200_tensor* t, con
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !t || !host, "null tensor or host buffer");
     TB200_ERROR_IF(ctx, !t->contiguous, "upload needs a contiguous tensor");
     TB200_ERROR_IF(ctx, ctx->capturing, "uploads are not allowed while capturing");
     TB200_ERROR_IF(ctx, bytes != t->bytes, "upload of %zu bytes into a tensor of %zu bytes", bytes, t->bytes);
     if (bytes)
+    {
         TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(t->data, host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+        // tables derived from this tensor (it may be a weight, bias, multiplier or shift) follow the new contents
+        return cache_note_upload(ctx, t->data, bytes);
+    }
     return TB200_OK;
 }
 
@@ -614,6 +693,7 @@ extern "C" tb200_status tb200_tensor_download(tb200_ctx* ctx, const tb200_tensor
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !t || !host, "null tensor or host buffer");
     TB200_ERROR_IF(ctx, !t->contiguous, "download needs a contiguous tensor");
     TB200_ERROR_IF(ctx, ctx->capturing, "downloads are not allowed while capturing");
@@ -641,6 +721,7 @@ extern "C" tb200_status tb200_tensor_slice(tb200_ctx* ctx, const tb200_tensor* p
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !parent || !start || !size || !out, "OpSlice: null operand");
     *out = nullptr;
     int64_t offset = 0, n = 1;
@@ -680,6 +761,7 @@ extern "C" tb200_status tb200_tensor_reshape(tb200_ctx* ctx, const tb200_tensor*
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !parent || !shape || !out, "OpReshape: null operand");
     TB200_ERROR_IF(ctx, !parent->contiguous, "OpReshape: a zero-copy reshape needs a contiguous tensor");
     int64_t n = 1;
@@ -705,10 +787,11 @@ static const tb200_status kNeedsDenseOutput = (tb200_status)-77;
 static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
                                 const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp, const int32_t pad[4],
                                 const int32_t stride[2], const int32_t dilation[2], const tb200_epilogue* epilogue,
-                                tb200_tensor* output, const ConvOutView* view, bool dry_run)
+                                tb200_tensor* output, const ConvOutView* view, bool dry_run, bool use_cache)
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !input || !weight || !bias || !output || !pad || !stride || !dilation, "OpConv2d: null operand");
     TB200_ERROR_IF(ctx, !all_contiguous({ weight, bias, output }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "OpConv2d");
     // OpConv2d::checkTensorAttributes (reference_model/src/ops/tensor_ops.cpp:690-720)
@@ -753,6 +836,8 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
         return st;
     if (numel(output) == 0)
         return TB200_OK;
+    if (!dry_run)
+        cache_note_write(ctx, output->data, output->bytes);
 
     // ---- tensor-core path
     const bool tc_rescale_ok = !epi.has_rescale || (epi.rs.scale32 && epi.rs.rounding != TB200_INEXACT_ROUND &&
@@ -792,54 +877,124 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
                 const bool padded  = pad[0] || pad[1] || pad[2] || pad[3];
                 const bool classes = input_zp != 0 && padded;
                 const size_t ncls  = classes ? (size_t)(KH + 1) * (KH + 1) * (KW + 1) * (KW + 1) : 1;
-                // scratch: prefix | corr | mult_pad | shift_pad
-                const size_t prefix_elems = (size_t)(KH + 1) * (KW + 1) * OC;
+                // block: prefix | corr | mult_pad | shift_pad
+                const size_t prefix_elems = ((size_t)(KH + 1) * (KW + 1) * OC + 3) & ~(size_t)3;
                 const size_t corr_elems   = ncls * OCpad;
                 const size_t bytes        = (prefix_elems + corr_elems + OCpad) * sizeof(int32_t) + OCpad + 64;
                 if (bytes <= ((size_t)64 << 20))
                 {
                     if (dry_run)
                         return TB200_OK;
-                    st = ensure_scratch(ctx, bytes);
-                    if (st != TB200_OK)
-                        return st;
-                    int32_t* prefix   = reinterpret_cast<int32_t*>(ctx->scratch);
-                    int32_t* corr     = prefix + ((prefix_elems + 3) & ~(size_t)3);
+                    const int8_t* wp   = reinterpret_cast<const int8_t*>(weight->data);
+                    const int32_t* bp  = reinterpret_cast<const int32_t*>(bias->data);
+                    const int32_t* mp  = epi.has_rescale ? reinterpret_cast<const int32_t*>(epi.rs.mult) : nullptr;
+                    const int8_t* sp   = epi.has_rescale ? epi.rs.shift : nullptr;
+                    const int bias_n = bias->shape[0], per_ch = epi.rs.per_channel, has_rs = epi.has_rescale ? 1 : 0;
+                    const int cls_i = classes ? 1 : 0;
+                    auto build = [=](tb200_ctx* c, void* block) -> tb200_status {
+                        int32_t* prefix   = reinterpret_cast<int32_t*>(block);
+                        int32_t* corr     = prefix + prefix_elems;
+                        int32_t* mult_pad = corr + corr_elems;
+                        int8_t* shift_pad = reinterpret_cast<int8_t*>(mult_pad + OCpad);
+                        conv_epilogue_tables_kernel<<<(OCpad * 32 + 127) / 128, 128, 0, c->stream>>>(
+                            wp, bp, bias_n, OC, OCpad, KH, KW, IC, input_zp, cls_i, mp, sp, per_ch, prefix, corr,
+                            has_rs ? mult_pad : nullptr, shift_pad);
+                        return post_launch(c, "conv_epilogue_tables");
+                    };
+                    void* block = nullptr;
+                    Prepared* e = nullptr;
+                    if (use_cache && ctx->const_cache_on)
+                    {
+                        std::string key;
+                        key_add(&key, (int)0);
+                        key_add(&key, wp); key_add(&key, bp); key_add(&key, mp); key_add(&key, sp);
+                        key_add(&key, OC); key_add(&key, KH); key_add(&key, KW); key_add(&key, IC); key_add(&key, bias_n);
+                        key_add(&key, input_zp); key_add(&key, per_ch); key_add(&key, has_rs); key_add(&key, cls_i);
+                        e = cache_find(ctx, key);
+                        if (!e)
+                        {
+                            std::vector<std::pair<const char*, size_t>> ops = {
+                                { reinterpret_cast<const char*>(wp), weight->bytes }, { reinterpret_cast<const char*>(bp), bias->bytes } };
+                            if (has_rs)
+                            {
+                                ops.push_back({ reinterpret_cast<const char*>(mp), epilogue->rescale.multiplier->bytes });
+                                ops.push_back({ reinterpret_cast<const char*>(sp), epilogue->rescale.shift->bytes });
+                            }
+                            e = cache_insert(ctx, key, std::move(ops), bytes, build);
+                        }
+                    }
+                    if (e)
+                    {
+                        st = cache_use(ctx, e);
+                        if (st != TB200_OK)
+                            return st;
+                        block = e->block;
+                    }
+                    else
+                    {
+                        st = ensure_scratch(ctx, bytes);
+                        if (st != TB200_OK)
+                            return st;
+                        st = build(ctx, ctx->scratch);
+                        if (st != TB200_OK)
+                            return st;
+                        block = ctx->scratch;
+                    }
+                    int32_t* corr     = reinterpret_cast<int32_t*>(block) + prefix_elems;
                     int32_t* mult_pad = corr + corr_elems;
-                    int8_t* shift_pad = reinterpret_cast<int8_t*>(mult_pad + OCpad);
-                    conv_epilogue_tables_kernel<<<(OCpad * 32 + 127) / 128, 128, 0, ctx->stream>>>(
-                        reinterpret_cast<const int8_t*>(weight->data), reinterpret_cast<const int32_t*>(bias->data),
-                        bias->shape[0], OC, OCpad, KH, KW, IC, input_zp, classes ? 1 : 0,
-                        epi.has_rescale ? reinterpret_cast<const int32_t*>(epi.rs.mult) : nullptr,
-                        epi.has_rescale ? epi.rs.shift : nullptr, epi.rs.per_channel, prefix, corr,
-                        epi.has_rescale ? mult_pad : nullptr, shift_pad);
-                    st = post_launch(ctx, "conv_epilogue_tables");
-                    if (st != TB200_OK)
-                        return st;
                     q.corr         = corr;
                     q.corr_stride  = OCpad;
-                    q.corr_classes = classes ? 1 : 0;
+                    q.corr_classes = cls_i;
                     q.mult_pad     = mult_pad;
-                    q.shift_pad    = shift_pad;
+                    q.shift_pad    = reinterpret_cast<int8_t*>(mult_pad + OCpad);
                     return tc_gemm_launch(ctx, q);
                 }
             }
             else
             {
-                st = ensure_scratch(ctx, (size_t)OCpad * sizeof(float));
-                if (st != TB200_OK)
-                    return st;
-                float* bf = reinterpret_cast<float*>(ctx->scratch);
-                if (bias->dtype == TB200_FP16)
-                    bias_to_f32_kernel<__half><<<(OCpad + 127) / 128, 128, 0, ctx->stream>>>(
-                        reinterpret_cast<const __half*>(bias->data), bias->shape[0], OC, bf, OCpad);
+                const void* bp   = bias->data;
+                const int bias_n = bias->shape[0];
+                const bool b16   = bias->dtype == TB200_FP16;
+                auto build = [=](tb200_ctx* c, void* block) -> tb200_status {
+                    float* bf = reinterpret_cast<float*>(block);
+                    if (b16)
+                        bias_to_f32_kernel<__half><<<(OCpad + 127) / 128, 128, 0, c->stream>>>(
+                            reinterpret_cast<const __half*>(bp), bias_n, OC, bf, OCpad);
+                    else
+                        bias_to_f32_kernel<__nv_bfloat16><<<(OCpad + 127) / 128, 128, 0, c->stream>>>(
+                            reinterpret_cast<const __nv_bfloat16*>(bp), bias_n, OC, bf, OCpad);
+                    return post_launch(c, "bias_to_f32");
+                };
+                Prepared* e = nullptr;
+                if (use_cache && ctx->const_cache_on)
+                {
+                    std::string key;
+                    key_add(&key, (int)2);
+                    key_add(&key, bp); key_add(&key, bias_n); key_add(&key, OC); key_add(&key, (int)bias->dtype);
+                    e = cache_find(ctx, key);
+                    if (!e)
+                        e = cache_insert(ctx, key, { { reinterpret_cast<const char*>(bp), bias->bytes } },
+                                         (size_t)OCpad * sizeof(float), build);
+                }
+                void* block = nullptr;
+                if (e)
+                {
+                    st = cache_use(ctx, e);
+                    if (st != TB200_OK)
+                        return st;
+                    block = e->block;
+                }
                 else
-                    bias_to_f32_kernel<__nv_bfloat16><<<(OCpad + 127) / 128, 128, 0, ctx->stream>>>(
-                        reinterpret_cast<const __nv_bfloat16*>(bias->data), bias->shape[0], OC, bf, OCpad);
-                st = post_launch(ctx, "bias_to_f32");
-                if (st != TB200_OK)
-                    return st;
-                q.bias_f_pad  = bf;
+                {
+                    st = ensure_scratch(ctx, (size_t)OCpad * sizeof(float));
+                    if (st != TB200_OK)
+                        return st;
+                    st = build(ctx, ctx->scratch);
+                    if (st != TB200_OK)
+                        return st;
+                    block = ctx->scratch;
+                }
+                q.bias_f_pad  = reinterpret_cast<const float*>(block);
                 q.corr_stride = OCpad;
                 return tc_gemm_launch(ctx, q);
             }
@@ -878,38 +1033,76 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
             q.out = output->data;
             q.epi = TC_EPI_I32;
             fill_tc_epilogue(&q, epi, output->dtype);
-            st = ensure_scratch(ctx, xp_bytes + wr_bytes + tab_bytes);
+            // Derived from the constants alone (cached): weights re-packed to [OC][KH][win] and the epilogue tables.
+            // Derived from the input (context scratch, every call): the border- and channel-padded copy.
+            const int8_t* wp  = reinterpret_cast<const int8_t*>(weight->data);
+            const int32_t* bp = reinterpret_cast<const int32_t*>(bias->data);
+            const int32_t* mp = epi.has_rescale ? reinterpret_cast<const int32_t*>(epi.rs.mult) : nullptr;
+            const int8_t* sp  = epi.has_rescale ? epi.rs.shift : nullptr;
+            const int bias_n = bias->shape[0], per_ch = epi.rs.per_channel, has_rs = epi.has_rescale ? 1 : 0;
+            const int block  = 256;
+            auto build = [=](tb200_ctx* c, void* blk) -> tb200_status {
+                int8_t* wr        = reinterpret_cast<int8_t*>(blk);
+                int32_t* prefix   = reinterpret_cast<int32_t*>(wr + wr_bytes);
+                int32_t* corr     = prefix + prefix_elems;
+                int32_t* mult_pad = corr + OCpad;
+                int8_t* shift_pad = reinterpret_cast<int8_t*>(mult_pad + OCpad);
+                repack_weights_smallc_kernel<<<(int)(((int64_t)OC * KH * win + block - 1) / block), block, 0, c->stream>>>(
+                    wp, wr, OC, KH, KW, IC, Cp, win);
+                // the border holds the zero point, so every tap is in scope and one correction row serves all pixels
+                conv_epilogue_tables_kernel<<<(OCpad * 32 + 127) / 128, 128, 0, c->stream>>>(
+                    wr, bp, bias_n, OC, OCpad, KH, 1, win, input_zp, 0, mp, sp, per_ch, prefix, corr,
+                    has_rs ? mult_pad : nullptr, shift_pad);
+                return post_launch(c, "conv_window_tables", 2);
+            };
+            Prepared* e = nullptr;
+            if (use_cache && ctx->const_cache_on)
+            {
+                std::string key;
+                key_add(&key, (int)1);
+                key_add(&key, wp); key_add(&key, bp); key_add(&key, mp); key_add(&key, sp);
+                key_add(&key, OC); key_add(&key, KH); key_add(&key, KW); key_add(&key, IC); key_add(&key, bias_n);
+                key_add(&key, input_zp); key_add(&key, per_ch); key_add(&key, has_rs); key_add(&key, Cp); key_add(&key, win);
+                e = cache_find(ctx, key);
+                if (!e)
+                {
+                    std::vector<std::pair<const char*, size_t>> ops = {
+                        { reinterpret_cast<const char*>(wp), weight->bytes }, { reinterpret_cast<const char*>(bp), bias->bytes } };
+                    if (has_rs)
+                    {
+                        ops.push_back({ reinterpret_cast<const char*>(mp), epilogue->rescale.multiplier->bytes });
+                        ops.push_back({ reinterpret_cast<const char*>(sp), epilogue->rescale.shift->bytes });
+                    }
+                    e = cache_insert(ctx, key, std::move(ops), wr_bytes + tab_bytes, build);
+                }
+            }
+            st = ensure_scratch(ctx, xp_bytes + (e ? 0 : wr_bytes + tab_bytes));
             if (st != TB200_OK)
                 return st;
             int8_t* xp = reinterpret_cast<int8_t*>(ctx->scratch);
-            int8_t* wr = xp + xp_bytes;
+            int8_t* wr = e ? reinterpret_cast<int8_t*>(e->block) : xp + xp_bytes;
             q.a = xp;
             q.b = wr;
             std::string why;
             if (tc_gemm_supported(q, &why))
             {
-                int32_t* prefix   = reinterpret_cast<int32_t*>(wr + wr_bytes);
-                int32_t* corr     = prefix + prefix_elems;
+                if (e)
+                    st = cache_use(ctx, e);
+                else
+                    st = build(ctx, wr);
+                if (st != TB200_OK)
+                    return st;
+                int32_t* corr     = reinterpret_cast<int32_t*>(wr + wr_bytes) + prefix_elems;
                 int32_t* mult_pad = corr + OCpad;
-                int8_t* shift_pad = reinterpret_cast<int8_t*>(mult_pad + OCpad);
-                const int block   = 256;
                 pad_expand_i8_kernel<<<grid_for(ctx, (int64_t)N * Hp * Wp, block), block, 0, ctx->stream>>>(
                     reinterpret_cast<const int8_t*>(input->data), xp, N, IH, IW, IC, Hp, Wp, Cp, pad[0], pad[2], input_zp);
-                repack_weights_smallc_kernel<<<(int)(((int64_t)OC * KH * win + block - 1) / block), block, 0, ctx->stream>>>(
-                    reinterpret_cast<const int8_t*>(weight->data), wr, OC, KH, KW, IC, Cp, win);
-                // the border holds the zero point, so every tap is in scope and one correction row serves all pixels
-                conv_epilogue_tables_kernel<<<(OCpad * 32 + 127) / 128, 128, 0, ctx->stream>>>(
-                    wr, reinterpret_cast<const int32_t*>(bias->data), bias->shape[0], OC, OCpad, KH, 1, win, input_zp, 0,
-                    epi.has_rescale ? reinterpret_cast<const int32_t*>(epi.rs.mult) : nullptr,
-                    epi.has_rescale ? epi.rs.shift : nullptr, epi.rs.per_channel, prefix, corr,
-                    epi.has_rescale ? mult_pad : nullptr, shift_pad);
-                st = post_launch(ctx, "conv_window_relayout", 3);
+                st = post_launch(ctx, "conv_window_relayout", 1);
                 if (st != TB200_OK)
                     return st;
                 q.corr        = corr;
                 q.corr_stride = OCpad;
                 q.mult_pad    = mult_pad;
-                q.shift_pad   = shift_pad;
+                q.shift_pad   = reinterpret_cast<int8_t*>(mult_pad + OCpad);
                 st = tc_gemm_launch(ctx, q);
                 // a driver that refuses the overlapping-window tensor map sends this shape to the CUDA-core kernel
                 if (!(st == TB200_INTERNAL && ctx->err.find("rejected") != std::string::npos))
@@ -976,7 +1169,7 @@ extern "C" tb200_status tb200_conv2d(tb200_ctx* ctx, const tb200_tensor* input, 
                                      tb200_tensor* output)
 {
     return conv2d_impl(ctx, input, weight, bias, input_zp, weight_zp, pad, stride, dilation, epilogue, output, nullptr,
-                       false);
+                       false, true);
 }
 
 // =================================================================================================== TRANSPOSE_CONV2D
@@ -987,9 +1180,7 @@ static tb200_status ensure_stage(tb200_ctx* ctx, size_t bytes)
         return TB200_OK;
     if (ctx->capturing)
         return fail(ctx, TB200_ERROR, "staging memory would have to grow during capture; evaluate once eagerly first");
-    TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
-    if (ctx->stage)
-        TB200_CUDA_CHECK(ctx, cudaFree(ctx->stage));
+    release_block(ctx, ctx->stage);
     ctx->stage       = nullptr;
     ctx->stage_bytes = 0;
     TB200_CUDA_CHECK(ctx, cudaMalloc(&ctx->stage, bytes));
@@ -1073,6 +1264,7 @@ extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tenso
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !input || !weight || !bias || !output || !out_pad || !stride, "OpTransposeConv2d: null operand");
     TB200_ERROR_IF(ctx, !all_contiguous({ input, weight, bias, output }), "OpTransposeConv2d: operands must be contiguous");
     // OpTransposeConv2d::checkTensorAttributes (reference_model/src/ops/tensor_ops.cpp:1982-2056)
@@ -1227,7 +1419,7 @@ extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tenso
             const ConvOutView view = { ay.J, ax.J, sy, sx, 0, 0, OC, sx };
             // the probe only looks at shapes and alignment: the unstaged operands stand in
             st = conv2d_impl(ctx, &xin, &wst, &bst, input_zp, weight_zp, pad, one, one, epilogue ? &epi2 : nullptr, output,
-                             &view, true);
+                             &view, true, false);
             if (st == TB200_OK)
             {
                 st = ensure_stage(ctx, total);
@@ -1263,7 +1455,7 @@ extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tenso
                 if (st != TB200_OK)
                     return st;
                 st = conv2d_impl(ctx, &xin, &wst, &bst, input_zp, weight_zp, pad, one, one, epilogue ? &epi2 : nullptr, output,
-                                 &view, false);
+                                 &view, false, false);
                 return st == kNeedsDenseOutput ? fail(ctx, TB200_INTERNAL, "OpTransposeConv2d: plan changed") : st;
             }
             if (st != kNeedsDenseOutput)
@@ -1312,7 +1504,7 @@ extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tenso
             wsub.stride[0] = (int64_t)ph.y.T * ph.x.T * IC;
             const int32_t pad[4]   = { ph.y.pad0, ph.y.pad1, ph.x.pad0, ph.x.pad1 };
             const ConvOutView view = { ph.y.J, ph.x.J, sy, sx, ph.py, ph.px, 0, 0 };
-            return conv2d_impl(ctx, &xin, &wsub, bias, input_zp, weight_zp, pad, one, one, epilogue, output, &view, dry);
+            return conv2d_impl(ctx, &xin, &wsub, bias, input_zp, weight_zp, pad, one, one, epilogue, output, &view, dry, false);
         };
         if (ok && !phases.empty())
         {
@@ -1419,7 +1611,8 @@ extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tenso
         din.stride[0] = (int64_t)DH * DW * IC;
     }
     const int32_t pad[4] = { KH - 1 + out_pad[0], KH - 1 + out_pad[1], KW - 1 + out_pad[2], KW - 1 + out_pad[3] };
-    st = tb200_conv2d(ctx, &din, &wmir, bias, input_zp, weight_zp, pad, one, one, epilogue, output);
+    // (the mirrored weights live in staging that the next call overwrites: nothing derived from them is cached)
+    st = conv2d_impl(ctx, &din, &wmir, bias, input_zp, weight_zp, pad, one, one, epilogue, output, nullptr, false, false);
     if (st != TB200_OK && ctx->err.compare(0, 8, "OpConv2d") == 0)
         ctx->err = "OpTransposeConv2d (as CONV2D): " + ctx->err;
     return st;
@@ -1433,6 +1626,7 @@ extern "C" tb200_status tb200_depthwise_conv2d(tb200_ctx* ctx, const tb200_tenso
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !input || !weight || !bias || !output || !pad || !stride || !dilation,
                    "OpDepthwiseConv2d: null operand");
     TB200_ERROR_IF(ctx, !all_contiguous({ input, weight, bias, output }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "OpDepthwiseConv2d");
@@ -1478,6 +1672,7 @@ extern "C" tb200_status tb200_depthwise_conv2d(tb200_ctx* ctx, const tb200_tenso
         return st;
     if (numel(output) == 0)
         return TB200_OK;
+    cache_note_write(ctx, output->data, output->bytes);
     ConvDev d;
     memset(&d, 0, sizeof(d));
     d.N = N; d.IH = IH; d.IW = IW; d.IC = C; d.OH = OH; d.OW = OW; d.OC = C * M; d.KH = KH; d.KW = KW; d.M = M;
@@ -1552,6 +1747,7 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !a || !b || !output, "OpMatMul: null operand");
     TB200_ERROR_IF(ctx, !all_contiguous({ a, b, output }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "OpMatMul");
     // OpMatMul::checkTensorAttributes (reference_model/src/ops/tensor_ops.cpp:1347-1420)
@@ -1586,6 +1782,7 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
     TB200_ERROR_IF(ctx, epi.has_rescale || epi.has_clamp, "OpMatMul: fused epilogues are not available for MATMUL");
     if (numel(output) == 0)
         return TB200_OK;
+    cache_note_write(ctx, output->data, output->bytes);
 
     if (a->dtype == TB200_FP32)
     {
@@ -1645,16 +1842,16 @@ extern "C" tb200_status tb200_matmul(tb200_ctx* ctx, const tb200_tensor* a, cons
                 // shared between tiles through flags in global memory (no pass over A or B at all), or the row sums only.
                 // The flags carry a per-launch epoch, which a replayed CUDA graph would repeat: not while capturing.
                 const bool pair      = tc_gemm_pair_supported(q, ctx->num_sms);
-                const bool fuse_all  = pair && !ctx->capturing && env_flag("TB200_FUSE_SUMS", 1);
-                const bool fuse_rows = !fuse_all && b_zp != 0 && pair && env_flag("TB200_FUSE_ROW_SUMS", 1);
+                // Sharing sums between tiles needs every CTA pair of the grid resident at once, which holds on a GPU
+                // this context has to itself; tb200_set_shared_gpu(ctx, 1) keeps the sums in separate kernels.
+                const bool fuse_all  = pair && !ctx->capturing && !ctx->shared_gpu && diag_env_int("TB200_FUSE_SUMS", 1) != 0;
+                const bool fuse_rows = !fuse_all && b_zp != 0 && pair && diag_env_int("TB200_FUSE_ROW_SUMS", 1) != 0;
                 if (fuse_all)
                 {
                     const size_t words = (size_t)N * 2 * ((H + 255) / 256 + (W + 255) / 256);
                     if (words > ctx->pair_flag_words)
                     {
-                        TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
-                        if (ctx->pair_flags)
-                            TB200_CUDA_CHECK(ctx, cudaFree(ctx->pair_flags));
+                        release_block(ctx, ctx->pair_flags);
                         ctx->pair_flags      = nullptr;
                         ctx->pair_flag_words = 0;
                         TB200_CUDA_CHECK(ctx, cudaMalloc(reinterpret_cast<void**>(&ctx->pair_flags), words * sizeof(uint32_t)));
@@ -1825,6 +2022,7 @@ extern "C" tb200_status tb200_rescale(tb200_ctx* ctx, const tb200_tensor* input,
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !input || !attr || !output, "OpRescale: null operand");
     TB200_ERROR_IF(ctx, !all_contiguous({ input, output, attr->multiplier, attr->shift }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "OpRescale");
     TB200_ERROR_IF(ctx, !same_shape(input, output), "OpRescale: input and output shapes differ");
@@ -1836,6 +2034,7 @@ extern "C" tb200_status tb200_rescale(tb200_ctx* ctx, const tb200_tensor* input,
     const int64_t n = numel(input);
     if (n == 0)
         return TB200_OK;
+    cache_note_write(ctx, output->data, output->bytes);
     const bool aligned = ((reinterpret_cast<uintptr_t>(input->data) | reinterpret_cast<uintptr_t>(output->data)) & 15) == 0;
     const bool vec4    = aligned && (n % 4 == 0) && (!attr->per_channel || C % 4 == 0);
     switch (dtype_size(input->dtype))
@@ -1859,6 +2058,7 @@ extern "C" tb200_status tb200_clamp(tb200_ctx* ctx, const tb200_tensor* input, i
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !input || !output, "OpClamp: null operand");
     TB200_ERROR_IF(ctx, !all_contiguous({ input, output }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "OpClamp");
     TB200_ERROR_IF(ctx, !same_shape(input, output) || input->dtype != output->dtype,
@@ -1866,6 +2066,7 @@ extern "C" tb200_status tb200_clamp(tb200_ctx* ctx, const tb200_tensor* input, i
     const int64_t n = numel(input);
     const int block = 256;
     const int grid  = grid_for(ctx, std::max<int64_t>(1, n / 8), block);
+    cache_note_write(ctx, output->data, output->bytes);
     switch (input->dtype)
     {
         case TB200_INT8:
@@ -1907,6 +2108,7 @@ extern "C" tb200_status tb200_add(tb200_ctx* ctx, const tb200_tensor* a, const t
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !a || !b || !output, "OpAdd: null operand");
     TB200_ERROR_IF(ctx, !all_contiguous({ a, b, output }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "OpAdd");
     // BinaryNodeBase::checkTensorAttributes / broadcast (reference_model/src/ops/ewise_binary.cpp:40-111)
@@ -1941,6 +2143,7 @@ extern "C" tb200_status tb200_add(tb200_ctx* ctx, const tb200_tensor* a, const t
     const int64_t n = numel(output);
     if (n == 0)
         return TB200_OK;
+    cache_note_write(ctx, output->data, output->bytes);
     if (((reinterpret_cast<uintptr_t>(a->data) | reinterpret_cast<uintptr_t>(b->data) |
           reinterpret_cast<uintptr_t>(output->data)) & 15) != 0 && bc.same_shape)
     {
@@ -1977,6 +2180,7 @@ extern "C" tb200_status tb200_residual_add(tb200_ctx* ctx, const tb200_tensor* a
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !a || !b || !output || !a_attr || !b_attr || !out_attr, "residual_add: null operand");
     TB200_ERROR_IF(ctx, !all_contiguous({ a, b, output }), "%s: zero-copy views are accepted only as the CONV2D input; this operand must be contiguous", "residual_add");
     TB200_ERROR_IF(ctx, !same_shape(a, b) || !same_shape(a, output), "residual_add: operand shapes differ");
@@ -1999,6 +2203,7 @@ extern "C" tb200_status tb200_residual_add(tb200_ctx* ctx, const tb200_tensor* a
     const int64_t n = numel(a);
     if (n == 0)
         return TB200_OK;
+    cache_note_write(ctx, output->data, output->bytes);
     const bool aligned = ((reinterpret_cast<uintptr_t>(a->data) | reinterpret_cast<uintptr_t>(b->data) |
                            reinterpret_cast<uintptr_t>(output->data)) & 15) == 0;
     const bool pc = a_attr->per_channel || b_attr->per_channel || out_attr->per_channel;
@@ -2027,24 +2232,68 @@ extern "C" tb200_status tb200_residual_add(tb200_ctx* ctx, const tb200_tensor* a
         f.lo = has_clamp ? std::min(std::max(-128, clamp_min), clamp_max) : -128;
         f.hi = has_clamp ? std::min(std::max(127, clamp_min), clamp_max) : 127;
         // Large joins pay for tabulating all 65536 byte pairs first (two launches, one lookup per element after that)
-        if (n >= ((int64_t)1 << 22) && (ctx->join_table != nullptr || !ctx->capturing))
+        if (n >= ((int64_t)1 << 22))
         {
             constexpr size_t kTableSmem = kJoinTableBytes + kJoinBadWords * sizeof(uint32_t);
-            if (ctx->join_table == nullptr)
+            // the table depends on the three RESCALEs' constants and the clip range alone: built once per join, cached
+            auto build = [=](tb200_ctx* c, void* block) -> tb200_status {
+                uint8_t* tab = reinterpret_cast<uint8_t*>(block);
+                residual_table_kernel<<<256, 256, 0, c->stream>>>(f, tab, reinterpret_cast<uint32_t*>(tab + kJoinTableBytes));
+                return post_launch(c, "residual_table");
+            };
+            Prepared* e = nullptr;
+            if (ctx->const_cache_on)
             {
-                TB200_CUDA_CHECK(ctx, cudaMalloc(&ctx->join_table, kTableSmem));
-                TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(residual_add_i8_table_kernel,
-                                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTableSmem));
+                std::string key;
+                key_add(&key, (int)3);
+                for (const ResidualLeg* l : { &f.a, &f.b, &f.o })
+                {
+                    key_add(&key, l->mult); key_add(&key, l->shift);
+                    key_add(&key, l->zp_in); key_add(&key, l->zp_out); key_add(&key, l->double_round);
+                }
+                key_add(&key, f.lo); key_add(&key, f.hi);
+                e = cache_find(ctx, key);
+                if (!e)
+                {
+                    std::vector<std::pair<const char*, size_t>> ops;
+                    for (const tb200_rescale_attr* at : { a_attr, b_attr, out_attr })
+                    {
+                        ops.push_back({ reinterpret_cast<const char*>(at->multiplier->data), at->multiplier->bytes });
+                        ops.push_back({ reinterpret_cast<const char*>(at->shift->data), at->shift->bytes });
+                    }
+                    e = cache_insert(ctx, key, std::move(ops), kTableSmem, build);
+                }
             }
-            uint8_t* table     = reinterpret_cast<uint8_t*>(ctx->join_table);
-            uint32_t* bad_bits = reinterpret_cast<uint32_t*>(table + kJoinTableBytes);
-            residual_table_kernel<<<256, 256, 0, ctx->stream>>>(f, table, bad_bits);
-            const int tblock = 512;
-            const int tgrid  = (int)std::min<int64_t>((n / 16 + tblock - 1) / tblock, (int64_t)ctx->num_sms * 2);
-            residual_add_i8_table_kernel<<<tgrid, tblock, kTableSmem, ctx->stream>>>(
-                reinterpret_cast<const int8_t*>(a->data), reinterpret_cast<const int8_t*>(b->data),
-                reinterpret_cast<int8_t*>(output->data), n / 16, table, bad_bits, ctx->d_status);
-            return post_launch(ctx, "residual_add_i8_table", 2);
+            uint8_t* table = nullptr;
+            if (e)
+            {
+                st = cache_use(ctx, e);
+                if (st != TB200_OK)
+                    return st;
+                table = reinterpret_cast<uint8_t*>(e->block);
+            }
+            else if (ctx->join_table != nullptr || !ctx->capturing)
+            {
+                if (ctx->join_table == nullptr)
+                    TB200_CUDA_CHECK(ctx, cudaMalloc(&ctx->join_table, kTableSmem));
+                st = build(ctx, ctx->join_table);
+                if (st != TB200_OK)
+                    return st;
+                table = reinterpret_cast<uint8_t*>(ctx->join_table);
+            }
+            if (table != nullptr)
+            {
+                st = raise_smem_limit(ctx, 16, reinterpret_cast<const void*>(residual_add_i8_table_kernel), (int)kTableSmem);
+                if (st != TB200_OK)
+                    return st;
+                uint32_t* bad_bits = reinterpret_cast<uint32_t*>(table + kJoinTableBytes);
+                const int tblock   = 512;
+                const int tgrid    = (int)std::min<int64_t>((n / 16 + tblock - 1) / tblock, (int64_t)ctx->num_sms * 2);
+                residual_add_i8_table_kernel<<<tgrid, tblock, kTableSmem, ctx->stream>>>(
+                    reinterpret_cast<const int8_t*>(a->data), reinterpret_cast<const int8_t*>(b->data),
+                    reinterpret_cast<int8_t*>(output->data), n / 16, table, bad_bits, ctx->d_status);
+                return post_launch(ctx, "residual_add_i8_table");
+            }
         }
         residual_add_i8_fast_kernel<<<grid_for(ctx, n / 16, block), block, 0, ctx->stream>>>(
             reinterpret_cast<const int8_t*>(a->data), reinterpret_cast<const int8_t*>(b->data),
@@ -2089,6 +2338,7 @@ extern "C" tb200_status tb200_max_pool2d(tb200_ctx* ctx, const tb200_tensor* inp
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     PoolDev p;
     tb200_status st = pool_common(ctx, "OpMaxPool2d", input, kernel, pad, stride, output, &p);
     if (st != TB200_OK)
@@ -2096,6 +2346,7 @@ extern "C" tb200_status tb200_max_pool2d(tb200_ctx* ctx, const tb200_tensor* inp
     const int64_t n = numel(output);
     if (n == 0)
         return TB200_OK;
+    cache_note_write(ctx, output->data, output->bytes);
     const int block = 256;
     const bool aligned = ((reinterpret_cast<uintptr_t>(input->data) | reinterpret_cast<uintptr_t>(output->data)) & 15) == 0;
     switch (input->dtype)
@@ -2137,6 +2388,7 @@ extern "C" tb200_status tb200_avg_pool2d(tb200_ctx* ctx, const tb200_tensor* inp
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     PoolDev p;
     tb200_status st = pool_common(ctx, "OpAvgPool2d", input, kernel, pad, stride, output, &p);
     if (st != TB200_OK)
@@ -2149,6 +2401,7 @@ extern "C" tb200_status tb200_avg_pool2d(tb200_ctx* ctx, const tb200_tensor* inp
     const int64_t n = numel(output);
     if (n == 0)
         return TB200_OK;
+    cache_note_write(ctx, output->data, output->bytes);
     const int block = 256;
     const int grid  = grid_for(ctx, n, block);
     switch (input->dtype)
@@ -2218,6 +2471,7 @@ extern "C" tb200_status tb200_matmul_host(tb200_ctx* ctx, tb200_dtype in_dtype, 
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !a || !b || !out, "matmul_host: null buffer");
     TB200_ERROR_IF(ctx, N < 0 || H < 0 || C < 0 || W < 0, "matmul_host: negative dimension");
     const size_t es_in = dtype_size(in_dtype), es_out = dtype_size(out_dtype);
@@ -2230,7 +2484,7 @@ extern "C" tb200_status tb200_matmul_host(tb200_ctx* ctx, tb200_dtype in_dtype, 
     // up).  The link is the bottleneck, so the first chunks are small and double in size (the first product starts after
     // one batch has been uploaded, not eight) and the last ones halve again (little is left to download after the last
     // upload).
-    const size_t chunk_target = (size_t)std::max(1, atoi(getenv("TB200_HOST_CHUNK_MB") ? getenv("TB200_HOST_CHUNK_MB") : "64")) << 20;
+    const size_t chunk_target = (size_t)std::max(1, diag_env_int("TB200_HOST_CHUNK_MB", 64)) << 20;
     int nb = (int)std::max<size_t>(1, std::min<size_t>((size_t)N, chunk_target / std::max<size_t>(a_b, 1)));
     std::vector<int> sizes;
     {

@@ -5,6 +5,9 @@
 #include <cstdio>
 #include <cstring>
 #include <cuda_runtime.h>
+#include <cstdlib>
+#include <functional>
+#include <memory>
 #include <string>
 #include <utility>
 #include <vector>
@@ -38,6 +41,27 @@ struct tb200_graph
     uint64_t launches    = 0;    // kernels recorded
 };
 
+namespace tb200
+{
+// What an operator derives from its constant operands alone: for a convolution the zero-point correction rows, the
+// per-column RESCALE records and padded multiplier / shift arrays, the fp32 bias, and for few-channel layers the
+// re-packed weights; for a residual join the table of all byte pairs.  Built on first use into a device block of its
+// own and reused by every later call with the same operands and attributes (the reference decodes constants once per
+// graph, reference_model/src/subgraph_traverser.cpp:617-781).
+struct Prepared
+{
+    std::string key;    // kind, operand addresses and every attribute the block's contents depend on
+    std::vector<std::pair<const char*, size_t>> operands;    // device ranges the contents were derived from
+    void* block   = nullptr;
+    size_t bytes  = 0;
+    bool valid    = false;    // the block holds what the operands' current contents give
+    bool unstable = false;    // an operator wrote into an operand: rebuild before every use
+    uint64_t last_use = 0;
+    // enqueues, on the context's stream, the kernels that fill `block` from the operands
+    std::function<tb200_status(tb200_ctx*, void* block)> rebuild;
+};
+}    // namespace tb200
+
 struct tb200_ctx
 {
     int device           = 0;
@@ -57,7 +81,27 @@ struct tb200_ctx
     uint64_t launches    = 0;
     int policy           = 0;
     int num_sms          = 148;
+    int max_smem_optin   = 0;    // largest dynamic shared memory a block may opt into on this device (0 = unknown)
     bool capturing       = false;    // between tb200_capture_begin / tb200_capture_end
+    // Captured graphs hold raw addresses of the blocks above: while any is alive a block that would have to move is
+    // refused (TB200_ERROR) and blocks of dropped cache entries are parked in `retired` instead of being freed.
+    int live_graphs      = 0;
+    std::vector<void*> retired;
+    // every bounded device-side wait gives up after this many SM clock cycles (about two seconds by default)
+    long long wait_limit_cycles = 4000000000LL;
+    // 1: other work may hold SMs of this GPU, so no kernel may wait for another CTA of its own grid (the CTA-pair
+    // MATMUL then takes its zero-point sums from separate kernels instead of exchanging them through flags)
+    int shared_gpu       = 0;
+    int max_pairs[3]     = { 0, 0, 0 };    // resident CTA pairs of the three CTA-pair kernels on this device, 0 = not asked yet
+    uint32_t smem_attr_set = 0;            // bit per kernel whose dynamic shared-memory limit has been raised on this device
+    // output gather across GPUs (dist.cu): an NCCL communicator created by tb200_comm_init or handed in by the host
+    void* comm           = nullptr;
+    bool comm_owned      = false;
+    int comm_rank        = 0;
+    int comm_nranks      = 1;
+    bool const_cache_on  = true;
+    uint64_t cache_clock = 0;
+    std::vector<std::unique_ptr<tb200::Prepared>> prepared;
     const char* last_kernel = "none";
     std::string err;
     // host-buffer pipeline of tb200_matmul_host: copy streams, events and two sets of device staging buffers
@@ -136,6 +180,16 @@ inline tb200_status fail(tb200_ctx* ctx, tb200_status st, const char* fmt, ...)
             return tb200::fail((ctx), TB200_INTERNAL, "%s failed: %s", #expr, cudaGetErrorString(e__));    \
     } while (0)
 
+// Entry points run on the context's device whatever device the calling thread had current (a worker thread starts on
+// device 0; a host may hold contexts on several GPUs): the thread is switched to the context's device and stays there.
+#define TB200_ENTER(ctx)                                                                                   \
+    do                                                                                                     \
+    {                                                                                                      \
+        int dev__ = -1;                                                                                    \
+        if (cudaGetDevice(&dev__) != cudaSuccess || dev__ != (ctx)->device)                                \
+            TB200_CUDA_CHECK((ctx), cudaSetDevice((ctx)->device));                                         \
+    } while (0)
+
 // The reference's ERROR_IF: a violated graph rule ends evaluation with TOSA_ERROR
 // (reference_model/include/func_debug.h:112-178).
 #define TB200_ERROR_IF(ctx, cond, ...)                                                                     \
@@ -145,7 +199,54 @@ inline tb200_status fail(tb200_ctx* ctx, tb200_status st, const char* fmt, ...)
             return tb200::fail((ctx), TB200_ERROR, __VA_ARGS__);                                           \
     } while (0)
 
+// Experiment switches.  The default build has none: these helpers return their default and TB200_DIAG_BIT is a
+// constant false, so no environment variable and no mask can change what the library computes.  A build with
+// -DTB200_DIAG reads TB200_* environment variables at launch and compiles the kernels' diagnostic skip masks in.
+#ifdef TB200_DIAG
+inline int diag_env_int(const char* name, int dflt)
+{
+    const char* v = getenv(name);
+    return v ? atoi(v) : dflt;
+}
+#define TB200_DIAG_BIT(mask, bit) (((mask) & (bit)) != 0)
+#else
+inline int diag_env_int(const char*, int dflt)
+{
+    return dflt;
+}
+#define TB200_DIAG_BIT(mask, bit) false
+#endif
+
 tb200_status ensure_scratch(tb200_ctx* ctx, size_t bytes);
+// ---- cache of blocks derived from constant operands (const_cache.cu)
+// Appends a value's bytes to a cache key.
+template <typename T>
+inline void key_add(std::string* key, const T& v)
+{
+    key->append(reinterpret_cast<const char*>(&v), sizeof(T));
+}
+// Entry with this key, or null.
+Prepared* cache_find(tb200_ctx* ctx, const std::string& key);
+// New entry with a device block of `bytes` (contents not built yet); null when the cache is off, while capturing
+// (nothing may allocate then) or when the allocation fails: the caller then works from context scratch as if there
+// were no cache.
+Prepared* cache_insert(tb200_ctx* ctx, const std::string& key, std::vector<std::pair<const char*, size_t>> operands,
+                       size_t bytes, std::function<tb200_status(tb200_ctx*, void*)> rebuild);
+// Makes the entry's block current (runs `rebuild` when it is not, or always for an unstable entry).
+tb200_status cache_use(tb200_ctx* ctx, Prepared* e);
+// An operator is about to write [ptr, ptr + bytes): entries derived from that memory stop being trusted.
+void cache_note_write(tb200_ctx* ctx, const void* ptr, size_t bytes);
+// New contents were copied into [ptr, ptr + bytes) from outside (upload, file load): entries derived from it are
+// rebuilt at once on the stream, behind the copy, so that captured graphs that hold their blocks stay right.
+tb200_status cache_note_upload(tb200_ctx* ctx, const void* ptr, size_t bytes);
+// [ptr, ptr + bytes) is being released: entries derived from it are dropped.
+void cache_note_free(tb200_ctx* ctx, const void* ptr, size_t bytes);
+void cache_clear(tb200_ctx* ctx);
+// Frees a device block now, or parks it until the context goes while a captured graph may still hold its address.
+void release_block(tb200_ctx* ctx, void* block);
+
+// Raises a kernel's dynamic shared-memory limit once per context (bit = a small id per kernel instantiation).
+tb200_status raise_smem_limit(tb200_ctx* ctx, int bit, const void* kernel, int bytes);
 tb200_status post_launch(tb200_ctx* ctx, const char* kernel_name, int n_launches = 1);
 // Event brackets for tb200_timer_*: call timer_begin before and timer_end after the main kernel's launch.
 void timer_begin(tb200_ctx* ctx);

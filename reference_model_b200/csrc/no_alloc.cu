@@ -128,7 +128,7 @@ extern "C" tb200_status tb200_matmul_i8_noalloc(void* stream, const int8_t* a, c
     {
         char msg[200];
         snprintf(msg, sizeof(msg),
-                 "tb200_matmul_i8_noalloc: N*(H+roundup(W,256)) = %lld exceeds the built-in scratch of %d entries; use tb200_matmul",
+                 "tb200_matmul_i8_noalloc: roundup(N*H,4) + N*roundup(W,256) = %lld exceeds the built-in scratch of %d entries; use tb200_matmul",
                  (long long)(rows + cols), kMaxSumEntries);
         set_err(err, err_len, msg);
         return TB200_ERROR;
@@ -139,6 +139,17 @@ extern "C" tb200_status tb200_matmul_i8_noalloc(void* stream, const int8_t* a, c
         return TB200_ERROR;
     }
 
+    if (synchronize)
+    {
+        // a synchronisation inside a stream capture would invalidate the capture
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(reinterpret_cast<cudaStream_t>(stream), &cap) == cudaSuccess &&
+            cap != cudaStreamCaptureStatusNone)
+        {
+            set_err(err, err_len, "tb200_matmul_i8_noalloc: synchronize != 0 is not possible while the stream is being captured");
+            return TB200_ERROR;
+        }
+    }
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     {
@@ -204,7 +215,9 @@ extern "C" tb200_status tb200_matmul_i8_noalloc(void* stream, const int8_t* a, c
     q.epi        = TC_EPI_I32;
     tb200_status st = TB200_OK;
     std::string why;
-    if (tc_gemm_supported(q, &why))
+    // the same choice of kernels as tb200_matmul: the CTA-pair kernel takes some shapes (K tails) the single-CTA one
+    // does not
+    if (tc_gemm_pair_supported(q, local.num_sms) || tc_gemm_supported(q, &why))
     {
         if (a_zp != 0 || b_zp != 0)
         {

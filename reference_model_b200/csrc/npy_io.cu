@@ -234,6 +234,7 @@ extern "C" tb200_status tb200_tensor_load_npy(tb200_ctx* ctx, const char* path, 
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !path || !out, "readFromNpyFile: null argument");
     *out = nullptr;
     TB200_ERROR_IF(ctx, ctx->capturing, "readFromNpyFile: not allowed while capturing");
@@ -346,6 +347,7 @@ extern "C" tb200_status tb200_tensor_save_npy(tb200_ctx* ctx, const tb200_tensor
 {
     if (!ctx)
         return TB200_ERROR;
+    TB200_ENTER(ctx);
     TB200_ERROR_IF(ctx, !t || !path, "writeToNpyFile: null argument");
     TB200_ERROR_IF(ctx, ctx->capturing, "writeToNpyFile: not allowed while capturing");
     TB200_ERROR_IF(ctx, !t->contiguous, "writeToNpyFile: a view must be copied into a dense tensor first");

@@ -32,7 +32,6 @@ constexpr int kMaxStages   = 8;
 constexpr int kTileM       = 128;
 constexpr int kNumThreads  = 320;    // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kEpiThreads  = 256;
-constexpr long long kWaitLimitCycles = 4000000000LL;    // about two seconds of SM clock
 
 struct TcKernelParams
 {
@@ -78,7 +77,8 @@ struct TcKernelParams
     int32_t out_zp, clamp_lo, clamp_hi;
     float clamp_lo_f, clamp_hi_f;
     int has_clamp;
-    int debug;    // diagnostic bit mask (TB200_TC_DEBUG): 1 skip epilogue memory work, 2 skip MMA issue, 4 skip loads
+    int debug;    // diagnostic bit mask, read only by builds with TB200_DIAG: 1 skip epilogue memory work, 2 skip MMA issue, 4 skip loads
+    long long wait_limit;    // SM cycles after which a pipeline wait gives up (TB200_DEV_TIMEOUT)
     int* status;
 };
 
@@ -162,6 +162,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
     __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
     __shared__ __align__(8) uint64_t bar_tmem_full[2];
     __shared__ __align__(8) uint64_t bar_tmem_empty[2];
+    __shared__ __align__(8) uint64_t bar_drain;    // teardown after a wait gave up: "every MMA issued so far has retired"
     __shared__ uint32_t tmem_base_holder;
     __shared__ int abort_flag;
     // TC_EPI_RESCALE: per-column scaling constants of the current column block, written once per block by the
@@ -188,6 +189,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             ptx::mbar_init(ptx::smem_u32(&bar_tmem_full[a]), 1);
             ptx::mbar_init(ptx::smem_u32(&bar_tmem_empty[a]), kEpiThreads);
         }
+        ptx::mbar_init(ptx::smem_u32(&bar_drain), 1);
         abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tmap(&p.tmA);
@@ -229,7 +231,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     // stages are released in groups of `commit_group` (one tcgen05.commit per group): the first stage
                     // of a group waits for the group's last barrier, the others are free by then
                     if (group_pos == 0 &&
-                        !ptx::mbar_wait_bounded(ptx::smem_u32(&bar_empty[stage + group - 1]), phase ^ 1u, kWaitLimitCycles))
+                        !ptx::mbar_wait_bounded(ptx::smem_u32(&bar_empty[stage + group - 1]), phase ^ 1u, p.wait_limit))
                     {
                         ok = false;
                         break;
@@ -239,7 +241,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     const uint32_t full = ptx::smem_u32(&bar_full[stage]);
                     uint32_t sA         = sA_stage;
                     uint32_t sB         = sA_stage + ksub * a_chunk_bytes;
-                    if (p.debug & 4)
+                    if (TB200_DIAG_BIT(p.debug, 4))
                     {
                         ptx::mbar_arrive(full);
                     }
@@ -312,10 +314,10 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             const uint64_t ad_ring0 = ptx::smem_desc(p.a_desc_hi, smem_base);
             const uint64_t bd_ring0 = ptx::smem_desc(p.b_desc_hi, smem_base + ksub * p.a_chunk_bytes);
             uint64_t ad_stage = ad_ring0, bd_stage = bd_ring0;
-            const bool issue = !(p.debug & 2);
+            const bool issue = !TB200_DIAG_BIT(p.debug, 2);
             for (int tile = p.tile_begin + blockIdx.x; tile < p.tile_end && ok; tile += gridDim.x)
             {
-                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, kWaitLimitCycles))
+                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, p.wait_limit))
                 {
                     ok = false;
                     break;
@@ -326,7 +328,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                 int chunks_left = p.total_chunks;
                 while (chunks_left > 0)
                 {
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_full[stage]), phase, kWaitLimitCycles))
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_full[stage]), phase, p.wait_limit))
                     {
                         ok = false;
                         break;
@@ -417,7 +419,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     // the short form packs to int8 with saturation and stores whole 32-column chunks
                     const bool shortable = p.out_es == 1 && (p.OC & 31) == 0 && p.clamp_lo >= -128 &&
                                            p.clamp_hi <= 127 && p.clamp_lo <= p.clamp_hi && p.out_zp >= -128 &&
-                                           p.out_zp <= 127 && !(p.debug & 8);
+                                           p.out_zp <= 127 && !TB200_DIAG_BIT(p.debug, 8);
                     epi_flags = shortable ? 0 : EPI_COLS_GENERIC;
                 }
                 asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -481,7 +483,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             // warps may still be running and would otherwise block on it); it does no further work.
             if (!ok)
                 continue;
-            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_full[acc]), acc_phase, kWaitLimitCycles);
+            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_full[acc]), acc_phase, p.wait_limit);
             // the whole warp must agree before the warp-collective TMEM loads
             ok = __all_sync(0xffffffffu, ok);
             if (!ok)
@@ -549,7 +551,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                 ptx::tmem_ld_32x32b_x32(taddr_row + (uint32_t)(c * 32), v);
                 ptx::tmem_ld_wait();
                 const int col = t.col0 + c * 32;
-                if (col >= p.OC || (p.debug & 1))
+                if (col >= p.OC || TB200_DIAG_BIT(p.debug, 1))
                     continue;
                 const int nvalid = min(32, p.OC - col);
                 // element offset of (this row, col) in the output, and of the neighbouring lane's row
@@ -568,7 +570,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     rv_pair       = false;    // such outputs are 32-byte aligned: the paired-lane store form is never taken
                 }
 
-                if (EPI != TC_EPI_FLOAT && corr_row != nullptr && !(p.debug & 16))
+                if (EPI != TC_EPI_FLOAT && corr_row != nullptr && !TB200_DIAG_BIT(p.debug, 16))
                 {
                     // every per-column array is padded to a multiple of the tile width: unconditional 128-bit loads
                     const int4* cp = reinterpret_cast<const int4*>(corr_row + col);
@@ -674,7 +676,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         // complete sector (two 16-byte stores would deliver two half-filled ones).  Outputs that are not
                         // 32-byte aligned (views) swap halves between the two lanes of a pair instead, so that one store
                         // instruction writes the even lane's row and the next one the odd lane's row.
-                        const bool skip = (p.debug & 32) && w[0] != 0x12345678u;
+                        const bool skip = TB200_DIAG_BIT(p.debug, 32) && w[0] != 0x12345678u;
                         if ((reinterpret_cast<uintptr_t>(p.out) & 31) == 0)
                         {
                             if (rv && !skip)
@@ -919,6 +921,13 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             ptx::mbar_wait_bounded(ptx::smem_u32(&bar_full[s]), 1u, 2000000LL);
         }
     }
+    if (warp == 1 && lane == 0 && abort_flag)
+    {
+        // ... and let the tensor-core work already issued retire before its accumulators' tensor memory is freed: the
+        // role that normally waits for it (the epilogue) may be the one that gave up
+        ptx::mma_commit(ptx::smem_u32(&bar_drain));
+        ptx::mbar_wait_bounded(ptx::smem_u32(&bar_drain), 0u, 40000000LL);
+    }
     __syncthreads();
     if (warp == 1)
     {
@@ -945,12 +954,6 @@ PFN_encodeTiled get_encode_fn()
             fn = reinterpret_cast<PFN_encodeTiled>(sym);
     });
     return fn;
-}
-
-int env_int(const char* name, int dflt)
-{
-    const char* v = getenv(name);
-    return v ? atoi(v) : dflt;
 }
 
 struct TcPlan
@@ -1059,7 +1062,7 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     k.tiles_y = (OH + BH - 1) / BH;
     k.tiles_n = (N + BN - 1) / BN;
 
-    int block_n = env_int("TB200_TC_BLOCK_N", 0);
+    int block_n = diag_env_int("TB200_TC_BLOCK_N", 0);
     // one column block that covers all channels when there are at most 256 of them (no half-empty second block);
     // the epilogue works in 32-column chunks
     if (block_n == 0)
@@ -1080,7 +1083,7 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     k.chunk_elems    = swz / es;
     k.chunks_per_tap = row_bytes / swz;
     k.total_chunks   = q.KH * q.KW * k.chunks_per_tap;
-    k.ksub           = std::min(std::max(1, env_int("TB200_TC_KSUB", 128 / swz)), k.total_chunks);
+    k.ksub           = std::min(std::max(1, diag_env_int("TB200_TC_KSUB", 128 / swz)), k.total_chunks);
     k.num_kstages    = (k.total_chunks + k.ksub - 1) / k.ksub;
     k.pad_t = q.pad_t;
     k.pad_l = q.pad_l;
@@ -1115,10 +1118,10 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
         k.b_nbox        = block_n / k.b_box_n;
         k.b_box_bytes   = k.chunk_elems * 128;
         k.b_chunk_bytes = k.b_nbox * k.b_box_bytes;
-        const int lbo   = env_int("TB200_TC_MN_LBO", k.b_box_bytes);
-        const int sbo   = env_int("TB200_TC_MN_SBO", 1024);
+        const int lbo   = diag_env_int("TB200_TC_MN_LBO", k.b_box_bytes);
+        const int sbo   = diag_env_int("TB200_TC_MN_SBO", 1024);
         k.b_desc_hi     = ptx::make_smem_desc_hi(lbo, sbo, 2u);
-        k.b_kstep_bytes = env_int("TB200_TC_MN_KSTEP", (32 / es) * 128);
+        k.b_kstep_bytes = diag_env_int("TB200_TC_MN_KSTEP", (32 / es) * 128);
         b_tx            = k.b_chunk_bytes;
     }
     k.tx_bytes_per_chunk = a_tx + b_tx;
@@ -1129,22 +1132,22 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     // a single accumulator buffer (256 TMEM columns) lets two CTAs share an SM there, which doubles the epilogue warps
     // in flight; the lost MMA / epilogue overlap inside one CTA is made up by the neighbour CTA.
     const int mmas_per_tile = k.total_chunks * k.mmas_per_chunk;
-    k.acc_bufs = env_int("TB200_TC_ACC_BUFS", (block_n > 128 && mmas_per_tile <= 16) ? 1 : 2);
+    k.acc_bufs = diag_env_int("TB200_TC_ACC_BUFS", (block_n > 128 && mmas_per_tile <= 16) ? 1 : 2);
     if (k.acc_bufs != 1)
         k.acc_bufs = 2;
     const bool pair_small = block_n <= 128 && 4 * k.stage_bytes <= 100 * 1024;
     const bool pair_short = k.acc_bufs == 1 && 2 * k.stage_bytes <= 100 * 1024;
-    plan->ctas_per_sm     = env_int("TB200_TC_CTAS_PER_SM", (pair_small || pair_short) ? 2 : 1);
+    plan->ctas_per_sm     = diag_env_int("TB200_TC_CTAS_PER_SM", (pair_small || pair_short) ? 2 : 1);
     plan->ctas_per_sm = std::max(1, std::min(plan->ctas_per_sm, 512 / std::max(32, k.acc_bufs * block_n)));
     const int smem_budget = (plan->ctas_per_sm > 1 ? 208 / plan->ctas_per_sm : 200) * 1024;
     k.num_stages = std::min(kMaxStages, smem_budget / k.stage_bytes);
     k.num_stages = std::min(k.num_stages, std::max(2, k.num_kstages * 2));
-    const int forced = env_int("TB200_TC_STAGES", 0);
+    const int forced = diag_env_int("TB200_TC_STAGES", 0);
     if (forced > 0)
         k.num_stages = std::min(forced, kMaxStages);
     if (k.num_stages < 2)
         return no("stage does not fit in shared memory");
-    k.commit_group = env_int("TB200_TC_COMMIT_GROUP", 1);
+    k.commit_group = diag_env_int("TB200_TC_COMMIT_GROUP", 1);
     if (k.commit_group < 1 || k.num_stages % k.commit_group != 0 || k.num_stages / k.commit_group < 2)
         k.commit_group = 1;
     plan->smem_bytes = k.num_stages * k.stage_bytes + 1024;
@@ -1161,7 +1164,7 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     }
     else
     {
-        const uint32_t ab_fmt = is_f16 ? (q.in_dtype == TB200_BF16 ? 1u : 0u) : (uint32_t)env_int("TB200_TC_I8_FMT", 1);
+        const uint32_t ab_fmt = is_f16 ? (q.in_dtype == TB200_BF16 ? 1u : 0u) : (uint32_t)diag_env_int("TB200_TC_I8_FMT", 1);
         k.idesc = ptx::make_idesc(is_f16 ? 1u : 2u, ab_fmt, ab_fmt, 0u, q.b_mn_major ? 1u : 0u, kTileM, (uint32_t)block_n);
     }
     int cols = 32;
@@ -1298,7 +1301,8 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
     k.clamp_hi_f   = q.clamp_hi_f;
     k.has_clamp    = q.has_clamp;
     k.status       = ctx->d_status;
-    k.debug        = env_int("TB200_TC_DEBUG", 0);
+    k.debug        = diag_env_int("TB200_TC_DEBUG", 0);
+    k.wait_limit   = ctx->wait_limit_cycles;
 
     void (*kern)(const TcKernelParams) = nullptr;
     const char* name                   = "";
@@ -1317,7 +1321,11 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
             name = dtype_is_fp8(q.in_dtype) ? "tc_gemm_f8" : "tc_gemm_f16";
             break;
     }
-    TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
+    {
+        const tb200_status ast = raise_smem_limit(ctx, q.epi, reinterpret_cast<const void*>(kern), plan.smem_bytes);
+        if (ast != TB200_OK)
+            return ast;
+    }
     timer_begin(ctx);
     kern<<<plan.grid, kNumThreads, plan.smem_bytes, ctx->stream>>>(k);
     timer_end(ctx);

@@ -1,6 +1,6 @@
 // int8 MATMUL on CTA pairs (tcgen05 cta_group::2) for sm_100a.
 //
-// OpMatMul with int8 operands and int32 output (reference_model/src/ops/tensor_ops.cc:1530-1610), for shapes large
+// OpMatMul with int8 operands and int32 output (reference_model/src/ops/tensor_ops.cpp:1423-1492), for shapes large
 // enough to fill 256 x 256 output tiles.  The kernel is launched as clusters of two CTAs on neighbouring SMs; a pair
 // owns one 256 x 256 tile at a time:
 //   * each CTA loads its own 128 rows of A and its own 128 columns of B per 128-byte K chunk (TMA, no multi-destination
@@ -40,7 +40,6 @@ constexpr int kPairThreads    = 64 + 32 * (kPairEpiWarps + kPairSumWarps);    //
 constexpr int kPairMaxStages  = 8;
 constexpr int kPairChunkBytes = 16384;    // 128 rows x 128 bytes (A: rows x K, B: K rows x columns), 128-byte swizzle
 constexpr int kPairTmemCols   = 512;      // two accumulator buffers of 256 columns
-constexpr long long kPairWaitLimit = 4000000000LL;    // about two seconds of SM clock
 
 struct PairParams
 {
@@ -75,7 +74,8 @@ struct PairParams
     uint32_t epoch;     // mode 2: value a flag takes in this launch
     const int32_t* corr;        // [batch][corr_stride] or null; corr_stride a multiple of 256 that covers W
     int corr_stride;
-    int debug;                  // diagnostic bit mask: 1 skip epilogue memory work, 2 skip MMA issue, 4 skip loads
+    int debug;                  // diagnostic bit mask, read only by builds with TB200_DIAG: 1 skip epilogue memory work, 2 skip MMA issue, 4 skip loads
+    long long wait_limit;       // SM cycles after which a pipeline or flag wait gives up (TB200_DEV_TIMEOUT)
     int* status;
 };
 
@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                 int k = 0;
                 while (chunks_left > 0)
                 {
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, kPairWaitLimit))
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, p.wait_limit))
                     {
                         ok = false;
                         break;
@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                     const int nch = min(p.ksub, chunks_left);
                     chunks_left -= nch;
                     const uint32_t full_local = ptx::smem_u32(&bar_full[stage]);
-                    if (p.debug & 4)
+                    if (TB200_DIAG_BIT(p.debug, 4))
                     {
                         if (rank == 0)
                             ptx::mbar_arrive(full_local);
@@ -232,13 +232,13 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            const bool issue = !(p.debug & 2);
+            const bool issue = !TB200_DIAG_BIT(p.debug, 2);
             for (int round = 0, base = 0; base < p.num_tiles && ok; round++, base += num_clusters)
             {
                 const int tile = base + (cluster_id + round) % num_clusters;
                 if (tile >= p.num_tiles)
                     continue;
-                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, kPairWaitLimit))
+                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, p.wait_limit))
                 {
                     ok = false;
                     break;
@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                 int chunks_left = p.total_chunks;
                 while (chunks_left > 0)
                 {
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_full[stage]), phase, kPairWaitLimit))
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_full[stage]), phase, p.wait_limit))
                     {
                         ok = false;
                         break;
@@ -339,7 +339,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                 while (chunks_left > 0 && ok)
                 {
                     const uint32_t ready = ptx::smem_u32(rank == 0 ? &bar_full[stage] : &bar_go[stage]);
-                    if (!ptx::mbar_wait_bounded(ready, phase, kPairWaitLimit))
+                    if (!ptx::mbar_wait_bounded(ready, phase, p.wait_limit))
                     {
                         ok = false;
                         break;
@@ -457,7 +457,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                 const int tile = base + (cluster_id + round) % num_clusters;
                 if (tile >= p.num_tiles)
                     continue;
-                ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_rs_empty[acc]), acc_phase ^ 1u, kPairWaitLimit);
+                ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_rs_empty[acc]), acc_phase ^ 1u, p.wait_limit);
                 int32_t s[8];
 #pragma unroll
                 for (int i = 0; i < 8; i++)
@@ -466,7 +466,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                 while (chunks_left > 0 && ok)
                 {
                     const uint32_t ready = ptx::smem_u32(rank == 0 ? &bar_full[stage] : &bar_go[stage]);
-                    if (!ptx::mbar_wait_bounded(ready, phase, kPairWaitLimit))
+                    if (!ptx::mbar_wait_bounded(ready, phase, p.wait_limit))
                     {
                         ok = false;
                         break;
@@ -528,7 +528,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
         const int row     = quarter * 32 + lane;
         const uint32_t empty_first[2] = { ptx::map_to_cta(ptx::smem_u32(&bar_tmem_empty[0]), 0),
                                           ptx::map_to_cta(ptx::smem_u32(&bar_tmem_empty[1]), 0) };
-        const bool wide_ok = (reinterpret_cast<uintptr_t>(p.out) & 31) == 0 && !(p.debug & 8);
+        const bool wide_ok = (reinterpret_cast<uintptr_t>(p.out) & 31) == 0 && !TB200_DIAG_BIT(p.debug, 8);
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -538,7 +538,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
             if (tile >= p.num_tiles)
                 continue;
             const PairTile t = decode_pair_tile(p, tile);
-            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_full[acc]), acc_phase, kPairWaitLimit);
+            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_tmem_full[acc]), acc_phase, p.wait_limit);
             // the whole warp must agree before the warp-collective TMEM loads
             ok = __all_sync(0xffffffffu, ok);
             if (!ok)
@@ -563,7 +563,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                     while ((p.row_corr != nullptr && ptx::ld_acquire_gpu(frow) != p.epoch) ||
                            (p.corr != nullptr && (ptx::ld_acquire_gpu(fcol) != p.epoch || ptx::ld_acquire_gpu(fcol + 1) != p.epoch)))
                     {
-                        if (clock64() - t0 > kPairWaitLimit)
+                        if (clock64() - t0 > p.wait_limit)
                         {
                             ok = false;
                             break;
@@ -580,7 +580,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
             }
             else if (p.fuse_row_sums)
             {
-                ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_rs_full[acc]), acc_phase, kPairWaitLimit);
+                ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_rs_full[acc]), acc_phase, p.wait_limit);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok)
                     break;
@@ -599,7 +599,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) tc_gemm_pair_kernel(const __g
                 ptx::tmem_ld_32x32b_x32(taddr_row + (uint32_t)(c * 32), v);
                 ptx::tmem_ld_wait();
                 const int col = t.w0 + c * 32;
-                if (col >= p.W || (p.debug & 1))
+                if (col >= p.W || TB200_DIAG_BIT(p.debug, 1))
                     continue;
                 if (KIND != 0)
                 {
@@ -756,25 +756,19 @@ PFN_encodeTiledPair pair_encode_fn()
     return fn;
 }
 
-int pair_env_int(const char* name, int dflt)
-{
-    const char* v = getenv(name);
-    return v ? atoi(v) : dflt;
-}
-
 }    // namespace
 
 // MATMUL problems as api.cu describes them: A [1][batch][H][C], B MN-major [batch][C][W], int32 output.
 bool tc_gemm_pair_supported(const TcProblem& q, int num_sms)
 {
-    if (pair_env_int("TB200_TC_PAIR", 1) == 0)
+    if (diag_env_int("TB200_TC_PAIR", 1) == 0)
         return false;
     const bool i8 = q.in_dtype == TB200_INT8 && q.epi == TC_EPI_I32 && q.out_dtype == TB200_INT32;
     const bool fl = q.epi == TC_EPI_FLOAT && !q.has_clamp && q.bias_f_pad == nullptr;
     const bool f8 = fl && dtype_is_fp8(q.in_dtype) && (q.out_dtype == TB200_FP16 || q.out_dtype == TB200_FP32) &&
-                    pair_env_int("TB200_TC_PAIR_F8", 1) != 0;
+                    diag_env_int("TB200_TC_PAIR_F8", 1) != 0;
     const bool f16 = fl && (q.in_dtype == TB200_FP16 || q.in_dtype == TB200_BF16) &&
-                     (q.out_dtype == q.in_dtype || q.out_dtype == TB200_FP32) && pair_env_int("TB200_TC_PAIR_F16", 1) != 0;
+                     (q.out_dtype == q.in_dtype || q.out_dtype == TB200_FP32) && diag_env_int("TB200_TC_PAIR_F16", 1) != 0;
     if ((!i8 && !f8 && !f16) || !q.b_mn_major)
         return false;
     if ((f8 || f16) && (q.corr != nullptr || q.row_corr != nullptr || q.fuse_row_sums != 0))
@@ -851,7 +845,8 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     k.b_zp          = q.b_zp;
     k.corr        = q.corr;
     k.corr_stride = q.corr_stride;
-    k.debug       = pair_env_int("TB200_TC_DEBUG", 0);
+    k.debug       = diag_env_int("TB200_TC_DEBUG", 0);
+    k.wait_limit  = ctx->wait_limit_cycles;
     k.status      = ctx->d_status;
 
     cuuint64_t a_dims[3]    = { (cuuint64_t)k.C, (cuuint64_t)k.H, (cuuint64_t)k.NB };
@@ -877,12 +872,16 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
 
     // The ring holds what is in flight from L2: the kernel is bound by latency x bytes in flight, so it takes all the
     // shared memory there is.  One commit per stage; 4 MMAs (one chunk) per commit costs tensor-pipe time, 8 do not.
-    k.ksub        = std::max(1, std::min(4, pair_env_int("TB200_PAIR_KSUB", 2)));
+    k.ksub        = std::max(1, std::min(4, diag_env_int("TB200_PAIR_KSUB", 2)));
     k.stage_bytes = 2 * k.ksub * kPairChunkBytes;
-    k.num_stages  = std::min(kPairMaxStages, std::max(2, pair_env_int("TB200_PAIR_STAGES", (224 * 1024) / k.stage_bytes)));
+    k.num_stages  = std::min(kPairMaxStages, std::max(2, diag_env_int("TB200_PAIR_STAGES", (224 * 1024) / k.stage_bytes)));
     const int smem_bytes = k.num_stages * k.stage_bytes + 1024;
     void (*kern)(const PairParams) = f16 ? tc_gemm_pair_kernel<2> : f8 ? tc_gemm_pair_kernel<1> : tc_gemm_pair_kernel<0>;
-    TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    {
+        const tb200_status ast = raise_smem_limit(ctx, 8 + k.mma_kind, reinterpret_cast<const void*>(kern), smem_bytes);
+        if (ast != TB200_OK)
+            return ast;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim         = dim3(kPairThreads);
     cfg.dynamicSmemBytes = (size_t)smem_bytes;
@@ -895,9 +894,9 @@ tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& q)
     cfg.attrs    = attr;
     cfg.numAttrs = 1;
     // Tiles wait for sums that other pairs publish, so every pair of the grid has to be resident at once: never more
-    // pairs than the device can hold of this kernel (asked once; one CTA per SM because of its shared memory).
-    static int max_pairs_of[3] = { 0, 0, 0 };
-    int& max_pairs = max_pairs_of[k.mma_kind];
+    // pairs than the device can hold of this kernel (asked once per context, i.e. per device; one CTA per SM because
+    // of its shared memory).
+    int& max_pairs = ctx->max_pairs[k.mma_kind];
     if (max_pairs == 0)
     {
         cfg.gridDim = dim3((unsigned)(2 * (ctx->num_sms / 2)));
