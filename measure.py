@@ -1,6 +1,6 @@
 """Device timings of the benchmark configurations other than the one bench.py reports.
 
-    python -m reference_model_b200.measure [--configs c1,c2b,c3a,c3b,c4] [--iters 20]
+    python measure.py [--configs c1,c2b,c3a,c3b,c4] [--iters 20]
 
 Prints one JSON line per configuration: device time per call (CUDA events on the context's stream, after warm-up,
 operands resident in HBM), derived throughput, and the roofline figure that bounds it.  Synthetic seeded operands of
@@ -14,7 +14,7 @@ import sys
 
 import numpy as np
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
