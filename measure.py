@@ -155,7 +155,7 @@ def graph_profile(batch):
     exceeds the replayed graph's time; the shares are what this is for)."""
     import collections
     import time
-    from . import graph as G
+    from reference_model_b200 import graph as G
     ctx = tb.Context(0)
     g = G.resnet50_int8(batch)
     run = G.DeviceRunner(ctx, g)

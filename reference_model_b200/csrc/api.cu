@@ -20,7 +20,14 @@ tb200_status raise_smem_limit(tb200_ctx* ctx, int bit, const void* kernel, int b
         return TB200_OK;
     // a context that knows its device's limit raises the kernel to it once; a bare one (the allocation-free entry
     // point's stack object) asks for what this launch needs, every time
-    const int want = ctx->max_smem_optin > 0 ? std::max(ctx->max_smem_optin, bytes) : bytes;
+    int want = bytes;
+    if (ctx->max_smem_optin > 0)
+    {
+        // the device's opt-in limit covers static and dynamic shared memory together
+        cudaFuncAttributes fa;
+        TB200_CUDA_CHECK(ctx, cudaFuncGetAttributes(&fa, kernel));
+        want = std::max(bytes, ctx->max_smem_optin - (int)fa.sharedSizeBytes);
+    }
     TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, want));
     if (ctx->max_smem_optin > 0)
         ctx->smem_attr_set |= 1u << bit;
@@ -784,6 +791,21 @@ struct ConvOutView
 };
 static const tb200_status kNeedsDenseOutput = (tb200_status)-77;
 
+// The word a builder left at `offset` of a cache entry's block (e.g. "every column's lean RESCALE record is usable"),
+// read back once per build: a copy and a stream synchronisation at the first use of the entry, nothing afterwards.
+// An entry that is rebuilt on every use, or that is first met while capturing, stays unread: the caller then takes
+// the path that needs no verdict.
+static tb200_status read_host_flag(tb200_ctx* ctx, Prepared* e, size_t offset)
+{
+    if (e->host_flag >= 0 || e->unstable || ctx->capturing || !e->valid)
+        return TB200_OK;
+    TB200_CUDA_CHECK(ctx, cudaMemcpyAsync(ctx->h_status, reinterpret_cast<const uint8_t*>(e->block) + offset, sizeof(int),
+                                          cudaMemcpyDeviceToHost, ctx->stream));
+    TB200_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    e->host_flag = *ctx->h_status != 0 ? 1 : 0;
+    return TB200_OK;
+}
+
 static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
                                 const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp, const int32_t pad[4],
                                 const int32_t stride[2], const int32_t dilation[2], const tb200_epilogue* epilogue,
@@ -878,9 +900,14 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
                 const bool classes = input_zp != 0 && padded;
                 const size_t ncls  = classes ? (size_t)(KH + 1) * (KH + 1) * (KW + 1) * (KW + 1) : 1;
                 // block: prefix | corr | mult_pad | shift_pad
+                // block: prefix | corr | mult_pad | shift_pad | records of the lean RESCALE form | border deltas
                 const size_t prefix_elems = ((size_t)(KH + 1) * (KW + 1) * OC + 3) & ~(size_t)3;
                 const size_t corr_elems   = ncls * OCpad;
-                const size_t bytes        = (prefix_elems + corr_elems + OCpad) * sizeof(int32_t) + OCpad + 64;
+                const size_t rec_off      = ((prefix_elems + corr_elems + OCpad) * sizeof(int32_t) + OCpad + 63) & ~(size_t)63;
+                const bool want_rec       = epi.has_rescale;
+                const size_t delta_off    = rec_off + (want_rec ? (size_t)OCpad * 8 * sizeof(int32_t) : 0);
+                const size_t flag_off     = delta_off + ((want_rec && classes) ? corr_elems * sizeof(int32_t) : 0);
+                const size_t bytes        = flag_off + 64;
                 if (bytes <= ((size_t)64 << 20))
                 {
                     if (dry_run)
@@ -891,14 +918,20 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
                     const int8_t* sp   = epi.has_rescale ? epi.rs.shift : nullptr;
                     const int bias_n = bias->shape[0], per_ch = epi.rs.per_channel, has_rs = epi.has_rescale ? 1 : 0;
                     const int cls_i = classes ? 1 : 0;
+                    const int dr_i  = epi.has_rescale && epi.rs.rounding == TB200_DOUBLE_ROUND ? 1 : 0;
+                    const int32_t ozp_i = epi.has_rescale ? (int32_t)epi.rs.out_zp_ext : 0;
                     auto build = [=](tb200_ctx* c, void* block) -> tb200_status {
                         int32_t* prefix   = reinterpret_cast<int32_t*>(block);
                         int32_t* corr     = prefix + prefix_elems;
                         int32_t* mult_pad = corr + corr_elems;
                         int8_t* shift_pad = reinterpret_cast<int8_t*>(mult_pad + OCpad);
+                        int32_t* rec      = want_rec ? reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(block) + rec_off) : nullptr;
+                        int32_t* delta    = (want_rec && cls_i) ? reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(block) + delta_off) : nullptr;
+                        int* all_ok       = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(block) + flag_off);
+                        TB200_CUDA_CHECK(c, cudaMemsetAsync(all_ok, want_rec ? 1 : 0, sizeof(int), c->stream));
                         conv_epilogue_tables_kernel<<<(OCpad * 32 + 127) / 128, 128, 0, c->stream>>>(
                             wp, bp, bias_n, OC, OCpad, KH, KW, IC, input_zp, cls_i, mp, sp, per_ch, prefix, corr,
-                            has_rs ? mult_pad : nullptr, shift_pad);
+                            has_rs ? mult_pad : nullptr, shift_pad, rec, delta, dr_i, ozp_i, all_ok);
                         return post_launch(c, "conv_epilogue_tables");
                     };
                     void* block = nullptr;
@@ -910,6 +943,7 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
                         key_add(&key, wp); key_add(&key, bp); key_add(&key, mp); key_add(&key, sp);
                         key_add(&key, OC); key_add(&key, KH); key_add(&key, KW); key_add(&key, IC); key_add(&key, bias_n);
                         key_add(&key, input_zp); key_add(&key, per_ch); key_add(&key, has_rs); key_add(&key, cls_i);
+                        key_add(&key, dr_i); key_add(&key, ozp_i);
                         e = cache_find(ctx, key);
                         if (!e)
                         {
@@ -923,12 +957,17 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
                             e = cache_insert(ctx, key, std::move(ops), bytes, build);
                         }
                     }
+                    bool lean_ok = false;
                     if (e)
                     {
                         st = cache_use(ctx, e);
                         if (st != TB200_OK)
                             return st;
                         block = e->block;
+                        st    = read_host_flag(ctx, e, flag_off);
+                        if (st != TB200_OK)
+                            return st;
+                        lean_ok = e->host_flag == 1;
                     }
                     else
                     {
@@ -940,6 +979,7 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
                             return st;
                         block = ctx->scratch;
                     }
+                    q.lean_ok         = lean_ok ? 1 : 0;
                     int32_t* corr     = reinterpret_cast<int32_t*>(block) + prefix_elems;
                     int32_t* mult_pad = corr + corr_elems;
                     q.corr         = corr;
@@ -947,6 +987,12 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
                     q.corr_classes = cls_i;
                     q.mult_pad     = mult_pad;
                     q.shift_pad    = reinterpret_cast<int8_t*>(mult_pad + OCpad);
+                    // the lean form packs with int8 saturation: it serves RESCALEs to signed int8 only
+                    const bool lean_out = want_rec && output->dtype == TB200_INT8 && !epi.rs.out_unsigned;
+                    q.rec   = lean_out ? reinterpret_cast<const int32_t*>(reinterpret_cast<const uint8_t*>(block) + rec_off) : nullptr;
+                    q.delta = (lean_out && classes)
+                                  ? reinterpret_cast<const int32_t*>(reinterpret_cast<const uint8_t*>(block) + delta_off)
+                                  : nullptr;
                     return tc_gemm_launch(ctx, q);
                 }
             }
@@ -1019,7 +1065,9 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
         const size_t xp_bytes = ((size_t)N * Hp * Wp * Cp + 255) & ~(size_t)255;
         const size_t wr_bytes = ((size_t)OC * KH * win + 255) & ~(size_t)255;
         const size_t prefix_elems = ((size_t)(KH + 1) * 2 * OC + 3) & ~(size_t)3;
-        const size_t tab_bytes = (prefix_elems + 2 * (size_t)OCpad) * sizeof(int32_t) + OCpad + 64;
+        const size_t rec_off   = ((prefix_elems + 2 * (size_t)OCpad) * sizeof(int32_t) + OCpad + 63) & ~(size_t)63;
+        const size_t flag_off  = rec_off + (size_t)OCpad * 8 * sizeof(int32_t);
+        const size_t tab_bytes = flag_off + 64;
         if (win != 0 && xp_bytes + wr_bytes + tab_bytes <= ((size_t)8 << 30))
         {
             TcProblem q;
@@ -1041,18 +1089,25 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
             const int8_t* sp  = epi.has_rescale ? epi.rs.shift : nullptr;
             const int bias_n = bias->shape[0], per_ch = epi.rs.per_channel, has_rs = epi.has_rescale ? 1 : 0;
             const int block  = 256;
+            const int dr_i   = epi.has_rescale && epi.rs.rounding == TB200_DOUBLE_ROUND ? 1 : 0;
+            const int32_t ozp_i = epi.has_rescale ? (int32_t)epi.rs.out_zp_ext : 0;
             auto build = [=](tb200_ctx* c, void* blk) -> tb200_status {
                 int8_t* wr        = reinterpret_cast<int8_t*>(blk);
                 int32_t* prefix   = reinterpret_cast<int32_t*>(wr + wr_bytes);
                 int32_t* corr     = prefix + prefix_elems;
                 int32_t* mult_pad = corr + OCpad;
                 int8_t* shift_pad = reinterpret_cast<int8_t*>(mult_pad + OCpad);
+                int32_t* rec      = has_rs ? reinterpret_cast<int32_t*>(wr + wr_bytes + rec_off) : nullptr;
+                int* all_ok       = reinterpret_cast<int*>(wr + wr_bytes + flag_off);
+                TB200_CUDA_CHECK(c, cudaMemsetAsync(all_ok, has_rs ? 1 : 0, sizeof(int), c->stream));
                 repack_weights_smallc_kernel<<<(int)(((int64_t)OC * KH * win + block - 1) / block), block, 0, c->stream>>>(
                     wp, wr, OC, KH, KW, IC, Cp, win);
                 // the border holds the zero point, so every tap is in scope and one correction row serves all pixels
+                // (the re-packed rows are `win` bytes of which KW * IC carry weights: the value bound counts them all,
+                // which only makes it more cautious)
                 conv_epilogue_tables_kernel<<<(OCpad * 32 + 127) / 128, 128, 0, c->stream>>>(
                     wr, bp, bias_n, OC, OCpad, KH, 1, win, input_zp, 0, mp, sp, per_ch, prefix, corr,
-                    has_rs ? mult_pad : nullptr, shift_pad);
+                    has_rs ? mult_pad : nullptr, shift_pad, rec, nullptr, dr_i, ozp_i, all_ok);
                 return post_launch(c, "conv_window_tables", 2);
             };
             Prepared* e = nullptr;
@@ -1063,6 +1118,7 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
                 key_add(&key, wp); key_add(&key, bp); key_add(&key, mp); key_add(&key, sp);
                 key_add(&key, OC); key_add(&key, KH); key_add(&key, KW); key_add(&key, IC); key_add(&key, bias_n);
                 key_add(&key, input_zp); key_add(&key, per_ch); key_add(&key, has_rs); key_add(&key, Cp); key_add(&key, win);
+                key_add(&key, dr_i); key_add(&key, ozp_i);
                 e = cache_find(ctx, key);
                 if (!e)
                 {
@@ -1087,7 +1143,12 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
             if (tc_gemm_supported(q, &why))
             {
                 if (e)
+                {
                     st = cache_use(ctx, e);
+                    if (st == TB200_OK)
+                        st = read_host_flag(ctx, e, wr_bytes + flag_off);
+                    q.lean_ok = e->host_flag == 1 ? 1 : 0;
+                }
                 else
                     st = build(ctx, wr);
                 if (st != TB200_OK)
@@ -1103,6 +1164,8 @@ static tb200_status conv2d_impl(tb200_ctx* ctx, const tb200_tensor* input, const
                 q.corr_stride = OCpad;
                 q.mult_pad    = mult_pad;
                 q.shift_pad   = reinterpret_cast<int8_t*>(mult_pad + OCpad);
+                if (has_rs && output->dtype == TB200_INT8 && !epi.rs.out_unsigned)
+                    q.rec = reinterpret_cast<const int32_t*>(wr + wr_bytes + rec_off);
                 st = tc_gemm_launch(ctx, q);
                 // a driver that refuses the overlapping-window tensor map sends this shape to the CUDA-core kernel
                 if (!(st == TB200_INTERNAL && ctx->err.find("rejected") != std::string::npos))

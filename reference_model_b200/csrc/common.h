@@ -56,6 +56,7 @@ struct Prepared
     size_t bytes  = 0;
     bool valid    = false;    // the block holds what the operands' current contents give
     bool unstable = false;    // an operator wrote into an operand: rebuild before every use
+    int host_flag = -1;       // a verdict the builder left in the block and the host has read back (-1: not read yet)
     uint64_t last_use = 0;
     // enqueues, on the context's stream, the kernels that fill `block` from the operands
     std::function<tb200_status(tb200_ctx*, void* block)> rebuild;
@@ -309,6 +310,9 @@ struct TcProblem
     const float* bias_f_pad;     // TC_EPI_FLOAT: fp32 bias padded to corr_stride, or null
     const int32_t* mult_pad;     // TC_EPI_RESCALE: multipliers / shifts expanded per column and padded to corr_stride
     const int8_t* shift_pad;
+    const int32_t* rec;          // optional: [corr_stride][8] prepared records of the lean RESCALE form (rescale_rec_build)
+    const int32_t* delta;        // optional, with corr_classes: [classes][corr_stride] class row minus interior row
+    int lean_ok;                 // the host knows every column's record is usable: tc_conv_lean_kernel may run
     int double_round;
     int32_t out_zp;
     int32_t clamp_lo, clamp_hi;    // also the dtype range

@@ -102,6 +102,7 @@ tb200_status cache_use(tb200_ctx* ctx, Prepared* e)
         return TB200_OK;
     const tb200_status st = e->rebuild(ctx, e->block);
     e->valid              = st == TB200_OK;
+    e->host_flag          = -1;
     return st;
 }
 
@@ -125,6 +126,7 @@ tb200_status cache_note_upload(tb200_ctx* ctx, const void* ptr, size_t bytes)
         {
             const tb200_status st = e->rebuild(ctx, e->block);
             e->valid              = st == TB200_OK;
+            e->host_flag          = -1;
             if (st != TB200_OK)
                 return st;
         }

@@ -1197,11 +1197,18 @@ __global__ void __launch_bounds__(256) matmul_col_corr_kernel(const int8_t* __re
 //                             has (KH+1)^2 (KW+1)^2 rows indexed ((ky_lo*(KH+1)+ky_hi)*(KW+1)+kx_lo)*(KW+1)+kx_hi;
 //                             otherwise a single row for the full filter
 //   mult_pad / shift_pad      RESCALE operands expanded per channel (per_channel == 0 repeats element 0), zero padded
+// Also writes, when `rec` is given, one record per column for the tensor-core epilogue's lean RESCALE form (see
+// rescale_rec_build) and, for padded layers with an input zero point, `delta`: per class of clipped tap rectangle the
+// difference between that class's correction row and the interior one (all taps in scope), which border pixels add
+// to their accumulators before the common arithmetic.  `all_ok`, preset to non-zero by the caller, is cleared when some
+// column's record is unusable.
 __global__ void conv_epilogue_tables_kernel(const int8_t* __restrict__ w, const int32_t* __restrict__ bias, int bias_n,
                                             int OC, int OCpad, int KH, int KW, int IC, int32_t in_zp, int classes,
                                             const int32_t* __restrict__ mult, const int8_t* __restrict__ shift,
                                             int per_channel, int32_t* __restrict__ prefix, int32_t* __restrict__ corr,
-                                            int32_t* __restrict__ mult_pad, int8_t* __restrict__ shift_pad)
+                                            int32_t* __restrict__ mult_pad, int8_t* __restrict__ shift_pad,
+                                            int32_t* __restrict__ rec = nullptr, int32_t* __restrict__ delta = nullptr,
+                                            int double_round = 0, int32_t out_zp = 0, int* __restrict__ all_ok = nullptr)
 {
     // One warp per output channel: lanes split the channel run of each tap (128-bit loads), the warp-reduced tap
     // sums become 2-D prefix sums kept in registers by lane 0 .. and mirrored to `prefix` for the class loop, which
@@ -1215,12 +1222,18 @@ __global__ void conv_epilogue_tables_kernel(const int8_t* __restrict__ w, const 
     if (oc >= OC)
     {
         for (int c = lane; c < ncls; c += 32)
+        {
             corr[(int64_t)c * OCpad + oc] = 0;
+            if (delta)
+                delta[(int64_t)c * OCpad + oc] = 0;
+        }
         if (mult_pad && lane == 0)
         {
             mult_pad[oc]  = 0;
             shift_pad[oc] = 2;
         }
+        if (rec && lane < 8)
+            rec[(int64_t)oc * 8 + lane] = lane == 7 ? 1 : 0;    // a padding column never disqualifies its block
         return;
     }
     int32_t* P = prefix + (int64_t)oc * H1 * W1;    // this channel's (KH+1) x (KW+1) prefix sums
@@ -1261,10 +1274,11 @@ __global__ void conv_epilogue_tables_kernel(const int8_t* __restrict__ w, const 
         }
     __syncwarp();
     const int32_t b = bias[bias_n == 1 ? 0 : oc];
+    const int32_t corr_interior = b - in_zp * P[KH * W1 + KW];    // every tap in scope
     if (!classes)
     {
         if (lane == 0)
-            corr[oc] = b - in_zp * P[KH * W1 + KW];
+            corr[oc] = corr_interior;
     }
     else
     {
@@ -1275,12 +1289,28 @@ __global__ void conv_epilogue_tables_kernel(const int8_t* __restrict__ w, const 
             if (yh > yl && xh > xl)
                 rs = P[yh * W1 + xh] - P[yl * W1 + xh] - P[yh * W1 + xl] + P[yl * W1 + xl];
             corr[(int64_t)c * OCpad + oc] = b - in_zp * rs;
+            if (delta)
+                delta[(int64_t)c * OCpad + oc] = (b - in_zp * rs) - corr_interior;
         }
     }
     if (mult_pad && lane == 0)
     {
         mult_pad[oc]  = mult[per_channel ? oc : 0];
         shift_pad[oc] = shift[per_channel ? oc : 0];
+    }
+    if (rec && lane == 0)
+    {
+        // largest magnitude bias + accumulator can reach: every tap at full scale |x - zp| <= 255, |w| <= 128
+        const int64_t vmax = (int64_t)KH * KW * IC * 255 * 128 + (b < 0 ? -(int64_t)b : (int64_t)b);
+        int32_t r8[8];
+        rescale_rec_build(mult[per_channel ? oc : 0], (int32_t)shift[per_channel ? oc : 0], double_round, out_zp,
+                          corr_interior, vmax, r8);
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            rec[(int64_t)oc * 8 + i] = r8[i];
+        // one word for the host (preset to non-zero): does every column of the layer have a usable record?
+        if (all_ok != nullptr && r8[7] == 0)
+            *all_ok = 0;
     }
 }
 

@@ -61,4 +61,70 @@ __host__ __device__ __forceinline__ int64_t value_extend64_dev(int32_t val, int 
     return is_unsigned ? (int64_t)(uint32_t)val : (int64_t)val;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Lean form of apply_scale_32 + output zero point for the tensor-core epilogue (int8 outputs).
+//
+// QuantUtil::apply_scale_32 (reference_model/src/quant_util.h:45-84) computes (v * m + round) >> shift with
+// round = 2^(shift-1), plus or minus 2^30 by the sign of v under double rounding when shift > 31.  Here every column
+// gets one record, built once from its constants, so that the per-element work is two multiply-adds and two shifts:
+//
+//     s  = acc * pk + cpk          (32-bit; pk a power of two, cpk = correction * pk: the zero-point / bias term rides
+//                                   on the pre-scale; wraps mod 2^32, the true value fits)
+//     P  = s * m + R               (64-bit)
+//     z  = (hi(P) + (s < 0 ? -dr : 0)) >> sh
+//
+//   shift <= 31: pk = 2^(32-shift), sh = 0, dr = 0, R = 2^31 + out_zp * 2^32: the product is aligned to the high word
+//                (no double rounding exists below shift 32);
+//   shift >= 32: pk = 2, sh = shift - 31, R = 2^shift + DR * 2^31 + out_zp * 2^(shift+1): everything is doubled, which
+//                makes the two rounding constants of double rounding differ by exactly 2^32, i.e. by one in the high
+//                word and nothing in the low word, so the sign-dependent choice is the -dr above.
+// out_zp added before the shift by its full weight comes out as exactly out_zp after it.  z still has to be saturated
+// to int8 (cvt.pack.sat does it).  The form is exact when t = acc + correction satisfies |t| < 2^(shift-1) for
+// shift <= 31 (which is also apply_scale_32's own REQUIRE, so it can never fail) and |t| < 2^30 for shift >= 32;
+// `vmax`, the largest magnitude t can take for this column given the layer's K and its bias, proves that statically or
+// the record is marked unusable (word 7 = 0) and the block takes the general epilogue.
+// Record words: {m, pk, cpk, sh | dr << 8, R low, R high, 0, usable}.
+__host__ __device__ __forceinline__ void rescale_rec_build(int32_t m, int32_t shift, int double_round, int32_t out_zp,
+                                                            int32_t correction, int64_t vmax, int32_t r8[8])
+{
+    bool ok = (m >= 0) && (shift >= 2) && (shift <= 53) && (out_zp >= -128) && (out_zp <= 127);
+    const int32_t sc = shift < 2 ? 2 : (shift > 53 ? 53 : shift);
+    int32_t pk, sh, dr = 0;
+    int64_t R;
+    if (sc <= 31)
+    {
+        ok  = ok && vmax < ((int64_t)1 << (sc - 1));
+        pk  = (int32_t)1 << (32 - sc);
+        sh  = 0;
+        R   = ((int64_t)1 << 31) + (int64_t)out_zp * ((int64_t)1 << 32);
+    }
+    else
+    {
+        ok  = ok && vmax < ((int64_t)1 << 30);
+        pk  = 2;
+        sh  = sc - 31;
+        dr  = double_round ? 1 : 0;
+        R   = ((int64_t)1 << sc) + (double_round ? ((int64_t)1 << 31) : 0) + (int64_t)out_zp * ((int64_t)1 << (sc + 1));
+    }
+    r8[0] = m;
+    r8[1] = pk;
+    r8[2] = (int32_t)((uint32_t)correction * (uint32_t)pk);
+    r8[3] = sh | (dr << 8);
+    r8[4] = (int32_t)(uint32_t)(R & 0xffffffffLL);
+    r8[5] = (int32_t)(R >> 32);
+    r8[6] = 0;
+    r8[7] = ok ? 1 : 0;
+}
+
+// One accumulator through the lean form; the result still needs saturation to int8.
+__host__ __device__ __forceinline__ int32_t rescale_rec_apply(int32_t acc, int32_t m, int32_t pk, int32_t cpk, int32_t shdr,
+                                                               int32_t rlo, int32_t rhi)
+{
+    const int32_t s  = (int32_t)((uint32_t)acc * (uint32_t)pk + (uint32_t)cpk);
+    const int32_t sg = s >> 31;
+    const int64_t P  = (int64_t)s * (int64_t)m + (int64_t)(((uint64_t)(uint32_t)rhi << 32) | (uint32_t)rlo);
+    const int32_t hi = (int32_t)(P >> 32) + sg * (shdr >> 8);
+    return hi >> (shdr & 31);
+}
+
 }    // namespace tb200

@@ -1,0 +1,431 @@
+// int8 CONV2D + RESCALE (+ CLAMP) to int8 on tcgen05, the form the quantized graphs spend their time in.
+// Included by tc_gemm.cu inside its anonymous namespace (it shares TcKernelParams, the tile geometry and the tensor
+// maps with the general kernel); the host chooses it when every column's lean RESCALE record is usable
+// (rescale_rec_build), the output is a dense, 32-byte aligned int8 tensor and the channel count is a multiple of 32.
+//
+// What measurement on this part said, and what this kernel does about it:
+//   * every tcgen05.commit idles the tensor pipe for 300-700 cycles (a 128 x 64 x 32 MMA takes 104): a tile whose
+//     operands fit one shared-memory slot is ONE stage, and its single commit both frees the slot and publishes the
+//     accumulator; larger K is cut into the fewest stages that fit;
+//   * for N <= 128 the MMA rate does not depend on N, so small layers are bound by bytes and commits, not by math: the
+//     weights of a layer with one column block are loaded once per CTA and stay (a third of the traffic of a 3x3
+//     64 -> 64 layer);
+//   * the fused epilogue is bound by integer issue and by latency: sixteen epilogue warps (four per scheduler) on one
+//     CTA per SM, the lean RESCALE form (two multiply-adds and two shifts per output, constants from shared memory,
+//     no range check left to do), accumulators fetched sixteen columns at a time (a 32-column tcgen05.ld
+//     costs five times two 16-column ones, and sixteen live values keep the loop out of local memory);
+//   * two accumulator buffers: warps 2..9 drain one tile while the MMAs fill the other and warps 10..17 wait for it.
+// Roles: warp 0 lane 0 TMA producer, warp 1 lane 0 MMA issuer, warps 2..17 epilogue in four groups of four warps
+// (a warp reads the TMEM lane quarter `warp % 4`); groups 0, 1 share accumulator buffer 0 (even / odd 32-column
+// chunks), groups 2, 3 buffer 1.  Every wait is bounded (p.wait_limit); a wait that gives up sets TB200_DEV_TIMEOUT,
+// the roles leave their loops, copies and MMAs in flight are waited for, TMEM is freed.
+
+constexpr int kLeanEpiWarps  = 16;
+constexpr int kLeanThreads   = 64 + 32 * kLeanEpiWarps;
+constexpr int kLeanAccBufs   = 2;
+constexpr int kLeanGroupsPerTile = 2;    // epilogue groups that share one accumulator buffer
+
+// tiles are numbered column block major here: a CTA stays in one column block as long as it can
+__device__ __forceinline__ TileCoord lean_decode_tile(const TcKernelParams& p, int tile)
+{
+    TileCoord t;
+    const int tiles_m = p.tiles_x * p.tiles_y * p.tiles_n;
+    const int cb      = tile / tiles_m;
+    int r             = tile - cb * tiles_m;
+    t.col0            = cb * p.block_n;
+    t.x0              = (r % p.tiles_x) * p.BW;
+    r /= p.tiles_x;
+    t.y0 = (r % p.tiles_y) * p.BH;
+    t.n0 = (r / p.tiles_y) * p.BN;
+    return t;
+}
+
+// Sixteen accumulators of one row through the lean RESCALE form, saturated and packed to sixteen int8.  `delta`, for a
+// border pixel, points at what its class of clipped tap rectangle adds to the interior correction (added four columns
+// at a time, right before they are used, to keep few values alive).
+__device__ __forceinline__ void lean_rescale_x16(const uint32_t (&v)[16], const int32_t (*rec)[8], const int32_t* delta,
+                                                 uint32_t (&w)[4])
+{
+#pragma unroll
+    for (int q = 0; q < 4; q++)
+    {
+        int4 d = make_int4(0, 0, 0, 0);
+        if (delta != nullptr)
+            d = __ldg(reinterpret_cast<const int4*>(delta) + q);
+        const int32_t dv[4] = { d.x, d.y, d.z, d.w };
+        int32_t z[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+        {
+            const int4 r0 = *reinterpret_cast<const int4*>(&rec[4 * q + j][0]);
+            const int2 r1 = *reinterpret_cast<const int2*>(&rec[4 * q + j][4]);
+            z[j] = rescale_rec_apply((int32_t)(v[4 * q + j] + (uint32_t)dv[j]), r0.x, r0.y, r0.z, r0.w, r1.x, r1.y);
+        }
+        w[q] = pack4_sat_i8(z[0], z[1], z[2], z[3]);
+    }
+}
+
+// (18 warps: the register file is four partitions of 16 K registers, one per scheduler, and the fullest partition holds
+// five of these warps, so a thread gets 96 registers, not the 112 that 65536 / 576 would suggest)
+// CLASSES: the layer has border classes (padding with a non-zero input zero point); the instantiation without them
+// carries no trace of the border path, which keeps its epilogue loop free of register spills.
+template <bool CLASSES>
+__global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __grid_constant__ TcKernelParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[kMaxStages];     // TMA -> MMA: the stage's bytes have landed
+    __shared__ __align__(8) uint64_t bar_empty[kMaxStages];    // MMA -> TMA (several stages per tile only): stage consumed
+    __shared__ __align__(8) uint64_t bar_acc_full[kLeanAccBufs];     // MMA -> epilogue (and -> TMA when a tile is one stage)
+    __shared__ __align__(8) uint64_t bar_acc_empty[kLeanAccBufs];    // epilogue -> MMA: accumulator buffer drained
+    __shared__ __align__(8) uint64_t bar_b;        // resident weights have landed
+    __shared__ __align__(8) uint64_t bar_drain;    // teardown after a wait gave up
+    __shared__ uint32_t tmem_base_holder;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* const smem_al   = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+    const uint32_t s_b       = smem_base + (uint32_t)p.lean_b_off;       // resident weights (when p.lean_b_resident)
+    const uint32_t s_ring    = smem_base + (uint32_t)p.lean_ring_off;    // stages: ksub A chunks, then ksub B chunks if streamed
+    const bool one_stage     = p.lean_stages_per_tile == 1;
+    if (threadIdx.x == 0)
+        TB200_TRACE(p, 0);
+
+    if (threadIdx.x == 0)
+    {
+        for (int s = 0; s < p.num_stages; s++)
+        {
+            ptx::mbar_init(ptx::smem_u32(&bar_full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bar_empty[s]), 1);
+        }
+        for (int a = 0; a < kLeanAccBufs; a++)
+        {
+            ptx::mbar_init(ptx::smem_u32(&bar_acc_full[a]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bar_acc_empty[a]), 4 * kLeanGroupsPerTile);    // one arrival per epilogue warp
+        }
+        ptx::mbar_init(ptx::smem_u32(&bar_b), 1);
+        ptx::mbar_init(ptx::smem_u32(&bar_drain), 1);
+        abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tmap(&p.tmA);
+        ptx::prefetch_tmap(&p.tmB);
+    }
+    if (warp == 1)
+    {
+        ptx::tmem_alloc(ptx::smem_u32(&tmem_base_holder), (uint32_t)p.tmem_cols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_holder;
+    const int my_tiles = (p.tile_end - p.tile_begin - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    if (threadIdx.x == 0)
+        TB200_TRACE(p, 1);
+
+    if (warp == 0)
+    {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0)
+        {
+            bool ok = true;
+            if (p.lean_b_resident)
+            {
+                // the whole K extent of the (only) column block, once
+                ptx::mbar_arrive_expect_tx(ptx::smem_u32(&bar_b), (uint32_t)(p.total_chunks * p.block_n * (p.chunk_elems)));
+                for (int ch = 0; ch < p.total_chunks; ch++)
+                    ptx::tma_load_3d(s_b + (uint32_t)(ch * p.b_chunk_bytes), &p.tmB, ptx::smem_u32(&bar_b), ch * p.chunk_elems, 0, 0);
+            }
+            int stage = 0;
+            uint32_t phase = 0;
+            const int a_chunk_bytes = p.a_chunk_bytes, b_chunk_bytes = p.b_chunk_bytes, chunk_elems = p.chunk_elems;
+            const uint32_t tx_per_chunk = (uint32_t)p.tx_bytes_per_chunk;
+            for (int i = 0; i < my_tiles && ok; i++)
+            {
+                const TileCoord t = lean_decode_tile(p, p.tile_begin + (int)blockIdx.x + i * (int)gridDim.x);
+                const int ax0 = t.x0 * p.stride_x - p.pad_l;
+                const int ay0 = t.y0 * p.stride_y - p.pad_t;
+                int chunk_k = 0, cc = 0, ky = 0, kx = 0;
+                int chunks_left = p.total_chunks;
+                while (chunks_left > 0)
+                {
+                    // a one-stage tile's slot is released by the commit that publishes its accumulator
+                    const uint32_t free_bar = one_stage ? ptx::smem_u32(&bar_acc_full[stage]) : ptx::smem_u32(&bar_empty[stage]);
+                    if (!ptx::mbar_wait_bounded(free_bar, phase ^ 1u, p.wait_limit))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    const int nchunks = min(p.ksub, chunks_left);
+                    chunks_left -= nchunks;
+                    const uint32_t full = ptx::smem_u32(&bar_full[stage]);
+                    uint32_t sA = s_ring + (uint32_t)(stage * p.stage_bytes);
+                    uint32_t sB = sA + (uint32_t)(p.ksub * a_chunk_bytes);
+                    ptx::mbar_arrive_expect_tx(full, (uint32_t)nchunks * tx_per_chunk);
+                    for (int j = 0; j < nchunks; j++)
+                    {
+                        ptx::tma_load_4d(sA, &p.tmA, full, cc * chunk_elems, ax0 + kx * p.dil_x, ay0 + ky * p.dil_y, t.n0);
+                        if (!p.lean_b_resident)
+                        {
+                            ptx::tma_load_3d(sB, &p.tmB, full, chunk_k, t.col0, 0);
+                            sB += b_chunk_bytes;
+                        }
+                        sA += a_chunk_bytes;
+                        chunk_k += chunk_elems;
+                        if (++cc == p.chunks_per_tap)
+                        {
+                            cc = 0;
+                            if (++kx == p.KW)
+                            {
+                                kx = 0;
+                                ky++;
+                            }
+                        }
+                    }
+                    if (++stage == p.num_stages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (i == 0)
+                    TB200_TRACE(p, 2);
+            }
+            TB200_TRACE(p, 3);
+            if (!ok)
+            {
+                atomicOr(p.status, TB200_DEV_TIMEOUT);
+                atomicExch(&abort_flag, 1);
+            }
+        }
+    }
+    else if (warp == 1)
+    {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0)
+        {
+            bool ok = true;
+            if (p.lean_b_resident)
+            {
+                ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_b), 0u, p.wait_limit);
+                ptx::tc_fence_after_sync();
+            }
+            int stage = 0;
+            uint32_t phase = 0;
+            const int mmas = p.mmas_per_chunk;
+            const uint32_t idesc = p.idesc;
+            const uint64_t a_chunk16 = (uint64_t)(p.a_chunk_bytes >> 4), b_chunk16 = (uint64_t)(p.b_chunk_bytes >> 4);
+            for (int i = 0; i < my_tiles && ok; i++)
+            {
+                const int acc            = i & 1;
+                const uint32_t acc_phase = (uint32_t)(i >> 1) & 1u;
+                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, p.wait_limit))
+                {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.block_n);
+                uint32_t accum  = 0;
+                int chunk_index = 0;
+                int chunks_left = p.total_chunks;
+                while (chunks_left > 0)
+                {
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_full[stage]), phase, p.wait_limit))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    if (i == 0 && chunks_left == p.total_chunks)
+                        TB200_TRACE(p, 4);
+                    const int nchunks = min(p.ksub, chunks_left);
+                    chunks_left -= nchunks;
+                    const uint32_t sA = s_ring + (uint32_t)(stage * p.stage_bytes);
+                    uint64_t ad_chunk = ptx::smem_desc(p.a_desc_hi, sA);
+                    uint64_t bd_chunk = p.lean_b_resident
+                                            ? ptx::smem_desc(p.b_desc_hi, s_b + (uint32_t)(chunk_index * p.b_chunk_bytes))
+                                            : ptx::smem_desc(p.b_desc_hi, sA + (uint32_t)(p.ksub * p.a_chunk_bytes));
+                    for (int j = 0; j < nchunks; j++)
+                    {
+                        uint64_t ad = ad_chunk, bd = bd_chunk;
+                        for (int m = 0; m < mmas; m++)
+                        {
+                            ptx::mma_i8_ss(d_tmem, ad, bd, idesc, accum);
+                            accum = 1;
+                            ad += 2;    // 32 bytes of K
+                            bd += 2;
+                        }
+                        ad_chunk += a_chunk16;
+                        bd_chunk += b_chunk16;
+                    }
+                    chunk_index += nchunks;
+                    if (!one_stage)
+                        ptx::mma_commit(ptx::smem_u32(&bar_empty[stage]));
+                    if (++stage == p.num_stages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok)
+                    break;
+                ptx::mma_commit(ptx::smem_u32(&bar_acc_full[acc]));
+                if (i == 0)
+                    TB200_TRACE(p, 5);
+            }
+            TB200_TRACE(p, 6);
+            if (!ok)
+            {
+                atomicOr(p.status, TB200_DEV_TIMEOUT);
+                atomicExch(&abort_flag, 1);
+            }
+        }
+    }
+    else
+    {
+        // ------------------------------------------------------------------ epilogue: 4 groups of 4 warps
+        const int quarter = warp & 3;                  // TMEM lane quarter this warp may read
+        const int group   = (warp - 2) >> 2;           // 0..3
+        const int acc     = group / kLeanGroupsPerTile;    // accumulator buffer of this group
+        const int sub     = group % kLeanGroupsPerTile;    // which 32-column chunks of a tile it takes
+        const int gtid    = (int)threadIdx.x - 64 - group * 128;    // 0..127 inside the group
+        int32_t(*rec)[8]  = reinterpret_cast<int32_t(*)[8]>(smem_al + p.lean_rec_off + (size_t)group * p.block_n * 32);
+        const int row     = quarter * 32 + lane;
+        const int xx      = row % p.BW;
+        const int yy      = (row / p.BW) % p.BH;
+        const int nn      = row / (p.BW * p.BH);
+        const bool narrow_clamp = p.clamp_lo > -128 || p.clamp_hi < 127;
+        const uint32_t lo4 = (uint32_t)(p.clamp_lo & 0xff) * 0x01010101u;
+        const uint32_t hi4 = (uint32_t)(p.clamp_hi & 0xff) * 0x01010101u;
+        const int nchunks32 = p.block_n / 32;
+        int loaded_col0 = -1;
+        bool ok = true;
+        for (int i = acc; i < my_tiles; i += kLeanAccBufs)
+        {
+            const TileCoord t = lean_decode_tile(p, p.tile_begin + (int)blockIdx.x + i * (int)gridDim.x);
+            if (loaded_col0 != t.col0)
+            {
+                // this group's copy of the column block's records (the barrier also keeps the copy from overtaking the
+                // group's last reads of the previous block)
+                asm volatile("bar.sync %0, 128;" ::"r"(2 + group) : "memory");
+                for (int c = gtid; c < p.block_n; c += 128)
+                {
+                    const int4* rp = reinterpret_cast<const int4*>(p.rec + (int64_t)(t.col0 + c) * 8);
+                    *reinterpret_cast<int4*>(&rec[c][0]) = __ldg(rp);
+                    *reinterpret_cast<int4*>(&rec[c][4]) = __ldg(rp + 1);
+                }
+                asm volatile("bar.sync %0, 128;" ::"r"(2 + group) : "memory");
+                loaded_col0 = t.col0;
+            }
+            // After a wait has given up, this warp keeps walking its tiles only to meet its group at the barrier above
+            // (the other three warps may still be working); it does no further work.
+            if (!ok)
+                continue;
+            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_full[acc]), (uint32_t)(i >> 1) & 1u, p.wait_limit);
+            ok = __all_sync(0xffffffffu, ok);    // the whole warp agrees before the warp-collective TMEM loads
+            if (!ok)
+                continue;
+            ptx::tc_fence_after_sync();
+            if (threadIdx.x == 64 && i == 0)
+                TB200_TRACE(p, 7);
+
+            const int ox = t.x0 + xx, oy = t.y0 + yy, on = t.n0 + nn;
+            const bool row_valid = (nn < p.BN) && (ox < p.OW) && (oy < p.OH) && (on < p.N);
+            int8_t* out_row = reinterpret_cast<int8_t*>(p.out) + (((int64_t)on * p.OH + oy) * p.OW + ox) * p.OC;
+            const int32_t* delta_row = nullptr;
+            if (CLASSES && row_valid)
+            {
+                int ky_lo = 0, ky_hi = p.KH, kx_lo = 0, kx_hi = p.KW;
+                const int iy0 = oy * p.stride_y - p.pad_t;
+                const int ix0 = ox * p.stride_x - p.pad_l;
+                if (iy0 < 0)
+                    ky_lo = (-iy0 + p.dil_y - 1) / p.dil_y;
+                if (ix0 < 0)
+                    kx_lo = (-ix0 + p.dil_x - 1) / p.dil_x;
+                if (iy0 + (p.KH - 1) * p.dil_y >= p.IH)
+                    ky_hi = iy0 >= p.IH ? 0 : (p.IH - 1 - iy0) / p.dil_y + 1;
+                if (ix0 + (p.KW - 1) * p.dil_x >= p.IW)
+                    kx_hi = ix0 >= p.IW ? 0 : (p.IW - 1 - ix0) / p.dil_x + 1;
+                ky_lo = min(ky_lo, p.KH);
+                kx_lo = min(kx_lo, p.KW);
+                ky_hi = max(ky_hi, ky_lo);
+                kx_hi = max(kx_hi, kx_lo);
+                const int cls = ((ky_lo * (p.KH + 1) + ky_hi) * (p.KW + 1) + kx_lo) * (p.KW + 1) + kx_hi;
+                if (cls != p.cls_interior)
+                    delta_row = p.delta + (int64_t)cls * p.corr_stride + t.col0;
+            }
+
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n);
+            // chunks past the last channel exist only in a last, partly filled column block (OC is a multiple of 32)
+            const int chunks_here = min(nchunks32, (p.OC - t.col0) / 32);
+            for (int c = sub; c < chunks_here; c += kLeanGroupsPerTile)
+            {
+                uint32_t w[8];
+#pragma unroll
+                for (int h = 0; h < 2; h++)
+                {
+                    uint32_t v[16];
+                    ptx::tmem_ld_32x32b_x16(taddr + (uint32_t)(c * 32 + h * 16), v);
+                    ptx::tmem_ld_wait();
+                    uint32_t w4[4];
+                    lean_rescale_x16(v, &rec[c * 32 + h * 16],
+                                     (CLASSES && delta_row != nullptr) ? delta_row + c * 32 + h * 16 : nullptr, w4);
+                    w[4 * h + 0] = w4[0]; w[4 * h + 1] = w4[1]; w[4 * h + 2] = w4[2]; w[4 * h + 3] = w4[3];
+                }
+                if (narrow_clamp)
+                {
+#pragma unroll
+                    for (int q = 0; q < 8; q++)
+                        w[q] = __vmins4(__vmaxs4(w[q], lo4), hi4);
+                }
+                if (row_valid)
+                    ptx::st_global_v8(out_row + t.col0 + c * 32, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+            }
+            // this warp has read its part of the buffer
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                ptx::mbar_arrive(ptx::smem_u32(&bar_acc_empty[acc]));
+            if (threadIdx.x == 64 && i == 0)
+                TB200_TRACE(p, 8);
+        }
+        if (threadIdx.x == 64)
+            TB200_TRACE(p, 9);
+        if (!ok && lane == 0)
+        {
+            atomicOr(p.status, TB200_DEV_TIMEOUT);
+            atomicExch(&abort_flag, 1);
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && abort_flag)
+    {
+        // a role gave up: let copies that may still be in flight land before the CTA's shared memory is released
+        for (int s = 0; s < p.num_stages; s++)
+        {
+            ptx::mbar_wait_bounded(ptx::smem_u32(&bar_full[s]), 0u, 2000000LL);
+            ptx::mbar_wait_bounded(ptx::smem_u32(&bar_full[s]), 1u, 2000000LL);
+        }
+        if (p.lean_b_resident)
+            ptx::mbar_wait_bounded(ptx::smem_u32(&bar_b), 0u, 2000000LL);
+    }
+    if (warp == 1 && lane == 0 && abort_flag)
+    {
+        // ... and let the tensor-core work already issued retire before its accumulators' tensor memory is freed
+        ptx::mma_commit(ptx::smem_u32(&bar_drain));
+        ptx::mbar_wait_bounded(ptx::smem_u32(&bar_drain), 0u, 40000000LL);
+    }
+    __syncthreads();
+    if (warp == 1)
+    {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    }
+    if (threadIdx.x == 0)
+        TB200_TRACE(p, 10);
+}

@@ -28,6 +28,24 @@ namespace tb200
 namespace
 {
 
+#ifdef TB200_DIAG
+#define TB200_TRACE(p, slot)                                                                              \
+    do                                                                                                    \
+    {                                                                                                     \
+        if ((p).trace)                                                                                    \
+        {                                                                                                 \
+            unsigned long long gt__;                                                                      \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt__));                                      \
+            (p).trace[(size_t)blockIdx.x * 16 + (slot)] = (long long)gt__;                                \
+        }                                                                                                 \
+    } while (0)
+#else
+#define TB200_TRACE(p, slot)                                                                              \
+    do                                                                                                    \
+    {                                                                                                     \
+    } while (0)
+#endif
+
 constexpr int kMaxStages   = 8;
 constexpr int kTileM       = 128;
 constexpr int kNumThreads  = 320;    // TMA warp, MMA warp, 8 epilogue warps
@@ -73,12 +91,23 @@ struct TcKernelParams
     const float* bias_f_pad;       // TC_EPI_FLOAT: padded fp32 bias or null
     const int32_t* mult_pad;       // TC_EPI_RESCALE: padded per-column multipliers and shifts
     const int8_t* shift_pad;
+    // TC_EPI_RESCALE, optional: one prepared record of 8 words per column for the lean RESCALE form (rescale_rec_build),
+    // and for layers with border classes the per-class difference to the interior correction row ([classes][corr_stride])
+    const int32_t* rec;
+    const int32_t* delta;
+    int cls_interior;
+    // tc_conv_lean_kernel only: shared-memory offsets from the 1024-byte aligned base (resident weights, stage ring,
+    // the four epilogue groups' record copies), whether the weights are resident, stages per tile
+    int lean_b_off, lean_ring_off, lean_rec_off, lean_b_resident, lean_stages_per_tile;
     int double_round;
     int32_t out_zp, clamp_lo, clamp_hi;
     float clamp_lo_f, clamp_hi_f;
     int has_clamp;
     int debug;    // diagnostic bit mask, read only by builds with TB200_DIAG: 1 skip epilogue memory work, 2 skip MMA issue, 4 skip loads
     long long wait_limit;    // SM cycles after which a pipeline wait gives up (TB200_DEV_TIMEOUT)
+#ifdef TB200_DIAG
+    long long* trace;        // diagnostic builds: [CTA][16] globaltimer stamps (ns) of the roles' milestones, or null
+#endif
     int* status;
 };
 
@@ -121,6 +150,7 @@ enum : int
 {
     EPI_COLS_GENERIC  = 1,    // some column has operands outside what the high-word form below handles
     EPI_COLS_PRESHIFT = 2,    // some shift is below 32: values are pre-scaled, and apply_scale_32's range check applies
+    EPI_COLS_NOT_LEAN = 4,    // some column's prepared record is marked unusable: the lean form is off for this block
 };
 
 // apply_scale_32 + output zero point + int8 saturation and packing of four accumulators, for column blocks whose
@@ -154,6 +184,8 @@ __device__ __forceinline__ uint32_t rescale32_high_x4(const uint32_t* v, const i
     return pack4_sat_i8(z[0], z[1], z[2], z[3]);
 }
 
+#include "tc_conv_lean.cuh"
+
 template <int EPI>
 __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_constant__ TcKernelParams p)
 {
@@ -173,6 +205,8 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0)
+        TB200_TRACE(p, 0);
 
     // ring buffer base, 1024-byte aligned (swizzle atoms repeat every 1024 bytes)
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -204,6 +238,8 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_holder;
+    if (threadIdx.x == 0)
+        TB200_TRACE(p, 1);
 
     if (warp == 0)
     {
@@ -286,7 +322,10 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         phase ^= 1u;
                     }
                 }
+                if (tile == p.tile_begin + (int)blockIdx.x)
+                    TB200_TRACE(p, 2);
             }
+            TB200_TRACE(p, 3);
             if (!ok)
             {
                 atomicOr(p.status, TB200_DEV_TIMEOUT);
@@ -334,6 +373,8 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                         break;
                     }
                     ptx::tc_fence_after_sync();
+                    if (tile == p.tile_begin + (int)blockIdx.x && chunks_left == p.total_chunks)
+                        TB200_TRACE(p, 4);
                     const int nchunks = min(ksub, chunks_left);
                     chunks_left -= nchunks;
                     if (issue)
@@ -379,12 +420,15 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                 if (!ok)
                     break;
                 ptx::mma_commit(ptx::smem_u32(&bar_tmem_full[acc]));
+                if (tile == p.tile_begin + (int)blockIdx.x)
+                    TB200_TRACE(p, 5);
                 if (++acc == p.acc_bufs)
                 {
                     acc = 0;
                     acc_phase ^= 1u;
                 }
             }
+            TB200_TRACE(p, 6);
             if (!ok)
             {
                 atomicOr(p.status, TB200_DEV_TIMEOUT);
@@ -406,6 +450,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
         bool ok = true;
         int dev_flags = 0;
         int cols_loaded_for = -1;
+        bool lean_block = false;    // the current column block runs the lean RESCALE form (same in every epilogue thread)
         for (int tile = p.tile_begin + blockIdx.x; tile < p.tile_end; tile += gridDim.x)
         {
             const TileCoord t = decode_tile(p, tile);
@@ -423,6 +468,30 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     epi_flags = shortable ? 0 : EPI_COLS_GENERIC;
                 }
                 asm volatile("bar.sync 1, 256;" ::: "memory");
+                // Lean form first: the records were prepared with the layer's other tables; one unusable column (its
+                // value range could not be proven small enough) sends the whole block to the forms below.
+                lean_block = false;
+                if (p.rec != nullptr && !(epi_flags & EPI_COLS_GENERIC))
+                {
+                    for (int c = (int)threadIdx.x - 64; c < p.block_n; c += kEpiThreads)
+                    {
+                        const int4* rp = reinterpret_cast<const int4*>(p.rec + (int64_t)(t.col0 + c) * 8);
+                        const int4 r0 = __ldg(rp), r1 = __ldg(rp + 1);
+                        if (r1.w == 0)
+                            atomicOr(&epi_flags, EPI_COLS_NOT_LEAN);
+                        *reinterpret_cast<int4*>(&epi_cols[c][0]) = r0;
+                        *reinterpret_cast<int4*>(&epi_cols[c][4]) = r1;
+                    }
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    lean_block = !(epi_flags & EPI_COLS_NOT_LEAN);
+                    if (lean_block)
+                    {
+                        cols_loaded_for = t.col0;
+                        goto cols_ready;
+                    }
+                    // (the general construction below overwrites epi_cols: every thread has read the flag by now)
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                }
                 for (int c = (int)threadIdx.x - 64; c < p.block_n; c += kEpiThreads)
                 {
                     if (t.col0 + c >= p.OC)
@@ -479,6 +548,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                 asm volatile("bar.sync 1, 256;" ::: "memory");
                 cols_loaded_for = t.col0;
             }
+        cols_ready:
             // After a wait has given up this warp only keeps visiting the named barrier above (the other epilogue
             // warps may still be running and would otherwise block on it); it does no further work.
             if (!ok)
@@ -489,6 +559,8 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             if (!ok)
                 continue;
             ptx::tc_fence_after_sync();
+            if (threadIdx.x == 64 && tile == p.tile_begin + (int)blockIdx.x)
+                TB200_TRACE(p, 7);
 
             const int ox = t.x0 + xx, oy = t.y0 + yy, on = t.n0 + nn;
             const bool row_valid = (nn < p.BN) && (ox < p.OW) && (oy < p.OH) && (on < p.N);
@@ -510,7 +582,8 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             // Additive per-column constants of this row (bias and zero-point terms).  For a padded convolution with a
             // non-zero input zero point the constant depends on which filter taps fall inside the image, so the table
             // has one row per (ky_lo, ky_hi, kx_lo, kx_hi) rectangle of in-scope taps; interior pixels share one row.
-            const int32_t* corr_row = nullptr;
+            const int32_t* corr_row  = nullptr;
+            const int32_t* delta_row = nullptr;    // lean form: what a border pixel adds to reach its own correction row
             if (EPI != TC_EPI_FLOAT && p.corr != nullptr)
             {
                 int cls = 0;
@@ -538,6 +611,8 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                 }
                 corr_row = p.corr + (int64_t)cls * p.corr_stride +
                            (int64_t)((p.corr_ystride && row_valid) ? oy : 0) * p.corr_ystride;
+                if (EPI == TC_EPI_RESCALE && p.corr_classes && p.delta != nullptr && cls != p.cls_interior)
+                    delta_row = p.delta + (int64_t)cls * p.corr_stride;
             }
             int32_t rc = 0;
             if (EPI == TC_EPI_I32 && p.row_corr != nullptr && row_valid)
@@ -570,7 +645,24 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     rv_pair       = false;    // such outputs are 32-byte aligned: the paired-lane store form is never taken
                 }
 
-                if (EPI != TC_EPI_FLOAT && corr_row != nullptr && !TB200_DIAG_BIT(p.debug, 16))
+                if (EPI == TC_EPI_RESCALE && lean_block)
+                {
+                    // the interior correction is part of the records; border pixels add their difference to it
+                    if (delta_row != nullptr)
+                    {
+                        const int4* dp = reinterpret_cast<const int4*>(delta_row + col);
+#pragma unroll
+                        for (int q = 0; q < 8; q++)
+                        {
+                            const int4 dv = __ldg(dp + q);
+                            v[4 * q + 0] += (uint32_t)dv.x;
+                            v[4 * q + 1] += (uint32_t)dv.y;
+                            v[4 * q + 2] += (uint32_t)dv.z;
+                            v[4 * q + 3] += (uint32_t)dv.w;
+                        }
+                    }
+                }
+                else if (EPI != TC_EPI_FLOAT && corr_row != nullptr && !TB200_DIAG_BIT(p.debug, 16))
                 {
                     // every per-column array is padded to a multiple of the tile width: unconditional 128-bit loads
                     const int4* cp = reinterpret_cast<const int4*>(corr_row + col);
@@ -627,7 +719,25 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                     {
                         bool bad = false;
                         uint32_t w[8];
-                        if (cflags & EPI_COLS_PRESHIFT)
+                        if (lean_block)
+                        {
+                            // no REQUIRE can fail here: the records exist only for columns whose value range was proven
+#pragma unroll
+                            for (int q = 0; q < 8; q++)
+                            {
+                                int32_t z[4];
+#pragma unroll
+                                for (int j = 0; j < 4; j++)
+                                {
+                                    const int32_t(*rcol)[8] = &epi_cols[c * 32 + 4 * q + j];
+                                    const int4 r0 = *reinterpret_cast<const int4*>(&(*rcol)[0]);
+                                    const int2 r1 = *reinterpret_cast<const int2*>(&(*rcol)[4]);
+                                    z[j] = rescale_rec_apply((int32_t)v[4 * q + j], r0.x, r0.y, r0.z, r0.w, r1.x, r1.y);
+                                }
+                                w[q] = pack4_sat_i8(z[0], z[1], z[2], z[3]);
+                            }
+                        }
+                        else if (cflags & EPI_COLS_PRESHIFT)
                         {
                             // some shift of the block is below 32: the range check of apply_scale_32 can fail there
                             int32_t vmax = -2147483647 - 1, vmin = 2147483647;
@@ -894,12 +1004,16 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
             }
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[acc]));
+            if (threadIdx.x == 64 && tile == p.tile_begin + (int)blockIdx.x)
+                TB200_TRACE(p, 8);
             if (++acc == p.acc_bufs)
             {
                 acc = 0;
                 acc_phase ^= 1u;
             }
         }
+        if (threadIdx.x == 64)
+            TB200_TRACE(p, 9);
         if (!ok && lane == 0)
         {
             atomicOr(p.status, TB200_DEV_TIMEOUT);
@@ -934,6 +1048,8 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
     }
+    if (threadIdx.x == 0)
+        TB200_TRACE(p, 10);
 }
 
 // ------------------------------------------------------------------------------------------------ host side
@@ -969,6 +1085,7 @@ struct TcPlan
     cuuint32_t b_box[3];
     CUtensorMapDataType dt;
     CUtensorMapSwizzle a_swz, b_swz;
+    bool lean;    // launch tc_conv_lean_kernel
 };
 
 bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
@@ -1240,6 +1357,75 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     return true;
 }
 
+
+// Re-plans a problem make_plan has laid out for tc_conv_lean_kernel: one CTA per SM, the fewest stages per tile that
+// fit (one when a tile's operands fit twice into shared memory), weights resident when there is a single column block.
+bool make_lean_plan(const TcProblem& q, int num_sms, int max_smem_optin, TcPlan* plan)
+{
+    if (diag_env_int("TB200_TC_LEAN", 1) == 0)
+        return false;
+    if (q.epi != TC_EPI_RESCALE || !q.lean_ok || q.rec == nullptr || q.b_mn_major || q.in_dtype != TB200_INT8 ||
+        q.out_dtype != TB200_INT8 || q.out_sy != 0 || q.tile_begin != 0 || q.tile_end != 0)
+        return false;
+    if ((q.OC % 32) != 0 || (reinterpret_cast<uintptr_t>(q.out) & 31) != 0)
+        return false;
+    if (q.clamp_lo < -128 || q.clamp_hi > 127 || q.clamp_lo > q.clamp_hi || q.out_zp < -128 || q.out_zp > 127)
+        return false;
+    if (q.corr_classes && q.delta == nullptr)
+        return false;
+    if (!make_plan(q, num_sms, plan, nullptr))
+        return false;
+    TcKernelParams& k = plan->kp;
+    const int budget     = (max_smem_optin > 0 ? max_smem_optin : 232448) - 1024 /* alignment */ - 2048 /* static + margin */;
+    const int rec_bytes  = 4 * k.block_n * 32;
+    const int b_tx       = k.block_n * k.chunk_elems;
+    const int a_tx       = k.tx_bytes_per_chunk - b_tx;
+    const int b_total    = k.total_chunks * k.b_chunk_bytes;
+    const bool b_res     = k.tiles_col == 1 && b_total <= 96 * 1024;
+    const int avail      = budget - rec_bytes - (b_res ? b_total : 0);
+    const int per_chunk  = k.a_chunk_bytes + (b_res ? 0 : k.b_chunk_bytes);
+    int ksub, spt, stages;
+    if (2 * k.total_chunks * per_chunk <= avail)
+    {
+        ksub   = k.total_chunks;
+        spt    = 1;
+        stages = kLeanAccBufs;    // a slot per accumulator buffer: one commit releases both
+    }
+    else
+    {
+        const int target = diag_env_int("TB200_LEAN_STAGE_KB", 48) * 1024;
+        ksub = std::max(1, std::min(k.total_chunks, target / per_chunk));
+        spt  = (k.total_chunks + ksub - 1) / ksub;
+        if (spt < 2)
+            spt = 2;
+        ksub   = (k.total_chunks + spt - 1) / spt;
+        spt    = (k.total_chunks + ksub - 1) / ksub;
+        stages = std::min(kMaxStages, avail / (ksub * per_chunk));
+        if (stages < 2 || spt < 2)
+            return false;
+    }
+    k.ksub                 = ksub;
+    k.num_kstages          = spt;
+    k.lean_stages_per_tile = spt;
+    k.num_stages           = stages;
+    k.stage_bytes          = ksub * per_chunk;
+    k.tx_bytes_per_chunk   = a_tx + (b_res ? 0 : b_tx);
+    k.lean_b_resident      = b_res ? 1 : 0;
+    k.lean_b_off           = 0;
+    k.lean_ring_off        = b_res ? b_total : 0;
+    k.lean_rec_off         = k.lean_ring_off + stages * k.stage_bytes;
+    k.acc_bufs             = kLeanAccBufs;
+    int cols = 32;
+    while (cols < kLeanAccBufs * k.block_n)
+        cols *= 2;
+    k.tmem_cols      = cols;
+    plan->smem_bytes = k.lean_rec_off + rec_bytes + 1024;
+    plan->ctas_per_sm = 1;
+    plan->grid        = std::max(1, std::min(k.num_tiles, num_sms));
+    plan->lean        = true;
+    return plan->smem_bytes <= budget + 1024;
+}
+
 }    // namespace
 
 bool tc_gemm_supported(const TcProblem& p, std::string* why)
@@ -1263,9 +1449,14 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
     if (tc_gemm_pair_supported(q, ctx->num_sms))
         return tc_gemm_pair_launch(ctx, q);
     TcPlan plan;
+    plan.lean = false;
     std::string why;
-    if (!make_plan(q, ctx->num_sms, &plan, &why))
-        return fail(ctx, TB200_ERROR, "tensor-core path not applicable: %s", why.c_str());
+    if (!make_lean_plan(q, ctx->num_sms, ctx->max_smem_optin, &plan))
+    {
+        plan.lean = false;
+        if (!make_plan(q, ctx->num_sms, &plan, &why))
+            return fail(ctx, TB200_ERROR, "tensor-core path not applicable: %s", why.c_str());
+    }
     PFN_encodeTiled enc = get_encode_fn();
     if (!enc)
         return fail(ctx, TB200_INTERNAL, "cuTensorMapEncodeTiled is not available from the driver");
@@ -1293,6 +1484,9 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
     k.bias_f_pad   = q.bias_f_pad;
     k.mult_pad     = q.mult_pad;
     k.shift_pad    = q.shift_pad;
+    k.rec          = q.rec;
+    k.delta        = q.delta;
+    k.cls_interior = ((0 * (q.KH + 1) + q.KH) * (q.KW + 1) + 0) * (q.KW + 1) + q.KW;
     k.double_round = q.double_round;
     k.out_zp       = q.out_zp;
     k.clamp_lo     = q.clamp_lo;
@@ -1302,8 +1496,36 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
     k.has_clamp    = q.has_clamp;
     k.status       = ctx->d_status;
     k.debug        = diag_env_int("TB200_TC_DEBUG", 0);
+#ifdef TB200_DIAG
+    {
+        // TB200_TC_TRACE=<device address>: room for 16 stamps per CTA (a tool allocates and reads it)
+        const char* tr = getenv("TB200_TC_TRACE");
+        k.trace        = tr ? reinterpret_cast<long long*>(strtoull(tr, nullptr, 0)) : nullptr;
+    }
+#endif
     k.wait_limit   = ctx->wait_limit_cycles;
 
+    if (plan.lean)
+    {
+        void (*lean)(const TcKernelParams) = k.corr_classes ? tc_conv_lean_kernel<true> : tc_conv_lean_kernel<false>;
+        const tb200_status ast = raise_smem_limit(ctx, k.corr_classes ? 5 : 4, reinterpret_cast<const void*>(lean), plan.smem_bytes);
+        if (ast != TB200_OK)
+            return ast;
+        timer_begin(ctx);
+        lean<<<plan.grid, kLeanThreads, plan.smem_bytes, ctx->stream>>>(k);
+        timer_end(ctx);
+        const tb200_status lst = post_launch(ctx, "tc_conv_lean_i8");
+        if (lst != TB200_OK)
+        {
+            // say what the launch asked for: the usual cause is a build whose register or shared-memory use grew
+            cudaFuncAttributes fa;
+            if (cudaFuncGetAttributes(&fa, reinterpret_cast<const void*>(lean)) == cudaSuccess)
+                ctx->err += " (" + std::to_string(kLeanThreads) + " threads x " + std::to_string(fa.numRegs) + " registers, " +
+                            std::to_string(plan.smem_bytes) + " + " + std::to_string((int)fa.sharedSizeBytes) +
+                            " bytes of shared memory, limit " + std::to_string(fa.maxDynamicSharedSizeBytes) + ")";
+        }
+        return lst;
+    }
     void (*kern)(const TcKernelParams) = nullptr;
     const char* name                   = "";
     switch (q.epi)

@@ -188,7 +188,7 @@ def test_resnet_stem_layer_batch_32(ctx):
     for rep in range(2):
         n0 = ctx.launch_count()
         ctx.conv2d(tx, tw, tbias, to, [3, 2, 3, 2], [2, 2], [1, 1], -128, 0, epi)
-        assert ctx.last_kernel() == "tc_gemm_i8_rescale"
+        assert ctx.last_kernel() == "tc_conv_lean_i8", ctx.last_kernel()
         launches = ctx.launch_count() - n0
         st, out = to.download()
         assert st == tb.Status.OK and np.array_equal(out.astype(np.int32), exp), "call %d" % rep

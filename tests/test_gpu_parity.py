@@ -27,8 +27,13 @@ def _free(*ts):
         t.free()
 
 
-def run_conv_i8(ctx, x, w, b, pad, stride, dil, izp, wzp, rescale=None, clamp=None, depthwise=False, policy=0):
-    """Runs CONV2D / DEPTHWISE (optionally with a fused RESCALE [+CLAMP]) on the device; returns (status, out, kernel)."""
+LEAN = "tc_conv_lean_i8"        # the dedicated CONV2D + RESCALE -> int8 kernel (chosen when the constant cache has proven
+GENERAL = "tc_gemm_i8_rescale"  # every column's lean record usable); the general tensor-core kernel takes the rest
+
+
+def run_conv_i8(ctx, x, w, b, pad, stride, dil, izp, wzp, rescale=None, clamp=None, depthwise=False, policy=0, cache=True):
+    """Runs CONV2D / DEPTHWISE (optionally with a fused RESCALE [+CLAMP]) on the device; returns (status, out, kernel).
+    cache=False switches the constant cache off for the call, which also keeps the convolution on the general kernel."""
     N, IH, IW, IC = x.shape
     if depthwise:
         KH, KW, _, M = w.shape
@@ -47,10 +52,16 @@ def run_conv_i8(ctx, x, w, b, pad, stride, dil, izp, wzp, rescale=None, clamp=No
         out_dt = I8
     to = ctx.empty(out_dt, (N, OH, OW, OC))
     old = ctx.set_kernel_policy(policy)
+    if not cache:
+        ctx.const_cache_control(ctx.CACHE_OFF)
     fn = ctx.depthwise_conv2d if depthwise else ctx.conv2d
-    fn(tx, tw, tbias, to, pad, stride, dil, izp, wzp, epi)
-    kernel = ctx.last_kernel()
-    ctx.set_kernel_policy(old)
+    try:
+        fn(tx, tw, tbias, to, pad, stride, dil, izp, wzp, epi)
+        kernel = ctx.last_kernel()
+    finally:
+        ctx.set_kernel_policy(old)
+        if not cache:
+            ctx.const_cache_control(ctx.CACHE_ON)
     st, out = to.download()
     _free(tx, tw, tbias, to, *extra)
     return st, out, kernel
@@ -288,9 +299,10 @@ def test_tensor_core_conv_int8(ctx, case):
     resc = (mult, shift, -128, "DOUBLE_ROUND")
     est, exp = oracle_conv_i8(x, w, b, *args, rescale=resc, clamp=(-128, 127))
     assert est == orc.VALID
-    st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=(-128, 127))
-    assert kernel == "tc_gemm_i8_rescale" and st == tb.Status.OK
-    assert np.array_equal(out, exp), "rescaled outputs differ: %d of %d" % ((out != exp).sum(), exp.size)
+    for cache, want in ((True, LEAN if OC % 32 == 0 else GENERAL), (False, GENERAL)):
+        st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=(-128, 127), cache=cache)
+        assert kernel == want and st == tb.Status.OK, (kernel, want)
+        assert np.array_equal(out, exp), "%s: rescaled outputs differ: %d of %d" % (kernel, (out != exp).sum(), exp.size)
     # the CUDA-core kernel must agree as well
     st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=(-128, 127), policy=1)
     assert kernel == "conv2d_direct" and np.array_equal(out, exp)
@@ -359,9 +371,13 @@ def test_fused_rescale_forms(ctx, case):
     resc = (mult, shift, ozp, rounding)
     est, exp = oracle_conv_i8(x, w, b, *args, rescale=resc, clamp=clamp)
     assert est == orc.VALID
-    st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=clamp)
-    assert kernel == "tc_gemm_i8_rescale" and st == tb.Status.OK
-    assert np.array_equal(out, exp), "rescaled outputs differ: %d of %d" % ((out != exp).sum(), exp.size)
+    kernels = set()
+    for cache in (True, False):
+        st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=clamp, cache=cache)
+        kernels.add(kernel)
+        assert kernel in (LEAN, GENERAL) and st == tb.Status.OK, kernel
+        assert np.array_equal(out, exp), "%s: rescaled outputs differ: %d of %d" % (kernel, (out != exp).sum(), exp.size)
+    assert GENERAL in kernels
     assert len(np.unique(exp)) > 4    # the case must not saturate everywhere
 
 
@@ -1215,8 +1231,9 @@ def test_resnet_3x3_layer_full_size(ctx):
     args = ([1, 1, 1, 1], [1, 1], [1, 1], -128, 0)
     est, exp = oracle_conv_i8(x, w, b, *args, rescale=resc, clamp=(-128, 127))
     assert est == orc.VALID
-    st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=(-128, 127))
-    assert kernel == "tc_gemm_i8_rescale" and st == tb.Status.OK and np.array_equal(out, exp)
+    for cache, want in ((True, LEAN), (False, GENERAL)):
+        st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=(-128, 127), cache=cache)
+        assert kernel == want and st == tb.Status.OK and np.array_equal(out, exp), kernel
 
 
 def test_resnet_stem_layer(ctx):
