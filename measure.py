@@ -150,6 +150,38 @@ def matmul_f16_config(ctx, timer, name, N, H, C, W, iters, seed):
             "algorithmic_ops": ops, "algorithmic_bytes": nbytes, "l2": note}
 
 
+def matmul_f32_config(ctx, timer, name, N, H, C, W, iters, seed):
+    """fp32 x fp32 -> fp32 batched MATMUL (FFMA kernel, no TF32)."""
+    r = np.random.default_rng(seed)
+    a = r.standard_normal((N, H, C), dtype=np.float32)
+    b = r.standard_normal((N, C, W), dtype=np.float32)
+    ta, tbb = ctx.from_numpy(a), ctx.from_numpy(b)
+    to = ctx.empty(tb.DType.FP32, (N, H, W))
+    fn = lambda: ctx.matmul(ta, tbb, to)
+    nbytes = a.nbytes + b.nbytes + N * H * W * 4
+    ms, note = timer.time(fn, iters, nbytes)
+    ops = 2.0 * N * H * C * W
+    peak = 148 * 128 * 2 * 1.965e9 / 1e12
+    return {"config": name, "kernel": ctx.last_kernel(), "ms": ms, "TFLOPS": ops / ms / 1e9, "frac_of_ffma_peak": ops / ms / 1e9 / peak,
+            "GBps": nbytes / ms / 1e6, "algorithmic_ops": ops, "algorithmic_bytes": nbytes, "l2": note}
+
+
+def depthwise_f16_config(ctx, timer, name, N, H, W, C, iters, seed):
+    """fp16 3x3 DEPTHWISE_CONV2D, stride 2, pad [1,0,1,0], multiplier 1, + CLAMP [0,6] (the inverted-residual block's)."""
+    r = np.random.default_rng(seed)
+    x = r.standard_normal((N, H, W, C)).astype(np.float16)
+    w = (r.standard_normal((3, 3, C, 1)) / 3).astype(np.float16)
+    b = np.zeros(C, np.float16)
+    tx, tw, tbias = ctx.from_numpy(x), ctx.from_numpy(w), ctx.from_numpy(b)
+    to = ctx.empty(tb.DType.FP16, (N, H // 2, W // 2, C))
+    relu6 = tb.Epilogue(None, (0.0, 6.0))
+    fn = lambda: ctx.depthwise_conv2d(tx, tw, tbias, to, [1, 0, 1, 0], [2, 2], [1, 1], 0, 0, relu6)
+    nbytes = x.nbytes + N * (H // 2) * (W // 2) * C * 2
+    ms, note = timer.time(fn, iters, nbytes)
+    return {"config": name, "kernel": ctx.last_kernel(), "ms": ms, "GBps": nbytes / ms / 1e6, "algorithmic_bytes": nbytes,
+            "l2": note}
+
+
 def graph_profile(batch):
     """Per-step times of one eager evaluation of the benchmark graph (each step bracketed by a device sync, so the sum
     exceeds the replayed graph's time; the shares are what this is for)."""
@@ -191,6 +223,8 @@ def main():
                     help="also time one int8 TRANSPOSE_CONV2D+RESCALE+CLAMP layer: N,IH,IW,IC,OC,K,stride,out_pad")
     ap.add_argument("--matmul-fp8", default=None, help="also time one FP8E4M3 MATMUL with FP16 output: N,H,C,W")
     ap.add_argument("--matmul-f16", default=None, help="also time one fp16 MATMUL with fp16 output: N,H,C,W")
+    ap.add_argument("--matmul-f32", default=None, help="also time one fp32 MATMUL (FFMA kernel): N,H,C,W")
+    ap.add_argument("--depthwise-f16", default=None, help="also time one fp16 3x3 stride-2 DEPTHWISE_CONV2D + CLAMP: N,H,W,C")
     ap.add_argument("--join", default=None,
                     help="also time one fused int8 residual join (RESCALE x2, ADD, RESCALE, CLAMP): N,H,W,C")
     ap.add_argument("--graph-profile", type=int, default=0, metavar="BATCH",
@@ -229,6 +263,14 @@ def main():
         if args.matmul_f16:
             n, h, c, w = [int(v) for v in args.matmul_f16.split(",")]
             print(json.dumps(matmul_f16_config(ctx, timer, "matmul fp16 %s" % args.matmul_f16, n, h, c, w, args.iters, 17)))
+            sys.stdout.flush()
+        if args.matmul_f32:
+            n, h, c, w = [int(v) for v in args.matmul_f32.split(",")]
+            print(json.dumps(matmul_f32_config(ctx, timer, "matmul fp32 %s" % args.matmul_f32, n, h, c, w, args.iters, 19)))
+            sys.stdout.flush()
+        if args.depthwise_f16:
+            n, h, w, c = [int(v) for v in args.depthwise_f16.split(",")]
+            print(json.dumps(depthwise_f16_config(ctx, timer, "depthwise fp16 %s" % args.depthwise_f16, n, h, w, c, args.iters, 23)))
             sys.stdout.flush()
         if args.join:
             shape = tuple(int(v) for v in args.join.split(","))
