@@ -200,15 +200,36 @@ def graph_profile(batch):
         return time.perf_counter()
 
     run.profile(stamp)
-    rows = run.profile(stamp)
-    print(json.dumps({"graph": "resnet50_int8", "batch": batch, "steps": len(rows), "sum_ms": sum(r[3] for r in rows)}))
-    for r in sorted(rows, key=lambda r: -r[3])[:24]:
-        print("%-20s %-16s %-24s %8.3f ms  shape=%s" % (r[0], r[1], r[2], r[3], g.meta[r[1]][1]))
+    # device time of each convolution's / MATMUL's main kernel, from the library's own event pairs around it (the host
+    # timestamps of every step carry a launch and a synchronisation, 25-35 us)
+    ctx.timer_enable(True)
+    dev_ms = {}
+
+    def stamp_dev():
+        t = stamp()
+        ms, n = ctx.timer_read()
+        stamp_dev.last = ms if n else None
+        return t
+
+    stamp_dev.last = None
+    rows = []
+    for step in run.steps:
+        r = run.profile(stamp_dev, [step])[0]
+        rows.append(r)
+        dev_ms[r[1]] = stamp_dev.last
+    ctx.timer_enable(False)
+    print(json.dumps({"graph": "resnet50_int8", "batch": batch, "steps": len(rows), "sum_ms": sum(r[3] for r in rows),
+                      "sum_main_kernel_ms": sum(v for v in dev_ms.values() if v)}))
+    for r in sorted(rows, key=lambda r: -(dev_ms[r[1]] or r[3]))[:40]:
+        print("%-20s %-16s %-24s host %8.3f ms  kernel %s  shape=%s" % (
+            r[0], r[1], r[2], r[3], "%8.4f ms" % dev_ms[r[1]] if dev_ms[r[1]] else "   -      ", g.meta[r[1]][1]))
     agg = collections.Counter()
+    aggd = collections.Counter()
     for r in rows:
         agg[(r[0], r[2])] += r[3]
+        aggd[(r[0], r[2])] += dev_ms[r[1]] or 0.0
     for (kind, kernel), ms in agg.most_common():
-        print("%-20s %-24s %8.3f ms" % (kind, kernel, ms))
+        print("%-20s %-24s host %8.3f ms  main kernels %8.3f ms" % (kind, kernel, ms, aggd[(kind, kernel)]))
 
 
 def main():

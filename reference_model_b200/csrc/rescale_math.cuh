@@ -71,60 +71,73 @@ __host__ __device__ __forceinline__ int64_t value_extend64_dev(int32_t val, int 
 //     s  = acc * pk + cpk          (32-bit; pk a power of two, cpk = correction * pk: the zero-point / bias term rides
 //                                   on the pre-scale; wraps mod 2^32, the true value fits)
 //     P  = s * m + R               (64-bit)
-//     z  = (hi(P) + (s < 0 ? -dr : 0)) >> sh
+//     z  = (hi(P) + (FIX ? s >> 31 : 0)) >> sh          FIX = the RESCALE's double_round attribute, one per layer
 //
-//   shift <= 31: pk = 2^(32-shift), sh = 0, dr = 0, R = 2^31 + out_zp * 2^32: the product is aligned to the high word
-//                (no double rounding exists below shift 32);
 //   shift >= 32: pk = 2, sh = shift - 31, R = 2^shift + DR * 2^31 + out_zp * 2^(shift+1): everything is doubled, which
 //                makes the two rounding constants of double rounding differ by exactly 2^32, i.e. by one in the high
-//                word and nothing in the low word, so the sign-dependent choice is the -dr above.
+//                word and nothing in the low word, so the sign-dependent choice is the "+ (s >> 31)" above;
+//   shift <= 31: pk = 2^(32-shift), sh = 0, R = 2^31 + out_zp * 2^32: the product is aligned to the high word.  No
+//                double rounding exists below shift 32, but a layer with double_round applies the sign term to every
+//                column (it is one instruction when unconditional, three when selected per column), so such a column
+//                is kept non-negative instead: cpk carries an extra B = 2^30 and R an extra -B * m, which cancel in P
+//                and make s > 0 whenever |t| * pk < 2^30.
 // out_zp added before the shift by its full weight comes out as exactly out_zp after it.  z still has to be saturated
-// to int8 (cvt.pack.sat does it).  The form is exact when t = acc + correction satisfies |t| < 2^(shift-1) for
-// shift <= 31 (which is also apply_scale_32's own REQUIRE, so it can never fail) and |t| < 2^30 for shift >= 32;
-// `vmax`, the largest magnitude t can take for this column given the layer's K and its bias, proves that statically or
-// the record is marked unusable (word 7 = 0) and the block takes the general epilogue.
-// Record words: {m, pk, cpk, sh | dr << 8, R low, R high, 0, usable}.
+// to int8 (cvt.pack.sat does it).  The form is exact when t = acc + correction satisfies |t| < 2^30 for shift >= 32,
+// |t| < 2^(shift-1) for shift <= 31 without double_round (apply_scale_32's own REQUIRE, so that can never fail either)
+// and |t| < 2^(shift-2) for shift <= 31 with it; `vmax`, the largest magnitude t can take for this column given the
+// layer's K and its bias, proves that statically or the record is marked unusable (word 7 = 0) and the block takes
+// the general epilogue.
+// Record words: {m, pk, cpk, sh, R low, R high, 0, usable}.
 __host__ __device__ __forceinline__ void rescale_rec_build(int32_t m, int32_t shift, int double_round, int32_t out_zp,
                                                             int32_t correction, int64_t vmax, int32_t r8[8])
 {
     bool ok = (m >= 0) && (shift >= 2) && (shift <= 53) && (out_zp >= -128) && (out_zp <= 127);
     const int32_t sc = shift < 2 ? 2 : (shift > 53 ? 53 : shift);
-    int32_t pk, sh, dr = 0;
-    int64_t R;
+    int32_t pk, sh;
+    uint32_t bias = 0;
+    uint64_t R;
     if (sc <= 31)
     {
-        ok  = ok && vmax < ((int64_t)1 << (sc - 1));
         pk  = (int32_t)1 << (32 - sc);
         sh  = 0;
-        R   = ((int64_t)1 << 31) + (int64_t)out_zp * ((int64_t)1 << 32);
+        R   = ((uint64_t)1 << 31) + (uint64_t)((int64_t)out_zp * ((int64_t)1 << 32));
+        if (double_round)
+        {
+            ok   = ok && vmax < ((int64_t)1 << (sc - 2));
+            bias = (uint32_t)1 << 30;
+            R -= (uint64_t)bias * (uint64_t)(uint32_t)m;
+        }
+        else
+            ok = ok && vmax < ((int64_t)1 << (sc - 1));
     }
     else
     {
         ok  = ok && vmax < ((int64_t)1 << 30);
         pk  = 2;
         sh  = sc - 31;
-        dr  = double_round ? 1 : 0;
-        R   = ((int64_t)1 << sc) + (double_round ? ((int64_t)1 << 31) : 0) + (int64_t)out_zp * ((int64_t)1 << (sc + 1));
+        R   = ((uint64_t)1 << sc) + (double_round ? ((uint64_t)1 << 31) : 0) +
+              (uint64_t)((int64_t)out_zp * ((int64_t)1 << (sc + 1)));
     }
     r8[0] = m;
     r8[1] = pk;
-    r8[2] = (int32_t)((uint32_t)correction * (uint32_t)pk);
-    r8[3] = sh | (dr << 8);
-    r8[4] = (int32_t)(uint32_t)(R & 0xffffffffLL);
-    r8[5] = (int32_t)(R >> 32);
+    r8[2] = (int32_t)((uint32_t)correction * (uint32_t)pk + bias);
+    r8[3] = sh;
+    r8[4] = (int32_t)(uint32_t)(R & 0xffffffffULL);
+    r8[5] = (int32_t)(uint32_t)(R >> 32);
     r8[6] = 0;
     r8[7] = ok ? 1 : 0;
 }
 
-// One accumulator through the lean form; the result still needs saturation to int8.
-__host__ __device__ __forceinline__ int32_t rescale_rec_apply(int32_t acc, int32_t m, int32_t pk, int32_t cpk, int32_t shdr,
-                                                               int32_t rlo, int32_t rhi)
+// One accumulator through the lean form; the result still needs saturation to int8.  `fix` is the layer's double_round.
+__host__ __device__ __forceinline__ int32_t rescale_rec_apply(int32_t acc, int32_t m, int32_t pk, int32_t cpk, int32_t sh,
+                                                               int32_t rlo, int32_t rhi, bool fix)
 {
     const int32_t s  = (int32_t)((uint32_t)acc * (uint32_t)pk + (uint32_t)cpk);
-    const int32_t sg = s >> 31;
     const int64_t P  = (int64_t)s * (int64_t)m + (int64_t)(((uint64_t)(uint32_t)rhi << 32) | (uint32_t)rlo);
-    const int32_t hi = (int32_t)(P >> 32) + sg * (shdr >> 8);
-    return hi >> (shdr & 31);
+    int32_t hi       = (int32_t)(P >> 32);
+    if (fix)
+        hi += s >> 31;
+    return hi >> sh;
 }
 
 }    // namespace tb200

@@ -43,6 +43,7 @@ __device__ __forceinline__ TileCoord lean_decode_tile(const TcKernelParams& p, i
 // Sixteen accumulators of one row through the lean RESCALE form, saturated and packed to sixteen int8.  `delta`, for a
 // border pixel, points at what its class of clipped tap rectangle adds to the interior correction (added four columns
 // at a time, right before they are used, to keep few values alive).
+template <bool FIX>
 __device__ __forceinline__ void lean_rescale_x16(const uint32_t (&v)[16], const int32_t (*rec)[8], const int32_t* delta,
                                                  uint32_t (&w)[4])
 {
@@ -59,7 +60,7 @@ __device__ __forceinline__ void lean_rescale_x16(const uint32_t (&v)[16], const 
         {
             const int4 r0 = *reinterpret_cast<const int4*>(&rec[4 * q + j][0]);
             const int2 r1 = *reinterpret_cast<const int2*>(&rec[4 * q + j][4]);
-            z[j] = rescale_rec_apply((int32_t)(v[4 * q + j] + (uint32_t)dv[j]), r0.x, r0.y, r0.z, r0.w, r1.x, r1.y);
+            z[j] = rescale_rec_apply((int32_t)(v[4 * q + j] + (uint32_t)dv[j]), r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, FIX);
         }
         w[q] = pack4_sat_i8(z[0], z[1], z[2], z[3]);
     }
@@ -68,8 +69,9 @@ __device__ __forceinline__ void lean_rescale_x16(const uint32_t (&v)[16], const 
 // (18 warps: the register file is four partitions of 16 K registers, one per scheduler, and the fullest partition holds
 // five of these warps, so a thread gets 96 registers, not the 112 that 65536 / 576 would suggest)
 // CLASSES: the layer has border classes (padding with a non-zero input zero point); the instantiation without them
-// carries no trace of the border path, which keeps its epilogue loop free of register spills.
-template <bool CLASSES>
+// carries no trace of the border path, which keeps its epilogue loop free of register spills.  FIX: the layer's RESCALE
+// has double_round (the sign term of rescale_rec_apply, applied to every column).
+template <bool CLASSES, bool FIX>
 __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __grid_constant__ TcKernelParams p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -370,7 +372,7 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
                     ptx::tmem_ld_32x32b_x16(taddr + (uint32_t)(c * 32 + h * 16), v);
                     ptx::tmem_ld_wait();
                     uint32_t w4[4];
-                    lean_rescale_x16(v, &rec[c * 32 + h * 16],
+                    lean_rescale_x16<FIX>(v, &rec[c * 32 + h * 16],
                                      (CLASSES && delta_row != nullptr) ? delta_row + c * 32 + h * 16 : nullptr, w4);
                     w[4 * h + 0] = w4[0]; w[4 * h + 1] = w4[1]; w[4 * h + 2] = w4[2]; w[4 * h + 3] = w4[3];
                 }

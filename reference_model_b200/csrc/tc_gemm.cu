@@ -732,7 +732,7 @@ __global__ void __launch_bounds__(kNumThreads, 2) tc_gemm_kernel(const __grid_co
                                     const int32_t(*rcol)[8] = &epi_cols[c * 32 + 4 * q + j];
                                     const int4 r0 = *reinterpret_cast<const int4*>(&(*rcol)[0]);
                                     const int2 r1 = *reinterpret_cast<const int2*>(&(*rcol)[4]);
-                                    z[j] = rescale_rec_apply((int32_t)v[4 * q + j], r0.x, r0.y, r0.z, r0.w, r1.x, r1.y);
+                                    z[j] = rescale_rec_apply((int32_t)v[4 * q + j], r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, p.double_round != 0);
                                 }
                                 w[q] = pack4_sat_i8(z[0], z[1], z[2], z[3]);
                             }
@@ -1507,8 +1507,11 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
 
     if (plan.lean)
     {
-        void (*lean)(const TcKernelParams) = k.corr_classes ? tc_conv_lean_kernel<true> : tc_conv_lean_kernel<false>;
-        const tb200_status ast = raise_smem_limit(ctx, k.corr_classes ? 5 : 4, reinterpret_cast<const void*>(lean), plan.smem_bytes);
+        void (*lean)(const TcKernelParams) =
+            k.corr_classes ? (k.double_round ? tc_conv_lean_kernel<true, true> : tc_conv_lean_kernel<true, false>)
+                           : (k.double_round ? tc_conv_lean_kernel<false, true> : tc_conv_lean_kernel<false, false>);
+        const tb200_status ast = raise_smem_limit(ctx, 4 + (k.corr_classes ? 1 : 0) + (k.double_round ? 2 : 0), reinterpret_cast<const void*>(lean),
+                                                  plan.smem_bytes);
         if (ast != TB200_OK)
             return ast;
         timer_begin(ctx);

@@ -262,11 +262,11 @@ class DeviceRunner:
                               a["rounding"], a["per_channel"], a.get("input_unsigned", False),
                               a.get("output_unsigned", False))
 
-    def profile(self, sync_time):
+    def profile(self, sync_time, steps=None):
         """Eager evaluation with a device synchronisation after every step.  `sync_time()` must synchronise and return
         a host timestamp in seconds.  Returns [(step kind, output tensor, kernel family, milliseconds)]."""
         rows = []
-        for step in self.steps:
+        for step in (self.steps if steps is None else steps):
             t0 = sync_time()
             self._eval([step])
             t1 = sync_time()

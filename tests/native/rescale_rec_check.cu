@@ -42,7 +42,9 @@ int main(int argc, char** argv)
         const bool dr      = rnd() & 1;
         const int32_t zp   = (int32_t)(rnd() % 256) - 128;
         const int32_t corr = (int32_t)(rnd() % (1u << 26)) - (1 << 25);
-        const int bits     = (s <= 31) ? s - 1 : 30;
+        // what the form can prove: |t| < 2^30 above shift 31; below, apply_scale_32's own limit 2^(shift-1), one bit less
+        // when the layer rounds twice (the sign term is applied to every column and such a column is kept non-negative)
+        const int bits     = (s <= 31) ? (dr ? s - 2 : s - 1) : 30;
         int64_t vmax       = ((int64_t)1 << bits) - 1;
         if (it % 7 == 0)
             vmax = (int64_t)1 << bits;    // one more than the form can prove: must be refused
@@ -72,9 +74,11 @@ int main(int argc, char** argv)
                 case 4: t = 1; break;
                 default: t = (int64_t)(rnd() % (2 * (uint64_t)vmax + 1)) - vmax;
             }
+            if (t > vmax || t < -vmax)
+                continue;    // +-1 when the provable range is {0}
             // the kernel sees the raw accumulator; the correction rides on the record
             const int32_t acc = (int32_t)((uint32_t)(int32_t)t - (uint32_t)corr);
-            const int32_t z   = rescale_rec_apply(acc, r8[0], r8[1], r8[2], r8[3], r8[4], r8[5]);
+            const int32_t z   = rescale_rec_apply(acc, r8[0], r8[1], r8[2], r8[3], r8[4], r8[5], dr);
             const int64_t e   = apply_scale_32_ref((int32_t)t, m, s, dr) + zp;
             checked++;
             if ((int64_t)z != e)
