@@ -127,6 +127,13 @@ extern "C"
      * them between tiles through flags (which needs the whole grid resident at once, true on a GPU the context has to
      * itself, the default). */
     TB200_API tb200_status tb200_set_shared_gpu(tb200_ctx* ctx, int32_t shared);
+    /* on != 0 (the default): the kernels that support it (the int8 CONV2D + RESCALE kernel, the residual join) are
+     * launched with programmatic stream serialization, so that one kernel's set-up and its reads of constants overlap
+     * the end of the kernel before it on the same stream; each waits for its predecessor (griddepcontrol.wait) before
+     * it reads an activation or writes an output, so results and ordering are those of plain stream order.  The
+     * reference evaluates node after node on one host thread and has no counterpart; the switch is there for hosts
+     * that want plain launches (for instance to read per-kernel times from a profiler's timeline). */
+    TB200_API tb200_status tb200_set_launch_overlap(tb200_ctx* ctx, int32_t on);
 
     /* Constant-operand cache.  The reference decodes a graph's constants once
      * (reference_model/src/subgraph_traverser.cpp:617-781); here everything an operator derives from constants alone

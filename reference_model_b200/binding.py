@@ -76,7 +76,7 @@ EXPORTS = [
     "tb200_rescale", "tb200_clamp", "tb200_add", "tb200_residual_add", "tb200_max_pool2d", "tb200_avg_pool2d",
     "tb200_matmul_host", "tb200_set_kernel_policy", "tb200_last_kernel", "tb200_matmul_i8_noalloc",
     "tb200_npy_probe", "tb200_tensor_load_npy", "tb200_tensor_save_npy",
-    "tb200_set_wait_limit", "tb200_set_shared_gpu", "tb200_const_cache_control", "tb200_const_cache_entries",
+    "tb200_set_wait_limit", "tb200_set_shared_gpu", "tb200_set_launch_overlap", "tb200_const_cache_control", "tb200_const_cache_entries",
     "tb200_comm_unique_id", "tb200_comm_init", "tb200_comm_attach", "tb200_comm_destroy", "tb200_comm_rank",
     "tb200_comm_size", "tb200_gather_output",
 ]
@@ -136,6 +136,7 @@ def load_library():
         "tb200_last_kernel": (cp, [vp]),
         "tb200_set_wait_limit": (i32, [vp, ctypes.c_uint64]),
         "tb200_set_shared_gpu": (i32, [vp, i32]),
+        "tb200_set_launch_overlap": (i32, [vp, i32]),
         "tb200_const_cache_control": (i32, [vp, i32]),
         "tb200_const_cache_entries": (i32, [vp]),
         "tb200_comm_unique_id": (i32, [ctypes.c_char_p]),
@@ -333,6 +334,10 @@ class Context:
 
     def set_shared_gpu(self, shared=True):
         return self._check(self.lib.tb200_set_shared_gpu(self.handle, int(bool(shared))))
+
+    def set_launch_overlap(self, on=True):
+        """Programmatic stream serialization for the kernels that support it (on by default): tb200_set_launch_overlap."""
+        return self._check(self.lib.tb200_set_launch_overlap(self.handle, int(bool(on))))
 
     CACHE_OFF, CACHE_ON, CACHE_CLEAR = 0, 1, 2
 

@@ -547,6 +547,14 @@ extern "C" tb200_status tb200_set_shared_gpu(tb200_ctx* ctx, int32_t shared)
     return TB200_OK;
 }
 
+extern "C" tb200_status tb200_set_launch_overlap(tb200_ctx* ctx, int32_t on)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    ctx->launch_overlap = on ? 1 : 0;
+    return TB200_OK;
+}
+
 extern "C" tb200_status tb200_const_cache_control(tb200_ctx* ctx, int32_t action)
 {
     if (!ctx)
@@ -2352,9 +2360,23 @@ extern "C" tb200_status tb200_residual_add(tb200_ctx* ctx, const tb200_tensor* a
                 uint32_t* bad_bits = reinterpret_cast<uint32_t*>(table + kJoinTableBytes);
                 const int tblock   = 512;
                 const int tgrid    = (int)std::min<int64_t>((n / 16 + tblock - 1) / tblock, (int64_t)ctx->num_sms * 2);
-                residual_add_i8_table_kernel<<<tgrid, tblock, kTableSmem, ctx->stream>>>(
-                    reinterpret_cast<const int8_t*>(a->data), reinterpret_cast<const int8_t*>(b->data),
-                    reinterpret_cast<int8_t*>(output->data), n / 16, table, bad_bits, ctx->d_status);
+                {
+                    cudaLaunchConfig_t cfg;
+                    memset(&cfg, 0, sizeof(cfg));
+                    cfg.gridDim          = dim3((unsigned)tgrid);
+                    cfg.blockDim         = dim3((unsigned)tblock);
+                    cfg.dynamicSmemBytes = kTableSmem;
+                    cfg.stream           = ctx->stream;
+                    cudaLaunchAttribute at[1];
+                    at[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+                    at[0].val.programmaticStreamSerializationAllowed = 1;
+                    cfg.attrs    = at;
+                    cfg.numAttrs = ctx->launch_overlap ? 1 : 0;
+                    cudaLaunchKernelEx(&cfg, residual_add_i8_table_kernel, reinterpret_cast<const int8_t*>(a->data),
+                                       reinterpret_cast<const int8_t*>(b->data), reinterpret_cast<int8_t*>(output->data),
+                                       (int64_t)(n / 16), reinterpret_cast<const uint8_t*>(table),
+                                       reinterpret_cast<const uint32_t*>(bad_bits), ctx->d_status);
+                }
                 return post_launch(ctx, "residual_add_i8_table");
             }
         }

@@ -93,6 +93,7 @@ struct tb200_ctx
     // 1: other work may hold SMs of this GPU, so no kernel may wait for another CTA of its own grid (the CTA-pair
     // MATMUL then takes its zero-point sums from separate kernels instead of exchanging them through flags)
     int shared_gpu       = 0;
+    int launch_overlap   = 1;    // launch the kernels that support it with programmatic stream serialization
     int max_pairs[3]     = { 0, 0, 0 };    // resident CTA pairs of the three CTA-pair kernels on this device, 0 = not asked yet
     uint32_t smem_attr_set = 0;            // bit per kernel whose dynamic shared-memory limit has been raised on this device
     // output gather across GPUs (dist.cu): an NCCL communicator created by tb200_comm_init or handed in by the host

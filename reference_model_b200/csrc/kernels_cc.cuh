@@ -399,6 +399,11 @@ __global__ void __launch_bounds__(512, 2) residual_add_i8_table_kernel(const int
     extern __shared__ __align__(16) uint8_t join_smem[];
     uint8_t* tab   = join_smem;
     uint32_t* bits = reinterpret_cast<uint32_t*>(join_smem + kJoinTableBytes);
+    // Programmatic dependent launch: the successor may be scheduled from now on; the table and the REQUIRE bits are
+    // constants of the join (a kernel that prepares them never lets its successor start early), so their copy to shared
+    // memory runs while the predecessor still drains; the operands are its output and wait for it.
+    if (threadIdx.x == 0)
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (int i = threadIdx.x; i < kJoinTableBytes / 16; i += blockDim.x)
         reinterpret_cast<int4*>(tab)[i] = __ldg(reinterpret_cast<const int4*>(table) + i);
     uint32_t any = 0;
@@ -410,6 +415,7 @@ __global__ void __launch_bounds__(512, 2) residual_add_i8_table_kernel(const int
     }
     // (also the barrier that publishes the table)
     const bool check = __syncthreads_or(any != 0) != 0;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     bool bad = false;
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     auto lookup16 = [&](const int4& va, const int4& vb) -> uint4 {

@@ -79,6 +79,22 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     return true;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor in the stream is
+// still running.  dep_launch_trigger: this grid lets its successor be scheduled (once every CTA of the grid has said so
+// or exited).  dep_launch_wait: returns when the predecessor grid has completed and its writes are visible; without the
+// launch attribute it returns at once.  Everything a kernel reads that its predecessor may have written, and everything
+// it writes that its predecessor may still read, has to come after the wait.
+__device__ __forceinline__ void dep_launch_trigger()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void dep_launch_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem()
 {

@@ -22,8 +22,8 @@
 
 constexpr int kLeanEpiWarps  = 16;
 constexpr int kLeanThreads   = 64 + 32 * kLeanEpiWarps;
-constexpr int kLeanAccBufs   = 2;
-constexpr int kLeanGroupsPerTile = 2;    // epilogue groups that share one accumulator buffer
+constexpr int kLeanAccBufs   = 2;    // accumulator buffers of a 256-column block
+constexpr int kLeanMaxAccBufs = 4;   // column blocks of at most 128 get four (one per epilogue group)
 
 // tiles are numbered column block major here: a CTA stays in one column block as long as it can
 __device__ __forceinline__ TileCoord lean_decode_tile(const TcKernelParams& p, int tile)
@@ -77,8 +77,8 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[kMaxStages];     // TMA -> MMA: the stage's bytes have landed
     __shared__ __align__(8) uint64_t bar_empty[kMaxStages];    // MMA -> TMA (several stages per tile only): stage consumed
-    __shared__ __align__(8) uint64_t bar_acc_full[kLeanAccBufs];     // MMA -> epilogue (and -> TMA when a tile is one stage)
-    __shared__ __align__(8) uint64_t bar_acc_empty[kLeanAccBufs];    // epilogue -> MMA: accumulator buffer drained
+    __shared__ __align__(8) uint64_t bar_acc_full[kLeanMaxAccBufs];     // MMA -> epilogue (and -> TMA when a tile is one stage)
+    __shared__ __align__(8) uint64_t bar_acc_empty[kLeanMaxAccBufs];    // epilogue -> MMA: accumulator buffer drained
     __shared__ __align__(8) uint64_t bar_b;        // resident weights have landed
     __shared__ __align__(8) uint64_t bar_drain;    // teardown after a wait gave up
     __shared__ uint32_t tmem_base_holder;
@@ -90,7 +90,17 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
     uint8_t* const smem_al   = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
     const uint32_t s_b       = smem_base + (uint32_t)p.lean_b_off;       // resident weights (when p.lean_b_resident)
     const uint32_t s_ring    = smem_base + (uint32_t)p.lean_ring_off;    // stages: ksub A chunks, then ksub B chunks if streamed
+    const int acc_bufs       = p.acc_bufs;                  // 2, or 4 when four buffers of block_n columns fit tensor memory
+    const int groups_per_buf = 4 / acc_bufs;                // epilogue groups that share one accumulator buffer
     const bool one_stage     = p.lean_stages_per_tile == 1;
+    // Halo mode (stride-1 convolutions with a window, weights resident): a tile is BH whole output rows, and ONE box
+    // per channel chunk brings the BH + KH - 1 input rows it needs, halo columns included (zero filled outside the
+    // image, which is the padding), as rows of `wp` = OW + KW - 1 pixels.  Accumulator row q stands for position
+    // (q / wp, q % wp) of that padded grid, and tap (ky, kx) reads the same shared-memory rows shifted by
+    // ky * wp + kx pixels: the shift goes into the start address of the operand descriptor (the swizzle is a function
+    // of the shared-memory address, so any row offset is a valid start).  Positions with q % wp >= OW compute garbage
+    // that is never stored.  Against one box per tap this is KH * KW times fewer bytes and copies per tile.
+    const bool halo          = p.lean_halo != 0;
     if (threadIdx.x == 0)
         TB200_TRACE(p, 0);
 
@@ -101,10 +111,10 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
             ptx::mbar_init(ptx::smem_u32(&bar_full[s]), 1);
             ptx::mbar_init(ptx::smem_u32(&bar_empty[s]), 1);
         }
-        for (int a = 0; a < kLeanAccBufs; a++)
+        for (int a = 0; a < acc_bufs; a++)
         {
             ptx::mbar_init(ptx::smem_u32(&bar_acc_full[a]), 1);
-            ptx::mbar_init(ptx::smem_u32(&bar_acc_empty[a]), 4 * kLeanGroupsPerTile);    // one arrival per epilogue warp
+            ptx::mbar_init(ptx::smem_u32(&bar_acc_empty[a]), 4 * groups_per_buf);    // one arrival per epilogue warp
         }
         ptx::mbar_init(ptx::smem_u32(&bar_b), 1);
         ptx::mbar_init(ptx::smem_u32(&bar_drain), 1);
@@ -125,6 +135,9 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
     const int my_tiles = (p.tile_end - p.tile_begin - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     if (threadIdx.x == 0)
         TB200_TRACE(p, 1);
+    // the successor kernel may be scheduled from here on: its CTAs take an SM as soon as this grid's leave it
+    if (threadIdx.x == 0)
+        ptx::dep_launch_trigger();
 
     if (warp == 0)
     {
@@ -139,6 +152,10 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
                 for (int ch = 0; ch < p.total_chunks; ch++)
                     ptx::tma_load_3d(s_b + (uint32_t)(ch * p.b_chunk_bytes), &p.tmB, ptx::smem_u32(&bar_b), ch * p.chunk_elems, 0, 0);
             }
+            // Weights and epilogue tables are constants (anything written since they were prepared puts a preparing
+            // kernel, which never lets its successor start early, between the writer and this launch); activations are
+            // the predecessor's output: wait for it.
+            ptx::dep_launch_wait();
             int stage = 0;
             uint32_t phase = 0;
             const int a_chunk_bytes = p.a_chunk_bytes, b_chunk_bytes = p.b_chunk_bytes, chunk_elems = p.chunk_elems;
@@ -164,6 +181,16 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
                     const uint32_t full = ptx::smem_u32(&bar_full[stage]);
                     uint32_t sA = s_ring + (uint32_t)(stage * p.stage_bytes);
                     uint32_t sB = sA + (uint32_t)(p.ksub * a_chunk_bytes);
+                    if (halo)
+                    {
+                        // one box per channel chunk: every input row the tile's taps touch, halo columns included
+                        ptx::mbar_arrive_expect_tx(full, (uint32_t)p.chunks_per_tap * tx_per_chunk);
+                        for (int c2 = 0; c2 < p.chunks_per_tap; c2++)
+                            ptx::tma_load_4d(sA + (uint32_t)(c2 * a_chunk_bytes), &p.tmA, full, c2 * chunk_elems, -p.pad_l, ay0, t.n0);
+                        chunks_left = 0;
+                    }
+                    else
+                    {
                     ptx::mbar_arrive_expect_tx(full, (uint32_t)nchunks * tx_per_chunk);
                     for (int j = 0; j < nchunks; j++)
                     {
@@ -184,6 +211,7 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
                                 ky++;
                             }
                         }
+                    }
                     }
                     if (++stage == p.num_stages)
                     {
@@ -220,8 +248,8 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
             const uint64_t a_chunk16 = (uint64_t)(p.a_chunk_bytes >> 4), b_chunk16 = (uint64_t)(p.b_chunk_bytes >> 4);
             for (int i = 0; i < my_tiles && ok; i++)
             {
-                const int acc            = i & 1;
-                const uint32_t acc_phase = (uint32_t)(i >> 1) & 1u;
+                const int acc            = i % acc_bufs;
+                const uint32_t acc_phase = (uint32_t)(i / acc_bufs) & 1u;
                 if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, p.wait_limit))
                 {
                     ok = false;
@@ -249,6 +277,34 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
                     uint64_t bd_chunk = p.lean_b_resident
                                             ? ptx::smem_desc(p.b_desc_hi, s_b + (uint32_t)(chunk_index * p.b_chunk_bytes))
                                             : ptx::smem_desc(p.b_desc_hi, sA + (uint32_t)(p.ksub * p.a_chunk_bytes));
+                    if (halo)
+                    {
+                        // the stage holds chunks_per_tap boxes; tap (ky, kx) starts ky * wp + kx pixel rows into each
+                        const uint64_t row16 = (uint64_t)(p.chunk_elems >> 4);    // one pixel row of a chunk, in 16-byte units
+                        uint64_t tap_row = ad_chunk;
+                        for (int ky = 0; ky < p.KH; ky++, tap_row += (uint64_t)p.lean_halo_wp * row16)
+                        {
+                            uint64_t tap = tap_row;
+                            for (int kx = 0; kx < p.KW; kx++, tap += row16)
+                            {
+                                uint64_t ac = tap;
+                                for (int c2 = 0; c2 < p.chunks_per_tap; c2++)
+                                {
+                                    uint64_t ad = ac, bd = bd_chunk;
+                                    for (int m = 0; m < mmas; m++)
+                                    {
+                                        ptx::mma_i8_ss(d_tmem, ad, bd, idesc, accum);
+                                        accum = 1;
+                                        ad += 2;
+                                        bd += 2;
+                                    }
+                                    ac += a_chunk16;
+                                    bd_chunk += b_chunk16;
+                                }
+                            }
+                        }
+                    }
+                    else
                     for (int j = 0; j < nchunks; j++)
                     {
                         uint64_t ad = ad_chunk, bd = bd_chunk;
@@ -290,21 +346,23 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
         // ------------------------------------------------------------------ epilogue: 4 groups of 4 warps
         const int quarter = warp & 3;                  // TMEM lane quarter this warp may read
         const int group   = (warp - 2) >> 2;           // 0..3
-        const int acc     = group / kLeanGroupsPerTile;    // accumulator buffer of this group
-        const int sub     = group % kLeanGroupsPerTile;    // which 32-column chunks of a tile it takes
+        const int acc     = group / groups_per_buf;    // accumulator buffer of this group
+        const int sub     = group % groups_per_buf;    // which 32-column chunks of a tile it takes
         const int gtid    = (int)threadIdx.x - 64 - group * 128;    // 0..127 inside the group
-        int32_t(*rec)[8]  = reinterpret_cast<int32_t(*)[8]>(smem_al + p.lean_rec_off + (size_t)group * p.block_n * 32);
+        int32_t(*rec)[8]  = reinterpret_cast<int32_t(*)[8]>(smem_al + p.lean_rec_off + (size_t)group * p.lean_rec_stride);
         const int row     = quarter * 32 + lane;
-        const int xx      = row % p.BW;
-        const int yy      = (row / p.BW) % p.BH;
-        const int nn      = row / (p.BW * p.BH);
+        const int row_w   = halo ? p.lean_halo_wp : p.BW;    // accumulator rows per output row (halo: with the halo columns)
+        const int xx      = row % row_w;
+        const int yy      = (row / row_w) % p.BH;
+        const int nn      = row / (row_w * p.BH);
         const bool narrow_clamp = p.clamp_lo > -128 || p.clamp_hi < 127;
         const uint32_t lo4 = (uint32_t)(p.clamp_lo & 0xff) * 0x01010101u;
         const uint32_t hi4 = (uint32_t)(p.clamp_hi & 0xff) * 0x01010101u;
         const int nchunks32 = p.block_n / 32;
         int loaded_col0 = -1;
         bool ok = true;
-        for (int i = acc; i < my_tiles; i += kLeanAccBufs)
+        bool dep_waited = false;
+        for (int i = acc; i < my_tiles; i += acc_bufs)
         {
             const TileCoord t = lean_decode_tile(p, p.tile_begin + (int)blockIdx.x + i * (int)gridDim.x);
             if (loaded_col0 != t.col0)
@@ -321,11 +379,17 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
                 asm volatile("bar.sync %0, 128;" ::"r"(2 + group) : "memory");
                 loaded_col0 = t.col0;
             }
+            // the records are constants; the border deltas are too, but the output may still be read by the predecessor
+            if (!dep_waited)
+            {
+                ptx::dep_launch_wait();
+                dep_waited = true;
+            }
             // After a wait has given up, this warp keeps walking its tiles only to meet its group at the barrier above
             // (the other three warps may still be working); it does no further work.
             if (!ok)
                 continue;
-            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_full[acc]), (uint32_t)(i >> 1) & 1u, p.wait_limit);
+            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_full[acc]), (uint32_t)(i / acc_bufs) & 1u, p.wait_limit);
             ok = __all_sync(0xffffffffu, ok);    // the whole warp agrees before the warp-collective TMEM loads
             if (!ok)
                 continue;
@@ -362,18 +426,51 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n);
             // chunks past the last channel exist only in a last, partly filled column block (OC is a multiple of 32)
             const int chunks_here = min(nchunks32, (p.OC - t.col0) / 32);
-            for (int c = sub; c < chunks_here; c += kLeanGroupsPerTile)
+            for (int c = sub; c < chunks_here; c += groups_per_buf)
             {
                 uint32_t w[8];
 #pragma unroll
                 for (int h = 0; h < 2; h++)
                 {
                     uint32_t v[16];
-                    ptx::tmem_ld_32x32b_x16(taddr + (uint32_t)(c * 32 + h * 16), v);
-                    ptx::tmem_ld_wait();
+                    if (TB200_DIAG_BIT(p.debug, 64))
+                    {
+                        // diagnostic: no tensor-memory load
+#pragma unroll
+                        for (int e = 0; e < 16; e++)
+                            v[e] = (uint32_t)(row + e + c);
+                    }
+                    else
+                    {
+                        ptx::tmem_ld_32x32b_x16(taddr + (uint32_t)(c * 32 + h * 16), v);
+                        ptx::tmem_ld_wait();
+                    }
                     uint32_t w4[4];
-                    lean_rescale_x16<FIX>(v, &rec[c * 32 + h * 16],
-                                     (CLASSES && delta_row != nullptr) ? delta_row + c * 32 + h * 16 : nullptr, w4);
+                    if (TB200_DIAG_BIT(p.debug, 128))
+                    {
+                        // diagnostic: no arithmetic, no record reads
+#pragma unroll
+                        for (int e = 0; e < 4; e++)
+                            w4[e] = v[4 * e] ^ v[4 * e + 1] ^ v[4 * e + 2] ^ v[4 * e + 3];
+                    }
+                    else if (TB200_DIAG_BIT(p.debug, 256))
+                    {
+                        // diagnostic: the arithmetic with one record for all columns (a single shared-memory read)
+                        const int4 r0 = *reinterpret_cast<const int4*>(&rec[0][0]);
+                        const int2 r1 = *reinterpret_cast<const int2*>(&rec[0][4]);
+#pragma unroll
+                        for (int e = 0; e < 4; e++)
+                        {
+                            int32_t z[4];
+#pragma unroll
+                            for (int j = 0; j < 4; j++)
+                                z[j] = rescale_rec_apply((int32_t)v[4 * e + j], r0.x, r0.y + j, r0.z + e, r0.w, r1.x, r1.y, FIX);
+                            w4[e] = pack4_sat_i8(z[0], z[1], z[2], z[3]);
+                        }
+                    }
+                    else
+                        lean_rescale_x16<FIX>(v, &rec[c * 32 + h * 16],
+                                              (CLASSES && delta_row != nullptr) ? delta_row + c * 32 + h * 16 : nullptr, w4);
                     w[4 * h + 0] = w4[0]; w[4 * h + 1] = w4[1]; w[4 * h + 2] = w4[2]; w[4 * h + 3] = w4[3];
                 }
                 if (narrow_clamp)
@@ -382,7 +479,7 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
                     for (int q = 0; q < 8; q++)
                         w[q] = __vmins4(__vmaxs4(w[q], lo4), hi4);
                 }
-                if (row_valid)
+                if (row_valid && !(TB200_DIAG_BIT(p.debug, 32) && w[0] != 0x12345678u))
                     ptx::st_global_v8(out_row + t.col0 + c * 32, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
             }
             // this warp has read its part of the buffer

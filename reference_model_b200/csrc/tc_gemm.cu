@@ -99,11 +99,13 @@ struct TcKernelParams
     // tc_conv_lean_kernel only: shared-memory offsets from the 1024-byte aligned base (resident weights, stage ring,
     // the four epilogue groups' record copies), whether the weights are resident, stages per tile
     int lean_b_off, lean_ring_off, lean_rec_off, lean_b_resident, lean_stages_per_tile;
+    int lean_rec_stride;           // bytes between the epilogue groups' copies of the records (0: one copy, single column block)
+    int lean_halo, lean_halo_wp;   // halo mode: one box per channel chunk and tile; wp = OW + KW - 1 accumulator rows per output row
     int double_round;
     int32_t out_zp, clamp_lo, clamp_hi;
     float clamp_lo_f, clamp_hi_f;
     int has_clamp;
-    int debug;    // diagnostic bit mask, read only by builds with TB200_DIAG: 1 skip epilogue memory work, 2 skip MMA issue, 4 skip loads
+    int debug;    // diagnostic bit mask, read only by builds with TB200_DIAG: 1 skip epilogue memory work, 2 skip MMA issue, 4 skip loads; lean kernel: 32 skip stores, 64 skip tensor-memory loads, 128 skip arithmetic, 256 one record for all columns
     long long wait_limit;    // SM cycles after which a pipeline wait gives up (TB200_DEV_TIMEOUT)
 #ifdef TB200_DIAG
     long long* trace;        // diagnostic builds: [CTA][16] globaltimer stamps (ns) of the roles' milestones, or null
@@ -1381,6 +1383,78 @@ bool make_lean_plan(const TcProblem& q, int num_sms, int max_smem_optin, TcPlan*
     const int b_tx       = k.block_n * k.chunk_elems;
     const int a_tx       = k.tx_bytes_per_chunk - b_tx;
     const int b_total    = k.total_chunks * k.b_chunk_bytes;
+    k.lean_rec_stride    = k.block_n * 32;
+    k.lean_halo          = 0;
+    k.lean_halo_wp       = 0;
+
+    // ---- halo mode: stride-1 window, one column block, weights resident (see tc_conv_lean_kernel).  Not for column
+    // blocks of 64: those layers are bound by the issue rate of their N = 64 MMAs (about 170 cycles each with the commit),
+    // which the halo form does not change, and measured 20 % slower with it (3x3 64 -> 64 at 56 x 56: 136 against 111 us at
+    // batch 256; 3x3 128 -> 128 at 28 x 28: 57 against 74 us).
+    {
+        const int swz = k.chunk_elems;    // int8: bytes of one pixel row of a chunk
+        const int wp  = q.OW + q.KW - 1;
+        if (diag_env_int("TB200_LEAN_HALO", 1) != 0 && q.KH * q.KW > 1 && q.stride_x == 1 && q.stride_y == 1 && q.dil_x == 1 &&
+            q.dil_y == 1 && k.tiles_col == 1 && wp <= kTileM && wp <= 256 && k.block_n >= diag_env_int("TB200_LEAN_HALO_MIN_N", 128))
+        {
+            int bh = std::min(q.OH, kTileM / wp);
+            for (int cand = bh; cand >= std::max(1, bh - 2); cand--)
+                if (q.OH % cand == 0)
+                {
+                    bh = cand;
+                    break;
+                }
+            const int hb        = bh + q.KH - 1;
+            const int alloc_pos = std::max(wp * hb, kTileM + (q.KH - 1) * wp + q.KW - 1);
+            const int a_chunk   = (alloc_pos * swz + 1023) & ~1023;
+            const int stage     = k.chunks_per_tap * a_chunk;
+            const int rec_one   = k.block_n * 32;
+            int nacc            = k.block_n <= 128 ? 4 : 2;
+            if (b_total + rec_one + nacc * stage > budget)
+                nacc = 2;
+            // at least three quarters of the accumulator rows must be output pixels, or the tensor pipe works on halo
+            if (bh * wp >= 96 && hb <= 256 && b_total + rec_one + nacc * stage <= budget)
+            {
+                k.lean_halo     = 1;
+                k.lean_halo_wp  = wp;
+                k.BW            = q.OW;
+                k.BH            = bh;
+                k.BN            = 1;
+                k.tiles_x       = 1;
+                k.tiles_y       = (q.OH + bh - 1) / bh;
+                k.tiles_n       = q.N;
+                k.num_tiles     = k.tiles_y * k.tiles_n;
+                k.tile_begin    = 0;
+                k.tile_end      = k.num_tiles;
+                k.a_chunk_bytes = a_chunk;
+                plan->a_box[0]  = (cuuint32_t)k.chunk_elems;
+                plan->a_box[1]  = (cuuint32_t)wp;
+                plan->a_box[2]  = (cuuint32_t)hb;
+                plan->a_box[3]  = 1;
+                k.ksub                 = k.total_chunks;
+                k.num_kstages          = 1;
+                k.lean_stages_per_tile = 1;
+                k.num_stages           = nacc;
+                k.stage_bytes          = stage;
+                k.tx_bytes_per_chunk   = wp * hb * swz;    // bytes of one box
+                k.lean_b_resident      = 1;
+                k.lean_b_off           = 0;
+                k.lean_ring_off        = b_total;
+                k.lean_rec_off         = b_total + nacc * stage;
+                k.lean_rec_stride      = 0;
+                k.acc_bufs             = nacc;
+                int cols = 32;
+                while (cols < nacc * k.block_n)
+                    cols *= 2;
+                k.tmem_cols       = cols;
+                plan->smem_bytes  = k.lean_rec_off + rec_one + 1024;
+                plan->ctas_per_sm = 1;
+                plan->grid        = std::max(1, std::min(k.num_tiles, num_sms));
+                plan->lean        = true;
+                return true;
+            }
+        }
+    }
     const bool b_res     = k.tiles_col == 1 && b_total <= 96 * 1024;
     const int avail      = budget - rec_bytes - (b_res ? b_total : 0);
     const int per_chunk  = k.a_chunk_bytes + (b_res ? 0 : k.b_chunk_bytes);
@@ -1515,7 +1589,22 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
         if (ast != TB200_OK)
             return ast;
         timer_begin(ctx);
-        lean<<<plan.grid, kLeanThreads, plan.smem_bytes, ctx->stream>>>(k);
+        {
+            // programmatic stream serialization: the kernel may be scheduled while its predecessor drains; it waits
+            // (griddepcontrol.wait) before it touches anything the predecessor may write or still read
+            cudaLaunchConfig_t cfg;
+            memset(&cfg, 0, sizeof(cfg));
+            cfg.gridDim          = dim3((unsigned)plan.grid);
+            cfg.blockDim         = dim3((unsigned)kLeanThreads);
+            cfg.dynamicSmemBytes = (size_t)plan.smem_bytes;
+            cfg.stream           = ctx->stream;
+            cudaLaunchAttribute at[1];
+            at[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+            at[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs    = at;
+            cfg.numAttrs = ctx->launch_overlap ? 1 : 0;
+            cudaLaunchKernelEx(&cfg, lean, k);
+        }
         timer_end(ctx);
         const tb200_status lst = post_launch(ctx, "tc_conv_lean_i8");
         if (lst != TB200_OK)

@@ -337,3 +337,33 @@ def test_resnet50_graph_at_the_8_gpu_shard_size(ctx):
     st, logits = run.output()
     assert st == tb.Status.OK and np.array_equal(logits, ref["logits"])
     ctx.graph_destroy(run.captured)
+
+
+# ------------------------------------------------------------------------------ programmatic dependent launch on / off
+def test_launch_overlap_gives_the_results_of_plain_launches(ctx):
+    """The convolution and join kernels are launched with programmatic stream serialization by default (a kernel may be
+    scheduled while its predecessor drains and waits for it before touching activations).  The same graph evaluated with
+    the switch off and on, eagerly and as a replayed CUDA graph, must give the same logits, and those of the oracle."""
+    nb = 8
+    g = G.resnet50_int8(nb)
+    images = G.synthetic_images(nb)
+    est, ref = graph_oracle.evaluate(g, {"input": images}, nthreads=orc.num_procs())
+    assert est == orc.VALID
+    outs = []
+    for on in (False, True):
+        ctx.set_launch_overlap(on)
+        run = G.DeviceRunner(ctx, g, fused=True)
+        run.set_input(images)
+        run.run()
+        st, eager = run.output()
+        assert st == tb.Status.OK
+        run.capture()
+        for _ in range(3):
+            run.run()
+        st, replay = run.output()
+        assert st == tb.Status.OK
+        assert np.array_equal(eager, replay)
+        outs.append(replay)
+    ctx.set_launch_overlap(True)
+    assert np.array_equal(outs[0], outs[1])
+    assert np.array_equal(outs[1], ref["logits"])
