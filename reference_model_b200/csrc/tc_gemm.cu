@@ -1185,7 +1185,19 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
     // one column block that covers all channels when there are at most 256 of them (no half-empty second block);
     // the epilogue works in 32-column chunks
     if (block_n == 0)
+    {
         block_n = q.OC >= 256 ? 256 : q.OC > 128 ? (q.OC + 31) / 32 * 32 : q.OC > 64 ? 128 : q.OC > 32 ? 64 : 32;
+        // A small layer (a shard of a batch, the last stages of a network) has fewer tiles than the GPU has SMs, and
+        // each tile is a serial chain of load, MMAs and epilogue: narrower column blocks give every SM a tile and
+        // shorten the chain.  Only for the fused int8 convolution, whose column blocks are independent.
+        if (q.epi == TC_EPI_RESCALE && !q.b_mn_major)
+        {
+            const int64_t tiles_m = (int64_t)k.tiles_x * k.tiles_y * k.tiles_n;
+            while ((block_n == 256 || block_n == 128) && q.OC % block_n == 0 &&
+                   tiles_m * (q.OC / block_n) * 4 < (int64_t)num_sms * 3)
+                block_n /= 2;
+        }
+    }
     if (q.b_mn_major && (block_n * es) % 128 != 0)
         block_n = 128 / es * ((block_n * es + 127) / 128);
     if (block_n > 256 || block_n % 32 != 0)
