@@ -2,12 +2,13 @@
 // AVG_POOL2D on the B200 through the tb200 C ABI.  Built inside the reference's tree (it needs graph_node.h, tensor.h,
 // the serialization library's attribute classes and Eigen); not compiled by this repository's own build.
 //
-// How they enter the reference: OpFactory::newOp (reference_model/src/ops/op_factory.cpp:36-131) asks
-// b200::newOpB200 first and falls through to its own switch when that returns nullptr (see INTEGRATION.md for the
-// three-line patch).  Each node wraps the stock node the factory would have built: checkTensorAttributes() is the stock
-// node's own (same ERROR_IFs, same messages), eval() replaces the scalar loops and ends in GraphNode::eval(), which
-// marks the outputs valid and counts the evaluation (reference_model/src/graph_node.cpp:77-89), exactly as the stock
-// eval() bodies do (e.g. reference_model/src/ops/tensor_ops.cpp:881).
+// How they enter the reference: OpFactory::newOp (reference_model/src/ops/op_factory.cpp:36-131) returns from inside its
+// type switch, so the adapter's patch renames that body to newOpStock and adds a newOp that builds the stock node first
+// and then offers it to b200::newOpB200, keeping the stock node when that returns nullptr.  Each node here wraps the
+// stock node the factory built: checkTensorAttributes() is the stock node's own (same ERROR_IFs, same messages), eval()
+// replaces the scalar loops and ends in GraphNode::eval(), which marks the outputs valid and counts the evaluation
+// (reference_model/src/graph_node.cpp:77-89), exactly as the stock eval() bodies do (e.g.
+// reference_model/src/ops/tensor_ops.cpp:881).
 #ifndef B200_NODES_H
 #define B200_NODES_H
 
@@ -38,7 +39,7 @@ struct Runtime
 };
 
 // What the side-table needs to know about a reference tensor.  `b200RawData()` is the one accessor the adapter adds to
-// TosaReference::Tensor (a virtual returning Eigen::Tensor::data() of the concrete TensorTemplate), see INTEGRATION.md.
+// TosaReference::Tensor (a virtual returning Eigen::Tensor::data() of the concrete TensorTemplate).
 HostView view_of(TosaReference::Tensor* t);
 // TOSA_REF_TYPE -> tb200_dtype; false for types this path does not take (INT4, INT48, FP64, BOOL, SHAPE).
 bool to_tb200_dtype(TOSA_REF_TYPE ref, tb200_dtype* out);

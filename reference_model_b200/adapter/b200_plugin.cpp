@@ -14,7 +14,7 @@
 //     matmul                 inputs [a, b], one output; attributes "a_zp=Z;b_zp=Z"
 //
 // Tensors arrive as TosaReference::Tensor*; their Eigen containers are reached through the accessor the adapter adds
-// (Tensor::b200RawData()).  Inputs are uploaded and the output downloaded around every call: a
+// (Tensor::b200RawData(), a virtual returning Eigen::Tensor::data() of the concrete TensorTemplate).  Inputs are uploaded and the output downloaded around every call: a
 // custom operator stands alone between CPU nodes, there is no neighbour on the device to hand the tensor to.
 #include <cstdlib>
 #include <cstring>

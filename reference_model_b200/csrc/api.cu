@@ -8,6 +8,7 @@
 
 #include "common.h"
 #include "kernels_cc.cuh"
+#include "join_stream.cuh"
 
 using namespace tb200;
 
@@ -2360,6 +2361,29 @@ extern "C" tb200_status tb200_residual_add(tb200_ctx* ctx, const tb200_tensor* a
                 uint32_t* bad_bits = reinterpret_cast<uint32_t*>(table + kJoinTableBytes);
                 const int tblock   = 512;
                 const int tgrid    = (int)std::min<int64_t>((n / 16 + tblock - 1) / tblock, (int64_t)ctx->num_sms * 2);
+                if (ctx->join_stream && n / 16 >= (int64_t)ctx->num_sms * kJoinStreamChunkVecs * 4)
+                {
+                    // streaming form: operands through a ring of bulk copies (large joins only: every SM needs a few chunks)
+                    st = raise_smem_limit(ctx, 17, reinterpret_cast<const void*>(residual_add_i8_stream_kernel), (int)kJoinStreamSmem);
+                    if (st != TB200_OK)
+                        return st;
+                    cudaLaunchConfig_t cfg;
+                    memset(&cfg, 0, sizeof(cfg));
+                    cfg.gridDim          = dim3((unsigned)ctx->num_sms);
+                    cfg.blockDim         = dim3((unsigned)kJoinStreamThreads);
+                    cfg.dynamicSmemBytes = kJoinStreamSmem;
+                    cfg.stream           = ctx->stream;
+                    cudaLaunchAttribute at[1];
+                    at[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+                    at[0].val.programmaticStreamSerializationAllowed = 1;
+                    cfg.attrs    = at;
+                    cfg.numAttrs = ctx->launch_overlap ? 1 : 0;
+                    cudaLaunchKernelEx(&cfg, residual_add_i8_stream_kernel, reinterpret_cast<const int8_t*>(a->data),
+                                       reinterpret_cast<const int8_t*>(b->data), reinterpret_cast<int8_t*>(output->data),
+                                       (int64_t)(n / 16), reinterpret_cast<const uint8_t*>(table),
+                                       reinterpret_cast<const uint32_t*>(bad_bits), ctx->d_status, ctx->wait_limit_cycles);
+                    return post_launch(ctx, "residual_add_i8_stream");
+                }
                 {
                     cudaLaunchConfig_t cfg;
                     memset(&cfg, 0, sizeof(cfg));
