@@ -41,10 +41,6 @@ struct tb200_graph
     uint64_t launches    = 0;    // kernels recorded
 };
 
-#ifndef TB200_JOIN_STREAM_DEFAULT
-#define TB200_JOIN_STREAM_DEFAULT 0
-#endif
-
 namespace tb200
 {
 // What an operator derives from its constant operands alone: for a convolution the zero-point correction rows, the
@@ -97,7 +93,7 @@ struct tb200_ctx
     // 1: other work may hold SMs of this GPU, so no kernel may wait for another CTA of its own grid (the CTA-pair
     // MATMUL then takes its zero-point sums from separate kernels instead of exchanging them through flags)
     int shared_gpu       = 0;
-    int join_stream      = TB200_JOIN_STREAM_DEFAULT;    // large table joins through the bulk-copy ring kernel (join_stream.cuh)
+    int join_stream      = 1;    // large table joins through the bulk-copy ring kernel (join_stream.cuh)
     int launch_overlap   = 1;    // launch the kernels that support it with programmatic stream serialization
     int max_pairs[3]     = { 0, 0, 0 };    // resident CTA pairs of the three CTA-pair kernels on this device, 0 = not asked yet
     uint32_t smem_attr_set = 0;            // bit per kernel whose dynamic shared-memory limit has been raised on this device
