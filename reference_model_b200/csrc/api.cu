@@ -2461,7 +2461,10 @@ extern "C" tb200_status tb200_max_pool2d(tb200_ctx* ctx, const tb200_tensor* inp
     switch (input->dtype)
     {
         case TB200_INT8:
-            if (p.C % 16 == 0 && aligned && ctx->policy == 0)
+            if (p.C % 16 == 0 && aligned && ctx->policy == 0 && p.ky == 3 && p.kx == 3)
+                max_pool3x3_i8x16_kernel<<<grid_for(ctx, n / 16, block), block, 0, ctx->stream>>>(
+                    reinterpret_cast<const int8_t*>(input->data), reinterpret_cast<int8_t*>(output->data), p);
+            else if (p.C % 16 == 0 && aligned && ctx->policy == 0)
                 max_pool_i8x16_kernel<<<grid_for(ctx, n / 16, block), block, 0, ctx->stream>>>(
                     reinterpret_cast<const int8_t*>(input->data), reinterpret_cast<int8_t*>(output->data), p);
             else
@@ -2516,7 +2519,13 @@ extern "C" tb200_status tb200_avg_pool2d(tb200_ctx* ctx, const tb200_tensor* inp
     switch (input->dtype)
     {
         case TB200_INT8:
-            avg_pool_int_kernel<int8_t><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const int8_t*>(input->data), reinterpret_cast<int8_t*>(output->data), p, input_zp, output_zp, -128, 127, ctx->d_status);
+            if (p.C % 4 == 0 && ctx->policy == 0 &&
+                ((reinterpret_cast<uintptr_t>(input->data) | reinterpret_cast<uintptr_t>(output->data)) & 3) == 0)
+                avg_pool_i8x4_kernel<<<grid_for(ctx, n / 4, block), block, 0, ctx->stream>>>(
+                    reinterpret_cast<const int8_t*>(input->data), reinterpret_cast<int8_t*>(output->data), p, input_zp, output_zp,
+                    -128, 127, ctx->d_status);
+            else
+                avg_pool_int_kernel<int8_t><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const int8_t*>(input->data), reinterpret_cast<int8_t*>(output->data), p, input_zp, output_zp, -128, 127, ctx->d_status);
             break;
         case TB200_INT16:
             avg_pool_int_kernel<int16_t><<<grid, block, 0, ctx->stream>>>(reinterpret_cast<const int16_t*>(input->data), reinterpret_cast<int16_t*>(output->data), p, 0, 0, -32768, 32767, ctx->d_status);

@@ -645,6 +645,54 @@ __global__ void max_pool_i8x16_kernel(const int8_t* __restrict__ in, int8_t* __r
     }
 }
 
+// The same for a 3 x 3 window (the pooling layer of ResNet-shaped graphs): all nine 16-byte loads are issued before the
+// first comparison, so a thread waits for memory once instead of nine times (taps outside the image read the centre,
+// which is always inside, and so do not change the maximum).
+__global__ void max_pool3x3_i8x16_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ out, PoolDev p)
+{
+    const int cv        = p.C / 16;
+    const int64_t total = (int64_t)p.N * p.OH * p.OW * cv;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int c16 = (int)(i % cv);
+        int64_t r     = i / cv;
+        const int ox  = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        const int n  = (int)(r / p.OH);
+        const int y0 = oy * p.sy - p.pad_t, x0 = ox * p.sx - p.pad_l;
+        // a tap that exists: the window always overlaps the image (checked on the host: pad < kernel)
+        const int yc = min(max(y0 + 1, 0), p.IH - 1), xc = min(max(x0 + 1, 0), p.IW - 1);
+        const int8_t* base = in + (int64_t)n * p.IH * p.IW * p.C + c16 * 16;
+        uint4 v[9];
+#pragma unroll
+        for (int ky = 0; ky < 3; ky++)
+        {
+            const int y  = y0 + ky;
+            const int yy = (y < 0 || y >= p.IH) ? yc : y;
+#pragma unroll
+            for (int kx = 0; kx < 3; kx++)
+            {
+                const int x  = x0 + kx;
+                const int xx = (x < 0 || x >= p.IW) ? xc : x;
+                v[ky * 3 + kx] = __ldg(reinterpret_cast<const uint4*>(base + ((int64_t)yy * p.IW + xx) * p.C));
+            }
+        }
+        uint32_t m[4] = { v[0].x, v[0].y, v[0].z, v[0].w };
+#pragma unroll
+        for (int t = 1; t < 9; t++)
+        {
+            m[0] = __vmaxs4(m[0], v[t].x);
+            m[1] = __vmaxs4(m[1], v[t].y);
+            m[2] = __vmaxs4(m[2], v[t].z);
+            m[3] = __vmaxs4(m[3], v[t].w);
+        }
+        *reinterpret_cast<uint4*>(out + (((int64_t)n * p.OH + oy) * p.OW + ox) * p.C + c16 * 16) =
+            make_uint4(m[0], m[1], m[2], m[3]);
+    }
+}
+
 // general MAX_POOL2D, one element per thread; `lowest` is the padding value of the dtype
 template <typename T, typename TCmp>
 __global__ void max_pool_kernel(const T* __restrict__ in, T* __restrict__ out, PoolDev p, TCmp lowest)
@@ -724,6 +772,65 @@ __global__ void avg_pool_int_kernel(const T* __restrict__ in, T* __restrict__ ou
         v = v > qmin ? v : qmin;
         v = v < qmax ? v : qmax;
         out[i] = (T)v;
+    }
+    if (bad)
+        atomicOr(status, TB200_DEV_UNPREDICTABLE);
+}
+
+// The int8 case with four channels per thread (one 32-bit load per tap and thread, 128 bytes per warp): the global
+// average pool at the end of a ResNet-shaped graph reads 49 taps per output and was bound by one-byte loads.
+__global__ void avg_pool_i8x4_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ out, PoolDev p, int32_t in_zp,
+                                     int32_t out_zp, int32_t qmin, int32_t qmax, int* status)
+{
+    const int cv        = p.C / 4;
+    const int64_t total = (int64_t)p.N * p.OH * p.OW * cv;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    bool bad            = false;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int c4 = (int)(i % cv) * 4;
+        int64_t r    = i / cv;
+        const int ox = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        const int n  = (int)(r / p.OH);
+        int32_t acc[4] = { 0, 0, 0, 0 };
+        int count      = 0;
+        for (int ky = 0; ky < p.ky; ky++)
+        {
+            const int y = oy * p.sy - p.pad_t + ky;
+            if (y < 0 || y >= p.IH)
+                continue;
+            for (int kx = 0; kx < p.kx; kx++)
+            {
+                const int x = ox * p.sx - p.pad_l + kx;
+                if (x < 0 || x >= p.IW)
+                    continue;
+                const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(in + (((int64_t)n * p.IH + y) * p.IW + x) * p.C + c4));
+                acc[0] += (int32_t)(int8_t)(w & 0xff) - in_zp;
+                acc[1] += (int32_t)(int8_t)((w >> 8) & 0xff) - in_zp;
+                acc[2] += (int32_t)(int8_t)((w >> 16) & 0xff) - in_zp;
+                acc[3] += (int32_t)(int8_t)(w >> 24) - in_zp;
+                count++;
+            }
+        }
+        int32_t mult, shift;
+        reciprocal_scale_dev(count, mult, shift);
+        uint32_t packed = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+        {
+            bool b    = false;
+            int32_t v = apply_scale_32_dev(acc[j], mult, shift, false, b);
+            if (b)
+                v = 0;
+            bad |= b;
+            v = (int32_t)((uint32_t)v + (uint32_t)out_zp);
+            v = v > qmin ? v : qmin;
+            v = v < qmax ? v : qmax;
+            packed |= ((uint32_t)v & 0xffu) << (8 * j);
+        }
+        *reinterpret_cast<uint32_t*>(out + (((int64_t)n * p.OH + oy) * p.OW + ox) * p.C + c4) = packed;
     }
     if (bad)
         atomicOr(status, TB200_DEV_UNPREDICTABLE);
