@@ -308,6 +308,34 @@ def test_tensor_core_conv_int8(ctx, case):
     assert kernel == "conv2d_direct" and np.array_equal(out, exp)
 
 
+HALO_CONV_CASES = [
+    # stride-1 window convolutions with one column block of at least 128 and weights that stay resident: the lean kernel
+    # loads one halo box per tile and reads the taps as shifted operand descriptors (enough tiles that the column block is
+    # not narrowed, or a block width that is never narrowed)
+    (16, 28, 28, 128, 128, 3, 3, (1, 1, 1, 1), 7),       # the ResNet 3x3 128 -> 128 layer
+    (5, 13, 17, 128, 160, 3, 3, (1, 1, 1, 1), -5),       # rows that do not divide into tiles, 19 positions per row
+    (6, 14, 30, 128, 160, 3, 3, (1, 0, 0, 1), -128),     # asymmetric padding
+    (6, 12, 40, 128, 160, 1, 3, (0, 0, 1, 1), 9),        # a 1 x 3 window
+    (3, 9, 100, 64, 192, 3, 3, (1, 1, 1, 1), -128),      # 64-byte channel runs, 102 positions per row, one row per tile
+]
+
+
+@pytest.mark.parametrize("case", HALO_CONV_CASES)
+def test_halo_conv_int8(ctx, case):
+    N, IH, IW, IC, OC, KH, KW, pad, izp = case
+    r = util.rng(400 + HALO_CONV_CASES.index(case))
+    x, w, b = util.conv_int8_case(r, N, IH, IW, IC, OC, KH, KW, bias_range=1 << 16)
+    args = (list(pad), [1, 1], [1, 1], izp, 0)
+    mult, shift = util.rescale_params(r, OC)    # shifts from 30 to 40: columns on both sides of the double-rounding limit
+    resc = (mult, shift, -128, "DOUBLE_ROUND")
+    est, exp = oracle_conv_i8(x, w, b, *args, rescale=resc, clamp=(-128, 127))
+    assert est == orc.VALID
+    for cache, want in ((True, LEAN), (False, GENERAL)):
+        st, out, kernel = run_conv_i8(ctx, x, w, b, *args, rescale=resc, clamp=(-128, 127), cache=cache)
+        assert kernel == want and st == tb.Status.OK, (kernel, want)
+        assert np.array_equal(out, exp), "%s: rescaled outputs differ: %d of %d" % (kernel, (out != exp).sum(), exp.size)
+
+
 FEW_CHANNEL_CASES = [
     # N, IH, IW, IC, OC, KH, KW, stride, pad, in_zp
     (2, 32, 32, 3, 64, 7, 7, 2, (3, 2, 3, 2), -128),
