@@ -315,6 +315,9 @@ struct TcProblem
     const int32_t* rec;          // optional: [corr_stride][8] prepared records of the lean RESCALE form (rescale_rec_build)
     const int32_t* delta;        // optional, with corr_classes: [classes][corr_stride] class row minus interior row
     int lean_ok;                 // the host knows every column's record is usable: tc_conv_lean_kernel may run
+    // tc_conv_lean_kernel only: the batch dimension is (image, parity of the output column): batch index 2 n + p holds
+    // the output columns 2 ox' + p of image n; out_ow_real is the true output width (OW is the per-parity width)
+    int xpar, out_ow_real;
     int double_round;
     int32_t out_zp;
     int32_t clamp_lo, clamp_hi;    // also the dtype range
@@ -327,6 +330,8 @@ struct TcProblem
 // Returns TB200_OK and launches, or TB200_ERROR with ctx->err set when the shape does not qualify
 // (the caller then uses the CUDA-core kernels).
 bool tc_gemm_supported(const TcProblem& p, std::string* why);
+// true when tc_gemm_launch would run the problem on tc_conv_lean_kernel (the only kernel that understands p.xpar)
+bool tc_gemm_lean_supported(const tb200_ctx* ctx, const TcProblem& p);
 tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& p);
 // Total tile count of a problem and the tiles per row block (per batch for MATMUL); tiles are numbered batch-major.
 bool tc_gemm_tile_counts(const TcProblem& p, int* num_tiles, int* tiles_per_row_block);

@@ -1606,6 +1606,44 @@ __global__ void pad_expand_i8_kernel(const int8_t* __restrict__ in, int8_t* __re
     }
 }
 
+// Few-channel input for a stride-2 window, four bytes per pixel, one copy per parity of the output column:
+// xq[n][p][y][xi] (4 bytes) = padded pixel (y, xi + 2 p), the input zero point outside the image.  The KW <= 8 taps of
+// output column 2 ox' + p then start at byte 16 ox' of row y of copy p, which is the 16-byte pitch a TMA row needs;
+// with one copy and eight bytes per pixel the same window is 64 bytes, twice the MMAs.  Four pixels per thread.
+__global__ void pad_expand_parity_i8_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ xq, int N, int IH, int IW, int IC,
+                                            int Hp, int Wq, int pad_t, int pad_l, int32_t zp)
+{
+    const int wq4       = Wq / 4;
+    const int64_t total = (int64_t)N * 2 * Hp * wq4;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    const uint32_t zp4  = (uint32_t)(zp & 0xff) * 0x01010101u;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int g    = (int)(i % wq4);
+        int64_t r      = i / wq4;
+        const int ypix = (int)(r % Hp);
+        r /= Hp;
+        const int par = (int)(r & 1);
+        const int n   = (int)(r >> 1);
+        const int y   = ypix - pad_t;
+        uint32_t v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+        {
+            const int x = g * 4 + j + 2 * par - pad_l;
+            uint32_t w  = zp4;
+            if (y >= 0 && y < IH && x >= 0 && x < IW)
+            {
+                const int8_t* src = in + (((int64_t)n * IH + y) * IW + x) * IC;
+                for (int c = 0; c < IC; c++)
+                    w = (w & ~(0xffu << (8 * c))) | ((uint32_t)(uint8_t)src[c] << (8 * c));
+            }
+            v[j] = w;
+        }
+        *reinterpret_cast<uint4*>(xq + i * 16) = make_uint4(v[0], v[1], v[2], v[3]);
+    }
+}
+
 // weights OHWI [OC][KH][KW][IC] -> [OC][KH][win] with win >= KW*Cp, element (kx*Cp + c) = w[oc][ky][kx][c], rest 0
 __global__ void repack_weights_smallc_kernel(const int8_t* __restrict__ w, int8_t* __restrict__ wr, int OC, int KH, int KW,
                                              int IC, int Cp, int win)

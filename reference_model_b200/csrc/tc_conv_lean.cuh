@@ -398,8 +398,13 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
                 TB200_TRACE(p, 7);
 
             const int ox = t.x0 + xx, oy = t.y0 + yy, on = t.n0 + nn;
-            const bool row_valid = (nn < p.BN) && (ox < p.OW) && (oy < p.OH) && (on < p.N);
-            int8_t* out_row = reinterpret_cast<int8_t*>(p.out) + (((int64_t)on * p.OH + oy) * p.OW + ox) * p.OC;
+            bool row_valid = (nn < p.BN) && (ox < p.OW) && (oy < p.OH) && (on < p.N);
+            // parity-split problems: batch index 2 n + parity holds the output columns 2 ox + parity of image n
+            const int on_r = p.lean_xpar ? (on >> 1) : on;
+            const int ox_r = p.lean_xpar ? 2 * ox + (on & 1) : ox;
+            const int ow_r = p.lean_xpar ? p.lean_ow_real : p.OW;
+            row_valid      = row_valid && ox_r < ow_r;
+            int8_t* out_row = reinterpret_cast<int8_t*>(p.out) + (((int64_t)on_r * p.OH + oy) * ow_r + ox_r) * p.OC;
             const int32_t* delta_row = nullptr;
             if (CLASSES && row_valid)
             {

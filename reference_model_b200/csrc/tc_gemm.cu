@@ -100,6 +100,7 @@ struct TcKernelParams
     // the four epilogue groups' record copies), whether the weights are resident, stages per tile
     int lean_b_off, lean_ring_off, lean_rec_off, lean_b_resident, lean_stages_per_tile;
     int lean_rec_stride;           // bytes between the epilogue groups' copies of the records (0: one copy, single column block)
+    int lean_xpar, lean_ow_real;   // batch index = 2 image + parity of the output column; true output width
     int lean_halo, lean_halo_wp;   // halo mode: one box per channel chunk and tile; wp = OW + KW - 1 accumulator rows per output row
     int double_round;
     int32_t out_zp, clamp_lo, clamp_hi;
@@ -1390,6 +1391,8 @@ bool make_lean_plan(const TcProblem& q, int num_sms, int max_smem_optin, TcPlan*
     if (!make_plan(q, num_sms, plan, nullptr))
         return false;
     TcKernelParams& k = plan->kp;
+    k.lean_xpar    = q.xpar;
+    k.lean_ow_real = q.out_ow_real;
     const int budget     = (max_smem_optin > 0 ? max_smem_optin : 232448) - 1024 /* alignment */ - 2048 /* static + margin */;
     const int rec_bytes  = 4 * k.block_n * 32;
     const int b_tx       = k.block_n * k.chunk_elems;
@@ -1406,7 +1409,7 @@ bool make_lean_plan(const TcProblem& q, int num_sms, int max_smem_optin, TcPlan*
     {
         const int swz = k.chunk_elems;    // int8: bytes of one pixel row of a chunk
         const int wp  = q.OW + q.KW - 1;
-        if (diag_env_int("TB200_LEAN_HALO", 1) != 0 && q.KH * q.KW > 1 && q.stride_x == 1 && q.stride_y == 1 && q.dil_x == 1 &&
+        if (diag_env_int("TB200_LEAN_HALO", 1) != 0 && !q.xpar && q.KH * q.KW > 1 && q.stride_x == 1 && q.stride_y == 1 && q.dil_x == 1 &&
             q.dil_y == 1 && k.tiles_col == 1 && wp <= kTileM && wp <= 256 && k.block_n >= diag_env_int("TB200_LEAN_HALO_MIN_N", 128))
         {
             int bh = std::min(q.OH, kTileM / wp);
@@ -1520,6 +1523,13 @@ bool tc_gemm_supported(const TcProblem& p, std::string* why)
     return make_plan(p, 148, &plan, why);
 }
 
+bool tc_gemm_lean_supported(const tb200_ctx* ctx, const TcProblem& p)
+{
+    TcPlan plan;
+    plan.lean = false;
+    return !tc_gemm_pair_supported(p, ctx->num_sms) && make_lean_plan(p, ctx->num_sms, ctx->max_smem_optin, &plan);
+}
+
 bool tc_gemm_tile_counts(const TcProblem& p, int* num_tiles, int* tiles_per_row_block)
 {
     TcPlan plan;
@@ -1540,6 +1550,8 @@ tb200_status tc_gemm_launch(tb200_ctx* ctx, const TcProblem& q)
     if (!make_lean_plan(q, ctx->num_sms, ctx->max_smem_optin, &plan))
     {
         plan.lean = false;
+        if (q.xpar)
+            return fail(ctx, TB200_INTERNAL, "a parity-split problem needs the lean convolution kernel");
         if (!make_plan(q, ctx->num_sms, &plan, &why))
             return fail(ctx, TB200_ERROR, "tensor-core path not applicable: %s", why.c_str());
     }
