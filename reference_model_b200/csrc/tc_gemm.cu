@@ -1479,6 +1479,14 @@ bool make_lean_plan(const TcProblem& q, int num_sms, int max_smem_optin, TcPlan*
         ksub   = k.total_chunks;
         spt    = 1;
         stages = kLeanAccBufs;    // a slot per accumulator buffer: one commit releases both
+        // (a deeper ring of such tiles with barriers of its own was measured: no faster, the loads are not what a
+        // short-K layer waits for)
+        // Column blocks of at most 128: four accumulator buffers fit tensor memory, one per epilogue group, so that all
+        // four groups work (with two buffers and two 32-column chunks per tile, half of them wait); taken when four
+        // one-tile stages fit as well.
+        if (k.block_n <= 128 && kLeanMaxAccBufs * k.total_chunks * per_chunk <= avail &&
+            diag_env_int("TB200_LEAN_ACC4", 1) != 0)
+            stages = kLeanMaxAccBufs;
     }
     else
     {
@@ -1503,9 +1511,9 @@ bool make_lean_plan(const TcProblem& q, int num_sms, int max_smem_optin, TcPlan*
     k.lean_b_off           = 0;
     k.lean_ring_off        = b_res ? b_total : 0;
     k.lean_rec_off         = k.lean_ring_off + stages * k.stage_bytes;
-    k.acc_bufs             = kLeanAccBufs;
+    k.acc_bufs             = (spt == 1) ? stages : kLeanAccBufs;
     int cols = 32;
-    while (cols < kLeanAccBufs * k.block_n)
+    while (cols < k.acc_bufs * k.block_n)
         cols *= 2;
     k.tmem_cols      = cols;
     plan->smem_bytes = k.lean_rec_off + rec_bytes + 1024;
