@@ -1891,6 +1891,18 @@ extern "C" tb200_status tb200_depthwise_conv2d(tb200_ctx* ctx, const tb200_tenso
     if (x8)
     {
         const int grid = grid_for(ctx, numel(output) / 8, block);
+        if (d.KH == 3 && d.KW == 3 && d.dy == 1 && d.dx == 1)
+        {
+            if (input->dtype == TB200_FP16)
+                depthwise3x3_fp_x8_kernel<__half><<<grid, block, 0, ctx->stream>>>(
+                    reinterpret_cast<const __half*>(input->data), reinterpret_cast<const __half*>(weight->data),
+                    reinterpret_cast<const __half*>(bias->data), reinterpret_cast<__half*>(output->data), d);
+            else
+                depthwise3x3_fp_x8_kernel<__nv_bfloat16><<<grid, block, 0, ctx->stream>>>(
+                    reinterpret_cast<const __nv_bfloat16*>(input->data), reinterpret_cast<const __nv_bfloat16*>(weight->data),
+                    reinterpret_cast<const __nv_bfloat16*>(bias->data), reinterpret_cast<__nv_bfloat16*>(output->data), d);
+            return post_launch(ctx, "depthwise_fp_x8");
+        }
         if (input->dtype == TB200_FP16)
             depthwise_fp_x8_kernel<__half><<<grid, block, 0, ctx->stream>>>(
                 reinterpret_cast<const __half*>(input->data), reinterpret_cast<const __half*>(weight->data),

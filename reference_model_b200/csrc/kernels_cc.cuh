@@ -1141,6 +1141,72 @@ __global__ void depthwise_fp_x8_kernel(const T* __restrict__ in, const T* __rest
     }
 }
 
+// The same for a 3 x 3 window without dilation: the nine input loads are issued before the first multiply-add (taps
+// outside the image load nothing and contribute a zero vector, added in its place so the accumulation order is the
+// reference's), so a thread waits for memory once.
+template <typename T>
+__global__ void depthwise3x3_fp_x8_kernel(const T* __restrict__ in, const T* __restrict__ w, const T* __restrict__ bias,
+                                          T* __restrict__ out, ConvDev p)
+{
+    const int cv        = p.IC / 8;
+    const int64_t total = (int64_t)p.N * p.OH * p.OW * cv;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int c8 = (int)(i % cv) * 8;
+        int64_t r    = i / cv;
+        const int ox = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        const int n  = (int)(r / p.OH);
+        const int y0 = oy * p.sy - p.pad_t, x0 = ox * p.sx - p.pad_l;
+        int4 vin[9];
+        bool ok[9];
+#pragma unroll
+        for (int ky = 0; ky < 3; ky++)
+#pragma unroll
+            for (int kx = 0; kx < 3; kx++)
+            {
+                const int y = y0 + ky, x = x0 + kx;
+                const int t = ky * 3 + kx;
+                ok[t]       = y >= 0 && y < p.IH && x >= 0 && x < p.IW;
+                vin[t]      = make_int4(0, 0, 0, 0);
+                if (ok[t])
+                    vin[t] = __ldg(reinterpret_cast<const int4*>(in + (((int64_t)n * p.IH + y) * p.IW + x) * p.IC + c8));
+            }
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            acc[j] = 0.f;
+#pragma unroll
+        for (int t = 0; t < 9; t++)
+        {
+            if (!ok[t])
+                continue;    // the reference skips taps outside the image: nothing is added for them
+            T vi[8], vw[8];
+            *reinterpret_cast<int4*>(vi) = vin[t];
+            *reinterpret_cast<int4*>(vw) = __ldg(reinterpret_cast<const int4*>(w + (int64_t)t * p.IC + c8));
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                acc[j] = fmaf(to_f32<T>(vi[j]), to_f32<T>(vw[j]), acc[j]);
+        }
+        T vo[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+        {
+            float v = to_f32<T>(bias[p.bias_n == 1 ? 0 : c8 + j]) + acc[j];
+            if (p.has_clamp)
+            {
+                v = (v < p.clamp_lo_f) ? p.clamp_lo_f : v;
+                v = (v > p.clamp_hi_f) ? p.clamp_hi_f : v;
+            }
+            vo[j] = from_f32<T>(v);
+        }
+        *reinterpret_cast<int4*>(out + (((int64_t)n * p.OH + oy) * p.OW + ox) * p.IC + c8) =
+            *reinterpret_cast<int4*>(vo);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ direct matmul
 __global__ void matmul_direct_i8_kernel(const int8_t* __restrict__ a, const int8_t* __restrict__ b,
                                         int32_t* __restrict__ out, int N, int H, int C, int W, int32_t a_zp,
