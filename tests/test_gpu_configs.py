@@ -313,11 +313,12 @@ def test_pipeline_wait_that_runs_out_is_reported_and_survivable(ctx):
     _free(ta, tbm, to)
 
 
-def test_lean_convolution_and_streaming_join_give_up_and_recover(ctx):
-    """The same for the two kernels a quantized graph spends its time in.  The lean convolution kernel on a 3 x 3
-    512 -> 512 layer (4608 bytes of K per tile, 144 MMAs: the first accumulator takes far more than 5 000 cycles), and
-    the streaming join with a limit below the latency of its first bulk copy.  Each reports
-    TB200_INTERNAL, leaves the context usable, and is bit-exact once the limit is back at its default."""
+def test_lean_convolution_gives_up_and_recovers(ctx):
+    """The same for the kernel a quantized graph spends its time in: the lean convolution kernel on a 3 x 3 512 -> 512
+    layer (4608 bytes of K per tile, 144 MMAs: the first accumulator takes far more than 5 000 cycles) reports
+    TB200_INTERNAL, leaves the context usable, and is bit-exact once the limit is back at its default.  (The streaming
+    join's waits cannot be made to run out this way: each is a hardware-suspended try_wait that returns when its bulk
+    copy lands, well inside the first poll.)"""
     r = util.rng(92)
     N, IH, IC, OC = 6, 7, 512, 512
     x = r.integers(-128, 128, size=(N, IH, IH, IC), dtype=np.int8)
@@ -325,7 +326,7 @@ def test_lean_convolution_and_streaming_join_give_up_and_recover(ctx):
     b = r.integers(-65536, 65536, size=OC).astype(np.int32)
     mult, shift = util.rescale_params(r, OC)
     shift = np.maximum(shift, 34).astype(np.int8)
-    est, acc = orc.conv2d(x, w, b, [1, 1, 1, 1], [1, 1], [1, 1], -128, 0)
+    acc = orc.conv2d(x, w, b, [1, 1, 1, 1], [1, 1], [1, 1], -128, 0, nthreads=orc.num_procs())
     est, exp = orc.rescale(acc, mult, shift, True, True, "DOUBLE_ROUND", 0, -128, 32, 8)
     assert est == orc.VALID
     tx, tw, tbias, tm, ts = (ctx.from_numpy(v) for v in (x, w, b, mult, shift))
@@ -347,35 +348,6 @@ def test_lean_convolution_and_streaming_join_give_up_and_recover(ctx):
     st, out = to.download()
     assert st == tb.Status.OK and np.array_equal(out.astype(np.int32), exp)
     _free(tx, tw, tbias, tm, ts, to)
-
-    shape = (9, 70, 66, 128)
-    a = r.integers(-128, 128, size=shape).astype(np.int8)
-    c = r.integers(-128, 128, size=shape).astype(np.int8)
-    ma, sa, mb, sb, mo, so = [1 << 30], [11], [1518500250], [12], [1270000000], [49]
-    _, ea = orc.rescale(a, ma, sa, False, True, "SINGLE_ROUND", -128, 0, 8, 32)
-    _, eb = orc.rescale(c, mb, sb, False, True, "SINGLE_ROUND", 3, 0, 8, 32)
-    _, es = orc.add(ea, eb)
-    est, eo = orc.rescale(es, mo, so, False, True, "DOUBLE_ROUND", 0, -128, 32, 8)
-    _, eo = orc.clamp(eo, -128, 127)
-    consts = [ctx.from_numpy(np.asarray(v, np.int32)) for v in (ma, mb, mo)] + \
-             [ctx.from_numpy(np.asarray(v, np.int8)) for v in (sa, sb, so)]
-    ta, tc, tj = ctx.from_numpy(a), ctx.from_numpy(c), ctx.empty(tb.DType.INT8, shape)
-    join = lambda: ctx.residual_add(ta, tb.RescaleAttr(consts[0], consts[3], -128, 0), tc, tb.RescaleAttr(consts[1], consts[4], 3, 0),
-                                    tb.RescaleAttr(consts[2], consts[5], 0, -128, rounding="DOUBLE_ROUND"), tj, clamp=(-128, 127))
-    join()
-    assert ctx.sync() == tb.Status.OK and ctx.last_kernel() == "residual_add_i8_stream"
-    ctx.set_wait_limit(300)
-    try:
-        join()
-        st = ctx.sync(check=False)
-        assert st == tb.Status.INTERNAL, st
-        assert "gave up" in ctx.last_error()
-    finally:
-        ctx.set_wait_limit(4000000000)
-    join()
-    st, out = tj.download()
-    assert st == tb.Status.OK and np.array_equal(out.astype(np.int32), eo)
-    _free(ta, tc, tj, *consts)
 
 
 # ------------------------------------------------------------------------------------------- whole graph, 32 images
