@@ -181,6 +181,51 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
         : "memory");
 }
 
+// One K chunk of an int8 tile in a single statement: `count` (1, 2 or 4) MMAs of 32 bytes of K each, the operand
+// descriptors advanced by 32 bytes (2 in descriptor units) between them, the first one accumulating only if `accumulate`
+// is non-zero.  The issuing thread shares its scheduler with busy epilogue warps, so every instruction it needs per MMA
+// delays the next MMA: this form costs two predicate set-ups per chunk and two adds per further MMA.
+__device__ __forceinline__ void mma_i8_ss_chunk(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
+                                                int count)
+{
+    if (count == 4)
+        asm volatile(
+            "{\n"
+            ".reg .pred p, t;\n"
+            ".reg .b64 a, b;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "setp.eq.u32 t, 0, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+            "add.s64 a, %1, 2;\n"
+            "add.s64 b, %2, 2;\n"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], a, b, %3, t;\n"
+            "add.s64 a, %1, 4;\n"
+            "add.s64 b, %2, 4;\n"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], a, b, %3, t;\n"
+            "add.s64 a, %1, 6;\n"
+            "add.s64 b, %2, 6;\n"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], a, b, %3, t;\n"
+            "}\n" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else if (count == 2)
+        asm volatile(
+            "{\n"
+            ".reg .pred p, t;\n"
+            ".reg .b64 a, b;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "setp.eq.u32 t, 0, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+            "add.s64 a, %1, 2;\n"
+            "add.s64 b, %2, 2;\n"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], a, b, %3, t;\n"
+            "}\n" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else
+        mma_i8_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
+}
+
 // 8-bit floating operands (E4M3 / E5M2, chosen per operand by the instruction descriptor), fp32 accumulators
 __device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                           uint32_t accumulate)

@@ -290,14 +290,8 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
                                 uint64_t ac = tap;
                                 for (int c2 = 0; c2 < p.chunks_per_tap; c2++)
                                 {
-                                    uint64_t ad = ac, bd = bd_chunk;
-                                    for (int m = 0; m < mmas; m++)
-                                    {
-                                        ptx::mma_i8_ss(d_tmem, ad, bd, idesc, accum);
-                                        accum = 1;
-                                        ad += 2;
-                                        bd += 2;
-                                    }
+                                    ptx::mma_i8_ss_chunk(d_tmem, ac, bd_chunk, idesc, accum, mmas);
+                                    accum = 1;
                                     ac += a_chunk16;
                                     bd_chunk += b_chunk16;
                                 }
@@ -307,14 +301,8 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
                     else
                     for (int j = 0; j < nchunks; j++)
                     {
-                        uint64_t ad = ad_chunk, bd = bd_chunk;
-                        for (int m = 0; m < mmas; m++)
-                        {
-                            ptx::mma_i8_ss(d_tmem, ad, bd, idesc, accum);
-                            accum = 1;
-                            ad += 2;    // 32 bytes of K
-                            bd += 2;
-                        }
+                        ptx::mma_i8_ss_chunk(d_tmem, ad_chunk, bd_chunk, idesc, accum, mmas);    // 32 bytes of K per MMA
+                        accum = 1;
                         ad_chunk += a_chunk16;
                         bd_chunk += b_chunk16;
                     }
