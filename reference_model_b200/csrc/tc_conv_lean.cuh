@@ -25,7 +25,8 @@ constexpr int kLeanThreads   = 64 + 32 * kLeanEpiWarps;
 constexpr int kLeanAccBufs   = 2;    // accumulator buffers of a 256-column block
 constexpr int kLeanMaxAccBufs = 4;   // column blocks of at most 128 get four (one per epilogue group)
 
-// tiles are numbered column block major here: a CTA stays in one column block as long as it can
+// Tiles are numbered column block major here (tile = column block * tiles_m + ((image block * tiles_y + y block) * tiles_x
+// + x block)): a CTA stays in one column block as long as it can.
 __device__ __forceinline__ TileCoord lean_decode_tile(const TcKernelParams& p, int tile)
 {
     TileCoord t;
@@ -39,6 +40,54 @@ __device__ __forceinline__ TileCoord lean_decode_tile(const TcKernelParams& p, i
     t.n0 = (r / p.tiles_y) * p.BN;
     return t;
 }
+
+// The walk over them without a division per tile: a role visits tiles first, first + step, first + 2 step, ...; the four
+// digits of the tile number (x block, y block, image block, column block) advance by the digits of `step` with carries.
+// (The producer is a single thread that shares its scheduler with busy epilogue warps: three integer divisions per tile
+// were a measurable part of its time per tile.)
+struct LeanTileWalk
+{
+    int xi, yi, ni, cb;        // digits of the current tile
+    int dx, dy, dn, dcb;       // digits of the step
+    __device__ __forceinline__ void start(const TcKernelParams& p, int first, int step)
+    {
+        const int tiles_m = p.tiles_x * p.tiles_y * p.tiles_n;
+        cb    = first / tiles_m;
+        int r = first - cb * tiles_m;
+        xi    = r % p.tiles_x;
+        r /= p.tiles_x;
+        yi = r % p.tiles_y;
+        ni = r / p.tiles_y;
+        dcb = step / tiles_m;
+        r   = step - dcb * tiles_m;
+        dx  = r % p.tiles_x;
+        r /= p.tiles_x;
+        dy = r % p.tiles_y;
+        dn = r / p.tiles_y;
+    }
+    __device__ __forceinline__ TileCoord coord(const TcKernelParams& p) const
+    {
+        TileCoord t;
+        t.col0 = cb * p.block_n;
+        t.x0   = xi * p.BW;
+        t.y0   = yi * p.BH;
+        t.n0   = ni * p.BN;
+        return t;
+    }
+    __device__ __forceinline__ void advance(const TcKernelParams& p)
+    {
+        xi += dx;
+        int c = xi >= p.tiles_x ? 1 : 0;
+        xi -= c * p.tiles_x;
+        yi += dy + c;
+        c = yi >= p.tiles_y ? 1 : 0;
+        yi -= c * p.tiles_y;
+        ni += dn + c;
+        c = ni >= p.tiles_n ? 1 : 0;
+        ni -= c * p.tiles_n;
+        cb += dcb + c;
+    }
+};
 
 // Sixteen accumulators of one row through the lean RESCALE form, saturated and packed to sixteen int8.  `delta`, for a
 // border pixel, points at what its class of clipped tap rectangle adds to the interior correction (added four columns
@@ -160,9 +209,11 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
             uint32_t phase = 0;
             const int a_chunk_bytes = p.a_chunk_bytes, b_chunk_bytes = p.b_chunk_bytes, chunk_elems = p.chunk_elems;
             const uint32_t tx_per_chunk = (uint32_t)p.tx_bytes_per_chunk;
-            for (int i = 0; i < my_tiles && ok; i++)
+            LeanTileWalk walk;
+            walk.start(p, p.tile_begin + (int)blockIdx.x, (int)gridDim.x);
+            for (int i = 0; i < my_tiles && ok; i++, walk.advance(p))
             {
-                const TileCoord t = lean_decode_tile(p, p.tile_begin + (int)blockIdx.x + i * (int)gridDim.x);
+                const TileCoord t = walk.coord(p);
                 const int ax0 = t.x0 * p.stride_x - p.pad_l;
                 const int ay0 = t.y0 * p.stride_y - p.pad_t;
                 int chunk_k = 0, cc = 0, ky = 0, kx = 0;
@@ -352,6 +403,8 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
         bool dep_waited = false;
         for (int i = acc; i < my_tiles; i += acc_bufs)
         {
+            // (the epilogue decodes with divisions: the eight registers of a LeanTileWalk cost it more in spills under the
+            // 96-register cap than the divisions cost, 1x1 64 -> 256 measured 139 against 130 us)
             const TileCoord t = lean_decode_tile(p, p.tile_begin + (int)blockIdx.x + i * (int)gridDim.x);
             if (loaded_col0 != t.col0)
             {
