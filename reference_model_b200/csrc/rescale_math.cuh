@@ -140,4 +140,29 @@ __host__ __device__ __forceinline__ int32_t rescale_rec_apply(int32_t acc, int32
     return hi >> sh;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Unsigned division by an invariant d >= 1 as a multiply-high and shifts, exact for every 32-bit dividend:
+// l = ceil(log2 d), m = floor(2^32 (2^l - d) / d) + 1, q = (t + ((n - t) >> 1)) >> (l - 1) with t = high word of m * n;
+// l = 0 (d = 1) stands for q = n.  The kernels decode tile numbers with it (three divisions per tile otherwise).
+__host__ __device__ __forceinline__ void fastdiv_make(uint32_t d, uint32_t out[2])
+{
+    uint32_t l = 0;
+    while ((1ull << l) < d)
+        l++;
+    out[0] = l == 0 ? 0u : (uint32_t)((((1ull << l) - d) << 32) / d + 1);
+    out[1] = l;
+}
+
+__host__ __device__ __forceinline__ uint32_t fastdiv_apply(uint32_t n, const uint32_t (&md)[2])
+{
+    if (md[1] == 0)
+        return n;
+#ifdef __CUDA_ARCH__
+    const uint32_t t = __umulhi(md[0], n);
+#else
+    const uint32_t t = (uint32_t)(((uint64_t)md[0] * n) >> 32);
+#endif
+    return (t + ((n - t) >> 1)) >> (md[1] - 1);
+}
+
 }    // namespace tb200

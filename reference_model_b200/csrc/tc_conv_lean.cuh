@@ -31,13 +31,14 @@ __device__ __forceinline__ TileCoord lean_decode_tile(const TcKernelParams& p, i
 {
     TileCoord t;
     const int tiles_m = p.tiles_x * p.tiles_y * p.tiles_n;
-    const int cb      = tile / tiles_m;
+    const int cb      = (int)fastdiv_apply((uint32_t)tile, p.fd_m);
     int r             = tile - cb * tiles_m;
     t.col0            = cb * p.block_n;
-    t.x0              = (r % p.tiles_x) * p.BW;
-    r /= p.tiles_x;
-    t.y0 = (r % p.tiles_y) * p.BH;
-    t.n0 = (r / p.tiles_y) * p.BN;
+    const int ry      = (int)fastdiv_apply((uint32_t)r, p.fd_x);
+    t.x0              = (r - ry * p.tiles_x) * p.BW;
+    const int rn      = (int)fastdiv_apply((uint32_t)ry, p.fd_y);
+    t.y0              = (ry - rn * p.tiles_y) * p.BH;
+    t.n0              = rn * p.BN;
     return t;
 }
 

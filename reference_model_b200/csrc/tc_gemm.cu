@@ -100,6 +100,7 @@ struct TcKernelParams
     // the four epilogue groups' record copies), whether the weights are resident, stages per tile
     int lean_b_off, lean_ring_off, lean_rec_off, lean_b_resident, lean_stages_per_tile;
     int lean_rec_stride;           // bytes between the epilogue groups' copies of the records (0: one copy, single column block)
+    uint32_t fd_m[2], fd_x[2], fd_y[2];    // division by tiles_m, tiles_x, tiles_y as multiply-high + shift (fastdiv_make)
     int lean_xpar, lean_ow_real;   // batch index = 2 image + parity of the output column; true output width
     int lean_halo, lean_halo_wp;   // halo mode: one box per channel chunk and tile; wp = OW + KW - 1 accumulator rows per output row
     int double_round;
@@ -1373,6 +1374,13 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
 }
 
 
+void lean_fastdiv_set(TcKernelParams& k)
+{
+    fastdiv_make((uint32_t)(k.tiles_x * k.tiles_y * k.tiles_n), k.fd_m);
+    fastdiv_make((uint32_t)k.tiles_x, k.fd_x);
+    fastdiv_make((uint32_t)k.tiles_y, k.fd_y);
+}
+
 // Re-plans a problem make_plan has laid out for tc_conv_lean_kernel: one CTA per SM, the fewest stages per tile that
 // fit (one when a tile's operands fit twice into shared memory), weights resident when there is a single column block.
 bool make_lean_plan(const TcProblem& q, int num_sms, int max_smem_optin, TcPlan* plan)
@@ -1466,6 +1474,7 @@ bool make_lean_plan(const TcProblem& q, int num_sms, int max_smem_optin, TcPlan*
                 plan->ctas_per_sm = 1;
                 plan->grid        = std::max(1, std::min(k.num_tiles, num_sms));
                 plan->lean        = true;
+                lean_fastdiv_set(k);
                 return true;
             }
         }
@@ -1520,6 +1529,7 @@ bool make_lean_plan(const TcProblem& q, int num_sms, int max_smem_optin, TcPlan*
     plan->ctas_per_sm = 1;
     plan->grid        = std::max(1, std::min(k.num_tiles, num_sms));
     plan->lean        = true;
+    lean_fastdiv_set(k);
     return plan->smem_bytes <= budget + 1024;
 }
 
