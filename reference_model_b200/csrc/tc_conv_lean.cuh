@@ -141,7 +141,8 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
     const uint32_t s_b       = smem_base + (uint32_t)p.lean_b_off;       // resident weights (when p.lean_b_resident)
     const uint32_t s_ring    = smem_base + (uint32_t)p.lean_ring_off;    // stages: ksub A chunks, then ksub B chunks if streamed
     const int acc_bufs       = p.acc_bufs;                  // 2, or 4 when four buffers of block_n columns fit tensor memory
-    const int groups_per_buf = 4 / acc_bufs;                // epilogue groups that share one accumulator buffer
+    const int acc_shift      = acc_bufs == 4 ? 2 : 1;       // log2(acc_bufs): tile counters are split with shifts, not divisions
+    const int groups_per_buf = 4 >> acc_shift;              // epilogue groups that share one accumulator buffer
     const bool one_stage     = p.lean_stages_per_tile == 1;
     // Halo mode (stride-1 convolutions with a window, weights resident): a tile is BH whole output rows, and ONE box
     // per channel chunk brings the BH + KH - 1 input rows it needs, halo columns included (zero filled outside the
@@ -300,8 +301,8 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
             const uint64_t a_chunk16 = (uint64_t)(p.a_chunk_bytes >> 4), b_chunk16 = (uint64_t)(p.b_chunk_bytes >> 4);
             for (int i = 0; i < my_tiles && ok; i++)
             {
-                const int acc            = i % acc_bufs;
-                const uint32_t acc_phase = (uint32_t)(i / acc_bufs) & 1u;
+                const int acc            = i & (acc_bufs - 1);
+                const uint32_t acc_phase = (uint32_t)(i >> acc_shift) & 1u;
                 if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, p.wait_limit))
                 {
                     ok = false;
@@ -431,7 +432,7 @@ __global__ void __launch_bounds__(kLeanThreads, 1) tc_conv_lean_kernel(const __g
             // (the other three warps may still be working); it does no further work.
             if (!ok)
                 continue;
-            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_full[acc]), (uint32_t)(i / acc_bufs) & 1u, p.wait_limit);
+            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_full[acc]), (uint32_t)(i >> acc_shift) & 1u, p.wait_limit);
             ok = __all_sync(0xffffffffu, ok);    // the whole warp agrees before the warp-collective TMEM loads
             if (!ok)
                 continue;
