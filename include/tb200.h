@@ -243,6 +243,25 @@ extern "C"
                                                   const int32_t stride[2], const int32_t dilation[2],
                                                   const tb200_epilogue* epilogue, tb200_tensor* output);
 
+    /* CONV2D with a 1x1 kernel (stride 1, no padding) -> optional CLAMP -> DEPTHWISE_CONV2D with a 3x3 kernel
+     * (multiplier 1, no dilation) -> optional CLAMP, evaluated as ONE kernel for FP16 and BF16: the tensor between the
+     * two operators (the largest tensor of an inverted-residual block, with a single consumer,
+     * reference_model/src/tensor.h:92-100) never reaches device memory.  Stands for OpConv2d::eval
+     * (reference_model/src/ops/tensor_ops.cpp:723-882), OpClamp (reference_model/src/ops/activation_funcs.cpp:27-128),
+     * OpDepthwiseConv2d::eval (tensor_ops.cpp:1172-1334) and OpClamp again, with the CONV2D result rounded to the
+     * storage type before the window runs over it, as the reference's intermediate tensor is.
+     * input NHWC [N,IH,IW,IC], weight [C,1,1,IC], bias [C] or [1]; dw_weight [3,3,C,1], dw_bias [C] or [1];
+     * dw_pad = {top,bottom,left,right}, dw_stride = {y,x}; output [N,OH,OW,C].  The one-kernel form needs IC of 16, 32
+     * or 64, C a multiple of 64, IW <= 128 and strides of 1 or 2 (tb200_last_kernel then names expand_dw_f16 or
+     * expand_dw_bf16, and `expanded` is not touched).  Any other shape runs tb200_conv2d into `expanded`
+     * ([N,IH,IW,C]) and tb200_depthwise_conv2d out of it; with `expanded` NULL such a shape is TB200_ERROR. */
+    TB200_API tb200_status tb200_conv2d_depthwise(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
+                                                  const tb200_tensor* bias, const tb200_epilogue* conv_epilogue,
+                                                  const tb200_tensor* dw_weight, const tb200_tensor* dw_bias,
+                                                  const int32_t dw_pad[4], const int32_t dw_stride[2],
+                                                  const tb200_epilogue* dw_epilogue, tb200_tensor* expanded,
+                                                  tb200_tensor* output);
+
     /* TRANSPOSE_CONV2D.  Replaces OpTransposeConv2d::eval (reference_model/src/ops/tensor_ops.cpp:2059-2197) and
      * OpTransposeConv2d::checkTensorAttributes (:1982-2056).  input NHWC, weight OHWI, bias [OC] or [1];
      * out_pad = {top,bottom,left,right} (each > -kernel), stride = {y,x}; the output must be

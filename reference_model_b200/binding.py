@@ -72,7 +72,7 @@ EXPORTS = [
     "tb200_timer_enable", "tb200_timer_read", "tb200_capture_begin", "tb200_capture_end", "tb200_graph_launch",
     "tb200_graph_destroy",
     "tb200_tensor_alloc", "tb200_tensor_wrap", "tb200_tensor_free", "tb200_tensor_upload", "tb200_tensor_download",
-    "tb200_tensor_data", "tb200_tensor_bytes", "tb200_tensor_slice", "tb200_tensor_reshape", "tb200_conv2d", "tb200_depthwise_conv2d", "tb200_transpose_conv2d", "tb200_matmul",
+    "tb200_tensor_data", "tb200_tensor_bytes", "tb200_tensor_slice", "tb200_tensor_reshape", "tb200_conv2d", "tb200_depthwise_conv2d", "tb200_conv2d_depthwise", "tb200_transpose_conv2d", "tb200_matmul",
     "tb200_rescale", "tb200_clamp", "tb200_add", "tb200_residual_add", "tb200_max_pool2d", "tb200_avg_pool2d",
     "tb200_matmul_host", "tb200_set_kernel_policy", "tb200_last_kernel", "tb200_matmul_i8_noalloc",
     "tb200_npy_probe", "tb200_tensor_load_npy", "tb200_tensor_save_npy",
@@ -116,6 +116,8 @@ def load_library():
         "tb200_tensor_bytes": (ctypes.c_size_t, [vp]),
         "tb200_conv2d": (i32, [vp, vp, vp, vp, i32, i32, p_i32, p_i32, p_i32, ctypes.POINTER(_Epilogue), vp]),
         "tb200_depthwise_conv2d": (i32, [vp, vp, vp, vp, i32, i32, p_i32, p_i32, p_i32, ctypes.POINTER(_Epilogue), vp]),
+        "tb200_conv2d_depthwise": (i32, [vp, vp, vp, vp, ctypes.POINTER(_Epilogue), vp, vp, p_i32, p_i32,
+                                         ctypes.POINTER(_Epilogue), vp, vp]),
         "tb200_transpose_conv2d": (i32, [vp, vp, vp, vp, i32, i32, p_i32, p_i32, ctypes.POINTER(_Epilogue), vp]),
         "tb200_matmul": (i32, [vp, vp, vp, i32, i32, ctypes.POINTER(_Epilogue), vp]),
         "tb200_rescale": (i32, [vp, vp, ctypes.POINTER(_RescaleAttr), vp]),
@@ -423,6 +425,16 @@ class Context:
                                                            _ivec(dilation),
                                                            ctypes.byref(epilogue.c) if epilogue else None,
                                                            out.handle), check)
+
+    def conv2d_depthwise(self, x, w, bias, dw_w, dw_bias, out, dw_pad, dw_stride, conv_epilogue=None, dw_epilogue=None,
+                         expanded=None, check=True):
+        """CONV2D 1x1 (+ CLAMP) -> DEPTHWISE_CONV2D 3x3 (+ CLAMP), one kernel where the shape allows; `expanded` is the
+        tensor between the two operators, used only by shapes that run as two kernels."""
+        return self._check(self.lib.tb200_conv2d_depthwise(
+            self.handle, x.handle, w.handle, bias.handle, ctypes.byref(conv_epilogue.c) if conv_epilogue else None,
+            dw_w.handle, dw_bias.handle, _ivec(dw_pad), _ivec(dw_stride),
+            ctypes.byref(dw_epilogue.c) if dw_epilogue else None, expanded.handle if expanded is not None else None,
+            out.handle), check)
 
     def transpose_conv2d(self, x, w, bias, out, out_pad, stride, input_zp=0, weight_zp=0, epilogue=None, check=True):
         return self._check(self.lib.tb200_transpose_conv2d(self.handle, x.handle, w.handle, bias.handle,

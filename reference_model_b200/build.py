@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(CSRC, "libtb200.so")
-SOURCES = ["api.cu", "const_cache.cu", "tc_gemm.cu", "tc_gemm_pair.cu", "sgemm_f32.cu", "no_alloc.cu", "npy_io.cu", "dist.cu"]
+SOURCES = ["api.cu", "const_cache.cu", "tc_gemm.cu", "tc_gemm_pair.cu", "sgemm_f32.cu", "expand_dw.cu", "no_alloc.cu", "npy_io.cu", "dist.cu"]
 HEADERS = ["common.h", "kernels_cc.cuh", "ptx_sm100.cuh", "rescale_math.cuh", "tc_conv_lean.cuh", "join_stream.cuh", os.path.join("..", "..", "include", "tb200.h")]
 
 NVCC_FLAGS = [

@@ -1441,6 +1441,76 @@ static PhaseAxis plan_phase_axis(int I, int K, int O, int s, int out_pad0, int p
     return a;
 }
 
+// CONV2D 1x1 -> CLAMP -> DEPTHWISE_CONV2D 3x3 -> CLAMP in one kernel (expand_dw.cu); see include/tb200.h.
+extern "C" tb200_status tb200_conv2d_depthwise(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
+                                               const tb200_tensor* bias, const tb200_epilogue* conv_epilogue,
+                                               const tb200_tensor* dw_weight, const tb200_tensor* dw_bias,
+                                               const int32_t dw_pad[4], const int32_t dw_stride[2],
+                                               const tb200_epilogue* dw_epilogue, tb200_tensor* expanded,
+                                               tb200_tensor* output)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ENTER(ctx);
+    TB200_ERROR_IF(ctx, !input || !weight || !bias || !dw_weight || !dw_bias || !dw_pad || !dw_stride || !output,
+                   "OpConv2d + OpDepthwiseConv2d: null operand");
+    TB200_ERROR_IF(ctx, !all_contiguous({ input, weight, bias, dw_weight, dw_bias, output }),
+                   "OpConv2d + OpDepthwiseConv2d: every operand must be contiguous");
+    TB200_ERROR_IF(ctx, input->rank != 4 || weight->rank != 4 || dw_weight->rank != 4 || output->rank != 4 || bias->rank != 1 ||
+                            dw_bias->rank != 1,
+                   "OpConv2d + OpDepthwiseConv2d: tensors must be rank 4 and biases rank 1");
+    const int N = input->shape[0], IH = input->shape[1], IW = input->shape[2], IC = input->shape[3];
+    const int C  = weight->shape[0];
+    const int OH = output->shape[1], OW = output->shape[2];
+    const int32_t one[2]  = { 1, 1 };
+    const int32_t zero[4] = { 0, 0, 0, 0 };
+    const tb200_dtype dt  = input->dtype;
+    bool fusable = weight->shape[1] == 1 && weight->shape[2] == 1 && weight->shape[3] == IC && dw_weight->shape[0] == 3 &&
+                   dw_weight->shape[1] == 3 && dw_weight->shape[2] == C && dw_weight->shape[3] == 1 && output->shape[0] == N &&
+                   output->shape[3] == C && (bias->shape[0] == C || bias->shape[0] == 1) &&
+                   (dw_bias->shape[0] == C || dw_bias->shape[0] == 1) && weight->dtype == dt && bias->dtype == dt &&
+                   dw_weight->dtype == dt && dw_bias->dtype == dt && output->dtype == dt && numel(output) > 0 && numel(input) > 0;
+    ExpandDwProblem q;
+    memset(&q, 0, sizeof(q));
+    if (fusable)
+    {
+        // the checks of the two operators the kernel stands for (the CONV2D's output shape is implied: [N, IH, IW, C])
+        tb200_status st = check_conv_attr(ctx, "OpDepthwiseConv2d", IH, IW, OH, OW, 3, 3, dw_pad, dw_stride, one);
+        if (st != TB200_OK)
+            return st;
+        EpiInfo e1, e2;
+        st = parse_epilogue(ctx, "OpConv2d", conv_epilogue, false, C, dt, &e1);
+        if (st != TB200_OK)
+            return st;
+        st = parse_epilogue(ctx, "OpDepthwiseConv2d", dw_epilogue, false, C, dt, &e2);
+        if (st != TB200_OK)
+            return st;
+        q.dtype = dt;
+        q.in = input->data; q.w1 = weight->data; q.b1 = bias->data; q.wd = dw_weight->data; q.bd = dw_bias->data;
+        q.out = output->data;
+        q.b1_n = bias->shape[0]; q.bd_n = dw_bias->shape[0];
+        q.N = N; q.IH = IH; q.IW = IW; q.IC = IC; q.C = C; q.OH = OH; q.OW = OW;
+        q.pad_t = dw_pad[0]; q.pad_l = dw_pad[2]; q.sy = dw_stride[0]; q.sx = dw_stride[1];
+        q.clamp1 = e1.has_clamp; q.lo1 = e1.clamp_lo_f; q.hi1 = e1.clamp_hi_f;
+        q.clamp2 = e2.has_clamp; q.lo2 = e2.clamp_lo_f; q.hi2 = e2.clamp_hi_f;
+        std::string why;
+        fusable = ctx->policy == 0 && expand_dw_supported(ctx, q, &why);
+    }
+    if (fusable)
+    {
+        cache_note_write(ctx, output->data, output->bytes);
+        return expand_dw_launch(ctx, q);
+    }
+    // shapes the kernel does not take: the two operators one after the other, through the caller's tensor
+    TB200_ERROR_IF(ctx, !expanded,
+                   "OpConv2d + OpDepthwiseConv2d: this shape does not run as one kernel and no tensor for the CONV2D output was given");
+    tb200_status st = tb200_conv2d(ctx, input, weight, bias, 0, 0, zero, one, one, conv_epilogue, expanded);
+    if (st != TB200_OK && st != TB200_UNPREDICTABLE)
+        return st;
+    const tb200_status st2 = tb200_depthwise_conv2d(ctx, expanded, dw_weight, dw_bias, 0, 0, dw_pad, dw_stride, one, dw_epilogue, output);
+    return st2 != TB200_OK ? st2 : st;
+}
+
 extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
                                                const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp,
                                                const int32_t out_pad[4], const int32_t stride[2],

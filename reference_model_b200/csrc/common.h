@@ -340,6 +340,26 @@ bool tc_gemm_tile_counts(const TcProblem& p, int* num_tiles, int* tiles_per_row_
 bool tc_gemm_pair_supported(const TcProblem& p, int num_sms);
 tb200_status tc_gemm_pair_launch(tb200_ctx* ctx, const TcProblem& p);
 
+// CONV2D 1x1 (+ CLAMP) -> DEPTHWISE_CONV2D 3x3 (+ CLAMP) as one kernel, fp16 / bf16 (expand_dw.cu): the expanded tensor
+// between the two operators stays in shared memory.
+struct ExpandDwProblem
+{
+    tb200_dtype dtype;    // TB200_FP16 or TB200_BF16: every operand and the output
+    const void* in;       // [N][IH][IW][IC]
+    const void* w1;       // CONV2D weights [C][1][1][IC]
+    const void* b1;       // CONV2D bias [C] or [1]
+    const void* wd;       // depthwise weights [3][3][C][1]
+    const void* bd;       // depthwise bias [C] or [1]
+    void* out;            // [N][OH][OW][C]
+    int b1_n, bd_n;
+    int N, IH, IW, IC, C, OH, OW;
+    int pad_t, pad_l, sy, sx;    // of the depthwise operator
+    int clamp1, clamp2;          // CLAMP after the CONV2D / after the depthwise operator
+    float lo1, hi1, lo2, hi2;
+};
+bool expand_dw_supported(const tb200_ctx* ctx, const ExpandDwProblem& q, std::string* why);
+tb200_status expand_dw_launch(tb200_ctx* ctx, const ExpandDwProblem& q);
+
 // fp32 SGEMM on CUDA cores (sgemm_f32.cu): out[n] = a[n] x b[n], a [N,H,C], b [N,C,W]
 tb200_status sgemm_f32_launch(tb200_ctx* ctx, const float* a, const float* b, float* out, int N, int H, int C, int W);
 

@@ -1,0 +1,659 @@
+// CONV2D 1x1 (+ CLAMP) followed by DEPTHWISE_CONV2D 3x3 (+ CLAMP) in fp16 / bf16 as ONE kernel: the first half of an
+// inverted-residual block, whose expanded tensor (six times the input for 32 -> 192 channels) is the largest tensor of
+// the block and has exactly one consumer.  Here it lives in shared memory only: a work item is one image, one group of
+// 64 expanded channels and a band of output rows; for every input row the band needs, the tensor cores multiply the row's
+// pixels ([<=128 pixels] x [IC]) by the group's weights ([IC] x [64]) into tensor memory, eight worker warps add the
+// bias, clamp, round to the storage type (the rounding the reference's CONV2D output has) and put the row into a ring
+// of three rows in shared memory; after the rows an output row needs are there, the same warps run the 3x3 window over
+// the ring with fp32 accumulation in the reference's tap order, add the depthwise bias, clamp, round and store.
+// Equivalent to OpConv2d::eval followed by OpClamp, OpDepthwiseConv2d::eval and OpClamp
+// (reference_model/src/ops/tensor_ops.cpp:723-882 and :1172-1334, reference_model/src/ops/activation_funcs.cpp:27-128).
+//
+// Roles: warps 0..7 workers (warp w reads the tensor-memory lane quarter w % 4, i.e. pixels 32 (w % 4) .. + 31, and the
+// 32-channel half w / 4 of the group; in the window pass warp w takes the output pixels w, w + 8, ... and lane l the
+// channel pair 2 l, 2 l + 1), warp 8 lane 0 TMA producer, warp 9 lane 0 MMA issuer (warp 9 owns tensor memory).
+// Every wait is bounded (p.wait_limit SM cycles); a wait that gives up sets TB200_DEV_TIMEOUT, the roles leave their
+// loops together, copies and MMAs in flight are waited for and tensor memory is freed.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <mutex>
+
+#include "common.h"
+#include "ptx_sm100.cuh"
+
+namespace tb200
+{
+namespace
+{
+
+constexpr int kXdWorkerWarps = 8;
+constexpr int kXdWorkers     = 32 * kXdWorkerWarps;
+constexpr int kXdThreads     = kXdWorkers + 64;
+constexpr int kXdGroup       = 64;    // expanded channels per work item = columns of one accumulator buffer
+constexpr int kXdAccBufs     = 2;
+constexpr int kXdMaxStages   = 4;
+constexpr int kXdRing        = 3;     // expanded rows kept: a 3-row window moving down by one or two rows
+constexpr int kXdPixelBytes  = kXdGroup * 2;    // one pixel of a ring row: 64 channels of 2 bytes
+// CTAs the compiler leaves register room for on one SM: three CTAs cover each other's expansion, window pass and waits
+// for memory (64 registers per thread)
+#ifndef TB200_XD_MIN_CTAS
+#define TB200_XD_MIN_CTAS 3
+#endif
+
+struct XdParams
+{
+    CUtensorMap tmA;    // input as [N*IH*IW][IC], box = (IC, a_box_rows)
+    CUtensorMap tmB;    // CONV2D weights as [C][IC], box = (IC, 64)
+    const void* b1;     // CONV2D bias [C] or [1]
+    const void* wd;     // depthwise weights [3][3][C][1]
+    const void* bd;     // depthwise bias [C] or [1]
+    void* out;          // [N][OH][OW][C]
+    int b1_n, bd_n;
+    int N, IH, IW, IC, C, OH, OW;
+    int pad_t, pad_l, sy, sx;
+    int clamp1, clamp2;
+    float lo1, hi1, lo2, hi2;
+    int groups, bands, band_rows, items;
+    int stages, a_stage_bytes, a_tx_bytes, b_group_bytes;
+    int b_off, a_off, ring_off, bias_off;    // from the 1024-byte aligned start of dynamic shared memory
+    int ring_row_bytes;
+    int mmas;    // MMAs (16 channels of K each) per input row
+    uint32_t idesc;
+    uint64_t desc_hi;
+    long long wait_limit;
+    int* status;
+};
+
+template <typename T>
+struct XdType;
+template <>
+struct XdType<__half>
+{
+    static __device__ __forceinline__ float2 up2(uint32_t w)
+    {
+        return __half22float2(*reinterpret_cast<const __half2*>(&w));
+    }
+    static __device__ __forceinline__ uint32_t down2(float a, float b)
+    {
+        const __half2 h = __halves2half2(__float2half_rn(a), __float2half_rn(b));
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+    static __device__ __forceinline__ float up(const void* p, int i)
+    {
+        return __half2float(reinterpret_cast<const __half*>(p)[i]);
+    }
+};
+template <>
+struct XdType<__nv_bfloat16>
+{
+    static __device__ __forceinline__ float2 up2(uint32_t w)
+    {
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    }
+    static __device__ __forceinline__ uint32_t down2(float a, float b)
+    {
+        const __nv_bfloat162 h = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(b));
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+    static __device__ __forceinline__ float up(const void* p, int i)
+    {
+        return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+    }
+};
+
+// NaN passes through: both comparisons are false for it (the reference's CLAMP on a NaN gives NaN as well)
+__device__ __forceinline__ float xd_clamp(float v, float lo, float hi)
+{
+    v = (v < lo) ? lo : v;
+    v = (v > hi) ? hi : v;
+    return v;
+}
+
+struct XdItem
+{
+    int n, g, oy0, oy1, r_lo, r_hi;    // image, channel group, output rows [oy0, oy1), input rows [r_lo, r_hi]
+};
+
+// Items are numbered (image, band, group) with the group fastest: the CTAs that work on the three groups of a band at
+// the same time read the same input rows.
+__device__ __forceinline__ XdItem xd_decode(const XdParams& p, int item)
+{
+    XdItem t;
+    t.g         = item % p.groups;
+    const int r = item / p.groups;
+    const int b = r % p.bands;
+    t.n         = r / p.bands;
+    t.oy0       = b * p.band_rows;
+    t.oy1       = min(p.OH, t.oy0 + p.band_rows);
+    t.r_lo      = max(0, t.oy0 * p.sy - p.pad_t);
+    t.r_hi      = min(p.IH - 1, (t.oy1 - 1) * p.sy - p.pad_t + 2);
+    return t;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kernel(const __grid_constant__ XdParams p)
+{
+    extern __shared__ uint8_t xd_smem_raw[];
+    __shared__ __align__(8) uint64_t bar_a_full[kXdMaxStages];     // TMA -> MMA: the input row has landed
+    __shared__ __align__(8) uint64_t bar_a_empty[kXdMaxStages];    // MMA -> TMA: the row's MMAs have read it
+    __shared__ __align__(8) uint64_t bar_acc_full[kXdAccBufs];     // MMA -> workers: the expanded row is in tensor memory
+    __shared__ __align__(8) uint64_t bar_acc_empty[kXdAccBufs];    // workers -> MMA: accumulator buffer drained
+    __shared__ __align__(8) uint64_t bar_b;                        // the CONV2D weights have landed
+    __shared__ __align__(8) uint64_t bar_drain;                    // teardown after a wait gave up
+    __shared__ uint32_t tmem_base_holder;
+    __shared__ int abort_flag;
+
+    const int warp           = threadIdx.x >> 5;
+    const int lane           = threadIdx.x & 31;
+    const uint32_t smem_base = (ptx::smem_u32(xd_smem_raw) + 1023u) & ~1023u;
+    uint8_t* const smem_al   = xd_smem_raw + (smem_base - ptx::smem_u32(xd_smem_raw));
+    const uint32_t s_b       = smem_base + (uint32_t)p.b_off;
+    const uint32_t s_a       = smem_base + (uint32_t)p.a_off;
+    float* const s_bias      = reinterpret_cast<float*>(smem_al + p.bias_off);
+
+    if (threadIdx.x == 0)
+    {
+        for (int s = 0; s < p.stages; s++)
+        {
+            ptx::mbar_init(ptx::smem_u32(&bar_a_full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bar_a_empty[s]), 1);
+        }
+        for (int a = 0; a < kXdAccBufs; a++)
+        {
+            ptx::mbar_init(ptx::smem_u32(&bar_acc_full[a]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bar_acc_empty[a]), kXdWorkerWarps);    // one arrival per worker warp
+        }
+        ptx::mbar_init(ptx::smem_u32(&bar_b), 1);
+        ptx::mbar_init(ptx::smem_u32(&bar_drain), 1);
+        abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tmap(&p.tmA);
+        ptx::prefetch_tmap(&p.tmB);
+    }
+    if (warp == kXdWorkerWarps + 1)
+    {
+        ptx::tmem_alloc(ptx::smem_u32(&tmem_base_holder), (uint32_t)(kXdAccBufs * kXdGroup));
+        ptx::tmem_relinquish();
+    }
+    // the CONV2D bias of every channel as fp32 (added to the fp32 accumulator, as the reference adds it before rounding)
+    for (int c = threadIdx.x; c < p.C; c += blockDim.x)
+        s_bias[c] = XdType<T>::up(p.b1, p.b1_n == 1 ? 0 : c);
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_holder;
+    const int my_items       = (p.items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+
+    if (warp == kXdWorkerWarps)
+    {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0)
+        {
+            // the weights of all channel groups, once
+            ptx::mbar_arrive_expect_tx(ptx::smem_u32(&bar_b), (uint32_t)(p.groups * p.b_group_bytes));
+            for (int g = 0; g < p.groups; g++)
+                ptx::tma_load_2d(s_b + (uint32_t)(g * p.b_group_bytes), &p.tmB, ptx::smem_u32(&bar_b), 0, g * kXdGroup);
+            bool ok        = true;
+            int stage      = 0;
+            uint32_t phase = 0;
+            for (int i = 0; i < my_items && ok; i++)
+            {
+                const XdItem t = xd_decode(p, (int)blockIdx.x + i * (int)gridDim.x);
+                for (int r = t.r_lo; r <= t.r_hi; r++)
+                {
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_a_empty[stage]), phase ^ 1u, p.wait_limit))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = ptx::smem_u32(&bar_a_full[stage]);
+                    ptx::mbar_arrive_expect_tx(full, (uint32_t)p.a_tx_bytes);
+                    ptx::tma_load_2d(s_a + (uint32_t)(stage * p.a_stage_bytes), &p.tmA, full, 0, (t.n * p.IH + r) * p.IW);
+                    if (++stage == p.stages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok)
+            {
+                atomicOr(p.status, TB200_DEV_TIMEOUT);
+                atomicExch(&abort_flag, 1);
+            }
+        }
+    }
+    else if (warp == kXdWorkerWarps + 1)
+    {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0)
+        {
+            bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_b), 0u, p.wait_limit);
+            ptx::tc_fence_after_sync();
+            int stage      = 0;
+            uint32_t phase = 0;
+            uint32_t k     = 0;    // input rows issued so far
+            for (int i = 0; i < my_items && ok; i++)
+            {
+                const XdItem t    = xd_decode(p, (int)blockIdx.x + i * (int)gridDim.x);
+                const uint64_t bd = ptx::smem_desc(p.desc_hi, s_b + (uint32_t)(t.g * p.b_group_bytes));
+                for (int r = t.r_lo; r <= t.r_hi; r++, k++)
+                {
+                    const uint32_t buf = k & 1u;
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_empty[buf]), ((k >> 1) & 1u) ^ 1u, p.wait_limit) ||
+                        !ptx::mbar_wait_bounded(ptx::smem_u32(&bar_a_full[stage]), phase, p.wait_limit))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint64_t ad     = ptx::smem_desc(p.desc_hi, s_a + (uint32_t)(stage * p.a_stage_bytes));
+                    const uint32_t d_tmem = tmem_base + buf * (uint32_t)kXdGroup;
+                    for (int m = 0; m < p.mmas; m++)    // 16 channels (32 bytes) of K per MMA
+                        ptx::mma_f16_ss(d_tmem, ad + (uint64_t)(2 * m), bd + (uint64_t)(2 * m), p.idesc, m > 0 ? 1u : 0u);
+                    ptx::mma_commit(ptx::smem_u32(&bar_a_empty[stage]));
+                    ptx::mma_commit(ptx::smem_u32(&bar_acc_full[buf]));
+                    if (++stage == p.stages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok)
+            {
+                atomicOr(p.status, TB200_DEV_TIMEOUT);
+                atomicExch(&abort_flag, 1);
+            }
+        }
+    }
+    else
+    {
+        // ------------------------------------------------------------------ workers
+        const int quarter         = warp & 3;     // tensor-memory lane quarter this warp may read
+        const int half            = warp >> 2;    // which 32 of the group's 64 channels it expands
+        const int px              = quarter * 32 + lane;    // its pixel of an input row
+        uint8_t* const ring       = smem_al + p.ring_off;
+        const uint32_t lane_chunk = (uint32_t)lane >> 2;          // window pass: 16-byte chunk of the lane's channel pair
+        const uint32_t lane_word  = ((uint32_t)lane & 3u) << 2;   // ... and its byte offset in the chunk
+        bool ok      = true;
+        uint32_t k   = 0;    // input rows expanded so far
+        int loaded_g = -1;
+        float wgt[9][2], dbias[2];
+        for (int i = 0; i < my_items && ok; i++)
+        {
+            const XdItem t = xd_decode(p, (int)blockIdx.x + i * (int)gridDim.x);
+            if (t.g != loaded_g)
+            {
+                const int c = t.g * kXdGroup + 2 * lane;
+#pragma unroll
+                for (int tap = 0; tap < 9; tap++)
+                {
+                    wgt[tap][0] = XdType<T>::up(p.wd, tap * p.C + c);
+                    wgt[tap][1] = XdType<T>::up(p.wd, tap * p.C + c + 1);
+                }
+                dbias[0] = XdType<T>::up(p.bd, p.bd_n == 1 ? 0 : c);
+                dbias[1] = XdType<T>::up(p.bd, p.bd_n == 1 ? 0 : c + 1);
+                loaded_g = t.g;
+            }
+            const float* const bb = s_bias + t.g * kXdGroup + half * 32;
+            int next_row          = t.r_lo;
+            for (int oy = t.oy0; oy < t.oy1; oy++)
+            {
+                const int iy0  = oy * p.sy - p.pad_t;
+                const int last = min(p.IH - 1, iy0 + 2);
+                // ---- expand the input rows this output row needs and the ring does not hold yet
+                for (; next_row <= last; next_row++, k++)
+                {
+                    if (!ok)
+                        continue;    // after a wait gave up: only keep the counters in step with the other warps
+                    const uint32_t buf = k & 1u;
+                    ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_full[buf]), (k >> 1) & 1u, p.wait_limit);
+                    ok = __all_sync(0xffffffffu, ok);    // the whole warp agrees before the warp-collective loads
+                    if (!ok)
+                        continue;
+                    ptx::tc_fence_after_sync();
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)kXdGroup + (uint32_t)(half * 32);
+                    uint8_t* const dst   = ring + (next_row % kXdRing) * p.ring_row_bytes + px * kXdPixelBytes;
+#pragma unroll
+                    for (int hh = 0; hh < 2; hh++)
+                    {
+                        uint32_t v[16];
+                        ptx::tmem_ld_32x32b_x16(taddr + (uint32_t)(hh * 16), v);
+                        ptx::tmem_ld_wait();
+                        uint32_t w[8];
+#pragma unroll
+                        for (int q = 0; q < 4; q++)
+                        {
+                            const float4 b4 = *reinterpret_cast<const float4*>(bb + hh * 16 + 4 * q);
+                            float f0 = __uint_as_float(v[4 * q + 0]) + b4.x;
+                            float f1 = __uint_as_float(v[4 * q + 1]) + b4.y;
+                            float f2 = __uint_as_float(v[4 * q + 2]) + b4.z;
+                            float f3 = __uint_as_float(v[4 * q + 3]) + b4.w;
+                            if (p.clamp1)
+                            {
+                                f0 = xd_clamp(f0, p.lo1, p.hi1);
+                                f1 = xd_clamp(f1, p.lo1, p.hi1);
+                                f2 = xd_clamp(f2, p.lo1, p.hi1);
+                                f3 = xd_clamp(f3, p.lo1, p.hi1);
+                            }
+                            w[2 * q]     = XdType<T>::down2(f0, f1);
+                            w[2 * q + 1] = XdType<T>::down2(f2, f3);
+                        }
+                        if (px < p.IW)
+                        {
+                            // 16-byte chunk j of a pixel sits at chunk position j ^ (pixel & 7): eight neighbouring lanes
+                            // write eight different bank groups
+                            const uint32_t j0 = (uint32_t)(half * 4 + hh * 2);
+                            const uint32_t sw = (uint32_t)px & 7u;
+                            *reinterpret_cast<uint4*>(dst + ((j0 ^ sw) << 4))        = make_uint4(w[0], w[1], w[2], w[3]);
+                            *reinterpret_cast<uint4*>(dst + (((j0 + 1u) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
+                    }
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0)
+                        ptx::mbar_arrive(ptx::smem_u32(&bar_acc_empty[buf]));
+                }
+                // the rows are in the ring for every warp (and every warp learns of a wait that gave up)
+                ok = ptx::named_barrier_and(1, kXdWorkers, ok);
+                if (!ok)
+                    break;
+                // ---- the 3x3 window over the ring: warp = output pixel (stride 8), lane = channel pair
+                bool yv[3];
+                uint32_t roff[3];
+#pragma unroll
+                for (int ky = 0; ky < 3; ky++)
+                {
+                    const int iy = iy0 + ky;
+                    yv[ky]       = iy >= 0 && iy < p.IH;
+                    roff[ky]     = (uint32_t)((yv[ky] ? iy % kXdRing : 0) * p.ring_row_bytes);
+                }
+                const bool rows_in = yv[0] && yv[1] && yv[2];
+                uint32_t* const orow =
+                    reinterpret_cast<uint32_t*>(reinterpret_cast<T*>(p.out) + ((int64_t)(t.n * p.OH + oy) * p.OW) * p.C + t.g * kXdGroup) + lane;
+                for (int ox = warp; ox < p.OW; ox += kXdWorkerWarps)
+                {
+                    const int ix0 = ox * p.sx - p.pad_l;
+                    float a0 = 0.f, a1 = 0.f;
+                    if (rows_in && ix0 >= 0 && ix0 + 2 < p.IW)
+                    {
+                        uint32_t win[9];
+#pragma unroll
+                        for (int ky = 0; ky < 3; ky++)
+#pragma unroll
+                            for (int kx = 0; kx < 3; kx++)
+                            {
+                                const uint32_t ix = (uint32_t)(ix0 + kx);
+                                win[ky * 3 + kx]  = *reinterpret_cast<const uint32_t*>(
+                                    ring + roff[ky] + ix * kXdPixelBytes + ((lane_chunk ^ (ix & 7u)) << 4) + lane_word);
+                            }
+#pragma unroll
+                        for (int tap = 0; tap < 9; tap++)
+                        {
+                            const float2 f = XdType<T>::up2(win[tap]);
+                            a0 = fmaf(f.x, wgt[tap][0], a0);
+                            a1 = fmaf(f.y, wgt[tap][1], a1);
+                        }
+                    }
+                    else
+                    {
+                        // taps outside the image are skipped, as the reference skips them
+#pragma unroll
+                        for (int ky = 0; ky < 3; ky++)
+#pragma unroll
+                            for (int kx = 0; kx < 3; kx++)
+                            {
+                                const int ixs = ix0 + kx;
+                                if (yv[ky] && ixs >= 0 && ixs < p.IW)
+                                {
+                                    const uint32_t ix = (uint32_t)ixs;
+                                    const float2 f    = XdType<T>::up2(*reinterpret_cast<const uint32_t*>(
+                                        ring + roff[ky] + ix * kXdPixelBytes + ((lane_chunk ^ (ix & 7u)) << 4) + lane_word));
+                                    a0 = fmaf(f.x, wgt[ky * 3 + kx][0], a0);
+                                    a1 = fmaf(f.y, wgt[ky * 3 + kx][1], a1);
+                                }
+                            }
+                    }
+                    float v0 = dbias[0] + a0, v1 = dbias[1] + a1;
+                    if (p.clamp2)
+                    {
+                        v0 = xd_clamp(v0, p.lo2, p.hi2);
+                        v1 = xd_clamp(v1, p.lo2, p.hi2);
+                    }
+                    orow[(int64_t)ox * (p.C / 2)] = XdType<T>::down2(v0, v1);
+                }
+                // the next row's expansion overwrites ring rows this pass has read
+                asm volatile("bar.sync 1, %0;" ::"n"(kXdWorkers) : "memory");
+            }
+        }
+        if (!ok && lane == 0)
+        {
+            atomicOr(p.status, TB200_DEV_TIMEOUT);
+            atomicExch(&abort_flag, 1);
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && abort_flag)
+    {
+        // a role gave up: let copies that may still be in flight land before the CTA's shared memory is released
+        for (int s = 0; s < p.stages; s++)
+        {
+            ptx::mbar_wait_bounded(ptx::smem_u32(&bar_a_full[s]), 0u, 2000000LL);
+            ptx::mbar_wait_bounded(ptx::smem_u32(&bar_a_full[s]), 1u, 2000000LL);
+        }
+        ptx::mbar_wait_bounded(ptx::smem_u32(&bar_b), 0u, 2000000LL);
+    }
+    if (warp == kXdWorkerWarps + 1 && lane == 0 && abort_flag)
+    {
+        // ... and let the tensor-core work already issued retire before its accumulators' tensor memory is freed
+        ptx::mma_commit(ptx::smem_u32(&bar_drain));
+        ptx::mbar_wait_bounded(ptx::smem_u32(&bar_drain), 0u, 40000000LL);
+    }
+    __syncthreads();
+    if (warp == kXdWorkerWarps + 1)
+    {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, (uint32_t)(kXdAccBufs * kXdGroup));
+    }
+}
+
+typedef CUresult (*PFN_xdEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+PFN_xdEncodeTiled xd_encode_fn()
+{
+    static PFN_xdEncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_xdEncodeTiled>(sym);
+    });
+    return fn;
+}
+
+struct XdLayout
+{
+    int stages, smem_bytes, b_off, a_off, ring_off, bias_off, a_stage_bytes, b_group_bytes, ring_row_bytes;
+};
+
+// Shared memory of one CTA with `stages` input-row stages: weights of all groups, the stages, the ring, the fp32 bias.
+XdLayout xd_layout(const ExpandDwProblem& q, int stages)
+{
+    XdLayout l;
+    const int row_bytes = q.IC * 2;
+    l.stages            = stages;
+    l.b_group_bytes     = std::max(1024, kXdGroup * row_bytes);
+    l.a_stage_bytes     = 128 * row_bytes;    // the MMA reads 128 rows whatever the image width
+    l.ring_row_bytes    = q.IW * kXdPixelBytes;
+    l.b_off             = 0;
+    l.a_off             = l.b_off + (q.C / kXdGroup) * l.b_group_bytes;
+    l.ring_off          = l.a_off + stages * l.a_stage_bytes;
+    l.bias_off          = l.ring_off + kXdRing * l.ring_row_bytes;
+    l.smem_bytes        = l.bias_off + q.C * 4 + 1024;    // + room to align the start to 1024 bytes
+    return l;
+}
+
+}    // namespace
+
+bool expand_dw_supported(const tb200_ctx* ctx, const ExpandDwProblem& q, std::string* why)
+{
+    auto no = [&](const char* m) {
+        if (why)
+            *why = m;
+        return false;
+    };
+    if (q.dtype != TB200_FP16 && q.dtype != TB200_BF16)
+        return no("fp16 and bf16 only");
+    if (q.IC != 16 && q.IC != 32 && q.IC != 64)
+        return no("input channels must be 16, 32 or 64 (one swizzled row of K per pixel)");
+    if (q.C % kXdGroup != 0 || q.C <= 0)
+        return no("expanded channels must be a multiple of 64");
+    if (q.IW > 128 || q.IW < 1)
+        return no("input rows wider than one 128-pixel MMA tile");
+    if (q.sy < 1 || q.sy > 2 || q.sx < 1 || q.sx > 2)
+        return no("strides other than 1 and 2");
+    if (q.pad_t < 0 || q.pad_l < 0)
+        return no("negative padding");
+    if ((int64_t)q.N * q.IH * q.IW >= (int64_t)1 << 31 || (int64_t)q.N * q.OH * q.OW * q.C >= (int64_t)1 << 40)
+        return no("tensor too large for 32-bit pixel coordinates");
+    if ((reinterpret_cast<uintptr_t>(q.in) | reinterpret_cast<uintptr_t>(q.w1)) & 15)
+        return no("input and weights must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(q.out) | reinterpret_cast<uintptr_t>(q.wd)) & 3)
+        return no("output and depthwise weights must be 4-byte aligned");
+    const int limit = ctx && ctx->max_smem_optin > 0 ? ctx->max_smem_optin : 227 * 1024;
+    if (xd_layout(q, 2).smem_bytes > limit)
+        return no("weights and ring do not fit in shared memory");
+    return true;
+}
+
+tb200_status expand_dw_launch(tb200_ctx* ctx, const ExpandDwProblem& q)
+{
+    std::string why;
+    if (!expand_dw_supported(ctx, q, &why))
+        return fail(ctx, TB200_ERROR, "fused CONV2D + DEPTHWISE_CONV2D not applicable: %s", why.c_str());
+    PFN_xdEncodeTiled enc = xd_encode_fn();
+    if (!enc)
+        return fail(ctx, TB200_INTERNAL, "cuTensorMapEncodeTiled is not available from the driver");
+    const bool bf16 = q.dtype == TB200_BF16;
+    const void* kernel = bf16 ? reinterpret_cast<const void*>(&expand_dw_kernel<__nv_bfloat16>)
+                              : reinterpret_cast<const void*>(&expand_dw_kernel<__half>);
+    const int limit    = ctx->max_smem_optin > 0 ? ctx->max_smem_optin : 227 * 1024;
+    // Shared memory: as many CTAs per SM as possible first (three hide each other's expansion, window pass and memory
+    // waits), then as many input-row stages as still fit.
+    const int sm_total = 228 * 1024;
+    XdLayout lay       = xd_layout(q, 2);
+    for (int ctas = 3; ctas >= 1; ctas--)
+    {
+        const int per_cta = std::min(limit, sm_total / ctas - 1024);
+        if (xd_layout(q, 2).smem_bytes > per_cta)
+            continue;
+        int stages = 2;
+        while (stages < kXdMaxStages && xd_layout(q, stages + 1).smem_bytes <= per_cta)
+            stages++;
+        lay = xd_layout(q, stages);
+        break;
+    }
+    const int attr_bit = bf16 ? 13 : 12;
+    if (!(ctx->smem_attr_set & (1u << attr_bit)))    // several CTAs of this size per SM need the largest shared-memory carve-out
+        TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    tb200_status st = raise_smem_limit(ctx, attr_bit, kernel, lay.smem_bytes);
+    if (st != TB200_OK)
+        return st;
+    int resident = 0;
+    TB200_CUDA_CHECK(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, kXdThreads, lay.smem_bytes));
+    if (resident < 1)
+        return fail(ctx, TB200_INTERNAL, "fused CONV2D + DEPTHWISE_CONV2D kernel does not fit on an SM");
+    resident = std::min(resident, 512 / (kXdAccBufs * kXdGroup));    // tensor memory: 512 columns per SM
+
+    XdParams k;
+    memset(&k, 0, sizeof(k));
+    const int row_bytes = q.IC * 2;
+    const CUtensorMapSwizzle swz =
+        row_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+    const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const int a_box_rows         = std::min(128, (q.IW + 7) & ~7);    // rows past the image row feed accumulator rows nobody reads
+    {
+        const cuuint64_t dims[2]    = { (cuuint64_t)q.IC, (cuuint64_t)q.N * q.IH * q.IW };
+        const cuuint64_t strides[1] = { (cuuint64_t)row_bytes };
+        const cuuint32_t box[2]     = { (cuuint32_t)q.IC, (cuuint32_t)a_box_rows };
+        const cuuint32_t estr[2]    = { 1, 1 };
+        CUresult r = enc(&k.tmA, dt, 2, const_cast<void*>(q.in), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return fail(ctx, TB200_INTERNAL, "tensor map for the input rejected (CUresult %d)", (int)r);
+    }
+    {
+        const cuuint64_t dims[2]    = { (cuuint64_t)q.IC, (cuuint64_t)q.C };
+        const cuuint64_t strides[1] = { (cuuint64_t)row_bytes };
+        const cuuint32_t box[2]     = { (cuuint32_t)q.IC, (cuuint32_t)kXdGroup };
+        const cuuint32_t estr[2]    = { 1, 1 };
+        CUresult r = enc(&k.tmB, dt, 2, const_cast<void*>(q.w1), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return fail(ctx, TB200_INTERNAL, "tensor map for the weights rejected (CUresult %d)", (int)r);
+    }
+    k.b1 = q.b1; k.wd = q.wd; k.bd = q.bd; k.out = q.out;
+    k.b1_n = q.b1_n; k.bd_n = q.bd_n;
+    k.N = q.N; k.IH = q.IH; k.IW = q.IW; k.IC = q.IC; k.C = q.C; k.OH = q.OH; k.OW = q.OW;
+    k.pad_t = q.pad_t; k.pad_l = q.pad_l; k.sy = q.sy; k.sx = q.sx;
+    k.clamp1 = q.clamp1; k.lo1 = q.lo1; k.hi1 = q.hi1;
+    k.clamp2 = q.clamp2; k.lo2 = q.lo2; k.hi2 = q.hi2;
+    k.groups = q.C / kXdGroup;
+    k.stages = lay.stages; k.a_stage_bytes = lay.a_stage_bytes; k.b_group_bytes = lay.b_group_bytes;
+    k.a_tx_bytes     = a_box_rows * row_bytes;
+    k.b_off = lay.b_off; k.a_off = lay.a_off; k.ring_off = lay.ring_off; k.bias_off = lay.bias_off;
+    k.ring_row_bytes = lay.ring_row_bytes;
+    k.mmas           = q.IC / 16;
+    k.idesc          = ptx::make_idesc(1u, bf16 ? 1u : 0u, bf16 ? 1u : 0u, 0u, 0u, 128u, (uint32_t)kXdGroup);
+    k.desc_hi        = ptx::make_smem_desc_hi(16, 8 * row_bytes, row_bytes == 32 ? 6u : row_bytes == 64 ? 4u : 2u);
+    k.wait_limit     = ctx->wait_limit_cycles;
+    k.status         = ctx->d_status;
+
+    // Band height: a band of R output rows expands R * sy + 2 input rows (two of them again in the next band); few rows
+    // per band waste expansions, many leave the last round of CTAs part empty.  Costs in instructions per thread: about
+    // four per expanded value, twenty-four per output value.
+    const int slots   = ctx->num_sms * resident;
+    double best_cost  = 0;
+    int best_rows     = 1;
+    for (int rows = 1; rows <= q.OH; rows++)
+    {
+        const int bands      = (q.OH + rows - 1) / rows;
+        const int64_t items  = (int64_t)q.N * bands * k.groups;
+        const int64_t rounds = (items + slots - 1) / slots;
+        const double item    = 4.0 * (rows * q.sy + 2) * q.IW + 24.0 * rows * q.OW;
+        const double cost    = (double)rounds * item;
+        if (rows == 1 || cost <= best_cost)
+        {
+            best_cost = cost;
+            best_rows = rows;
+        }
+    }
+    k.band_rows = best_rows;
+    k.bands     = (q.OH + best_rows - 1) / best_rows;
+    const int64_t items = (int64_t)q.N * k.bands * k.groups;
+    if (items >= (int64_t)1 << 31)
+        return fail(ctx, TB200_ERROR, "fused CONV2D + DEPTHWISE_CONV2D: too many work items");
+    k.items        = (int)items;
+    const int grid = (int)std::min<int64_t>(items, slots);
+
+    timer_begin(ctx);
+    if (bf16)
+        expand_dw_kernel<__nv_bfloat16><<<grid, kXdThreads, lay.smem_bytes, ctx->stream>>>(k);
+    else
+        expand_dw_kernel<__half><<<grid, kXdThreads, lay.smem_bytes, ctx->stream>>>(k);
+    timer_end(ctx);
+    return post_launch(ctx, bf16 ? "expand_dw_bf16" : "expand_dw_f16");
+}
+
+}    // namespace tb200

@@ -1,0 +1,136 @@
+"""CONV2D 1x1 (+ CLAMP) -> DEPTHWISE_CONV2D 3x3 (+ CLAMP) as one kernel (tb200_conv2d_depthwise), fp16 and bf16.
+
+The one-kernel form has to give, bit for bit, what the two operators give one after the other on the device (the CONV2D
+result rounded to the storage type, the window pass in fp32 in the reference's tap order); the two-kernel chain is the
+one the other parity tests hold against the oracle.  On top of that the fused result is checked against the oracle
+directly: DEPTHWISE_CONV2D in fp64 on the device's own CONV2D output, under the TOSA DOT_PRODUCT rule
+(reference_model/src/verify/verify_dot_product.cpp:29-139).
+"""
+import numpy as np
+import pytest
+
+import reference_model_b200 as tb
+from oracle import oracle as orc
+from tests import util
+from tests.test_gpu_configs import _down, _up, _verify_clamped
+
+pytestmark = pytest.mark.gpu
+
+F16, BF16 = tb.DType.FP16, tb.DType.BF16
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = tb.Context(0)
+    yield c
+    c.close()
+
+
+def _free(*ts):
+    for t in ts:
+        t.free()
+
+
+def _out_dim(i, pad0, pad1, stride):
+    assert (i + pad0 + pad1 - 3) % stride == 0
+    return (i + pad0 + pad1 - 3) // stride + 1
+
+
+def _operands(seed, name, N, IH, IW, IC, C, bias1, biasd):
+    r = util.rng(seed)
+    x = orc.fptrunc(r.standard_normal((N, IH, IW, IC), dtype=np.float32), name)
+    w1 = orc.fptrunc((r.standard_normal((C, 1, 1, IC)) / np.sqrt(IC)).astype(np.float32), name)
+    b1 = orc.fptrunc((0.1 * r.standard_normal(bias1)).astype(np.float32), name)
+    wd = orc.fptrunc((r.standard_normal((3, 3, C, 1)) / 3.0).astype(np.float32), name)
+    bd = orc.fptrunc((0.1 * r.standard_normal(biasd)).astype(np.float32), name)
+    return x, w1, b1, wd, bd
+
+
+def _run_both(ctx, dt, name, seed, N, IH, IW, IC, C, pad, stride, clamp1, clamp2, bias1=None, biasd=None, oracle_images=None):
+    OH, OW = _out_dim(IH, pad[0], pad[1], stride[0]), _out_dim(IW, pad[2], pad[3], stride[1])
+    x, w1, b1, wd, bd = _operands(seed, name, N, IH, IW, IC, C, bias1 or C, biasd or C)
+    tx, tw1, tb1, twd, tbd = (_up(ctx, a, dt) for a in (x, w1, b1, wd, bd))
+    t1 = ctx.empty(dt, (N, IH, IW, C))
+    t2 = ctx.empty(dt, (N, OH, OW, C))
+    tf = ctx.empty(dt, (N, OH, OW, C))
+    e1 = tb.Epilogue(None, clamp1) if clamp1 else None
+    e2 = tb.Epilogue(None, clamp2) if clamp2 else None
+    ctx.conv2d(tx, tw1, tb1, t1, [0, 0, 0, 0], [1, 1], [1, 1], 0, 0, e1)
+    ctx.depthwise_conv2d(t1, twd, tbd, t2, pad, stride, [1, 1], 0, 0, e2)
+    ctx.conv2d_depthwise(tx, tw1, tb1, twd, tbd, tf, pad, stride, e1, e2)
+    assert ctx.last_kernel() == ("expand_dw_f16" if dt == F16 else "expand_dw_bf16"), ctx.last_kernel()
+    assert ctx.sync() == tb.Status.OK
+    st, raw2 = t2.download()
+    st, rawf = tf.download()
+    same = np.array_equal(raw2.view(np.uint16), rawf.view(np.uint16))
+    if not same:
+        bad = np.argwhere(raw2.view(np.uint16) != rawf.view(np.uint16))
+        raise AssertionError("fused and two-kernel results differ at %d places, first %s: %r vs %r" %
+                             (len(bad), bad[0], _down(tf, dt)[tuple(bad[0])], _down(t2, dt)[tuple(bad[0])]))
+    # the oracle on the device's own expanded tensor
+    o1, of = _down(t1, dt), _down(tf, dt)
+    for n in (oracle_images if oracle_images is not None else range(N)):
+        xs = o1[n:n + 1].astype(np.float64)
+        ref = orc.depthwise_conv2d(xs, wd.astype(np.float64), np.broadcast_to(bd, (C,)).astype(np.float64), pad, stride, [1, 1],
+                                   mode="f64", nthreads=orc.num_procs())
+        bnd = orc.depthwise_conv2d(np.abs(xs), np.abs(wd).astype(np.float64), np.abs(np.broadcast_to(bd, (C,))).astype(np.float64),
+                                   pad, stride, [1, 1], mode="f64", nthreads=orc.num_procs())
+        _verify_clamped(of[n:n + 1], ref, bnd, clamp2, 9 + 1, name, "image %d" % n)
+    _free(tx, tw1, tb1, twd, tbd, t1, t2, tf)
+
+
+# (N, IH, IW, IC, C, pad, stride, clamp1, clamp2, bias lengths): strides 1 and 2 in both directions, every padding side,
+# the three channel widths of one swizzled row, one to three channel groups, widths from 3 pixels to a full MMA tile,
+# bands that end on the image border, broadcast biases, no CLAMP
+SMALL_CASES = [
+    (2, 9, 9, 32, 64, [1, 1, 1, 1], [1, 1], (0.0, 6.0), (0.0, 6.0), None, None),
+    (3, 12, 14, 32, 192, [1, 0, 1, 0], [2, 2], (0.0, 6.0), (0.0, 6.0), None, None),
+    (1, 8, 128, 16, 64, [0, 1, 0, 1], [2, 2], (0.0, 6.0), None, 1, None),
+    (2, 7, 33, 64, 128, [1, 1, 1, 1], [2, 1], None, (-1.0, 1.0), None, 1),
+    (1, 3, 3, 32, 64, [0, 0, 0, 0], [1, 1], None, None, 1, 1),
+    (2, 30, 17, 32, 128, [1, 1, 0, 0], [1, 2], (-0.5, 0.5), (0.0, 6.0), None, None),
+    (5, 12, 112, 32, 192, [1, 0, 1, 0], [2, 2], (0.0, 6.0), (0.0, 6.0), None, None),
+    (1, 58, 20, 64, 256, [2, 2, 2, 2], [1, 1], (0.0, 6.0), (0.0, 6.0), None, None),
+]
+
+
+@pytest.mark.parametrize("dt,name", [(F16, "fp16"), (BF16, "bf16")])
+@pytest.mark.parametrize("case", range(len(SMALL_CASES)))
+def test_fused_equals_two_kernels_small(ctx, dt, name, case):
+    N, IH, IW, IC, C, pad, stride, c1, c2, nb1, nbd = SMALL_CASES[case]
+    _run_both(ctx, dt, name, 300 + case, N, IH, IW, IC, C, pad, stride, c1, c2, nb1, nbd)
+
+
+@pytest.mark.parametrize("dt,name", [(F16, "fp16"), (BF16, "bf16")])
+def test_fused_inverted_residual_head_full_size(ctx, dt, name):
+    """64x112x112x32 -> 1x1 CONV2D 32->192 + CLAMP[0,6] -> 3x3 DEPTHWISE s2 pad [1,0,1,0] + CLAMP[0,6]: the fused kernel
+    against the two-kernel chain on all 64 images bit for bit, and against the oracle on three of them."""
+    _run_both(ctx, dt, name, 41, 64, 112, 112, 32, 192, [1, 0, 1, 0], [2, 2], (0.0, 6.0), (0.0, 6.0), oracle_images=(0, 31, 63))
+
+
+def test_shapes_outside_the_fused_form(ctx):
+    """A shape the one-kernel form does not take (24 input channels) runs as the two operators through `expanded`, with
+    the same result as calling them one by one; without `expanded` it is an ERROR, and so is a graph error of either
+    operator (an output height the attributes do not give)."""
+    N, IH, IW, IC, C = 2, 9, 9, 24, 64
+    x, w1, b1, wd, bd = _operands(77, "fp16", N, IH, IW, IC, C, C, C)
+    tx, tw1, tb1, twd, tbd = (_up(ctx, a, F16) for a in (x, w1, b1, wd, bd))
+    t1, t2, tf = ctx.empty(F16, (N, IH, IW, C)), ctx.empty(F16, (N, 9, 9, C)), ctx.empty(F16, (N, 9, 9, C))
+    te = ctx.empty(F16, (N, IH, IW, C))
+    relu6 = tb.Epilogue(None, (0.0, 6.0))
+    ctx.conv2d(tx, tw1, tb1, t1, [0, 0, 0, 0], [1, 1], [1, 1], 0, 0, relu6)
+    ctx.depthwise_conv2d(t1, twd, tbd, t2, [1, 1, 1, 1], [1, 1], [1, 1], 0, 0, relu6)
+    ctx.conv2d_depthwise(tx, tw1, tb1, twd, tbd, tf, [1, 1, 1, 1], [1, 1], relu6, relu6, expanded=te)
+    assert ctx.last_kernel().startswith("depthwise"), ctx.last_kernel()
+    assert np.array_equal(t2.download()[1].view(np.uint16), tf.download()[1].view(np.uint16))
+    assert np.array_equal(t1.download()[1].view(np.uint16), te.download()[1].view(np.uint16))
+    st = ctx.conv2d_depthwise(tx, tw1, tb1, twd, tbd, tf, [1, 1, 1, 1], [1, 1], relu6, relu6, check=False)
+    assert st == tb.Status.ERROR and "one kernel" in ctx.last_error()
+    _free(tx, tw1, tb1)
+    # a fusable shape with an output height the padding and stride do not give
+    x, w1, b1, wd, bd = _operands(78, "fp16", N, IH, IW, 32, C, C, C)
+    tx, tw1, tb1, twd2, tbd2 = (_up(ctx, a, F16) for a in (x, w1, b1, wd, bd))
+    tbad = ctx.empty(F16, (N, 8, 9, C))
+    st = ctx.conv2d_depthwise(tx, tw1, tb1, twd2, tbd2, tbad, [1, 1, 1, 1], [1, 1], relu6, relu6, check=False)
+    assert st == tb.Status.ERROR
+    _free(tx, tw1, tb1, twd, tbd, twd2, tbd2, t1, t2, tf, te, tbad)
