@@ -76,9 +76,16 @@ struct XdType<__half>
     {
         return __half22float2(*reinterpret_cast<const __half2*>(&w));
     }
-    static __device__ __forceinline__ uint32_t down2(float a, float b)
+    static __device__ __forceinline__ uint32_t down2(float2 v)
     {
-        const __half2 h = __halves2half2(__float2half_rn(a), __float2half_rn(b));
+        const __half2 h = __floats2half2_rn(v.x, v.y);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+    // CLAMP of two rounded values; a NaN stays a NaN
+    static __device__ __forceinline__ uint32_t clamp2(uint32_t w, uint32_t lo, uint32_t hi)
+    {
+        const __half2 h = __hmin2_nan(__hmax2_nan(*reinterpret_cast<const __half2*>(&w), *reinterpret_cast<const __half2*>(&lo)),
+                                      *reinterpret_cast<const __half2*>(&hi));
         return *reinterpret_cast<const uint32_t*>(&h);
     }
     static __device__ __forceinline__ float up(const void* p, int i)
@@ -93,9 +100,16 @@ struct XdType<__nv_bfloat16>
     {
         return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
     }
-    static __device__ __forceinline__ uint32_t down2(float a, float b)
+    static __device__ __forceinline__ uint32_t down2(float2 v)
     {
-        const __nv_bfloat162 h = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(b));
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v.x, v.y);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+    static __device__ __forceinline__ uint32_t clamp2(uint32_t w, uint32_t lo, uint32_t hi)
+    {
+        const __nv_bfloat162 h =
+            __hmin2_nan(__hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&w), *reinterpret_cast<const __nv_bfloat162*>(&lo)),
+                        *reinterpret_cast<const __nv_bfloat162*>(&hi));
         return *reinterpret_cast<const uint32_t*>(&h);
     }
     static __device__ __forceinline__ float up(const void* p, int i)
@@ -104,11 +118,13 @@ struct XdType<__nv_bfloat16>
     }
 };
 
-// NaN passes through: both comparisons are false for it (the reference's CLAMP on a NaN gives NaN as well)
-__device__ __forceinline__ float xd_clamp(float v, float lo, float hi)
+// CLAMP runs on the rounded, packed values: rounding is monotonic, so clamping the rounded value to the rounded bounds
+// gives what rounding the clamped fp32 value gives, at one instruction per bound for two values.
+
+__device__ __forceinline__ uint32_t xd_lds32(uint32_t addr)
 {
-    v = (v < lo) ? lo : v;
-    v = (v > hi) ? hi : v;
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
 
@@ -277,12 +293,24 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
         const int half            = warp >> 2;    // which 32 of the group's 64 channels it expands
         const int px              = quarter * 32 + lane;    // its pixel of an input row
         uint8_t* const ring       = smem_al + p.ring_off;
-        const uint32_t lane_chunk = (uint32_t)lane >> 2;          // window pass: 16-byte chunk of the lane's channel pair
-        const uint32_t lane_word  = ((uint32_t)lane & 3u) << 2;   // ... and its byte offset in the chunk
+        const uint32_t ring_s     = smem_base + (uint32_t)p.ring_off;
+        // Window pass: lane l reads the channel pair 2 l, 2 l + 1 = word l & 3 of 16-byte chunk l >> 2 of a pixel, which
+        // sits at chunk position (l >> 2) ^ (pixel & 7).  A warp's pixels advance by 8 * sx per output pixel, so
+        // pixel & 7 depends on the tap column only: one byte offset per tap column for the whole kernel.
+        int koff[3];
+#pragma unroll
+        for (int kx = 0; kx < 3; kx++)
+        {
+            const int ix = warp * p.sx - p.pad_l + kx;    // may be negative: then only later pixels of the warp use it
+            koff[kx]     = ix * kXdPixelBytes + (int)(((((uint32_t)lane >> 2) ^ ((uint32_t)ix & 7u)) << 4) + (((uint32_t)lane & 3u) << 2));
+        }
+        const int jstep = kXdWorkerWarps * p.sx * kXdPixelBytes;    // bytes between a warp's consecutive output pixels
+        const uint32_t lo1 = XdType<T>::down2(make_float2(p.lo1, p.lo1)), hi1 = XdType<T>::down2(make_float2(p.hi1, p.hi1));
+        const uint32_t lo2 = XdType<T>::down2(make_float2(p.lo2, p.lo2)), hi2 = XdType<T>::down2(make_float2(p.hi2, p.hi2));
         bool ok      = true;
         uint32_t k   = 0;    // input rows expanded so far
         int loaded_g = -1;
-        float wgt[9][2], dbias[2];
+        float2 wgt[9], dbias;
         for (int i = 0; i < my_items && ok; i++)
         {
             const XdItem t = xd_decode(p, (int)blockIdx.x + i * (int)gridDim.x);
@@ -291,12 +319,8 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
                 const int c = t.g * kXdGroup + 2 * lane;
 #pragma unroll
                 for (int tap = 0; tap < 9; tap++)
-                {
-                    wgt[tap][0] = XdType<T>::up(p.wd, tap * p.C + c);
-                    wgt[tap][1] = XdType<T>::up(p.wd, tap * p.C + c + 1);
-                }
-                dbias[0] = XdType<T>::up(p.bd, p.bd_n == 1 ? 0 : c);
-                dbias[1] = XdType<T>::up(p.bd, p.bd_n == 1 ? 0 : c + 1);
+                    wgt[tap] = make_float2(XdType<T>::up(p.wd, tap * p.C + c), XdType<T>::up(p.wd, tap * p.C + c + 1));
+                dbias    = make_float2(XdType<T>::up(p.bd, p.bd_n == 1 ? 0 : c), XdType<T>::up(p.bd, p.bd_n == 1 ? 0 : c + 1));
                 loaded_g = t.g;
             }
             const float* const bb = s_bias + t.g * kXdGroup + half * 32;
@@ -329,19 +353,16 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
                         for (int q = 0; q < 4; q++)
                         {
                             const float4 b4 = *reinterpret_cast<const float4*>(bb + hh * 16 + 4 * q);
-                            float f0 = __uint_as_float(v[4 * q + 0]) + b4.x;
-                            float f1 = __uint_as_float(v[4 * q + 1]) + b4.y;
-                            float f2 = __uint_as_float(v[4 * q + 2]) + b4.z;
-                            float f3 = __uint_as_float(v[4 * q + 3]) + b4.w;
+                            // accumulator + bias in fp32, two channels per instruction, then one rounding
+                            w[2 * q] = XdType<T>::down2(__fadd2_rn(make_float2(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1])),
+                                                                   make_float2(b4.x, b4.y)));
+                            w[2 * q + 1] = XdType<T>::down2(__fadd2_rn(make_float2(__uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3])),
+                                                                       make_float2(b4.z, b4.w)));
                             if (p.clamp1)
                             {
-                                f0 = xd_clamp(f0, p.lo1, p.hi1);
-                                f1 = xd_clamp(f1, p.lo1, p.hi1);
-                                f2 = xd_clamp(f2, p.lo1, p.hi1);
-                                f3 = xd_clamp(f3, p.lo1, p.hi1);
+                                w[2 * q]     = XdType<T>::clamp2(w[2 * q], lo1, hi1);
+                                w[2 * q + 1] = XdType<T>::clamp2(w[2 * q + 1], lo1, hi1);
                             }
-                            w[2 * q]     = XdType<T>::down2(f0, f1);
-                            w[2 * q + 1] = XdType<T>::down2(f2, f3);
                         }
                         if (px < p.IW)
                         {
@@ -364,21 +385,23 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
                     break;
                 // ---- the 3x3 window over the ring: warp = output pixel (stride 8), lane = channel pair
                 bool yv[3];
-                uint32_t roff[3];
+                uint32_t rrow[3];    // shared-memory address of each window row in the ring
 #pragma unroll
                 for (int ky = 0; ky < 3; ky++)
                 {
                     const int iy = iy0 + ky;
                     yv[ky]       = iy >= 0 && iy < p.IH;
-                    roff[ky]     = (uint32_t)((yv[ky] ? iy % kXdRing : 0) * p.ring_row_bytes);
+                    rrow[ky]     = ring_s + (uint32_t)((yv[ky] ? iy % kXdRing : 0) * p.ring_row_bytes);
                 }
                 const bool rows_in = yv[0] && yv[1] && yv[2];
-                uint32_t* const orow =
-                    reinterpret_cast<uint32_t*>(reinterpret_cast<T*>(p.out) + ((int64_t)(t.n * p.OH + oy) * p.OW) * p.C + t.g * kXdGroup) + lane;
-                for (int ox = warp; ox < p.OW; ox += kXdWorkerWarps)
+                uint32_t* optr =
+                    reinterpret_cast<uint32_t*>(reinterpret_cast<T*>(p.out) + ((int64_t)(t.n * p.OH + oy) * p.OW + warp) * p.C + t.g * kXdGroup) + lane;
+                const int ostep = kXdWorkerWarps * (p.C / 2);    // 32-bit words between a warp's consecutive output pixels
+                int joff        = 0;
+                for (int ox = warp; ox < p.OW; ox += kXdWorkerWarps, joff += jstep, optr += ostep)
                 {
                     const int ix0 = ox * p.sx - p.pad_l;
-                    float a0 = 0.f, a1 = 0.f;
+                    float2 acc    = make_float2(0.f, 0.f);
                     if (rows_in && ix0 >= 0 && ix0 + 2 < p.IW)
                     {
                         uint32_t win[9];
@@ -386,18 +409,10 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
                         for (int ky = 0; ky < 3; ky++)
 #pragma unroll
                             for (int kx = 0; kx < 3; kx++)
-                            {
-                                const uint32_t ix = (uint32_t)(ix0 + kx);
-                                win[ky * 3 + kx]  = *reinterpret_cast<const uint32_t*>(
-                                    ring + roff[ky] + ix * kXdPixelBytes + ((lane_chunk ^ (ix & 7u)) << 4) + lane_word);
-                            }
+                                win[ky * 3 + kx] = xd_lds32(rrow[ky] + (uint32_t)(koff[kx] + joff));
 #pragma unroll
                         for (int tap = 0; tap < 9; tap++)
-                        {
-                            const float2 f = XdType<T>::up2(win[tap]);
-                            a0 = fmaf(f.x, wgt[tap][0], a0);
-                            a1 = fmaf(f.y, wgt[tap][1], a1);
-                        }
+                            acc = __ffma2_rn(XdType<T>::up2(win[tap]), wgt[tap], acc);
                     }
                     else
                     {
@@ -409,22 +424,13 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
                             {
                                 const int ixs = ix0 + kx;
                                 if (yv[ky] && ixs >= 0 && ixs < p.IW)
-                                {
-                                    const uint32_t ix = (uint32_t)ixs;
-                                    const float2 f    = XdType<T>::up2(*reinterpret_cast<const uint32_t*>(
-                                        ring + roff[ky] + ix * kXdPixelBytes + ((lane_chunk ^ (ix & 7u)) << 4) + lane_word));
-                                    a0 = fmaf(f.x, wgt[ky * 3 + kx][0], a0);
-                                    a1 = fmaf(f.y, wgt[ky * 3 + kx][1], a1);
-                                }
+                                    acc = __ffma2_rn(XdType<T>::up2(xd_lds32(rrow[ky] + (uint32_t)(koff[kx] + joff))), wgt[ky * 3 + kx], acc);
                             }
                     }
-                    float v0 = dbias[0] + a0, v1 = dbias[1] + a1;
+                    uint32_t o = XdType<T>::down2(__fadd2_rn(dbias, acc));
                     if (p.clamp2)
-                    {
-                        v0 = xd_clamp(v0, p.lo2, p.hi2);
-                        v1 = xd_clamp(v1, p.lo2, p.hi2);
-                    }
-                    orow[(int64_t)ox * (p.C / 2)] = XdType<T>::down2(v0, v1);
+                        o = XdType<T>::clamp2(o, lo2, hi2);
+                    *optr = o;
                 }
                 // the next row's expansion overwrites ring rows this pass has read
                 asm volatile("bar.sync 1, %0;" ::"n"(kXdWorkers) : "memory");
@@ -620,25 +626,29 @@ tb200_status expand_dw_launch(tb200_ctx* ctx, const ExpandDwProblem& q)
     k.wait_limit     = ctx->wait_limit_cycles;
     k.status         = ctx->d_status;
 
-    // Band height: a band of R output rows expands R * sy + 2 input rows (two of them again in the next band); few rows
-    // per band waste expansions, many leave the last round of CTAs part empty.  Costs in instructions per thread: about
-    // four per expanded value, twenty-four per output value.
-    const int slots   = ctx->num_sms * resident;
-    double best_cost  = 0;
-    int best_rows     = 1;
-    for (int rows = 1; rows <= q.OH; rows++)
-    {
-        const int bands      = (q.OH + rows - 1) / rows;
-        const int64_t items  = (int64_t)q.N * bands * k.groups;
-        const int64_t rounds = (items + slots - 1) / slots;
-        const double item    = 4.0 * (rows * q.sy + 2) * q.IW + 24.0 * rows * q.OW;
-        const double cost    = (double)rounds * item;
-        if (rows == 1 || cost <= best_cost)
+    // Band height: a band of R output rows expands R * sy + 2 input rows (two of them again in the next band).  Few rows per
+    // band waste expansions; many leave SMs with unequal shares (the CTAs resident on one SM share its issue slots, so
+    // what counts is the number of items the fullest SM gets) or fewer CTAs than the SMs can hold.  Costs in instructions
+    // per thread: about three per expanded value, twenty-two per output value.
+    const int slots  = ctx->num_sms * resident;
+    double best_cost = 0;
+    int best_rows    = 0;
+    for (int pass = 0; pass < 2 && best_rows == 0; pass++)    // first only band heights that fill every resident slot
+        for (int rows = 1; rows <= q.OH; rows++)
         {
-            best_cost = cost;
-            best_rows = rows;
+            const int bands     = (q.OH + rows - 1) / rows;
+            const int64_t items = (int64_t)q.N * bands * k.groups;
+            if (pass == 0 && items < slots)
+                continue;
+            const int64_t per_sm = (items + ctx->num_sms - 1) / ctx->num_sms;
+            const double item    = 3.0 * (rows * q.sy + 2) * q.IW + 22.0 * rows * q.OW;
+            const double cost    = (double)per_sm * item;
+            if (best_rows == 0 || cost <= best_cost)
+            {
+                best_cost = cost;
+                best_rows = rows;
+            }
         }
-    }
     k.band_rows = best_rows;
     k.bands     = (q.OH + best_rows - 1) / best_rows;
     const int64_t items = (int64_t)q.N * k.bands * k.groups;
