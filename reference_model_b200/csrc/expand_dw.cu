@@ -576,11 +576,19 @@ tb200_status expand_dw_launch(tb200_ctx* ctx, const ExpandDwProblem& q)
     tb200_status st = raise_smem_limit(ctx, attr_bit, kernel, lay.smem_bytes);
     if (st != TB200_OK)
         return st;
-    int resident = 0;
-    TB200_CUDA_CHECK(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, kXdThreads, lay.smem_bytes));
+    // CTAs one SM holds: registers, shared memory (each block also pays the driver's reserve), threads, tensor memory
+    // (512 columns per SM).  Only the grid size and the band height depend on it: a wrong figure costs time, not results.
+    cudaFuncAttributes fa;
+    TB200_CUDA_CHECK(ctx, cudaFuncGetAttributes(&fa, kernel));
+    int sm_regs = 0, sm_smem = 0, blk_reserve = 0;
+    TB200_CUDA_CHECK(ctx, cudaDeviceGetAttribute(&sm_regs, cudaDevAttrMaxRegistersPerMultiprocessor, ctx->device));
+    TB200_CUDA_CHECK(ctx, cudaDeviceGetAttribute(&sm_smem, cudaDevAttrMaxSharedMemoryPerMultiprocessor, ctx->device));
+    TB200_CUDA_CHECK(ctx, cudaDeviceGetAttribute(&blk_reserve, cudaDevAttrReservedSharedMemoryPerBlock, ctx->device));
+    const int regs_per_cta = ((fa.numRegs * 32 + 511) / 512 * 512) * (kXdThreads / 32);
+    int resident = std::min(sm_regs / std::max(1, regs_per_cta), sm_smem / (lay.smem_bytes + (int)fa.sharedSizeBytes + blk_reserve));
+    resident     = std::min(resident, std::min(2048 / kXdThreads, 512 / (kXdAccBufs * kXdGroup)));
     if (resident < 1)
         return fail(ctx, TB200_INTERNAL, "fused CONV2D + DEPTHWISE_CONV2D kernel does not fit on an SM");
-    resident = std::min(resident, 512 / (kXdAccBufs * kXdGroup));    // tensor memory: 512 columns per SM
 
     XdParams k;
     memset(&k, 0, sizeof(k));
