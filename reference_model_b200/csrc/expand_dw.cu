@@ -36,7 +36,6 @@ constexpr int kXdGroup       = 64;    // expanded channels per work item = colum
 constexpr int kXdAccBufs     = 2;
 constexpr int kXdMaxStages   = 4;
 constexpr int kXdRing        = 3;     // expanded rows kept: a 3-row window moving down by one or two rows
-constexpr int kXdPixelBytes  = kXdGroup * 2;    // one pixel of a ring row: 64 channels of 2 bytes
 // CTAs the compiler leaves register room for on one SM: three CTAs cover each other's expansion, window pass and waits
 // for memory (64 registers per thread)
 #ifndef TB200_XD_MIN_CTAS
@@ -59,7 +58,7 @@ struct XdParams
     int groups, bands, band_rows, items;
     int stages, a_stage_bytes, a_tx_bytes, b_group_bytes;
     int b_off, a_off, ring_off, bias_off;    // from the 1024-byte aligned start of dynamic shared memory
-    int ring_row_bytes;
+    int ring_row_bytes, plane_bytes;    // a ring row is eight planes (8 channels each) of plane_bytes
     int mmas;    // MMAs (16 channels of K each) per input row
     uint32_t idesc;
     uint64_t desc_hi;
@@ -92,6 +91,20 @@ struct XdType<__half>
     {
         return __half2float(reinterpret_cast<const __half*>(p)[i]);
     }
+    // acc.x = fma(low(a), low(b), acc.x), acc.y = fma(high(a), high(b), acc.y): the 16-bit operands widened exactly, the
+    // product exact, one rounding to fp32 (what fmaf on the converted values gives), without a conversion instruction
+    static __device__ __forceinline__ void fma2(float2& acc, uint32_t a, uint32_t b)
+    {
+        asm("{\n"
+            ".reg .b16 al, ah, bl, bh;\n"
+            "mov.b32 {al, ah}, %2;\n"
+            "mov.b32 {bl, bh}, %3;\n"
+            "fma.rn.f32.f16 %0, al, bl, %0;\n"
+            "fma.rn.f32.f16 %1, ah, bh, %1;\n"
+            "}\n"
+            : "+f"(acc.x), "+f"(acc.y)
+            : "r"(a), "r"(b));
+    }
 };
 template <>
 struct XdType<__nv_bfloat16>
@@ -116,15 +129,28 @@ struct XdType<__nv_bfloat16>
     {
         return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
     }
+    static __device__ __forceinline__ void fma2(float2& acc, uint32_t a, uint32_t b)
+    {
+        asm("{\n"
+            ".reg .b16 al, ah, bl, bh;\n"
+            "mov.b32 {al, ah}, %2;\n"
+            "mov.b32 {bl, bh}, %3;\n"
+            "fma.rn.f32.bf16 %0, al, bl, %0;\n"
+            "fma.rn.f32.bf16 %1, ah, bh, %1;\n"
+            "}\n"
+            : "+f"(acc.x), "+f"(acc.y)
+            : "r"(a), "r"(b));
+    }
 };
 
 // CLAMP runs on the rounded, packed values: rounding is monotonic, so clamping the rounded value to the rounded bounds
 // gives what rounding the clamped fp32 value gives, at one instruction per bound for two values.
 
+template <int OFF>
 __device__ __forceinline__ uint32_t xd_lds32(uint32_t addr)
 {
     uint32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    asm volatile("ld.shared.b32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
     return v;
 }
 
@@ -294,23 +320,28 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
         const int px              = quarter * 32 + lane;    // its pixel of an input row
         uint8_t* const ring       = smem_al + p.ring_off;
         const uint32_t ring_s     = smem_base + (uint32_t)p.ring_off;
-        // Window pass: lane l reads the channel pair 2 l, 2 l + 1 = word l & 3 of 16-byte chunk l >> 2 of a pixel, which
-        // sits at chunk position (l >> 2) ^ (pixel & 7).  A warp's pixels advance by 8 * sx per output pixel, so
-        // pixel & 7 depends on the tap column only: one byte offset per tap column for the whole kernel.
-        int koff[3];
-#pragma unroll
-        for (int kx = 0; kx < 3; kx++)
-        {
-            const int ix = warp * p.sx - p.pad_l + kx;    // may be negative: then only later pixels of the warp use it
-            koff[kx]     = ix * kXdPixelBytes + (int)(((((uint32_t)lane >> 2) ^ ((uint32_t)ix & 7u)) << 4) + (((uint32_t)lane & 3u) << 2));
-        }
-        const int jstep = kXdWorkerWarps * p.sx * kXdPixelBytes;    // bytes between a warp's consecutive output pixels
+        // A ring row is eight planes of 8 channels: plane j holds, pixel after pixel, the 16 bytes of channels 8 j .. 8 j + 7.
+        // Expanding, a warp's lanes are neighbouring pixels and write neighbouring 16-byte slots of a plane.  In the window
+        // pass lane l reads the channel pair 2 l, 2 l + 1 = word l & 3 of plane l >> 2; the plane stride is 16 bytes more
+        // than a multiple of 128, so the 32 lanes hit 32 different banks, and the three taps of a window row are 16 bytes
+        // apart: immediate offsets of one address.
+        const uint32_t lane_off = ((uint32_t)lane >> 2) * (uint32_t)p.plane_bytes + (((uint32_t)lane & 3u) << 2);
+        const int base_ix       = warp * p.sx - p.pad_l;               // first tap column of the warp's first output pixel
+        const int jstep         = kXdWorkerWarps * p.sx * 16;          // bytes between a warp's consecutive output pixels
+        const int nj            = warp < p.OW ? (p.OW - warp + kXdWorkerWarps - 1) / kXdWorkerWarps : 0;    // its output pixels per row
+        // its pixels whose three tap columns all lie inside the image: [jf0, jf1)
+        const int xstep = kXdWorkerWarps * p.sx;
+        int jf0         = base_ix >= 0 ? 0 : (-base_ix + xstep - 1) / xstep;
+        int jf1         = p.IW - 3 - base_ix >= 0 ? (p.IW - 3 - base_ix) / xstep + 1 : 0;
+        jf0             = min(jf0, nj);
+        jf1             = max(jf0, min(jf1, nj));
         const uint32_t lo1 = XdType<T>::down2(make_float2(p.lo1, p.lo1)), hi1 = XdType<T>::down2(make_float2(p.hi1, p.hi1));
         const uint32_t lo2 = XdType<T>::down2(make_float2(p.lo2, p.lo2)), hi2 = XdType<T>::down2(make_float2(p.hi2, p.hi2));
         bool ok      = true;
         uint32_t k   = 0;    // input rows expanded so far
         int loaded_g = -1;
-        float2 wgt[9], dbias;
+        uint32_t wgt[9];    // the lane's two channels of every tap, as stored
+        float2 dbias;
         for (int i = 0; i < my_items && ok; i++)
         {
             const XdItem t = xd_decode(p, (int)blockIdx.x + i * (int)gridDim.x);
@@ -319,7 +350,7 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
                 const int c = t.g * kXdGroup + 2 * lane;
 #pragma unroll
                 for (int tap = 0; tap < 9; tap++)
-                    wgt[tap] = make_float2(XdType<T>::up(p.wd, tap * p.C + c), XdType<T>::up(p.wd, tap * p.C + c + 1));
+                    wgt[tap] = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const T*>(p.wd) + tap * p.C + c);
                 dbias    = make_float2(XdType<T>::up(p.bd, p.bd_n == 1 ? 0 : c), XdType<T>::up(p.bd, p.bd_n == 1 ? 0 : c + 1));
                 loaded_g = t.g;
             }
@@ -341,7 +372,7 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
                         continue;
                     ptx::tc_fence_after_sync();
                     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)kXdGroup + (uint32_t)(half * 32);
-                    uint8_t* const dst   = ring + (next_row % kXdRing) * p.ring_row_bytes + px * kXdPixelBytes;
+                    uint8_t* const dst   = ring + (next_row % kXdRing) * p.ring_row_bytes + px * 16 + (half * 4) * p.plane_bytes;
 #pragma unroll
                     for (int hh = 0; hh < 2; hh++)
                     {
@@ -366,12 +397,8 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
                         }
                         if (px < p.IW)
                         {
-                            // 16-byte chunk j of a pixel sits at chunk position j ^ (pixel & 7): eight neighbouring lanes
-                            // write eight different bank groups
-                            const uint32_t j0 = (uint32_t)(half * 4 + hh * 2);
-                            const uint32_t sw = (uint32_t)px & 7u;
-                            *reinterpret_cast<uint4*>(dst + ((j0 ^ sw) << 4))        = make_uint4(w[0], w[1], w[2], w[3]);
-                            *reinterpret_cast<uint4*>(dst + (((j0 + 1u) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+                            *reinterpret_cast<uint4*>(dst + (hh * 2) * p.plane_bytes)     = make_uint4(w[0], w[1], w[2], w[3]);
+                            *reinterpret_cast<uint4*>(dst + (hh * 2 + 1) * p.plane_bytes) = make_uint4(w[4], w[5], w[6], w[7]);
                         }
                     }
                     ptx::tc_fence_before_sync();
@@ -385,53 +412,65 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
                     break;
                 // ---- the 3x3 window over the ring: warp = output pixel (stride 8), lane = channel pair
                 bool yv[3];
-                uint32_t rrow[3];    // shared-memory address of each window row in the ring
+                uint32_t rrow[3];    // shared-memory address of the lane's word of the warp's first tap column, per window row
 #pragma unroll
                 for (int ky = 0; ky < 3; ky++)
                 {
                     const int iy = iy0 + ky;
                     yv[ky]       = iy >= 0 && iy < p.IH;
-                    rrow[ky]     = ring_s + (uint32_t)((yv[ky] ? iy % kXdRing : 0) * p.ring_row_bytes);
+                    rrow[ky]     = ring_s + (uint32_t)((yv[ky] ? iy % kXdRing : 0) * p.ring_row_bytes) + lane_off + (uint32_t)(base_ix * 16);
                 }
                 const bool rows_in = yv[0] && yv[1] && yv[2];
-                uint32_t* optr =
+                uint32_t* const orow =
                     reinterpret_cast<uint32_t*>(reinterpret_cast<T*>(p.out) + ((int64_t)(t.n * p.OH + oy) * p.OW + warp) * p.C + t.g * kXdGroup) + lane;
                 const int ostep = kXdWorkerWarps * (p.C / 2);    // 32-bit words between a warp's consecutive output pixels
-                int joff        = 0;
-                for (int ox = warp; ox < p.OW; ox += kXdWorkerWarps, joff += jstep, optr += ostep)
-                {
-                    const int ix0 = ox * p.sx - p.pad_l;
-                    float2 acc    = make_float2(0.f, 0.f);
-                    if (rows_in && ix0 >= 0 && ix0 + 2 < p.IW)
-                    {
-                        uint32_t win[9];
-#pragma unroll
-                        for (int ky = 0; ky < 3; ky++)
-#pragma unroll
-                            for (int kx = 0; kx < 3; kx++)
-                                win[ky * 3 + kx] = xd_lds32(rrow[ky] + (uint32_t)(koff[kx] + joff));
-#pragma unroll
-                        for (int tap = 0; tap < 9; tap++)
-                            acc = __ffma2_rn(XdType<T>::up2(win[tap]), wgt[tap], acc);
-                    }
-                    else
-                    {
-                        // taps outside the image are skipped, as the reference skips them
-#pragma unroll
-                        for (int ky = 0; ky < 3; ky++)
-#pragma unroll
-                            for (int kx = 0; kx < 3; kx++)
-                            {
-                                const int ixs = ix0 + kx;
-                                if (yv[ky] && ixs >= 0 && ixs < p.IW)
-                                    acc = __ffma2_rn(XdType<T>::up2(xd_lds32(rrow[ky] + (uint32_t)(koff[kx] + joff))), wgt[ky * 3 + kx], acc);
-                            }
-                    }
+                auto finish = [&](int j, float2 acc) {
                     uint32_t o = XdType<T>::down2(__fadd2_rn(dbias, acc));
                     if (p.clamp2)
                         o = XdType<T>::clamp2(o, lo2, hi2);
-                    *optr = o;
+                    orow[(int64_t)j * ostep] = o;
+                };
+                // taps outside the image are skipped, as the reference skips them
+                auto edge = [&](int j) {
+                    const int ix0      = base_ix + j * xstep;
+                    const uint32_t off = (uint32_t)(j * jstep);
+                    float2 acc         = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int ky = 0; ky < 3; ky++)
+                    {
+                        if (!yv[ky])
+                            continue;
+                        if (ix0 >= 0 && ix0 < p.IW)
+                            XdType<T>::fma2(acc, xd_lds32<0>(rrow[ky] + off), wgt[ky * 3 + 0]);
+                        if (ix0 + 1 >= 0 && ix0 + 1 < p.IW)
+                            XdType<T>::fma2(acc, xd_lds32<16>(rrow[ky] + off), wgt[ky * 3 + 1]);
+                        if (ix0 + 2 >= 0 && ix0 + 2 < p.IW)
+                            XdType<T>::fma2(acc, xd_lds32<32>(rrow[ky] + off), wgt[ky * 3 + 2]);
+                    }
+                    finish(j, acc);
+                };
+                const int f0 = rows_in ? jf0 : nj, f1 = rows_in ? jf1 : nj;
+                for (int j = 0; j < f0; j++)
+                    edge(j);
+                for (int j = f0; j < f1; j++)
+                {
+                    const uint32_t off = (uint32_t)(j * jstep);
+                    uint32_t win[9];
+#pragma unroll
+                    for (int ky = 0; ky < 3; ky++)
+                    {
+                        win[ky * 3 + 0] = xd_lds32<0>(rrow[ky] + off);
+                        win[ky * 3 + 1] = xd_lds32<16>(rrow[ky] + off);
+                        win[ky * 3 + 2] = xd_lds32<32>(rrow[ky] + off);
+                    }
+                    float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int tap = 0; tap < 9; tap++)
+                        XdType<T>::fma2(acc, win[tap], wgt[tap]);
+                    finish(j, acc);
                 }
+                for (int j = f1; j < nj; j++)
+                    edge(j);
                 // the next row's expansion overwrites ring rows this pass has read
                 asm volatile("bar.sync 1, %0;" ::"n"(kXdWorkers) : "memory");
             }
@@ -490,7 +529,7 @@ PFN_xdEncodeTiled xd_encode_fn()
 
 struct XdLayout
 {
-    int stages, smem_bytes, b_off, a_off, ring_off, bias_off, a_stage_bytes, b_group_bytes, ring_row_bytes;
+    int stages, smem_bytes, b_off, a_off, ring_off, bias_off, a_stage_bytes, b_group_bytes, ring_row_bytes, plane_bytes;
 };
 
 // Shared memory of one CTA with `stages` input-row stages: weights of all groups, the stages, the ring, the fp32 bias.
@@ -501,7 +540,8 @@ XdLayout xd_layout(const ExpandDwProblem& q, int stages)
     l.stages            = stages;
     l.b_group_bytes     = std::max(1024, kXdGroup * row_bytes);
     l.a_stage_bytes     = 128 * row_bytes;    // the MMA reads 128 rows whatever the image width
-    l.ring_row_bytes    = q.IW * kXdPixelBytes;
+    l.plane_bytes       = ((q.IW * 16 + 127) & ~127) + 16;    // 16 bytes past a multiple of 128: see the window pass
+    l.ring_row_bytes    = (kXdGroup / 8) * l.plane_bytes;
     l.b_off             = 0;
     l.a_off             = l.b_off + (q.C / kXdGroup) * l.b_group_bytes;
     l.ring_off          = l.a_off + stages * l.a_stage_bytes;
@@ -628,6 +668,7 @@ tb200_status expand_dw_launch(tb200_ctx* ctx, const ExpandDwProblem& q)
     k.a_tx_bytes     = a_box_rows * row_bytes;
     k.b_off = lay.b_off; k.a_off = lay.a_off; k.ring_off = lay.ring_off; k.bias_off = lay.bias_off;
     k.ring_row_bytes = lay.ring_row_bytes;
+    k.plane_bytes    = lay.plane_bytes;
     k.mmas           = q.IC / 16;
     k.idesc          = ptx::make_idesc(1u, bf16 ? 1u : 0u, bf16 ? 1u : 0u, 0u, 0u, 128u, (uint32_t)kXdGroup);
     k.desc_hi        = ptx::make_smem_desc_hi(16, 8 * row_bytes, row_bytes == 32 ? 6u : row_bytes == 64 ? 4u : 2u);
