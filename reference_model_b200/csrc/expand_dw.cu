@@ -14,6 +14,18 @@
 // channel pair 2 l, 2 l + 1), warp 8 lane 0 TMA producer, warp 9 lane 0 MMA issuer (warp 9 owns tensor memory).
 // Every wait is bounded (p.wait_limit SM cycles); a wait that gives up sets TB200_DEV_TIMEOUT, the roles leave their
 // loops together, copies and MMAs in flight are waited for and tensor memory is freed.
+//
+// What measurement said about this kernel (64 x 112 x 112 x 32 -> 192 channels, stride 2):
+//   * the worker warps' instruction issue is the bound, not memory (the tensors that reach device memory are 128 MB, 20 us
+//     at the copy rate; the tensor pipe is 2 % busy): every instruction per expanded or output value counts.  CLAMP runs on
+//     the rounded, packed pairs (two instructions per pair); bias and accumulator are added two channels per instruction;
+//     the window pass multiplies the 16-bit values directly (fma.rn.f32.f16 / .bf16: exact product, one fp32 rounding, the
+//     result fmaf gives on the converted values) instead of converting them first;
+//   * a ring row is stored as eight channel planes, so that the three taps of a window row are immediate offsets of one
+//     address and neither side needs swizzle arithmetic (see the worker code);
+//   * one tcgen05.commit per input row kept the tensor pipe idle most of the time (the MMAs of a row take about 200 cycles,
+//     a commit several hundred): two rows share a commit, which both publishes their accumulators and frees their stages;
+//   * more input-row stages, three CTAs per SM instead of two, or two output pixels per thread at once changed nothing.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -33,14 +45,20 @@ constexpr int kXdWorkerWarps = 8;
 constexpr int kXdWorkers     = 32 * kXdWorkerWarps;
 constexpr int kXdThreads     = kXdWorkers + 64;
 constexpr int kXdGroup       = 64;    // expanded channels per work item = columns of one accumulator buffer
-constexpr int kXdAccBufs     = 2;
-constexpr int kXdMaxStages   = 4;
+constexpr int kXdBatchRows   = 2;     // input rows whose MMAs share one tcgen05.commit (a commit idles the tensor pipe for hundreds of cycles)
+constexpr int kXdAccBufs     = 2;     // accumulator buffers, each of kXdBatchRows rows x kXdGroup columns
+constexpr int kXdStages      = kXdAccBufs * kXdBatchRows;    // input-row stages: one per accumulator row
+constexpr int kXdTmemCols    = kXdAccBufs * kXdBatchRows * kXdGroup;
 constexpr int kXdRing        = 3;     // expanded rows kept: a 3-row window moving down by one or two rows
-// CTAs the compiler leaves register room for on one SM: three CTAs cover each other's expansion, window pass and waits
-// for memory (64 registers per thread)
+// CTAs the compiler leaves register room for on one SM (two CTAs of 256 tensor-memory columns fill an SM's 512)
 #ifndef TB200_XD_MIN_CTAS
-#define TB200_XD_MIN_CTAS 3
+#define TB200_XD_MIN_CTAS 2
 #endif
+// output pixels of the window pass a thread works on at once (independent accumulation chains)
+#ifndef TB200_XD_UNROLL
+#define TB200_XD_UNROLL 1
+#endif
+constexpr int kXdUnroll = TB200_XD_UNROLL;
 
 struct XdParams
 {
@@ -56,7 +74,7 @@ struct XdParams
     int clamp1, clamp2;
     float lo1, hi1, lo2, hi2;
     int groups, bands, band_rows, items;
-    int stages, a_stage_bytes, a_tx_bytes, b_group_bytes;
+    int a_stage_bytes, a_tx_bytes, b_group_bytes;
     int b_off, a_off, ring_off, bias_off;    // from the 1024-byte aligned start of dynamic shared memory
     int ring_row_bytes, plane_bytes;    // a ring row is eight planes (8 channels each) of plane_bytes
     int mmas;    // MMAs (16 channels of K each) per input row
@@ -179,9 +197,9 @@ template <typename T>
 __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kernel(const __grid_constant__ XdParams p)
 {
     extern __shared__ uint8_t xd_smem_raw[];
-    __shared__ __align__(8) uint64_t bar_a_full[kXdMaxStages];     // TMA -> MMA: the input row has landed
-    __shared__ __align__(8) uint64_t bar_a_empty[kXdMaxStages];    // MMA -> TMA: the row's MMAs have read it
-    __shared__ __align__(8) uint64_t bar_acc_full[kXdAccBufs];     // MMA -> workers: the expanded row is in tensor memory
+    __shared__ __align__(8) uint64_t bar_a_full[kXdStages];        // TMA -> MMA: the input row has landed
+    __shared__ __align__(8) uint64_t bar_acc_full[kXdAccBufs];     // MMA -> workers: a batch of expanded rows is in tensor memory
+                                                                   // (and -> TMA: the batch's input-row stages are free)
     __shared__ __align__(8) uint64_t bar_acc_empty[kXdAccBufs];    // workers -> MMA: accumulator buffer drained
     __shared__ __align__(8) uint64_t bar_b;                        // the CONV2D weights have landed
     __shared__ __align__(8) uint64_t bar_drain;                    // teardown after a wait gave up
@@ -198,11 +216,8 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
 
     if (threadIdx.x == 0)
     {
-        for (int s = 0; s < p.stages; s++)
-        {
+        for (int s = 0; s < kXdStages; s++)
             ptx::mbar_init(ptx::smem_u32(&bar_a_full[s]), 1);
-            ptx::mbar_init(ptx::smem_u32(&bar_a_empty[s]), 1);
-        }
         for (int a = 0; a < kXdAccBufs; a++)
         {
             ptx::mbar_init(ptx::smem_u32(&bar_acc_full[a]), 1);
@@ -217,7 +232,7 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
     }
     if (warp == kXdWorkerWarps + 1)
     {
-        ptx::tmem_alloc(ptx::smem_u32(&tmem_base_holder), (uint32_t)(kXdAccBufs * kXdGroup));
+        ptx::tmem_alloc(ptx::smem_u32(&tmem_base_holder), (uint32_t)kXdTmemCols);
         ptx::tmem_relinquish();
     }
     // the CONV2D bias of every channel as fp32 (added to the fp32 accumulator, as the reference adds it before rounding)
@@ -238,27 +253,33 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
             ptx::mbar_arrive_expect_tx(ptx::smem_u32(&bar_b), (uint32_t)(p.groups * p.b_group_bytes));
             for (int g = 0; g < p.groups; g++)
                 ptx::tma_load_2d(s_b + (uint32_t)(g * p.b_group_bytes), &p.tmB, ptx::smem_u32(&bar_b), 0, g * kXdGroup);
-            bool ok        = true;
-            int stage      = 0;
-            uint32_t phase = 0;
+            bool ok     = true;
+            uint32_t bi = 0;    // batches issued so far: batch bi uses accumulator buffer bi & 1 and that buffer's row stages
             for (int i = 0; i < my_items && ok; i++)
             {
                 const XdItem t = xd_decode(p, (int)blockIdx.x + i * (int)gridDim.x);
-                for (int r = t.r_lo; r <= t.r_hi; r++)
+                for (int r = t.r_lo; r <= t.r_hi; r += kXdBatchRows, bi++)
                 {
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_a_empty[stage]), phase ^ 1u, p.wait_limit))
+                    // the stages are free once the MMAs of the batch that used them last (bi - 2) have completed: the commit
+                    // that published that batch's accumulators says so
+                    const uint32_t buf = bi & 1u;
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_full[buf]), ((bi >> 1) & 1u) ^ 1u, p.wait_limit))
                     {
                         ok = false;
                         break;
                     }
-                    const uint32_t full = ptx::smem_u32(&bar_a_full[stage]);
-                    ptx::mbar_arrive_expect_tx(full, (uint32_t)p.a_tx_bytes);
-                    ptx::tma_load_2d(s_a + (uint32_t)(stage * p.a_stage_bytes), &p.tmA, full, 0, (t.n * p.IH + r) * p.IW);
-                    if (++stage == p.stages)
+                    const int nb = min(kXdBatchRows, t.r_hi - r + 1);
+                    for (int rr = 0; rr < nb; rr++)
                     {
-                        stage = 0;
-                        phase ^= 1u;
+                        const uint32_t stage = buf * kXdBatchRows + rr;
+                        const uint32_t full  = ptx::smem_u32(&bar_a_full[stage]);
+                        ptx::mbar_arrive_expect_tx(full, (uint32_t)p.a_tx_bytes);
+                        ptx::tma_load_2d(s_a + stage * (uint32_t)p.a_stage_bytes, &p.tmA, full, 0, (t.n * p.IH + r + rr) * p.IW);
                     }
+                    // a short last batch of an item: complete the unused stages' phase too, so that every stage barrier
+                    // advances once per batch of its buffer and one parity serves them all
+                    for (int rr = nb; rr < kXdBatchRows; rr++)
+                        ptx::mbar_arrive(ptx::smem_u32(&bar_a_full[buf * kXdBatchRows + rr]));
                 }
             }
             if (!ok)
@@ -275,34 +296,41 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
         {
             bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_b), 0u, p.wait_limit);
             ptx::tc_fence_after_sync();
-            int stage      = 0;
-            uint32_t phase = 0;
-            uint32_t k     = 0;    // input rows issued so far
+            uint32_t bi = 0;    // batches issued so far
             for (int i = 0; i < my_items && ok; i++)
             {
                 const XdItem t    = xd_decode(p, (int)blockIdx.x + i * (int)gridDim.x);
                 const uint64_t bd = ptx::smem_desc(p.desc_hi, s_b + (uint32_t)(t.g * p.b_group_bytes));
-                for (int r = t.r_lo; r <= t.r_hi; r++, k++)
+                for (int r = t.r_lo; r <= t.r_hi && ok; r += kXdBatchRows, bi++)
                 {
-                    const uint32_t buf = k & 1u;
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_empty[buf]), ((k >> 1) & 1u) ^ 1u, p.wait_limit) ||
-                        !ptx::mbar_wait_bounded(ptx::smem_u32(&bar_a_full[stage]), phase, p.wait_limit))
+                    const uint32_t buf    = bi & 1u;
+                    const uint32_t parity = (bi >> 1) & 1u;
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_empty[buf]), parity ^ 1u, p.wait_limit))
                     {
                         ok = false;
                         break;
                     }
-                    ptx::tc_fence_after_sync();
-                    const uint64_t ad     = ptx::smem_desc(p.desc_hi, s_a + (uint32_t)(stage * p.a_stage_bytes));
-                    const uint32_t d_tmem = tmem_base + buf * (uint32_t)kXdGroup;
-                    for (int m = 0; m < p.mmas; m++)    // 16 channels (32 bytes) of K per MMA
-                        ptx::mma_f16_ss(d_tmem, ad + (uint64_t)(2 * m), bd + (uint64_t)(2 * m), p.idesc, m > 0 ? 1u : 0u);
-                    ptx::mma_commit(ptx::smem_u32(&bar_a_empty[stage]));
-                    ptx::mma_commit(ptx::smem_u32(&bar_acc_full[buf]));
-                    if (++stage == p.stages)
+                    const int nb = min(kXdBatchRows, t.r_hi - r + 1);
+                    for (int rr = 0; rr < kXdBatchRows; rr++)
                     {
-                        stage = 0;
-                        phase ^= 1u;
+                        const uint32_t stage = buf * kXdBatchRows + rr;
+                        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bar_a_full[stage]), parity, p.wait_limit))
+                        {
+                            ok = false;
+                            break;
+                        }
+                        if (rr >= nb)
+                            continue;    // unused stage of a short batch: only its phase is consumed
+                        ptx::tc_fence_after_sync();
+                        const uint64_t ad     = ptx::smem_desc(p.desc_hi, s_a + stage * (uint32_t)p.a_stage_bytes);
+                        const uint32_t d_tmem = tmem_base + stage * (uint32_t)kXdGroup;
+                        for (int m = 0; m < p.mmas; m++)    // 16 channels (32 bytes) of K per MMA
+                            ptx::mma_f16_ss(d_tmem, ad + (uint64_t)(2 * m), bd + (uint64_t)(2 * m), p.idesc, m > 0 ? 1u : 0u);
                     }
+                    // one commit per batch: it publishes the rows and frees their stages (MMAs issued before a wait that
+                    // gave up are covered by the teardown's commit)
+                    if (ok)
+                        ptx::mma_commit(ptx::smem_u32(&bar_acc_full[buf]));
                 }
             }
             if (!ok)
@@ -338,7 +366,7 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
         const uint32_t lo1 = XdType<T>::down2(make_float2(p.lo1, p.lo1)), hi1 = XdType<T>::down2(make_float2(p.hi1, p.hi1));
         const uint32_t lo2 = XdType<T>::down2(make_float2(p.lo2, p.lo2)), hi2 = XdType<T>::down2(make_float2(p.hi2, p.hi2));
         bool ok      = true;
-        uint32_t k   = 0;    // input rows expanded so far
+        uint32_t bi  = 0;    // batches drained so far
         int loaded_g = -1;
         uint32_t wgt[9];    // the lane's two channels of every tap, as stored
         float2 dbias;
@@ -356,22 +384,36 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
             }
             const float* const bb = s_bias + t.g * kXdGroup + half * 32;
             int next_row          = t.r_lo;
+            int in_batch          = 0;    // rows of the current batch already drained
             for (int oy = t.oy0; oy < t.oy1; oy++)
             {
                 const int iy0  = oy * p.sy - p.pad_t;
                 const int last = min(p.IH - 1, iy0 + 2);
                 // ---- expand the input rows this output row needs and the ring does not hold yet
-                for (; next_row <= last; next_row++, k++)
+                for (; next_row <= last; next_row++)
                 {
+                    const uint32_t buf  = bi & 1u;
+                    const int batch_len = min(kXdBatchRows, t.r_hi - (next_row - in_batch) + 1);    // rows of the current batch
+                    const int row_slot  = (int)buf * kXdBatchRows + in_batch;                        // its accumulator row
+                    const bool first    = in_batch == 0;
+                    const bool lastrow  = ++in_batch == batch_len;
+                    const uint32_t par  = (bi >> 1) & 1u;
+                    if (lastrow)
+                    {
+                        in_batch = 0;
+                        bi++;
+                    }
                     if (!ok)
                         continue;    // after a wait gave up: only keep the counters in step with the other warps
-                    const uint32_t buf = k & 1u;
-                    ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_full[buf]), (k >> 1) & 1u, p.wait_limit);
-                    ok = __all_sync(0xffffffffu, ok);    // the whole warp agrees before the warp-collective loads
-                    if (!ok)
-                        continue;
+                    if (first)
+                    {
+                        ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar_acc_full[buf]), par, p.wait_limit);
+                        ok = __all_sync(0xffffffffu, ok);    // the whole warp agrees before the warp-collective loads
+                        if (!ok)
+                            continue;
+                    }
                     ptx::tc_fence_after_sync();
-                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)kXdGroup + (uint32_t)(half * 32);
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(row_slot * kXdGroup + half * 32);
                     uint8_t* const dst   = ring + (next_row % kXdRing) * p.ring_row_bytes + px * 16 + (half * 4) * p.plane_bytes;
 #pragma unroll
                     for (int hh = 0; hh < 2; hh++)
@@ -401,10 +443,14 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
                             *reinterpret_cast<uint4*>(dst + (hh * 2 + 1) * p.plane_bytes) = make_uint4(w[4], w[5], w[6], w[7]);
                         }
                     }
-                    ptx::tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0)
-                        ptx::mbar_arrive(ptx::smem_u32(&bar_acc_empty[buf]));
+                    if (lastrow)
+                    {
+                        // this warp has read its part of every row of the batch
+                        ptx::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0)
+                            ptx::mbar_arrive(ptx::smem_u32(&bar_acc_empty[buf]));
+                    }
                 }
                 // the rows are in the ring for every warp (and every warp learns of a wait that gave up)
                 ok = ptx::named_barrier_and(1, kXdWorkers, ok);
@@ -452,6 +498,7 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
                 const int f0 = rows_in ? jf0 : nj, f1 = rows_in ? jf1 : nj;
                 for (int j = 0; j < f0; j++)
                     edge(j);
+#pragma unroll kXdUnroll
                 for (int j = f0; j < f1; j++)
                 {
                     const uint32_t off = (uint32_t)(j * jstep);
@@ -488,7 +535,7 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
     if (threadIdx.x == 0 && abort_flag)
     {
         // a role gave up: let copies that may still be in flight land before the CTA's shared memory is released
-        for (int s = 0; s < p.stages; s++)
+        for (int s = 0; s < kXdStages; s++)
         {
             ptx::mbar_wait_bounded(ptx::smem_u32(&bar_a_full[s]), 0u, 2000000LL);
             ptx::mbar_wait_bounded(ptx::smem_u32(&bar_a_full[s]), 1u, 2000000LL);
@@ -505,7 +552,7 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
     if (warp == kXdWorkerWarps + 1)
     {
         ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc(tmem_base, (uint32_t)(kXdAccBufs * kXdGroup));
+        ptx::tmem_dealloc(tmem_base, (uint32_t)kXdTmemCols);
     }
 }
 
@@ -578,7 +625,7 @@ bool expand_dw_supported(const tb200_ctx* ctx, const ExpandDwProblem& q, std::st
     if ((reinterpret_cast<uintptr_t>(q.out) | reinterpret_cast<uintptr_t>(q.wd)) & 3)
         return no("output and depthwise weights must be 4-byte aligned");
     const int limit = ctx && ctx->max_smem_optin > 0 ? ctx->max_smem_optin : 227 * 1024;
-    if (xd_layout(q, 2).smem_bytes > limit)
+    if (xd_layout(q, kXdStages).smem_bytes > limit)
         return no("weights and ring do not fit in shared memory");
     return true;
 }
@@ -594,22 +641,7 @@ tb200_status expand_dw_launch(tb200_ctx* ctx, const ExpandDwProblem& q)
     const bool bf16 = q.dtype == TB200_BF16;
     const void* kernel = bf16 ? reinterpret_cast<const void*>(&expand_dw_kernel<__nv_bfloat16>)
                               : reinterpret_cast<const void*>(&expand_dw_kernel<__half>);
-    const int limit    = ctx->max_smem_optin > 0 ? ctx->max_smem_optin : 227 * 1024;
-    // Shared memory: as many CTAs per SM as possible first (three hide each other's expansion, window pass and memory
-    // waits), then as many input-row stages as still fit.
-    const int sm_total = 228 * 1024;
-    XdLayout lay       = xd_layout(q, 2);
-    for (int ctas = 3; ctas >= 1; ctas--)
-    {
-        const int per_cta = std::min(limit, sm_total / ctas - 1024);
-        if (xd_layout(q, 2).smem_bytes > per_cta)
-            continue;
-        int stages = 2;
-        while (stages < kXdMaxStages && xd_layout(q, stages + 1).smem_bytes <= per_cta)
-            stages++;
-        lay = xd_layout(q, stages);
-        break;
-    }
+    const XdLayout lay = xd_layout(q, kXdStages);
     const int attr_bit = bf16 ? 13 : 12;
     if (!(ctx->smem_attr_set & (1u << attr_bit)))    // several CTAs of this size per SM need the largest shared-memory carve-out
         TB200_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
@@ -626,7 +658,7 @@ tb200_status expand_dw_launch(tb200_ctx* ctx, const ExpandDwProblem& q)
     TB200_CUDA_CHECK(ctx, cudaDeviceGetAttribute(&blk_reserve, cudaDevAttrReservedSharedMemoryPerBlock, ctx->device));
     const int regs_per_cta = ((fa.numRegs * 32 + 511) / 512 * 512) * (kXdThreads / 32);
     int resident = std::min(sm_regs / std::max(1, regs_per_cta), sm_smem / (lay.smem_bytes + (int)fa.sharedSizeBytes + blk_reserve));
-    resident     = std::min(resident, std::min(2048 / kXdThreads, 512 / (kXdAccBufs * kXdGroup)));
+    resident     = std::min(resident, std::min(2048 / kXdThreads, 512 / kXdTmemCols));
     if (resident < 1)
         return fail(ctx, TB200_INTERNAL, "fused CONV2D + DEPTHWISE_CONV2D kernel does not fit on an SM");
 
@@ -664,7 +696,7 @@ tb200_status expand_dw_launch(tb200_ctx* ctx, const ExpandDwProblem& q)
     k.clamp1 = q.clamp1; k.lo1 = q.lo1; k.hi1 = q.hi1;
     k.clamp2 = q.clamp2; k.lo2 = q.lo2; k.hi2 = q.hi2;
     k.groups = q.C / kXdGroup;
-    k.stages = lay.stages; k.a_stage_bytes = lay.a_stage_bytes; k.b_group_bytes = lay.b_group_bytes;
+    k.a_stage_bytes = lay.a_stage_bytes; k.b_group_bytes = lay.b_group_bytes;
     k.a_tx_bytes     = a_box_rows * row_bytes;
     k.b_off = lay.b_off; k.a_off = lay.a_off; k.ring_off = lay.ring_off; k.bias_off = lay.bias_off;
     k.ring_row_bytes = lay.ring_row_bytes;

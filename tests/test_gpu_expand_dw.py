@@ -81,7 +81,7 @@ def _run_both(ctx, dt, name, seed, N, IH, IW, IC, C, pad, stride, clamp1, clamp2
 
 # (N, IH, IW, IC, C, pad, stride, clamp1, clamp2, bias lengths): strides 1 and 2 in both directions, every padding side,
 # the three channel widths of one swizzled row, one to three channel groups, widths from 3 pixels to a full MMA tile,
-# bands that end on the image border, broadcast biases, no CLAMP
+# bands that end on the image border, broadcast biases, no CLAMP, several work items per CTA
 SMALL_CASES = [
     (2, 9, 9, 32, 64, [1, 1, 1, 1], [1, 1], (0.0, 6.0), (0.0, 6.0), None, None),
     (3, 12, 14, 32, 192, [1, 0, 1, 0], [2, 2], (0.0, 6.0), (0.0, 6.0), None, None),
@@ -91,6 +91,10 @@ SMALL_CASES = [
     (2, 30, 17, 32, 128, [1, 1, 0, 0], [1, 2], (-0.5, 0.5), (0.0, 6.0), None, None),
     (5, 12, 112, 32, 192, [1, 0, 1, 0], [2, 2], (0.0, 6.0), (0.0, 6.0), None, None),
     (1, 58, 20, 64, 256, [2, 2, 2, 2], [1, 1], (0.0, 6.0), (0.0, 6.0), None, None),
+    # more work items than CTAs, bands with an odd number of input rows: a CTA runs several items one after the other and
+    # ends each on a short batch of rows
+    (40, 7, 9, 32, 192, [1, 1, 1, 1], [1, 1], (0.0, 6.0), (0.0, 6.0), None, None),
+    (48, 10, 12, 16, 128, [1, 0, 1, 0], [2, 2], None, (0.0, 6.0), None, None),
 ]
 
 
