@@ -182,6 +182,25 @@ def depthwise_f16_config(ctx, timer, name, N, H, W, C, iters, seed):
             "l2": note}
 
 
+def fused_head_f16_config(ctx, timer, name, N, H, W, IC, C, iters, seed):
+    """fp16 1x1 CONV2D IC->C + CLAMP [0,6] -> 3x3 DEPTHWISE_CONV2D stride 2, pad [1,0,1,0] + CLAMP [0,6] as one kernel (the
+    head of the inverted-residual block); the bytes counted are the input and the output, the tensor between the two
+    operators never reaches device memory."""
+    r = np.random.default_rng(seed)
+    x = r.standard_normal((N, H, W, IC)).astype(np.float16)
+    w1 = (r.standard_normal((C, 1, 1, IC)) / np.sqrt(IC)).astype(np.float16)
+    wd = (r.standard_normal((3, 3, C, 1)) / 3).astype(np.float16)
+    tx, tw1, twd = ctx.from_numpy(x), ctx.from_numpy(w1), ctx.from_numpy(wd)
+    tb1, tbd = ctx.from_numpy(np.zeros(C, np.float16)), ctx.from_numpy(np.zeros(C, np.float16))
+    to = ctx.empty(tb.DType.FP16, (N, H // 2, W // 2, C))
+    relu6 = tb.Epilogue(None, (0.0, 6.0))
+    fn = lambda: ctx.conv2d_depthwise(tx, tw1, tb1, twd, tbd, to, [1, 0, 1, 0], [2, 2], relu6, relu6)
+    nbytes = x.nbytes + N * (H // 2) * (W // 2) * C * 2
+    ms, note = timer.time(fn, iters, nbytes)
+    return {"config": name, "kernel": ctx.last_kernel(), "ms": ms, "GBps": nbytes / ms / 1e6, "algorithmic_bytes": nbytes,
+            "l2": note}
+
+
 def graph_profile(batch):
     """Per-step times of one eager evaluation of the benchmark graph (each step bracketed by a device sync, so the sum
     exceeds the replayed graph's time; the shares are what this is for)."""
@@ -246,6 +265,8 @@ def main():
     ap.add_argument("--matmul-f16", default=None, help="also time one fp16 MATMUL with fp16 output: N,H,C,W")
     ap.add_argument("--matmul-f32", default=None, help="also time one fp32 MATMUL (FFMA kernel): N,H,C,W")
     ap.add_argument("--depthwise-f16", default=None, help="also time one fp16 3x3 stride-2 DEPTHWISE_CONV2D + CLAMP: N,H,W,C")
+    ap.add_argument("--fused-head", default=None,
+                    help="also time one fp16 1x1 CONV2D + CLAMP + 3x3 stride-2 DEPTHWISE_CONV2D + CLAMP as one kernel: N,H,W,IC,C")
     ap.add_argument("--join", default=None,
                     help="also time one fused int8 residual join (RESCALE x2, ADD, RESCALE, CLAMP): N,H,W,C")
     ap.add_argument("--graph-profile", type=int, default=0, metavar="BATCH",
@@ -288,6 +309,10 @@ def main():
         if args.matmul_f32:
             n, h, c, w = [int(v) for v in args.matmul_f32.split(",")]
             print(json.dumps(matmul_f32_config(ctx, timer, "matmul fp32 %s" % args.matmul_f32, n, h, c, w, args.iters, 19)))
+            sys.stdout.flush()
+        if args.fused_head:
+            n, h, w, ic, c = [int(v) for v in args.fused_head.split(",")]
+            print(json.dumps(fused_head_f16_config(ctx, timer, "fused head fp16 %s" % args.fused_head, n, h, w, ic, c, args.iters, 29)))
             sys.stdout.flush()
         if args.depthwise_f16:
             n, h, w, c = [int(v) for v in args.depthwise_f16.split(",")]
