@@ -518,6 +518,75 @@ def run_graph(args, rank, local_rank, world, barrier, all_max, all_min, exchange
                        "frac": tops / (2 * peaks["bf16_burst"] * world)}}
 
 
+def run_block_f16(local_rank, iters=20):
+    """The fp16 inverted-residual block (64 x 112 x 112 x 32: 1x1 CONV2D 32->192 + CLAMP, 3x3 DEPTHWISE_CONV2D stride 2 + CLAMP,
+    1x1 CONV2D 192->64) on one GPU, reported as the `block_f16` object: the fused head (tb200_conv2d_depthwise) + the
+    second 1x1 against the three operators run one by one, L2 flushed between timed calls, the fused head's output compared
+    bit for bit with the two-kernel chain's outside the timed region."""
+    import torch
+    import reference_model_b200 as tb
+
+    N, HW, C0, C1, C2 = 64, 112, 32, 192, 64
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ctx = tb.Context(local_rank, stream.cuda_stream)
+        g = torch.Generator(device="cuda").manual_seed(4)
+        x = torch.randn((N, HW, HW, C0), device="cuda", generator=g).half()
+        w1 = (torch.randn((C1, 1, 1, C0), device="cuda", generator=g) / C0 ** 0.5).half()
+        wd = (torch.randn((3, 3, C1, 1), device="cuda", generator=g) / 3).half()
+        w2 = (torch.randn((C2, 1, 1, C1), device="cuda", generator=g) / C1 ** 0.5).half()
+        b1, bd, b2 = ((0.1 * torch.randn(n, device="cuda", generator=g)).half() for n in (C1, C1, C2))
+        t1 = torch.empty((N, HW, HW, C1), device="cuda", dtype=torch.float16)
+        t2 = torch.empty((N, HW // 2, HW // 2, C1), device="cuda", dtype=torch.float16)
+        t2f = torch.empty_like(t2)
+        y = torch.empty((N, HW // 2, HW // 2, C2), device="cuda", dtype=torch.float16)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        wrap = lambda t: ctx.wrap(tb.DType.FP16, tuple(t.shape), t.data_ptr(), t)
+        X, W1, WD, W2, B1, BD, B2, T1, T2, T2F, Y = map(wrap, (x, w1, wd, w2, b1, bd, b2, t1, t2, t2f, y))
+        relu6 = tb.Epilogue(None, (0.0, 6.0))
+        pad, stride = [1, 0, 1, 0], [2, 2]
+
+        def fused():
+            ctx.conv2d_depthwise(X, W1, B1, WD, BD, T2F, pad, stride, relu6, relu6)
+            ctx.conv2d(T2F, W2, B2, Y, [0, 0, 0, 0], [1, 1], [1, 1], 0, 0, None)
+
+        def three():
+            ctx.conv2d(X, W1, B1, T1, [0, 0, 0, 0], [1, 1], [1, 1], 0, 0, relu6)
+            ctx.depthwise_conv2d(T1, WD, BD, T2, pad, stride, [1, 1], 0, 0, relu6)
+            ctx.conv2d(T2, W2, B2, Y, [0, 0, 0, 0], [1, 1], [1, 1], 0, 0, None)
+
+        def timed(fn):
+            for _ in range(3):
+                fn()
+            total = 0.0
+            for _ in range(iters):
+                flush.fill_(1)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                fn()
+                e1.record(stream)
+                e1.synchronize()
+                total += e0.elapsed_time(e1)
+            assert ctx.sync() == tb.Status.OK, ctx.last_error()
+            return total / iters
+
+        ms_three = timed(three)
+        ms_fused = timed(fused)
+        ctx.conv2d_depthwise(X, W1, B1, WD, BD, T2F, pad, stride, relu6, relu6)
+        kernel = ctx.last_kernel()
+        assert ctx.sync() == tb.Status.OK, ctx.last_error()
+        same = bool(torch.equal(t2.view(torch.int16), t2f.view(torch.int16)))
+        nbytes = 2 * (x.numel() + 2 * t2.numel() + y.numel())
+        peaks = measured_peaks()
+        hbm, src = peaks["hbm"], peaks["source"]
+        ctx.close()
+    return {"config": "fp16 inverted-residual block 64x112x112x32 -> 192 -> 56x56x64, L2 flushed between calls",
+            "kernel": kernel, "ms": ms_fused, "ms_three_kernels": ms_three, "algorithmic_bytes": nbytes,
+            "hbm": {"achieved": nbytes / ms_fused / 1e6, "peak": hbm, "unit": "GB/s", "frac": nbytes / ms_fused / 1e6 / hbm,
+                    "peak_source": src},
+            "bit_equal_to_two_kernel_head": same}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="both", choices=["both", "matmul", "resnet50"])
@@ -583,6 +652,12 @@ def main():
     gr = None
     if args.workload in ("both", "resnet50"):
         gr = run_graph(args, rank, local_rank, world, barrier, all_max, all_min, exchange_bytes)
+    blk = None
+    if rank == 0 and args.workload == "both":
+        try:
+            blk = run_block_f16(local_rank)
+        except Exception as exc:    # an extra object: its failure is reported, it does not take the line with it
+            blk = {"error": "%s: %s" % (type(exc).__name__, exc)}
     if rank == 0:
         if mm is not None:
             line = {"metric": METRIC, "value": mm["value"], "unit": "TOPS", "n_gpus": world, "steps": args.steps,
@@ -594,6 +669,8 @@ def main():
                 line["sustained"] = mm["sustained"]
             if gr is not None:
                 line["graph"] = gr
+            if blk is not None:
+                line["block_f16"] = blk
         else:
             line = {"metric": gr["metric"], "value": gr["value"], "unit": "images/s", "n_gpus": world, "steps": args.steps,
                     "warmup": args.warmup, "ms_per_step": gr["ms_per_batch"], "higher_is_better": True,
