@@ -5,6 +5,9 @@ import numpy as np
 from oracle import oracle as orc
 
 _BITS = {"INT8": 8, "INT16": 16, "INT32": 32, "UINT8": 8, "UINT16": 16}
+# floating tensors travel as float32 arrays holding values of the tensor's type; every floating operator accumulates in
+# fp32 in the reference's order and rounds its result to the output type (fpTrunc, arith_util.h:206-230)
+_FDT = {"FP16": "fp16", "BF16": "bf16", "FP32": "fp32"}
 
 
 def evaluate(graph, inputs, nthreads=8):
@@ -14,9 +17,21 @@ def evaluate(graph, inputs, nthreads=8):
     status = orc.VALID
     for op in graph.ops:
         a = op.attr
-        if op.kind == "CONV2D":
+        fdt = _FDT.get(graph.meta[op.inputs[0]][0].name)
+        if op.kind in ("CONV2D", "DEPTHWISE_CONV2D") and fdt is not None:
+            fn = orc.conv2d if op.kind == "CONV2D" else orc.depthwise_conv2d
+            out = fn(np.asarray(t[op.inputs[0]], np.float32), np.asarray(t[op.inputs[1]], np.float32),
+                     np.asarray(t[op.inputs[2]], np.float32), a["pad"], a["stride"], a["dilation"], mode="f32", nthreads=nthreads)
+            out = orc.fptrunc(out, _FDT[graph.meta[op.outputs[0]][0].name])
+        elif op.kind == "CLAMP" and fdt is not None:
+            st, out = orc.clamp(np.asarray(t[op.inputs[0]], np.float32), a["min_val"], a["max_val"], mode="f32", fdt=fdt)
+            status = max(status, st)
+        elif op.kind == "CONV2D":
             out = orc.conv2d(t[op.inputs[0]], t[op.inputs[1]], t[op.inputs[2]], a["pad"], a["stride"], a["dilation"],
                              a["input_zp"], a["weight_zp"], nthreads=nthreads)
+        elif op.kind == "DEPTHWISE_CONV2D":
+            out = orc.depthwise_conv2d(t[op.inputs[0]], t[op.inputs[1]], t[op.inputs[2]], a["pad"], a["stride"], a["dilation"],
+                                       a["input_zp"], a["weight_zp"], nthreads=nthreads)
         elif op.kind == "TRANSPOSE_CONV2D":
             out = orc.transpose_conv2d(t[op.inputs[0]], t[op.inputs[1]], t[op.inputs[2]], a["out_pad"], a["stride"],
                                        a["input_zp"], a["weight_zp"], nthreads=nthreads)

@@ -8,8 +8,12 @@ outputs are allocated before a node runs.  Two things are added for the device:
   * a fuser that collapses CONV2D -> RESCALE -> CLAMP chains and the five-node int8 residual join
     (RESCALE, RESCALE, ADD, RESCALE, CLAMP) when every intermediate has a single consumer
     (reference_model/src/tensor.h:92-100 exposes the same producer / consumer links), and
+  * for floating-point graphs, CONV2D -> CLAMP and DEPTHWISE_CONV2D -> CLAMP pairs, and the head of an inverted-residual
+    block (1x1 CONV2D -> CLAMP -> 3x3 DEPTHWISE_CONV2D -> CLAMP), which tb200_conv2d_depthwise evaluates as one kernel
+    without the expanded tensor ever reaching device memory, and
   * optional CUDA-graph capture of the whole evaluation so that a replay costs one launch.
 
+`inverted_residual_f16` builds the fp16 inverted-residual block of the floating-point configuration.
 `resnet50_int8` builds the ResNet-50-shaped int8 graph of the benchmark configuration: TOSA-legal pads
 (the exact-division rule, reference_model/src/ops/tensor_ops.cpp:203-223), SLICE to an odd size in front of the
 stride-2 1x1 shortcut convolutions, INT32-only ADD for the residual joins (reference_model/src/ops/op_factory.cpp:189-195).
@@ -41,7 +45,8 @@ class Graph:
         arr = np.ascontiguousarray(array)
         if dtype is None:
             dtype = {np.dtype(np.int8): tb.DType.INT8, np.dtype(np.int32): tb.DType.INT32,
-                     np.dtype(np.int16): tb.DType.INT16}[arr.dtype]
+                     np.dtype(np.int16): tb.DType.INT16, np.dtype(np.float16): tb.DType.FP16,
+                     np.dtype(np.float32): tb.DType.FP32}[arr.dtype]
         self.consts[name] = arr
         return self.tensor(name, dtype, arr.shape)
 
@@ -70,6 +75,38 @@ class Graph:
                 n, h, c = self.meta[op.inputs[0]][1]
                 total += n * h * c * self.meta[op.inputs[1]][1][2]
         return total
+
+
+# ------------------------------------------------------------------------------------------------ fp16 block builder
+def inverted_residual_f16(batch, hw=112, c_in=32, expand=6, c_out=64, seed=20251125 + 7):
+    """The fp16 inverted-residual block of the floating-point configuration as a TOSA graph: 1x1 CONV2D c_in -> expand *
+    c_in, CLAMP [0, 6], 3x3 DEPTHWISE_CONV2D stride 2 with pad [1, 0, 1, 0], CLAMP [0, 6], 1x1 CONV2D -> c_out (no
+    residual: the stride is 2).  Weights are seeded, of unit output variance."""
+    r = np.random.default_rng(seed)
+    g = Graph()
+    F16 = tb.DType.FP16
+    c_mid, oh = expand * c_in, _conv_out(hw, 3, 1, 0, 2)
+    x = g.tensor("input", F16, (batch, hw, hw, c_in))
+    g.inputs.append(x)
+    w1 = g.const("w_expand", (r.standard_normal((c_mid, 1, 1, c_in)) / np.sqrt(c_in)).astype(np.float16))
+    b1 = g.const("b_expand", (0.1 * r.standard_normal(c_mid)).astype(np.float16))
+    wd = g.const("w_dw", (r.standard_normal((3, 3, c_mid, 1)) / 3.0).astype(np.float16))
+    bd = g.const("b_dw", (0.1 * r.standard_normal(c_mid)).astype(np.float16))
+    w2 = g.const("w_project", (r.standard_normal((c_out, 1, 1, c_mid)) / np.sqrt(c_mid)).astype(np.float16))
+    b2 = g.const("b_project", (0.1 * r.standard_normal(c_out)).astype(np.float16))
+    conv = dict(pad=[0, 0, 0, 0], stride=[1, 1], dilation=[1, 1], input_zp=0, weight_zp=0)
+    t1 = g.tensor("expand", F16, (batch, hw, hw, c_mid))
+    g.add("CONV2D", [x, w1, b1], [t1], **conv)
+    t1c = g.tensor("expand_relu6", F16, (batch, hw, hw, c_mid))
+    g.add("CLAMP", [t1], [t1c], min_val=0.0, max_val=6.0)
+    t2 = g.tensor("dw", F16, (batch, oh, oh, c_mid))
+    g.add("DEPTHWISE_CONV2D", [t1c, wd, bd], [t2], pad=[1, 0, 1, 0], stride=[2, 2], dilation=[1, 1], input_zp=0, weight_zp=0)
+    t2c = g.tensor("dw_relu6", F16, (batch, oh, oh, c_mid))
+    g.add("CLAMP", [t2], [t2c], min_val=0.0, max_val=6.0)
+    y = g.tensor("project", F16, (batch, oh, oh, c_out))
+    g.add("CONV2D", [t2c, w2, b2], [y], **conv)
+    g.outputs.append(y)
+    return g
 
 
 # ------------------------------------------------------------------------------------------------ ResNet-50 builder
@@ -186,6 +223,9 @@ def shard_range(total, rank, world):
 
 
 # ------------------------------------------------------------------------------------------------ fuser
+_FLOATS = (tb.DType.FP16, tb.DType.BF16, tb.DType.FP32)
+
+
 def fuse(graph):
     """Returns a list of device steps.  A step is (kind, op-or-ops): fused convolutions carry their RESCALE / CLAMP,
     fused joins carry the five nodes; everything else is passed through one to one."""
@@ -207,6 +247,26 @@ def fuse(graph):
                 else:
                     steps.append(("CONV_RESCALE_CLAMP", (op, r, None)))
                     skip.add(id(r))
+                continue
+        if op.kind in ("CONV2D", "DEPTHWISE_CONV2D") and graph.meta[op.inputs[0]][0] in _FLOATS:
+            # floating point: a CLAMP behind the operator, and the 1x1 CONV2D -> 3x3 DEPTHWISE_CONV2D pair
+            def with_clamp(o):
+                c = cons[o.outputs[0]][0] if single(o.outputs[0]) else None
+                return c if (c is not None and c.kind == "CLAMP") else None
+            c1 = with_clamp(op)
+            tail = c1 or op
+            dw = cons[tail.outputs[0]][0] if single(tail.outputs[0]) else None
+            if (op.kind == "CONV2D" and dw is not None and dw.kind == "DEPTHWISE_CONV2D" and dw.inputs[0] == tail.outputs[0] and
+                    tuple(graph.meta[op.inputs[1]][1][1:3]) == (1, 1) and list(op.attr["stride"]) == [1, 1] and
+                    list(op.attr["pad"]) == [0, 0, 0, 0] and tuple(graph.meta[dw.inputs[1]][1][0:2]) == (3, 3) and
+                    graph.meta[dw.inputs[1]][1][3] == 1 and list(dw.attr["dilation"]) == [1, 1]):
+                c2 = with_clamp(dw)
+                steps.append(("CONV_DW", (op, c1, dw, c2)))
+                skip.update(id(o) for o in (c1, dw, c2) if o is not None)
+                continue
+            if c1 is not None:
+                steps.append(("CONV_CLAMP" if op.kind == "CONV2D" else "DW_CLAMP", (op, c1)))
+                skip.add(id(c1))
                 continue
         if op.kind == "RESCALE" and graph.meta[op.inputs[0]][0] == tb.DType.INT8 and single(op.outputs[0]):
             add = cons[op.outputs[0]][0]
@@ -295,6 +355,30 @@ class DeviceRunner:
                 ctx.residual_add(t[ra.inputs[0]], self._rescale_attr(ra), t[rb.inputs[0]], self._rescale_attr(rb),
                                  self._rescale_attr(ro), t[out],
                                  (c.attr["min_val"], c.attr["max_val"]) if c else None)
+            elif kind == "CONV_DW":
+                conv, c1, dw, c2 = p
+                e1 = tb.Epilogue(None, (c1.attr["min_val"], c1.attr["max_val"])) if c1 else None
+                e2 = tb.Epilogue(None, (c2.attr["min_val"], c2.attr["max_val"])) if c2 else None
+                out, mid = (c2 or dw).outputs[0], (c1 or conv).outputs[0]
+                args = (t[conv.inputs[0]], t[conv.inputs[1]], t[conv.inputs[2]], t[dw.inputs[1]], t[dw.inputs[2]], t[out],
+                        dw.attr["pad"], dw.attr["stride"], e1, e2)
+                st = ctx.conv2d_depthwise(*args, expanded=t.get(mid), check=False)
+                if st == tb.Status.ERROR and mid not in t and "one kernel" in ctx.last_error():
+                    # a shape the one-kernel form does not take: it needs the tensor between the two operators after all
+                    t[mid] = ctx.empty(*self.graph.meta[mid])
+                    st = ctx.conv2d_depthwise(*args, expanded=t[mid], check=False)
+                if st not in (tb.Status.OK, tb.Status.UNPREDICTABLE):
+                    raise tb.Tb200Error(st, ctx.last_error())
+            elif kind in ("CONV_CLAMP", "DW_CLAMP"):
+                op, c = p
+                a = op.attr
+                fn = ctx.conv2d if kind == "CONV_CLAMP" else ctx.depthwise_conv2d
+                fn(t[op.inputs[0]], t[op.inputs[1]], t[op.inputs[2]], t[c.outputs[0]], a["pad"], a["stride"], a["dilation"],
+                   a["input_zp"], a["weight_zp"], tb.Epilogue(None, (c.attr["min_val"], c.attr["max_val"])))
+            elif kind == "DEPTHWISE_CONV2D":
+                a = p.attr
+                ctx.depthwise_conv2d(t[p.inputs[0]], t[p.inputs[1]], t[p.inputs[2]], t[p.outputs[0]], a["pad"], a["stride"],
+                                     a["dilation"], a["input_zp"], a["weight_zp"])
             elif kind == "CONV2D":
                 a = p.attr
                 ctx.conv2d(t[p.inputs[0]], t[p.inputs[1]], t[p.inputs[2]], t[p.outputs[0]], a["pad"], a["stride"],

@@ -138,3 +138,33 @@ def test_shapes_outside_the_fused_form(ctx):
     st = ctx.conv2d_depthwise(tx, tw1, tb1, twd2, tbd2, tbad, [1, 1, 1, 1], [1, 1], relu6, relu6, check=False)
     assert st == tb.Status.ERROR
     _free(tx, tw1, tb1, twd, tbd, twd2, tbd2, t1, t2, tf, te, tbad)
+
+
+def test_graph_fuser_reaches_the_fused_kernel(ctx):
+    """The fp16 inverted-residual block as a TOSA graph through the host mirror: the fuser hands the 1x1 CONV2D, its CLAMP,
+    the 3x3 DEPTHWISE_CONV2D and its CLAMP to tb200_conv2d_depthwise; eager, as a replayed CUDA graph and node by node
+    (every operator on its own) the output is the same bit for bit, and it agrees with the oracle's node-by-node
+    evaluation within the few fp16 steps that fp32 sums taken in another order can move a value."""
+    from oracle import graph_eval
+    from reference_model_b200 import graph as G
+    g = G.inverted_residual_f16(3, hw=28)
+    x = orc.fptrunc(util.rng(17).standard_normal((3, 28, 28, 32)).astype(np.float32), "fp16")
+    fused = G.DeviceRunner(ctx, g, fused=True)
+    assert [k for k, _ in fused.steps] == ["CONV_DW", "CONV2D"]
+    fused.set_input(x.astype(np.float16))
+    fused.run()
+    assert ctx.sync() == tb.Status.OK
+    st, y_fused = fused.output()
+    assert "expand_relu6" not in fused.t, "the expanded tensor must not exist on the device"
+    plain = G.DeviceRunner(ctx, g, fused=False)
+    plain.set_input(x.astype(np.float16))
+    plain.run()
+    st, y_plain = plain.output()
+    assert np.array_equal(y_fused.view(np.uint16), y_plain.view(np.uint16))
+    fused.capture()
+    fused.run()
+    st, y_replay = fused.output()
+    assert st == tb.Status.OK and np.array_equal(y_replay.view(np.uint16), y_fused.view(np.uint16))
+    est, t = graph_eval.evaluate(g, {"input": x}, nthreads=orc.num_procs())
+    assert est == orc.VALID
+    np.testing.assert_allclose(y_fused.astype(np.float32), t["project"], rtol=2.0 ** -7, atol=2.0 ** -7)
