@@ -168,3 +168,43 @@ def test_graph_fuser_reaches_the_fused_kernel(ctx):
     est, t = graph_eval.evaluate(g, {"input": x}, nthreads=orc.num_procs())
     assert est == orc.VALID
     np.testing.assert_allclose(y_fused.astype(np.float32), t["project"], rtol=2.0 ** -7, atol=2.0 ** -7)
+
+
+@pytest.mark.parametrize("dt,name", [(F16, "fp16"), (BF16, "bf16")])
+def test_fused_special_values(ctx, dt, name):
+    """NaN, infinities, zeros of both signs and values that overflow the storage type in the input: the fused kernel and the
+    two-kernel chain agree bit for bit (a NaN reaches the output as the type's canonical NaN through both, an infinity is
+    clamped, -0 products leave no trace), and NaNs land exactly in the windows that hold one."""
+    N, IH, IW, IC, C = 2, 10, 12, 32, 64
+    x, w1, b1, wd, bd = _operands(91, name, N, IH, IW, IC, C, C, C)
+    x[0, 3, 4, 5] = np.nan
+    x[0, 7, 2, :] = np.inf
+    x[1, 1, 1, 0] = -np.inf
+    x[1, 5:8, :, :] = 0.0
+    x[1, 8, :, ::2] = -0.0
+    x[1, 2, 6, :] = 60000.0 if name == "fp16" else 3.0e38    # sums beyond the largest finite value of the type
+    tx, tw1, tb1, twd, tbd = (_up(ctx, a, dt) for a in (x, w1, b1, wd, bd))
+    t1, t2, tf = ctx.empty(dt, (N, IH, IW, C)), ctx.empty(dt, (N, 5, 6, C)), ctx.empty(dt, (N, 5, 6, C))
+    relu6 = tb.Epilogue(None, (0.0, 6.0))
+    pad, stride = [1, 0, 1, 0], [2, 2]
+    for e1, e2 in ((relu6, relu6), (None, None)):
+        ctx.conv2d(tx, tw1, tb1, t1, [0, 0, 0, 0], [1, 1], [1, 1], 0, 0, e1)
+        ctx.depthwise_conv2d(t1, twd, tbd, t2, pad, stride, [1, 1], 0, 0, e2)
+        ctx.conv2d_depthwise(tx, tw1, tb1, twd, tbd, tf, pad, stride, e1, e2)
+        assert ctx.last_kernel().startswith("expand_dw")
+        assert ctx.sync() == tb.Status.OK
+        a, b = t2.download()[1].view(np.uint16), tf.download()[1].view(np.uint16)
+        assert np.array_equal(a, b), np.argwhere(a != b)[:5]
+        if e1 is not None:
+            # with the CLAMPs no infinity is left in the expanded tensor, and an output is NaN exactly where a tap of its
+            # window (same channel) is
+            o1, of = _down(t1, dt), _down(tf, dt)
+            assert np.isnan(o1).any() and not np.isinf(o1).any()
+            padded = np.zeros((N, IH + 1, IW + 1, C), bool)
+            padded[:, 1:, 1:, :] = np.isnan(o1)
+            exp = np.zeros((N, 5, 6, C), bool)
+            for ky in range(3):
+                for kx in range(3):
+                    exp |= padded[:, ky:ky + 9:2, kx:kx + 11:2, :]
+            assert np.array_equal(np.isnan(of), exp), "NaN positions"
+    _free(tx, tw1, tb1, twd, tbd, t1, t2, tf)
