@@ -208,3 +208,23 @@ def test_fused_special_values(ctx, dt, name):
                     exp |= padded[:, ky:ky + 9:2, kx:kx + 11:2, :]
             assert np.array_equal(np.isnan(of), exp), "NaN positions"
     _free(tx, tw1, tb1, twd, tbd, t1, t2, tf)
+
+
+def test_test_directory_runner_on_the_float_block(ctx, tmp_path):
+    """The fp16 block as a test directory (desc.json, graph, .npy constants and input): the runner loads the fp16 files,
+    evaluates the graph with the fused head, writes the fp16 result, and reports VALID; node by node it writes the same
+    bytes."""
+    from oracle import graph_eval
+    from reference_model_b200 import graph as G, run_test as RT
+    g = G.inverted_residual_f16(2, hw=20)
+    x = util.rng(23).standard_normal(g.meta["input"][1]).astype(np.float16)
+    desc = RT.save_test(g, {"input": x}, str(tmp_path / "block"))
+    status, msg, written = RT.run_test(desc)
+    assert status == 0 and msg is None and len(written) == 1
+    out = np.load(written[0])
+    assert out.dtype == np.float16 and out.shape == g.meta["project"][1]
+    status, msg, written2 = RT.run_test(desc, fused=False)
+    assert status == 0 and np.array_equal(np.load(written2[0]).view(np.uint16), out.view(np.uint16))
+    est, t = graph_eval.evaluate(g, {"input": x.astype(np.float32)}, nthreads=orc.num_procs())
+    assert est == orc.VALID
+    np.testing.assert_allclose(out.astype(np.float32), t["project"], rtol=2.0 ** -7, atol=2.0 ** -7)
