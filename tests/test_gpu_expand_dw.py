@@ -228,3 +228,35 @@ def test_test_directory_runner_on_the_float_block(ctx, tmp_path):
     est, t = graph_eval.evaluate(g, {"input": x.astype(np.float32)}, nthreads=orc.num_procs())
     assert est == orc.VALID
     np.testing.assert_allclose(out.astype(np.float32), t["project"], rtol=2.0 ** -7, atol=2.0 ** -7)
+
+
+def test_fused_kernel_with_a_tiny_wait_limit(ctx):
+    """Every wait of the fused kernel is bounded by the context's limit.  With a limit of a few hundred cycles the first
+    waits (weights and input rows coming from device memory) may run out: the call then reports TB200_INTERNAL, never
+    hangs, frees its tensor memory and leaves the context usable; with the default limit back the result is exact."""
+    N, IH, IW, IC, C = 8, 56, 112, 32, 192
+    x, w1, b1, wd, bd = _operands(55, "fp16", N, IH, IW, IC, C, C, C)
+    tx, tw1, tb1, twd, tbd = (_up(ctx, a, F16) for a in (x, w1, b1, wd, bd))
+    t1, t2, tf = ctx.empty(F16, (N, IH, IW, C)), ctx.empty(F16, (N, 28, 56, C)), ctx.empty(F16, (N, 28, 56, C))
+    relu6 = tb.Epilogue(None, (0.0, 6.0))
+    pad, stride = [1, 0, 1, 0], [2, 2]
+    ctx.conv2d(tx, tw1, tb1, t1, [0, 0, 0, 0], [1, 1], [1, 1], 0, 0, relu6)
+    ctx.depthwise_conv2d(t1, twd, tbd, t2, pad, stride, [1, 1], 0, 0, relu6)
+    assert ctx.sync() == tb.Status.OK
+    gave_up = 0
+    ctx.set_wait_limit(200)
+    try:
+        for _ in range(3):
+            ctx.conv2d_depthwise(tx, tw1, tb1, twd, tbd, tf, pad, stride, relu6, relu6)
+            st = ctx.sync(check=False)
+            assert st in (tb.Status.OK, tb.Status.INTERNAL), st
+            if st == tb.Status.INTERNAL:
+                assert "gave up" in ctx.last_error()
+                gave_up += 1
+    finally:
+        ctx.set_wait_limit(4000000000)
+    ctx.conv2d_depthwise(tx, tw1, tb1, twd, tbd, tf, pad, stride, relu6, relu6)
+    assert ctx.sync() == tb.Status.OK
+    assert np.array_equal(t2.download()[1].view(np.uint16), tf.download()[1].view(np.uint16))
+    print("calls that gave up with a 200-cycle limit: %d of 3" % gave_up)
+    _free(tx, tw1, tb1, twd, tbd, t1, t2, tf)
