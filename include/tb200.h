@@ -262,6 +262,19 @@ extern "C"
                                                   const tb200_epilogue* dw_epilogue, tb200_tensor* expanded,
                                                   tb200_tensor* output);
 
+    /* CONV3D.  Replaces OpConv3d<In,W,Acc,Out>::eval (reference_model/src/ops/tensor_ops.cpp:934-1120) and the checks of
+     * check_conv_attribute with conv_dimension 3 (:120-226) / OpConv3d::checkTensorAttributes (:902-931).
+     * input [N,ID,IH,IW,IC], weight [OC,KD,KH,KW,IC], bias [OC] or [1]; pad = {d0,d1,top,bottom,left,right}, stride and
+     * dilation = {d,y,x}; output [N,OD,OH,OW,OC].  Type tuples INT8/INT8/INT32/INT32 (or, with a RESCALE epilogue, the
+     * RESCALE's output type), FP16, BF16 and FP32 with fp32 accumulation (:2231-2235); taps outside the input are skipped,
+     * order kd, ky, kx, ic.  A kernel of depth 1 with depth stride 1 and no depth padding runs as a CONV2D over N * ID
+     * images (tb200_conv2d's kernels, tensor cores included); every other shape runs a CUDA-core kernel, one thread per
+     * output. */
+    TB200_API tb200_status tb200_conv3d(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
+                                        const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp, const int32_t pad[6],
+                                        const int32_t stride[3], const int32_t dilation[3], const tb200_epilogue* epilogue,
+                                        tb200_tensor* output);
+
     /* TRANSPOSE_CONV2D.  Replaces OpTransposeConv2d::eval (reference_model/src/ops/tensor_ops.cpp:2059-2197) and
      * OpTransposeConv2d::checkTensorAttributes (:1982-2056).  input NHWC, weight OHWI, bias [OC] or [1];
      * out_pad = {top,bottom,left,right} (each > -kernel), stride = {y,x}; the output must be

@@ -32,6 +32,9 @@ def evaluate(graph, inputs, nthreads=8):
         elif op.kind == "DEPTHWISE_CONV2D":
             out = orc.depthwise_conv2d(t[op.inputs[0]], t[op.inputs[1]], t[op.inputs[2]], a["pad"], a["stride"], a["dilation"],
                                        a["input_zp"], a["weight_zp"], nthreads=nthreads)
+        elif op.kind == "CONV3D":
+            out = orc.conv3d(t[op.inputs[0]], t[op.inputs[1]], t[op.inputs[2]], a["pad"], a["stride"], a["dilation"],
+                             a["input_zp"], a["weight_zp"], nthreads=nthreads)
         elif op.kind == "TRANSPOSE_CONV2D":
             out = orc.transpose_conv2d(t[op.inputs[0]], t[op.inputs[1]], t[op.inputs[2]], a["out_pad"], a["stride"],
                                        a["input_zp"], a["weight_zp"], nthreads=nthreads)

@@ -124,6 +124,38 @@ def conv2d(x, w, bias, pad, stride, dilation, in_zp=0, w_zp=0, mode="i32", bound
                          nthreads)
 
 
+def conv3d_out_dhw(ID, IH, IW, KD, KH, KW, pad, stride, dilation):
+    return tuple((i - 1 + pad[2 * a] + pad[2 * a + 1] - (k - 1) * dilation[a]) // stride[a] + 1
+                 for a, (i, k) in enumerate(((ID, KD), (IH, KH), (IW, KW))))
+
+
+def check_conv3d_attribute(ID, IH, IW, OD, OH, OW, KD, KH, KW, pad, stride, dilation):
+    return int(lib().orc_check_conv3d_attribute(ID, IH, IW, OD, OH, OW, KD, KH, KW, _ivec(pad), _ivec(stride), _ivec(dilation)))
+
+
+def conv3d(x, w, bias, pad, stride, dilation, in_zp=0, w_zp=0, mode="i32", bounds=False, local_bound=True, nthreads=1):
+    """OpConv3d::eval (tensor_ops.cpp:934-1120).  x [N,ID,IH,IW,IC], w [OC,KD,KH,KW,IC], pad (d0,d1,t,b,l,r), stride and
+    dilation (d,y,x).  mode: i32 | f32 (normal) | f64 (precise / bounds)."""
+    N, ID, IH, IW, IC = x.shape
+    OC, KD, KH, KW, _ = w.shape
+    OD, OH, OW = conv3d_out_dhw(ID, IH, IW, KD, KH, KW, pad, stride, dilation)
+    conv = {"i32": _i32, "f32": _f32, "f64": _f64}[mode]
+    dt = {"i32": np.int32, "f32": np.float32, "f64": np.float64}[mode]
+    x_, w_, b_ = conv(x), conv(w), conv(bias).reshape(-1)
+    out = np.zeros((N, OD, OH, OW, OC), dtype=dt)
+    args = [_p(x_), _p(w_), _p(b_), int(b_.size), _ivec([N, ID, IH, IW, IC, OC, KD, KH, KW, OD, OH, OW]), _ivec(pad),
+            _ivec(stride), _ivec(dilation)]
+    fn = getattr(lib(), "orc_conv3d_%s" % mode)
+    if mode == "i32":
+        args += [ctypes.c_int32(int(in_zp)), ctypes.c_int32(int(w_zp))]
+    if mode == "f64":
+        args += [int(bool(bounds)), int(bool(local_bound))]
+    args += [_p(out), int(nthreads)]
+    fn.restype = None
+    fn(*args)
+    return out
+
+
 def depthwise_conv2d(x, w, bias, pad, stride, dilation, in_zp=0, w_zp=0, mode="i32", bounds=False,
                      local_bound=True, nthreads=1):
     """OpDepthwiseConv2d::eval (tensor_ops.cpp:1172-1334); w is [KH, KW, C, M]."""

@@ -265,6 +265,129 @@ ORC_API void orc_conv2d_f64(const double* in, const double* w, const double* bia
 }
 
 /* ------------------------------------------------------------------------- */
+/* CONV3D (OpConv3d::eval, src/ops/tensor_ops.cpp:934-1120)                    */
+/*   input [N,ID,IH,IW,IC], weights [OC,KD,KH,KW,IC], pad = (d0,d1,t,b,l,r),   */
+/*   stride / dilation = (d,y,x); taps outside the input are skipped (:1077);  */
+/*   order kd -> ky -> kx -> ic, sequential (:1060-1099); bias added last.     */
+/* ------------------------------------------------------------------------- */
+
+/* check_conv_attribute with conv_dimension 3 (src/ops/tensor_ops.cpp:120-226) */
+ORC_API int orc_check_conv3d_attribute(int ID, int IH, int IW, int OD, int OH, int OW, int KD, int KH, int KW,
+                                       const int* pad, const int* stride, const int* dilation)
+{
+    for (int i = 0; i < 6; i++)
+        if (pad[i] < 0)
+            return 1;
+    for (int i = 0; i < 3; i++)
+        if (stride[i] < 1)
+            return 2;
+    for (int i = 0; i < 3; i++)
+        if (dilation[i] < 1)
+            return 3;
+    int full_D = ID - 1 + pad[0] + pad[1] - (KD - 1) * dilation[0];
+    int full_H = IH - 1 + pad[2] + pad[3] - (KH - 1) * dilation[1];
+    int full_W = IW - 1 + pad[4] + pad[5] - (KW - 1) * dilation[2];
+    if ((full_D % stride[0] != 0) || (full_H % stride[1] != 0) || (full_W % stride[2] != 0))
+        return 4;
+    if ((OD != full_D / stride[0] + 1) || (OH != full_H / stride[1] + 1) || (OW != full_W / stride[2] + 1))
+        return 5;
+    return 0;
+}
+
+#define ORC_CONV3D_BODY(TIN, TACC, TOUT, ABSFN, BOUNDS)                                                         \
+    _Pragma("omp parallel for collapse(2) num_threads(nthreads) if (nthreads > 1)") for (int ob = 0; ob < N; ob++) \
+    {                                                                                                           \
+        for (int od = 0; od < OD; od++)                                                                         \
+        {                                                                                                       \
+            for (int oy = 0; oy < OH; oy++)                                                                     \
+                for (int ox = 0; ox < OW; ox++)                                                                 \
+                    for (int oc = 0; oc < OC; oc++)                                                             \
+                    {                                                                                           \
+                        TACC acc = 0;                                                                           \
+                        for (int kd = 0; kd < KD; kd++)                                                         \
+                        {                                                                                       \
+                            int d = od * stride[0] + kd * dilation[0] - pad[0];                                 \
+                            for (int ky = 0; ky < KH; ky++)                                                     \
+                            {                                                                                   \
+                                int y = oy * stride[1] + ky * dilation[1] - pad[2];                             \
+                                for (int kx = 0; kx < KW; kx++)                                                 \
+                                {                                                                               \
+                                    int x = ox * stride[2] + kx * dilation[2] - pad[4];                         \
+                                    if (!((0 <= x && x < IW) && (0 <= y && y < IH) && (0 <= d && d < ID)))      \
+                                        continue;                                                               \
+                                    const TIN* ip = in + ((((int64_t)ob * ID + d) * IH + y) * IW + x) * IC;     \
+                                    const TIN* wp = w + ((((int64_t)oc * KD + kd) * KH + ky) * KW + kx) * IC;   \
+                                    for (int ic = 0; ic < IC; ic++)                                             \
+                                    {                                                                           \
+                                        TACC a = (BOUNDS) ? (TACC)ABSFN(ip[ic]) : (TACC)ip[ic];                 \
+                                        TACC b = (BOUNDS) ? (TACC)ABSFN(wp[ic]) : (TACC)wp[ic];                 \
+                                        if ((BOUNDS) && !local_bound)                                           \
+                                            a = (TACC)in_absmax;                                                \
+                                        acc += (a - (TACC)in_zp) * (b - (TACC)w_zp);                            \
+                                    }                                                                           \
+                                }                                                                               \
+                            }                                                                                   \
+                        }                                                                                       \
+                        TOUT bv = bias[bias_n == 1 ? 0 : oc];                                                   \
+                        if (BOUNDS)                                                                             \
+                            bv = (TOUT)ABSFN(bv);                                                               \
+                        out[((((int64_t)ob * OD + od) * OH + oy) * OW + ox) * OC + oc] = bv + (TOUT)acc;        \
+                    }                                                                                           \
+        }                                                                                                       \
+    }
+
+/* dims = {N, ID, IH, IW, IC, OC, KD, KH, KW, OD, OH, OW} */
+#define ORC_CONV3D_DIMS                                                                                          \
+    const int N = dims[0], ID = dims[1], IH = dims[2], IW = dims[3], IC = dims[4], OC = dims[5], KD = dims[6],   \
+              KH = dims[7], KW = dims[8], OD = dims[9], OH = dims[10], OW = dims[11];
+
+/* integer instantiation <INT8,INT8,INT32,INT32> (src/ops/tensor_ops.cpp:2235) */
+ORC_API void orc_conv3d_i32(const int32_t* in, const int32_t* w, const int32_t* bias, int bias_n, const int* dims,
+                            const int* pad, const int* stride, const int* dilation, int32_t in_zp, int32_t w_zp,
+                            int32_t* out, int nthreads)
+{
+    ORC_CONV3D_DIMS
+    const int local_bound   = 1;
+    const int32_t in_absmax = 0;
+    ORC_CONV3D_BODY(int32_t, uint32_t, uint32_t, abs, 0)
+}
+
+/* floating instantiations with an fp32 accumulator: sequential float accumulation, result left as float */
+ORC_API void orc_conv3d_f32(const float* in, const float* w, const float* bias, int bias_n, const int* dims,
+                            const int* pad, const int* stride, const int* dilation, float* out, int nthreads)
+{
+    ORC_CONV3D_DIMS
+    const float in_zp = 0, w_zp = 0, in_absmax = 0;
+    const int local_bound = 1;
+    ORC_CONV3D_BODY(float, float, float, fabsf, 0)
+}
+
+/* precise mode and its bounds variant (abs of operands, src/ops/tensor_ops.cpp:1015-1027) */
+ORC_API void orc_conv3d_f64(const double* in, const double* w, const double* bias, int bias_n, const int* dims,
+                            const int* pad, const int* stride, const int* dilation, int bounds_mode, int local_bound,
+                            double* out, int nthreads)
+{
+    ORC_CONV3D_DIMS
+    const double in_zp = 0, w_zp = 0;
+    double in_absmax = 0;
+    if (bounds_mode && !local_bound)
+    {
+        int64_t n = (int64_t)N * ID * IH * IW * IC;
+        for (int64_t i = 0; i < n; i++)
+            if (fabs(in[i]) > in_absmax)
+                in_absmax = fabs(in[i]);
+    }
+    if (bounds_mode)
+    {
+        ORC_CONV3D_BODY(double, double, double, fabs, 1)
+    }
+    else
+    {
+        ORC_CONV3D_BODY(double, double, double, fabs, 0)
+    }
+}
+
+/* ------------------------------------------------------------------------- */
 /* DEPTHWISE_CONV2D (OpDepthwiseConv2d::eval, src/ops/tensor_ops.cpp:1172-1334)*/
 /*   weights [KH,KW,C,M]; output channel c*M+m (:1320); order ky -> kx         */
 /* ------------------------------------------------------------------------- */

@@ -72,7 +72,7 @@ EXPORTS = [
     "tb200_timer_enable", "tb200_timer_read", "tb200_capture_begin", "tb200_capture_end", "tb200_graph_launch",
     "tb200_graph_destroy",
     "tb200_tensor_alloc", "tb200_tensor_wrap", "tb200_tensor_free", "tb200_tensor_upload", "tb200_tensor_download",
-    "tb200_tensor_data", "tb200_tensor_bytes", "tb200_tensor_slice", "tb200_tensor_reshape", "tb200_conv2d", "tb200_depthwise_conv2d", "tb200_conv2d_depthwise", "tb200_transpose_conv2d", "tb200_matmul",
+    "tb200_tensor_data", "tb200_tensor_bytes", "tb200_tensor_slice", "tb200_tensor_reshape", "tb200_conv2d", "tb200_depthwise_conv2d", "tb200_conv2d_depthwise", "tb200_conv3d", "tb200_transpose_conv2d", "tb200_matmul",
     "tb200_rescale", "tb200_clamp", "tb200_add", "tb200_residual_add", "tb200_max_pool2d", "tb200_avg_pool2d",
     "tb200_matmul_host", "tb200_set_kernel_policy", "tb200_last_kernel", "tb200_matmul_i8_noalloc",
     "tb200_npy_probe", "tb200_tensor_load_npy", "tb200_tensor_save_npy",
@@ -116,6 +116,7 @@ def load_library():
         "tb200_tensor_bytes": (ctypes.c_size_t, [vp]),
         "tb200_conv2d": (i32, [vp, vp, vp, vp, i32, i32, p_i32, p_i32, p_i32, ctypes.POINTER(_Epilogue), vp]),
         "tb200_depthwise_conv2d": (i32, [vp, vp, vp, vp, i32, i32, p_i32, p_i32, p_i32, ctypes.POINTER(_Epilogue), vp]),
+        "tb200_conv3d": (i32, [vp, vp, vp, vp, i32, i32, p_i32, p_i32, p_i32, ctypes.POINTER(_Epilogue), vp]),
         "tb200_conv2d_depthwise": (i32, [vp, vp, vp, vp, ctypes.POINTER(_Epilogue), vp, vp, p_i32, p_i32,
                                          ctypes.POINTER(_Epilogue), vp, vp]),
         "tb200_transpose_conv2d": (i32, [vp, vp, vp, vp, i32, i32, p_i32, p_i32, ctypes.POINTER(_Epilogue), vp]),
@@ -425,6 +426,12 @@ class Context:
                                                            _ivec(dilation),
                                                            ctypes.byref(epilogue.c) if epilogue else None,
                                                            out.handle), check)
+
+    def conv3d(self, x, w, bias, out, pad, stride, dilation, input_zp=0, weight_zp=0, epilogue=None, check=True):
+        """CONV3D: x [N,ID,IH,IW,IC], w [OC,KD,KH,KW,IC], pad (d0,d1,top,bottom,left,right), stride / dilation (d,y,x)."""
+        return self._check(self.lib.tb200_conv3d(self.handle, x.handle, w.handle, bias.handle, int(input_zp), int(weight_zp),
+                                                 _ivec(pad), _ivec(stride), _ivec(dilation),
+                                                 ctypes.byref(epilogue.c) if epilogue else None, out.handle), check)
 
     def conv2d_depthwise(self, x, w, bias, dw_w, dw_bias, out, dw_pad, dw_stride, conv_epilogue=None, dw_epilogue=None,
                          expanded=None, check=True):

@@ -1511,6 +1511,139 @@ extern "C" tb200_status tb200_conv2d_depthwise(tb200_ctx* ctx, const tb200_tenso
     return st2 != TB200_OK ? st2 : st;
 }
 
+// check_conv_attribute with conv_dimension 3 (reference_model/src/ops/tensor_ops.cpp:120-226): pad = (d0, d1, top, bottom,
+// left, right), stride and dilation = (d, y, x)
+static tb200_status check_conv3d_attr(tb200_ctx* ctx, const int in[3], const int out[3], const int k[3], const int32_t* pad,
+                                      const int32_t* stride, const int32_t* dilation)
+{
+    const char* op = "OpConv3d";
+    for (int i = 0; i < 6; i++)
+        TB200_ERROR_IF(ctx, pad[i] < 0, "%s: At least one pad is smaller than zero", op);
+    for (int i = 0; i < 3; i++)
+        TB200_ERROR_IF(ctx, stride[i] < 1, "%s: At least one stride dimension is smaller than one", op);
+    for (int i = 0; i < 3; i++)
+        TB200_ERROR_IF(ctx, dilation[i] < 1, "%s: At least one dilation dimension is smaller than one", op);
+    int full[3];
+    for (int a = 0; a < 3; a++)
+        full[a] = in[a] - 1 + pad[2 * a] + pad[2 * a + 1] - (k[a] - 1) * dilation[a];
+    TB200_ERROR_IF(ctx, (full[0] % stride[0] != 0) || (full[1] % stride[1] != 0) || (full[2] % stride[2] != 0),
+                   "%s: Parameters must yield exact integer output dimensions", op);
+    TB200_ERROR_IF(ctx, out[0] != full[0] / stride[0] + 1 || out[1] != full[1] / stride[1] + 1 || out[2] != full[2] / stride[2] + 1,
+                   "%s: Mismatch between output shape provided and expected output shape (%d,%d,%d)", op,
+                   full[0] / stride[0] + 1, full[1] / stride[1] + 1, full[2] / stride[2] + 1);
+    return TB200_OK;
+}
+
+// A contiguous rank-4 view [a, b, c, d] over a tensor's memory (no ownership).
+static tb200_tensor view4(const tb200_tensor* t, int a, int b, int c, int d)
+{
+    tb200_tensor v = *t;
+    v.rank         = 4;
+    v.shape[0] = a; v.shape[1] = b; v.shape[2] = c; v.shape[3] = d;
+    v.stride[3] = 1; v.stride[2] = d; v.stride[1] = (int64_t)c * d; v.stride[0] = (int64_t)b * c * d;
+    v.owns       = false;
+    v.contiguous = true;
+    return v;
+}
+
+// CONV3D; see include/tb200.h.
+extern "C" tb200_status tb200_conv3d(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
+                                     const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp, const int32_t pad[6],
+                                     const int32_t stride[3], const int32_t dilation[3], const tb200_epilogue* epilogue,
+                                     tb200_tensor* output)
+{
+    if (!ctx)
+        return TB200_ERROR;
+    TB200_ENTER(ctx);
+    TB200_ERROR_IF(ctx, !input || !weight || !bias || !output || !pad || !stride || !dilation, "OpConv3d: null operand");
+    TB200_ERROR_IF(ctx, !all_contiguous({ input, weight, bias, output }), "OpConv3d: every operand must be contiguous");
+    TB200_ERROR_IF(ctx, input->rank != 5 || weight->rank != 5 || output->rank != 5 || bias->rank != 1,
+                   "OpConv3d: input, weight and output must be rank 5 and bias rank 1");
+    const int N = input->shape[0], ID = input->shape[1], IH = input->shape[2], IW = input->shape[3], IC = input->shape[4];
+    const int OC = weight->shape[0], KD = weight->shape[1], KH = weight->shape[2], KW = weight->shape[3];
+    const int OD = output->shape[1], OH = output->shape[2], OW = output->shape[3];
+    const int in3[3] = { ID, IH, IW }, out3[3] = { OD, OH, OW }, k3[3] = { KD, KH, KW };
+    tb200_status st = check_conv3d_attr(ctx, in3, out3, k3, pad, stride, dilation);
+    if (st != TB200_OK)
+        return st;
+    // OpConv3d::eval ERROR_IFs (reference_model/src/ops/tensor_ops.cpp:961-967)
+    TB200_ERROR_IF(ctx, N != output->shape[0], "OpConv3d: tensor batch mismatch %d != %d", N, output->shape[0]);
+    TB200_ERROR_IF(ctx, weight->shape[4] != IC, "OpConv3d: tensor input channel mismatch %d != %d", weight->shape[4], IC);
+    TB200_ERROR_IF(ctx, OC != output->shape[4], "OpConv3d: tensor output channel mismatch %d != %d", OC, output->shape[4]);
+    TB200_ERROR_IF(ctx, bias->shape[0] != OC && bias->shape[0] != 1, "OpConv3d: bias channel mismatch %d != %d", bias->shape[0], OC);
+    const bool int_path = input->dtype == TB200_INT8;
+    TB200_ERROR_IF(ctx, weight->dtype != input->dtype, "OpConv3d: input and weight dtypes differ");
+    if (int_path)
+        TB200_ERROR_IF(ctx, bias->dtype != TB200_INT32, "OpConv3d: INT8 convolution needs an INT32 bias");
+    else
+    {
+        TB200_ERROR_IF(ctx, !dtype_is_float(input->dtype), "OpConv3d: unsupported input dtype");
+        TB200_ERROR_IF(ctx, bias->dtype != input->dtype || output->dtype != input->dtype,
+                       "OpConv3d: floating bias and output must have the input dtype");
+        TB200_ERROR_IF(ctx, input_zp != 0, "Input zero point must be zero for non int8_t data");
+        TB200_ERROR_IF(ctx, weight_zp != 0, "Weight zero point must be zero for non int8_t data");
+    }
+    TB200_ERROR_IF(ctx, input_zp < -128 || input_zp > 127 || weight_zp < -128 || weight_zp > 127,
+                   "OpConv3d: zero point outside the int8 range");
+    EpiInfo epi;
+    st = parse_epilogue(ctx, "OpConv3d", epilogue, int_path, OC, output->dtype, &epi);
+    if (st != TB200_OK)
+        return st;
+    if (numel(output) == 0)
+        return TB200_OK;
+    // One depth tap, depth stride 1, no depth padding: every depth slice is an image of a CONV2D with the same weights
+    // (output depth od reads input depth od only), so the batch of N x ID images takes CONV2D's kernels, the tensor-core
+    // ones included.
+    if (KD == 1 && stride[0] == 1 && pad[0] == 0 && pad[1] == 0 && (int64_t)N * ID < ((int64_t)1 << 31))
+    {
+        const tb200_tensor in4 = view4(input, N * ID, IH, IW, IC), w4 = view4(weight, OC, KH, KW, IC);
+        tb200_tensor out4      = view4(output, N * OD, OH, OW, OC);
+        return tb200_conv2d(ctx, &in4, &w4, bias, input_zp, weight_zp, pad + 2, stride + 1, dilation + 1, epilogue, &out4);
+    }
+    cache_note_write(ctx, output->data, output->bytes);
+    ConvDev d;
+    memset(&d, 0, sizeof(d));
+    d.N = N; d.IH = IH; d.IW = IW; d.IC = IC; d.OH = OH; d.OW = OW; d.OC = OC; d.KH = KH; d.KW = KW; d.M = 1;
+    d.pad_t = pad[2]; d.pad_l = pad[4]; d.sy = stride[1]; d.sx = stride[2]; d.dy = dilation[1]; d.dx = dilation[2];
+    d.in_zp = input_zp; d.w_zp = weight_zp; d.bias_n = bias->shape[0];
+    fill_conv_dev(&d, epi);
+    ConvDepthDev z;
+    z.ID = ID; z.OD = OD; z.KD = KD; z.pad_d = pad[0]; z.sd = stride[0]; z.dd = dilation[0];
+    const int block = 256;
+    const int grid  = grid_for(ctx, numel(output), block);
+    if (int_path)
+    {
+        const int8_t* in = reinterpret_cast<const int8_t*>(input->data);
+        const int8_t* w  = reinterpret_cast<const int8_t*>(weight->data);
+        const int32_t* b = reinterpret_cast<const int32_t*>(bias->data);
+        switch (dtype_size(output->dtype))
+        {
+            case 1:
+                conv3d_direct_i8_kernel<int8_t><<<grid, block, 0, ctx->stream>>>(in, w, b, reinterpret_cast<int8_t*>(output->data), d, z, ctx->d_status);
+                break;
+            case 2:
+                conv3d_direct_i8_kernel<int16_t><<<grid, block, 0, ctx->stream>>>(in, w, b, reinterpret_cast<int16_t*>(output->data), d, z, ctx->d_status);
+                break;
+            default:
+                conv3d_direct_i8_kernel<int32_t><<<grid, block, 0, ctx->stream>>>(in, w, b, reinterpret_cast<int32_t*>(output->data), d, z, ctx->d_status);
+                break;
+        }
+    }
+    else if (input->dtype == TB200_FP16)
+        conv3d_direct_fp_kernel<__half><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __half*>(input->data), reinterpret_cast<const __half*>(weight->data),
+            reinterpret_cast<const __half*>(bias->data), reinterpret_cast<__half*>(output->data), d, z);
+    else if (input->dtype == TB200_BF16)
+        conv3d_direct_fp_kernel<__nv_bfloat16><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const __nv_bfloat16*>(input->data), reinterpret_cast<const __nv_bfloat16*>(weight->data),
+            reinterpret_cast<const __nv_bfloat16*>(bias->data), reinterpret_cast<__nv_bfloat16*>(output->data), d, z);
+    else
+        conv3d_direct_fp_kernel<float><<<grid, block, 0, ctx->stream>>>(
+            reinterpret_cast<const float*>(input->data), reinterpret_cast<const float*>(weight->data),
+            reinterpret_cast<const float*>(bias->data), reinterpret_cast<float*>(output->data), d, z);
+    return post_launch(ctx, "conv3d_direct");
+}
+
 extern "C" tb200_status tb200_transpose_conv2d(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
                                                const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp,
                                                const int32_t out_pad[4], const int32_t stride[2],

@@ -993,6 +993,138 @@ __global__ void conv2d_direct_fp_kernel(const T* __restrict__ in, const T* __res
     }
 }
 
+// CONV3D (reference_model/src/ops/tensor_ops.cpp:934-1120): input [N,ID,IH,IW,IC], weights [OC,KD,KH,KW,IC], one thread per
+// output element, channel fastest; taps outside the input are skipped, order kd, ky, kx, ic.  `p` carries the height and
+// width attributes, `z` the depth ones.
+struct ConvDepthDev
+{
+    int ID, OD, KD, pad_d, sd, dd;
+};
+
+template <typename TOut>
+__global__ void conv3d_direct_i8_kernel(const int8_t* __restrict__ in, const int8_t* __restrict__ w,
+                                        const int32_t* __restrict__ bias, TOut* __restrict__ out, ConvDev p, ConvDepthDev z,
+                                        int* status)
+{
+    const int64_t total = (int64_t)p.N * z.OD * p.OH * p.OW * p.OC;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    bool bad            = false;
+    const bool vec4     = (p.IC % 4) == 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int oc = (int)(i % p.OC);
+        int64_t r    = i / p.OC;
+        const int ox = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        r /= p.OH;
+        const int od = (int)(r % z.OD);
+        const int n  = (int)(r / z.OD);
+        int32_t acc  = 0;
+        for (int kd = 0; kd < z.KD; kd++)
+        {
+            const int d = od * z.sd + kd * z.dd - z.pad_d;
+            if (d < 0 || d >= z.ID)
+                continue;
+            for (int ky = 0; ky < p.KH; ky++)
+            {
+                const int y = oy * p.sy + ky * p.dy - p.pad_t;
+                if (y < 0 || y >= p.IH)
+                    continue;
+                for (int kx = 0; kx < p.KW; kx++)
+                {
+                    const int x = ox * p.sx + kx * p.dx - p.pad_l;
+                    if (x < 0 || x >= p.IW)
+                        continue;
+                    const int8_t* ip = in + ((((int64_t)n * z.ID + d) * p.IH + y) * p.IW + x) * p.IC;
+                    const int8_t* wp = w + ((((int64_t)oc * z.KD + kd) * p.KH + ky) * p.KW + kx) * p.IC;
+                    if (vec4)
+                    {
+                        // sum (a - za)(b - zb) = sum ab - zb sum a - za sum b + n za zb, four lanes at a time
+                        int32_t sab = 0, sa = 0, sb = 0;
+                        for (int ic = 0; ic < p.IC; ic += 4)
+                        {
+                            const int a4 = *reinterpret_cast<const int*>(ip + ic);
+                            const int b4 = *reinterpret_cast<const int*>(wp + ic);
+                            sab          = __dp4a(a4, b4, sab);
+                            sa           = __dp4a(a4, 0x01010101, sa);
+                            sb           = __dp4a(b4, 0x01010101, sb);
+                        }
+                        acc += sab - p.w_zp * sa - p.in_zp * sb + p.IC * p.in_zp * p.w_zp;
+                    }
+                    else
+                    {
+                        for (int ic = 0; ic < p.IC; ic++)
+                            acc += ((int32_t)ip[ic] - p.in_zp) * ((int32_t)wp[ic] - p.w_zp);
+                    }
+                }
+            }
+        }
+        int32_t v = (int32_t)((uint32_t)bias[p.bias_n == 1 ? 0 : oc] + (uint32_t)acc);
+        if (p.has_rescale)
+        {
+            v = rescale_elem(v, oc, p.rs, bad);
+            if (p.has_clamp)
+            {
+                v = v >= p.clamp_lo ? v : p.clamp_lo;
+                v = v < p.clamp_hi ? v : p.clamp_hi;
+            }
+        }
+        out[i] = (TOut)v;
+    }
+    if (bad)
+        atomicOr(status, TB200_DEV_UNPREDICTABLE);
+}
+
+template <typename T>
+__global__ void conv3d_direct_fp_kernel(const T* __restrict__ in, const T* __restrict__ w, const T* __restrict__ bias,
+                                        T* __restrict__ out, ConvDev p, ConvDepthDev z)
+{
+    const int64_t total = (int64_t)p.N * z.OD * p.OH * p.OW * p.OC;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int oc = (int)(i % p.OC);
+        int64_t r    = i / p.OC;
+        const int ox = (int)(r % p.OW);
+        r /= p.OW;
+        const int oy = (int)(r % p.OH);
+        r /= p.OH;
+        const int od = (int)(r % z.OD);
+        const int n  = (int)(r / z.OD);
+        float acc    = 0.f;
+        for (int kd = 0; kd < z.KD; kd++)
+        {
+            const int d = od * z.sd + kd * z.dd - z.pad_d;
+            if (d < 0 || d >= z.ID)
+                continue;
+            for (int ky = 0; ky < p.KH; ky++)
+            {
+                const int y = oy * p.sy + ky * p.dy - p.pad_t;
+                if (y < 0 || y >= p.IH)
+                    continue;
+                for (int kx = 0; kx < p.KW; kx++)
+                {
+                    const int x = ox * p.sx + kx * p.dx - p.pad_l;
+                    if (x < 0 || x >= p.IW)
+                        continue;
+                    const T* ip = in + ((((int64_t)n * z.ID + d) * p.IH + y) * p.IW + x) * p.IC;
+                    const T* wp = w + ((((int64_t)oc * z.KD + kd) * p.KH + ky) * p.KW + kx) * p.IC;
+                    for (int ic = 0; ic < p.IC; ic++)
+                        acc = fmaf(to_f32<T>(ip[ic]), to_f32<T>(wp[ic]), acc);
+                }
+            }
+        }
+        float v = to_f32<T>(bias[p.bias_n == 1 ? 0 : oc]) + acc;
+        if (p.has_clamp)
+        {
+            v = (v < p.clamp_lo_f) ? p.clamp_lo_f : v;
+            v = (v > p.clamp_hi_f) ? p.clamp_hi_f : v;
+        }
+        out[i] = from_f32<T>(v);
+    }
+}
+
 // DEPTHWISE_CONV2D, weights [KH,KW,C,M], output channel c*M+m (reference_model/src/ops/tensor_ops.cpp:1283-1325)
 template <typename TOut>
 __global__ void depthwise_direct_i8_kernel(const int8_t* __restrict__ in, const int8_t* __restrict__ w,

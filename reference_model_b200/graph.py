@@ -383,6 +383,10 @@ class DeviceRunner:
                 a = p.attr
                 ctx.conv2d(t[p.inputs[0]], t[p.inputs[1]], t[p.inputs[2]], t[p.outputs[0]], a["pad"], a["stride"],
                            a["dilation"], a["input_zp"], a["weight_zp"])
+            elif kind == "CONV3D":
+                a = p.attr
+                ctx.conv3d(t[p.inputs[0]], t[p.inputs[1]], t[p.inputs[2]], t[p.outputs[0]], a["pad"], a["stride"],
+                           a["dilation"], a["input_zp"], a["weight_zp"])
             elif kind == "TRANSPOSE_CONV2D":
                 a = p.attr
                 ctx.transpose_conv2d(t[p.inputs[0]], t[p.inputs[1]], t[p.inputs[2]], t[p.outputs[0]], a["out_pad"],

@@ -300,3 +300,62 @@ def test_fp8_decode_matches_torch_casts():
         assert np.array_equal(mine[ok], theirs[ok]) and np.array_equal(np.signbit(mine[ok]), np.signbit(theirs[ok]))
     assert orc.fp8_to_f32([0x7E], "e4m3")[0] == 448.0 and orc.fp8_to_f32([0x01], "e4m3")[0] == 2.0 ** -9
     assert orc.fp8_to_f32([0x7B], "e5m2")[0] == 57344.0 and orc.fp8_to_f32([0x01], "e5m2")[0] == 2.0 ** -16
+
+
+# reference_model/test/ref_model_tests/tensor_ops_tests.cpp:685-735 (inVals, weightVals, inZp, weightZp)
+ZP_CASES_3D = [
+    ([127, -128, 126, -127, 125, -126, 124, -125], [2, -2, 1, -1, 3, -3, 4, -4], 4, 15),          # :691-696
+    ([122, -7, -120, 121, 123, -8, -119, 120], [2, 1, 4, -7, 3, -2, 5, -6], -10, -5),             # :703-708
+    ([3, -12, 5, 70, -10, 20, 15, 25], [-120, -12, 0, -7, -50, 10, -30, 5], 55, 15),              # :715-720
+    ([-5, 65, -1, 32, 20, -10, -15, 5], [-2, 125, 4, -1, -20, 30, 60, 120], -10, -5),             # :727-732
+]
+
+
+@pytest.mark.parametrize("inv,wv,izp,wzp", ZP_CASES_3D)
+def test_conv3d_zero_point_kat(inv, wv, izp, wzp):
+    # testConv3d, tensor_ops_tests.cpp:395-445: 1x2x2x2x1 input, 1x2x2x2x1 weight, no padding, stride 1, one output
+    x = np.array(inv, np.int8).reshape(1, 2, 2, 2, 1)
+    w = np.array(wv, np.int8).reshape(1, 2, 2, 2, 1)
+    out = orc.conv3d(x, w, np.zeros(1, np.int32), [0] * 6, [1, 1, 1], [1, 1, 1], izp, wzp)
+    assert out.shape == (1, 1, 1, 1, 1)
+    assert int(out[0, 0, 0, 0, 0]) == _expected_dot(inv, wv, izp, wzp)
+
+
+def test_conv3d_against_conv2d_and_numpy():
+    """A CONV3D with one depth tap is a CONV2D over the depth slices (the CONV2D restatement is pinned above), and a full
+    3-D case agrees with a plain numpy evaluation of the definition (tensor_ops.cpp:1060-1106), padding, strides and
+    dilation included."""
+    r = np.random.default_rng(11)
+    x = r.integers(-128, 128, size=(2, 3, 6, 5, 4), dtype=np.int8)
+    w = r.integers(-127, 128, size=(3, 1, 3, 2, 4), dtype=np.int8)
+    b = r.integers(-1000, 1000, size=3).astype(np.int32)
+    out = orc.conv3d(x, w, b, [0, 0, 1, 1, 0, 1], [1, 2, 1], [1, 1, 2], -3, 5)
+    ref = orc.conv2d(x.reshape(6, 6, 5, 4), w.reshape(3, 3, 2, 4), b, [1, 1, 0, 1], [2, 1], [1, 2], -3, 5)
+    assert np.array_equal(out.reshape(ref.shape), ref)
+    x = r.integers(-128, 128, size=(1, 5, 4, 6, 3), dtype=np.int8)
+    w = r.integers(-127, 128, size=(2, 2, 3, 2, 3), dtype=np.int8)
+    b = r.integers(-1000, 1000, size=1).astype(np.int32)
+    pad, stride, dil, izp, wzp = [1, 1, 1, 1, 0, 2], [2, 1, 2], [2, 1, 3], 7, -2
+    out = orc.conv3d(x, w, b, pad, stride, dil, izp, wzp)
+    OD, OH, OW = orc.conv3d_out_dhw(5, 4, 6, 2, 3, 2, pad, stride, dil)
+    assert orc.check_conv3d_attribute(5, 4, 6, OD, OH, OW, 2, 3, 2, pad, stride, dil) == 0
+    assert orc.check_conv3d_attribute(5, 4, 6, OD, OH, OW + 1, 2, 3, 2, pad, stride, dil) == 5
+    assert orc.check_conv3d_attribute(5, 4, 7, OD, OH, OW, 2, 3, 2, pad, stride, dil) == 4    # (7 - 1 + 2 - 3) % 2 != 0
+    exp = np.zeros((1, OD, OH, OW, 2), np.int64)
+    for od in range(OD):
+        for oy in range(OH):
+            for ox in range(OW):
+                for kd in range(2):
+                    for ky in range(3):
+                        for kx in range(2):
+                            d, y, xx = od * 2 + kd * 2 - 1, oy + ky - 1, ox * 2 + kx * 3
+                            if 0 <= d < 5 and 0 <= y < 4 and 0 <= xx < 6:
+                                exp[0, od, oy, ox] += (x[0, d, y, xx].astype(np.int64) - izp) @ (w[:, kd, ky, kx].astype(np.int64) - wzp).T
+    assert np.array_equal(out, exp + int(b[0]))
+    # the floating instantiations on the same taps
+    xf, wf = x.astype(np.float32) / 16, w.astype(np.float32) / 64
+    f32 = orc.conv3d(xf, wf, np.zeros(1, np.float32), pad, stride, dil, mode="f32")
+    f64 = orc.conv3d(xf, wf, np.zeros(1), pad, stride, dil, mode="f64")
+    np.testing.assert_allclose(f32, f64, rtol=1e-5, atol=1e-5)
+    bnd = orc.conv3d(xf, wf, np.zeros(1), pad, stride, dil, mode="f64", bounds=True)
+    assert np.all(bnd >= np.abs(f64) - 1e-12)
