@@ -268,8 +268,10 @@ extern "C"
      * dilation = {d,y,x}; output [N,OD,OH,OW,OC].  Type tuples INT8/INT8/INT32/INT32 (or, with a RESCALE epilogue, the
      * RESCALE's output type), FP16, BF16 and FP32 with fp32 accumulation (:2231-2235); taps outside the input are skipped,
      * order kd, ky, kx, ic.  A kernel of depth 1 with depth stride 1 and no depth padding runs as a CONV2D over N * ID
-     * images (tb200_conv2d's kernels, tensor cores included); every other shape runs a CUDA-core kernel, one thread per
-     * output. */
+     * images (tb200_conv2d's kernels, tensor cores included); a shape whose KD * IC elements make whole 32-byte runs is
+     * staged (depth taps gathered beside the channels, weights re-ordered) and runs as a CONV2D over N * OD images with
+     * KD * IC channels, the same products summed in another order; every other shape runs a CUDA-core kernel, one thread
+     * per output. */
     TB200_API tb200_status tb200_conv3d(tb200_ctx* ctx, const tb200_tensor* input, const tb200_tensor* weight,
                                         const tb200_tensor* bias, int32_t input_zp, int32_t weight_zp, const int32_t pad[6],
                                         const int32_t stride[3], const int32_t dilation[3], const tb200_epilogue* epilogue,

@@ -201,6 +201,22 @@ def fused_head_f16_config(ctx, timer, name, N, H, W, IC, C, iters, seed):
             "l2": note}
 
 
+def conv3d_i8_config(ctx, timer, name, N, ID, IH, IW, IC, OC, K, iters, seed):
+    """int8 CONV3D K x K x K, stride 1, pad K // 2, input_zp -128, int32 output."""
+    r = np.random.default_rng(seed)
+    x = r.integers(-128, 128, size=(N, ID, IH, IW, IC), dtype=np.int8)
+    w = r.integers(-127, 128, size=(OC, K, K, K, IC), dtype=np.int8)
+    b = r.integers(-65536, 65536, size=OC).astype(np.int32)
+    tx, tw, tbias = ctx.from_numpy(x), ctx.from_numpy(w), ctx.from_numpy(b)
+    to = ctx.empty(tb.DType.INT32, (N, ID, IH, IW, OC))
+    fn = lambda: ctx.conv3d(tx, tw, tbias, to, [K // 2] * 6, [1, 1, 1], [1, 1, 1], -128, 0)
+    nbytes = x.nbytes + w.nbytes + N * ID * IH * IW * OC * 4
+    ops = 2.0 * N * ID * IH * IW * OC * K * K * K * IC
+    ms, note = timer.time(fn, iters, nbytes)
+    return {"config": name, "kernel": ctx.last_kernel(), "ms": ms, "TOPS": ops / ms / 1e9, "GBps": nbytes / ms / 1e6,
+            "algorithmic_ops": ops, "algorithmic_bytes": nbytes, "l2": note}
+
+
 def graph_profile(batch):
     """Per-step times of one eager evaluation of the benchmark graph (each step bracketed by a device sync, so the sum
     exceeds the replayed graph's time; the shares are what this is for)."""
@@ -265,6 +281,7 @@ def main():
     ap.add_argument("--matmul-f16", default=None, help="also time one fp16 MATMUL with fp16 output: N,H,C,W")
     ap.add_argument("--matmul-f32", default=None, help="also time one fp32 MATMUL (FFMA kernel): N,H,C,W")
     ap.add_argument("--depthwise-f16", default=None, help="also time one fp16 3x3 stride-2 DEPTHWISE_CONV2D + CLAMP: N,H,W,C")
+    ap.add_argument("--conv3d", default=None, help="also time one int8 CONV3D (cubic kernel, stride 1, same padding): N,ID,IH,IW,IC,OC,K")
     ap.add_argument("--fused-head", default=None,
                     help="also time one fp16 1x1 CONV2D + CLAMP + 3x3 stride-2 DEPTHWISE_CONV2D + CLAMP as one kernel: N,H,W,IC,C")
     ap.add_argument("--join", default=None,
@@ -309,6 +326,10 @@ def main():
         if args.matmul_f32:
             n, h, c, w = [int(v) for v in args.matmul_f32.split(",")]
             print(json.dumps(matmul_f32_config(ctx, timer, "matmul fp32 %s" % args.matmul_f32, n, h, c, w, args.iters, 19)))
+            sys.stdout.flush()
+        if args.conv3d:
+            v = [int(a) for a in args.conv3d.split(",")]
+            print(json.dumps(conv3d_i8_config(ctx, timer, "conv3d int8 %s" % args.conv3d, *v, args.iters, 31)))
             sys.stdout.flush()
         if args.fused_head:
             n, h, w, ic, c = [int(v) for v in args.fused_head.split(",")]

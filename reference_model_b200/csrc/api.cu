@@ -1600,6 +1600,74 @@ extern "C" tb200_status tb200_conv3d(tb200_ctx* ctx, const tb200_tensor* input, 
         tb200_tensor out4      = view4(output, N * OD, OH, OW, OC);
         return tb200_conv2d(ctx, &in4, &w4, bias, input_zp, weight_zp, pad + 2, stride + 1, dilation + 1, epilogue, &out4);
     }
+    // Any other kernel whose depth taps make whole 32-byte runs of K: the taps of every output depth are gathered beside
+    // the channels (staging of KD times the input) and the weights re-ordered to match, which leaves a CONV2D over
+    // N x OD images with KD x IC channels for the tensor-core kernels.  The sum runs over the same products in another
+    // order: exact for integers, inside the floating-point rule like every tensor-core sum.
+    const size_t es  = dtype_size(input->dtype);
+    const size_t run = (size_t)IC * es;
+    if (ctx->policy == 0 && ((size_t)KD * run) % 32 == 0 && (int64_t)N * OD < ((int64_t)1 << 31) && (int64_t)KD * IC < (1 << 24))
+    {
+        const int64_t pixels = (int64_t)IH * IW;
+        const size_t w_bytes = ((size_t)OC * KH * KW * KD * run + 255) & ~(size_t)255;
+        const size_t x_bytes = (size_t)N * OD * pixels * KD * run;
+        st                   = ensure_stage(ctx, w_bytes + x_bytes + 256);
+        if (st != TB200_OK)
+            return st;
+        uint8_t* wm = reinterpret_cast<uint8_t*>(ctx->stage);
+        uint8_t* xm = wm + w_bytes;
+        const int block = 256;
+        const uint32_t zb = (uint32_t)(uint8_t)(int8_t)input_zp * 0x01010101u;    // floating types: zero point 0
+        if (run % 16 == 0)
+        {
+            const int units = (int)(run / 16);
+            const uint4 fill = es == 1 ? make_uint4(zb, zb, zb, zb) : make_uint4(0, 0, 0, 0);
+            conv3d_unfold_depth_kernel<uint4><<<grid_for(ctx, (int64_t)N * OD * pixels * KD * units, block), block, 0, ctx->stream>>>(
+                reinterpret_cast<const uint4*>(input->data), reinterpret_cast<uint4*>(xm), N, ID, OD, KD, pixels, units, stride[0],
+                dilation[0], pad[0], fill);
+            conv3d_fold_weights_kernel<uint4><<<grid_for(ctx, (int64_t)OC * KH * KW * KD * units, block), block, 0, ctx->stream>>>(
+                reinterpret_cast<const uint4*>(weight->data), reinterpret_cast<uint4*>(wm), OC, KD, KH * KW, units);
+        }
+        else if (es == 1)
+        {
+            conv3d_unfold_depth_kernel<uint8_t><<<grid_for(ctx, (int64_t)N * OD * pixels * KD * IC, block), block, 0, ctx->stream>>>(
+                reinterpret_cast<const uint8_t*>(input->data), xm, N, ID, OD, KD, pixels, IC, stride[0], dilation[0], pad[0],
+                (uint8_t)(int8_t)input_zp);
+            conv3d_fold_weights_kernel<uint8_t><<<grid_for(ctx, (int64_t)OC * KH * KW * KD * IC, block), block, 0, ctx->stream>>>(
+                reinterpret_cast<const uint8_t*>(weight->data), wm, OC, KD, KH * KW, IC);
+        }
+        else if (es == 2)
+        {
+            conv3d_unfold_depth_kernel<uint16_t><<<grid_for(ctx, (int64_t)N * OD * pixels * KD * IC, block), block, 0, ctx->stream>>>(
+                reinterpret_cast<const uint16_t*>(input->data), reinterpret_cast<uint16_t*>(xm), N, ID, OD, KD, pixels, IC, stride[0],
+                dilation[0], pad[0], (uint16_t)0);
+            conv3d_fold_weights_kernel<uint16_t><<<grid_for(ctx, (int64_t)OC * KH * KW * KD * IC, block), block, 0, ctx->stream>>>(
+                reinterpret_cast<const uint16_t*>(weight->data), reinterpret_cast<uint16_t*>(wm), OC, KD, KH * KW, IC);
+        }
+        else
+        {
+            conv3d_unfold_depth_kernel<uint32_t><<<grid_for(ctx, (int64_t)N * OD * pixels * KD * IC, block), block, 0, ctx->stream>>>(
+                reinterpret_cast<const uint32_t*>(input->data), reinterpret_cast<uint32_t*>(xm), N, ID, OD, KD, pixels, IC, stride[0],
+                dilation[0], pad[0], 0u);
+            conv3d_fold_weights_kernel<uint32_t><<<grid_for(ctx, (int64_t)OC * KH * KW * KD * IC, block), block, 0, ctx->stream>>>(
+                reinterpret_cast<const uint32_t*>(weight->data), reinterpret_cast<uint32_t*>(wm), OC, KD, KH * KW, IC);
+        }
+        st = post_launch(ctx, "conv3d_depth_staging", 2);
+        if (st != TB200_OK)
+            return st;
+        tb200_tensor xin = view4(input, N * OD, IH, IW, KD * IC), wst = view4(weight, OC, KH, KW, KD * IC);
+        xin.data  = xm;
+        xin.bytes = x_bytes;
+        wst.data  = wm;
+        wst.bytes = (size_t)OC * KH * KW * KD * run;
+        tb200_tensor out4 = view4(output, N * OD, OH, OW, OC);
+        // (input and weights live in staging that the next call overwrites: nothing derived from them is cached)
+        st = conv2d_impl(ctx, &xin, &wst, bias, input_zp, weight_zp, pad + 2, stride + 1, dilation + 1, epilogue, &out4, nullptr,
+                         false, false);
+        if (st != TB200_OK && ctx->err.compare(0, 8, "OpConv2d") == 0)
+            ctx->err = "OpConv3d (as CONV2D): " + ctx->err;
+        return st;
+    }
     cache_note_write(ctx, output->data, output->bytes);
     ConvDev d;
     memset(&d, 0, sizeof(d));

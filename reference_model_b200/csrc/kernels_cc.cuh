@@ -1001,6 +1001,48 @@ struct ConvDepthDev
     int ID, OD, KD, pad_d, sd, dd;
 };
 
+// CONV3D as a CONV2D: the depth taps of every output depth gathered beside the channels,
+// out[n][od][pixel][kd][unit] = in[n][od * sd + kd * dd - pad_d][pixel][unit] (`fill` for a depth outside the input: the
+// input zero point, so that the tap contributes nothing), `units` elements of type U per pixel; and the weights
+// [OC][KD][KH][KW][units] re-ordered to [OC][KH][KW][KD][units].
+template <typename U>
+__global__ void conv3d_unfold_depth_kernel(const U* __restrict__ in, U* __restrict__ out, int N, int ID, int OD, int KD,
+                                           int64_t pixels, int units, int sd, int dd, int pad_d, U fill)
+{
+    const int64_t total = (int64_t)N * OD * pixels * KD * units;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int u   = (int)(i % units);
+        int64_t r     = i / units;
+        const int kd  = (int)(r % KD);
+        r /= KD;
+        const int64_t px = r % pixels;
+        r /= pixels;
+        const int od = (int)(r % OD);
+        const int n  = (int)(r / OD);
+        const int d  = od * sd + kd * dd - pad_d;
+        out[i]       = (d >= 0 && d < ID) ? in[(((int64_t)n * ID + d) * pixels + px) * units + u] : fill;
+    }
+}
+
+template <typename U>
+__global__ void conv3d_fold_weights_kernel(const U* __restrict__ w, U* __restrict__ out, int OC, int KD, int taps, int units)
+{
+    const int64_t total = (int64_t)OC * taps * KD * units;
+    const int64_t step  = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    {
+        const int u  = (int)(i % units);
+        int64_t r    = i / units;
+        const int kd = (int)(r % KD);
+        r /= KD;
+        const int t  = (int)(r % taps);
+        const int oc = (int)(r / taps);
+        out[i]       = w[(((int64_t)oc * KD + kd) * taps + t) * units + u];
+    }
+}
+
 template <typename TOut>
 __global__ void conv3d_direct_i8_kernel(const int8_t* __restrict__ in, const int8_t* __restrict__ w,
                                         const int32_t* __restrict__ bias, TOut* __restrict__ out, ConvDev p, ConvDepthDev z,

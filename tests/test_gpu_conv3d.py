@@ -29,6 +29,10 @@ INT_CASES = [
     (2, 4, 9, 9, 32, 64, 1, 3, 3, [0, 0, 1, 1, 1, 1], [1, 1, 1], [1, 1, 1], -128, 0, 64),       # depth 1: CONV2D over 8 slices
     (1, 3, 9, 9, 64, 32, 1, 1, 1, [0, 0, 0, 0, 0, 0], [1, 2, 2], [1, 1, 1], 3, 0, 32),          # depth 1, 1x1 stride 2
     (1, 6, 5, 5, 4, 8, 3, 1, 1, [2, 2, 0, 0, 0, 0], [1, 1, 1], [2, 1, 1], -5, 9, 8),            # depth taps only, depth padding
+    (2, 5, 10, 10, 32, 64, 3, 3, 3, [1, 1, 1, 1, 1, 1], [1, 1, 1], [1, 1, 1], -128, 0, 64),     # depth taps folded into K
+    (1, 6, 7, 9, 64, 32, 2, 1, 3, [1, 0, 0, 0, 1, 1], [1, 2, 1], [1, 1, 1], 5, 0, 32),          # folded, one-sided depth pad
+    (1, 5, 8, 8, 32, 32, 1, 3, 3, [0, 0, 1, 1, 1, 1], [2, 1, 1], [1, 1, 1], -128, 0, 1),        # depth 1 but depth stride 2
+    (3, 7, 6, 6, 16, 48, 4, 2, 2, [2, 1, 0, 0, 0, 0], [1, 1, 1], [2, 1, 1], -7, 0, 48),         # folded, depth dilation
 ]
 
 
@@ -46,15 +50,20 @@ def test_conv3d_int8(ctx, case):
     kernel = ctx.last_kernel()
     st, out = to.download()
     assert st == tb.Status.OK and np.array_equal(out, exp), kernel
+    # depth-1 kernels and kernels whose depth taps make whole 32-byte runs of K run as a CONV2D, the rest on the general kernel
     one_slice = KD == 1 and stride[0] == 1 and pad[0] == 0 and pad[1] == 0
-    assert (kernel != "conv3d_direct") == one_slice, kernel
+    assert (kernel == "conv3d_direct") == (not one_slice and (KD * IC) % 32 != 0), kernel
+    if case in (3, 6):
+        assert kernel.startswith("tc_"), kernel    # these two shapes qualify for the tensor-core kernels
     for t in (tx, tw, tbias, to):
         t.free()
 
 
 def test_conv3d_int8_rescale_clamp(ctx):
-    """The fused RESCALE + CLAMP epilogue on both routes (general kernel; depth-1 kernel through CONV2D's lean kernel)."""
-    for shape in ((2, 4, 6, 6, 32, 64, 3, 3, 3, [1, 1, 1, 1, 1, 1]), (2, 4, 14, 14, 64, 64, 1, 3, 3, [0, 0, 1, 1, 1, 1])):
+    """The fused RESCALE + CLAMP epilogue on the three routes (general kernel; depth taps folded into K; depth-1 kernel
+    through CONV2D's lean kernel)."""
+    for shape in ((2, 4, 6, 6, 8, 64, 3, 3, 3, [1, 1, 1, 1, 1, 1]), (2, 4, 6, 6, 32, 64, 3, 3, 3, [1, 1, 1, 1, 1, 1]),
+                  (2, 4, 14, 14, 64, 64, 1, 3, 3, [0, 0, 1, 1, 1, 1])):
         N, ID, IH, IW, IC, OC, KD, KH, KW, pad = shape
         r = util.rng(61)
         x = r.integers(-128, 128, size=(N, ID, IH, IW, IC), dtype=np.int8)
