@@ -57,6 +57,8 @@ def evaluate(graph, inputs, nthreads=8):
             status = max(status, st)
         elif op.kind == "MATMUL":
             out = orc.matmul(t[op.inputs[0]], t[op.inputs[1]], a["a_zp"], a["b_zp"], nthreads=nthreads)
+        elif op.kind == "IDENTITY":
+            out = np.asarray(t[op.inputs[0]])
         elif op.kind == "SLICE":
             sl = tuple(slice(b, b + s) for b, s in zip(a["start"], a["size"]))
             out = np.ascontiguousarray(np.asarray(t[op.inputs[0]])[sl])

@@ -67,6 +67,9 @@ class Graph:
                 oc, kh, kw, ic = self.meta[op.inputs[1]][1]
                 n, oh, ow, _ = self.meta[op.outputs[0]][1]
                 total += n * oh * ow * oc * kh * kw * ic
+            elif op.kind == "CONV3D":
+                oc, kd, kh, kw, ic = self.meta[op.inputs[1]][1]
+                total += int(np.prod(self.meta[op.outputs[0]][1])) * kd * kh * kw * ic
             elif op.kind == "TRANSPOSE_CONV2D":    # every input pixel stamps the whole kernel
                 oc, kh, kw, ic = self.meta[op.inputs[1]][1]
                 n, ih, iw, _ = self.meta[op.inputs[0]][1]
@@ -237,7 +240,7 @@ def fuse(graph):
     for i, op in enumerate(ops):
         if id(op) in skip:
             continue
-        if op.kind in ("CONV2D", "TRANSPOSE_CONV2D") and single(op.outputs[0]):
+        if op.kind in ("CONV2D", "CONV3D", "TRANSPOSE_CONV2D") and single(op.outputs[0]):
             r = cons[op.outputs[0]][0]
             if r.kind == "RESCALE" and r.attr["scale32"] and r.attr["rounding"] != "INEXACT_ROUND":
                 c = cons[r.outputs[0]][0] if single(r.outputs[0]) else None
@@ -305,7 +308,7 @@ class DeviceRunner:
         for kind, payload in self.steps:
             ops = payload if isinstance(payload, tuple) else (payload,)
             last = [o for o in ops if o is not None][-1]
-            if kind in ("SLICE", "RESHAPE"):
+            if kind in ("SLICE", "RESHAPE", "IDENTITY"):
                 continue
             for o in last.outputs:
                 produced.add(o)
@@ -346,6 +349,9 @@ class DeviceRunner:
                 if conv.kind == "TRANSPOSE_CONV2D":
                     ctx.transpose_conv2d(t[conv.inputs[0]], t[conv.inputs[1]], t[conv.inputs[2]], t[out], a["out_pad"],
                                          a["stride"], a["input_zp"], a["weight_zp"], epi)
+                elif conv.kind == "CONV3D":
+                    ctx.conv3d(t[conv.inputs[0]], t[conv.inputs[1]], t[conv.inputs[2]], t[out], a["pad"], a["stride"],
+                               a["dilation"], a["input_zp"], a["weight_zp"], epi)
                 else:
                     ctx.conv2d(t[conv.inputs[0]], t[conv.inputs[1]], t[conv.inputs[2]], t[out], a["pad"], a["stride"],
                                a["dilation"], a["input_zp"], a["weight_zp"], epi)
@@ -404,6 +410,9 @@ class DeviceRunner:
                                p.attr["input_zp"], p.attr["output_zp"])
             elif kind == "MATMUL":
                 ctx.matmul(t[p.inputs[0]], t[p.inputs[1]], t[p.outputs[0]], p.attr["a_zp"], p.attr["b_zp"])
+            elif kind == "IDENTITY":
+                if p.outputs[0] not in t:
+                    t[p.outputs[0]] = t[p.inputs[0]]
             elif kind == "SLICE":
                 if p.outputs[0] not in t:
                     t[p.outputs[0]] = t[p.inputs[0]].slice(p.attr["start"], p.attr["size"])

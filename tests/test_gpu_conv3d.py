@@ -132,3 +132,38 @@ def test_conv3d_errors(ctx):
     assert "zero point must be zero" in ctx.last_error()
     for t in (x, w, b, good, bad, wbad, xf, wf, bf, of):
         t.free()
+
+
+def test_conv3d_in_a_graph(ctx):
+    """CONV3D -> RESCALE -> CLAMP -> IDENTITY as a TOSA graph through the host mirror: the fuser hands RESCALE and CLAMP to
+    the convolution, fused = node by node = the oracle's node-by-node evaluation, bit for bit."""
+    from oracle import graph_eval
+    from reference_model_b200 import graph as G
+    r = util.rng(88)
+    g = G.Graph()
+    x = g.tensor("input", I8, (2, 4, 8, 8, 32))
+    g.inputs.append(x)
+    w = g.const("w", r.integers(-127, 128, size=(64, 3, 3, 3, 32), dtype=np.int8))
+    b = g.const("b", r.integers(-65536, 65536, size=64).astype(np.int32))
+    mult, shift = util.rescale_params(r, 64)
+    m, s = g.const("m", mult), g.const("s", shift)
+    acc = g.tensor("acc", I32, (2, 4, 8, 8, 64))
+    g.add("CONV3D", [x, w, b], [acc], pad=[1] * 6, stride=[1, 1, 1], dilation=[1, 1, 1], input_zp=-128, weight_zp=0)
+    q = g.tensor("q", I8, (2, 4, 8, 8, 64))
+    g.add("RESCALE", [acc, m, s], [q], input_zp=0, output_zp=-128, scale32=True, rounding="DOUBLE_ROUND", per_channel=True)
+    c = g.tensor("c", I8, (2, 4, 8, 8, 64))
+    g.add("CLAMP", [q], [c], min_val=-128, max_val=100)
+    y = g.tensor("y", I8, (2, 4, 8, 8, 64))
+    g.add("IDENTITY", [c], [y])
+    g.outputs.append(y)
+    xin = r.integers(-128, 128, size=(2, 4, 8, 8, 32), dtype=np.int8)
+    est, ref = graph_eval.evaluate(g, {"input": xin}, nthreads=orc.num_procs())
+    fused = G.DeviceRunner(ctx, g, fused=True)
+    assert [k for k, _ in fused.steps] == ["CONV_RESCALE_CLAMP", "IDENTITY"]
+    plain = G.DeviceRunner(ctx, g, fused=False)
+    for run in (fused, plain):
+        run.set_input(xin)
+        run.run()
+        st, out = run.output()
+        assert int(st) == est == orc.VALID
+        assert np.array_equal(out.astype(np.int32), ref["y"])
