@@ -50,15 +50,7 @@ constexpr int kXdAccBufs     = 2;     // accumulator buffers, each of kXdBatchRo
 constexpr int kXdStages      = kXdAccBufs * kXdBatchRows;    // input-row stages: one per accumulator row
 constexpr int kXdTmemCols    = kXdAccBufs * kXdBatchRows * kXdGroup;
 constexpr int kXdRing        = 3;     // expanded rows kept: a 3-row window moving down by one or two rows
-// CTAs the compiler leaves register room for on one SM (two CTAs of 256 tensor-memory columns fill an SM's 512)
-#ifndef TB200_XD_MIN_CTAS
-#define TB200_XD_MIN_CTAS 2
-#endif
-// output pixels of the window pass a thread works on at once (independent accumulation chains)
-#ifndef TB200_XD_UNROLL
-#define TB200_XD_UNROLL 1
-#endif
-constexpr int kXdUnroll = TB200_XD_UNROLL;
+constexpr int kXdMinCtas     = 2;     // CTAs the compiler leaves register room for on one SM (two CTAs of 256 tensor-memory columns fill its 512)
 
 struct XdParams
 {
@@ -194,7 +186,7 @@ __device__ __forceinline__ XdItem xd_decode(const XdParams& p, int item)
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kernel(const __grid_constant__ XdParams p)
+__global__ void __launch_bounds__(kXdThreads, kXdMinCtas) expand_dw_kernel(const __grid_constant__ XdParams p)
 {
     extern __shared__ uint8_t xd_smem_raw[];
     __shared__ __align__(8) uint64_t bar_a_full[kXdStages];        // TMA -> MMA: the input row has landed
@@ -498,7 +490,7 @@ __global__ void __launch_bounds__(kXdThreads, TB200_XD_MIN_CTAS) expand_dw_kerne
                 const int f0 = rows_in ? jf0 : nj, f1 = rows_in ? jf1 : nj;
                 for (int j = 0; j < f0; j++)
                     edge(j);
-#pragma unroll kXdUnroll
+#pragma unroll 1
                 for (int j = f0; j < f1; j++)
                 {
                     const uint32_t off = (uint32_t)(j * jstep);

@@ -95,6 +95,9 @@ SMALL_CASES = [
     # ends each on a short batch of rows
     (40, 7, 9, 32, 192, [1, 1, 1, 1], [1, 1], (0.0, 6.0), (0.0, 6.0), None, None),
     (48, 10, 12, 16, 128, [1, 0, 1, 0], [2, 2], None, (0.0, 6.0), None, None),
+    # padding as wide as the window: output rows and columns whose window lies wholly outside the image (bias only)
+    (2, 6, 6, 32, 64, [3, 3, 3, 3], [1, 1], (0.0, 6.0), (-6.0, 6.0), None, None),
+    (1, 8, 6, 32, 64, [4, 3, 3, 4], [2, 2], None, None, None, None),
 ]
 
 
