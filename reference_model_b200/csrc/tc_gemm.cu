@@ -1192,12 +1192,30 @@ bool make_plan(const TcProblem& q, int num_sms, TcPlan* plan, std::string* why)
         // A small layer (a shard of a batch, the last stages of a network) has fewer tiles than the GPU has SMs, and
         // each tile is a serial chain of load, MMAs and epilogue: narrower column blocks give every SM a tile and
         // shorten the chain.  Only for the fused int8 convolution, whose column blocks are independent.
-        if (q.epi == TC_EPI_RESCALE && !q.b_mn_major)
+        // Which width: the one with the smallest (rounds of CTAs) x (time of one tile), a tile costing its MMAs (about 190
+        // cycles each at 256 columns, 125 below, commits included) plus its epilogue (about 25 cycles per column).  Halving
+        // until every SM has a tile, as an earlier version did, went one step too far where the halved blocks needed a
+        // second round (3x3 256 -> 256 on 32 x 14 x 14: 196 tiles of 64 columns, 21 us, against 98 tiles of 128).
+        if (q.epi == TC_EPI_RESCALE && !q.b_mn_major && (block_n == 256 || block_n == 128) && q.OC % block_n == 0)
         {
             const int64_t tiles_m = (int64_t)k.tiles_x * k.tiles_y * k.tiles_n;
-            while ((block_n == 256 || block_n == 128) && q.OC % block_n == 0 &&
-                   tiles_m * (q.OC / block_n) * 4 < (int64_t)num_sms * 3)
-                block_n /= 2;
+            if (tiles_m * (q.OC / block_n) < (int64_t)num_sms)    // only layers that cannot give every SM a tile at the default width
+            {
+                const int64_t kmmas = ((int64_t)q.KH * q.KW * q.IC * es + 31) / 32;
+                int64_t best_cost   = 0;
+                int best            = block_n;
+                for (int bn = block_n; bn >= 64 && q.OC % bn == 0; bn /= 2)
+                {
+                    const int64_t rounds = (tiles_m * (q.OC / bn) + num_sms - 1) / num_sms;
+                    const int64_t cost   = rounds * (kmmas * (bn == 256 ? 190 : 125) + 25 * bn);
+                    if (bn == block_n || cost * 100 < best_cost * 97)    // a narrower block has to win by 3 %
+                    {
+                        best_cost = cost;
+                        best      = bn;
+                    }
+                }
+                block_n = best;
+            }
         }
     }
     if (q.b_mn_major && (block_n * es) % 128 != 0)
