@@ -796,14 +796,44 @@ __global__ void avg_pool_i8x4_kernel(const int8_t* __restrict__ in, int8_t* __re
         const int n  = (int)(r / p.OH);
         int32_t acc[4] = { 0, 0, 0, 0 };
         int count      = 0;
+        const int y0 = oy * p.sy - p.pad_t, x0 = ox * p.sx - p.pad_l;
+        if (y0 >= 0 && y0 + p.ky <= p.IH && x0 >= 0 && x0 + p.kx <= p.IW)
+        {
+            // the whole window lies inside the image: eight loads are issued before the first of them is used (a 7 x 7
+            // global pool took 49 memory latencies one after the other, 29 us whatever the batch)
+            const int taps       = p.ky * p.kx;
+            const int8_t* base   = in + (((int64_t)n * p.IH + y0) * p.IW + x0) * p.C + c4;
+            for (int t0 = 0; t0 < taps; t0 += 8)
+            {
+                uint32_t w[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                {
+                    const int t = min(t0 + j, taps - 1);
+                    const int ky = t / p.kx, kx = t - ky * p.kx;
+                    w[j] = __ldg(reinterpret_cast<const uint32_t*>(base + ((int64_t)ky * p.IW + kx) * p.C));
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    if (t0 + j < taps)
+                    {
+                        acc[0] += (int32_t)(int8_t)(w[j] & 0xff) - in_zp;
+                        acc[1] += (int32_t)(int8_t)((w[j] >> 8) & 0xff) - in_zp;
+                        acc[2] += (int32_t)(int8_t)((w[j] >> 16) & 0xff) - in_zp;
+                        acc[3] += (int32_t)(int8_t)(w[j] >> 24) - in_zp;
+                    }
+            }
+            count = taps;
+        }
+        else
         for (int ky = 0; ky < p.ky; ky++)
         {
-            const int y = oy * p.sy - p.pad_t + ky;
+            const int y = y0 + ky;
             if (y < 0 || y >= p.IH)
                 continue;
             for (int kx = 0; kx < p.kx; kx++)
             {
-                const int x = ox * p.sx - p.pad_l + kx;
+                const int x = x0 + kx;
                 if (x < 0 || x >= p.IW)
                     continue;
                 const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(in + (((int64_t)n * p.IH + y) * p.IW + x) * p.C + c4));
