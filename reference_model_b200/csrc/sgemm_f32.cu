@@ -3,7 +3,7 @@
 //
 // 128 x 128 output tile per 256-thread block, K stepped 16 at a time through double-buffered shared memory,
 // 8 x 8 accumulators per thread arranged as 2 x 2 groups of 4 x 4 so that shared-memory reads are 128-bit
-// and conflict-free.  A [N,H,C] is read along C (transposed into shared memory), B [N,C,W] along W.
+// and conflict-free, held as pairs of neighbouring columns for the packed multiply-add.  A [N,H,C] is read along C (transposed into shared memory), B [N,C,W] along W.
 #include <cuda_runtime.h>
 
 #include "common.h"
@@ -38,12 +38,14 @@ __global__ void __launch_bounds__(256, 2)
     const int a_row = tid / 2, a_k = (tid % 2) * 4;
     const int b_k = tid / 32, b_col = (tid % 32) * 4;
 
-    float acc[8][8];
+    // accumulators as pairs of neighbouring columns: one packed multiply-add (fma.rn.f32x2, two IEEE fp32 operations,
+    // the results fmaf gives) per pair
+    float2 acc[8][4];
 #pragma unroll
     for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 8; j++)
-            acc[i][j] = 0.f;
+        for (int j = 0; j < 4; j++)
+            acc[i][j] = make_float2(0.f, 0.f);
 
     float4 ra[2], rb[2];
     auto load_tiles = [&](int k0, int nbuf) {
@@ -116,13 +118,16 @@ __global__ void __launch_bounds__(256, 2)
             const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4 + 64]);
             const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4]);
             const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4 + 64]);
-            const float av[8] = { a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w };
-            const float bv[8] = { b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w };
+            const float av[8]  = { a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w };
+            const float2 bv[4] = { make_float2(b0.x, b0.y), make_float2(b0.z, b0.w), make_float2(b1.x, b1.y), make_float2(b1.z, b1.w) };
 #pragma unroll
             for (int i = 0; i < 8; i++)
+            {
+                const float2 a2 = make_float2(av[i], av[i]);
 #pragma unroll
-                for (int j = 0; j < 8; j++)
-                    acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                for (int j = 0; j < 4; j++)
+                    acc[i][j] = __ffma2_rn(a2, bv[j], acc[i][j]);
+            }
         }
         if (kt + 1 < nk)
         {
@@ -143,11 +148,14 @@ __global__ void __launch_bounds__(256, 2)
             const int gn = n0 + tx * 4 + jh * 64;
             float* o     = Cb + (int64_t)gm * W + gn;
             if (VEC && gn + 3 < W)
-                *reinterpret_cast<float4*>(o) = make_float4(acc[i][jh * 4], acc[i][jh * 4 + 1], acc[i][jh * 4 + 2], acc[i][jh * 4 + 3]);
+                *reinterpret_cast<float4*>(o) = make_float4(acc[i][jh * 2].x, acc[i][jh * 2].y, acc[i][jh * 2 + 1].x, acc[i][jh * 2 + 1].y);
             else
+            {
+                const float v[4] = { acc[i][jh * 2].x, acc[i][jh * 2].y, acc[i][jh * 2 + 1].x, acc[i][jh * 2 + 1].y };
                 for (int j = 0; j < 4; j++)
                     if (gn + j < W)
-                        o[j] = acc[i][jh * 4 + j];
+                        o[j] = v[j];
+            }
         }
     }
 }
