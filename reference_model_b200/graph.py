@@ -5,7 +5,7 @@ covers (reference_model/src/subgraph_traverser.cpp:222-514 initializeGraph, :827
 a list of TOSA operators over named tensors; constants arrive as CONST tensors; nodes are evaluated in order,
 outputs are allocated before a node runs.  Two things are added for the device:
 
-  * a fuser that collapses CONV2D -> RESCALE -> CLAMP chains and the five-node int8 residual join
+  * a fuser that collapses CONV2D / CONV3D / DEPTHWISE_CONV2D / TRANSPOSE_CONV2D -> RESCALE -> CLAMP chains and the five-node int8 residual join
     (RESCALE, RESCALE, ADD, RESCALE, CLAMP) when every intermediate has a single consumer
     (reference_model/src/tensor.h:92-100 exposes the same producer / consumer links), and
   * for floating-point graphs, CONV2D -> CLAMP and DEPTHWISE_CONV2D -> CLAMP pairs, and the head of an inverted-residual
@@ -240,7 +240,7 @@ def fuse(graph):
     for i, op in enumerate(ops):
         if id(op) in skip:
             continue
-        if op.kind in ("CONV2D", "CONV3D", "TRANSPOSE_CONV2D") and single(op.outputs[0]):
+        if op.kind in ("CONV2D", "CONV3D", "DEPTHWISE_CONV2D", "TRANSPOSE_CONV2D") and single(op.outputs[0]):
             r = cons[op.outputs[0]][0]
             if r.kind == "RESCALE" and r.attr["scale32"] and r.attr["rounding"] != "INEXACT_ROUND":
                 c = cons[r.outputs[0]][0] if single(r.outputs[0]) else None
@@ -352,6 +352,9 @@ class DeviceRunner:
                 elif conv.kind == "CONV3D":
                     ctx.conv3d(t[conv.inputs[0]], t[conv.inputs[1]], t[conv.inputs[2]], t[out], a["pad"], a["stride"],
                                a["dilation"], a["input_zp"], a["weight_zp"], epi)
+                elif conv.kind == "DEPTHWISE_CONV2D":
+                    ctx.depthwise_conv2d(t[conv.inputs[0]], t[conv.inputs[1]], t[conv.inputs[2]], t[out], a["pad"], a["stride"],
+                                         a["dilation"], a["input_zp"], a["weight_zp"], epi)
                 else:
                     ctx.conv2d(t[conv.inputs[0]], t[conv.inputs[1]], t[conv.inputs[2]], t[out], a["pad"], a["stride"],
                                a["dilation"], a["input_zp"], a["weight_zp"], epi)

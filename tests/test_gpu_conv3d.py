@@ -167,3 +167,39 @@ def test_conv3d_in_a_graph(ctx):
         st, out = run.output()
         assert int(st) == est == orc.VALID
         assert np.array_equal(out.astype(np.int32), ref["y"])
+
+
+def test_depthwise_rescale_clamp_in_a_graph(ctx):
+    """int8 DEPTHWISE_CONV2D -> RESCALE -> CLAMP (a quantized depthwise layer) as a TOSA graph: the fuser hands RESCALE and
+    CLAMP to the depthwise operator (one launch), fused = node by node = oracle, bit for bit."""
+    from oracle import graph_eval
+    from reference_model_b200 import graph as G
+    r = util.rng(89)
+    g = G.Graph()
+    x = g.tensor("input", I8, (2, 12, 12, 48))
+    g.inputs.append(x)
+    w = g.const("w", r.integers(-127, 128, size=(3, 3, 48, 1), dtype=np.int8))
+    b = g.const("b", r.integers(-4096, 4096, size=48).astype(np.int32))
+    mult, shift = util.rescale_params(r, 48)
+    m, s = g.const("m", mult), g.const("s", shift)
+    acc = g.tensor("acc", I32, (2, 6, 6, 48))
+    g.add("DEPTHWISE_CONV2D", [x, w, b], [acc], pad=[1, 0, 1, 0], stride=[2, 2], dilation=[1, 1], input_zp=-128, weight_zp=0)
+    q = g.tensor("q", I8, (2, 6, 6, 48))
+    g.add("RESCALE", [acc, m, s], [q], input_zp=0, output_zp=-128, scale32=True, rounding="DOUBLE_ROUND", per_channel=True)
+    c = g.tensor("c", I8, (2, 6, 6, 48))
+    g.add("CLAMP", [q], [c], min_val=-128, max_val=127)
+    g.outputs.append(c)
+    xin = r.integers(-128, 128, size=(2, 12, 12, 48), dtype=np.int8)
+    est, ref = graph_eval.evaluate(g, {"input": xin}, nthreads=4)
+    fused = G.DeviceRunner(ctx, g, fused=True)
+    assert [k for k, _ in fused.steps] == ["CONV_RESCALE_CLAMP"]
+    plain = G.DeviceRunner(ctx, g, fused=False)
+    for run in (fused, plain):
+        run.set_input(xin)
+        n0 = ctx.launch_count()
+        run.run()
+        launches = ctx.launch_count() - n0
+        st, out = run.output()
+        assert int(st) == est == orc.VALID
+        assert np.array_equal(out.astype(np.int32), ref["c"])
+        assert launches == (1 if run is fused else 3)
