@@ -2136,6 +2136,29 @@ extern "C" tb200_status tb200_depthwise_conv2d(tb200_ctx* ctx, const tb200_tenso
     d.in_zp = input_zp; d.w_zp = weight_zp; d.bias_n = bias->shape[0];
     fill_conv_dev(&d, epi);
     const int block = 256;
+    if (int_path && M == 1 && C % 16 == 0 && KH == 3 && KW == 3 && dilation[0] == 1 && dilation[1] == 1 && ctx->policy == 0 &&
+        ((reinterpret_cast<uintptr_t>(input->data) | reinterpret_cast<uintptr_t>(weight->data) |
+          reinterpret_cast<uintptr_t>(output->data)) & 15) == 0)
+    {
+        // sixteen channels per thread
+        const int grid   = grid_for(ctx, numel(output) / 16, block);
+        const int8_t* in = reinterpret_cast<const int8_t*>(input->data);
+        const int8_t* w  = reinterpret_cast<const int8_t*>(weight->data);
+        const int32_t* b = reinterpret_cast<const int32_t*>(bias->data);
+        switch (dtype_size(output->dtype))
+        {
+            case 1:
+                depthwise3x3_i8x16_kernel<int8_t><<<grid, block, 0, ctx->stream>>>(in, w, b, reinterpret_cast<int8_t*>(output->data), d, ctx->d_status);
+                break;
+            case 2:
+                depthwise3x3_i8x16_kernel<int16_t><<<grid, block, 0, ctx->stream>>>(in, w, b, reinterpret_cast<int16_t*>(output->data), d, ctx->d_status);
+                break;
+            default:
+                depthwise3x3_i8x16_kernel<int32_t><<<grid, block, 0, ctx->stream>>>(in, w, b, reinterpret_cast<int32_t*>(output->data), d, ctx->d_status);
+                break;
+        }
+        return post_launch(ctx, "depthwise3x3_i8x16");
+    }
     if (int_path)
     {
         const int grid    = grid_for(ctx, numel(output), block);
